@@ -1,0 +1,492 @@
+// CPU oracle (test infrastructure only, parity unpinned: see bits.hpp): the engine's step --
+// plan, forward pass, sampling, acceptance, KV compaction, test drafter -- on host memory,
+// for a Llama-style decoder described by the weight file's `meta` tensor.
+//
+// The reference hard-codes one architecture (engine/src/model.rs:6-20). Here its numeric
+// conventions are applied to a plain pre-norm decoder (RMSNorm, RoPE, grouped-query
+// attention, SwiGLU), every layer paged ("global", engine/src/engine/kv.rs). What is kept
+// from the reference, with the place it comes from:
+//   - the residual stream is fp32 and a layer's RMSNorm is folded into the next matmul:
+//     y = (W . x) * rsqrt(mean(x^2) + eps)                       kernels.metal:184-199,286
+//   - weights are bf16, or int8 with bf16 scales per group of consecutive k   :150-181
+//   - gate_up rows are interleaved (gate_0, up_0, gate_1, ...), act = silu(g) * u   :204-209
+//   - RoPE rotates interleaved pairs with a (cos, sin) table rounded to bf16   :725-736,
+//     engine.rs:392-409
+//   - K and V are rounded to bf16 before caching and that rounded value is what attention
+//     multiplies, for the step's own rows too                    kernels.metal:925-931
+//   - a row's K/V go to cache position p0 + row, its RoPE angle is that of lens + depth  :74-77
+//   - softmax in base 2 with scale * log2(e) folded into q       :1036, encode.rs:246
+// What differs, because the target device multiplies on bf16 tensor cores: a matmul's input
+// activations and the scaled, rotated q are rounded to bf16 first (the reference keeps them
+// fp32), and the softmax subtracts the row maximum (the reference's q/k norms bound its
+// scores, kernels.metal:803-806; a plain decoder's are unbounded). Sums inside matmuls and
+// attention have no pinned order in the reference (Metal's matrix units), so those results are
+// compared with a tolerance; everything integer is compared bit for bit.
+#pragma once
+#include <algorithm>
+#include <cmath>
+#include <memory>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "bits.hpp"
+#include "sampling.hpp"
+#include "vlt.hpp"
+
+namespace orc {
+
+struct ModelDesc {
+    uint32_t n_layers, d, n_heads, n_kv, hd, ffn, vocab, vocab_real;
+    float eps;
+    uint32_t page;
+    float attn_scale;
+    uint32_t qkv_w() const { return (n_heads + 2 * n_kv) * hd; }
+};
+
+struct Matrix {
+    const uint8_t* w = nullptr;
+    const uint16_t* scales = nullptr;  // int8 only: [m][k / group]
+    uint32_t m = 0, k = 0, group = 0;
+    bool int8 = false;
+};
+
+// engine/src/model.rs:81-103 `matrix`: bf16, or int8 with `<name>.scale`. The reference accepts
+// groups of 8..256; a whole row per scale (group = k) is accepted here as well.
+inline Matrix load_matrix(const VltFile& f, const std::string& name, uint32_t m, uint32_t k) {
+    const Tensor& t = f.tensor(name);
+    Matrix out;
+    out.m = m;
+    out.k = k;
+    if (t.dtype != I8) {
+        out.w = f.ptr(f.get(name, BF16, {m, k}));
+        return out;
+    }
+    out.w = f.ptr(f.get(name, I8, {m, k}));
+    const Tensor& s = f.tensor(name + ".scale");
+    const uint32_t groups = s.shape.size() > 1 ? s.shape[1] : 0;
+    const uint32_t group = k / std::max(groups, 1u);
+    if (group < 8 || (group & (group - 1)) || group * groups != k) throw std::runtime_error(name + ".scale: bad group count");
+    out.scales = reinterpret_cast<const uint16_t*>(f.ptr(f.get(name + ".scale", BF16, {m, groups})));
+    out.group = group;
+    out.int8 = true;
+    return out;
+}
+
+// acc[t][row] = sum_k W[row][k] * bf16(X[t][k]), int8 groups scaled as they are added.
+inline void matmul_raw(const Matrix& W, const float* X, uint32_t n, float* acc) {
+    std::vector<float> xb(size_t(n) * W.k);
+    for (size_t i = 0; i < xb.size(); i++) xb[i] = round_bf16(X[i]);
+#pragma omp parallel
+    {
+        std::vector<float> wr(W.k);
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < int64_t(W.m); r++) {
+            if (W.int8) {
+                const int8_t* q = reinterpret_cast<const int8_t*>(W.w) + uint64_t(r) * W.k;
+                for (uint32_t i = 0; i < W.k; i++) wr[i] = float(q[i]);
+            } else {
+                const uint16_t* b = reinterpret_cast<const uint16_t*>(W.w) + uint64_t(r) * W.k;
+                for (uint32_t i = 0; i < W.k; i++) wr[i] = bf16_to_f32(b[i]);
+            }
+            const uint32_t group = W.int8 ? W.group : W.k, ng = W.k / group;
+            for (uint32_t t = 0; t < n; t++) {
+                const float* x = xb.data() + size_t(t) * W.k;
+                float total = 0.0f;
+                for (uint32_t g = 0; g < ng; g++) {
+                    float a = 0.0f;
+#pragma omp simd reduction(+ : a)
+                    for (uint32_t i = g * group; i < (g + 1) * group; i++) a += wr[i] * x[i];
+                    total += W.int8 ? a * bf16_to_f32(W.scales[uint64_t(r) * ng + g]) : a;
+                }
+                acc[size_t(t) * W.m + r] = total;
+            }
+        }
+    }
+}
+
+// engine.rs:392-409 `rope_table`: theta = float32(pos) * frequency; cos, sin rounded to bf16.
+inline void rope_cs(uint32_t pos, float freq, float& c, float& s) {
+    const float theta = float(pos) * freq;
+    c = round_bf16(std::cos(theta));
+    s = round_bf16(std::sin(theta));
+}
+// kernels.metal:727-736 `norm_rope` without the norm: interleaved pairs, in place; cs [hd/2][2].
+inline void rope_pairs(float* v, uint32_t hd, const float* cs) {
+    for (uint32_t i = 0; i < hd / 2; i++) {
+        const float c = cs[2 * i], s = cs[2 * i + 1], a0 = v[2 * i], a1 = v[2 * i + 1];
+        v[2 * i] = c * a0 + s * a1;
+        v[2 * i + 1] = c * a1 - s * a0;
+    }
+}
+
+inline void inv_rms(const float* X, uint32_t n, uint32_t k, float eps, float* inv) {
+    for (uint32_t t = 0; t < n; t++) {
+        float ss = 0.0f;
+        for (uint32_t i = 0; i < k; i++) ss += X[size_t(t) * k + i] * X[size_t(t) * k + i];
+        inv[t] = 1.0f / std::sqrt(ss / float(k) + eps);
+    }
+}
+
+struct EngineConfig {
+    uint32_t max_seqs = 8, max_step_tokens = 512, max_chunk = 512, kv_tokens = 65536, max_seq_len = 131072,
+             max_head_rows = 64;
+};
+struct Sampling { float temperature = 0.0f, top_p = 1.0f; uint64_t seed = 0; };
+enum Rows : uint32_t { ROWS_NONE = 0, ROWS_LAST = 1, ROWS_ALL = 2 };
+constexpr uint32_t VERIFY_T = 8;
+
+struct PlanRun { uint32_t seq; std::vector<uint32_t> tokens; Rows head; bool verify; };
+struct Plan { uint32_t n = 0, n_head = 0, n_hidden = 0, n_runs = 0, n_tiles = 0; bool branches = false; };
+
+struct Seq { uint32_t len = 0; std::vector<uint32_t> pages; Sampling sampling; };
+
+struct Layer { Matrix qkv, o, gate_up, down; };
+
+// The drafter of the benchmark configurations: one decoder layer over
+// fc([tapped target hidden of position p-1 ; embedding of token p]) per position p, with its
+// own KV cache that shares the target's page table, proposing a chain of drafts one at a time.
+// Not in the reference (its drafter is a block drafter with a draft tree,
+// engine/src/engine/drafter.rs:278-447); it writes the same feed/tree interface
+// (kernels.metal:51-60) and reads the same tapped hidden states (kernels.metal:133-148).
+struct Drafter {
+    VltFile file;
+    Matrix fc;  // [d][2 d]
+    Layer layer;
+    Matrix head;  // [v][d]
+    std::vector<uint32_t> vocab;
+    std::vector<uint16_t> k_cache, v_cache;  // [n_pages][n_kv][page][hd]
+    std::vector<float> carry;                // [max_seqs][d]: the tap of each slot's last position
+};
+
+struct Engine {
+    VltFile file;
+    ModelDesc md{};
+    EngineConfig cfg;
+    const uint16_t* embed = nullptr;
+    Matrix head;
+    std::vector<Layer> layers;
+    std::vector<float> rope;  // [pos][hd / 2][cos, sin]
+    // KV pool: [layer][page][n_kv][page_tok][hd] (kernels.metal:692-711), and the page table.
+    std::vector<uint16_t> k_cache, v_cache;
+    std::vector<uint32_t> page_table, free_pages;
+    uint32_t n_pages = 0, max_pages = 0;
+    std::vector<std::optional<Seq>> seqs;
+    // Per-slot state that lives on the GPU in the reference (engine/buffers.rs:42-55).
+    std::vector<uint32_t> lens, feed, tree, path, path_len, on_path, trace, trace_len;
+    std::vector<GenState> gen;
+    // One step's inputs and outputs (engine/buffers.rs:120-156).
+    std::vector<uint32_t> tokens, tin, vis, head_rows, hidden_rows, out_ids, tiles, emitted, meta;
+    std::vector<SampleRow> sample_rows;
+    std::vector<RunIn> runs;
+    std::vector<float> logits, hidden_out, taps;  // taps: bf16(rms_norm(last layer's output)) as fp32, [n][d]
+    ReplayArgs replay{0, 0, 0.0f, 0};
+    std::unique_ptr<Drafter> drafter;
+    std::vector<float> draft_logits;  // the drafter's last pass, [rows][v]
+
+    Engine(const std::string& file_path, const EngineConfig& c) : file(VltFile::load(file_path)), cfg(c) {
+        std::vector<float> m = file.f32s("meta");
+        if (m.size() < 14 || m[0] != 1.0f || m[1] != 0.0f) throw std::runtime_error(file_path + ": meta is not a version-1 llama descriptor");
+        md.n_layers = uint32_t(m[2]); md.d = uint32_t(m[3]); md.n_heads = uint32_t(m[4]); md.n_kv = uint32_t(m[5]);
+        md.hd = uint32_t(m[6]); md.ffn = uint32_t(m[7]); md.vocab = uint32_t(m[8]); md.vocab_real = uint32_t(m[9]);
+        md.eps = m[10]; md.page = uint32_t(m[11]); md.attn_scale = m[13];
+        embed = reinterpret_cast<const uint16_t*>(file.ptr(file.get("embed", BF16, {md.vocab, md.d})));
+        // engine/src/model.rs:139-140: the head is the embedding unless the file has one.
+        if (file.has("head")) head = load_matrix(file, "head", md.vocab, md.d);
+        else { head.w = reinterpret_cast<const uint8_t*>(embed); head.m = md.vocab; head.k = md.d; }
+        for (uint32_t i = 0; i < md.n_layers; i++) {
+            char nm[32];
+            auto name = [&](const char* k) { std::snprintf(nm, sizeof nm, "L%02u.%s", i, k); return std::string(nm); };
+            Layer l;
+            l.qkv = load_matrix(file, name("qkv"), md.qkv_w(), md.d);
+            l.o = load_matrix(file, name("o"), md.d, md.n_heads * md.hd);
+            l.gate_up = load_matrix(file, name("gate_up"), 2 * md.ffn, md.d);
+            l.down = load_matrix(file, name("down"), md.d, md.ffn);
+            layers.push_back(l);
+        }
+        // engine.rs:392-421 `rope_table`: theta = float32(pos) * freq, cos and sin rounded to bf16.
+        std::vector<float> freq = file.f32s("rope_freq");
+        if (freq.size() != md.hd / 2) throw std::runtime_error("rope_freq: expected head_dim / 2 entries");
+        const uint32_t npos = cfg.max_seq_len + FEED_W;
+        rope.resize(size_t(npos) * md.hd);
+        for (uint32_t p = 0; p < npos; p++)
+            for (uint32_t i = 0; i < md.hd / 2; i++)
+                rope_cs(p, freq[i], rope[(size_t(p) * (md.hd / 2) + i) * 2], rope[(size_t(p) * (md.hd / 2) + i) * 2 + 1]);
+        // kv.rs:23-48 `KvCache::new`.
+        n_pages = (cfg.kv_tokens + md.page - 1) / md.page;
+        max_pages = (cfg.max_seq_len + md.page - 1) / md.page;
+        const size_t kv = size_t(md.n_layers) * n_pages * md.n_kv * md.page * md.hd;
+        k_cache.assign(kv, 0);
+        v_cache.assign(kv, 0);
+        page_table.assign(size_t(cfg.max_seqs) * max_pages, 0);
+        for (uint32_t i = n_pages; i-- > 0;) free_pages.push_back(i);
+        seqs.resize(cfg.max_seqs);
+        lens.assign(cfg.max_seqs, 0);
+        feed.assign(cfg.max_seqs * FEED_W, 0);
+        tree.resize(cfg.max_seqs * FEED_W);
+        for (uint32_t i = 0; i < tree.size(); i++) tree[i] = chain_node(i % FEED_W);  // buffers.rs:112-113
+        gen.assign(cfg.max_seqs, GenState{0xffffffffu, 0, 0, 0, {0}});
+        path.assign(cfg.max_seqs * FEED_W, 0);
+        path_len.assign(cfg.max_seqs, 0);
+        trace.assign(size_t(cfg.max_seqs) * cfg.max_seq_len, 0);
+        trace_len.assign(cfg.max_seqs, 0);
+    }
+
+    // ---- engine.rs:259-303
+    uint32_t new_seq() {
+        for (uint32_t s = 0; s < seqs.size(); s++)
+            if (!seqs[s]) {
+                seqs[s] = Seq{};
+                lens[s] = 0;
+                trace_len[s] = 0;
+                gen[s] = GenState{0xffffffffu, 0, 0, 0, {0}};
+                return s;
+            }
+        throw std::runtime_error("no free sequence slot");
+    }
+    void free_seq(uint32_t s) {
+        if (s < seqs.size() && seqs[s]) {
+            for (size_t i = seqs[s]->pages.size(); i-- > 0;) free_pages.push_back(seqs[s]->pages[i]);  // kv.rs:60-62
+            seqs[s].reset();
+        }
+    }
+    Seq& seq(uint32_t s) {
+        if (s >= seqs.size() || !seqs[s]) throw std::runtime_error("unknown sequence");
+        return *seqs[s];
+    }
+    // kv.rs:51-58 `reserve`.
+    void reserve(uint32_t slot, std::vector<uint32_t>& pages, uint32_t len) {
+        while (pages.size() * md.page < len) {
+            if (free_pages.empty()) throw std::runtime_error("global KV pool exhausted");
+            uint32_t page = free_pages.back();
+            free_pages.pop_back();
+            page_table[size_t(slot) * max_pages + pages.size()] = page;
+            pages.push_back(page);
+        }
+    }
+    // hooks.rs:28-36 `bench_fill`.
+    void bench_fill(uint32_t s, uint32_t len) {
+        Seq& q = seq(s);
+        q.len += len;
+        lens[s] = q.len;
+        reserve(s, q.pages, q.len);
+    }
+
+    // ---- plan.rs:47-150 `plan` (the attention split heuristics are device-specific and left out).
+    Plan plan(const std::vector<PlanRun>& in, Rows hidden) {
+        uint32_t n = 0;
+        for (auto& r : in) n += uint32_t(r.tokens.size());
+        if (n == 0 || n > cfg.max_step_tokens) throw std::runtime_error("step has " + std::to_string(n) + " tokens (max " + std::to_string(cfg.max_step_tokens) + ")");
+        tokens.clear(); tin.clear(); vis.clear(); head_rows.clear(); hidden_rows.clear(); sample_rows.clear(); tiles.clear(); runs.clear();
+        Plan p;
+        for (size_t ri = 0; ri < in.size(); ri++) {
+            const PlanRun& run = in[ri];
+            const uint32_t id = run.seq, count = uint32_t(run.tokens.size());
+            if (count == 0 || count > cfg.max_chunk) throw std::runtime_error(std::to_string(count) + " tokens for one sequence in a step (max_chunk " + std::to_string(cfg.max_chunk) + ")");
+            for (uint32_t t : run.tokens)
+                if (t >= FEED_ROW && t - FEED_ROW >= FEED_W) throw std::runtime_error("only 16 GPU-fed tokens per slot");
+            for (size_t j = 0; j < ri; j++)
+                if (in[j].seq == id) throw std::runtime_error("a sequence appears twice in one step");
+            Seq& s = seq(id);
+            const uint32_t new_len = s.len + count;
+            if (new_len > cfg.max_seq_len) throw std::runtime_error("sequence would reach " + std::to_string(new_len) + " tokens (max " + std::to_string(cfg.max_seq_len) + ")");
+            reserve(id, s.pages, new_len);
+            const uint32_t first_row = uint32_t(tokens.size());
+            tokens.insert(tokens.end(), run.tokens.begin(), run.tokens.end());
+            for (uint32_t row = 0; row < count; row++) {
+                tin.push_back(id);
+                tin.push_back(row);
+                vis.push_back(0xffffffffu >> (31 - row % 8));
+            }
+            auto rows = [&](Rows r, std::vector<uint32_t>& v) {
+                if (r == ROWS_LAST) v.push_back(first_row + count - 1);
+                if (r == ROWS_ALL) for (uint32_t x = first_row; x < first_row + count; x++) v.push_back(x);
+            };
+            const uint32_t first_head = uint32_t(head_rows.size());
+            rows(run.verify ? ROWS_ALL : run.head, head_rows);
+            rows(hidden, hidden_rows);
+            for (uint32_t h = first_head; h < head_rows.size(); h++)  // engine.rs:123-138 `row_of`
+                sample_rows.push_back(SampleRow{uint32_t(s.sampling.seed), uint32_t(s.sampling.seed >> 32), 0, s.sampling.temperature, s.sampling.top_p, head_rows[h]});
+            runs.push_back(RunIn{id, first_row, count, first_head, uint32_t(head_rows.size()) - first_head, run.verify ? 1u : 0u});
+            for (uint32_t i = 0; i < count; i += 8) {
+                tiles.push_back(first_row + i);
+                tiles.push_back(std::min(count - i, 8u));
+            }
+            p.branches = p.branches || (run.verify && count > 2);
+            s.len = new_len;
+        }
+        if (head_rows.size() > cfg.max_head_rows) throw std::runtime_error(std::to_string(head_rows.size()) + " head rows (max " + std::to_string(cfg.max_head_rows) + ")");
+        p.n = n;
+        p.n_head = uint32_t(head_rows.size());
+        p.n_hidden = uint32_t(hidden_rows.size());
+        p.n_runs = uint32_t(in.size());
+        p.n_tiles = uint32_t(tiles.size() / 2);
+        return p;
+    }
+
+    // Where kv head g's row for cache position pos starts (kernels.metal:704-711, global layers).
+    size_t kv_row(uint32_t layer, uint32_t slot, uint32_t g, uint32_t pos) const {
+        const uint32_t page = page_table[size_t(slot) * max_pages + pos / md.page];
+        return ((size_t(layer) * n_pages + page) * md.n_kv + g) * md.page * md.hd + size_t(pos % md.page) * md.hd;
+    }
+
+    void rope_head(float* v, uint32_t pos) const { rope_pairs(v, md.hd, rope.data() + size_t(pos) * md.hd); }
+
+    // One decoder layer's attention over the step, K/V written first (kernels.metal:749-801
+    // `qkv_post`), then every query tile against the cache (kernels.metal:891-1167).
+    void attention(uint32_t layer, uint16_t* kc, uint16_t* vc, const float* qkv, uint32_t n, uint32_t n_tiles, float* out) {
+        const uint32_t hd = md.hd, G = md.n_heads / md.n_kv, QW = md.qkv_w();
+        const uint32_t koff = md.n_heads * hd, voff = koff + md.n_kv * hd;
+        for (uint32_t t = 0; t < n; t++) {
+            const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1];
+            const uint32_t cpos = meta[2 * (t - row) + 1] + row;  // kernels.metal:74-77 `cache_pos`
+            for (uint32_t g = 0; g < md.n_kv; g++) {
+                std::vector<float> k(qkv + size_t(t) * QW + koff + g * hd, qkv + size_t(t) * QW + koff + (g + 1) * hd);
+                rope_head(k.data(), pos);
+                const size_t at = kv_row(layer, slot, g, cpos);
+                for (uint32_t d = 0; d < hd; d++) {
+                    kc[at + d] = f32_to_bf16(k[d]);
+                    vc[at + d] = f32_to_bf16(qkv[size_t(t) * QW + voff + g * hd + d]);
+                }
+            }
+        }
+        const float sl2 = md.attn_scale * LOG2E;
+#pragma omp parallel for schedule(dynamic) collapse(2)
+        for (int64_t ti = 0; ti < int64_t(n_tiles); ti++) {
+            for (int64_t h = 0; h < int64_t(md.n_heads); h++) {
+                const uint32_t t0 = tiles[2 * ti], T = tiles[2 * ti + 1], g = uint32_t(h) / G;
+                const uint32_t slot = meta[2 * t0], p0 = meta[2 * t0 + 1];
+                std::vector<float> sc(p0 + T), q(hd), o(hd);
+                for (uint32_t i = 0; i < T; i++) {
+                    const uint32_t t = t0 + i;
+                    for (uint32_t d = 0; d < hd; d++) q[d] = qkv[size_t(t) * QW + h * hd + d];
+                    rope_head(q.data(), meta[2 * t + 1]);
+                    for (uint32_t d = 0; d < hd; d++) q[d] = round_bf16(q[d] * sl2);
+                    float mx = -INFINITY;
+                    for (uint32_t kp = 0; kp < p0 + T; kp++) {
+                        const bool seen = kp < p0 || ((vis[t] >> (kp - p0)) & 1u);
+                        if (!seen) { sc[kp] = -INFINITY; continue; }
+                        const uint16_t* kr = kc + kv_row(layer, slot, g, kp);
+                        float a = 0.0f;
+#pragma omp simd reduction(+ : a)
+                        for (uint32_t d = 0; d < hd; d++) a += q[d] * bf16_to_f32(kr[d]);
+                        sc[kp] = a;
+                        mx = std::max(mx, a);
+                    }
+                    float l = 0.0f;
+                    std::fill(o.begin(), o.end(), 0.0f);
+                    for (uint32_t kp = 0; kp < p0 + T; kp++) {
+                        if (sc[kp] == -INFINITY) continue;
+                        const float pz = std::exp2(sc[kp] - mx);
+                        l += pz;
+                        const uint16_t* vr = vc + kv_row(layer, slot, g, kp);
+                        for (uint32_t d = 0; d < hd; d++) o[d] += pz * bf16_to_f32(vr[d]);
+                    }
+                    for (uint32_t d = 0; d < hd; d++) out[size_t(t) * md.n_heads * hd + h * hd + d] = o[d] / l;
+                }
+            }
+        }
+    }
+
+    // One decoder layer on x [n][d] in place: encode.rs:142-192 with the plain decoder's
+    // parameters (scales and lambdas 1, no MUDD, gates, XSA or value embeddings).
+    void layer_forward(const Layer& L, uint32_t li, uint16_t* kc, uint16_t* vc, float* x, uint32_t n, uint32_t n_tiles) {
+        const uint32_t d = md.d, QW = md.qkv_w();
+        std::vector<float> inv(n), qkv(size_t(n) * QW), attn(size_t(n) * md.n_heads * md.hd), acc(size_t(n) * std::max(2 * md.ffn, QW)), act(size_t(n) * md.ffn);
+        inv_rms(x, n, d, md.eps, inv.data());
+        matmul_raw(L.qkv, x, n, qkv.data());
+        for (uint32_t t = 0; t < n; t++)
+            for (uint32_t j = 0; j < QW; j++) qkv[size_t(t) * QW + j] *= inv[t];  // EPI_NORM
+        attention(li, kc, vc, qkv.data(), n, n_tiles, attn.data());
+        matmul_raw(L.o, attn.data(), n, acc.data());
+        for (size_t i = 0; i < size_t(n) * d; i++) x[i] += acc[i];  // EPI_RESID: mixed
+        inv_rms(x, n, d, md.eps, inv.data());
+        matmul_raw(L.gate_up, x, n, acc.data());
+        for (uint32_t t = 0; t < n; t++)
+            for (uint32_t j = 0; j < md.ffn; j++) {  // EPI_SWIGLU, kernels.metal:204-209
+                const float g = acc[size_t(t) * 2 * md.ffn + 2 * j] * inv[t], u = acc[size_t(t) * 2 * md.ffn + 2 * j + 1] * inv[t];
+                act[size_t(t) * md.ffn + j] = g * (1.0f / (1.0f + std::exp(-g))) * u;
+            }
+        matmul_raw(L.down, act.data(), n, acc.data());
+        for (size_t i = 0; i < size_t(n) * d; i++) x[i] += acc[i];
+    }
+
+    // encode.rs:99-105 `encode_forward` + :383-412 `encode_tail`.
+    void forward(const Plan& p) {
+        const uint32_t n = p.n, d = md.d;
+        meta.assign(2 * n, 0);
+        std::vector<float> x(size_t(n) * d);
+        for (uint32_t t = 0; t < n; t++) {  // kernels.metal:82-114 `embed` (a plain decoder: no norm)
+            const uint32_t slot = tin[2 * t];
+            uint32_t tok = tokens[t], depth = tin[2 * t + 1];
+            if (tok >= FEED_ROW) {
+                const uint32_t i = tok - FEED_ROW, node = tree[slot * FEED_W + i];
+                tok = feed[slot * FEED_W + i];
+                depth = node_depth(node);
+                vis[t] = node_sees(node);
+            }
+            tokens[t] = tok;
+            meta[2 * t] = slot;
+            meta[2 * t + 1] = lens[slot] + depth;
+            for (uint32_t i = 0; i < d; i++) x[size_t(t) * d + i] = bf16_to_f32(embed[size_t(tok) * d + i]);
+        }
+        for (uint32_t li = 0; li < md.n_layers; li++)
+            layer_forward(layers[li], li, k_cache.data(), v_cache.data(), x.data(), n, p.n_tiles);
+        std::vector<float> inv(n);
+        inv_rms(x.data(), n, d, md.eps, inv.data());
+        taps.resize(size_t(n) * d);  // kernels.metal:133-148 `tap_rows`
+        for (uint32_t t = 0; t < n; t++)
+            for (uint32_t i = 0; i < d; i++) taps[size_t(t) * d + i] = round_bf16(x[size_t(t) * d + i] * inv[t]);
+        hidden_out.resize(size_t(p.n_hidden) * d);
+        for (uint32_t r = 0; r < p.n_hidden; r++)
+            for (uint32_t i = 0; i < d; i++) hidden_out[size_t(r) * d + i] = x[size_t(hidden_rows[r]) * d + i] * inv[hidden_rows[r]];
+        out_ids.assign(p.n_head, 0);
+        if (p.n_head) {
+            std::vector<float> hx(size_t(p.n_head) * d);
+            for (uint32_t r = 0; r < p.n_head; r++) std::copy_n(x.data() + size_t(head_rows[r]) * d, d, hx.data() + size_t(r) * d);
+            logits.resize(size_t(p.n_head) * md.vocab);
+            matmul_raw(head, hx.data(), p.n_head, logits.data());
+            for (uint32_t r = 0; r < p.n_head; r++)
+                for (uint32_t j = 0; j < md.vocab; j++) {
+                    float& l = logits[size_t(r) * md.vocab + j];
+                    l = j < md.vocab_real ? l * inv[head_rows[r]] : -INFINITY;
+                }
+#pragma omp parallel for schedule(dynamic)
+            for (int64_t r = 0; r < int64_t(p.n_head); r++) {
+                const SampleRow& sr = sample_rows[r];
+                const uint32_t pos = sr.tok == NO_TOK ? sr.pos : meta[2 * sr.tok + 1] + 1;
+                out_ids[r] = sample_row(logits.data() + size_t(r) * md.vocab, md.vocab, sr, pos);
+            }
+        }
+        emitted.assign(p.n_runs, 0);
+        on_path.assign(n, 0);
+        for (uint32_t r = 0; r < p.n_runs; r++)
+            accept_run(r, runs.data(), tokens.data(), out_ids.data(), lens.data(), feed.data(), gen.data(), emitted.data(), tree.data(), path.data(), path_len.data(), on_path.data());
+        if (p.branches) kv_compact(p, k_cache.data(), v_cache.data(), md.n_layers);
+    }
+
+    // kernels.metal:1663-1693 `kv_compact` over `nl` layers of a cache with the pool's layout.
+    void kv_compact(const Plan& p, uint16_t* kc, uint16_t* vc, uint32_t nl) {
+        for (uint32_t r = 0; r < p.n_runs; r++) {
+            const uint32_t k = path_len[r], slot = runs[r].slot, p0 = lens[slot] - k;
+            for (uint32_t l = 0; l < nl; l++)
+                for (uint32_t g = 0; g < md.n_kv; g++)
+                    for (uint32_t j = 1; j < k; j++) {
+                        const uint32_t from = path[r * FEED_W + j];
+                        if (from == j) continue;
+                        const size_t src = kv_row(l, slot, g, p0 + from), dst = kv_row(l, slot, g, p0 + j);
+                        std::copy_n(kc + src, md.hd, kc + dst);
+                        std::copy_n(vc + src, md.hd, vc + dst);
+                    }
+        }
+    }
+
+    // encode.rs:439-451 `encode_replay`.
+    void run_replay(const Plan& p) {
+        for (uint32_t r = 0; r < p.n_runs; r++)
+            replay_draft_run(r, runs.data(), lens.data(), feed.data(), trace.data(), trace_len.data(), replay, tree.data());
+    }
+};
+
+}  // namespace orc
