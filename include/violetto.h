@@ -1,0 +1,212 @@
+/* C ABI of the B200 back end for Silicon Violetto's speculative-decoding decode step.
+ *
+ * The reference is a Rust crate whose public API is `violetto::{Engine, Generator, ...}`
+ * (engine/src/lib.rs:6-10) over Metal. This library offers the same calls over CUDA, one
+ * `extern "C"` function per method, so that a thin Rust shim can re-export the crate's API
+ * unchanged. Each declaration cites the reference item it replaces (paths are relative to
+ * the reference repository).
+ *
+ * Conventions. Every fallible call returns 0 on success and non-zero on failure;
+ * `vlt_last_error()` then gives the message (the reference returns `Result<_, String>`).
+ * Handles are opaque and, like the reference's `Engine`, thread-affine: use an engine and its
+ * generator from the thread that created them (cli/src/serve.rs:100). Output buffers are
+ * owned by the caller and passed with their capacities. All arithmetic runs on the GPU
+ * selected by `device_ordinal`; there is no CPU path, and creating an engine without a
+ * usable CUDA device fails unless `VLT_FLAG_HOST_ONLY` is set, in which case the engine plans
+ * steps (page tables, step layout) but refuses to run them.
+ */
+#ifndef VIOLETTO_B200_H
+#define VIOLETTO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct VltEngine VltEngine;
+typedef struct VltGenerator VltGenerator;
+
+/* engine/src/engine/kernels.rs:14-29 */
+#define VLT_FEED_ROW 0xffff0000u /* input token VLT_FEED_ROW + i: the slot's GPU-fed token i */
+#define VLT_FEED_W 16u
+#define VLT_NO_TOK 0xffffffffu
+#define VLT_VERIFY_T 8u /* rows per run that one attention tile takes */
+#define VLT_MAX_STOP 8u
+
+/* engine/src/engine.rs:31-57 `EngineConfig`; device_ordinal and flags are new. */
+typedef struct {
+    uint32_t max_seqs;         /* sequence slots */
+    uint32_t max_step_tokens;  /* tokens per step, all sequences together */
+    uint32_t max_chunk;        /* tokens one sequence may add in one step */
+    uint32_t global_kv_tokens; /* capacity of the paged KV pool, in tokens */
+    uint32_t max_seq_len;
+    uint32_t max_head_rows;    /* rows that can go through the head in one step */
+    int32_t device_ordinal;    /* CUDA device; one engine per GPU makes a replica */
+    uint32_t flags;            /* VLT_FLAG_* */
+} VltEngineConfig;
+#define VLT_FLAG_HOST_ONLY 1u /* plan only: no device memory, steps cannot run */
+
+/* engine/src/engine.rs:59-95 `Tuning`. The reference's Apple-GPU knobs (gpu_cores,
+ * splitk_target, decode_split, verify_ki) are replaced by B200 ones; the rows policy is kept. 0 = default. */
+typedef struct {
+    uint32_t spec_tokens;       /* default 32 */
+    uint32_t spec_tokens_short; /* default 8 */
+    uint32_t spec_kv;           /* default 24576 */
+    uint32_t spec_rows_long;    /* default 4 */
+    uint32_t spec_policy_off;   /* 1: rows as requested (the reference's spec_tokens = 0) */
+    uint32_t sm_count;          /* SMs to size grids for; 0: the device's */
+    uint32_t attn_keys_per_cta; /* keys one attention CTA takes; 0: sized to fill the SMs */
+    uint32_t gemm_min_rows;     /* steps with at least this many tokens use the tensor-core GEMM; 0: default */
+    uint32_t plain_attention;   /* 1: the scalar attention kernel (cross-check only) */
+    uint32_t use_graphs;        /* 1: replay decode steps as CUDA graphs */
+} VltTuning;
+
+/* engine/src/engine.rs:100-138 `Sampling`. */
+typedef struct {
+    float temperature; /* 0: argmax */
+    float top_p;       /* (0, 1] */
+    uint64_t seed;
+} VltSampling;
+
+/* engine/src/engine.rs:140-172 `Rows`, `Run`, `StepOptions`, `StepOutput`. */
+enum { VLT_ROWS_NONE = 0, VLT_ROWS_LAST = 1, VLT_ROWS_ALL = 2 };
+typedef struct {
+    uint32_t seq;
+    const uint32_t* tokens;
+    uint32_t n_tokens;
+} VltRun;
+typedef struct {
+    uint32_t head;   /* VLT_ROWS_* */
+    uint32_t hidden; /* VLT_ROWS_* */
+    uint32_t read_logits;
+    uint32_t read_taps;
+} VltStepOptions;
+typedef struct {
+    uint32_t* ids; /* the token each head row got */
+    uint32_t ids_cap, n_ids;
+    float* logits; /* [n_ids][vocab] if read_logits */
+    uint64_t logits_cap;
+    float* hidden; /* [n_hidden][d_model]: final normed hidden state per hidden row */
+    uint64_t hidden_cap;
+    uint32_t n_hidden;
+    uint16_t* taps; /* [n_tokens][d_model] bf16(rms_norm(last layer's output)) if read_taps */
+    uint64_t taps_cap;
+    double gpu_seconds;
+} VltStepOutput;
+
+/* New: what the weight file's `meta` tensor describes (the reference hard-codes its model,
+ * engine/src/model.rs:6-20). */
+typedef struct {
+    uint32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn, vocab, vocab_real, page_size;
+    float rms_eps, attn_scale;
+    uint32_t int8; /* 1 if the layer matrices are int8 */
+} VltModelDesc;
+
+const char* vlt_last_error(void);
+
+/* Engine::new, engine/src/engine.rs:221-250. `tuning` may be NULL. */
+int vlt_engine_new(const char* weights_path, const VltEngineConfig* cfg, const VltTuning* tuning, VltEngine** out);
+/* Drop for Engine. */
+void vlt_engine_free(VltEngine* e);
+/* Engine::device_name, engine.rs:252-254. */
+int vlt_device_name(VltEngine* e, char* buf, size_t cap);
+int vlt_model_desc(VltEngine* e, VltModelDesc* out);
+/* Engine::new_seq / free_seq / seq_len / set_sampling, engine.rs:259-307. */
+int vlt_seq_new(VltEngine* e, uint32_t* seq);
+void vlt_seq_free(VltEngine* e, uint32_t seq);
+uint32_t vlt_seq_len(VltEngine* e, uint32_t seq);
+int vlt_seq_set_sampling(VltEngine* e, uint32_t seq, const VltSampling* s);
+/* Engine::step, engine.rs:310-314: one synchronous step of CPU-fed runs. */
+int vlt_step(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOptions* opts, VltStepOutput* out);
+/* Engine::set_taps / load_drafter / has_drafter, engine.rs:381-389, engine/drafter.rs:250-262.
+ * The plain decoder taps its last layer only, so set_taps takes a switch. */
+int vlt_set_taps(VltEngine* e, uint32_t on);
+int vlt_load_drafter(VltEngine* e, const char* path);
+int vlt_has_drafter(VltEngine* e);
+
+/* Hooks, engine/src/engine/hooks.rs. */
+/* bench_fill, hooks.rs:28-36: advance a sequence without computing it. `seed` != 0 also fills
+ * the new positions' K/V with small pseudo-random values, so that later steps read finite numbers. */
+int vlt_bench_fill(VltEngine* e, uint32_t seq, uint32_t len, uint32_t seed);
+/* sample_logits, hooks.rs:41-54: rows of logits [n][vocab] (NULL: the previous call's) through
+ * the sampler, each row with its own settings and drawn-token position. */
+int vlt_sample_logits(VltEngine* e, const float* logits, const VltSampling* rows, const uint32_t* pos, uint32_t n, uint32_t* out);
+/* set_profile_skip, hooks.rs:9-26: leave kernel groups out (results are then wrong). */
+enum { VLT_SKIP_QKV = 1, VLT_SKIP_POST = 2, VLT_SKIP_ATTN = 4, VLT_SKIP_REDUCE = 8, VLT_SKIP_O = 16, VLT_SKIP_GATE_UP = 32, VLT_SKIP_DOWN = 64, VLT_SKIP_HEAD = 256 };
+void vlt_set_profile_skip(VltEngine* e, uint32_t mask);
+/* bench_matmul, hooks.rs:56-111: GPU seconds (best of reps) of one matmul kind ("qkv", "o",
+ * "gate_up", "down", "head") over all layers for n tokens, and the weight bytes one pass reads.
+ * variant 0: the engine's choice, 1: GEMV, 2: tensor-core GEMM. */
+int vlt_bench_matmul(VltEngine* e, const char* kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes);
+
+/* Generator, engine/src/engine/generate.rs:12-518. */
+enum { VLT_DRAFT_NONE = 0, VLT_DRAFT_REPLAY = 1, VLT_DRAFT_MODEL = 2 };
+enum { VLT_PROMPT_TOKENS = 0, VLT_PROMPT_RESUME = 1 };
+typedef struct {
+    uint32_t prompt_kind;          /* VLT_PROMPT_* */
+    const uint32_t* prompt_tokens; /* TOKENS: the prompt */
+    uint32_t n_prompt;
+    uint32_t resume_seq, resume_token; /* RESUME: a sequence of the engine, continued by this token */
+    uint32_t max_tokens;
+    const uint32_t* stop; /* at most VLT_MAX_STOP */
+    uint32_t n_stop;
+    VltSampling sampling;
+    uint32_t draft_kind; /* VLT_DRAFT_* */
+    uint32_t draft_rows; /* rows verified per step (1 + drafts) */
+    const uint32_t* trace; /* REPLAY: the recorded sequence, prompt and continuation */
+    uint32_t n_trace;
+} VltRequest;
+enum { VLT_EVENT_TOKEN = 0, VLT_EVENT_DONE = 1 };
+enum { VLT_FINISH_STOP = 0, VLT_FINISH_LENGTH = 1 };
+typedef struct {
+    uint32_t kind; /* VLT_EVENT_* */
+    uint32_t req;
+    uint32_t value; /* TOKEN: the token; DONE: VLT_FINISH_* */
+} VltEvent;
+/* generate.rs:81-91 `StepStats`. */
+typedef struct {
+    uint32_t tokens, decode, emitted;
+    double gpu_seconds, encode_seconds;
+} VltStepStats;
+
+/* Engine::generator, generate.rs:153-176. The generator borrows the engine until freed. */
+int vlt_generator_new(VltEngine* e, VltGenerator** out);
+/* Drop for Generator, generate.rs:503-518. */
+void vlt_generator_free(VltGenerator* g);
+int vlt_generator_submit(VltGenerator* g, const VltRequest* req, uint32_t* req_id);
+void vlt_generator_cancel(VltGenerator* g, uint32_t req_id);
+/* Generator::step, generate.rs:271-280: commits the next step, returns the previous step's events. */
+int vlt_generator_step(VltGenerator* g, VltEvent* events, uint32_t cap, uint32_t* n_events);
+int vlt_generator_is_idle(VltGenerator* g);
+void vlt_generator_counts(VltGenerator* g, uint32_t* queued, uint32_t* running);
+/* Takes the step statistics gathered so far (the reference's `stats` field). */
+int vlt_generator_stats(VltGenerator* g, VltStepStats* out, uint32_t cap, uint32_t* n);
+void vlt_generator_set_hold(VltGenerator* g, uint32_t hold);
+void vlt_generator_set_replay_mistakes(VltGenerator* g, float rate, uint32_t seed);
+
+/* Inspection, for parity tests against the CPU oracle: copies a named engine array into `out`
+ * (u32 words: "lens", "feed", "tree", "gen", "path", "path_len", "on_path", "page_table",
+ * "free_pages", "tokens", "tin", "vis", "head_rows", "sample_rows", "runs", "out_ids",
+ * "emitted", "meta", "tiles"). Returns the word count through n. */
+int vlt_debug_read(VltEngine* e, const char* name, uint32_t* out, uint64_t cap, uint64_t* n);
+/* Plans a step without running it (Engine::plan, engine/src/engine/plan.rs:47-150); works on a host-only engine. */
+int vlt_debug_plan(VltEngine* e, const VltRun* runs, const uint32_t* verify, const uint32_t* heads, uint32_t n_runs, uint32_t hidden);
+/* Corrects a sequence's length as `collect` does (engine.rs:281-285 `settle`). */
+void vlt_debug_settle(VltEngine* e, uint32_t seq, uint32_t unused);
+/* Overwrites words of "lens", "feed", "tree" or "gen" (the per-slot state the GPU keeps), from word `index`. */
+int vlt_debug_write(VltEngine* e, const char* name, uint64_t index, const uint32_t* data, uint64_t n);
+/* One synchronous step of runs with their own head rows and verify flags, which may name GPU-fed
+ * tokens (what Generator::encode_next plans, generate.rs:380-392); optionally followed by the
+ * replay drafter (encode_replay, encode.rs:439-451). */
+int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, const uint32_t* heads, uint32_t n_runs, const VltStepOptions* opts,
+                   uint32_t replay, float replay_rate, uint32_t replay_seed, VltStepOutput* out);
+/* A slot's generation state as `admit` writes it (generate.rs:307-309), and its replay trace. */
+int vlt_debug_set_gen(VltEngine* e, uint32_t slot, uint32_t remaining, const uint32_t* stop, uint32_t n_stop);
+int vlt_debug_set_trace(VltEngine* e, uint32_t slot, const uint32_t* trace, uint32_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

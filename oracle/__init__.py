@@ -299,6 +299,11 @@ class Engine:
         if lib().orc_step(self.h, C.c_uint32(len(runs)), _p(seq), _p(count), _p(verify), _p(heads), _p(toks), C.c_uint32(hidden), C.c_uint32(mode)):
             raise RuntimeError(_err())
 
+    def write(self, name: str, index: int, data):
+        d = np.ascontiguousarray(data, np.uint32)
+        if lib().orc_array_write(self.h, name.encode(), C.c_uint64(index), _p(d), C.c_uint64(d.size)):
+            raise RuntimeError(_err())
+
     _F32 = ("logits", "hidden_out", "taps", "draft_logits")
     _U16 = ("k_cache", "v_cache")
 

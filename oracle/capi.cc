@@ -182,6 +182,15 @@ uint64_t orc_array(void* h, const char* name, const void** ptr) {
     *ptr = nullptr;
     return 0;
 }
+// Overwrites words of lens, feed or tree from word `index`.
+int orc_array_write(void* h, const char* name, uint64_t index, const uint32_t* data, uint64_t n) {
+    Engine* e = static_cast<Engine*>(h);
+    const std::string nm = name;
+    std::vector<uint32_t>* v = nm == "lens" ? &e->lens : nm == "feed" ? &e->feed : nm == "tree" ? &e->tree : nullptr;
+    if (!v || index + n > v->size()) { g_err = "orc_array_write: " + nm; return 1; }
+    std::copy_n(data, n, v->begin() + index);
+    return 0;
+}
 void orc_model_desc(void* h, uint32_t* out12) {
     const ModelDesc& m = static_cast<Engine*>(h)->md;
     const uint32_t v[12] = {m.n_layers, m.d, m.n_heads, m.n_kv, m.hd, m.ffn, m.vocab, m.vocab_real, m.page, f2u(m.eps), f2u(m.attn_scale),

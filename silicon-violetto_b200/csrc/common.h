@@ -1,0 +1,125 @@
+// Shared host-side helpers: errors, device buffers, the structs mirrored on the GPU.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace vlt {
+
+struct Error : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+#define VLT_CUDA(call)                                                                                         \
+    do {                                                                                                       \
+        cudaError_t err__ = (call);                                                                            \
+        if (err__ != cudaSuccess)                                                                              \
+            throw ::vlt::Error(std::string(#call) + ": " + cudaGetErrorString(err__) + " (" __FILE__ ":" + std::to_string(__LINE__) + ")"); \
+    } while (0)
+
+// engine/src/engine/kernels.rs:14-29.
+constexpr uint32_t FEED_ROW = 0xffff0000u;
+constexpr uint32_t FEED_W = 16;
+constexpr uint32_t NO_TOK = 0xffffffffu;
+constexpr uint32_t VERIFY_T = 8;
+constexpr uint32_t MAX_STOP = 8;
+constexpr uint32_t NO_PARENT = 0xffu;
+
+// engine/src/engine/kernels.rs:20-24 `chain_node`.
+inline uint32_t chain_node(uint32_t row) {
+    const uint32_t parent = row == 0 ? NO_PARENT : row - 1;
+    return row | parent << 8 | ((2u << row) - 1u) << 16;
+}
+
+// engine/src/engine/kernels.rs:87-127: bit-compatible with the reference's #[repr(C)] structs.
+struct SampleRow {
+    uint32_t seed_lo, seed_hi;
+    uint32_t pos;  // the drawn token's position, if tok is NO_TOK
+    float temperature;
+    float top_p;
+    uint32_t tok;  // the step's token whose head row this is: the draw is at its position + 1
+};
+struct RunIn {
+    uint32_t slot, first, count;
+    uint32_t head0, nhead;
+    uint32_t verify;
+};
+struct GenState {
+    uint32_t remaining, done, nstop, pad;
+    uint32_t stop[MAX_STOP];
+};
+inline GenState gen_open() { return GenState{0xffffffffu, 0, 0, 0, {0, 0, 0, 0, 0, 0, 0, 0}}; }
+struct ReplayArgs {
+    uint32_t stride, seed;
+    float rate;
+    uint32_t vocab;
+};
+
+// A buffer on the device, or on the host for a host-only (planning) engine. Written and read
+// through explicit copies; step inputs use the pinned mirror for asynchronous uploads.
+struct Buffer {
+    void* dev = nullptr;
+    size_t bytes = 0;
+    bool host_only = false;
+
+    Buffer() = default;
+    Buffer(const Buffer&) = delete;
+    Buffer& operator=(const Buffer&) = delete;
+    Buffer(Buffer&& o) noexcept { *this = std::move(o); }
+    Buffer& operator=(Buffer&& o) noexcept {
+        release();
+        dev = o.dev; bytes = o.bytes; host_only = o.host_only;
+        o.dev = nullptr; o.bytes = 0;
+        return *this;
+    }
+    ~Buffer() { release(); }
+
+    void alloc(size_t n, bool host) {
+        release();
+        bytes = n;
+        host_only = host;
+        if (n == 0) return;
+        if (host) {
+            dev = std::calloc(1, n);
+            if (!dev) throw Error("out of host memory");
+        } else {
+            VLT_CUDA(cudaMalloc(&dev, n));
+            VLT_CUDA(cudaMemset(dev, 0, n));
+        }
+    }
+    void release() {
+        if (!dev) return;
+        if (host_only) std::free(dev);
+        else cudaFree(dev);
+        dev = nullptr;
+    }
+    template <typename T> T* as() const { return static_cast<T*>(dev); }
+
+    // Synchronous copies (set-up and inspection paths).
+    void write(size_t offset_bytes, const void* src, size_t n) const {
+        if (n == 0) return;
+        if (offset_bytes + n > bytes) throw Error("buffer write out of range");
+        if (host_only) std::memcpy(static_cast<char*>(dev) + offset_bytes, src, n);
+        else VLT_CUDA(cudaMemcpy(static_cast<char*>(dev) + offset_bytes, src, n, cudaMemcpyHostToDevice));
+    }
+    void read(size_t offset_bytes, void* dst, size_t n) const {
+        if (n == 0) return;
+        if (offset_bytes + n > bytes) throw Error("buffer read out of range");
+        if (host_only) std::memcpy(dst, static_cast<char*>(dev) + offset_bytes, n);
+        else VLT_CUDA(cudaMemcpy(dst, static_cast<char*>(dev) + offset_bytes, n, cudaMemcpyDeviceToHost));
+    }
+    template <typename T> void write_vec(size_t index, const std::vector<T>& v) const { write(index * sizeof(T), v.data(), v.size() * sizeof(T)); }
+    template <typename T> std::vector<T> read_vec(size_t index, size_t count) const {
+        std::vector<T> v(count);
+        read(index * sizeof(T), v.data(), count * sizeof(T));
+        return v;
+    }
+};
+
+}  // namespace vlt

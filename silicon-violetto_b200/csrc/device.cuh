@@ -1,0 +1,106 @@
+// Device-side helpers shared by the kernels: bf16 bits, Philox, the sampler's exp2, reductions.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace vlt {
+
+// kernels.metal:17 `bf`.
+__device__ __forceinline__ float bf16_to_f32(uint16_t u) { return __uint_as_float(uint32_t(u) << 16); }
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// kernels.metal:22-27 `to_bf`: round to nearest even, finite inputs.
+__device__ __forceinline__ uint16_t f32_to_bf16(float f) {
+    uint32_t u = __float_as_uint(f);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return uint16_t(u >> 16);
+}
+__device__ __forceinline__ float round_bf16(float f) { return bf16_to_f32(f32_to_bf16(f)); }
+// Two floats to packed bf16 (lo in the low half), same rounding.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return uint32_t(f32_to_bf16(lo)) | uint32_t(f32_to_bf16(hi)) << 16; }
+
+// kernels.metal:1462-1472 `philox`: Philox4x32-10.
+__device__ __forceinline__ uint4 philox(uint4 c, uint32_t k0, uint32_t k1) {
+#pragma unroll
+    for (int i = 0; i < 10; i++) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return c;
+}
+// kernels.metal:1474-1477 `uniform01`.
+__device__ __forceinline__ float uniform01(uint32_t seed_lo, uint32_t seed_hi, uint32_t pos, uint32_t round) {
+    return __fmul_rn(float(philox(make_uint4(pos, round, 0, 0), seed_lo, seed_hi).x >> 8), 0x1p-24f);
+}
+
+// 2^x for the sampler, from IEEE operations only so that a draw is the same on every device
+// and on the host: round x to the nearest integer n, a degree-6 polynomial in x - n on
+// [-0.5, 0.5] by Horner with fused multiply-adds, n added to the exponent. 0 below 2^-125.
+// (The reference calls Metal's exp2, kernels.metal:1536, whose last bits are the vendor's.)
+__device__ __forceinline__ float soft_exp2(float x) {
+    if (!(x > -125.5f)) return 0.0f;
+    if (x > 126.0f) x = 126.0f;
+    const float magic = 12582912.0f;
+    const float t = __fadd_rn(x, magic);
+    const int n = __float_as_int(t) - 0x4B400000;
+    const float f = __fsub_rn(x, __fsub_rn(t, magic));
+    float p = 0.00015403530393381608f;
+    p = __fmaf_rn(p, f, 0.0013333558146428443f);
+    p = __fmaf_rn(p, f, 0.009618129107628477f);
+    p = __fmaf_rn(p, f, 0.05550410866482158f);
+    p = __fmaf_rn(p, f, 0.2402265069591007f);
+    p = __fmaf_rn(p, f, 0.6931471805599453f);
+    p = __fmaf_rn(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + (n << 23));
+}
+
+constexpr float LOG2E = 1.44269504088896340736f;
+
+// kernels.metal:64-72.
+__device__ __forceinline__ uint32_t d_tree_node(uint32_t depth, uint32_t parent, uint32_t sees) { return depth | parent << 8 | sees << 16; }
+__device__ __forceinline__ uint32_t d_chain_node(uint32_t row) { return d_tree_node(row, row == 0 ? 0xffu : row - 1, (2u << row) - 1u); }
+__device__ __forceinline__ uint32_t d_dead_node(uint32_t row) { return d_tree_node(1, 0xffu, 1u | 1u << row); }
+__device__ __forceinline__ uint32_t node_depth(uint32_t n) { return n & 0xffu; }
+__device__ __forceinline__ uint32_t node_parent(uint32_t n) { return (n >> 8) & 0xffu; }
+__device__ __forceinline__ uint32_t node_sees(uint32_t n) { return n >> 16; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// kernels.metal:1418-1427 `better`, `simd_best`: (value, id) with ties to the lowest id.
+__device__ __forceinline__ void better(float& bv, uint32_t& bi, float v, uint32_t i) {
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+__device__ __forceinline__ void warp_best(float& bv, uint32_t& bi) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t i = __shfl_xor_sync(0xffffffffu, bi, o);
+        better(bv, bi, v, i);
+    }
+}
+
+// Where kv head g's row for cache position pos starts, in elements (kernels.metal:704-711,
+// the paged layout): [layer][page][kv head][page_tok][head_dim].
+struct KvArgs {
+    uint32_t n_pages, max_pages, n_kv, page_shift, hd;
+};
+__device__ __forceinline__ size_t kv_row(const KvArgs& kv, uint32_t layer, const uint32_t* page_table, uint32_t slot, uint32_t g, uint32_t pos) {
+    const uint32_t page = page_table[size_t(slot) * kv.max_pages + (pos >> kv.page_shift)];
+    const uint32_t psize = 1u << kv.page_shift;
+    return ((size_t(layer) * kv.n_pages + page) * kv.n_kv + g) * psize * kv.hd + size_t(pos & (psize - 1)) * kv.hd;
+}
+
+}  // namespace vlt

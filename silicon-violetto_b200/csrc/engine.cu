@@ -1,0 +1,623 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace vlt {
+
+// engine/src/engine.rs:110-117 `Sampling::check`.
+void Sampling::check() const {
+    const bool t_ok = temperature == 0.0f || (std::isnormal(temperature) && temperature > 0.0f);
+    if (!(t_ok && top_p > 0.0f && top_p <= 1.0f))
+        throw Error("sampling {temperature " + std::to_string(temperature) + ", top_p " + std::to_string(top_p) +
+                    "}: needs a temperature of 0 or a normal positive one, and 0 < top_p <= 1");
+}
+
+// ------------------------------------------------------------------ KV cache
+void KvCache::init(const EngineConfig& cfg, const ModelDesc& md, uint32_t n_layers, bool with_pool) {
+    page = md.page;
+    n_pages = (cfg.global_kv_tokens + page - 1) / page;
+    max_pages = (cfg.max_seq_len + page - 1) / page;
+    const size_t bytes = size_t(n_layers) * n_pages * page * md.n_kv * md.hd * 2;
+    if (with_pool) {
+        k.alloc(bytes, false);
+        v.alloc(bytes, false);
+    }
+    page_table.alloc(size_t(cfg.max_seqs) * max_pages * 4, !with_pool);
+    free_pages.clear();
+    for (uint32_t i = n_pages; i-- > 0;) free_pages.push_back(i);  // kv.rs:43: a stack that pops 0, 1, 2, ...
+}
+
+// engine/src/engine/kv.rs:51-58.
+void KvCache::reserve(uint32_t slot, std::vector<uint32_t>& pages, uint32_t len) {
+    while (size_t(pages.size()) * page < len) {
+        if (free_pages.empty()) throw Error("global KV pool exhausted");
+        const uint32_t pg = free_pages.back();
+        free_pages.pop_back();
+        page_table.write((size_t(slot) * max_pages + pages.size()) * 4, &pg, 4);
+        pages.push_back(pg);
+    }
+}
+
+// engine/src/engine/kv.rs:60-62.
+void KvCache::release(const std::vector<uint32_t>& pages) {
+    for (size_t i = pages.size(); i-- > 0;) free_pages.push_back(pages[i]);
+}
+
+// ------------------------------------------------------------------ step sets
+void StepSet::init(const EngineConfig& cfg) {
+    host_only = cfg.host_only;
+    const size_t n = cfg.max_step_tokens, hr = cfg.max_head_rows, ms = cfg.max_seqs;
+    size_t at = 0;
+    auto take = [&](size_t bytes) { const size_t o = at; at += (bytes + 255) / 256 * 256; return o; };
+    o_tokens = take(n * 4);
+    o_tin = take(2 * n * 4);
+    o_vis = take(n * 4);
+    o_head_rows = take(hr * 4);
+    o_hidden_rows = take(n * 4);
+    o_sample_rows = take(hr * sizeof(SampleRow));
+    o_tiles = take(2 * (n / 8 + ms + 1) * 4);
+    o_runs = take(ms * sizeof(RunIn));
+    in_bytes = at;
+    at = 0;
+    o_out_ids = take(hr * 4);
+    o_emitted = take(ms * 4);
+    out_bytes = at;
+    dev_in.alloc(in_bytes, host_only);
+    dev_out.alloc(out_bytes, host_only);
+    if (host_only) {
+        host_in = static_cast<uint8_t*>(dev_in.dev);
+        host_out = static_cast<uint8_t*>(dev_out.dev);
+    } else {
+        VLT_CUDA(cudaMallocHost(reinterpret_cast<void**>(&host_in), in_bytes));
+        VLT_CUDA(cudaMallocHost(reinterpret_cast<void**>(&host_out), out_bytes));
+        std::memset(host_in, 0, in_bytes);
+        std::memset(host_out, 0, out_bytes);
+        VLT_CUDA(cudaEventCreate(&start));
+        VLT_CUDA(cudaEventCreate(&done));
+    }
+}
+
+void StepSet::release() {
+    if (!host_only) {
+        if (host_in) cudaFreeHost(host_in);
+        if (host_out) cudaFreeHost(host_out);
+        if (start) cudaEventDestroy(start);
+        if (done) cudaEventDestroy(done);
+    }
+    host_in = host_out = nullptr;
+}
+
+// --------------------------------------------------------------------- engine
+Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& t) : cfg(c), tuning(t) {
+    if (!cfg.host_only) {
+        int count = 0;
+        const cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0)
+            throw Error(std::string("no usable CUDA device (") + cudaGetErrorString(e) + "): this engine has no CPU path");
+        if (cfg.device < 0 || cfg.device >= count) throw Error("device_ordinal " + std::to_string(cfg.device) + " of " + std::to_string(count) + " devices");
+        VLT_CUDA(cudaSetDevice(cfg.device));
+        cudaDeviceProp prop;
+        VLT_CUDA(cudaGetDeviceProperties(&prop, cfg.device));
+        if (prop.major < 10) throw Error(std::string(prop.name) + ": compute capability " + std::to_string(prop.major) + "." + std::to_string(prop.minor) + " (the kernels are built for sm_100a)");
+        sm_count = tuning.sm_count ? tuning.sm_count : uint32_t(prop.multiProcessorCount);
+        VLT_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    } else if (tuning.sm_count) {
+        sm_count = tuning.sm_count;
+    }
+    if (cfg.max_seqs == 0 || cfg.max_step_tokens == 0 || cfg.max_chunk == 0 || cfg.max_head_rows == 0) throw Error("engine config: zero capacity");
+    model.load(weights, cfg.host_only);
+    const ModelDesc& md = model.md;
+    kv.init(cfg, md, md.n_layers, !cfg.host_only);
+    seqs.resize(cfg.max_seqs);
+    for (auto& st : sets) st.init(cfg);
+
+    const bool ho = cfg.host_only;
+    const size_t n = cfg.max_step_tokens, hr = cfg.max_head_rows, ms = cfg.max_seqs;
+    auto f = [&](Buffer& b, size_t floats) { b.alloc(floats * 4, ho); };
+    if (!ho) {
+        f(s.h, n * md.d);
+        f(s.qkv, n * md.qkv_w());
+        f(s.attn, n * md.n_heads * md.hd);
+        f(s.act, n * md.ffn);
+        f(s.part, n * 16 * md.n_heads * ATTN_PART);  // buffers.rs:9: 16 partial slots per token of a full step
+        f(s.hfin_head, hr * md.d);
+        f(s.hfin_all, n * md.d);
+        f(s.logits, hr * md.vocab);
+        f(s.taps, n * md.d);
+        f(s.inv, n);
+    }
+    f(s.meta, 2 * n);
+    f(s.lens, ms);
+    f(s.feed, ms * FEED_W);
+    f(s.tree, ms * FEED_W);
+    s.gen.alloc(ms * sizeof(GenState), ho);
+    f(s.path, ms * FEED_W);
+    f(s.path_len, ms);
+    f(s.on_path, n);
+    f(s.trace, ho ? 1 : ms * size_t(cfg.max_seq_len));
+    f(s.trace_len, ms);
+    f(s.err_flag, 1);
+    std::vector<uint32_t> chains(ms * FEED_W);
+    for (size_t i = 0; i < chains.size(); i++) chains[i] = chain_node(uint32_t(i % FEED_W));  // buffers.rs:112-113
+    s.tree.write_vec(0, chains);
+    std::vector<GenState> open(ms, gen_open());
+    s.gen.write_vec(0, open);
+
+    if (!ho) {
+        // engine.rs:392-421 `rope_table`: theta = float32(pos) * frequency, cos and sin rounded to bf16.
+        const uint32_t npos = cfg.max_seq_len + FEED_W, half = md.hd / 2;
+        std::vector<float> tab(size_t(npos) * half * 2);
+        auto rb = [](float x) { uint32_t u; std::memcpy(&u, &x, 4); u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u; std::memcpy(&x, &u, 4); return x; };
+        for (uint32_t p = 0; p < npos; p++)
+            for (uint32_t i = 0; i < half; i++) {
+                const float theta = float(p) * model.rope_freq[i];
+                tab[(size_t(p) * half + i) * 2] = rb(std::cos(theta));
+                tab[(size_t(p) * half + i) * 2 + 1] = rb(std::sin(theta));
+            }
+        rope_tab.alloc(tab.size() * 4, false);
+        rope_tab.write_vec(0, tab);
+        attn_maps_init(&attn_maps, kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), uint64_t(md.n_layers) * kv.n_pages * md.n_kv * md.page);
+        VLT_CUDA(cudaDeviceSynchronize());
+    }
+}
+
+Engine::~Engine() {
+    if (stream) {
+        cudaStreamSynchronize(stream);
+        cudaStreamDestroy(stream);
+    }
+    for (auto& st : sets) st.release();
+}
+
+std::string Engine::device_name() const {
+    if (cfg.host_only) return "host (planning only)";
+    cudaDeviceProp prop;
+    VLT_CUDA(cudaGetDeviceProperties(&prop, cfg.device));
+    return prop.name;
+}
+
+// engine/src/engine.rs:259-267.
+uint32_t Engine::new_seq() {
+    for (uint32_t slot = 0; slot < seqs.size(); slot++)
+        if (!seqs[slot]) {
+            seqs[slot] = Seq{};
+            const uint32_t zero = 0;
+            s.lens.write(slot * 4, &zero, 4);
+            s.trace_len.write(slot * 4, &zero, 4);
+            set_gen(slot, gen_open());
+            return slot;
+        }
+    throw Error("no free sequence slot");
+}
+
+void Engine::set_gen(uint32_t slot, const GenState& g) { s.gen.write(slot * sizeof(GenState), &g, sizeof g); }
+
+void Engine::set_trace(uint32_t slot, const uint32_t* trace, uint32_t n) {
+    if (n > cfg.max_seq_len) throw Error("replay trace longer than max_seq_len");
+    if (!cfg.host_only) s.trace.write(size_t(slot) * cfg.max_seq_len * 4, trace, size_t(n) * 4);
+    s.trace_len.write(slot * 4, &n, 4);
+}
+
+// engine/src/engine.rs:281-285.
+void Engine::settle(uint32_t id, uint32_t unused) {
+    if (id < seqs.size() && seqs[id]) seqs[id]->len -= unused;
+}
+
+void Engine::set_sampling(uint32_t id, const Sampling& sm) {
+    sm.check();
+    if (id >= seqs.size() || !seqs[id]) throw Error("unknown sequence");
+    seqs[id]->sampling = sm;
+}
+
+// engine/src/engine.rs:298-303.
+void Engine::free_seq(uint32_t id) {
+    if (id < seqs.size() && seqs[id]) {
+        kv.release(seqs[id]->pages);
+        seqs[id].reset();
+    }
+}
+
+uint32_t Engine::seq_len(uint32_t id) const { return id < seqs.size() && seqs[id] ? seqs[id]->len : 0; }
+
+void Engine::set_taps(bool on) { taps_on = on; }
+
+KvArgs Engine::kv_args() const {
+    uint32_t shift = 0;
+    while ((1u << shift) < model.md.page) shift++;
+    return KvArgs{kv.n_pages, kv.max_pages, model.md.n_kv, shift, model.md.hd};
+}
+
+// How the cached keys are split across attention blocks (the reference's decode_splits,
+// engine/src/engine/plan.rs:153-163, re-derived for this GPU): blocks of 4 warps, three per SM;
+// among the split counts that leave a block at least 8 pages, the one that fills whole waves best.
+void Engine::attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const {
+    const uint32_t page = model.md.page, unit = 4 * page;  // a block's four warps take a page each
+    const uint32_t cap = std::min<uint32_t>(std::max<uint32_t>(cfg.max_step_tokens * 16 / std::max(p.n, 1u), 1u), 64u);  // plan.rs:127
+    const uint32_t slots = 3 * sm_count, base = std::max(n_tiles * model.md.n_kv, 1u);
+    uint32_t best = 1;
+    if (tuning.attn_keys_per_cta) {
+        best = std::max(1u, (max_keys + tuning.attn_keys_per_cta - 1) / tuning.attn_keys_per_cta);
+    } else {
+        double best_eff = -1.0;
+        for (uint32_t sp = 1; sp <= cap; sp++) {
+            if (sp > 1 && max_keys / sp < 8 * page) break;
+            const double waves = double(base) * sp / slots;
+            const double eff = waves / std::ceil(waves) - 0.002 * sp;  // ties go to fewer splits
+            if (eff > best_eff) { best_eff = eff; best = sp; }
+        }
+    }
+    best = std::min(best, cap);
+    uint32_t kps = ((max_keys + best - 1) / best + unit - 1) / unit * unit;
+    kps = std::max(kps, unit);
+    p.keys_per_split = kps;
+    p.max_splits = std::max(1u, (max_keys + kps - 1) / kps);
+}
+
+// engine/src/engine/plan.rs:47-150 `plan`.
+Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
+    uint32_t n = 0;
+    for (const PlanRun& r : runs) n += r.count;
+    if (n == 0 || n > cfg.max_step_tokens) throw Error("step has " + std::to_string(n) + " tokens (max " + std::to_string(cfg.max_step_tokens) + ")");
+    std::vector<uint32_t> tokens, tin, vis, head_rows, hidden_rows, tiles;
+    std::vector<SampleRow> samples;
+    std::vector<RunIn> run_in;
+    uint32_t max_keys = 0, max_count = 0;
+    Plan p;
+    for (size_t ri = 0; ri < runs.size(); ri++) {
+        const PlanRun& run = runs[ri];
+        const uint32_t id = run.seq, count = run.count;
+        if (count == 0 || count > cfg.max_chunk) throw Error(std::to_string(count) + " tokens for one sequence in a step (max_chunk " + std::to_string(cfg.max_chunk) + ")");
+        for (uint32_t i = 0; i < count; i++) {
+            const uint32_t tk = run.tokens[i];
+            if (tk >= FEED_ROW && tk - FEED_ROW >= FEED_W) throw Error("only " + std::to_string(FEED_W) + " GPU-fed tokens per slot");
+            if (tk < FEED_ROW && tk >= model.md.vocab) throw Error("token id out of range");
+        }
+        for (size_t j = 0; j < ri; j++)
+            if (runs[j].seq == id) throw Error("a sequence appears twice in one step");
+        if (id >= seqs.size() || !seqs[id]) throw Error("unknown sequence");
+        Seq& sq = *seqs[id];
+        const uint32_t new_len = sq.len + count;
+        if (new_len > cfg.max_seq_len) throw Error("sequence would reach " + std::to_string(new_len) + " tokens (max " + std::to_string(cfg.max_seq_len) + ")");
+        kv.reserve(id, sq.pages, new_len);
+        const uint32_t first_row = uint32_t(tokens.size());
+        tokens.insert(tokens.end(), run.tokens, run.tokens + count);
+        for (uint32_t row = 0; row < count; row++) {
+            tin.push_back(id);
+            tin.push_back(row);
+            vis.push_back(0xffffffffu >> (31 - row % 8));  // causal within its tile of 8; `embed` overwrites a draft tree's
+        }
+        auto rows = [&](Rows r, std::vector<uint32_t>& v) {
+            if (r == Rows::Last) v.push_back(first_row + count - 1);
+            if (r == Rows::All) for (uint32_t x = first_row; x < first_row + count; x++) v.push_back(x);
+        };
+        const uint32_t first_head = uint32_t(head_rows.size());
+        rows(run.verify ? Rows::All : run.head, head_rows);
+        rows(hidden, hidden_rows);
+        for (uint32_t h = first_head; h < head_rows.size(); h++) samples.push_back(sq.sampling.row_of(head_rows[h]));
+        run_in.push_back(RunIn{id, first_row, count, first_head, uint32_t(head_rows.size()) - first_head, run.verify ? 1u : 0u});
+        for (uint32_t i = 0; i < count; i += 8) {
+            tiles.push_back(first_row + i);
+            tiles.push_back(std::min(count - i, 8u));
+        }
+        max_keys = std::max(max_keys, new_len);
+        max_count = std::max(max_count, count);
+        p.branches = p.branches || (run.verify && count > 2);
+        sq.len = new_len;
+    }
+    if (head_rows.size() > cfg.max_head_rows) throw Error(std::to_string(head_rows.size()) + " head rows (max " + std::to_string(cfg.max_head_rows) + ")");
+    StepSet& st = sets[set];
+    auto put = [&](size_t off, const void* src, size_t bytes) { if (bytes) std::memcpy(st.host_in + off, src, bytes); };
+    put(st.o_tokens, tokens.data(), tokens.size() * 4);
+    put(st.o_tin, tin.data(), tin.size() * 4);
+    put(st.o_vis, vis.data(), vis.size() * 4);
+    put(st.o_head_rows, head_rows.data(), head_rows.size() * 4);
+    put(st.o_hidden_rows, hidden_rows.data(), hidden_rows.size() * 4);
+    put(st.o_sample_rows, samples.data(), samples.size() * sizeof(SampleRow));
+    put(st.o_tiles, tiles.data(), tiles.size() * 4);
+    put(st.o_runs, run_in.data(), run_in.size() * sizeof(RunIn));
+    p.n = n;
+    p.n_head = uint32_t(head_rows.size());
+    p.n_hidden = uint32_t(hidden_rows.size());
+    p.n_runs = uint32_t(runs.size());
+    p.tiles = uint32_t(tiles.size() / 2);
+    p.max_run = max_count;
+    attention_split(p, max_keys, p.tiles);
+    last_plan_n = n;
+    return p;
+}
+
+// Y = epilogue(W . X) for n tokens: steps of at most 8 tokens stream the weights through the
+// tensor cores from registers; larger ones go in token blocks of 8 (the weights of one matrix
+// stay in L2 between blocks).
+void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out) {
+    MatArgs a{};
+    a.W = w.w;
+    a.scales = w.scales;
+    a.k = w.k;
+    a.m = w.m;
+    a.group = w.group;
+    a.int8 = w.int8;
+    a.epi = epi;
+    a.vocab_real = model.md.vocab_real;
+    a.eps = model.md.eps;
+    const uint32_t out_w = epi == EPI_SWIGLU ? w.m / 2 : w.m;
+    for (uint32_t t0 = 0; t0 < n; t0 += 8) {
+        a.n = std::min(8u, n - t0);
+        a.X = x + size_t(t0) * w.k;
+        a.Y = y + size_t(t0) * out_w;
+        a.base = base ? base + size_t(t0) * out_w : nullptr;
+        a.inv_out = inv_out ? inv_out + t0 : nullptr;
+        launch_matmul_stream(a, sm_count, stream);
+    }
+}
+
+// engine/src/engine/encode.rs:142-192 `encode_layer`, a plain decoder's.
+void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
+    const Layer& l = model.layers[li];
+    const ModelDesc& md = model.md;
+    StepSet& st = sets[set];
+    const uint32_t n = p.n;
+    float* h = s.h.as<float>();
+    if (!(skip & 1)) matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
+    const KvArgs kva = kv_args();
+    if (!(skip & 2))
+        launch_qkv_post(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tin), rope_tab.as<float>(), kv.k.as<uint16_t>(), kv.v.as<uint16_t>(),
+                        kv.page_table.as<uint32_t>(), kva, li, n, md.n_heads, stream);
+    const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
+    if (tuning.plain_attention) {
+        if (!(skip & 4))
+            launch_attn_plain(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tiles), st.in<uint32_t>(st.o_vis), rope_tab.as<float>(),
+                              kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kva, li, p.tiles, md.n_heads, scale_log2,
+                              s.attn.as<float>(), stream);
+    } else {
+        AttnArgs a{};
+        a.maps = &attn_maps;
+        a.err_flag = s.err_flag.as<uint32_t>();
+        a.qkv = s.qkv.as<float>();
+        a.meta = s.meta.as<uint32_t>();
+        a.tiles = st.in<uint32_t>(st.o_tiles);
+        a.vis = st.in<uint32_t>(st.o_vis);
+        a.rope = rope_tab.as<float>();
+        a.k_cache = kv.k.as<uint16_t>();
+        a.v_cache = kv.v.as<uint16_t>();
+        a.page_table = kv.page_table.as<uint32_t>();
+        a.kv = kva;
+        a.layer = li;
+        a.n_tiles = p.tiles;
+        a.n_heads = md.n_heads;
+        a.scale_log2 = scale_log2;
+        a.keys_per_split = p.keys_per_split;
+        a.max_splits = p.max_splits;
+        a.part = s.part.as<float>();
+        a.out = s.attn.as<float>();
+        a.out_b = nullptr;
+        a.n = n;
+        if (!(skip & 4)) launch_attn_mma(a, stream);
+        if (!(skip & 8)) launch_attn_combine(a, stream);
+    }
+    if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr);
+    if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+    if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr);
+}
+
+// engine/src/engine/encode.rs:557-573 `encode_sample`.
+void Engine::encode_sample(uint32_t set, uint32_t rows) {
+    StepSet& st = sets[set];
+    launch_sample(s.logits.as<float>(), st.in<SampleRow>(st.o_sample_rows), st.out<uint32_t>(st.o_out_ids), s.meta.as<uint32_t>(), rows, model.md.vocab, stream);
+}
+
+// engine/src/engine/encode.rs:383-412 `encode_tail`.
+void Engine::encode_tail(uint32_t set, const Plan& p) {
+    StepSet& st = sets[set];
+    const ModelDesc& md = model.md;
+    const float* h = s.h.as<float>();
+    if (taps_on) launch_prep_rows(h, nullptr, p.n, md.d, md.eps, s.taps.as<float>(), nullptr, nullptr, true, true, stream);
+    if (p.n_hidden) launch_prep_rows(h, st.in<uint32_t>(st.o_hidden_rows), p.n_hidden, md.d, md.eps, s.hfin_all.as<float>(), nullptr, nullptr, true, false, stream);
+    if (p.n_head && !(skip & 256)) {
+        launch_prep_rows(h, st.in<uint32_t>(st.o_head_rows), p.n_head, md.d, md.eps, s.hfin_head.as<float>(), nullptr, nullptr, false, false, stream);
+        matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
+        encode_sample(set, p.n_head);
+    }
+    launch_accept(st.in<RunIn>(st.o_runs), st.in<uint32_t>(st.o_tokens), st.out<uint32_t>(st.o_out_ids), s.lens.as<uint32_t>(), s.feed.as<uint32_t>(),
+                  s.gen.as<GenState>(), st.out<uint32_t>(st.o_emitted), p.n_runs, s.tree.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(),
+                  s.on_path.as<uint32_t>(), stream);
+    if (p.branches)
+        launch_kv_compact(st.in<RunIn>(st.o_runs), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.lens.as<uint32_t>(), kv.k.as<uint16_t>(),
+                          kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kv_args(), p.n_runs, md.n_layers, stream);
+}
+
+// engine/src/engine/encode.rs:99-105 `encode_forward`, after the step set's upload.
+void Engine::encode_forward(uint32_t set, const Plan& p) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it plans steps but cannot run them (no CPU path)");
+    StepSet& st = sets[set];
+    VLT_CUDA(cudaEventRecord(st.start, stream));
+    VLT_CUDA(cudaMemcpyAsync(st.dev_in.dev, st.host_in, st.in_bytes, cudaMemcpyHostToDevice, stream));
+    launch_embed(model.embed, st.in<uint32_t>(st.o_tokens), s.h.as<float>(), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.lens.as<uint32_t>(),
+                 s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), st.in<uint32_t>(st.o_vis), p.n, model.md.d, stream);
+    for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
+    encode_tail(set, p);
+}
+
+// engine/src/engine/encode.rs:439-451 `encode_replay`.
+void Engine::encode_replay(uint32_t set, const Plan& p, const ReplayArgs& ra) {
+    StepSet& st = sets[set];
+    launch_replay_draft(st.in<RunIn>(st.o_runs), s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.trace.as<uint32_t>(), s.trace_len.as<uint32_t>(), ra,
+                        p.n_runs, s.tree.as<uint32_t>(), stream);
+}
+
+void Engine::commit(uint32_t set) {
+    StepSet& st = sets[set];
+    VLT_CUDA(cudaMemcpyAsync(st.host_out, st.dev_out.dev, st.out_bytes, cudaMemcpyDeviceToHost, stream));
+    VLT_CUDA(cudaEventRecord(st.done, stream));
+    VLT_CUDA(cudaGetLastError());
+}
+
+double Engine::wait(uint32_t set) {
+    StepSet& st = sets[set];
+    VLT_CUDA(cudaEventSynchronize(st.done));
+    float ms = 0.0f;
+    VLT_CUDA(cudaEventElapsedTime(&ms, st.start, st.done));
+    return double(ms) * 1e-3;
+}
+
+void Engine::check_device_error() {
+    uint32_t flag = 0;
+    s.err_flag.read(0, &flag, 4);
+    if (flag) {
+        const uint32_t zero = 0;
+        s.err_flag.write(0, &zero, 4);
+        throw Error("a kernel's bounded wait ran out (device error flag " + std::to_string(flag) + ")");
+    }
+}
+
+// engine/src/engine.rs:310-314 `step` + :357-371 `read_output`.
+StepOutput Engine::step(const std::vector<PlanRun>& runs, const StepOptions& opts) { return step_runs(runs, opts, nullptr); }
+
+void Engine::upload_set(uint32_t set) {
+    if (cfg.host_only) return;
+    StepSet& st = sets[set];
+    VLT_CUDA(cudaMemcpyAsync(st.dev_in.dev, st.host_in, st.in_bytes, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaStreamSynchronize(stream));
+}
+
+void Engine::load_drafter(const std::string& path) { throw Error(path + ": the model drafter is not built yet"); }
+bool Engine::has_drafter() const { return false; }
+void Engine::encode_drafter(uint32_t, const Plan&) {}
+
+StepOutput Engine::step_runs(const std::vector<PlanRun>& runs, const StepOptions& opts, const ReplayArgs* replay) {
+    Plan p = plan(0, runs, opts.hidden);
+    encode_forward(0, p);
+    if (replay) encode_replay(0, p, *replay);
+    commit(0);
+    StepOutput out;
+    out.gpu_seconds = wait(0);
+    check_device_error();
+    const StepSet& st = sets[0];
+    out.ids.assign(st.hout<uint32_t>(st.o_out_ids), st.hout<uint32_t>(st.o_out_ids) + p.n_head);
+    if (opts.read_logits) out.logits = s.logits.read_vec<float>(0, size_t(p.n_head) * model.md.vocab);
+    out.hidden = s.hfin_all.read_vec<float>(0, size_t(p.n_hidden) * model.md.d);
+    if (opts.read_taps && taps_on) {
+        std::vector<float> tf = s.taps.read_vec<float>(0, size_t(p.n) * model.md.d);
+        out.taps.resize(tf.size());
+        for (size_t i = 0; i < tf.size(); i++) { uint32_t u; std::memcpy(&u, &tf[i], 4); out.taps[i] = uint16_t(u >> 16); }  // bf16 values held as f32
+    }
+    return out;
+}
+
+// engine/src/engine/hooks.rs:28-36 `bench_fill`.
+void Engine::bench_fill(uint32_t id, uint32_t len, uint32_t seed) {
+    if (id >= seqs.size() || !seqs[id]) throw Error("unknown sequence");
+    Seq& sq = *seqs[id];
+    const uint32_t from = sq.len;
+    if (sq.len + len > cfg.max_seq_len) throw Error("sequence would reach " + std::to_string(sq.len + len) + " tokens (max " + std::to_string(cfg.max_seq_len) + ")");
+    sq.len += len;
+    s.lens.write(id * 4, &sq.len, 4);
+    kv.reserve(id, sq.pages, sq.len);
+    if (seed && !cfg.host_only) {
+        launch_kv_fill(kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kv_args(), model.md.n_layers, id, from, sq.len, seed, stream);
+        VLT_CUDA(cudaStreamSynchronize(stream));
+    }
+}
+
+// engine/src/engine/hooks.rs:41-54 `sample_logits`.
+std::vector<uint32_t> Engine::sample_logits(const float* logits, const std::vector<std::pair<Sampling, uint32_t>>& rows) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");
+    const size_t n = rows.size();
+    if (n == 0 || n > cfg.max_head_rows) throw Error(std::to_string(n) + " rows of logits (max " + std::to_string(cfg.max_head_rows) + " rows)");
+    StepSet& st = sets[0];
+    for (size_t i = 0; i < n; i++) {
+        rows[i].first.check();
+        st.hin<SampleRow>(st.o_sample_rows)[i] = rows[i].first.row_at(rows[i].second);
+    }
+    if (logits) VLT_CUDA(cudaMemcpyAsync(s.logits.dev, logits, n * model.md.vocab * 4, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaMemcpyAsync(st.dev_in.dev, st.host_in, st.in_bytes, cudaMemcpyHostToDevice, stream));
+    encode_sample(0, uint32_t(n));
+    VLT_CUDA(cudaMemcpyAsync(st.host_out, st.dev_out.dev, st.out_bytes, cudaMemcpyDeviceToHost, stream));
+    VLT_CUDA(cudaStreamSynchronize(stream));
+    return std::vector<uint32_t>(st.hout<uint32_t>(st.o_out_ids), st.hout<uint32_t>(st.o_out_ids) + n);
+}
+
+// engine/src/engine/hooks.rs:56-111 `bench_matmul`.
+void Engine::bench_matmul(const std::string& kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");
+    const bool head = kind == "head";
+    if (!head && kind != "qkv" && kind != "o" && kind != "gate_up" && kind != "down") throw Error("unknown matmul " + kind);
+    if (n == 0 || n > (head ? cfg.max_head_rows : cfg.max_step_tokens)) throw Error(kind + " can't take " + std::to_string(n) + " tokens");
+    (void)variant;
+    cudaEvent_t e0, e1;
+    VLT_CUDA(cudaEventCreate(&e0));
+    VLT_CUDA(cudaEventCreate(&e1));
+    double best = 1e30;
+    for (uint32_t r = 0; r < std::max(reps, 1u); r++) {
+        VLT_CUDA(cudaEventRecord(e0, stream));
+        if (head) matmul(model.head, n, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
+        else
+            for (const Layer& l : model.layers) {
+                if (kind == "qkv") matmul(l.qkv, n, s.h.as<float>(), s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
+                else if (kind == "o") matmul(l.o, n, s.attn.as<float>(), s.hfin_all.as<float>(), EPI_RESID, s.h.as<float>(), nullptr);
+                else if (kind == "gate_up") matmul(l.gate_up, n, s.h.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+                else matmul(l.down, n, s.act.as<float>(), s.hfin_all.as<float>(), EPI_RESID, s.h.as<float>(), nullptr);
+            }
+        VLT_CUDA(cudaEventRecord(e1, stream));
+        VLT_CUDA(cudaEventSynchronize(e1));
+        float ms = 0;
+        VLT_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        best = std::min(best, double(ms) * 1e-3);
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *seconds = best;
+    uint64_t b = 0;
+    if (head) b = model.head.bytes();
+    else
+        for (const Layer& l : model.layers) b += kind == "qkv" ? l.qkv.bytes() : kind == "o" ? l.o.bytes() : kind == "gate_up" ? l.gate_up.bytes() : l.down.bytes();
+    *bytes = b;
+}
+
+// Named views for parity tests.
+std::vector<uint32_t> Engine::debug_read(const std::string& name) {
+    if (!cfg.host_only) VLT_CUDA(cudaStreamSynchronize(stream));
+    const size_t ms = cfg.max_seqs;
+    auto whole = [&](const Buffer& b, size_t words) { return b.read_vec<uint32_t>(0, words); };
+    if (name == "lens") return whole(s.lens, ms);
+    if (name == "feed") return whole(s.feed, ms * FEED_W);
+    if (name == "tree") return whole(s.tree, ms * FEED_W);
+    if (name == "gen") return whole(s.gen, ms * sizeof(GenState) / 4);
+    if (name == "path") return whole(s.path, ms * FEED_W);
+    if (name == "path_len") return whole(s.path_len, ms);
+    if (name == "on_path") return whole(s.on_path, last_plan_n);
+    if (name == "trace_len") return whole(s.trace_len, ms);
+    if (name == "meta") return whole(s.meta, 2 * size_t(last_plan_n));
+    if (name == "page_table") return whole(kv.page_table, ms * kv.max_pages);
+    if (name == "free_pages") return kv.free_pages;
+    const StepSet& st = sets[0];
+    auto in = [&](size_t off, size_t words) {
+        std::vector<uint32_t> v(words);
+        if (cfg.host_only) std::memcpy(v.data(), st.host_in + off, words * 4);
+        else st.dev_in.read(off, v.data(), words * 4);
+        return v;
+    };
+    const size_t n = last_plan_n;
+    if (name == "tokens") return in(st.o_tokens, n);
+    if (name == "tin") return in(st.o_tin, 2 * n);
+    if (name == "vis") return in(st.o_vis, n);
+    if (name == "head_rows") return in(st.o_head_rows, cfg.max_head_rows);
+    if (name == "hidden_rows") return in(st.o_hidden_rows, n);
+    if (name == "sample_rows") return in(st.o_sample_rows, cfg.max_head_rows * 6);
+    if (name == "tiles") return in(st.o_tiles, 2 * (cfg.max_step_tokens / 8 + ms + 1));
+    if (name == "runs") return in(st.o_runs, ms * 6);
+    if (name == "out_ids") return st.dev_out.read_vec<uint32_t>(st.o_out_ids / 4, cfg.max_head_rows);
+    if (name == "emitted") return st.dev_out.read_vec<uint32_t>(st.o_emitted / 4, ms);
+    throw Error("no engine array named " + name);
+}
+
+void Engine::debug_write(const std::string& name, size_t index, const uint32_t* data, size_t n) {
+    if (!cfg.host_only) VLT_CUDA(cudaStreamSynchronize(stream));
+    Buffer* b = name == "lens" ? &s.lens : name == "feed" ? &s.feed : name == "tree" ? &s.tree : name == "gen" ? &s.gen : nullptr;
+    if (!b) throw Error("engine array " + name + " is not writable");
+    b->write(index * 4, data, n * 4);
+}
+
+}  // namespace vlt

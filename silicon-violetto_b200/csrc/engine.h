@@ -1,0 +1,169 @@
+// The engine: sequences, the paged KV cache, the step planner and the step's kernel sequence.
+// Mirrors the reference's `Engine` (engine/src/engine.rs) with CUDA underneath.
+#pragma once
+#include <array>
+#include <memory>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "common.h"
+#include "kernels.h"
+#include "weights.h"
+
+namespace vlt {
+
+// engine/src/engine.rs:31-57.
+struct EngineConfig {
+    uint32_t max_seqs = 8, max_step_tokens = 512, max_chunk = 512, global_kv_tokens = 65536, max_seq_len = 131072, max_head_rows = 64;
+    int device = 0;
+    bool host_only = false;
+};
+
+// engine/src/engine.rs:59-95, with B200 knobs in place of the Apple-GPU ones.
+struct Tuning {
+    uint32_t spec_tokens = 32, spec_tokens_short = 8, spec_kv = 24576, spec_rows_long = 4;
+    uint32_t sm_count = 0, attn_keys_per_cta = 0, gemm_min_rows = 0;
+    bool plain_attention = false, use_graphs = false;
+};
+
+// engine/src/engine.rs:100-138.
+struct Sampling {
+    float temperature = 0.0f, top_p = 1.0f;
+    uint64_t seed = 0;
+    void check() const;
+    SampleRow row_at(uint32_t pos) const { return SampleRow{uint32_t(seed), uint32_t(seed >> 32), pos, temperature, top_p, NO_TOK}; }
+    SampleRow row_of(uint32_t tok) const { SampleRow r = row_at(0); r.tok = tok; return r; }
+};
+
+enum class Rows : uint32_t { None = 0, Last = 1, All = 2 };
+
+// engine/src/engine/plan.rs:8-18.
+struct PlanRun {
+    uint32_t seq;
+    const uint32_t* tokens;
+    uint32_t count;
+    Rows head;
+    bool verify;
+};
+
+// engine/src/engine/plan.rs:20-37.
+struct Plan {
+    uint32_t n = 0, n_head = 0, n_hidden = 0, n_runs = 0, tiles = 0, max_run = 0;
+    bool branches = false;
+    uint32_t keys_per_split = 0, max_splits = 1;  // the attention's key split
+};
+
+struct Seq {
+    uint32_t len = 0;  // positions with KV; while a speculative step is in flight, the most it can reach
+    std::vector<uint32_t> pages;
+    Sampling sampling;
+};
+
+// engine/src/engine/kv.rs:9-90, every layer paged.
+struct KvCache {
+    Buffer k, v, page_table;
+    std::vector<uint32_t> free_pages;
+    uint32_t n_pages = 0, max_pages = 0, page = 16;
+    void init(const EngineConfig& cfg, const ModelDesc& md, uint32_t n_layers, bool with_pool);
+    void reserve(uint32_t slot, std::vector<uint32_t>& pages, uint32_t len);
+    void release(const std::vector<uint32_t>& pages);
+};
+
+// One step's inputs in one block of pinned host memory mirrored on the device (one upload
+// per step), and its outputs (one download). engine/src/engine/buffers.rs:120-156.
+struct StepSet {
+    Buffer dev_in, dev_out;
+    uint8_t* host_in = nullptr;   // pinned
+    uint8_t* host_out = nullptr;  // pinned
+    size_t in_bytes = 0, out_bytes = 0;
+    size_t o_tokens = 0, o_tin = 0, o_vis = 0, o_head_rows = 0, o_hidden_rows = 0, o_sample_rows = 0, o_tiles = 0, o_runs = 0;  // byte offsets in *_in
+    size_t o_out_ids = 0, o_emitted = 0;                                                                                       // in *_out
+    cudaEvent_t start = nullptr, done = nullptr;
+    bool host_only = false;
+    void init(const EngineConfig& cfg);
+    void release();
+    template <typename T> T* in(size_t off) const { return reinterpret_cast<T*>(static_cast<uint8_t*>(dev_in.dev) + off); }
+    template <typename T> T* out(size_t off) const { return reinterpret_cast<T*>(static_cast<uint8_t*>(dev_out.dev) + off); }
+    template <typename T> T* hin(size_t off) const { return reinterpret_cast<T*>(host_in + off); }
+    template <typename T> T* hout(size_t off) const { return reinterpret_cast<T*>(host_out + off); }
+};
+
+struct StepOptions {
+    Rows head = Rows::Last, hidden = Rows::None;
+    bool read_logits = false, read_taps = false;
+};
+struct StepOutput {
+    std::vector<uint32_t> ids;
+    std::vector<float> logits, hidden;
+    std::vector<uint16_t> taps;
+    double gpu_seconds = 0;
+};
+
+class Engine {
+  public:
+    Engine(const std::string& weights, const EngineConfig& cfg, const Tuning& tuning);
+    ~Engine();
+    Engine(const Engine&) = delete;
+
+    std::string device_name() const;
+    uint32_t new_seq();
+    void free_seq(uint32_t id);
+    uint32_t seq_len(uint32_t id) const;
+    void set_sampling(uint32_t id, const Sampling& s);
+    void settle(uint32_t id, uint32_t unused);
+    StepOutput step(const std::vector<PlanRun>& runs, const StepOptions& opts);
+    // The same with each run's own head rows and verify flag, optionally followed by the replay drafter (tests).
+    StepOutput step_runs(const std::vector<PlanRun>& runs, const StepOptions& opts, const ReplayArgs* replay);
+    void upload_set(uint32_t set);
+    void load_drafter(const std::string& path);
+    bool has_drafter() const;
+    void encode_drafter(uint32_t set, const Plan& p);
+    void set_taps(bool on);
+    void bench_fill(uint32_t id, uint32_t len, uint32_t seed);
+    std::vector<uint32_t> sample_logits(const float* logits, const std::vector<std::pair<Sampling, uint32_t>>& rows);
+    void bench_matmul(const std::string& kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes);
+
+    // The generator's building blocks (engine/src/engine/generate.rs uses the same ones).
+    Plan plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden);
+    void encode_forward(uint32_t set, const Plan& p);   // uploads the set, queues the whole step
+    void encode_replay(uint32_t set, const Plan& p, const ReplayArgs& ra);
+    void commit(uint32_t set);                          // queues the result download and the step's end event
+    double wait(uint32_t set);                          // waits for it; GPU seconds of the step
+    void set_gen(uint32_t slot, const GenState& g);
+    void set_trace(uint32_t slot, const uint32_t* trace, uint32_t n);
+    std::vector<uint32_t> debug_read(const std::string& name);
+    void debug_write(const std::string& name, size_t index, const uint32_t* data, size_t n);
+    void check_device_error();
+
+    Model model;
+    EngineConfig cfg;
+    Tuning tuning;
+    uint32_t sm_count = 148;
+    KvCache kv;
+    std::vector<std::optional<Seq>> seqs;
+    std::array<StepSet, 3> sets;  // three rotate, so the CPU prepares step t+1 while the GPU runs step t
+    uint32_t skip = 0;
+    bool taps_on = false;
+    cudaStream_t stream = nullptr;
+
+    // Activations (engine/src/engine/buffers.rs:14-118) and per-slot state on the GPU.
+    struct Scratch {
+        Buffer h, qkv, attn, act, part, hfin_head, hfin_all, logits, taps, inv, meta;
+        Buffer lens, feed, tree, gen, path, path_len, on_path, trace, trace_len, err_flag;
+    } s;
+    Buffer rope_tab;
+    AttnMaps attn_maps;
+
+  private:
+    KvArgs kv_args() const;
+    void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out);
+    void encode_layer(uint32_t set, const Plan& p, uint32_t li);
+    void encode_tail(uint32_t set, const Plan& p);
+    void encode_sample(uint32_t set, uint32_t rows);
+    void attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const;
+    const Buffer* named(const std::string& name, uint32_t* set_off, size_t* words) const;
+    uint32_t last_plan_n = 0;
+};
+
+}  // namespace vlt

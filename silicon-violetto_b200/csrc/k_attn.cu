@@ -1,0 +1,370 @@
+// Decode / verify attention over the paged KV cache on the tensor cores.
+//
+// The reference's attn_verify (kernels.metal:891-1167) reads a sequence's cached keys once for
+// all rows of its run: the run's T <= 8 tokens x the G query heads of one kv head are packed into
+// the MMA's query dimension (column p = G i + h, :896), the cached keys are split across
+// threadgroups (:900), the run's own rows are attended under each token's visibility mask (:989),
+// and each threadgroup writes a partial per (token, head, split) that a second kernel merges.
+// This kernel keeps that decomposition and changes what B200 wants changed:
+//   - K and V pages (16 tokens x 64 dims, 2 KiB each) come in by TMA into 128-byte-swizzled
+//     shared memory, a four-stage ring per warp, and go to the MMAs through ldmatrix;
+//   - the softmax keeps a running maximum (a plain decoder has no q/k norm to bound the
+//     scores, kernels.metal:803-806), and partials carry (m, l, o[64]);
+//   - the step's own rows are already in the cache (written by qkv_post), so they are read like
+//     any other key and only the pages at or past the run's first position are masked.
+// grid (splits, kv heads, tiles), 4 warps; warp w takes pages w, w + 4, ... of its split.
+#include <cuda.h>
+
+#include "kernels.h"
+
+namespace vlt {
+
+static constexpr int ATTN_WARPS = 4;
+static constexpr int ATTN_STAGES = 4;
+static constexpr uint32_t PAGE = 16, HD = 64;
+static constexpr uint32_t STAGE_BYTES = 2 * PAGE * HD * 2;  // K then V
+static constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// A bounded wait: false if the barrier did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = SPIN_LIMIT) {
+    for (uint32_t i = 0; i < limit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map), "r"(x),
+                 "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// MT: m16 tiles of query columns (T * G <= 16 MT).
+template <int MT>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4..9.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t bars[ATTN_WARPS][ATTN_STAGES];
+
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, tile = blockIdx.z;
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
+    const uint32_t G = a.n_heads / a.kv.n_kv;
+    const uint32_t t0 = a.tiles[2 * tile], T = a.tiles[2 * tile + 1];
+    const uint32_t slot = a.meta[2 * t0], p0 = a.meta[2 * t0 + 1];
+    const uint32_t n_keys = p0 + T, n_cols = T * G;
+    const uint32_t k_begin = split * a.keys_per_split;
+    const uint32_t k_end = min(k_begin + a.keys_per_split, n_keys);
+
+    auto part_of = [&](uint32_t p) {  // column p's partial for this split
+        return a.part + ((size_t(t0 + p / G) * a.n_heads + kvh * G + p % G) * a.max_splits + split) * ATTN_PART;
+    };
+    if (k_begin >= n_keys) {  // nothing for this split: the merge skips m = -inf
+        for (uint32_t p = threadIdx.x; p < n_cols; p += blockDim.x) {
+            float* pp = part_of(p);
+            pp[0] = -INFINITY;
+            pp[1] = 0.0f;
+        }
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < ATTN_WARPS; w++)
+            for (int s = 0; s < ATTN_STAGES; s++) mbar_init(smem_u32(&bars[w][s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // This warp's pages: page_begin + warp, + ATTN_WARPS, ...
+    const uint32_t page_begin = k_begin / PAGE, page_end = (k_end + PAGE - 1) / PAGE;
+    const uint32_t my_pages = page_begin + warp < page_end ? (page_end - page_begin - warp + ATTN_WARPS - 1) / ATTN_WARPS : 0;
+    uint8_t* wbuf = smem + size_t(warp) * ATTN_STAGES * STAGE_BYTES;
+    const uint32_t* ptab = a.page_table + size_t(slot) * a.kv.max_pages;
+    const uint32_t row_base = a.layer * a.kv.n_pages;  // in pages
+
+    // Page ids are fetched 32 at a time (lane j holds the id of this warp's page 32 b + j), a batch
+    // ahead, so that no TMA issue waits on a page-table load.
+    auto load_ids = [&](uint32_t batch) {
+        const uint32_t i = batch * 32 + lane;
+        return i < my_pages ? ptab[page_begin + warp + i * ATTN_WARPS] : 0u;
+    };
+    uint32_t ids0 = load_ids(0), ids1 = load_ids(1), cur_batch = 0;
+    auto issue = [&](uint32_t i) {  // all lanes: page i of this warp into stage i % STAGES
+        if (i / 32 > cur_batch) {
+            ids0 = ids1;
+            cur_batch++;
+            ids1 = load_ids(cur_batch + 1);
+        }
+        const uint32_t pg = __shfl_sync(0xffffffffu, ids0, i % 32);
+        if (lane == 0) {
+            const int y = int(((row_base + pg) * a.kv.n_kv + kvh) * PAGE);
+            const uint32_t st = i % ATTN_STAGES, bar = smem_u32(&bars[warp][st]), dst = smem_u32(wbuf + st * STAGE_BYTES);
+            mbar_expect_tx(bar, STAGE_BYTES);
+            tma_load_2d(dst, &maps.k, 0, y, bar);
+            tma_load_2d(dst + PAGE * HD * 2, &maps.v, 0, y, bar);
+        }
+    };
+    for (uint32_t i = 0; i < min(my_pages, uint32_t(ATTN_STAGES)); i++) issue(i);
+
+    // Q as A operands: row p = G i + h is token i, head h of this kv head; RoPE at the token's
+    // position, scale * log2(e) folded in, rounded to bf16. A lane owns whole RoPE pairs.
+    uint32_t qf[MT][4][4];
+    uint32_t vmask[MT][2];  // the visibility masks of this lane's rows g and g + 8
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const uint32_t p = mt * 16 + g + 8 * half;
+            const bool ok = p < n_cols;
+            const uint32_t tok = t0 + (ok ? p / G : 0), hq = kvh * G + p % G;
+            vmask[mt][half] = ok ? a.vis[tok] : 0xffffffffu;
+            const uint32_t pos = a.meta[2 * tok + 1];
+            const float* qp = a.qkv + size_t(tok) * ((a.n_heads + 2 * a.kv.n_kv) * HD) + hq * HD;
+            const float2* cs = reinterpret_cast<const float2*>(a.rope) + size_t(pos) * (HD / 2);
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+#pragma unroll
+                for (int hi = 0; hi < 2; hi++) {
+                    const uint32_t d = 16 * ks + 8 * hi + 2 * t;
+                    uint32_t packed = 0;
+                    if (ok) {
+                        const float2 v = *reinterpret_cast<const float2*>(qp + d);
+                        const float2 c = cs[d / 2];
+                        const float r0 = __fadd_rn(__fmul_rn(c.x, v.x), __fmul_rn(c.y, v.y));
+                        const float r1 = __fsub_rn(__fmul_rn(c.x, v.y), __fmul_rn(c.y, v.x));
+                        packed = pack_bf16(__fmul_rn(r0, a.scale_log2), __fmul_rn(r1, a.scale_log2));
+                    }
+                    qf[mt][ks][half + 2 * hi] = packed;  // a0: (g, lo), a1: (g+8, lo), a2: (g, hi), a3: (g+8, hi)
+                }
+            }
+        }
+    }
+
+    float oacc[MT][8][4];
+    float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+        for (int dn = 0; dn < 8; dn++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) oacc[mt][dn][i] = 0.0f;
+        m_run[mt][0] = m_run[mt][1] = -INFINITY;
+        l_run[mt][0] = l_run[mt][1] = 0.0f;
+    }
+
+    // ldmatrix row addresses within a page: lane -> (matrix lane / 8, row lane % 8).
+    const uint32_t lm = lane >> 3, lr = lane & 7;
+    bool failed = false;
+    for (uint32_t i = 0; i < my_pages; i++) {
+        const uint32_t st = i % ATTN_STAGES, parity = (i / ATTN_STAGES) & 1;
+        if (!mbar_wait(smem_u32(&bars[warp][st]), parity)) { failed = true; break; }
+        const uint32_t kbase = smem_u32(wbuf + st * STAGE_BYTES), vbase = kbase + PAGE * HD * 2;
+        const uint32_t key0 = (page_begin + warp + i * ATTN_WARPS) * PAGE;
+
+        // S = Q K^T: n-tile nt = keys 8 nt .. 8 nt + 7 of the page.
+        float sacc[MT][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sacc[mt][nt][e] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t kb[4];  // b0, b1 of nt 0, then of nt 1
+            const uint32_t key = 8 * (lm >> 1) + lr, chunk = 2 * ks + (lm & 1);
+            ldmatrix_x4(kb, kbase + key * 128 + ((chunk ^ (key & 7)) << 4));
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                mma16816(sacc[mt][0], qf[mt][ks], kb[0], kb[1]);
+                mma16816(sacc[mt][1], qf[mt][ks], kb[2], kb[3]);
+            }
+        }
+        // Visibility: keys below p0 are seen by every row; key p0 + j by the rows whose mask has
+        // bit j; keys from p0 + T on by none.
+        if (key0 + PAGE > p0) {
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const uint32_t key = key0 + 8 * nt + 2 * t + (e & 1);
+                        const uint32_t mask = vmask[mt][e >> 1];
+                        const bool seen = key < p0 || (key < n_keys && ((mask >> (key - p0)) & 1u));
+                        if (!seen) sacc[mt][nt][e] = -INFINITY;
+                    }
+        }
+        // Online softmax; a row's statistics are shared by the four lanes of its quad.
+        uint32_t pa[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float mx = fmaxf(fmaxf(sacc[mt][0][2 * half], sacc[mt][0][2 * half + 1]), fmaxf(sacc[mt][1][2 * half], sacc[mt][1][2 * half + 1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run[mt][half], mx);
+                const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+                const float corr = fast_exp2(m_run[mt][half] - m_use);
+                m_run[mt][half] = m_new;
+                const float p00 = fast_exp2(sacc[mt][0][2 * half] - m_use), p01 = fast_exp2(sacc[mt][0][2 * half + 1] - m_use);
+                const float p10 = fast_exp2(sacc[mt][1][2 * half] - m_use), p11 = fast_exp2(sacc[mt][1][2 * half + 1] - m_use);
+                l_run[mt][half] = l_run[mt][half] * corr + (p00 + p01 + p10 + p11);
+                pa[mt][half] = pack_bf16(p00, p01);      // a0 / a1: keys 2t, 2t + 1
+                pa[mt][half + 2] = pack_bf16(p10, p11);  // a2 / a3: keys 8 + 2t, 9 + 2t
+                if (corr != 1.0f) {
+#pragma unroll
+                    for (int dn = 0; dn < 8; dn++) {
+                        oacc[mt][dn][2 * half] *= corr;
+                        oacc[mt][dn][2 * half + 1] *= corr;
+                    }
+                }
+            }
+        }
+        // O += P V: n-tile dn = dims 8 dn .. 8 dn + 7.
+#pragma unroll
+        for (int dp = 0; dp < 4; dp++) {
+            uint32_t vb[4];  // b0, b1 of dn = 2 dp, then of dn = 2 dp + 1
+            const uint32_t key = 8 * (lm & 1) + lr, chunk = 2 * dp + (lm >> 1);
+            ldmatrix_x4_trans(vb, vbase + key * 128 + ((chunk ^ (key & 7)) << 4));
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                mma16816(oacc[mt][2 * dp], pa[mt], vb[0], vb[1]);
+                mma16816(oacc[mt][2 * dp + 1], pa[mt], vb[2], vb[3]);
+            }
+        }
+        __syncwarp();
+        if (i + ATTN_STAGES < my_pages) issue(i + ATTN_STAGES);
+    }
+    if (failed) {
+        // A copy never arrived: say so, give the other copies in flight a bounded time, and leave.
+        if (lane == 0) {
+            atomicExch(a.err_flag, 1u);
+            for (int s = 0; s < ATTN_STAGES; s++) mbar_wait(smem_u32(&bars[warp][s]), 0, 1u << 16);
+        }
+        return;
+    }
+
+    // Merge the four warps through shared memory (the stage ring is free now), then write the partial.
+    __syncthreads();
+    float* ms = reinterpret_cast<float*>(smem);      // [warp][row]
+    float* ls = ms + ATTN_WARPS * MT * 16;           // [warp][row]
+    float* os = ls + ATTN_WARPS * MT * 16;           // [warp][row][HD + 1]
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            float l = l_run[mt][half];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const uint32_t row = mt * 16 + g + 8 * half;
+            if (t == 0) {
+                ms[warp * MT * 16 + row] = m_run[mt][half];
+                ls[warp * MT * 16 + row] = l;
+            }
+#pragma unroll
+            for (int dn = 0; dn < 8; dn++) {
+                float* o = os + (size_t(warp) * MT * 16 + row) * (HD + 1) + 8 * dn + 2 * t;
+                o[0] = oacc[mt][dn][2 * half];
+                o[1] = oacc[mt][dn][2 * half + 1];
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t idx = threadIdx.x; idx < n_cols * HD; idx += blockDim.x) {
+        const uint32_t p = idx / HD, d = idx % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * MT * 16 + p]);
+        float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; w++) {
+            const float mw = ms[w * MT * 16 + p];
+            if (mw == -INFINITY) continue;
+            const float wgt = exp2f(mw - mm);
+            ll += ls[w * MT * 16 + p] * wgt;
+            oo += os[(size_t(w) * MT * 16 + p) * (HD + 1) + d] * wgt;
+        }
+        float* pp = part_of(p);
+        if (d == 0) { pp[0] = mm; pp[1] = ll; }
+        pp[4 + d] = oo;
+    }
+}
+
+// A 2-D tensor [rows][inner] with a box of [box_rows][box_inner], optionally 128-byte swizzled.
+struct TmaEncoder {
+    typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    Fn fn = nullptr;
+    TmaEncoder() {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p)
+            throw Error("cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<Fn>(p);
+    }
+};
+
+void make_tensor_map_2d(void* out_map, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows, uint32_t elem_bytes,
+                        bool swizzle128) {
+    static TmaEncoder enc;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {inner * elem_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUresult r = enc.fn(static_cast<CUtensorMap*>(out_map), dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+}
+
+// The K and V pools as [all layers' rows][64] bf16, a box of one page.
+void attn_maps_init(AttnMaps* m, const uint16_t* k_cache, const uint16_t* v_cache, uint64_t total_rows) {
+    static_assert(sizeof(CUtensorMap) == sizeof(m->k), "tensor map size");
+    make_tensor_map_2d(&m->k, k_cache, HD, total_rows, HD, PAGE, 2, true);
+    make_tensor_map_2d(&m->v, v_cache, HD, total_rows, HD, PAGE, 2, true);
+}
+
+void launch_attn_mma(const AttnArgs& a, cudaStream_t s) {
+    const uint32_t G = a.n_heads / a.kv.n_kv;
+    const size_t smem = size_t(ATTN_WARPS) * ATTN_STAGES * STAGE_BYTES + 1024;
+    const dim3 grid(a.max_splits, a.kv.n_kv, a.n_tiles);
+    static bool configured = false;
+    if (!configured) {
+        VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        configured = true;
+    }
+    if (VERIFY_T * G <= 16) attn_mma_kernel<1><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps);
+    else attn_mma_kernel<2><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps);
+}
+
+}  // namespace vlt

@@ -1,0 +1,87 @@
+// Launchers of the CUDA kernels (all asynchronous on the given stream).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "common.h"
+#include "device.cuh"
+#include "weights.h"
+
+namespace vlt {
+
+// Epilogues of a matmul, engine/src/engine/kernels.rs:3-9 and kernels.metal:154-209.
+enum : uint32_t { EPI_NORM = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_HEAD = 4, EPI_RAW = 5 };
+
+// Y[t][row] = epilogue(W[row] . bf16(X[t])). X fp32 [n][k]; Y fp32 (SWIGLU: [n][m/2]).
+struct MatArgs {
+    const uint8_t* W;
+    const uint16_t* scales;  // int8: bf16 [m][k / group]
+    const float* X;          // [n][k]
+    const uint16_t* Xb;      // bf16 copy of X [n_pad][k] (tensor-core GEMM only)
+    float* Y;
+    const float* base;  // EPI_RESID: y = base + acc (may alias Y)
+    float* inv_out;     // EPI_NORM / EPI_SWIGLU / EPI_HEAD: 1 / rms(X[t]) is computed here ...
+    const float* inv_in;  // ... or, if not null, read from here (tensor-core GEMM)
+    uint16_t* Yb;       // optional bf16 copy of Y (feeds the next tensor-core GEMM)
+    uint32_t n, k, m, group;  // group: 0 for bf16 weights
+    uint32_t epi, vocab_real;
+    float eps;
+    bool int8;
+};
+
+void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
+                  const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, cudaStream_t s);
+void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
+                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, cudaStream_t s);
+void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* tiles, const uint32_t* vis, const float* rope, const uint16_t* k_cache,
+                       const uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n_tiles, uint32_t n_heads,
+                       float scale_log2, float* out, cudaStream_t s);
+// Tensor-core decode attention over paged KV, split over keys; then the merge of the splits.
+// The TMA descriptors of the K and V pools (opaque 128-byte CUtensorMap objects).
+struct alignas(64) AttnMaps {
+    alignas(64) uint8_t k[128];
+    alignas(64) uint8_t v[128];
+};
+void attn_maps_init(AttnMaps* m, const uint16_t* k_cache, const uint16_t* v_cache, uint64_t total_rows);
+void make_tensor_map_2d(void* out_map, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows, uint32_t elem_bytes,
+                        bool swizzle128);
+struct AttnArgs {
+    const AttnMaps* maps;  // host pointer
+    uint32_t* err_flag;    // device word set if a bounded wait ran out
+    const float* qkv;
+    const uint32_t* meta;
+    const uint32_t* tiles;
+    const uint32_t* vis;
+    const float* rope;
+    const uint16_t* k_cache;
+    const uint16_t* v_cache;
+    const uint32_t* page_table;
+    KvArgs kv;
+    uint32_t layer, n_tiles, n_heads;
+    float scale_log2;
+    uint32_t keys_per_split, max_splits;
+    float* part;  // [token][head][max_splits][PART]
+    float* out;   // [n][n_heads * hd]
+    uint16_t* out_b;  // optional bf16 copy
+    uint32_t n;
+};
+constexpr uint32_t ATTN_PART = 68;  // floats per partial: m, l, 2 pad, o[64]
+void launch_attn_mma(const AttnArgs& a, cudaStream_t s);
+void launch_attn_combine(const AttnArgs& a, cudaStream_t s);
+
+void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s);  // n <= 8, tensor cores fed from registers
+void launch_matmul_rows(const MatArgs& a, cudaStream_t s);                      // any n, scalar (cross-check, odd scale groups)
+// out[r] = in[rows ? rows[r] : r] as fp32 (and bf16); inv[r] = 1 / rms (kernels.metal:117-148).
+void launch_prep_rows(const float* in, const uint32_t* rows, uint32_t n, uint32_t k, float eps, float* out_f32, uint16_t* out_bf16, float* inv,
+                      bool normalize, bool round_out, cudaStream_t s);
+
+void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s);
+void launch_accept(const RunIn* runs, const uint32_t* tokens, uint32_t* out, uint32_t* lens, uint32_t* feed, GenState* gen, uint32_t* emitted,
+                   uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s);
+void launch_kv_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_cache, uint16_t* v_cache,
+                       const uint32_t* page_table, KvArgs kv, uint32_t n_runs, uint32_t n_layers, cudaStream_t s);
+void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed, const uint32_t* trace, const uint32_t* trace_len, ReplayArgs ra,
+                         uint32_t n_runs, uint32_t* tree, cudaStream_t s);
+void launch_kv_fill(uint16_t* k_cache, uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t n_layers, uint32_t slot, uint32_t from,
+                    uint32_t to, uint32_t seed, cudaStream_t s);
+
+}  // namespace vlt

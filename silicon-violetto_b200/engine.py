@@ -1,0 +1,441 @@
+"""ctypes mirror of the reference's public API (`violetto::{Engine, Generator, ...}`,
+engine/src/lib.rs:6-10) over libvioletto_b200.so's C ABI (include/violetto.h).
+
+Names, argument meaning and error behaviour follow the reference: a failing call raises
+`EngineError` with the message the Rust API would return in `Err(String)`. There is no CPU
+path: the library must be built (`build.build()`) and, except for host-only planning
+engines, a CUDA device must be present.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libvioletto_b200.so"
+
+FEED_ROW = 0xFFFF0000
+FEED_W = 16
+NO_TOK = 0xFFFFFFFF
+VERIFY_T = 8
+FLAG_HOST_ONLY = 1
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+class Rows:
+    NONE, LAST, ALL = 0, 1, 2
+
+
+class _Config(C.Structure):
+    _fields_ = [("max_seqs", C.c_uint32), ("max_step_tokens", C.c_uint32), ("max_chunk", C.c_uint32), ("global_kv_tokens", C.c_uint32),
+                ("max_seq_len", C.c_uint32), ("max_head_rows", C.c_uint32), ("device_ordinal", C.c_int32), ("flags", C.c_uint32)]
+
+
+class _Tuning(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("spec_tokens", "spec_tokens_short", "spec_kv", "spec_rows_long", "spec_policy_off", "sm_count",
+                                          "attn_keys_per_cta", "gemm_min_rows", "plain_attention", "use_graphs")]
+
+
+class _Sampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("seed", C.c_uint64)]
+
+
+class _Run(C.Structure):
+    _fields_ = [("seq", C.c_uint32), ("tokens", C.POINTER(C.c_uint32)), ("n_tokens", C.c_uint32)]
+
+
+class _StepOptions(C.Structure):
+    _fields_ = [("head", C.c_uint32), ("hidden", C.c_uint32), ("read_logits", C.c_uint32), ("read_taps", C.c_uint32)]
+
+
+class _StepOutput(C.Structure):
+    _fields_ = [("ids", C.POINTER(C.c_uint32)), ("ids_cap", C.c_uint32), ("n_ids", C.c_uint32), ("logits", C.POINTER(C.c_float)), ("logits_cap", C.c_uint64),
+                ("hidden", C.POINTER(C.c_float)), ("hidden_cap", C.c_uint64), ("n_hidden", C.c_uint32), ("taps", C.POINTER(C.c_uint16)),
+                ("taps_cap", C.c_uint64), ("gpu_seconds", C.c_double)]
+
+
+class _ModelDesc(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "vocab_real", "page_size")] + \
+               [("rms_eps", C.c_float), ("attn_scale", C.c_float), ("int8", C.c_uint32)]
+
+
+class _Request(C.Structure):
+    _fields_ = [("prompt_kind", C.c_uint32), ("prompt_tokens", C.POINTER(C.c_uint32)), ("n_prompt", C.c_uint32), ("resume_seq", C.c_uint32),
+                ("resume_token", C.c_uint32), ("max_tokens", C.c_uint32), ("stop", C.POINTER(C.c_uint32)), ("n_stop", C.c_uint32),
+                ("sampling", _Sampling), ("draft_kind", C.c_uint32), ("draft_rows", C.c_uint32), ("trace", C.POINTER(C.c_uint32)), ("n_trace", C.c_uint32)]
+
+
+class _Event(C.Structure):
+    _fields_ = [("kind", C.c_uint32), ("req", C.c_uint32), ("value", C.c_uint32)]
+
+
+class _StepStats(C.Structure):
+    _fields_ = [("tokens", C.c_uint32), ("decode", C.c_uint32), ("emitted", C.c_uint32), ("gpu_seconds", C.c_double), ("encode_seconds", C.c_double)]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The product library. Fails loudly if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise EngineError(f"{LIB_PATH} is missing: build it with silicon_violetto_b200.build.build() (nvcc, sm_100a)")
+        _lib = C.CDLL(str(LIB_PATH))
+        _lib.vlt_last_error.restype = C.c_char_p
+        _lib.vlt_seq_len.restype = C.c_uint32
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise EngineError(lib().vlt_last_error().decode())
+
+
+def _u32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def _ptr(a: np.ndarray, t=C.c_uint32):
+    return a.ctypes.data_as(C.POINTER(t))
+
+
+@dataclass
+class EngineConfig:
+    """engine/src/engine.rs:31-57."""
+    max_seqs: int = 8
+    max_step_tokens: int = 512
+    max_chunk: int = 512
+    global_kv_tokens: int = 65536
+    max_seq_len: int = 131072
+    max_head_rows: int = 64
+    device_ordinal: int = 0
+    host_only: bool = False
+
+
+@dataclass
+class Tuning:
+    """engine/src/engine.rs:59-95 (rows policy) plus the B200 knobs; 0 means the default."""
+    spec_tokens: int = 0
+    spec_tokens_short: int = 0
+    spec_kv: int = 0
+    spec_rows_long: int = 0
+    spec_policy_off: bool = False
+    sm_count: int = 0
+    attn_keys_per_cta: int = 0
+    gemm_min_rows: int = 0
+    plain_attention: bool = False
+    use_graphs: bool = False
+
+
+@dataclass
+class Sampling:
+    """engine/src/engine.rs:100-138."""
+    temperature: float = 0.0
+    top_p: float = 1.0
+    seed: int = 0
+
+    def c(self) -> _Sampling:
+        return _Sampling(self.temperature, self.top_p, self.seed)
+
+
+GREEDY = Sampling()
+
+
+@dataclass
+class Run:
+    seq: int
+    tokens: list
+
+
+@dataclass
+class StepOptions:
+    head: int = Rows.LAST
+    hidden: int = Rows.NONE
+    read_logits: bool = False
+    read_taps: bool = False
+
+
+@dataclass
+class StepOutput:
+    ids: np.ndarray
+    logits: np.ndarray
+    hidden: np.ndarray
+    taps: np.ndarray
+    gpu_seconds: float
+
+
+class Engine:
+    """engine/src/engine.rs `Engine`."""
+
+    def __init__(self, weights, cfg: EngineConfig | None = None, tuning: Tuning | None = None):
+        cfg = cfg or EngineConfig()
+        t = tuning or Tuning()
+        c = _Config(cfg.max_seqs, cfg.max_step_tokens, cfg.max_chunk, cfg.global_kv_tokens, cfg.max_seq_len, cfg.max_head_rows, cfg.device_ordinal,
+                    FLAG_HOST_ONLY if cfg.host_only else 0)
+        ct = _Tuning(t.spec_tokens, t.spec_tokens_short, t.spec_kv, t.spec_rows_long, int(t.spec_policy_off), t.sm_count, t.attn_keys_per_cta,
+                     t.gemm_min_rows, int(t.plain_attention), int(t.use_graphs))
+        self.h = C.c_void_p()
+        self.cfg = cfg
+        _check(lib().vlt_engine_new(str(weights).encode(), C.byref(c), C.byref(ct), C.byref(self.h)))
+        d = _ModelDesc()
+        _check(lib().vlt_model_desc(self.h, C.byref(d)))
+        self.desc = d
+
+    def close(self) -> None:
+        if getattr(self, "h", None):
+            lib().vlt_engine_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        self.close()
+
+    def device_name(self) -> str:
+        buf = C.create_string_buffer(256)
+        _check(lib().vlt_device_name(self.h, buf, C.c_size_t(256)))
+        return buf.value.decode()
+
+    def new_seq(self) -> int:
+        s = C.c_uint32()
+        _check(lib().vlt_seq_new(self.h, C.byref(s)))
+        return s.value
+
+    def free_seq(self, seq: int) -> None:
+        lib().vlt_seq_free(self.h, C.c_uint32(seq))
+
+    def seq_len(self, seq: int) -> int:
+        return int(lib().vlt_seq_len(self.h, C.c_uint32(seq)))
+
+    def set_sampling(self, seq: int, s: Sampling) -> None:
+        cs = s.c()
+        _check(lib().vlt_seq_set_sampling(self.h, C.c_uint32(seq), C.byref(cs)))
+
+    def set_taps(self, on: bool) -> None:
+        _check(lib().vlt_set_taps(self.h, C.c_uint32(int(on))))
+
+    def load_drafter(self, path) -> None:
+        _check(lib().vlt_load_drafter(self.h, str(path).encode()))
+
+    def has_drafter(self) -> bool:
+        return bool(lib().vlt_has_drafter(self.h))
+
+    def _runs(self, runs):
+        keep = [_u32(r.tokens if isinstance(r, Run) else r[1]) for r in runs]
+        arr = (_Run * len(runs))()
+        for i, r in enumerate(runs):
+            arr[i] = _Run(r.seq if isinstance(r, Run) else r[0], _ptr(keep[i]), len(keep[i]))
+        return arr, keep
+
+    def _out(self, n_tokens: int, opts: StepOptions):
+        d = self.desc
+        rows = self.cfg.max_head_rows
+        ids = np.zeros(rows, np.uint32)
+        logits = np.zeros(rows * d.vocab if opts.read_logits else 0, np.float32)
+        hidden = np.zeros(n_tokens * d.d_model if opts.hidden != Rows.NONE else 0, np.float32)
+        taps = np.zeros(n_tokens * d.d_model if opts.read_taps else 0, np.uint16)
+        out = _StepOutput(_ptr(ids), rows, 0, _ptr(logits, C.c_float), logits.size, _ptr(hidden, C.c_float), hidden.size, 0, _ptr(taps, C.c_uint16), taps.size, 0.0)
+        return out, (ids, logits, hidden, taps)
+
+    def _result(self, out, bufs, n_tokens, opts) -> StepOutput:
+        ids, logits, hidden, taps = bufs
+        d = self.desc
+        return StepOutput(ids[:out.n_ids].copy(), logits[:out.n_ids * d.vocab].reshape(-1, d.vocab) if opts.read_logits else logits,
+                          hidden[:out.n_hidden * d.d_model].reshape(-1, d.d_model), taps.reshape(-1, d.d_model) if taps.size else taps, out.gpu_seconds)
+
+    def step(self, runs, opts: StepOptions | None = None) -> StepOutput:
+        """engine.rs:310-314: one synchronous step of CPU-fed runs."""
+        opts = opts or StepOptions()
+        arr, keep = self._runs(runs)
+        n = sum(len(k) for k in keep)
+        co = _StepOptions(opts.head, opts.hidden, int(opts.read_logits), int(opts.read_taps))
+        out, bufs = self._out(n, opts)
+        _check(lib().vlt_step(self.h, arr, C.c_uint32(len(runs)), C.byref(co), C.byref(out)))
+        return self._result(out, bufs, n, opts)
+
+    def bench_fill(self, seq: int, n: int, seed: int = 0) -> None:
+        _check(lib().vlt_bench_fill(self.h, C.c_uint32(seq), C.c_uint32(n), C.c_uint32(seed)))
+
+    def sample_logits(self, logits, rows) -> np.ndarray:
+        """hooks.rs:41-54: rows is a list of (Sampling, position of the drawn token)."""
+        n = len(rows)
+        cs = (_Sampling * n)(*[s.c() for s, _ in rows])
+        pos = _u32([p for _, p in rows])
+        out = np.zeros(n, np.uint32)
+        lp = None
+        if logits is not None:
+            logits = np.ascontiguousarray(logits, np.float32)
+            if logits.size != n * self.desc.vocab:
+                raise EngineError(f"{n} rows of logits need {n * self.desc.vocab} values")
+            lp = _ptr(logits, C.c_float)
+        _check(lib().vlt_sample_logits(self.h, lp, cs, _ptr(pos), C.c_uint32(n), _ptr(out)))
+        return out
+
+    def set_profile_skip(self, mask: int) -> None:
+        lib().vlt_set_profile_skip(self.h, C.c_uint32(mask))
+
+    def bench_matmul(self, kind: str, n: int, variant: int = 0, reps: int = 5):
+        secs, nbytes = C.c_double(), C.c_uint64()
+        _check(lib().vlt_bench_matmul(self.h, kind.encode(), C.c_uint32(n), C.c_uint32(variant), C.c_uint32(reps), C.byref(secs), C.byref(nbytes)))
+        return secs.value, nbytes.value
+
+    def generator(self) -> "Generator":
+        return Generator(self)
+
+    # ---- inspection (parity tests)
+    def debug_read(self, name: str) -> np.ndarray:
+        cap = 1 << 16
+        while True:
+            buf = np.zeros(cap, np.uint32)
+            n = C.c_uint64()
+            rc = lib().vlt_debug_read(self.h, name.encode(), _ptr(buf), C.c_uint64(cap), C.byref(n))
+            if rc != 0 and n.value > cap:
+                cap = int(n.value)
+                continue
+            _check(rc)
+            return buf[:n.value].copy()
+
+    def debug_write(self, name: str, index: int, data) -> None:
+        d = _u32(data)
+        _check(lib().vlt_debug_write(self.h, name.encode(), C.c_uint64(index), _ptr(d), C.c_uint64(d.size)))
+
+    def debug_plan(self, runs, hidden: int = Rows.NONE) -> None:
+        """runs: (seq, tokens, head Rows, verify)."""
+        arr, keep = self._runs([(r[0], r[1]) for r in runs])
+        heads = _u32([r[2] for r in runs])
+        verify = _u32([1 if r[3] else 0 for r in runs])
+        _check(lib().vlt_debug_plan(self.h, arr, _ptr(verify), _ptr(heads), C.c_uint32(len(runs)), C.c_uint32(hidden)))
+
+    def debug_step(self, runs, opts: StepOptions | None = None, replay=None) -> StepOutput:
+        """runs: (seq, tokens, head Rows, verify); replay: None or (mistake rate, seed)."""
+        opts = opts or StepOptions()
+        arr, keep = self._runs([(r[0], r[1]) for r in runs])
+        n = sum(len(k) for k in keep)
+        heads = _u32([r[2] for r in runs])
+        verify = _u32([1 if r[3] else 0 for r in runs])
+        co = _StepOptions(0, opts.hidden, int(opts.read_logits), int(opts.read_taps))
+        out, bufs = self._out(n, opts)
+        rate, seed = replay if replay else (0.0, 0)
+        _check(lib().vlt_debug_step(self.h, arr, _ptr(verify), _ptr(heads), C.c_uint32(len(runs)), C.byref(co), C.c_uint32(1 if replay else 0),
+                                    C.c_float(rate), C.c_uint32(seed), C.byref(out)))
+        return self._result(out, bufs, n, opts)
+
+    def settle(self, seq: int, unused: int) -> None:
+        lib().vlt_debug_settle(self.h, C.c_uint32(seq), C.c_uint32(unused))
+
+    def set_gen(self, slot: int, remaining: int, stop=()) -> None:
+        st = _u32(list(stop))
+        _check(lib().vlt_debug_set_gen(self.h, C.c_uint32(slot), C.c_uint32(remaining), _ptr(st), C.c_uint32(st.size)))
+
+    def set_trace(self, slot: int, trace) -> None:
+        t = _u32(trace)
+        _check(lib().vlt_debug_set_trace(self.h, C.c_uint32(slot), _ptr(t), C.c_uint32(t.size)))
+
+
+class Draft:
+    """engine/src/engine/generate.rs:24-42."""
+    NONE, REPLAY, MODEL = 0, 1, 2
+
+
+class Finish:
+    STOP, LENGTH = 0, 1
+
+
+@dataclass
+class Request:
+    """engine/src/engine/generate.rs:12-21; prompt is a token list, or ("resume", seq, token)."""
+    prompt: object
+    max_tokens: int
+    stop: list = field(default_factory=list)
+    sampling: Sampling = field(default_factory=Sampling)
+    draft: int = Draft.NONE
+    rows: int = 1
+    trace: list = field(default_factory=list)
+
+
+@dataclass
+class Event:
+    kind: str  # "token" or "done"
+    req: int
+    value: int
+
+
+class Generator:
+    """engine/src/engine/generate.rs `Generator`."""
+
+    def __init__(self, engine: Engine):
+        self.engine = engine
+        self.h = C.c_void_p()
+        _check(lib().vlt_generator_new(engine.h, C.byref(self.h)))
+
+    def close(self) -> None:
+        if getattr(self, "h", None):
+            lib().vlt_generator_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        self.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def submit(self, req: Request) -> int:
+        r = _Request()
+        keep = []
+        if isinstance(req.prompt, tuple) and req.prompt and req.prompt[0] == "resume":
+            r.prompt_kind, r.resume_seq, r.resume_token = 1, req.prompt[1], req.prompt[2]
+        else:
+            p = _u32(req.prompt)
+            keep.append(p)
+            r.prompt_kind, r.prompt_tokens, r.n_prompt = 0, _ptr(p), p.size
+        st, tr = _u32(req.stop), _u32(req.trace)
+        keep += [st, tr]
+        r.max_tokens, r.stop, r.n_stop = req.max_tokens, _ptr(st), st.size
+        r.sampling = req.sampling.c()
+        r.draft_kind, r.draft_rows, r.trace, r.n_trace = req.draft, req.rows, _ptr(tr), tr.size
+        rid = C.c_uint32()
+        _check(lib().vlt_generator_submit(self.h, C.byref(r), C.byref(rid)))
+        return rid.value
+
+    def cancel(self, req: int) -> None:
+        lib().vlt_generator_cancel(self.h, C.c_uint32(req))
+
+    def step(self) -> list:
+        cap = 4096
+        ev = (_Event * cap)()
+        n = C.c_uint32()
+        _check(lib().vlt_generator_step(self.h, ev, C.c_uint32(cap), C.byref(n)))
+        return [Event("token" if ev[i].kind == 0 else "done", ev[i].req, ev[i].value) for i in range(n.value)]
+
+    def is_idle(self) -> bool:
+        return bool(lib().vlt_generator_is_idle(self.h))
+
+    def counts(self):
+        q, r = C.c_uint32(), C.c_uint32()
+        lib().vlt_generator_counts(self.h, C.byref(q), C.byref(r))
+        return q.value, r.value
+
+    def take_stats(self) -> list:
+        out = []
+        while True:
+            buf = (_StepStats * 1024)()
+            n = C.c_uint32()
+            _check(lib().vlt_generator_stats(self.h, buf, C.c_uint32(1024), C.byref(n)))
+            out += [dict(tokens=b.tokens, decode=bool(b.decode), emitted=b.emitted, gpu_seconds=b.gpu_seconds, encode_seconds=b.encode_seconds) for b in buf[:n.value]]
+            if n.value < 1024:
+                return out
+
+    def set_hold(self, hold: bool) -> None:
+        lib().vlt_generator_set_hold(self.h, C.c_uint32(int(hold)))
+
+    def set_replay_mistakes(self, rate: float, seed: int) -> None:
+        lib().vlt_generator_set_replay_mistakes(self.h, C.c_float(rate), C.c_uint32(seed))
