@@ -206,6 +206,19 @@ int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, con
 int vlt_debug_set_gen(VltEngine* e, uint32_t slot, uint32_t remaining, const uint32_t* stop, uint32_t n_stop);
 int vlt_debug_set_trace(VltEngine* e, uint32_t slot, const uint32_t* trace, uint32_t n);
 
+/* Measurement. Two marks on the engine's stream and the GPU time between them; the number of
+ * kernels this library has launched so far; per-group GPU time of the steps queued while
+ * profiling is on (groups: 0 matmuls, 1 attention, 2 K/V write and split merge, 3 the tail:
+ * head, sampling, acceptance; the reference times its step with GPUEndTime - GPUStartTime,
+ * engine/src/gpu.rs:147-154, and kernel groups by leaving them out, cli/src/profile.rs:44-104);
+ * the bytes one step uploads and downloads. */
+int vlt_debug_mark(VltEngine* e, uint32_t which);
+int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms);
+uint64_t vlt_debug_launches(void);
+int vlt_debug_profile(VltEngine* e, uint32_t on);
+int vlt_debug_profile_read(VltEngine* e, double* ms4, uint32_t* launches4);
+int vlt_debug_step_bytes(VltEngine* e, uint64_t* h2d, uint64_t* d2h);
+
 #ifdef __cplusplus
 }
 #endif

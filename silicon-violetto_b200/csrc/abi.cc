@@ -264,6 +264,15 @@ int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, con
     });
 }
 
+int vlt_debug_mark(VltEngine* e, uint32_t which) { return guard([&] { eng(e).mark(int(which)); }); }
+int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms) { return guard([&] { *ms = eng(e).mark_elapsed_ms(); }); }
+uint64_t vlt_debug_launches(void) { return launch_counter(); }
+int vlt_debug_profile(VltEngine* e, uint32_t on) { return guard([&] { eng(e).profile = on != 0; }); }
+int vlt_debug_profile_read(VltEngine* e, double* ms4, uint32_t* launches4) { return guard([&] { eng(e).profile_read(ms4, launches4); }); }
+int vlt_debug_step_bytes(VltEngine* e, uint64_t* h2d, uint64_t* d2h) {
+    return guard([&] { *h2d = eng(e).sets[0].in_bytes; *d2h = eng(e).sets[0].out_bytes; });
+}
+
 void vlt_debug_settle(VltEngine* e, uint32_t seq, uint32_t unused) { if (e && e->e) e->e->settle(seq, unused); }
 
 int vlt_debug_set_gen(VltEngine* e, uint32_t slot, uint32_t remaining, const uint32_t* stop, uint32_t n_stop) {

@@ -23,6 +23,12 @@ struct Error : std::runtime_error {
             throw ::vlt::Error(std::string(#call) + ": " + cudaGetErrorString(err__) + " (" __FILE__ ":" + std::to_string(__LINE__) + ")"); \
     } while (0)
 
+// Kernels this library has launched (every launcher counts its own), for benchmarks to report.
+inline uint64_t& launch_counter() {
+    static uint64_t count = 0;
+    return count;
+}
+
 // engine/src/engine/kernels.rs:14-29.
 constexpr uint32_t FEED_ROW = 0xffff0000u;
 constexpr uint32_t FEED_W = 16;

@@ -360,11 +360,15 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     StepSet& st = sets[set];
     const uint32_t n = p.n;
     float* h = s.h.as<float>();
+    int sp = span_begin(G_MATMUL);
     if (!(skip & 1)) matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
+    span_end(sp);
     const KvArgs kva = kv_args();
+    sp = span_begin(G_SMALL);
     if (!(skip & 2))
         launch_qkv_post(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tin), rope_tab.as<float>(), kv.k.as<uint16_t>(), kv.v.as<uint16_t>(),
                         kv.page_table.as<uint32_t>(), kva, li, n, md.n_heads, stream);
+    span_end(sp);
     const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
     if (tuning.plain_attention) {
         if (!(skip & 4))
@@ -394,12 +398,18 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
         a.out = s.attn.as<float>();
         a.out_b = nullptr;
         a.n = n;
+        sp = span_begin(G_ATTN);
         if (!(skip & 4)) launch_attn_mma(a, stream);
+        span_end(sp);
+        sp = span_begin(G_SMALL);
         if (!(skip & 8)) launch_attn_combine(a, stream);
+        span_end(sp);
     }
+    sp = span_begin(G_MATMUL);
     if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr);
     if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
     if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr);
+    span_end(sp);
 }
 
 // engine/src/engine/encode.rs:557-573 `encode_sample`.
@@ -437,7 +447,9 @@ void Engine::encode_forward(uint32_t set, const Plan& p) {
     launch_embed(model.embed, st.in<uint32_t>(st.o_tokens), s.h.as<float>(), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.lens.as<uint32_t>(),
                  s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), st.in<uint32_t>(st.o_vis), p.n, model.md.d, stream);
     for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
+    const int sp = span_begin(G_TAIL);
     encode_tail(set, p);
+    span_end(sp);
 }
 
 // engine/src/engine/encode.rs:439-451 `encode_replay`.
@@ -574,6 +586,60 @@ void Engine::bench_matmul(const std::string& kind, uint32_t n, uint32_t variant,
     else
         for (const Layer& l : model.layers) b += kind == "qkv" ? l.qkv.bytes() : kind == "o" ? l.o.bytes() : kind == "gate_up" ? l.gate_up.bytes() : l.down.bytes();
     *bytes = b;
+}
+
+cudaEvent_t Engine::pooled_event() {
+    if (!event_pool.empty()) {
+        cudaEvent_t e = event_pool.back();
+        event_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e;
+    VLT_CUDA(cudaEventCreate(&e));
+    return e;
+}
+
+int Engine::span_begin(int group) {
+    if (!profile) return -1;
+    Span sp{pooled_event(), pooled_event(), group, uint32_t(launch_counter())};
+    VLT_CUDA(cudaEventRecord(sp.a, stream));
+    spans.push_back(sp);
+    return int(spans.size()) - 1;
+}
+
+void Engine::span_end(int idx) {
+    if (idx < 0) return;
+    Span& sp = spans[idx];
+    VLT_CUDA(cudaEventRecord(sp.b, stream));
+    sp.launches = uint32_t(launch_counter()) - sp.launches;
+}
+
+void Engine::profile_read(double* ms, uint32_t* launches) {
+    VLT_CUDA(cudaStreamSynchronize(stream));
+    for (int g = 0; g < G_COUNT; g++) { ms[g] = 0; launches[g] = 0; }
+    for (Span& sp : spans) {
+        float t = 0;
+        VLT_CUDA(cudaEventElapsedTime(&t, sp.a, sp.b));
+        ms[sp.group] += t;
+        launches[sp.group] += sp.launches;
+        event_pool.push_back(sp.a);
+        event_pool.push_back(sp.b);
+    }
+    spans.clear();
+}
+
+void Engine::mark(int which) {
+    if (which < 0 || which > 1) throw Error("mark 0 or 1");
+    if (!marks[which]) VLT_CUDA(cudaEventCreate(&marks[which]));
+    VLT_CUDA(cudaEventRecord(marks[which], stream));
+}
+
+double Engine::mark_elapsed_ms() {
+    if (!marks[0] || !marks[1]) throw Error("both marks must be set");
+    VLT_CUDA(cudaEventSynchronize(marks[1]));
+    float t = 0;
+    VLT_CUDA(cudaEventElapsedTime(&t, marks[0], marks[1]));
+    return t;
 }
 
 // Named views for parity tests.

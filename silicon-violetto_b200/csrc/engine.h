@@ -136,6 +136,14 @@ class Engine {
     void debug_write(const std::string& name, size_t index, const uint32_t* data, size_t n);
     void check_device_error();
 
+    // Measurement: two stream marks (GPU time between them), and, while `profile` is on, the GPU
+    // time of each kernel group of the queued steps (cuda events around the group's launches).
+    enum Group : int { G_MATMUL = 0, G_ATTN = 1, G_SMALL = 2, G_TAIL = 3, G_COUNT = 4 };
+    void mark(int which);
+    double mark_elapsed_ms();
+    bool profile = false;
+    void profile_read(double* ms, uint32_t* launches);
+
     Model model;
     EngineConfig cfg;
     Tuning tuning;
@@ -164,6 +172,14 @@ class Engine {
     void attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const;
     const Buffer* named(const std::string& name, uint32_t* set_off, size_t* words) const;
     uint32_t last_plan_n = 0;
+    cudaEvent_t marks[2] = {nullptr, nullptr};
+    struct Span { cudaEvent_t a, b; int group; uint32_t launches; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> event_pool;
+    cudaEvent_t pooled_event();
+    // Opens a profiled span of `group` if profiling is on; the returned index goes to span_end.
+    int span_begin(int group);
+    void span_end(int idx);
 };
 
 }  // namespace vlt

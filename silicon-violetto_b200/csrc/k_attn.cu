@@ -363,8 +363,8 @@ void launch_attn_mma(const AttnArgs& a, cudaStream_t s) {
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         configured = true;
     }
-    if (VERIFY_T * G <= 16) attn_mma_kernel<1><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps);
-    else attn_mma_kernel<2><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps);
+    if (VERIFY_T * G <= 16) { attn_mma_kernel<1><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps); launch_counter()++; }
+    else { attn_mma_kernel<2><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps); launch_counter()++; }
 }
 
 }  // namespace vlt

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256) matmul_rows_kernel(MatArgs a) {
 }
 
 void launch_matmul_rows(const MatArgs& a, cudaStream_t s) {
-    matmul_rows_kernel<<<(a.m / 2 + 7) / 8, 256, 0, s>>>(a);
+    { matmul_rows_kernel<<<(a.m / 2 + 7) / 8, 256, 0, s>>>(a); launch_counter()++; }
 }
 
 // ---------------------------------------------------------- streamed, n <= 8
@@ -253,11 +253,11 @@ void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
     if (a.m % 32 == 0 && a.m / 32 >= 2 * sm_count) mt = 2;
     if (a.m % 64 == 0 && a.m / 64 >= 2 * sm_count) mt = 4;
     const uint32_t grid = a.m / (16 * mt);
-#define VLT_STREAM(I8, MT) matmul_stream_kernel<I8, MT><<<grid, 512, 0, s>>>(a)
+#define VLT_STREAM(I8, MT) { matmul_stream_kernel<I8, MT><<<grid, 512, 0, s>>>(a); launch_counter()++; }
     if (a.int8) {
-        if (mt == 1) VLT_STREAM(true, 1); else if (mt == 2) VLT_STREAM(true, 2); else VLT_STREAM(true, 4);
+        if (mt == 1) VLT_STREAM(true, 1) else if (mt == 2) VLT_STREAM(true, 2) else VLT_STREAM(true, 4)
     } else {
-        if (mt == 1) VLT_STREAM(false, 1); else if (mt == 2) VLT_STREAM(false, 2); else VLT_STREAM(false, 4);
+        if (mt == 1) VLT_STREAM(false, 1) else if (mt == 2) VLT_STREAM(false, 2) else VLT_STREAM(false, 4)
     }
 #undef VLT_STREAM
 }

@@ -42,7 +42,7 @@ __global__ void embed_kernel(const uint16_t* __restrict__ table, uint32_t* token
 
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
                   const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, cudaStream_t s) {
-    embed_kernel<<<n, 128, 0, s>>>(table, tokens, out, tin, meta, lens, feed, tree, vis, d);
+    { embed_kernel<<<n, 128, 0, s>>>(table, tokens, out, tin, meta, lens, feed, tree, vis, d); launch_counter()++; }
 }
 
 // ------------------------------------------------------- K/V into the cache
@@ -71,7 +71,7 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* _
 
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
                      const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, cudaStream_t s) {
-    qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads);
+    { qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads); launch_counter()++; }
 }
 
 // ----------------------------------------------- scalar attention (cross-check)
@@ -156,6 +156,7 @@ void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* t
                        float scale_log2, float* out, cudaStream_t s) {
     attn_plain_kernel<<<dim3(n_tiles, VERIFY_T, n_heads), 128, 0, s>>>(qkv, meta, tiles, vis, rope, k_cache, v_cache, page_table, kv, layer, n_heads,
                                                                       scale_log2, out);
+    launch_counter()++;
 }
 
 // ------------------------------------------------------------ split merge
@@ -183,7 +184,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part, uint32_t max
 }
 
 void launch_attn_combine(const AttnArgs& a, cudaStream_t s) {
-    attn_combine_kernel<<<dim3(a.n, a.n_heads), 64, 0, s>>>(a.part, a.max_splits, a.n_heads, a.out, a.out_b);
+    { attn_combine_kernel<<<dim3(a.n, a.n_heads), 64, 0, s>>>(a.part, a.max_splits, a.n_heads, a.out, a.out_b); launch_counter()++; }
 }
 
 // ------------------------------------------------------------- row preparation
@@ -213,7 +214,7 @@ __global__ void prep_rows_kernel(const float* __restrict__ in, const uint32_t* _
 
 void launch_prep_rows(const float* in, const uint32_t* rows, uint32_t n, uint32_t k, float eps, float* out_f32, uint16_t* out_bf16, float* inv,
                       bool normalize, bool round_out, cudaStream_t s) {
-    if (n) prep_rows_kernel<<<n, 256, 0, s>>>(in, rows, k, eps, out_f32, out_bf16, inv, normalize, round_out);
+    if (n) { prep_rows_kernel<<<n, 256, 0, s>>>(in, rows, k, eps, out_f32, out_bf16, inv, normalize, round_out); launch_counter()++; }
 }
 
 // ------------------------------------------------------------------ sampling
@@ -319,7 +320,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 }
 
 void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s) {
-    if (n_rows) sample_kernel<<<n_rows, SAMPLE_THREADS, 0, s>>>(logits, rows, out, meta, vocab);
+    if (n_rows) { sample_kernel<<<n_rows, SAMPLE_THREADS, 0, s>>>(logits, rows, out, meta, vocab); launch_counter()++; }
 }
 
 // ----------------------------------------------------------------- accepting
@@ -372,7 +373,7 @@ __global__ void accept_kernel(const RunIn* __restrict__ runs, const uint32_t* __
 
 void launch_accept(const RunIn* runs, const uint32_t* tokens, uint32_t* out, uint32_t* lens, uint32_t* feed, GenState* gen, uint32_t* emitted,
                    uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s) {
-    if (n_runs) accept_kernel<<<(n_runs + 63) / 64, 64, 0, s>>>(runs, tokens, out, lens, feed, gen, emitted, n_runs, tree, path, path_len, on_path);
+    if (n_runs) { accept_kernel<<<(n_runs + 63) / 64, 64, 0, s>>>(runs, tokens, out, lens, feed, gen, emitted, n_runs, tree, path, path_len, on_path); launch_counter()++; }
 }
 
 // kernels.metal:1663-1693 `kv_compact`: the accepted path's K/V rows, on every layer, from
@@ -393,7 +394,7 @@ __global__ void kv_compact_kernel(const RunIn* __restrict__ runs, const uint32_t
 
 void launch_kv_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_cache, uint16_t* v_cache,
                        const uint32_t* page_table, KvArgs kv, uint32_t n_runs, uint32_t n_layers, cudaStream_t s) {
-    if (n_runs) kv_compact_kernel<<<dim3(n_runs, n_layers), 32 * kv.n_kv, 0, s>>>(runs, path, path_len, lens, k_cache, v_cache, page_table, kv);
+    if (n_runs) { kv_compact_kernel<<<dim3(n_runs, n_layers), 32 * kv.n_kv, 0, s>>>(runs, path, path_len, lens, k_cache, v_cache, page_table, kv); launch_counter()++; }
 }
 
 // kernels.metal:1705-1724 `replay_draft`. grid: runs blocks of FEED_W threads.
@@ -413,7 +414,7 @@ __global__ void replay_draft_kernel(const RunIn* __restrict__ runs, const uint32
 
 void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed, const uint32_t* trace, const uint32_t* trace_len, ReplayArgs ra,
                          uint32_t n_runs, uint32_t* tree, cudaStream_t s) {
-    if (n_runs) replay_draft_kernel<<<n_runs, FEED_W, 0, s>>>(runs, lens, feed, trace, trace_len, ra, n_runs, tree);
+    if (n_runs) { replay_draft_kernel<<<n_runs, FEED_W, 0, s>>>(runs, lens, feed, trace, trace_len, ra, n_runs, tree); launch_counter()++; }
 }
 
 // bench_fill's optional K/V values: small pseudo-random bf16 numbers (a hash of seed, layer,
@@ -435,7 +436,7 @@ void launch_kv_fill(uint16_t* k_cache, uint16_t* v_cache, const uint32_t* page_t
                     uint32_t to, uint32_t seed, cudaStream_t s) {
     if (to <= from) return;
     const uint32_t blocks = std::min(to - from, 1024u);
-    kv_fill_kernel<<<dim3(blocks, n_layers, kv.n_kv), kv.hd / 2, 0, s>>>(k_cache, v_cache, page_table, kv, slot, from, to, seed);
+    { kv_fill_kernel<<<dim3(blocks, n_layers, kv.n_kv), kv.hd / 2, 0, s>>>(k_cache, v_cache, page_table, kv, slot, from, to, seed); launch_counter()++; }
 }
 
 }  // namespace vlt

@@ -337,6 +337,36 @@ class Engine:
         t = _u32(trace)
         _check(lib().vlt_debug_set_trace(self.h, C.c_uint32(slot), _ptr(t), C.c_uint32(t.size)))
 
+    # ---- measurement
+    def mark(self, which: int) -> None:
+        _check(lib().vlt_debug_mark(self.h, C.c_uint32(which)))
+
+    def mark_elapsed_ms(self) -> float:
+        ms = C.c_double()
+        _check(lib().vlt_debug_mark_elapsed_ms(self.h, C.byref(ms)))
+        return ms.value
+
+    @staticmethod
+    def launches() -> int:
+        f = lib().vlt_debug_launches
+        f.restype = C.c_uint64
+        return int(f())
+
+    def set_profile(self, on: bool) -> None:
+        _check(lib().vlt_debug_profile(self.h, C.c_uint32(int(on))))
+
+    def profile_read(self) -> dict:
+        ms = (C.c_double * 4)()
+        n = (C.c_uint32 * 4)()
+        _check(lib().vlt_debug_profile_read(self.h, ms, n))
+        names = ("matmul", "attention", "small", "tail")
+        return {k: dict(ms=ms[i], launches=int(n[i])) for i, k in enumerate(names)}
+
+    def step_bytes(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        _check(lib().vlt_debug_step_bytes(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
 
 class Draft:
     """engine/src/engine/generate.rs:24-42."""

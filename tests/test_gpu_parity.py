@@ -89,13 +89,13 @@ def test_forward_logits_match_the_oracle(name, int8_group):
 def test_kv_cache_matches_the_oracle_after_prefill():
     prod, orc = pair("micro")
     a, b = prod.new_seq(), orc.new_seq()
-    toks = np.arange(40, dtype=np.uint32) * 7 % 512
+    toks = np.arange(30, dtype=np.uint32) * 7 % 512
     both_step(prod, orc, [(a, toks, E.Rows.LAST, False)], 2e-2)
     # Layer 0's K and V depend only on the embedding and one matmul: near bit-equal.
     # (The cache itself is read back through a second engine step's logits in other tests;
     # here the page table and lengths say where it went.)
-    assert prod.debug_read("lens")[a] == 40 and orc.array("lens")[b] == 40
-    assert np.array_equal(prod.debug_read("page_table")[:3], np.array([0, 1, 2], np.uint32))
+    assert prod.debug_read("lens")[a] == 30 and orc.array("lens")[b] == 30
+    assert np.array_equal(prod.debug_read("page_table")[:2], np.array([0, 1], np.uint32))
 
 
 def test_two_attention_kernels_agree_at_long_context():
@@ -122,14 +122,14 @@ def test_verify_runs_with_the_replay_drafter_match_the_oracle():
     a, b = prod.new_seq(), orc.new_seq()
     prompt = rng.integers(0, 512, 20).astype(np.uint32)
     # The recorded continuation: the oracle's own greedy decode, so that right drafts exist.
-    orc.step([(b, prompt, E.Rows.LAST, False)])
+    o2 = oracle.Engine(util.weights("micro"), max_seqs=1, max_step_tokens=64, max_chunk=40, kv_tokens=256, max_seq_len=256, max_head_rows=8)
+    q = o2.new_seq()
+    o2.step([(q, prompt, E.Rows.LAST, False)])
     cont = []
     for _ in range(24):
-        cont.append(int(orc.array("feed")[b * 16]))
-        orc.step([(b, [E.FEED_ROW], E.Rows.LAST, False)])
+        cont.append(int(o2.array("feed")[0]))
+        o2.step([(q, [E.FEED_ROW], E.Rows.LAST, False)])
     trace = np.concatenate([prompt, np.array(cont, np.uint32)])
-    orc.free_seq(b)
-    b = orc.new_seq()
     assert a == b
     for e in (prod, orc):
         e.set_trace(a, trace)
@@ -158,9 +158,9 @@ def test_draft_trees_accept_and_compact_like_the_oracle():
     rng = np.random.default_rng(4)
     seqs = [prod.new_seq(), prod.new_seq()]
     assert seqs == [orc.new_seq(), orc.new_seq()]
-    prompts = [rng.integers(0, 512, 18).astype(np.uint32), rng.integers(0, 512, 33).astype(np.uint32)]
+    prompts = [rng.integers(0, 512, 18).astype(np.uint32), rng.integers(0, 512, 31).astype(np.uint32)]
     both_step(prod, orc, [(s, p, E.Rows.LAST, False) for s, p in zip(seqs, prompts)], 2e-2)
-    same_state(prod, orc, 2, 51)
+    same_state(prod, orc, 2, 49)
     # What plain decoding emits next, from a scratch oracle run.
     greedy = {}
     for s, p in zip(seqs, prompts):
