@@ -1,0 +1,300 @@
+"""Decode tokens/s of the speculative-decoding step: the 1B int8 target at 8k context.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--streams S] [--ctx C] [--impl reference]
+
+One rank per GPU (torchrun for N > 1): each rank is an independent replica with its own
+streams -- no collective on the data path; ranks only meet at the timing barriers. A "step"
+is one verify step of every stream on the rank: k = 4 drafts + 1 row per stream through the
+target, sampling at T = 0.6 / top-p 0.95, acceptance and KV commit. Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+CACHE = Path(os.environ.get("VLT_BENCH_CACHE", "/tmp/vlt_bench"))
+
+
+def _package():
+    name = "silicon_violetto_b200"
+    if name not in sys.modules:
+        pkg_dir = ROOT / "silicon-violetto_b200"
+        spec = importlib.util.spec_from_file_location(name, pkg_dir / "__init__.py", submodule_search_locations=[str(pkg_dir)])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+    if str(ROOT) not in sys.path:
+        sys.path.insert(0, str(ROOT))
+
+
+def model_file(config: str, int8: bool, rank: int) -> Path:
+    """The random-init weight file (seed 0, N(0, 0.02^2), int8 per output row), written once per box."""
+    from silicon_violetto_b200 import synth
+    CACHE.mkdir(parents=True, exist_ok=True)
+    path = CACHE / f"{config}_{'int8row' if int8 else 'bf16'}.vlt"
+    done = path.with_suffix(".ok")
+    if rank == 0 and not done.exists():
+        synth.write_target(path, config, seed=0, int8_group=0 if int8 else None)
+        done.write_text("ok")
+    while not done.exists():
+        time.sleep(0.5)
+    return path
+
+
+class Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.rows, self.proc = device, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.device)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v == "Active"})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+ROWS = 5           # k = 4 drafts + the bonus row
+KV_BYTES_PER_TOKEN_LAYER = 8 * 64 * 2 * 2  # 8 kv heads x 64 dims x bf16 x (K, V)
+WEIGHT_PARAMS = 16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048
+
+
+def make_engine(E, path, streams, ctx, steps_total, device):
+    room = ROWS * (steps_total + 8) + 64
+    cfg = E.EngineConfig(max_seqs=streams, max_step_tokens=max(streams * ROWS, 64), max_chunk=16, global_kv_tokens=streams * (ctx + room + 16),
+                         max_seq_len=ctx + room, max_head_rows=max(streams * ROWS, 8), device_ordinal=device)
+    return E.Engine(path, cfg, E.Tuning(spec_policy_off=True)), room
+
+
+def fill(eng, streams, ctx, rank):
+    seqs = [eng.new_seq() for _ in range(streams)]
+    for j, s in enumerate(seqs):
+        eng.bench_fill(s, ctx, seed=1000 * rank + 7 + j)  # the reference seeds stream j's prompt with 7 + j (cli/src/bench.rs:165)
+    return seqs
+
+
+def record_plain(E, eng, streams, ctx, n_tokens, rank, sampling):
+    """Plain decoding (one row per stream and step) from the filled context: the tokens the replay drafter will draft."""
+    seqs = fill(eng, streams, ctx, rank)
+    out = [[] for _ in seqs]
+    with eng.generator() as g:
+        for j, s in enumerate(seqs):
+            g.submit(E.Request(("resume", s, 100 + j), n_tokens, sampling=sampling(j)))
+        while not g.is_idle():
+            for ev in g.step():
+                if ev.kind == "token":
+                    out[ev.req].append(ev.value)
+        g.take_stats()
+    return out
+
+
+def run_replica(args, rank, world, barrier, device, eng, mistakes):
+    """One timed pass: `warmup` + `steps` verify steps of every stream, drafts from the replay drafter."""
+    from silicon_violetto_b200 import engine as E
+    total_steps = args.warmup + args.steps + 6
+    sampling = lambda j: E.Sampling(args.temperature, 0.95, 1 + 1000 * rank + j)
+    n_rec = ROWS * total_steps + 8
+    recorded = record_plain(E, eng, args.streams, args.ctx, n_rec, rank, sampling) if mistakes < 1.0 else [[0] * n_rec] * args.streams
+    seqs = fill(eng, args.streams, args.ctx, rank)
+    g = eng.generator()
+    g.set_replay_mistakes(mistakes, 1)
+    for j, s in enumerate(seqs):
+        trace = [0] * args.ctx + [100 + j] + recorded[j]
+        g.submit(E.Request(("resume", s, 100 + j), n_rec - 2, sampling=sampling(j), draft=E.Draft.REPLAY, rows=ROWS, trace=trace))
+    for _ in range(args.warmup):
+        g.step()
+    barrier()
+    launches0 = E.Engine.launches()
+    with Clocks(device) as clocks:
+        eng.mark(0)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            g.step()
+        eng.mark(1)
+        g.step()  # collects the last timed step (and queues one more, outside both timings)
+        wall = time.perf_counter() - t0
+        dev_ms = eng.mark_elapsed_ms()
+    launches = E.Engine.launches() - launches0
+    barrier()
+    stats = g.take_stats()
+    timed = stats[args.warmup:args.warmup + args.steps]
+    emitted = sum(s["emitted"] for s in timed)
+    # A profiling pass: GPU time of each kernel group, from events around the group's launches.
+    eng.set_profile(True)
+    prof_steps = 3
+    for _ in range(prof_steps):
+        g.step()
+    prof = eng.profile_read()
+    eng.set_profile(False)
+    mean_len = float(np.mean([eng.seq_len(s) for s in seqs]))
+    h2d, d2h = eng.step_bytes()
+    g.close()
+    return dict(dev_ms=dev_ms, wall=wall, emitted=emitted, launches=launches * args.steps // (args.steps + 1), prof=prof, prof_steps=prof_steps,
+                mean_len=mean_len, h2d=h2d, d2h=d2h, clocks=clocks.summary(), tokens_per_step=[s["tokens"] for s in timed])
+
+
+def cpu_reference(args, streams, steps, threads_note=True):
+    """The CPU restatement of the path (the oracle) timed on this machine's cores, on a bounded
+    sample of the workload: `streams` streams at the full context, `steps` verify steps of 5 rows."""
+    _package()
+    import oracle
+    path = model_file("1b", not args.bf16, 0)
+    room = ROWS * (steps + 2) + 32
+    eng = oracle.Engine(path, max_seqs=streams, max_step_tokens=streams * ROWS, max_chunk=16, kv_tokens=streams * (args.ctx + room + 16),
+                        max_seq_len=args.ctx + room, max_head_rows=streams * ROWS)
+    seqs = [eng.new_seq() for _ in range(streams)]
+    for j, s in enumerate(seqs):
+        eng.set_sampling(s, args.temperature, 0.95, 1 + j)
+        eng.bench_fill(s, args.ctx)
+        eng.write("feed", s * 16, [100 + j, 1, 2, 3, 4])
+    runs = [(s, [oracle.FEED_ROW + i for i in range(ROWS)], oracle.ROWS_LAST, True) for s in seqs]
+    times, emitted = [], []
+    for i in range(steps + 1):
+        t0 = time.perf_counter()
+        eng.step(runs)
+        dt = time.perf_counter() - t0
+        em = eng.array("emitted")[:streams]
+        for j, s in enumerate(seqs):  # what `collect` does: give back the rows that were not accepted
+            eng.settle(s, ROWS - int(em[j]))
+        if i > 0:
+            times.append(dt)
+            emitted.append(int(em.sum()))
+    return float(np.median(times)), os.cpu_count(), float(np.mean(emitted))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--streams", type=int, default=32, help="streams per GPU")
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--temperature", type=float, default=0.6)
+    ap.add_argument("--mistakes", type=float, default=1.0, help="share of positions drafted wrong in the headline pass (1: every draft wrong, what a random-init drafter gives)")
+    ap.add_argument("--replay-mistakes", type=float, default=0.3, help="a second pass with the replay drafter at this mistake rate (cli/src/bench_spec.rs:26-28); 1: skip")
+    ap.add_argument("--bf16", action="store_true", help="bf16 weights instead of int8")
+    ap.add_argument("--cpu-streams", type=int, default=2)
+    ap.add_argument("--cpu-steps", type=int, default=2)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    peaks = {}
+    if (ROOT / "MEASURED_PEAKS.json").exists():
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+    workload = f"1B llama-style target, {'bf16' if args.bf16 else 'int8 per-row'} weights, {args.streams} streams/GPU, ctx {args.ctx}, k=4 (5 rows), T={args.temperature} top-p 0.95"
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)
+        v = em / t_step
+        print(json.dumps({"impl": "reference", "metric": "decode tokens/s at 8k context", "value": v, "unit": "tokens/s",
+                          "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16 activations, int8 weights" if not args.bf16 else "bf16", "data": "synthetic",
+                          "config": {"workload": workload, "streams_timed": args.cpu_streams, "drafter": "every draft wrong", "mean_accepted_len": em / args.cpu_streams},
+                          "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                           "sample": f"{args.cpu_streams} streams x {args.cpu_steps} verify steps of 5 rows at ctx {args.ctx}; the reference has no CPU path, this is the C++ restatement of its shader math"},
+                          "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        torch.cuda.set_device(local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(local)
+
+    _package()
+    from silicon_violetto_b200 import engine as E
+    path = model_file("1b", not args.bf16, rank)
+    eng, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local)
+    r = run_replica(args, rank, world, barrier, local, eng, args.mistakes)
+    extra = run_replica(args, rank, world, barrier, local, eng, args.replay_mistakes) if args.replay_mistakes < 1.0 else None
+    vals = torch.tensor([r["dev_ms"], r["wall"]], dtype=torch.float64, device=f"cuda:{local}")
+    sums = torch.tensor([float(r["emitted"]), float(r["launches"])], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    dev_s, wall_s = vals[0].item() * 1e-3, vals[1].item()
+    emitted = sums[0].item()
+    steps = args.steps
+    tau = emitted / (steps * args.streams * world)
+    # Roofline of the dominant kernel (the paged attention at 32 streams): algorithmic bytes of one
+    # launch = every stream's cached and new K/V rows of one layer, read once.
+    att = r["prof"]["attention"]
+    att_ms = att["ms"] / max(att["launches"], 1)
+    att_bytes = args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER
+    achieved = att_bytes / (att_ms * 1e-3) / 1e9 if att_ms > 0 else 0.0
+    step_bytes = WEIGHT_PARAMS * (2 if args.bf16 else 1) + args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER * 16
+    out = {
+        "metric": "decode tokens/s at 8k context", "value": emitted / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": dev_s * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.bf16 else "bf16 activations x int8 weights, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": workload, "drafter": f"replay drafter, {args.mistakes:.2f} of positions drafted wrong", "mean_accepted_len": tau,
+                   "kv": "filled without computing it (timing does not depend on KV values)", "l2": "per-step traffic (weights 1.2 GB + KV) exceeds the 126 MB L2",
+                   "parallelism": f"{world} replica(s), streams sharded, no collective"},
+        "e2e": {"value": emitted / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+        "gpu_launches": int(sums[1].item()),
+        "clocks": r["clocks"],
+        "roofline": {"bound": "hbm", "kernel": "attn_mma_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
+                     "traffic": None, "step_frac": step_bytes / (dev_s / steps) / 1e9 / hbm_peak},
+        "kernel_groups_ms_per_step": {k: v["ms"] / r["prof_steps"] for k, v in r["prof"].items()},
+    }
+    if extra is not None:
+        out["replay_pass"] = {"mistakes": args.replay_mistakes, "value": extra["emitted"] / (extra["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)",
+                              "mean_accepted_len": extra["emitted"] / (steps * args.streams), "ms_per_step": extra["dev_ms"] / steps}
+    if world == 1 and not args.no_cpu:
+        eng.close()
+        t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)
+        out["cpu_baseline"] = {"value": em / t_step, "unit": "tokens/s", "cores": cores, "kind": "port",
+                               "sample": f"{args.cpu_streams} streams x {args.cpu_steps} verify steps of 5 rows at ctx {args.ctx} ({t_step:.2f} s/step), every draft wrong"}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
