@@ -127,6 +127,12 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
         f(s.logits, hr * md.vocab);
         f(s.taps, n * md.d);
         f(s.inv, n);
+        const size_t n16 = (n + 15) / 16 * 16, hr16 = (hr + 15) / 16 * 16;
+        s.h_b.alloc(n16 * md.d * 2, false);
+        s.attn_b.alloc(n16 * md.n_heads * md.hd * 2, false);
+        s.act_b.alloc(n16 * md.ffn * 2, false);
+        s.hfin_b.alloc(hr16 * md.d * 2, false);
+        f(s.inv_head, hr);
     }
     f(s.meta, 2 * n);
     f(s.lens, ms);
@@ -353,6 +359,35 @@ void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint3
     }
 }
 
+// The matmul variant by step size (the reference's Matmul::for_tokens, encode.rs:33-44): the
+// tcgen05 GEMM from gemm_min_rows tokens (default 16), the streamed kernel below.
+bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
+    const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 16;
+    const bool grouped = w.int8 && w.group < w.k;
+    return n >= min_rows && n <= 256 && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
+}
+
+void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv) {
+    MatArgs a{};
+    a.W = w.w;
+    a.scales = w.scales;
+    a.Xb = xb;
+    a.Y = y;
+    a.Yb = yb;
+    a.base = base;
+    a.inv_in = inv;
+    a.n = n;
+    a.k = w.k;
+    a.m = w.m;
+    a.group = w.group;
+    a.int8 = w.int8;
+    a.epi = epi;
+    a.vocab_real = model.md.vocab_real;
+    a.eps = model.md.eps;
+    if (!gemm_supported(a)) throw Error("internal: GEMM asked for an unsupported shape");
+    launch_gemm(a, s.err_flag.as<uint32_t>(), stream);
+}
+
 // engine/src/engine/encode.rs:142-192 `encode_layer`, a plain decoder's.
 void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     const Layer& l = model.layers[li];
@@ -360,8 +395,18 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     StepSet& st = sets[set];
     const uint32_t n = p.n;
     float* h = s.h.as<float>();
+    // Steps of 16 tokens or more multiply on tcgen05: activations go in as bf16 copies and 1/rms
+    // comes from a row pass, since the GEMM does not see whole rows of X.
+    const bool big = use_gemm(l.qkv, n) && use_gemm(l.o, n) && use_gemm(l.gate_up, n) && use_gemm(l.down, n);
     int sp = span_begin(G_MATMUL);
-    if (!(skip & 1)) matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
+    if (!(skip & 1)) {
+        if (big) {
+            launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>());
+        } else {
+            matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
+        }
+    }
     span_end(sp);
     const KvArgs kva = kv_args();
     sp = span_begin(G_SMALL);
@@ -375,6 +420,7 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
             launch_attn_plain(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tiles), st.in<uint32_t>(st.o_vis), rope_tab.as<float>(),
                               kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kva, li, p.tiles, md.n_heads, scale_log2,
                               s.attn.as<float>(), stream);
+        if (big) launch_prep_rows(s.attn.as<float>(), nullptr, n, md.n_heads * md.hd, md.eps, nullptr, s.attn_b.as<uint16_t>(), nullptr, false, false, stream);
     } else {
         AttnArgs a{};
         a.maps = &attn_maps;
@@ -396,7 +442,7 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
         a.max_splits = p.max_splits;
         a.part = s.part.as<float>();
         a.out = s.attn.as<float>();
-        a.out_b = nullptr;
+        a.out_b = big ? s.attn_b.as<uint16_t>() : nullptr;
         a.n = n;
         sp = span_begin(G_ATTN);
         if (!(skip & 4)) launch_attn_mma(a, stream);
@@ -406,9 +452,18 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
         span_end(sp);
     }
     sp = span_begin(G_MATMUL);
-    if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr);
-    if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
-    if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr);
+    if (big) {
+        if (!(skip & 16)) matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), h, nullptr, EPI_RESID, h, nullptr);
+        if (!(skip & 32)) {
+            launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), s.act.as<float>(), s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());
+        }
+        if (!(skip & 64)) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), h, nullptr, EPI_RESID, h, nullptr);
+    } else {
+        if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr);
+        if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+        if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr);
+    }
     span_end(sp);
 }
 
@@ -426,8 +481,13 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
     if (taps_on) launch_prep_rows(h, nullptr, p.n, md.d, md.eps, s.taps.as<float>(), nullptr, nullptr, true, true, stream);
     if (p.n_hidden) launch_prep_rows(h, st.in<uint32_t>(st.o_hidden_rows), p.n_hidden, md.d, md.eps, s.hfin_all.as<float>(), nullptr, nullptr, true, false, stream);
     if (p.n_head && !(skip & 256)) {
-        launch_prep_rows(h, st.in<uint32_t>(st.o_head_rows), p.n_head, md.d, md.eps, s.hfin_head.as<float>(), nullptr, nullptr, false, false, stream);
-        matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
+        if (use_gemm(model.head, p.n_head)) {
+            launch_prep_rows(h, st.in<uint32_t>(st.o_head_rows), p.n_head, md.d, md.eps, nullptr, s.hfin_b.as<uint16_t>(), s.inv_head.as<float>(), false, false, stream);
+            matmul_gemm(model.head, p.n_head, s.hfin_b.as<uint16_t>(), s.logits.as<float>(), nullptr, EPI_HEAD, nullptr, s.inv_head.as<float>());
+        } else {
+            launch_prep_rows(h, st.in<uint32_t>(st.o_head_rows), p.n_head, md.d, md.eps, s.hfin_head.as<float>(), nullptr, nullptr, false, false, stream);
+            matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
+        }
         encode_sample(set, p.n_head);
     }
     launch_accept(st.in<RunIn>(st.o_runs), st.in<uint32_t>(st.o_tokens), st.out<uint32_t>(st.o_out_ids), s.lens.as<uint32_t>(), s.feed.as<uint32_t>(),

@@ -158,6 +158,7 @@ class Engine {
     // Activations (engine/src/engine/buffers.rs:14-118) and per-slot state on the GPU.
     struct Scratch {
         Buffer h, qkv, attn, act, part, hfin_head, hfin_all, logits, taps, inv, meta;
+        Buffer h_b, attn_b, act_b, hfin_b, inv_head;  // bf16 copies that feed the tensor-core GEMM, rows padded to 16
         Buffer lens, feed, tree, gen, path, path_len, on_path, trace, trace_len, err_flag;
     } s;
     Buffer rope_tab;
@@ -166,6 +167,9 @@ class Engine {
   private:
     KvArgs kv_args() const;
     void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out);
+    // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
+    void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv);
+    bool use_gemm(const Matrix& w, uint32_t n) const;
     void encode_layer(uint32_t set, const Plan& p, uint32_t li);
     void encode_tail(uint32_t set, const Plan& p);
     void encode_sample(uint32_t set, uint32_t rows);

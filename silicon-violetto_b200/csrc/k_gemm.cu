@@ -1,0 +1,313 @@
+// The verify GEMM on the 5th-generation tensor cores: Y[t][row] = epilogue(W[row] . Xb[t]) for
+// steps of 16 to 256 tokens (S streams x k+1 rows). The reference's tiled GEMM
+// (kernels.metal:319-514) stages k tiles through threadgroup memory and dequantises on the way;
+// here
+//   - the weight tile is the MMA's M side (128 rows) and the tokens its N side (16..256), so a
+//     weight is read from HBM once whatever the number of streams;
+//   - operands come in by TMA (no multicast) into 128-byte-swizzled shared memory, a ring of
+//     stages guarded by mbarriers; tcgen05.mma, issued by one thread, accumulates fp32 in TMEM;
+//   - int8 weights arrive as raw bytes and four warps turn each stage into bf16 (exactly) in the
+//     swizzled layout the MMA reads; their scale per output row is applied in the epilogue;
+//   - the epilogue warps read TMEM with tcgen05.ld and apply the fused epilogues (RMSNorm scale,
+//     residual add, SwiGLU on interleaved gate/up rows, head) before the coalesced store.
+// Every wait is bounded: on a time-out the kernel sets the error flag, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
+#include "kernels.h"
+
+namespace vlt {
+
+namespace gemm {
+
+constexpr uint32_t BM = 128, BK = 64;
+constexpr uint32_t THREADS = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: conversion and epilogue
+constexpr uint32_t SPIN = 1u << 26;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map), "r"(x),
+                 "r"(y), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 64 bf16; groups of
+// 8 rows are 1024 bytes apart. Bits: [0,14) address >> 4, [16,30) leading offset >> 4 (unused for
+// swizzled K-major), [32,46) stride offset >> 4, [46,48) version 1, [61,64) swizzle mode 2 (128 B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, both K-major, M x N.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d), "l"(adesc), "l"(bdesc),
+                 "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Four int8 (one word) to two bf16 pairs, exactly (see k_matmul.cu).
+__device__ __forceinline__ void cvt_i8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t u = w ^ 0x80808080u;
+    const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+    const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+    const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+    const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+    lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+    hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+}
+
+struct Maps {
+    alignas(64) uint8_t a[128];
+    alignas(64) uint8_t b[128];
+};
+
+struct Args {
+    MatArgs m;
+    uint32_t n_pad;     // tokens rounded up to 16: the MMA's N
+    uint32_t stages;
+    uint32_t tmem_cols; // power of two >= max(32, n_pad)
+    uint32_t* err_flag;
+};
+
+}  // namespace gemm
+
+namespace gemm {
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (uint32_t i = 0; i < SPIN; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+
+// grid: m / 128 blocks; one block owns a 128-row weight tile over all of k.
+template <bool INT8>
+__global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t n_pad = a.n_pad, stages = a.stages;
+    const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = INT8 ? BM * BK : 0;
+    const uint32_t stage_bytes = a_bytes + b_bytes + raw_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(stages) * stage_bytes);
+    // full[s], conv[s], empty[s], then the accumulator's barrier
+    const uint32_t bar_full = smem_u32(bars), bar_conv = bar_full + 8 * stages, bar_empty = bar_conv + 8 * stages, bar_accum = bar_empty + 8 * stages;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * stages + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    const uint32_t smem_base = smem_u32(smem);
+    auto stage_a = [&](uint32_t s) { return smem_base + s * stage_bytes; };
+    auto stage_b = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes; };
+    auto stage_raw = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes + b_bytes; };
+
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t row0 = blockIdx.x * BM, nkb = a.m.k / BK;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < stages; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_conv + 8 * s, 128);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_accum, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t tx = (INT8 ? raw_bytes : a_bytes) + b_bytes;
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t s = kb % stages, ph = (kb / stages) & 1;
+                ok = wait_or_abort(bar_empty + 8 * s, ph ^ 1, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(bar_full + 8 * s, tx);
+                tma_load_2d(INT8 ? stage_raw(s) : stage_a(s), &maps.a, int(kb * BK), int(row0), bar_full + 8 * s);
+                tma_load_2d(stage_b(s), &maps.b, int(kb * BK), 0, bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(BM, n_pad);
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t s = kb % stages, ph = (kb / stages) & 1;
+                ok = wait_or_abort((INT8 ? bar_conv : bar_full) + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < BK / 16; k4++)
+                    mma_f16(tmem_base, smem_desc(stage_a(s) + k4 * 32), smem_desc(stage_b(s) + k4 * 32), idesc, (kb | k4) != 0 ? 1u : 0u);
+                mma_commit(bar_empty + 8 * s);  // arrives once these MMAs have read the stage
+            }
+            if (ok) mma_commit(bar_accum);
+        }
+    } else {
+        const uint32_t cid = tid - 64;
+        if (INT8) {
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t s = kb % stages, ph = (kb / stages) & 1;
+                ok = wait_or_abort(bar_full + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                const uint32_t q = cid & 3;
+#pragma unroll
+                for (uint32_t p = 0; p < 4; p++) {
+                    const uint32_t row = (cid >> 2) + 32 * p;
+                    uint4 raw;
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(stage_raw(s) + row * 64 + q * 16));
+                    uint4 lo, hi;
+                    cvt_i8x4(raw.x, lo.x, lo.y);
+                    cvt_i8x4(raw.y, lo.z, lo.w);
+                    cvt_i8x4(raw.z, hi.x, hi.y);
+                    cvt_i8x4(raw.w, hi.z, hi.w);
+                    const uint32_t base = stage_a(s) + row * 128, sw = row & 7;
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q) ^ sw) << 4)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q + 1) ^ sw) << 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+                mbar_arrive(bar_conv + 8 * s);
+            }
+        }
+        if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const MatArgs& m = a.m;
+            const uint32_t quarter = warp & 3, row = row0 + quarter * 32 + lane;
+            const float scale = INT8 ? bf16_to_f32(m.scales[row]) : 1.0f;
+            for (uint32_t c0 = 0; c0 < n_pad; c0 += 32) {
+                float acc[32];
+                tmem_ld32(tmem_base + ((quarter * 32) << 16) + c0, acc);
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j++) {
+                    const uint32_t t = c0 + j;
+                    if (t >= m.n) break;  // uniform across the warp
+                    const float v = acc[j] * scale;
+                    if (m.epi == EPI_SWIGLU) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                        if ((lane & 1) == 0) {
+                            const float inv = m.inv_in[t], g = v * inv, u = other * inv;
+                            const float y = g * (1.0f / (1.0f + expf(-g))) * u;
+                            const size_t o = size_t(t) * (m.m / 2) + row / 2;
+                            m.Y[o] = y;
+                            if (m.Yb) m.Yb[o] = f32_to_bf16(y);
+                        }
+                    } else {
+                        const size_t o = size_t(t) * m.m + row;
+                        float y;
+                        if (m.epi == EPI_NORM) y = v * m.inv_in[t];
+                        else if (m.epi == EPI_RESID) y = m.base[o] + v;
+                        else if (m.epi == EPI_HEAD) y = row < m.vocab_real ? v * m.inv_in[t] : -INFINITY;
+                        else y = v;
+                        m.Y[o] = y;
+                        if (m.Yb) m.Yb[o] = f32_to_bf16(y);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) {
+        *abort_flag = 1;
+        atomicExch(a.err_flag, 2u);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    }
+}
+
+}  // namespace gemm
+
+// Tensor maps are made once per (operand pointer, shape) and kept: the engine's buffers never move.
+struct GemmMapCache {
+    std::map<std::tuple<const void*, const void*, uint32_t, uint32_t, uint32_t>, gemm::Maps> maps;
+};
+
+bool gemm_supported(const MatArgs& a) {
+    const bool grouped = a.int8 && a.group < a.k;
+    return a.n >= 1 && a.n <= 256 && a.m % gemm::BM == 0 && a.k % gemm::BK == 0 && !grouped && a.Xb != nullptr &&
+           (a.epi == EPI_RESID || a.epi == EPI_RAW || a.inv_in != nullptr);
+}
+
+void launch_gemm(const MatArgs& a, uint32_t* err_flag, cudaStream_t s) {
+    static thread_local GemmMapCache cache;
+    static bool configured = false;
+    const uint32_t n_pad = (a.n + 15) / 16 * 16;
+    auto key = std::make_tuple(static_cast<const void*>(a.W), static_cast<const void*>(a.Xb), a.m, a.k, n_pad);
+    auto it = cache.maps.find(key);
+    if (it == cache.maps.end()) {
+        gemm::Maps m;
+        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 1, false);
+        else make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 2, true);
+        make_tensor_map_2d(m.b, a.Xb, a.k, n_pad, gemm::BK, n_pad, 2, true);
+        it = cache.maps.emplace(key, m).first;
+    }
+    const uint32_t stage_bytes = gemm::BM * gemm::BK * 2 + n_pad * gemm::BK * 2 + (a.int8 ? gemm::BM * gemm::BK : 0);
+    const uint32_t budget = 200 * 1024;
+    uint32_t stages = std::min<uint32_t>(8, (budget - 1024 - 256) / stage_bytes);
+    stages = std::max(stages, 2u);
+    const size_t smem = size_t(stages) * stage_bytes + 1024 + (3 * stages + 1) * 8 + 16;
+    if (!configured) {
+        VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    gemm::Args g;
+    g.m = a;
+    g.n_pad = n_pad;
+    g.stages = stages;
+    uint32_t cols = 32;
+    while (cols < n_pad) cols *= 2;
+    g.tmem_cols = cols;
+    g.err_flag = err_flag;
+    const uint32_t grid = a.m / gemm::BM;
+    if (a.int8) gemm::gemm_kernel<true><<<grid, gemm::THREADS, smem, s>>>(it->second, g);
+    else gemm::gemm_kernel<false><<<grid, gemm::THREADS, smem, s>>>(it->second, g);
+    launch_counter()++;
+}
+
+}  // namespace vlt

@@ -68,6 +68,10 @@ constexpr uint32_t ATTN_PART = 68;  // floats per partial: m, l, 2 pad, o[64]
 void launch_attn_mma(const AttnArgs& a, cudaStream_t s);
 void launch_attn_combine(const AttnArgs& a, cudaStream_t s);
 
+// The tcgen05 GEMM for 16..256 tokens: needs Xb (bf16 X, rows padded to 16), inv_in for the
+// normed epilogues, m a multiple of 128, one int8 scale per row.
+bool gemm_supported(const MatArgs& a);
+void launch_gemm(const MatArgs& a, uint32_t* err_flag, cudaStream_t s);
 void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s);  // n <= 8, tensor cores fed from registers
 void launch_matmul_rows(const MatArgs& a, cudaStream_t s);                      // any n, scalar (cross-check, odd scale groups)
 // out[r] = in[rows ? rows[r] : r] as fp32 (and bf16); inv[r] = 1 / rms (kernels.metal:117-148).
