@@ -133,11 +133,11 @@ def run_replica(args, rank, world, barrier, device, eng, mistakes):
     for j, s in enumerate(seqs):
         trace = [0] * args.ctx + [100 + j] + recorded[j]
         g.submit(E.Request(("resume", s, 100 + j), n_rec - 2, sampling=sampling(j), draft=E.Draft.REPLAY, rows=ROWS, trace=trace))
-    for _ in range(args.warmup):
-        g.step()
-    barrier()
-    launches0 = E.Engine.launches()
-    with Clocks(device) as clocks:
+    with Clocks(device) as clocks:  # nvidia-smi needs a moment to start: it samples from the warm-up on
+        for _ in range(args.warmup):
+            g.step()
+        barrier()
+        launches0 = E.Engine.launches()
         eng.mark(0)
         t0 = time.perf_counter()
         for _ in range(args.steps):

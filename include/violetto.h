@@ -133,6 +133,16 @@ int vlt_bench_fill(VltEngine* e, uint32_t seq, uint32_t len, uint32_t seed);
 /* sample_logits, hooks.rs:41-54: rows of logits [n][vocab] (NULL: the previous call's) through
  * the sampler, each row with its own settings and drawn-token position. */
 int vlt_sample_logits(VltEngine* e, const float* logits, const VltSampling* rows, const uint32_t* pos, uint32_t n, uint32_t* out);
+/* Rejection-sampling acceptance on caller-supplied logits: p [streams][k+1][vocab] target rows and
+ * q [streams][k][vocab] draft rows (bf16), the k draft tokens per stream, one seed and the position
+ * of the first draft per stream. Draft i is accepted with probability min(1, P(x)/Q(x)); the first
+ * rejected one is replaced by a draw from the normalised max(0, P - Q); with all accepted a bonus
+ * token is drawn from the last target row. No counterpart in the reference, whose acceptance is
+ * sample-then-match (`accept`, kernels.metal:1578-1657); it reuses the reference sampler's
+ * uniforms and summation order (kernels.metal:1462-1576). gpu_seconds (may be NULL): the kernels'
+ * time, best of reps. */
+int vlt_spec_accept(VltEngine* e, const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature,
+                    const uint64_t* seeds, const uint32_t* pos0, uint32_t reps, uint32_t* accepted, uint32_t* token, uint32_t* rollback, double* gpu_seconds);
 /* set_profile_skip, hooks.rs:9-26: leave kernel groups out (results are then wrong). */
 enum { VLT_SKIP_QKV = 1, VLT_SKIP_POST = 2, VLT_SKIP_ATTN = 4, VLT_SKIP_REDUCE = 8, VLT_SKIP_O = 16, VLT_SKIP_GATE_UP = 32, VLT_SKIP_DOWN = 64, VLT_SKIP_HEAD = 256 };
 void vlt_set_profile_skip(VltEngine* e, uint32_t mask);

@@ -156,6 +156,18 @@ int vlt_sample_logits(VltEngine* e, const float* logits, const VltSampling* rows
     });
 }
 
+int vlt_spec_accept(VltEngine* e, const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature,
+                    const uint64_t* seeds, const uint32_t* pos0, uint32_t reps, uint32_t* accepted, uint32_t* token, uint32_t* rollback, double* gpu_seconds) {
+    return guard([&] {
+        std::vector<uint32_t> out(size_t(3) * streams);
+        const double t = eng(e).spec_accept(p, q, drafts, streams, k, temperature, seeds, pos0, reps, out.data());
+        std::memcpy(accepted, out.data(), size_t(streams) * 4);
+        std::memcpy(token, out.data() + streams, size_t(streams) * 4);
+        std::memcpy(rollback, out.data() + 2 * streams, size_t(streams) * 4);
+        if (gpu_seconds) *gpu_seconds = t;
+    });
+}
+
 void vlt_set_profile_skip(VltEngine* e, uint32_t mask) { if (e && e->e) e->e->skip = mask; }
 
 int vlt_bench_matmul(VltEngine* e, const char* kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes) {

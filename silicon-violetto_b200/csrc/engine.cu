@@ -385,7 +385,7 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
     a.vocab_real = model.md.vocab_real;
     a.eps = model.md.eps;
     if (!gemm_supported(a)) throw Error("internal: GEMM asked for an unsupported shape");
-    launch_gemm(a, s.err_flag.as<uint32_t>(), stream);
+    launch_gemm(a, sm_count, s.err_flag.as<uint32_t>(), stream);
 }
 
 // engine/src/engine/encode.rs:142-192 `encode_layer`, a plain decoder's.
@@ -611,27 +611,82 @@ std::vector<uint32_t> Engine::sample_logits(const float* logits, const std::vect
     return std::vector<uint32_t>(st.hout<uint32_t>(st.o_out_ids), st.hout<uint32_t>(st.o_out_ids) + n);
 }
 
+double Engine::spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature,
+                           const uint64_t* seeds, const uint32_t* pos0, uint32_t reps, uint32_t* out) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");
+    if (streams == 0 || k == 0 || k > 15) throw Error("spec_accept: needs at least one stream and 1..15 drafts");
+    if (!(std::isnormal(temperature) && temperature > 0.0f)) throw Error("spec_accept: needs a normal positive temperature");
+    const uint32_t vocab = model.md.vocab;
+    for (uint32_t i = 0; i < streams * k; i++)
+        if (drafts[i] >= vocab) throw Error("spec_accept: draft token id out of range");
+    const size_t pb = size_t(streams) * (k + 1) * vocab * 2, qb = size_t(streams) * k * vocab * 2;
+    if (spec_p.bytes < pb) spec_p.alloc(pb, false);
+    if (spec_q.bytes < qb) spec_q.alloc(qb, false);
+    // small: drafts | seeds | pos0 | accepted | token | rollback | row statistics
+    const size_t o_seeds = (size_t(streams) * k * 4 + 255) / 256 * 256, o_pos = o_seeds + (size_t(streams) * 8 + 255) / 256 * 256;
+    const size_t o_out = o_pos + (size_t(streams) * 4 + 255) / 256 * 256, o_stats = o_out + (size_t(streams) * 12 + 255) / 256 * 256;
+    const size_t small = o_stats + size_t(streams) * (2 * k + 1) * 16;
+    if (spec_small.bytes < small) spec_small.alloc(small, false);
+    uint8_t* sm = spec_small.as<uint8_t>();
+    VLT_CUDA(cudaMemcpyAsync(spec_p.dev, p, pb, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaMemcpyAsync(spec_q.dev, q, qb, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaMemcpyAsync(sm, drafts, size_t(streams) * k * 4, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaMemcpyAsync(sm + o_seeds, seeds, size_t(streams) * 8, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaMemcpyAsync(sm + o_pos, pos0, size_t(streams) * 4, cudaMemcpyHostToDevice, stream));
+    cudaEvent_t e0, e1;
+    VLT_CUDA(cudaEventCreate(&e0));
+    VLT_CUDA(cudaEventCreate(&e1));
+    double best = 1e30;
+    uint32_t* o = reinterpret_cast<uint32_t*>(sm + o_out);
+    for (uint32_t r = 0; r < std::max(reps, 1u); r++) {
+        VLT_CUDA(cudaEventRecord(e0, stream));
+        launch_spec_accept(spec_p.as<uint16_t>(), spec_q.as<uint16_t>(), reinterpret_cast<const uint32_t*>(sm), streams, k, vocab, temperature,
+                           reinterpret_cast<const uint64_t*>(sm + o_seeds), reinterpret_cast<const uint32_t*>(sm + o_pos), sm + o_stats, o, o + streams,
+                           o + 2 * streams, stream);
+        VLT_CUDA(cudaEventRecord(e1, stream));
+        VLT_CUDA(cudaEventSynchronize(e1));
+        float ms = 0;
+        VLT_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        best = std::min(best, double(ms) * 1e-3);
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    VLT_CUDA(cudaMemcpy(out, o, size_t(streams) * 12, cudaMemcpyDeviceToHost));
+    return best;
+}
+
 // engine/src/engine/hooks.rs:56-111 `bench_matmul`.
 void Engine::bench_matmul(const std::string& kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes) {
     if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");
     const bool head = kind == "head";
     if (!head && kind != "qkv" && kind != "o" && kind != "gate_up" && kind != "down") throw Error("unknown matmul " + kind);
     if (n == 0 || n > (head ? cfg.max_head_rows : cfg.max_step_tokens)) throw Error(kind + " can't take " + std::to_string(n) + " tokens");
-    (void)variant;
     cudaEvent_t e0, e1;
     VLT_CUDA(cudaEventCreate(&e0));
     VLT_CUDA(cudaEventCreate(&e1));
     double best = 1e30;
     for (uint32_t r = 0; r < std::max(reps, 1u); r++) {
         VLT_CUDA(cudaEventRecord(e0, stream));
-        if (head) matmul(model.head, n, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
-        else
+        const bool gemm = variant != 1 && use_gemm(head ? model.head : model.layers[0].o, n);
+        if (variant == 2 && !gemm) throw Error(kind + ": the tensor-core GEMM can't take " + std::to_string(n) + " tokens");
+        if (head) {
+            if (gemm) matmul_gemm(model.head, n, s.hfin_b.as<uint16_t>(), s.logits.as<float>(), nullptr, EPI_HEAD, nullptr, s.inv_head.as<float>());
+            else matmul(model.head, n, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
+        } else {
             for (const Layer& l : model.layers) {
-                if (kind == "qkv") matmul(l.qkv, n, s.h.as<float>(), s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
-                else if (kind == "o") matmul(l.o, n, s.attn.as<float>(), s.hfin_all.as<float>(), EPI_RESID, s.h.as<float>(), nullptr);
-                else if (kind == "gate_up") matmul(l.gate_up, n, s.h.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
-                else matmul(l.down, n, s.act.as<float>(), s.hfin_all.as<float>(), EPI_RESID, s.h.as<float>(), nullptr);
+                if (gemm) {
+                    if (kind == "qkv") matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>());
+                    else if (kind == "o") matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), s.hfin_all.as<float>(), nullptr, EPI_RESID, s.h.as<float>(), nullptr);
+                    else if (kind == "gate_up") matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), s.act.as<float>(), s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());
+                    else matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), s.hfin_all.as<float>(), nullptr, EPI_RESID, s.h.as<float>(), nullptr);
+                } else {
+                    if (kind == "qkv") matmul(l.qkv, n, s.h.as<float>(), s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
+                    else if (kind == "o") matmul(l.o, n, s.attn.as<float>(), s.hfin_all.as<float>(), EPI_RESID, s.h.as<float>(), nullptr);
+                    else if (kind == "gate_up") matmul(l.gate_up, n, s.h.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+                    else matmul(l.down, n, s.act.as<float>(), s.hfin_all.as<float>(), EPI_RESID, s.h.as<float>(), nullptr);
+                }
             }
+        }
         VLT_CUDA(cudaEventRecord(e1, stream));
         VLT_CUDA(cudaEventSynchronize(e1));
         float ms = 0;

@@ -122,6 +122,10 @@ class Engine {
     void set_taps(bool on);
     void bench_fill(uint32_t id, uint32_t len, uint32_t seed);
     std::vector<uint32_t> sample_logits(const float* logits, const std::vector<std::pair<Sampling, uint32_t>>& rows);
+    // Rejection-sampling acceptance on caller-supplied logits (host pointers); out: 3 x streams words
+    // (accepted, token, rollback). Returns the kernels' GPU seconds (best of reps).
+    double spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature, const uint64_t* seeds,
+                       const uint32_t* pos0, uint32_t reps, uint32_t* out);
     void bench_matmul(const std::string& kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes);
 
     // The generator's building blocks (engine/src/engine/generate.rs uses the same ones).
@@ -162,6 +166,7 @@ class Engine {
         Buffer lens, feed, tree, gen, path, path_len, on_path, trace, trace_len, err_flag;
     } s;
     Buffer rope_tab;
+    Buffer spec_p, spec_q, spec_small;  // spec_accept's device copies, grown on demand
     AttnMaps attn_maps;
 
   private:

@@ -13,6 +13,7 @@
 // Every wait is bounded: on a time-out the kernel sets the error flag, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <algorithm>
 #include <map>
 #include <tuple>
 
@@ -23,7 +24,8 @@ namespace vlt {
 namespace gemm {
 
 constexpr uint32_t BM = 128, BK = 64;
-constexpr uint32_t THREADS = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: conversion and epilogue
+constexpr uint32_t CONV_WARPS = 8;
+constexpr uint32_t THREADS = 64 + 32 * CONV_WARPS;  // warp 0: TMA, warp 1: MMA, the rest: conversion and epilogue
 constexpr uint32_t SPIN = 1u << 26;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -101,10 +103,12 @@ struct Args {
     uint32_t n_pad;     // tokens rounded up to 16: the MMA's N
     uint32_t stages;
     uint32_t tmem_cols; // power of two >= max(32, n_pad)
+    uint32_t splits;    // blocks of a cluster that share a weight tile, each over a slice of k
     uint32_t* err_flag;
 };
 
 }  // namespace gemm
+
 
 namespace gemm {
 
@@ -115,16 +119,38 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     return false;
 }
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address of this block's shared-memory location `addr` in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster(uint32_t addr) {
+    float v;
+    asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));  // ordered by the cluster barrier before it
+    return v;
+}
 
-// grid: m / 128 blocks; one block owns a 128-row weight tile over all of k.
+// grid: (m / 128) * splits blocks in clusters of `splits`. A cluster owns a 128-row weight tile;
+// its blocks each stream a slice of k into their own TMEM accumulator, put it in shared memory,
+// and each then adds up, over distributed shared memory and in rank order, the rows it owns.
 template <bool INT8>
 __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t n_pad = a.n_pad, stages = a.stages;
+    const uint32_t n_pad = a.n_pad, stages = a.stages, splits = a.splits;
     const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = INT8 ? BM * BK : 0;
     const uint32_t stage_bytes = a_bytes + b_bytes + raw_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(stages) * stage_bytes);
+    const uint32_t ring_bytes = max(stages * stage_bytes, BM * (n_pad + 1) * 4);  // the partial tile reuses the ring
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes);
     // full[s], conv[s], empty[s], then the accumulator's barrier
     const uint32_t bar_full = smem_u32(bars), bar_conv = bar_full + 8 * stages, bar_empty = bar_conv + 8 * stages, bar_accum = bar_empty + 8 * stages;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * stages + 1);
@@ -135,12 +161,16 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     auto stage_raw = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes + b_bytes; };
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const uint32_t row0 = blockIdx.x * BM, nkb = a.m.k / BK;
+    const uint32_t rank = splits > 1 ? cluster_rank() : 0, tile = blockIdx.x / splits;
+    const uint32_t row0 = tile * BM, nkb_all = a.m.k / BK;
+    // This block's k blocks: an even share, the first ranks one more.
+    const uint32_t kb_begin = rank * (nkb_all / splits) + min(rank, nkb_all % splits);
+    const uint32_t nkb = nkb_all / splits + (rank < nkb_all % splits ? 1 : 0);
 
     if (tid == 0) {
         for (uint32_t s = 0; s < stages; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_conv + 8 * s, 128);
+            mbar_init(bar_conv + 8 * s, 32 * CONV_WARPS);
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_accum, 1);
@@ -161,8 +191,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     if (warp == 0) {
         if (lane == 0) {
             const uint32_t tx = (INT8 ? raw_bytes : a_bytes) + b_bytes;
-            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-                const uint32_t s = kb % stages, ph = (kb / stages) & 1;
+            for (uint32_t i = 0; i < nkb && ok; i++) {
+                const uint32_t s = i % stages, ph = (i / stages) & 1, kb = kb_begin + i;
                 ok = wait_or_abort(bar_empty + 8 * s, ph ^ 1, abort_flag);
                 if (!ok) break;
                 mbar_expect_tx(bar_full + 8 * s, tx);
@@ -173,78 +203,59 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, n_pad);
-            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-                const uint32_t s = kb % stages, ph = (kb / stages) & 1;
+            for (uint32_t i = 0; i < nkb && ok; i++) {
+                const uint32_t s = i % stages, ph = (i / stages) & 1;
                 ok = wait_or_abort((INT8 ? bar_conv : bar_full) + 8 * s, ph, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (uint32_t k4 = 0; k4 < BK / 16; k4++)
-                    mma_f16(tmem_base, smem_desc(stage_a(s) + k4 * 32), smem_desc(stage_b(s) + k4 * 32), idesc, (kb | k4) != 0 ? 1u : 0u);
+                    mma_f16(tmem_base, smem_desc(stage_a(s) + k4 * 32), smem_desc(stage_b(s) + k4 * 32), idesc, (i | k4) != 0 ? 1u : 0u);
                 mma_commit(bar_empty + 8 * s);  // arrives once these MMAs have read the stage
             }
             if (ok) mma_commit(bar_accum);
         }
-    } else {
+    } else if (INT8) {
+        // Raw int8 [128][64] to bf16 in the swizzled layout: a thread takes 16 bytes of a row at a time.
         const uint32_t cid = tid - 64;
-        if (INT8) {
-            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-                const uint32_t s = kb % stages, ph = (kb / stages) & 1;
-                ok = wait_or_abort(bar_full + 8 * s, ph, abort_flag);
-                if (!ok) break;
-                const uint32_t q = cid & 3;
+        for (uint32_t i = 0; i < nkb && ok; i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            ok = wait_or_abort(bar_full + 8 * s, ph, abort_flag);
+            if (!ok) break;
+            const uint32_t q = cid & 3;
 #pragma unroll
-                for (uint32_t p = 0; p < 4; p++) {
-                    const uint32_t row = (cid >> 2) + 32 * p;
-                    uint4 raw;
-                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(stage_raw(s) + row * 64 + q * 16));
-                    uint4 lo, hi;
-                    cvt_i8x4(raw.x, lo.x, lo.y);
-                    cvt_i8x4(raw.y, lo.z, lo.w);
-                    cvt_i8x4(raw.z, hi.x, hi.y);
-                    cvt_i8x4(raw.w, hi.z, hi.w);
-                    const uint32_t base = stage_a(s) + row * 128, sw = row & 7;
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q) ^ sw) << 4)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q + 1) ^ sw) << 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
-                mbar_arrive(bar_conv + 8 * s);
+            for (uint32_t p = 0; p < 512 / (32 * CONV_WARPS); p++) {
+                const uint32_t row = (cid >> 2) + (8 * CONV_WARPS) * p;
+                uint4 raw;
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(stage_raw(s) + row * 64 + q * 16));
+                uint4 lo, hi;
+                cvt_i8x4(raw.x, lo.x, lo.y);
+                cvt_i8x4(raw.y, lo.z, lo.w);
+                cvt_i8x4(raw.z, hi.x, hi.y);
+                cvt_i8x4(raw.w, hi.z, hi.w);
+                const uint32_t base = stage_a(s) + row * 128, sw = row & 7;
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q) ^ sw) << 4)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q + 1) ^ sw) << 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+            mbar_arrive(bar_conv + 8 * s);
         }
+    }
+
+    // The accumulator to shared memory as fp32 [128][n_pad + 1] (the ring is free once the MMAs are done).
+    const uint32_t pitch = n_pad + 1;
+    if (warp >= 2) {
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const MatArgs& m = a.m;
-            const uint32_t quarter = warp & 3, row = row0 + quarter * 32 + lane;
-            const float scale = INT8 ? bf16_to_f32(m.scales[row]) : 1.0f;
-            for (uint32_t c0 = 0; c0 < n_pad; c0 += 32) {
+            const uint32_t quarter = warp & 3, half = (warp - 2) >> 2, r = quarter * 32 + lane;
+            float* part = reinterpret_cast<float*>(smem) + size_t(r) * pitch;
+            for (uint32_t c0 = 32 * half; c0 < n_pad; c0 += 64) {
                 float acc[32];
                 tmem_ld32(tmem_base + ((quarter * 32) << 16) + c0, acc);
 #pragma unroll
-                for (uint32_t j = 0; j < 32; j++) {
-                    const uint32_t t = c0 + j;
-                    if (t >= m.n) break;  // uniform across the warp
-                    const float v = acc[j] * scale;
-                    if (m.epi == EPI_SWIGLU) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-                        if ((lane & 1) == 0) {
-                            const float inv = m.inv_in[t], g = v * inv, u = other * inv;
-                            const float y = g * (1.0f / (1.0f + expf(-g))) * u;
-                            const size_t o = size_t(t) * (m.m / 2) + row / 2;
-                            m.Y[o] = y;
-                            if (m.Yb) m.Yb[o] = f32_to_bf16(y);
-                        }
-                    } else {
-                        const size_t o = size_t(t) * m.m + row;
-                        float y;
-                        if (m.epi == EPI_NORM) y = v * m.inv_in[t];
-                        else if (m.epi == EPI_RESID) y = m.base[o] + v;
-                        else if (m.epi == EPI_HEAD) y = row < m.vocab_real ? v * m.inv_in[t] : -INFINITY;
-                        else y = v;
-                        m.Y[o] = y;
-                        if (m.Yb) m.Yb[o] = f32_to_bf16(y);
-                    }
-                }
+                for (uint32_t j = 0; j < 32; j++)
+                    if (c0 + j < n_pad) part[c0 + j] = acc[j];
             }
         }
     }
@@ -253,6 +264,71 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         atomicExch(a.err_flag, 2u);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (splits > 1) cluster_sync();  // every block's partial is in place
+
+    if (warp >= 2 && !*abort_flag) {
+        const MatArgs& m = a.m;
+        // Rows this block finishes: an even share of the tile's 64 row pairs (a gate/up pair stays together).
+        const uint32_t u_begin = rank * (64 / splits) + min(rank, 64 % splits), u_count = 64 / splits + (rank < 64 % splits ? 1 : 0);
+        const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
+        uint32_t remote[8];
+#pragma unroll
+        for (uint32_t s = 0; s < 8; s++) remote[s] = s < splits ? map_to_rank(smem_base, s) : 0;  // (also orders the loads below after the barrier)
+        const uint32_t ew = warp - 2;
+        for (uint32_t rg = r_begin; rg < r_end; rg += 32) {
+            const uint32_t r = rg + lane;
+            const bool valid = r < r_end;
+            const uint32_t row = row0 + r;
+            const float scale = INT8 && valid ? bf16_to_f32(m.scales[row]) : 1.0f;
+            // Tokens in batches of TB per warp, so that the loads of a batch are all in flight together.
+            constexpr uint32_t TB = 4;
+            for (uint32_t t0 = ew * TB; t0 < m.n; t0 += CONV_WARPS * TB) {
+                float v[TB], inv[TB], base[TB];
+#pragma unroll
+                for (uint32_t j = 0; j < TB; j++) v[j] = 0.0f;
+                if (valid) {
+#pragma unroll
+                    for (uint32_t s = 0; s < 8; s++)
+                        if (s < splits) {
+#pragma unroll
+                            for (uint32_t j = 0; j < TB; j++) v[j] += ld_cluster(remote[s] + (r * pitch + min(t0 + j, n_pad - 1)) * 4);
+                        }
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < TB; j++) {
+                    const uint32_t t = min(t0 + j, m.n - 1);
+                    inv[j] = m.inv_in ? __ldg(m.inv_in + t) : 1.0f;
+                    base[j] = (m.epi == EPI_RESID && valid) ? m.base[size_t(t) * m.m + row] : 0.0f;
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < TB; j++) {
+                    const uint32_t t = t0 + j;
+                    const float x = v[j] * scale;
+                    if (m.epi == EPI_SWIGLU) {
+                        const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                        if (valid && t < m.n && (lane & 1) == 0) {
+                            const float g = x * inv[j], u = other * inv[j];
+                            const float y = g * (1.0f / (1.0f + __expf(-g))) * u;
+                            const size_t o = size_t(t) * (m.m / 2) + row / 2;
+                            m.Y[o] = y;
+                            if (m.Yb) m.Yb[o] = f32_to_bf16(y);
+                        }
+                    } else if (valid && t < m.n) {
+                        const size_t o = size_t(t) * m.m + row;
+                        float y;
+                        if (m.epi == EPI_NORM) y = x * inv[j];
+                        else if (m.epi == EPI_RESID) y = base[j] + x;
+                        else if (m.epi == EPI_HEAD) y = row < m.vocab_real ? x * inv[j] : -INFINITY;
+                        else y = x;
+                        m.Y[o] = y;
+                        if (m.Yb) m.Yb[o] = f32_to_bf16(y);
+                    }
+                }
+            }
+        }
+    }
+    if (splits > 1) cluster_sync();  // nobody leaves while its shared memory may still be read
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -273,7 +349,7 @@ bool gemm_supported(const MatArgs& a) {
            (a.epi == EPI_RESID || a.epi == EPI_RAW || a.inv_in != nullptr);
 }
 
-void launch_gemm(const MatArgs& a, uint32_t* err_flag, cudaStream_t s) {
+void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s) {
     static thread_local GemmMapCache cache;
     static bool configured = false;
     const uint32_t n_pad = (a.n + 15) / 16 * 16;
@@ -290,12 +366,18 @@ void launch_gemm(const MatArgs& a, uint32_t* err_flag, cudaStream_t s) {
     const uint32_t budget = 200 * 1024;
     uint32_t stages = std::min<uint32_t>(8, (budget - 1024 - 256) / stage_bytes);
     stages = std::max(stages, 2u);
-    const size_t smem = size_t(stages) * stage_bytes + 1024 + (3 * stages + 1) * 8 + 16;
+    const uint32_t ring = std::max(stages * stage_bytes, gemm::BM * (n_pad + 1) * 4);
+    const size_t smem = size_t(ring) + 1024 + (3 * stages + 1) * 8 + 16;
     if (!configured) {
         VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
+    // Split k over a cluster when the tiles alone cannot fill the SMs (the reference splits K the
+    // same way when a GEMM has few tiles, encode.rs:545-553).
+    const uint32_t tiles = a.m / gemm::BM, nkb = a.k / gemm::BK;
+    uint32_t splits = std::min(8u, std::min(sm_count / tiles, nkb));
+    splits = std::max(splits, 1u);
     gemm::Args g;
     g.m = a;
     g.n_pad = n_pad;
@@ -303,10 +385,22 @@ void launch_gemm(const MatArgs& a, uint32_t* err_flag, cudaStream_t s) {
     uint32_t cols = 32;
     while (cols < n_pad) cols *= 2;
     g.tmem_cols = cols;
+    g.splits = splits;
     g.err_flag = err_flag;
-    const uint32_t grid = a.m / gemm::BM;
-    if (a.int8) gemm::gemm_kernel<true><<<grid, gemm::THREADS, smem, s>>>(it->second, g);
-    else gemm::gemm_kernel<false><<<grid, gemm::THREADS, smem, s>>>(it->second, g);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * splits);
+    cfg.blockDim = dim3(gemm::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = splits > 1 ? 1 : 0;
+    if (a.int8) VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm::gemm_kernel<true>, it->second, g));
+    else VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm::gemm_kernel<false>, it->second, g));
     launch_counter()++;
 }
 

@@ -1,0 +1,181 @@
+// Rejection-sampling acceptance over draft and target logits (not in the reference, whose rule
+// is "draw the target's token on every row and accept a draft that equals it",
+// kernels.metal:1578-1589; this is the textbook speculative-sampling rule, built on the
+// reference sampler's conventions so that it can be checked bit for bit).
+//
+// Per stream, with k drafts x_1..x_k drawn from q_1..q_k and target rows p_0..p_k (bf16 logits):
+//   e(x) = 2^((x - max) log2(e) / T) with the sampler's exp2; Z = the sum of e in the sampler's
+//   order (thread t of 1024 adds ids t, t + 1024, ...; then tg_scan's association);
+//   draft i is accepted iff (u_i * eq(x_i)) * Zp < ep(x_i) * Zq, u_i = uniform01(seed, pos0 + i, 0);
+//   at the first rejected i the replacement is drawn from max(0, ep_j Zq - eq_j Zp) by the sampler's
+//   inverse CDF at uniform01(seed, pos0 + i, 1); with all accepted, the bonus token from p_k at
+//   uniform01(seed, pos0 + k, 0). Outputs: accepted count, that token, rollback = k - accepted.
+// Two kernels: per-row statistics (max, argmax, Z) for all S (2k + 1) rows at once -- one pass
+// over the logits from HBM -- then one block per stream that decides and draws (its two rows
+// come from L2).
+#include <cfloat>
+
+#include "kernels.h"
+
+namespace vlt {
+
+namespace spec {
+
+constexpr uint32_t THREADS = 1024;
+__device__ __forceinline__ uint32_t ex_at(uint32_t t) { return t + t / 32; }
+
+// kernels.metal:1482-1501 `tg_scan` (see k_small.cu).
+__device__ void tg_scan(float v, float* ex, float* base, uint32_t tid) {
+    ex[ex_at(tid)] = v;
+    __syncthreads();
+    if (tid < 32) {
+        float acc = 0.0f;
+        for (uint32_t i = 32 * tid; i < 32 * tid + 32; i++) {
+            const float x = ex[ex_at(i)];
+            ex[ex_at(i)] = acc;
+            acc = __fadd_rn(acc, x);
+        }
+        base[tid] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float acc = 0.0f;
+        for (uint32_t g = 0; g < 32; g++) {
+            const float x = base[g];
+            base[g] = acc;
+            acc = __fadd_rn(acc, x);
+        }
+        ex[ex_at(THREADS)] = acc;
+    }
+    __syncthreads();
+    ex[ex_at(tid)] = __fadd_rn(ex[ex_at(tid)], base[tid / 32]);
+    __syncthreads();
+}
+
+struct RowStats {
+    float max;
+    uint32_t argmax;
+    float z;
+    uint32_t pad;
+};
+
+__device__ __forceinline__ float e_of(uint16_t x, float mx, float c) { return soft_exp2(__fmul_rn(__fsub_rn(bf16_to_f32(x), mx), c)); }
+
+// One block per row of logits (p rows first, then q rows): max, argmax (ties to the lowest id), Z.
+__global__ void __launch_bounds__(THREADS) stats_kernel(const uint16_t* __restrict__ p, const uint16_t* __restrict__ q, uint32_t p_rows, uint32_t vocab,
+                                                        float c, RowStats* out) {
+    __shared__ float ex[THREADS + THREADS / 32 + 1];
+    __shared__ float base[32];
+    __shared__ float bvs[32];
+    __shared__ uint32_t bis[32];
+    const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid % 32;
+    const uint16_t* x = r < p_rows ? p + size_t(r) * vocab : q + size_t(r - p_rows) * vocab;
+    float mx = -FLT_MAX;
+    uint32_t am = 0xffffffffu;
+    for (uint32_t i = tid; i < vocab; i += THREADS) better(mx, am, bf16_to_f32(x[i]), i);
+    warp_best(mx, am);
+    if (lane == 0) { bvs[tid / 32] = mx; bis[tid / 32] = am; }
+    __syncthreads();
+    mx = bvs[0];
+    am = bis[0];
+    for (uint32_t i = 1; i < 32; i++) better(mx, am, bvs[i], bis[i]);
+    float s = 0.0f;
+    for (uint32_t i = tid; i < vocab; i += THREADS) s = __fadd_rn(s, e_of(x[i], mx, c));
+    tg_scan(s, ex, base, tid);
+    if (tid == 0) out[r] = RowStats{mx, am, ex[ex_at(THREADS)], 0};
+}
+
+// The sampler's inverse CDF (kernels.metal:1540-1559) over weights w(i) >= 0; `fallback` if they
+// sum to 0 or the target falls past the last term.
+template <typename W>
+__device__ uint32_t inverse_cdf(uint32_t vocab, W w, float u, uint32_t fallback, float* ex, float* base, uint32_t* pick, uint32_t tid) {
+    float a = 0.0f;
+    for (uint32_t i = tid; i < vocab; i += THREADS) a = __fadd_rn(a, w(i));
+    tg_scan(a, ex, base, tid);
+    const float total = ex[ex_at(THREADS)];
+    if (!(total > 0.0f)) return fallback;
+    const float target = __fmul_rn(u, total);
+    if (tid == 0) *pick = 0xffffffffu;
+    __syncthreads();
+    const float lo = ex[ex_at(tid)];
+    if (lo <= target && target < ex[ex_at(tid + 1)]) {
+        float acc = 0.0f;
+        uint32_t j = 0xffffffffu;
+        for (uint32_t i = tid; i < vocab; i += THREADS) {
+            const float e = w(i);
+            acc = __fadd_rn(acc, e);
+            if (e > 0.0f) j = i;
+            if (__fsub_rn(target, lo) < acc) break;
+        }
+        *pick = j;
+    }
+    __syncthreads();
+    const uint32_t j = *pick;
+    return j == 0xffffffffu ? fallback : j;
+}
+
+// One block per stream.
+__global__ void __launch_bounds__(THREADS) decide_kernel(const uint16_t* __restrict__ p, const uint16_t* __restrict__ q, const uint32_t* __restrict__ drafts,
+                                                         const RowStats* __restrict__ stats, uint32_t streams, uint32_t k, uint32_t vocab, float c,
+                                                         const uint64_t* __restrict__ seeds, const uint32_t* __restrict__ pos0, uint32_t* accepted,
+                                                         uint32_t* token, uint32_t* rollback) {
+    __shared__ float ex[THREADS + THREADS / 32 + 1];
+    __shared__ float base[32];
+    __shared__ uint32_t pick, first_reject;
+    const uint32_t s = blockIdx.x, tid = threadIdx.x;
+    const uint32_t seed_lo = uint32_t(seeds[s]), seed_hi = uint32_t(seeds[s] >> 32);
+    const RowStats* ps = stats + size_t(s) * (k + 1);
+    const RowStats* qs = stats + size_t(streams) * (k + 1) + size_t(s) * k;
+    const uint16_t* pp = p + size_t(s) * (k + 1) * vocab;
+    const uint16_t* qq = q + size_t(s) * k * vocab;
+    if (tid == 0) {
+        uint32_t i = 0;
+        for (; i < k; i++) {
+            const uint32_t x = drafts[s * k + i];
+            const float ep = e_of(pp[size_t(i) * vocab + x], ps[i].max, c), eq = e_of(qq[size_t(i) * vocab + x], qs[i].max, c);
+            const float u = uniform01(seed_lo, seed_hi, pos0[s] + i, 0);
+            const float lhs = __fmul_rn(__fmul_rn(u, eq), ps[i].z), rhs = __fmul_rn(ep, qs[i].z);
+            if (!(lhs < rhs)) break;
+        }
+        first_reject = i;
+    }
+    __syncthreads();
+    const uint32_t i = first_reject;
+    uint32_t tok;
+    if (i < k) {
+        const uint16_t* pi = pp + size_t(i) * vocab;
+        const uint16_t* qi = qq + size_t(i) * vocab;
+        const float pm = ps[i].max, qm = qs[i].max, zp = ps[i].z, zq = qs[i].z;
+        auto resid = [&](uint32_t j) {
+            const float a = __fmul_rn(e_of(pi[j], pm, c), zq), b = __fmul_rn(e_of(qi[j], qm, c), zp);
+            const float d = __fsub_rn(a, b);
+            return d > 0.0f ? d : 0.0f;
+        };
+        tok = inverse_cdf(vocab, resid, uniform01(seed_lo, seed_hi, pos0[s] + i, 1), ps[i].argmax, ex, base, &pick, tid);
+    } else {
+        const uint16_t* pk = pp + size_t(k) * vocab;
+        const float pm = ps[k].max;
+        auto w = [&](uint32_t j) { return e_of(pk[j], pm, c); };
+        tok = inverse_cdf(vocab, w, uniform01(seed_lo, seed_hi, pos0[s] + k, 0), ps[k].argmax, ex, base, &pick, tid);
+    }
+    if (tid == 0) {
+        accepted[s] = i;
+        token[s] = tok;
+        rollback[s] = k - i;
+    }
+}
+
+}  // namespace spec
+
+// p [S][k+1][V], q [S][k][V] bf16 on the device; stats: scratch for S (2k + 1) rows of 16 bytes.
+void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab, float temperature,
+                        const uint64_t* seeds, const uint32_t* pos0, void* stats, uint32_t* accepted, uint32_t* token, uint32_t* rollback, cudaStream_t s) {
+    const float c = LOG2E / temperature;  // the same IEEE division as the device's __fdiv_rn
+    spec::stats_kernel<<<streams * (2 * k + 1), spec::THREADS, 0, s>>>(p, q, streams * (k + 1), vocab, c, static_cast<spec::RowStats*>(stats));
+    launch_counter()++;
+    spec::decide_kernel<<<streams, spec::THREADS, 0, s>>>(p, q, drafts, static_cast<const spec::RowStats*>(stats), streams, k, vocab, c, seeds, pos0, accepted,
+                                                          token, rollback);
+    launch_counter()++;
+}
+
+}  // namespace vlt

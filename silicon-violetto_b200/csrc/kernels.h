@@ -71,7 +71,7 @@ void launch_attn_combine(const AttnArgs& a, cudaStream_t s);
 // The tcgen05 GEMM for 16..256 tokens: needs Xb (bf16 X, rows padded to 16), inv_in for the
 // normed epilogues, m a multiple of 128, one int8 scale per row.
 bool gemm_supported(const MatArgs& a);
-void launch_gemm(const MatArgs& a, uint32_t* err_flag, cudaStream_t s);
+void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s);
 void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s);  // n <= 8, tensor cores fed from registers
 void launch_matmul_rows(const MatArgs& a, cudaStream_t s);                      // any n, scalar (cross-check, odd scale groups)
 // out[r] = in[rows ? rows[r] : r] as fp32 (and bf16); inv[r] = 1 / rms (kernels.metal:117-148).
@@ -85,6 +85,9 @@ void launch_kv_compact(const RunIn* runs, const uint32_t* path, const uint32_t* 
                        const uint32_t* page_table, KvArgs kv, uint32_t n_runs, uint32_t n_layers, cudaStream_t s);
 void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed, const uint32_t* trace, const uint32_t* trace_len, ReplayArgs ra,
                          uint32_t n_runs, uint32_t* tree, cudaStream_t s);
+// Rejection-sampling acceptance over bf16 draft and target logits on the device (k_spec.cu).
+void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab, float temperature,
+                        const uint64_t* seeds, const uint32_t* pos0, void* stats, uint32_t* accepted, uint32_t* token, uint32_t* rollback, cudaStream_t s);
 void launch_kv_fill(uint16_t* k_cache, uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t n_layers, uint32_t slot, uint32_t from,
                     uint32_t to, uint32_t seed, cudaStream_t s);
 

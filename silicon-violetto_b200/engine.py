@@ -277,6 +277,23 @@ class Engine:
         _check(lib().vlt_sample_logits(self.h, lp, cs, _ptr(pos), C.c_uint32(n), _ptr(out)))
         return out
 
+    def spec_accept(self, p, q, drafts, temperature: float, seeds, pos0, reps: int = 1):
+        """Rejection-sampling acceptance on bf16 logits (uint16 bit patterns): p [S][k+1][V], q [S][k][V],
+        drafts [S][k]. Returns (accepted, token, rollback, kernel seconds)."""
+        p = np.ascontiguousarray(p, np.uint16)
+        q = np.ascontiguousarray(q, np.uint16)
+        s, k, v = q.shape
+        if p.shape != (s, k + 1, v) or v != self.desc.vocab:
+            raise EngineError(f"spec_accept: p {p.shape} / q {q.shape} do not fit k+1 / k rows of vocab {self.desc.vocab}")
+        drafts = _u32(drafts).reshape(s, k)
+        seeds = np.ascontiguousarray(seeds, np.uint64)
+        pos0 = _u32(pos0)
+        acc, tok, rb = (np.zeros(s, np.uint32) for _ in range(3))
+        secs = C.c_double()
+        _check(lib().vlt_spec_accept(self.h, _ptr(p, C.c_uint16), _ptr(q, C.c_uint16), _ptr(drafts), C.c_uint32(s), C.c_uint32(k), C.c_float(temperature),
+                                     _ptr(seeds, C.c_uint64), _ptr(pos0), C.c_uint32(reps), _ptr(acc), _ptr(tok), _ptr(rb), C.byref(secs)))
+        return acc, tok, rb, secs.value
+
     def set_profile_skip(self, mask: int) -> None:
         lib().vlt_set_profile_skip(self.h, C.c_uint32(mask))
 
