@@ -105,6 +105,7 @@ struct Args {
     uint32_t tmem_cols; // power of two >= max(32, n_pad)
     uint32_t splits;    // blocks of a cluster that share a weight tile, each over a slice of k
     uint32_t* err_flag;
+    unsigned long long* dbg;  // TEMP timing probe
 };
 
 }  // namespace gemm
@@ -119,6 +120,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     return false;
 }
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define PROBE(i) do { if (a.dbg && blockIdx.x == 0 && (tid == 64 || ((i) == 1 && tid == 0) || ((i) == 2 && tid == 32))) a.dbg[i] = gtime(); } while (0)
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     const uint32_t n_pad = a.n_pad, stages = a.stages, splits = a.splits;
     const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = INT8 ? BM * BK : 0;
     const uint32_t stage_bytes = a_bytes + b_bytes + raw_bytes;
-    const uint32_t ring_bytes = max(stages * stage_bytes, BM * (n_pad + 1) * 4);  // the partial tile reuses the ring
+    const uint32_t ring_bytes = max(stages * stage_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the ring
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes);
     // full[s], conv[s], empty[s], then the accumulator's barrier
     const uint32_t bar_full = smem_u32(bars), bar_conv = bar_full + 8 * stages, bar_empty = bar_conv + 8 * stages, bar_accum = bar_empty + 8 * stages;
@@ -161,6 +164,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     auto stage_raw = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes + b_bytes; };
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    PROBE(10);
     const uint32_t rank = splits > 1 ? cluster_rank() : 0, tile = blockIdx.x / splits;
     const uint32_t row0 = tile * BM, nkb_all = a.m.k / BK;
     // This block's k blocks: an even share, the first ranks one more.
@@ -187,6 +191,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    PROBE(0);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -199,6 +204,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
                 tma_load_2d(INT8 ? stage_raw(s) : stage_a(s), &maps.a, int(kb * BK), int(row0), bar_full + 8 * s);
                 tma_load_2d(stage_b(s), &maps.b, int(kb * BK), 0, bar_full + 8 * s);
             }
+            PROBE(1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -214,6 +220,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
                 mma_commit(bar_empty + 8 * s);  // arrives once these MMAs have read the stage
             }
             if (ok) mma_commit(bar_accum);
+            PROBE(2);
         }
     } else if (INT8) {
         // Raw int8 [128][64] to bf16 in the swizzled layout: a thread takes 16 bytes of a row at a time.
@@ -245,7 +252,9 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     // The accumulator to shared memory as fp32 [128][n_pad + 1] (the ring is free once the MMAs are done).
     const uint32_t pitch = n_pad + 1;
     if (warp >= 2) {
+        PROBE(3);
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
+        PROBE(4);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t quarter = warp & 3, half = (warp - 2) >> 2, r = quarter * 32 + lane;
@@ -265,71 +274,92 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    PROBE(5);
     if (splits > 1) cluster_sync();  // every block's partial is in place
+    PROBE(6);
 
-    if (warp >= 2 && !*abort_flag) {
-        const MatArgs& m = a.m;
-        // Rows this block finishes: an even share of the tile's 64 row pairs (a gate/up pair stays together).
-        const uint32_t u_begin = rank * (64 / splits) + min(rank, 64 % splits), u_count = 64 / splits + (rank < 64 % splits ? 1 : 0);
-        const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
+    // Rows this block finishes: an even share of the tile's 64 row pairs (a gate/up pair stays together).
+    const uint32_t u_begin = rank * (64 / splits) + min(rank, 64 % splits), u_count = 64 / splits + (rank < 64 % splits ? 1 : 0);
+    const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
+    // With a split, the rows' sums over the cluster's partials go to a second buffer first: a warp reads
+    // a row's tokens, contiguous in the other block's shared memory, and adds the ranks up in order.
+    float* sums = reinterpret_cast<float*>(smem) + size_t(BM) * pitch;
+    if (splits > 1 && warp >= 2 && !*abort_flag) {
         uint32_t remote[8];
 #pragma unroll
         for (uint32_t s = 0; s < 8; s++) remote[s] = s < splits ? map_to_rank(smem_base, s) : 0;  // (also orders the loads below after the barrier)
-        const uint32_t ew = warp - 2;
-        for (uint32_t rg = r_begin; rg < r_end; rg += 32) {
-            const uint32_t r = rg + lane;
-            const bool valid = r < r_end;
-            const uint32_t row = row0 + r;
-            const float scale = INT8 && valid ? bf16_to_f32(m.scales[row]) : 1.0f;
-            // Tokens in batches of TB per warp, so that the loads of a batch are all in flight together.
-            constexpr uint32_t TB = 4;
-            for (uint32_t t0 = ew * TB; t0 < m.n; t0 += CONV_WARPS * TB) {
-                float v[TB], inv[TB], base[TB];
+        for (uint32_t r = r_begin + (warp - 2); r < r_end; r += CONV_WARPS) {
+            for (uint32_t t = lane; t < n_pad; t += 32) {
+                float v = 0.0f;
 #pragma unroll
-                for (uint32_t j = 0; j < TB; j++) v[j] = 0.0f;
-                if (valid) {
-#pragma unroll
-                    for (uint32_t s = 0; s < 8; s++)
-                        if (s < splits) {
-#pragma unroll
-                            for (uint32_t j = 0; j < TB; j++) v[j] += ld_cluster(remote[s] + (r * pitch + min(t0 + j, n_pad - 1)) * 4);
-                        }
-                }
-#pragma unroll
-                for (uint32_t j = 0; j < TB; j++) {
-                    const uint32_t t = min(t0 + j, m.n - 1);
-                    inv[j] = m.inv_in ? __ldg(m.inv_in + t) : 1.0f;
-                    base[j] = (m.epi == EPI_RESID && valid) ? m.base[size_t(t) * m.m + row] : 0.0f;
-                }
-#pragma unroll
-                for (uint32_t j = 0; j < TB; j++) {
-                    const uint32_t t = t0 + j;
-                    const float x = v[j] * scale;
-                    if (m.epi == EPI_SWIGLU) {
-                        const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-                        if (valid && t < m.n && (lane & 1) == 0) {
-                            const float g = x * inv[j], u = other * inv[j];
-                            const float y = g * (1.0f / (1.0f + __expf(-g))) * u;
-                            const size_t o = size_t(t) * (m.m / 2) + row / 2;
-                            m.Y[o] = y;
-                            if (m.Yb) m.Yb[o] = f32_to_bf16(y);
-                        }
-                    } else if (valid && t < m.n) {
-                        const size_t o = size_t(t) * m.m + row;
-                        float y;
-                        if (m.epi == EPI_NORM) y = x * inv[j];
-                        else if (m.epi == EPI_RESID) y = base[j] + x;
-                        else if (m.epi == EPI_HEAD) y = row < m.vocab_real ? x * inv[j] : -INFINITY;
-                        else y = x;
-                        m.Y[o] = y;
-                        if (m.Yb) m.Yb[o] = f32_to_bf16(y);
-                    }
-                }
+                for (uint32_t s = 0; s < 8; s++)
+                    if (s < splits) v += ld_cluster(remote[s] + (r * pitch + t) * 4);
+                sums[(r - r_begin) * pitch + t] = v;
             }
         }
     }
+    PROBE(7);
+    __syncthreads();
+    if (warp >= 2 && !*abort_flag) {
+        const MatArgs& m = a.m;
+        const float* src = splits > 1 ? sums : reinterpret_cast<const float*>(smem) + size_t(r_begin) * pitch;
+        const uint32_t ew = warp - 2;
+        // A warp's work is a list of batches (32 rows x TB tokens). The residual may alias the output,
+        // so the compiler cannot move a batch's loads above the previous batch's stores: the next
+        // batch's loads are issued by hand before the current one is stored.
+        constexpr uint32_t TB = 8;
+        const uint32_t per_rg = (m.n + CONV_WARPS * TB - 1) / (CONV_WARPS * TB), n_rg = (r_end - r_begin + 31) / 32, total = per_rg * n_rg;
+        struct Batch { float v[TB], inv[TB], base[TB]; };
+        auto load = [&](uint32_t bi, Batch& bt) {
+            const uint32_t r = r_begin + 32 * (bi / per_rg) + lane, t0 = (ew + CONV_WARPS * (bi % per_rg)) * TB;
+            const bool valid = r < r_end;
+#pragma unroll
+            for (uint32_t j = 0; j < TB; j++) {
+                const uint32_t t = min(t0 + j, m.n - 1);
+                bt.v[j] = valid ? src[(r - r_begin) * pitch + t] : 0.0f;
+                bt.inv[j] = m.inv_in ? __ldg(m.inv_in + t) : 1.0f;
+                bt.base[j] = (m.epi == EPI_RESID && valid) ? m.base[size_t(t) * m.m + row0 + r] : 0.0f;
+            }
+        };
+        Batch cur, nxt;
+        if (total) load(0, cur);
+        for (uint32_t bi = 0; bi < total; bi++) {
+            if (bi + 1 < total) load(bi + 1, nxt);
+            const uint32_t r = r_begin + 32 * (bi / per_rg) + lane, t0 = (ew + CONV_WARPS * (bi % per_rg)) * TB;
+            const bool valid = r < r_end;
+            const uint32_t row = row0 + r;
+            const float scale = INT8 && valid ? bf16_to_f32(__ldg(m.scales + row)) : 1.0f;
+#pragma unroll
+            for (uint32_t j = 0; j < TB; j++) {
+                const uint32_t t = t0 + j;
+                const float x = cur.v[j] * scale;
+                if (m.epi == EPI_SWIGLU) {
+                    const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                    if (valid && t < m.n && (lane & 1) == 0) {
+                        const float g = x * cur.inv[j], u = other * cur.inv[j];
+                        const float y = g * (1.0f / (1.0f + __expf(-g))) * u;
+                        const size_t o = size_t(t) * (m.m / 2) + row / 2;
+                        m.Y[o] = y;
+                        if (m.Yb) m.Yb[o] = f32_to_bf16(y);
+                    }
+                } else if (valid && t < m.n) {
+                    const size_t o = size_t(t) * m.m + row;
+                    float y;
+                    if (m.epi == EPI_NORM) y = x * cur.inv[j];
+                    else if (m.epi == EPI_RESID) y = cur.base[j] + x;
+                    else if (m.epi == EPI_HEAD) y = row < m.vocab_real ? x * cur.inv[j] : -INFINITY;
+                    else y = x;
+                    m.Y[o] = y;
+                    if (m.Yb) m.Yb[o] = f32_to_bf16(y);
+                }
+            }
+            cur = nxt;
+        }
+    }
+    PROBE(8);
     if (splits > 1) cluster_sync();  // nobody leaves while its shared memory may still be read
     __syncthreads();
+    PROBE(9);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
@@ -366,7 +396,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     const uint32_t budget = 200 * 1024;
     uint32_t stages = std::min<uint32_t>(8, (budget - 1024 - 256) / stage_bytes);
     stages = std::max(stages, 2u);
-    const uint32_t ring = std::max(stages * stage_bytes, gemm::BM * (n_pad + 1) * 4);
+    const uint32_t ring = std::max(stages * stage_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
     const size_t smem = size_t(ring) + 1024 + (3 * stages + 1) * 8 + 16;
     if (!configured) {
         VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -376,8 +406,29 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     // Split k over a cluster when the tiles alone cannot fill the SMs (the reference splits K the
     // same way when a GEMM has few tiles, encode.rs:545-553).
     const uint32_t tiles = a.m / gemm::BM, nkb = a.k / gemm::BK;
-    uint32_t splits = std::min(8u, std::min(sm_count / tiles, nkb));
-    splits = std::max(splits, 1u);
+    static thread_local std::map<std::tuple<bool, uint32_t, uint32_t>, uint32_t> wave;  // (int8, smem, cluster size) -> clusters one wave holds
+    uint32_t splits = std::max(1u, std::min(8u, std::min(sm_count / tiles, nkb)));
+    for (; splits > 1; splits--) {
+        auto wk = std::make_tuple(a.int8, uint32_t(smem), splits);
+        auto w = wave.find(wk);
+        if (w == wave.end()) {
+            cudaLaunchConfig_t q = {};
+            q.gridDim = dim3(tiles * splits);
+            q.blockDim = dim3(gemm::THREADS);
+            q.dynamicSmemBytes = smem;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = splits;
+            qa[0].val.clusterDim.y = qa[0].val.clusterDim.z = 1;
+            q.attrs = qa;
+            q.numAttrs = 1;
+            int n_clusters = 0;
+            const cudaError_t e = a.int8 ? cudaOccupancyMaxActiveClusters(&n_clusters, gemm::gemm_kernel<true>, &q)
+                                         : cudaOccupancyMaxActiveClusters(&n_clusters, gemm::gemm_kernel<false>, &q);
+            w = wave.emplace(wk, e == cudaSuccess ? uint32_t(n_clusters) : 0u).first;
+        }
+        if (tiles <= w->second) break;  // every cluster is resident at once
+    }
     gemm::Args g;
     g.m = a;
     g.n_pad = n_pad;
@@ -387,6 +438,9 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     g.tmem_cols = cols;
     g.splits = splits;
     g.err_flag = err_flag;
+    static unsigned long long* dbg = nullptr;
+    if (getenv("VLT_GEMM_DEBUG") && !dbg) { cudaMalloc(&dbg, 128); }
+    g.dbg = dbg;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * splits);
     cfg.blockDim = dim3(gemm::THREADS);
@@ -402,6 +456,13 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     if (a.int8) VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm::gemm_kernel<true>, it->second, g));
     else VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm::gemm_kernel<false>, it->second, g));
     launch_counter()++;
+    if (dbg) {
+        cudaStreamSynchronize(s);
+        unsigned long long h[16];
+        cudaMemcpy(h, dbg, 128, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u: tma_done %lld mma_done %lld conv_done %lld accum %lld dumped %lld csync %lld summed %lld stored %lld end %lld | setup took %lld (ns from setup)\n", a.m, a.k, a.n, splits,
+                (long long)(h[1]-h[0]), (long long)(h[2]-h[0]), (long long)(h[3]-h[0]), (long long)(h[4]-h[0]), (long long)(h[5]-h[0]), (long long)(h[6]-h[0]), (long long)(h[7]-h[0]), (long long)(h[8]-h[0]), (long long)(h[9]-h[0]), (long long)(h[0]-h[10]));
+    }
 }
 
 }  // namespace vlt
