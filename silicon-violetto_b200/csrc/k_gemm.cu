@@ -82,6 +82,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
 // Four int8 (one word) to two bf16 pairs, exactly (see k_matmul.cu).
 __device__ __forceinline__ void cvt_i8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
     const uint32_t u = w ^ 0x80808080u;
@@ -106,6 +117,7 @@ struct Args {
     uint32_t splits;    // blocks of a cluster that share a weight tile, each over a slice of k
     uint32_t* err_flag;
     unsigned long long* dbg;  // TEMP timing probe
+    uint32_t abl;             // TEMP ablation bits
 };
 
 }  // namespace gemm
@@ -145,7 +157,7 @@ __device__ __forceinline__ float ld_cluster(uint32_t addr) {
 // grid: (m / 128) * splits blocks in clusters of `splits`. A cluster owns a 128-row weight tile;
 // its blocks each stream a slice of k into their own TMEM accumulator, put it in shared memory,
 // and each then adds up, over distributed shared memory and in rank order, the rows it owns.
-template <bool INT8>
+template <bool INT8, uint32_t EPI>
 __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -158,6 +170,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     const uint32_t bar_full = smem_u32(bars), bar_conv = bar_full + 8 * stages, bar_empty = bar_conv + 8 * stages, bar_accum = bar_empty + 8 * stages;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * stages + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* inv_s = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);  // 1/rms per token
     const uint32_t smem_base = smem_u32(smem);
     auto stage_a = [&](uint32_t s) { return smem_base + s * stage_bytes; };
     auto stage_b = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes; };
@@ -182,6 +195,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (tid >= 64)
+        for (uint32_t t = tid - 64; t < n_pad; t += THREADS - 64) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -206,6 +221,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             }
             PROBE(1);
         }
+        __syncwarp();  // the idle lanes wait here, so that the warp reaches the block barriers converged
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, n_pad);
@@ -222,6 +238,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             if (ok) mma_commit(bar_accum);
             PROBE(2);
         }
+        __syncwarp();
     } else if (INT8) {
         // Raw int8 [128][64] to bf16 in the swizzled layout: a thread takes 16 bytes of a row at a time.
         const uint32_t cid = tid - 64;
@@ -249,22 +266,70 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         }
     }
 
-    // The accumulator to shared memory as fp32 [128][n_pad + 1] (the ring is free once the MMAs are done).
+    // Rows this block finishes: an even share of the tile's 64 row pairs (a gate/up pair stays together).
+    const uint32_t u_begin = rank * (64 / splits) + min(rank, 64 % splits), u_count = 64 / splits + (rank < 64 % splits ? 1 : 0);
+    const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
     const uint32_t pitch = n_pad + 1;
+    const MatArgs& m = a.m;
+    const uint32_t ew = warp - 2;
+
+    // One row's 16 consecutive tokens to global memory (kept small and specialised per epilogue: the
+    // code of a fat, fully unrolled epilogue does not stay in the instruction cache). The residual's
+    // loads go out together before the first store (it may alias the output); 1/rms comes from
+    // shared memory.
+    auto emit = [&](uint32_t r, bool valid, uint32_t t0, float scale, float (&v)[16]) {
+        const uint32_t row = row0 + r;
+        // Loads first, then the arithmetic, then the stores: in that order the 16 tokens overlap.
+        float base[16], inv[16], y[16];
+#pragma unroll
+        for (uint32_t j = 0; j < 16; j++) {
+            inv[j] = inv_s[t0 + j];
+            base[j] = (EPI == EPI_RESID && valid && t0 + j < m.n) ? m.base[size_t(t0 + j) * m.m + row] : 0.0f;
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 16; j++) {
+            const float x = v[j] * scale;
+            if (EPI == EPI_SWIGLU) {
+                const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                const float gt = x * inv[j], up = other * inv[j];
+                y[j] = gt * __fdividef(1.0f, 1.0f + __expf(-gt)) * up;
+            } else if (EPI == EPI_NORM) y[j] = x * inv[j];
+            else if (EPI == EPI_RESID) y[j] = base[j] + x;
+            else if (EPI == EPI_HEAD) y[j] = row < m.vocab_real ? x * inv[j] : -INFINITY;
+            else y[j] = x;
+        }
+        const bool writes = valid && (EPI != EPI_SWIGLU || (lane & 1) == 0);
+        const uint32_t out_w = EPI == EPI_SWIGLU ? m.m / 2 : m.m, out_r = EPI == EPI_SWIGLU ? row / 2 : row;
+        if (writes) {
+#pragma unroll
+            for (uint32_t j = 0; j < 16; j++)
+                if (t0 + j < m.n) {
+                    const size_t o = size_t(t0 + j) * out_w + out_r;
+                    m.Y[o] = y[j];
+                    if (m.Yb) m.Yb[o] = f32_to_bf16(y[j]);
+                }
+        }
+    };
+
     if (warp >= 2) {
         PROBE(3);
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
         PROBE(4);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t quarter = warp & 3, half = (warp - 2) >> 2, r = quarter * 32 + lane;
+            // Two warps share a quarter of the TMEM lanes (rows) and take alternate groups of 16 tokens.
+            const uint32_t quarter = warp & 3, half = ew >> 2, r = quarter * 32 + lane;
+            const float scale = INT8 ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
             float* part = reinterpret_cast<float*>(smem) + size_t(r) * pitch;
-            for (uint32_t c0 = 32 * half; c0 < n_pad; c0 += 64) {
-                float acc[32];
-                tmem_ld32(tmem_base + ((quarter * 32) << 16) + c0, acc);
+            for (uint32_t c0 = 16 * half; c0 < n_pad; c0 += 32) {
+                float acc[16];
+                tmem_ld16(tmem_base + ((quarter * 32) << 16) + c0, acc);
+                if (splits == 1) {
+                    emit(r, true, c0, scale, acc);  // no other block adds to this tile: straight out
+                } else {
 #pragma unroll
-                for (uint32_t j = 0; j < 32; j++)
-                    if (c0 + j < n_pad) part[c0 + j] = acc[j];
+                    for (uint32_t j = 0; j < 16; j++) part[c0 + j] = acc[j];  // fp32 [128][n_pad + 1]: the ring is free once the MMAs are done
+                }
             }
         }
     }
@@ -275,85 +340,47 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     PROBE(5);
-    if (splits > 1) cluster_sync();  // every block's partial is in place
-    PROBE(6);
-
-    // Rows this block finishes: an even share of the tile's 64 row pairs (a gate/up pair stays together).
-    const uint32_t u_begin = rank * (64 / splits) + min(rank, 64 % splits), u_count = 64 / splits + (rank < 64 % splits ? 1 : 0);
-    const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
-    // With a split, the rows' sums over the cluster's partials go to a second buffer first: a warp reads
-    // a row's tokens, contiguous in the other block's shared memory, and adds the ranks up in order.
-    float* sums = reinterpret_cast<float*>(smem) + size_t(BM) * pitch;
-    if (splits > 1 && warp >= 2 && !*abort_flag) {
-        uint32_t remote[8];
+    if (splits > 1) {
+        cluster_sync();  // every block's partial is in place
+        PROBE(6);
+        // Each block finishes its share of the rows. First their sums over the cluster's partials, into a
+        // second buffer: a warp reads a row's tokens, contiguous in the other block's shared memory, and
+        // adds the ranks up in order (deterministic). Then a lane takes a row and emits 32 tokens at a time.
+        float* sums = reinterpret_cast<float*>(smem) + size_t(BM) * pitch;
+        if (warp >= 2 && !*abort_flag) {
+            uint32_t remote[8];
 #pragma unroll
-        for (uint32_t s = 0; s < 8; s++) remote[s] = s < splits ? map_to_rank(smem_base, s) : 0;  // (also orders the loads below after the barrier)
-        for (uint32_t r = r_begin + (warp - 2); r < r_end; r += CONV_WARPS) {
-            for (uint32_t t = lane; t < n_pad; t += 32) {
-                float v = 0.0f;
+            for (uint32_t s = 0; s < 8; s++) remote[s] = s < splits ? map_to_rank(smem_base, s) : 0;  // (also orders the loads below after the barrier)
+            // A row at a time: all of its tokens' loads from every rank go out together (n_pad <= 256: 8 chunks of 32).
+            for (uint32_t r = r_begin + ew; r < r_end; r += CONV_WARPS) {
+                float v[8];
+#pragma unroll
+                for (uint32_t c = 0; c < 8; c++) v[c] = 0.0f;
 #pragma unroll
                 for (uint32_t s = 0; s < 8; s++)
-                    if (s < splits) v += ld_cluster(remote[s] + (r * pitch + t) * 4);
-                sums[(r - r_begin) * pitch + t] = v;
+                    if (s < splits) {
+#pragma unroll
+                        for (uint32_t c = 0; c < 8; c++)
+                            if (32 * c + lane < n_pad) v[c] += ld_cluster(remote[s] + (r * pitch + 32 * c + lane) * 4);
+                    }
+#pragma unroll
+                for (uint32_t c = 0; c < 8; c++)
+                    if (32 * c + lane < n_pad) sums[(r - r_begin) * pitch + 32 * c + lane] = v[c];
             }
         }
-    }
-    PROBE(7);
-    __syncthreads();
-    if (warp >= 2 && !*abort_flag) {
-        const MatArgs& m = a.m;
-        const float* src = splits > 1 ? sums : reinterpret_cast<const float*>(smem) + size_t(r_begin) * pitch;
-        const uint32_t ew = warp - 2;
-        // A warp's work is a list of batches (32 rows x TB tokens). The residual may alias the output,
-        // so the compiler cannot move a batch's loads above the previous batch's stores: the next
-        // batch's loads are issued by hand before the current one is stored.
-        constexpr uint32_t TB = 8;
-        const uint32_t per_rg = (m.n + CONV_WARPS * TB - 1) / (CONV_WARPS * TB), n_rg = (r_end - r_begin + 31) / 32, total = per_rg * n_rg;
-        struct Batch { float v[TB], inv[TB], base[TB]; };
-        auto load = [&](uint32_t bi, Batch& bt) {
-            const uint32_t r = r_begin + 32 * (bi / per_rg) + lane, t0 = (ew + CONV_WARPS * (bi % per_rg)) * TB;
-            const bool valid = r < r_end;
+        PROBE(7);
+        __syncthreads();
+        if (warp >= 2 && !*abort_flag) {
+            const uint32_t chunks = n_pad / 16, n_rg = (r_end - r_begin + 31) / 32;
+            for (uint32_t item = ew; item < chunks * n_rg; item += CONV_WARPS) {
+                const uint32_t r = r_begin + 32 * (item / chunks) + lane, c0 = 16 * (item % chunks);
+                const bool valid = r < r_end;
+                const float scale = (INT8 && valid) ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
+                float v[16];
 #pragma unroll
-            for (uint32_t j = 0; j < TB; j++) {
-                const uint32_t t = min(t0 + j, m.n - 1);
-                bt.v[j] = valid ? src[(r - r_begin) * pitch + t] : 0.0f;
-                bt.inv[j] = m.inv_in ? __ldg(m.inv_in + t) : 1.0f;
-                bt.base[j] = (m.epi == EPI_RESID && valid) ? m.base[size_t(t) * m.m + row0 + r] : 0.0f;
+                for (uint32_t j = 0; j < 16; j++) v[j] = valid ? sums[(r - r_begin) * pitch + c0 + j] : 0.0f;
+                emit(r, valid, c0, scale, v);
             }
-        };
-        Batch cur, nxt;
-        if (total) load(0, cur);
-        for (uint32_t bi = 0; bi < total; bi++) {
-            if (bi + 1 < total) load(bi + 1, nxt);
-            const uint32_t r = r_begin + 32 * (bi / per_rg) + lane, t0 = (ew + CONV_WARPS * (bi % per_rg)) * TB;
-            const bool valid = r < r_end;
-            const uint32_t row = row0 + r;
-            const float scale = INT8 && valid ? bf16_to_f32(__ldg(m.scales + row)) : 1.0f;
-#pragma unroll
-            for (uint32_t j = 0; j < TB; j++) {
-                const uint32_t t = t0 + j;
-                const float x = cur.v[j] * scale;
-                if (m.epi == EPI_SWIGLU) {
-                    const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-                    if (valid && t < m.n && (lane & 1) == 0) {
-                        const float g = x * cur.inv[j], u = other * cur.inv[j];
-                        const float y = g * (1.0f / (1.0f + __expf(-g))) * u;
-                        const size_t o = size_t(t) * (m.m / 2) + row / 2;
-                        m.Y[o] = y;
-                        if (m.Yb) m.Yb[o] = f32_to_bf16(y);
-                    }
-                } else if (valid && t < m.n) {
-                    const size_t o = size_t(t) * m.m + row;
-                    float y;
-                    if (m.epi == EPI_NORM) y = x * cur.inv[j];
-                    else if (m.epi == EPI_RESID) y = cur.base[j] + x;
-                    else if (m.epi == EPI_HEAD) y = row < m.vocab_real ? x * cur.inv[j] : -INFINITY;
-                    else y = x;
-                    m.Y[o] = y;
-                    if (m.Yb) m.Yb[o] = f32_to_bf16(y);
-                }
-            }
-            cur = nxt;
         }
     }
     PROBE(8);
@@ -372,6 +399,17 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
 struct GemmMapCache {
     std::map<std::tuple<const void*, const void*, uint32_t, uint32_t, uint32_t>, gemm::Maps> maps;
 };
+
+typedef void (*GemmEntry)(const gemm::Maps, const gemm::Args);
+static GemmEntry gemm_entry(bool int8, uint32_t epi) {
+    switch (epi) {
+    case EPI_NORM: return int8 ? gemm::gemm_kernel<true, EPI_NORM> : gemm::gemm_kernel<false, EPI_NORM>;
+    case EPI_RESID: return int8 ? gemm::gemm_kernel<true, EPI_RESID> : gemm::gemm_kernel<false, EPI_RESID>;
+    case EPI_SWIGLU: return int8 ? gemm::gemm_kernel<true, EPI_SWIGLU> : gemm::gemm_kernel<false, EPI_SWIGLU>;
+    case EPI_HEAD: return int8 ? gemm::gemm_kernel<true, EPI_HEAD> : gemm::gemm_kernel<false, EPI_HEAD>;
+    default: return int8 ? gemm::gemm_kernel<true, EPI_RAW> : gemm::gemm_kernel<false, EPI_RAW>;
+    }
+}
 
 bool gemm_supported(const MatArgs& a) {
     const bool grouped = a.int8 && a.group < a.k;
@@ -397,10 +435,10 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     uint32_t stages = std::min<uint32_t>(8, (budget - 1024 - 256) / stage_bytes);
     stages = std::max(stages, 2u);
     const uint32_t ring = std::max(stages * stage_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
-    const size_t smem = size_t(ring) + 1024 + (3 * stages + 1) * 8 + 16;
+    const size_t smem = size_t(ring) + 1024 + (3 * stages + 1) * 8 + 16 + n_pad * 4;
     if (!configured) {
-        VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        VLT_CUDA(cudaFuncSetAttribute(gemm::gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        for (int i8 = 0; i8 < 2; i8++)
+            for (uint32_t epi = EPI_NORM; epi <= EPI_RAW; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
     // Split k over a cluster when the tiles alone cannot fill the SMs (the reference splits K the
@@ -409,7 +447,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     static thread_local std::map<std::tuple<bool, uint32_t, uint32_t>, uint32_t> wave;  // (int8, smem, cluster size) -> clusters one wave holds
     uint32_t splits = std::max(1u, std::min(8u, std::min(sm_count / tiles, nkb)));
     for (; splits > 1; splits--) {
-        auto wk = std::make_tuple(a.int8, uint32_t(smem), splits);
+        auto wk = std::make_tuple(a.int8, uint32_t(smem) * 8 + a.epi, splits);
         auto w = wave.find(wk);
         if (w == wave.end()) {
             cudaLaunchConfig_t q = {};
@@ -423,8 +461,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
             q.attrs = qa;
             q.numAttrs = 1;
             int n_clusters = 0;
-            const cudaError_t e = a.int8 ? cudaOccupancyMaxActiveClusters(&n_clusters, gemm::gemm_kernel<true>, &q)
-                                         : cudaOccupancyMaxActiveClusters(&n_clusters, gemm::gemm_kernel<false>, &q);
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, gemm_entry(a.int8, a.epi), &q);
             w = wave.emplace(wk, e == cudaSuccess ? uint32_t(n_clusters) : 0u).first;
         }
         if (tiles <= w->second) break;  // every cluster is resident at once
@@ -441,6 +478,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     static unsigned long long* dbg = nullptr;
     if (getenv("VLT_GEMM_DEBUG") && !dbg) { cudaMalloc(&dbg, 128); }
     g.dbg = dbg;
+    g.abl = getenv("VLT_GEMM_ABL") ? atoi(getenv("VLT_GEMM_ABL")) : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * splits);
     cfg.blockDim = dim3(gemm::THREADS);
@@ -453,13 +491,13 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = splits > 1 ? 1 : 0;
-    if (a.int8) VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm::gemm_kernel<true>, it->second, g));
-    else VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm::gemm_kernel<false>, it->second, g));
+    VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm_entry(a.int8, a.epi), it->second, g));
     launch_counter()++;
     if (dbg) {
         cudaStreamSynchronize(s);
         unsigned long long h[16];
         cudaMemcpy(h, dbg, 128, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "  loop: before_ld %lld after_ld %lld after_emit0 %lld after_emit1 %lld\n", (long long)(h[11]-h[0]), (long long)(h[12]-h[0]), (long long)(h[13]-h[0]), (long long)(h[14]-h[0]));
         fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u: tma_done %lld mma_done %lld conv_done %lld accum %lld dumped %lld csync %lld summed %lld stored %lld end %lld | setup took %lld (ns from setup)\n", a.m, a.k, a.n, splits,
                 (long long)(h[1]-h[0]), (long long)(h[2]-h[0]), (long long)(h[3]-h[0]), (long long)(h[4]-h[0]), (long long)(h[5]-h[0]), (long long)(h[6]-h[0]), (long long)(h[7]-h[0]), (long long)(h[8]-h[0]), (long long)(h[9]-h[0]), (long long)(h[0]-h[10]));
     }
