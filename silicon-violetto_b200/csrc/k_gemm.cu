@@ -24,8 +24,10 @@ namespace vlt {
 namespace gemm {
 
 constexpr uint32_t BM = 128, BK = 64;
+constexpr uint32_t RAW_KB = 1;  // k blocks per raw int8 stage (wider boxes measured no faster)
 constexpr uint32_t CONV_WARPS = 8;
-constexpr uint32_t THREADS = 64 + 32 * CONV_WARPS;  // warp 0: TMA, warp 1: MMA, the rest: conversion and epilogue
+constexpr uint32_t FIRST_CONV = 3;
+constexpr uint32_t THREADS = 32 * (FIRST_CONV + CONV_WARPS);  // warp 0: weight TMA, warp 1: MMA, warp 2: activation TMA, the rest: conversion and epilogue
 constexpr uint32_t SPIN = 1u << 26;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -112,7 +114,8 @@ struct Maps {
 struct Args {
     MatArgs m;
     uint32_t n_pad;     // tokens rounded up to 16: the MMA's N
-    uint32_t stages;
+    uint32_t stages;      // operand stages (A bf16 | B)
+    uint32_t raw_stages;  // int8 only: raw weight stages in front of them
     uint32_t tmem_cols; // power of two >= max(32, n_pad)
     uint32_t splits;    // blocks of a cluster that share a weight tile, each over a slice of k
     uint32_t* err_flag;
@@ -133,7 +136,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return false;
 }
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define PROBE(i) do { if (a.dbg && blockIdx.x == 0 && (tid == 64 || ((i) == 1 && tid == 0) || ((i) == 2 && tid == 32))) a.dbg[i] = gtime(); } while (0)
+#define PROBE(i) do { if (a.dbg && blockIdx.x == 0 && (tid == 96 || ((i) == 1 && tid == 0) || ((i) == 2 && tid == 32))) a.dbg[i] = gtime(); } while (0)
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -161,20 +164,24 @@ template <bool INT8, uint32_t EPI>
 __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t n_pad = a.n_pad, stages = a.stages, splits = a.splits;
-    const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = INT8 ? BM * BK : 0;
-    const uint32_t stage_bytes = a_bytes + b_bytes + raw_bytes;
-    const uint32_t ring_bytes = max(stages * stage_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the ring
+    // Two rings. `C` operand stages of (A bf16 16 KiB | B n_pad x 128 B) feed the MMA; for int8 weights `R`
+    // raw stages of 8 KiB sit in front of them, deep enough to keep this SM's share of HBM bandwidth in
+    // flight (a converted stage carries 36 KiB of shared memory for 8 KiB of HBM traffic; a raw one 8 for 8).
+    const uint32_t n_pad = a.n_pad, C = a.stages, R = INT8 ? a.raw_stages : 0, splits = a.splits;
+    const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = BM * BK * RAW_KB;
+    const uint32_t ab_bytes = a_bytes + b_bytes;
+    const uint32_t ring_bytes = max(C * ab_bytes + R * raw_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the rings
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes);
-    // full[s], conv[s], empty[s], then the accumulator's barrier
-    const uint32_t bar_full = smem_u32(bars), bar_conv = bar_full + 8 * stages, bar_empty = bar_conv + 8 * stages, bar_accum = bar_empty + 8 * stages;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * stages + 1);
+    // a_full[C], b_full[C], ab_empty[C], raw_full[R], raw_empty[R], then the accumulator's barrier
+    const uint32_t bar_afull = smem_u32(bars), bar_bfull = bar_afull + 8 * C, bar_empty = bar_bfull + 8 * C, bar_rfull = bar_empty + 8 * C,
+                   bar_rempty = bar_rfull + 8 * R, bar_accum = bar_rempty + 8 * R;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * C + 2 * R + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* inv_s = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);  // 1/rms per token
     const uint32_t smem_base = smem_u32(smem);
-    auto stage_a = [&](uint32_t s) { return smem_base + s * stage_bytes; };
-    auto stage_b = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes; };
-    auto stage_raw = [&](uint32_t s) { return smem_base + s * stage_bytes + a_bytes + b_bytes; };
+    auto stage_a = [&](uint32_t c) { return smem_base + c * ab_bytes; };
+    auto stage_b = [&](uint32_t c) { return smem_base + c * ab_bytes + a_bytes; };
+    auto stage_raw = [&](uint32_t r) { return smem_base + C * ab_bytes + r * raw_bytes; };
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     PROBE(10);
@@ -185,18 +192,22 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     const uint32_t nkb = nkb_all / splits + (rank < nkb_all % splits ? 1 : 0);
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < stages; s++) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_conv + 8 * s, 32 * CONV_WARPS);
-            mbar_init(bar_empty + 8 * s, 1);
+        for (uint32_t c = 0; c < C; c++) {
+            mbar_init(bar_afull + 8 * c, INT8 ? CONV_WARPS : 1);
+            mbar_init(bar_bfull + 8 * c, 1);
+            mbar_init(bar_empty + 8 * c, 1);
+        }
+        for (uint32_t r = 0; r < R; r++) {
+            mbar_init(bar_rfull + 8 * r, 1);
+            mbar_init(bar_rempty + 8 * r, CONV_WARPS);
         }
         mbar_init(bar_accum, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (tid >= 64)
-        for (uint32_t t = tid - 64; t < n_pad; t += THREADS - 64) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
+    if (tid >= FIRST_CONV * 32)
+        for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -209,31 +220,52 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     PROBE(0);
 
     if (warp == 0) {
+        // The weights' loader: raw int8 tiles into the deep ring, or bf16 tiles straight into the operand ring.
         if (lane == 0) {
-            const uint32_t tx = (INT8 ? raw_bytes : a_bytes) + b_bytes;
             for (uint32_t i = 0; i < nkb && ok; i++) {
-                const uint32_t s = i % stages, ph = (i / stages) & 1, kb = kb_begin + i;
-                ok = wait_or_abort(bar_empty + 8 * s, ph ^ 1, abort_flag);
-                if (!ok) break;
-                mbar_expect_tx(bar_full + 8 * s, tx);
-                tma_load_2d(INT8 ? stage_raw(s) : stage_a(s), &maps.a, int(kb * BK), int(row0), bar_full + 8 * s);
-                tma_load_2d(stage_b(s), &maps.b, int(kb * BK), 0, bar_full + 8 * s);
+                const uint32_t kb = kb_begin + i;
+                if (INT8) {
+                    if (i % RAW_KB) continue;  // one request brings RAW_KB k blocks
+                    const uint32_t j = i / RAW_KB, r = j % R, ph = (j / R) & 1;
+                    ok = wait_or_abort(bar_rempty + 8 * r, ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(bar_rfull + 8 * r, raw_bytes);
+                    tma_load_2d(stage_raw(r), &maps.a, int(kb * BK), int(row0), bar_rfull + 8 * r);
+                } else {
+                    const uint32_t c = i % C, ph = (i / C) & 1;
+                    ok = wait_or_abort(bar_empty + 8 * c, ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(bar_afull + 8 * c, a_bytes);
+                    tma_load_2d(stage_a(c), &maps.a, int(kb * BK), int(row0), bar_afull + 8 * c);
+                }
             }
             PROBE(1);
         }
         __syncwarp();  // the idle lanes wait here, so that the warp reaches the block barriers converged
+    } else if (warp == 2) {
+        // The activations' loader (they come from L2: every block reads the same rows).
+        if (lane == 0) {
+            for (uint32_t i = 0; i < nkb && ok; i++) {
+                const uint32_t c = i % C, ph = (i / C) & 1;
+                ok = wait_or_abort(bar_empty + 8 * c, ph ^ 1, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(bar_bfull + 8 * c, b_bytes);
+                tma_load_2d(stage_b(c), &maps.b, int((kb_begin + i) * BK), 0, bar_bfull + 8 * c);
+            }
+        }
+        __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, n_pad);
             for (uint32_t i = 0; i < nkb && ok; i++) {
-                const uint32_t s = i % stages, ph = (i / stages) & 1;
-                ok = wait_or_abort((INT8 ? bar_conv : bar_full) + 8 * s, ph, abort_flag);
+                const uint32_t c = i % C, ph = (i / C) & 1;
+                ok = wait_or_abort(bar_afull + 8 * c, ph, abort_flag) && wait_or_abort(bar_bfull + 8 * c, ph, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (uint32_t k4 = 0; k4 < BK / 16; k4++)
-                    mma_f16(tmem_base, smem_desc(stage_a(s) + k4 * 32), smem_desc(stage_b(s) + k4 * 32), idesc, (i | k4) != 0 ? 1u : 0u);
-                mma_commit(bar_empty + 8 * s);  // arrives once these MMAs have read the stage
+                    mma_f16(tmem_base, smem_desc(stage_a(c) + k4 * 32), smem_desc(stage_b(c) + k4 * 32), idesc, (i | k4) != 0 ? 1u : 0u);
+                mma_commit(bar_empty + 8 * c);  // arrives once these MMAs have read the stage
             }
             if (ok) mma_commit(bar_accum);
             PROBE(2);
@@ -241,28 +273,33 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         __syncwarp();
     } else if (INT8) {
         // Raw int8 [128][64] to bf16 in the swizzled layout: a thread takes 16 bytes of a row at a time.
-        const uint32_t cid = tid - 64;
+        const uint32_t cid = tid - FIRST_CONV * 32;
         for (uint32_t i = 0; i < nkb && ok; i++) {
-            const uint32_t s = i % stages, ph = (i / stages) & 1;
-            ok = wait_or_abort(bar_full + 8 * s, ph, abort_flag);
+            const uint32_t jr = i / RAW_KB, r = jr % R, rph = (jr / R) & 1, sub = i % RAW_KB, c = i % C, cph = (i / C) & 1;
+            ok = wait_or_abort(bar_rfull + 8 * r, rph, abort_flag) && wait_or_abort(bar_empty + 8 * c, cph ^ 1, abort_flag);
             if (!ok) break;
             const uint32_t q = cid & 3;
 #pragma unroll
             for (uint32_t p = 0; p < 512 / (32 * CONV_WARPS); p++) {
                 const uint32_t row = (cid >> 2) + (8 * CONV_WARPS) * p;
                 uint4 raw;
-                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(stage_raw(s) + row * 64 + q * 16));
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(stage_raw(r) + row * (64 * RAW_KB) + sub * 64 + q * 16));
                 uint4 lo, hi;
+                if (a.abl & 64) { lo = raw; hi = raw; } else {
                 cvt_i8x4(raw.x, lo.x, lo.y);
                 cvt_i8x4(raw.y, lo.z, lo.w);
                 cvt_i8x4(raw.z, hi.x, hi.y);
-                cvt_i8x4(raw.w, hi.z, hi.w);
-                const uint32_t base = stage_a(s) + row * 128, sw = row & 7;
+                cvt_i8x4(raw.w, hi.z, hi.w); }
+                const uint32_t base = stage_a(c) + row * 128, sw = row & 7;
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q) ^ sw) << 4)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q + 1) ^ sw) << 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
-            mbar_arrive(bar_conv + 8 * s);
+            if (!(a.abl & 32)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+            __syncwarp();
+            if (lane == 0) {  // one arrival per warp: 256 arrivals per stage would serialise on the barrier
+                mbar_arrive(bar_afull + 8 * c);
+                if (sub == RAW_KB - 1 || i == nkb - 1) mbar_arrive(bar_rempty + 8 * r);  // the raw stage's last k block
+            }
         }
     }
 
@@ -271,7 +308,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
     const uint32_t pitch = n_pad + 1;
     const MatArgs& m = a.m;
-    const uint32_t ew = warp - 2;
+    const uint32_t ew = warp - FIRST_CONV;
 
     // One row's 16 consecutive tokens to global memory (kept small and specialised per epilogue: the
     // code of a fat, fully unrolled epilogue does not stay in the instruction cache). The residual's
@@ -311,7 +348,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         }
     };
 
-    if (warp >= 2) {
+    if (warp >= FIRST_CONV) {
         PROBE(3);
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
         PROBE(4);
@@ -347,7 +384,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         // second buffer: a warp reads a row's tokens, contiguous in the other block's shared memory, and
         // adds the ranks up in order (deterministic). Then a lane takes a row and emits 32 tokens at a time.
         float* sums = reinterpret_cast<float*>(smem) + size_t(BM) * pitch;
-        if (warp >= 2 && !*abort_flag) {
+        if (warp >= FIRST_CONV && !*abort_flag) {
             uint32_t remote[8];
 #pragma unroll
             for (uint32_t s = 0; s < 8; s++) remote[s] = s < splits ? map_to_rank(smem_base, s) : 0;  // (also orders the loads below after the barrier)
@@ -370,7 +407,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         }
         PROBE(7);
         __syncthreads();
-        if (warp >= 2 && !*abort_flag) {
+        if (warp >= FIRST_CONV && !*abort_flag) {
             const uint32_t chunks = n_pad / 16, n_rg = (r_end - r_begin + 31) / 32;
             for (uint32_t item = ew; item < chunks * n_rg; item += CONV_WARPS) {
                 const uint32_t r = r_begin + 32 * (item / chunks) + lane, c0 = 16 * (item % chunks);
@@ -425,17 +462,23 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     auto it = cache.maps.find(key);
     if (it == cache.maps.end()) {
         gemm::Maps m;
-        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 1, false);
+        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK * gemm::RAW_KB, gemm::BM, 1, false);
         else make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 2, true);
         make_tensor_map_2d(m.b, a.Xb, a.k, n_pad, gemm::BK, n_pad, 2, true);
         it = cache.maps.emplace(key, m).first;
     }
-    const uint32_t stage_bytes = gemm::BM * gemm::BK * 2 + n_pad * gemm::BK * 2 + (a.int8 ? gemm::BM * gemm::BK : 0);
-    const uint32_t budget = 200 * 1024;
-    uint32_t stages = std::min<uint32_t>(8, (budget - 1024 - 256) / stage_bytes);
-    stages = std::max(stages, 2u);
-    const uint32_t ring = std::max(stages * stage_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
-    const size_t smem = size_t(ring) + 1024 + (3 * stages + 1) * 8 + 16 + n_pad * 4;
+    // Shared memory: operand stages of (16 KiB + n_pad x 128 B); for int8, raw stages of 8 KiB in front.
+    const uint32_t ab_bytes = gemm::BM * gemm::BK * 2 + n_pad * gemm::BK * 2, raw_bytes = gemm::BM * gemm::BK * gemm::RAW_KB;
+    const uint32_t budget = 208 * 1024;
+    uint32_t stages, raw_stages = 0;
+    if (a.int8) {
+        stages = std::max(2u, std::min(4u, (budget - 8 * raw_bytes) / ab_bytes));
+        raw_stages = std::max(2u, std::min(12u, (budget - stages * ab_bytes) / raw_bytes));
+    } else {
+        stages = std::max(2u, std::min(8u, budget / ab_bytes));
+    }
+    const uint32_t ring = std::max(stages * ab_bytes + raw_stages * raw_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
+    const size_t smem = size_t(ring) + 1024 + (3 * stages + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4;
     if (!configured) {
         for (int i8 = 0; i8 < 2; i8++)
             for (uint32_t epi = EPI_NORM; epi <= EPI_RAW; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -470,6 +513,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     g.m = a;
     g.n_pad = n_pad;
     g.stages = stages;
+    g.raw_stages = raw_stages;
     uint32_t cols = 32;
     while (cols < n_pad) cols *= 2;
     g.tmem_cols = cols;
