@@ -37,14 +37,16 @@ def _package():
         sys.path.insert(0, str(ROOT))
 
 
-def model_file(config: str, int8: bool, rank: int) -> Path:
-    """The random-init weight file (seed 0, N(0, 0.02^2), int8 per output row), written once per box."""
+def model_file(config: str, int8: bool, rank: int, layers: int = 0) -> Path:
+    """The random-init weight file (seed 0, N(0, 0.02^2), int8 per output row), written once per box.
+    `layers` > 0 cuts the model to that many layers (a profiling-size case of the same shapes)."""
     from silicon_violetto_b200 import synth
     CACHE.mkdir(parents=True, exist_ok=True)
-    path = CACHE / f"{config}_{'int8row' if int8 else 'bf16'}.vlt"
+    path = CACHE / f"{config}{f'_L{layers}' if layers else ''}_{'int8row' if int8 else 'bf16'}.vlt"
     done = path.with_suffix(".ok")
     if rank == 0 and not done.exists():
-        synth.write_target(path, config, seed=0, int8_group=0 if int8 else None)
+        c = dict(synth.CONFIGS[config], n_layers=layers) if layers else config
+        synth.write_target(path, c, seed=0, int8_group=0 if int8 else None)
         done.write_text("ok")
     while not done.exists():
         time.sleep(0.5)
@@ -91,11 +93,11 @@ KV_BYTES_PER_TOKEN_LAYER = 8 * 64 * 2 * 2  # 8 kv heads x 64 dims x bf16 x (K, V
 WEIGHT_PARAMS = 16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048
 
 
-def make_engine(E, path, streams, ctx, steps_total, device):
+def make_engine(E, path, streams, ctx, steps_total, device, attn_keys=0):
     room = ROWS * (steps_total + 8) + 64
     cfg = E.EngineConfig(max_seqs=streams, max_step_tokens=max(streams * ROWS, 64), max_chunk=16, global_kv_tokens=streams * (ctx + room + 16),
                          max_seq_len=ctx + room, max_head_rows=max(streams * ROWS, 8), device_ordinal=device)
-    return E.Engine(path, cfg, E.Tuning(spec_policy_off=True)), room
+    return E.Engine(path, cfg, E.Tuning(spec_policy_off=True, attn_keys_per_cta=attn_keys)), room
 
 
 def fill(eng, streams, ctx, rank):
@@ -209,6 +211,8 @@ def main():
     ap.add_argument("--cpu-streams", type=int, default=2)
     ap.add_argument("--cpu-steps", type=int, default=2)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
+    ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -217,6 +221,8 @@ def main():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
     hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
     workload = f"1B llama-style target, {'bf16' if args.bf16 else 'int8 per-row'} weights, {args.streams} streams/GPU, ctx {args.ctx}, k=4 (5 rows), T={args.temperature} top-p 0.95"
+    if args.layers:
+        workload += f" -- CUT TO {args.layers} LAYERS (profiler-size case)"
 
     if args.impl == "reference":
         if rank != 0:
@@ -245,8 +251,8 @@ def main():
 
     _package()
     from silicon_violetto_b200 import engine as E
-    path = model_file("1b", not args.bf16, rank)
-    eng, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local)
+    path = model_file("1b", not args.bf16, rank, args.layers)
+    eng, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
     r = run_replica(args, rank, world, barrier, local, eng, args.mistakes)
     extra = run_replica(args, rank, world, barrier, local, eng, args.replay_mistakes) if args.replay_mistakes < 1.0 else None
     vals = torch.tensor([r["dev_ms"], r["wall"]], dtype=torch.float64, device=f"cuda:{local}")
@@ -268,7 +274,7 @@ def main():
     att_ms = att["ms"] / max(att["launches"], 1)
     att_bytes = args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER
     achieved = att_bytes / (att_ms * 1e-3) / 1e9 if att_ms > 0 else 0.0
-    step_bytes = WEIGHT_PARAMS * (2 if args.bf16 else 1) + args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER * 16
+    step_bytes = WEIGHT_PARAMS * (2 if args.bf16 else 1) + args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER * (args.layers or 16)
     out = {
         "metric": "decode tokens/s at 8k context", "value": emitted / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
         "ms_per_step": dev_s * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

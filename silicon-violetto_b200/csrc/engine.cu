@@ -130,6 +130,7 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
         const size_t n16 = (n + 15) / 16 * 16, hr16 = (hr + 15) / 16 * 16;
         s.h_b.alloc(n16 * md.d * 2, false);
         s.attn_b.alloc(n16 * md.n_heads * md.hd * 2, false);
+        s.q_b.alloc(n16 * md.n_heads * md.hd * 2, false);
         s.act_b.alloc(n16 * md.ffn * 2, false);
         s.hfin_b.alloc(hr16 * md.d * 2, false);
         f(s.inv_head, hr);
@@ -236,8 +237,9 @@ KvArgs Engine::kv_args() const {
 }
 
 // How the cached keys are split across attention blocks (the reference's decode_splits,
-// engine/src/engine/plan.rs:153-163, re-derived for this GPU): blocks of 4 warps, three per SM;
-// among the split counts that leave a block at least 8 pages, the one that fills whole waves best.
+// engine/src/engine/plan.rs:153-163, re-derived for this GPU): blocks of 4 warps, three per SM.
+// A block costs its warps' pages plus a fixed part (loading q, merging and writing the partial)
+// worth about six pages; the split count with the lowest waves x block cost wins.
 void Engine::attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const {
     const uint32_t page = model.md.page, unit = 4 * page;  // a block's four warps take a page each
     const uint32_t cap = std::min<uint32_t>(std::max<uint32_t>(cfg.max_step_tokens * 16 / std::max(p.n, 1u), 1u), 64u);  // plan.rs:127
@@ -246,12 +248,13 @@ void Engine::attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const
     if (tuning.attn_keys_per_cta) {
         best = std::max(1u, (max_keys + tuning.attn_keys_per_cta - 1) / tuning.attn_keys_per_cta);
     } else {
-        double best_eff = -1.0;
+        const double fixed = 6.0, pages = double(max_keys + page - 1) / page;
+        double best_cost = 1e30;
         for (uint32_t sp = 1; sp <= cap; sp++) {
             if (sp > 1 && max_keys / sp < 8 * page) break;
-            const double waves = double(base) * sp / slots;
-            const double eff = waves / std::ceil(waves) - 0.002 * sp;  // ties go to fewer splits
-            if (eff > best_eff) { best_eff = eff; best = sp; }
+            const double waves = std::ceil(double(base) * sp / slots);
+            const double cost = waves * (std::ceil(pages / (4.0 * sp)) + fixed);
+            if (cost < best_cost) { best_cost = cost; best = sp; }
         }
     }
     best = std::min(best, cap);
@@ -409,12 +412,12 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     }
     span_end(sp);
     const KvArgs kva = kv_args();
+    const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
     sp = span_begin(G_SMALL);
     if (!(skip & 2))
         launch_qkv_post(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tin), rope_tab.as<float>(), kv.k.as<uint16_t>(), kv.v.as<uint16_t>(),
-                        kv.page_table.as<uint32_t>(), kva, li, n, md.n_heads, stream);
+                        kv.page_table.as<uint32_t>(), kva, li, n, md.n_heads, scale_log2, tuning.plain_attention ? nullptr : s.q_b.as<uint16_t>(), stream);
     span_end(sp);
-    const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
     if (tuning.plain_attention) {
         if (!(skip & 4))
             launch_attn_plain(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tiles), st.in<uint32_t>(st.o_vis), rope_tab.as<float>(),
@@ -425,11 +428,10 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
         AttnArgs a{};
         a.maps = &attn_maps;
         a.err_flag = s.err_flag.as<uint32_t>();
-        a.qkv = s.qkv.as<float>();
+        a.q_b = s.q_b.as<uint16_t>();
         a.meta = s.meta.as<uint32_t>();
         a.tiles = st.in<uint32_t>(st.o_tiles);
         a.vis = st.in<uint32_t>(st.o_vis);
-        a.rope = rope_tab.as<float>();
         a.k_cache = kv.k.as<uint16_t>();
         a.v_cache = kv.v.as<uint16_t>();
         a.page_table = kv.page_table.as<uint32_t>();

@@ -162,7 +162,7 @@ class Engine {
     // Activations (engine/src/engine/buffers.rs:14-118) and per-slot state on the GPU.
     struct Scratch {
         Buffer h, qkv, attn, act, part, hfin_head, hfin_all, logits, taps, inv, meta;
-        Buffer h_b, attn_b, act_b, hfin_b, inv_head;  // bf16 copies that feed the tensor-core GEMM, rows padded to 16
+        Buffer h_b, attn_b, act_b, hfin_b, inv_head, q_b;  // bf16 copies that feed the tensor-core GEMM, rows padded to 16
         Buffer lens, feed, tree, gen, path, path_len, on_path, trace, trace_len, err_flag;
     } s;
     Buffer rope_tab;

@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
     // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4..9.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t bars[ATTN_WARPS][ATTN_STAGES];
+    __shared__ uint4 qs[MT * 16 * 8];
 
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, tile = blockIdx.z;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
@@ -93,14 +94,6 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
         return;
     }
 
-    if (threadIdx.x == 0) {
-        for (int w = 0; w < ATTN_WARPS; w++)
-            for (int s = 0; s < ATTN_STAGES; s++) mbar_init(smem_u32(&bars[w][s]), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
-
     // This warp's pages: page_begin + warp, + ATTN_WARPS, ...
     const uint32_t page_begin = k_begin / PAGE, page_end = (k_end + PAGE - 1) / PAGE;
     const uint32_t my_pages = page_begin + warp < page_end ? (page_end - page_begin - warp + ATTN_WARPS - 1) / ATTN_WARPS : 0;
@@ -115,6 +108,26 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
         return i < my_pages ? ptab[page_begin + warp + i * ATTN_WARPS] : 0u;
     };
     uint32_t ids0 = load_ids(0), ids1 = load_ids(1), cur_batch = 0;
+
+    // Q (bf16, RoPE and the softmax scale already applied) into shared memory as [row p][64 dims],
+    // 16-byte chunks XOR-swizzled by the row; row p = G i + h is token i, head h of this kv head.
+    {
+        const uint4* qg = reinterpret_cast<const uint4*>(a.q_b);
+        for (uint32_t c = threadIdx.x; c < MT * 16 * 8; c += ATTN_WARPS * 32) {
+            const uint32_t p = c / 8, chunk = c % 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (p < n_cols) v = qg[(size_t(t0 + p / G) * a.n_heads + kvh * G + p % G) * 8 + chunk];
+            qs[p * 8 + (chunk ^ (p & 7))] = v;
+        }
+    }
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < ATTN_WARPS; w++)
+            for (int s = 0; s < ATTN_STAGES; s++) mbar_init(smem_u32(&bars[w][s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
     auto issue = [&](uint32_t i) {  // all lanes: page i of this warp into stage i % STAGES
         if (i / 32 > cur_batch) {
             ids0 = ids1;
@@ -132,37 +145,22 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
     };
     for (uint32_t i = 0; i < min(my_pages, uint32_t(ATTN_STAGES)); i++) issue(i);
 
-    // Q as A operands: row p = G i + h is token i, head h of this kv head; RoPE at the token's
-    // position, scale * log2(e) folded in, rounded to bf16. A lane owns whole RoPE pairs.
+    // Q as A operands (a0: rows g, dims lo; a1: rows g + 8, lo; a2: g, hi; a3: g + 8, hi), and
+    // the visibility masks of this lane's rows g and g + 8.
+    const uint32_t lm = lane >> 3, lr = lane & 7;  // ldmatrix: lane -> (matrix, row)
     uint32_t qf[MT][4][4];
-    uint32_t vmask[MT][2];  // the visibility masks of this lane's rows g and g + 8
+    uint32_t vmask[MT][2];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            const uint32_t p = mt * 16 + 8 * (lm & 1) + lr, chunk = 2 * ks + (lm >> 1);
+            ldmatrix_x4(qf[mt][ks], smem_u32(&qs[p * 8 + (chunk ^ (p & 7))]));
+        }
+#pragma unroll
         for (int half = 0; half < 2; half++) {
             const uint32_t p = mt * 16 + g + 8 * half;
-            const bool ok = p < n_cols;
-            const uint32_t tok = t0 + (ok ? p / G : 0), hq = kvh * G + p % G;
-            vmask[mt][half] = ok ? a.vis[tok] : 0xffffffffu;
-            const uint32_t pos = a.meta[2 * tok + 1];
-            const float* qp = a.qkv + size_t(tok) * ((a.n_heads + 2 * a.kv.n_kv) * HD) + hq * HD;
-            const float2* cs = reinterpret_cast<const float2*>(a.rope) + size_t(pos) * (HD / 2);
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-#pragma unroll
-                for (int hi = 0; hi < 2; hi++) {
-                    const uint32_t d = 16 * ks + 8 * hi + 2 * t;
-                    uint32_t packed = 0;
-                    if (ok) {
-                        const float2 v = *reinterpret_cast<const float2*>(qp + d);
-                        const float2 c = cs[d / 2];
-                        const float r0 = __fadd_rn(__fmul_rn(c.x, v.x), __fmul_rn(c.y, v.y));
-                        const float r1 = __fsub_rn(__fmul_rn(c.x, v.y), __fmul_rn(c.y, v.x));
-                        packed = pack_bf16(__fmul_rn(r0, a.scale_log2), __fmul_rn(r1, a.scale_log2));
-                    }
-                    qf[mt][ks][half + 2 * hi] = packed;  // a0: (g, lo), a1: (g+8, lo), a2: (g, hi), a3: (g+8, hi)
-                }
-            }
+            vmask[mt][half] = p < n_cols ? a.vis[t0 + p / G] : 0xffffffffu;
         }
     }
 
@@ -178,8 +176,6 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
         l_run[mt][0] = l_run[mt][1] = 0.0f;
     }
 
-    // ldmatrix row addresses within a page: lane -> (matrix lane / 8, row lane % 8).
-    const uint32_t lm = lane >> 3, lr = lane & 7;
     bool failed = false;
     for (uint32_t i = 0; i < my_pages; i++) {
         const uint32_t st = i % ATTN_STAGES, parity = (i / ATTN_STAGES) & 1;
@@ -272,48 +268,54 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
         return;
     }
 
-    // Merge the four warps through shared memory (the stage ring is free now), then write the partial.
+    // Merge the four warps through shared memory (the stage ring is free now): every warp scales
+    // its rows to the block's maximum, the block adds them up and writes the partial.
     __syncthreads();
+    constexpr int ROWS = MT * 16, OS = HD + 8;        // the row stride keeps the float2 stores off each other's banks
     float* ms = reinterpret_cast<float*>(smem);      // [warp][row]
-    float* ls = ms + ATTN_WARPS * MT * 16;           // [warp][row]
-    float* os = ls + ATTN_WARPS * MT * 16;           // [warp][row][HD + 1]
+    float* ls = ms + ATTN_WARPS * ROWS;              // [warp][row], scaled
+    float* os = ls + ATTN_WARPS * ROWS;              // [warp][row][OS], scaled
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int half = 0; half < 2; half++)
+            if (t == 0) ms[warp * ROWS + mt * 16 + g + 8 * half] = m_run[mt][half];
+    __syncthreads();
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
+            const uint32_t row = mt * 16 + g + 8 * half;
+            float mm = ms[row];
+#pragma unroll
+            for (int w = 1; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * ROWS + row]);
+            const float wgt = m_run[mt][half] == -INFINITY ? 0.0f : fast_exp2(m_run[mt][half] - mm);
             float l = l_run[mt][half];
             l += __shfl_xor_sync(0xffffffffu, l, 1);
             l += __shfl_xor_sync(0xffffffffu, l, 2);
-            const uint32_t row = mt * 16 + g + 8 * half;
-            if (t == 0) {
-                ms[warp * MT * 16 + row] = m_run[mt][half];
-                ls[warp * MT * 16 + row] = l;
-            }
+            if (t == 0) ls[warp * ROWS + row] = l * wgt;
 #pragma unroll
-            for (int dn = 0; dn < 8; dn++) {
-                float* o = os + (size_t(warp) * MT * 16 + row) * (HD + 1) + 8 * dn + 2 * t;
-                o[0] = oacc[mt][dn][2 * half];
-                o[1] = oacc[mt][dn][2 * half + 1];
-            }
+            for (int dn = 0; dn < 8; dn++)
+                *reinterpret_cast<float2*>(os + (size_t(warp) * ROWS + row) * OS + 8 * dn + 2 * t) =
+                    make_float2(oacc[mt][dn][2 * half] * wgt, oacc[mt][dn][2 * half + 1] * wgt);
         }
     }
     __syncthreads();
     for (uint32_t idx = threadIdx.x; idx < n_cols * HD; idx += blockDim.x) {
         const uint32_t p = idx / HD, d = idx % HD;
-        float mm = -INFINITY;
+        float oo = 0.0f;
 #pragma unroll
-        for (int w = 0; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * MT * 16 + p]);
-        float ll = 0.0f, oo = 0.0f;
-#pragma unroll
-        for (int w = 0; w < ATTN_WARPS; w++) {
-            const float mw = ms[w * MT * 16 + p];
-            if (mw == -INFINITY) continue;
-            const float wgt = exp2f(mw - mm);
-            ll += ls[w * MT * 16 + p] * wgt;
-            oo += os[(size_t(w) * MT * 16 + p) * (HD + 1) + d] * wgt;
-        }
+        for (int w = 0; w < ATTN_WARPS; w++) oo += os[(size_t(w) * ROWS + p) * OS + d];
         float* pp = part_of(p);
-        if (d == 0) { pp[0] = mm; pp[1] = ll; }
+        if (d == 0) {
+            float mm = ms[p], ll = 0.0f;
+#pragma unroll
+            for (int w = 1; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * ROWS + p]);
+#pragma unroll
+            for (int w = 0; w < ATTN_WARPS; w++) ll += ls[w * ROWS + p];
+            pp[0] = mm;
+            pp[1] = ll;
+        }
         pp[4 + d] = oo;
     }
 }

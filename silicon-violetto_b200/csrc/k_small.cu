@@ -49,10 +49,12 @@ void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uin
 // kernels.metal:749-801 `qkv_post`, a plain decoder's part of it: RoPE on k (interleaved
 // pairs, kernels.metal:727-736, angle of the token's position), k and v rounded to bf16 and
 // written at the token's cache row (its run's first position + its row, kernels.metal:74-77).
-// One block per token, one warp per kv head, a lane per pair of dims (head_dim 64).
+// One block per token, one warp per kv head, a lane per pair of dims (head_dim 64). The same
+// warps then leave q as the tensor-core attention wants it: RoPE, the softmax scale * log2(e)
+// folded in, rounded to bf16 (kernels.metal:776-789 does this for q in the same kernel).
 __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin,
                                 const float* __restrict__ rope, uint16_t* k_cache, uint16_t* v_cache, const uint32_t* __restrict__ page_table,
-                                KvArgs kv, uint32_t layer, uint32_t n_heads) {
+                                KvArgs kv, uint32_t layer, uint32_t n_heads, float scale_log2, uint32_t* __restrict__ q_b) {
     const uint32_t t = blockIdx.x, g = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1];
     const uint32_t cpos = meta[2 * (t - row) + 1] + row;
@@ -67,11 +69,19 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* _
     const size_t at = kv_row(kv, layer, page_table, slot, g, cpos);
     reinterpret_cast<uint32_t*>(k_cache + at)[lane] = pack_bf16(r0, r1);
     reinterpret_cast<uint32_t*>(v_cache + at)[lane] = pack_bf16(v.x, v.y);
+    if (q_b) {
+        for (uint32_t h = g; h < n_heads; h += kv.n_kv) {
+            const float2 q = reinterpret_cast<const float2*>(qkv + size_t(t) * qw + h * kv.hd)[lane];
+            const float q0 = __fadd_rn(__fmul_rn(cs.x, q.x), __fmul_rn(cs.y, q.y));
+            const float q1 = __fsub_rn(__fmul_rn(cs.x, q.y), __fmul_rn(cs.y, q.x));
+            q_b[(size_t(t) * n_heads + h) * (kv.hd / 2) + lane] = pack_bf16(__fmul_rn(q0, scale_log2), __fmul_rn(q1, scale_log2));
+        }
+    }
 }
 
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
-                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, cudaStream_t s) {
-    { qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads); launch_counter()++; }
+                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, cudaStream_t s) {
+    { qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads, scale_log2, reinterpret_cast<uint32_t*>(q_b)); launch_counter()++; }
 }
 
 // ----------------------------------------------- scalar attention (cross-check)

@@ -31,7 +31,7 @@ struct MatArgs {
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
                   const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, cudaStream_t s);
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
-                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, cudaStream_t s);
+                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, cudaStream_t s);
 void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* tiles, const uint32_t* vis, const float* rope, const uint16_t* k_cache,
                        const uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n_tiles, uint32_t n_heads,
                        float scale_log2, float* out, cudaStream_t s);
@@ -47,11 +47,10 @@ void make_tensor_map_2d(void* out_map, const void* base, uint64_t inner, uint64_
 struct AttnArgs {
     const AttnMaps* maps;  // host pointer
     uint32_t* err_flag;    // device word set if a bounded wait ran out
-    const float* qkv;
+    const uint16_t* q_b;  // [token][head][64] bf16: q after RoPE, scale * log2(e) folded in (qkv_post writes it)
     const uint32_t* meta;
     const uint32_t* tiles;
     const uint32_t* vis;
-    const float* rope;
     const uint16_t* k_cache;
     const uint16_t* v_cache;
     const uint32_t* page_table;
