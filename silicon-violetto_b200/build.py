@@ -33,7 +33,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(job):
         src, obj = job
-        r = subprocess.run([NVCC, *FLAGS, "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+        r = subprocess.run([NVCC, *FLAGS, *os.environ.get("VLT_NVCC_FLAGS", "").split(), "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
         (objdir / (src.name + ".log")).write_text(r.stdout + r.stderr)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")

@@ -6,8 +6,9 @@
 //     weight is read from HBM once whatever the number of streams;
 //   - operands come in by TMA (no multicast) into 128-byte-swizzled shared memory, a ring of
 //     stages guarded by mbarriers; tcgen05.mma, issued by one thread, accumulates fp32 in TMEM;
-//   - int8 weights arrive as raw bytes and four warps turn each stage into bf16 (exactly) in the
-//     swizzled layout the MMA reads; their scale per output row is applied in the epilogue;
+//   - int8 weights arrive as raw bytes in a ring of their own; eight warps, in four groups that
+//     take k blocks in turn, turn each into bf16 (exactly) in the swizzled layout the MMA reads;
+//     the scale per output row is applied in the epilogue;
 //   - the epilogue warps read TMEM with tcgen05.ld and apply the fused epilogues (RMSNorm scale,
 //     residual add, SwiGLU on interleaved gate/up rows, head) before the coalesced store.
 // Every wait is bounded: on a time-out the kernel sets the error flag, frees its TMEM and returns.
@@ -24,8 +25,9 @@ namespace vlt {
 namespace gemm {
 
 constexpr uint32_t BM = 128, BK = 64;
-constexpr uint32_t RAW_KB = 1;  // k blocks per raw int8 stage (wider boxes measured no faster)
 constexpr uint32_t CONV_WARPS = 8;
+constexpr uint32_t CONV_GROUPS = 4;                      // converter groups, each on its own k block
+constexpr uint32_t CONV_WPG = CONV_WARPS / CONV_GROUPS;  // warps per group
 constexpr uint32_t FIRST_CONV = 3;
 constexpr uint32_t THREADS = 32 * (FIRST_CONV + CONV_WARPS);  // warp 0: weight TMA, warp 1: MMA, warp 2: activation TMA, the rest: conversion and epilogue
 constexpr uint32_t SPIN = 1u << 26;
@@ -119,8 +121,6 @@ struct Args {
     uint32_t tmem_cols; // power of two >= max(32, n_pad)
     uint32_t splits;    // blocks of a cluster that share a weight tile, each over a slice of k
     uint32_t* err_flag;
-    unsigned long long* dbg;  // TEMP timing probe
-    uint32_t abl;             // TEMP ablation bits
 };
 
 }  // namespace gemm
@@ -135,8 +135,13 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     return false;
 }
+#ifdef VLT_GEMM_PROBE
+__device__ unsigned long long g_probe[8][64];
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define PROBE(i) do { if (a.dbg && blockIdx.x == 0 && (tid == 96 || ((i) == 1 && tid == 0) || ((i) == 2 && tid == 32))) a.dbg[i] = gtime(); } while (0)
+#define PROBE(e, i) do { if (blockIdx.x == 0 && (i) < 64) g_probe[e][i] = gtime(); } while (0)
+#else
+#define PROBE(e, i) do { } while (0)
+#endif
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -168,14 +173,14 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     // raw stages of 8 KiB sit in front of them, deep enough to keep this SM's share of HBM bandwidth in
     // flight (a converted stage carries 36 KiB of shared memory for 8 KiB of HBM traffic; a raw one 8 for 8).
     const uint32_t n_pad = a.n_pad, C = a.stages, R = INT8 ? a.raw_stages : 0, splits = a.splits;
-    const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = BM * BK * RAW_KB;
+    const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = BM * BK;
     const uint32_t ab_bytes = a_bytes + b_bytes;
     const uint32_t ring_bytes = max(C * ab_bytes + R * raw_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the rings
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes);
-    // a_full[C], b_full[C], ab_empty[C], raw_full[R], raw_empty[R], then the accumulator's barrier
-    const uint32_t bar_afull = smem_u32(bars), bar_bfull = bar_afull + 8 * C, bar_empty = bar_bfull + 8 * C, bar_rfull = bar_empty + 8 * C,
-                   bar_rempty = bar_rfull + 8 * R, bar_accum = bar_rempty + 8 * R;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * C + 2 * R + 1);
+    // full[C] (both operands of a stage), empty[C], raw_full[R], raw_empty[R], then the accumulator's barrier
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * C, bar_rfull = bar_empty + 8 * C, bar_rempty = bar_rfull + 8 * R,
+                   bar_accum = bar_rempty + 8 * R;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * C + 2 * R + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* inv_s = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);  // 1/rms per token
     const uint32_t smem_base = smem_u32(smem);
@@ -184,7 +189,6 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     auto stage_raw = [&](uint32_t r) { return smem_base + C * ab_bytes + r * raw_bytes; };
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    PROBE(10);
     const uint32_t rank = splits > 1 ? cluster_rank() : 0, tile = blockIdx.x / splits;
     const uint32_t row0 = tile * BM, nkb_all = a.m.k / BK;
     // This block's k blocks: an even share, the first ranks one more.
@@ -193,13 +197,12 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
 
     if (tid == 0) {
         for (uint32_t c = 0; c < C; c++) {
-            mbar_init(bar_afull + 8 * c, INT8 ? CONV_WARPS : 1);
-            mbar_init(bar_bfull + 8 * c, 1);
+            mbar_init(bar_full + 8 * c, (INT8 ? CONV_WPG : 1) + 1);  // the weights' side (converter warps, or the loader's expect_tx) + the activations' loader
             mbar_init(bar_empty + 8 * c, 1);
         }
         for (uint32_t r = 0; r < R; r++) {
             mbar_init(bar_rfull + 8 * r, 1);
-            mbar_init(bar_rempty + 8 * r, CONV_WARPS);
+            mbar_init(bar_rempty + 8 * r, CONV_WPG);
         }
         mbar_init(bar_accum, 1);
         *abort_flag = 0;
@@ -217,89 +220,98 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
-    PROBE(0);
 
+    // The loops below keep their stage index and phase bit by increment: a thread that feeds the tensor
+    // core runs alone in its warp, and every division or descriptor rebuilt per k block is on the critical path.
     if (warp == 0) {
         // The weights' loader: raw int8 tiles into the deep ring, or bf16 tiles straight into the operand ring.
         if (lane == 0) {
-            for (uint32_t i = 0; i < nkb && ok; i++) {
-                const uint32_t kb = kb_begin + i;
-                if (INT8) {
-                    if (i % RAW_KB) continue;  // one request brings RAW_KB k blocks
-                    const uint32_t j = i / RAW_KB, r = j % R, ph = (j / R) & 1;
-                    ok = wait_or_abort(bar_rempty + 8 * r, ph ^ 1, abort_flag);
-                    if (!ok) break;
-                    mbar_expect_tx(bar_rfull + 8 * r, raw_bytes);
-                    tma_load_2d(stage_raw(r), &maps.a, int(kb * BK), int(row0), bar_rfull + 8 * r);
-                } else {
-                    const uint32_t c = i % C, ph = (i / C) & 1;
-                    ok = wait_or_abort(bar_empty + 8 * c, ph ^ 1, abort_flag);
-                    if (!ok) break;
-                    mbar_expect_tx(bar_afull + 8 * c, a_bytes);
-                    tma_load_2d(stage_a(c), &maps.a, int(kb * BK), int(row0), bar_afull + 8 * c);
-                }
+            const uint32_t n_st = INT8 ? R : C, bar_e = INT8 ? bar_rempty : bar_empty, bar_f = INT8 ? bar_rfull : bar_full;
+            const uint32_t dst0 = INT8 ? stage_raw(0) : stage_a(0), step = INT8 ? raw_bytes : ab_bytes, bytes = INT8 ? raw_bytes : a_bytes;
+            uint32_t st = 0, ph = 1;
+            for (uint32_t i = 0; i < nkb; i++) {
+                ok = wait_or_abort(bar_e + 8 * st, ph, abort_flag);
+                if (!ok) break;
+                PROBE(0, i);
+                mbar_expect_tx(bar_f + 8 * st, bytes);
+                tma_load_2d(dst0 + st * step, &maps.a, int((kb_begin + i) * BK), int(row0), bar_f + 8 * st);
+                if (++st == n_st) { st = 0; ph ^= 1; }
             }
-            PROBE(1);
         }
         __syncwarp();  // the idle lanes wait here, so that the warp reaches the block barriers converged
     } else if (warp == 2) {
         // The activations' loader (they come from L2: every block reads the same rows).
         if (lane == 0) {
-            for (uint32_t i = 0; i < nkb && ok; i++) {
-                const uint32_t c = i % C, ph = (i / C) & 1;
-                ok = wait_or_abort(bar_empty + 8 * c, ph ^ 1, abort_flag);
+            uint32_t c = 0, ph = 1;
+            for (uint32_t i = 0; i < nkb; i++) {
+                ok = wait_or_abort(bar_empty + 8 * c, ph, abort_flag);
                 if (!ok) break;
-                mbar_expect_tx(bar_bfull + 8 * c, b_bytes);
-                tma_load_2d(stage_b(c), &maps.b, int((kb_begin + i) * BK), 0, bar_bfull + 8 * c);
+                PROBE(3, i);
+                mbar_expect_tx(bar_full + 8 * c, b_bytes);
+                tma_load_2d(stage_b(c), &maps.b, int((kb_begin + i) * BK), 0, bar_full + 8 * c);
+                if (++c == C) { c = 0; ph ^= 1; }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, n_pad);
-            for (uint32_t i = 0; i < nkb && ok; i++) {
-                const uint32_t c = i % C, ph = (i / C) & 1;
-                ok = wait_or_abort(bar_afull + 8 * c, ph, abort_flag) && wait_or_abort(bar_bfull + 8 * c, ph, abort_flag);
+            // A descriptor's low word holds (address >> 4); the stages and the four 32-byte k steps of a
+            // stage differ only there.
+            const uint64_t da0 = smem_desc(stage_a(0)), db0 = smem_desc(stage_b(0));
+            const uint32_t hi_a = uint32_t(da0 >> 32), hi_b = uint32_t(db0 >> 32), lo_a0 = uint32_t(da0), lo_b0 = uint32_t(db0), lo_step = ab_bytes >> 4;
+            uint32_t c = 0, ph = 0;
+            for (uint32_t i = 0; i < nkb; i++) {
+                ok = wait_or_abort(bar_full + 8 * c, ph, abort_flag);
                 if (!ok) break;
+                PROBE(5, i);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t lo_a = lo_a0 + c * lo_step, lo_b = lo_b0 + c * lo_step;
 #pragma unroll
                 for (uint32_t k4 = 0; k4 < BK / 16; k4++)
-                    mma_f16(tmem_base, smem_desc(stage_a(c) + k4 * 32), smem_desc(stage_b(c) + k4 * 32), idesc, (i | k4) != 0 ? 1u : 0u);
+                    mma_f16(tmem_base, (uint64_t(hi_a) << 32) | (lo_a + 2 * k4), (uint64_t(hi_b) << 32) | (lo_b + 2 * k4), idesc, (i | k4) != 0 ? 1u : 0u);
                 mma_commit(bar_empty + 8 * c);  // arrives once these MMAs have read the stage
+                PROBE(6, i);
+                if (++c == C) { c = 0; ph ^= 1; }
             }
             if (ok) mma_commit(bar_accum);
-            PROBE(2);
         }
         __syncwarp();
     } else if (INT8) {
-        // Raw int8 [128][64] to bf16 in the swizzled layout: a thread takes 16 bytes of a row at a time.
-        const uint32_t cid = tid - FIRST_CONV * 32;
-        for (uint32_t i = 0; i < nkb && ok; i++) {
-            const uint32_t jr = i / RAW_KB, r = jr % R, rph = (jr / R) & 1, sub = i % RAW_KB, c = i % C, cph = (i / C) & 1;
-            ok = wait_or_abort(bar_rfull + 8 * r, rph, abort_flag) && wait_or_abort(bar_empty + 8 * c, cph ^ 1, abort_flag);
+        // Raw int8 [128][64] to bf16 in the swizzled layout, 16 bytes of a row at a time. The warps work
+        // in CONV_GROUPS groups that take k blocks in turn: a k block's wait -> load -> convert -> store ->
+        // fence -> arrive chain is long, and with every warp on the same k block nothing would overlap it.
+        const uint32_t grp = (warp - FIRST_CONV) / CONV_WPG, gtid = tid - (FIRST_CONV + grp * CONV_WPG) * 32;
+        uint32_t r = grp % R, rph = (grp / R) & 1, c = grp % C, cph = ((grp / C) & 1) ^ 1;
+        const uint32_t row_q = (gtid >> 2) * 128, q = gtid & 3, sw = (gtid >> 2) & 7;  // a thread's rows are 16 apart: the same swizzle phase
+        const uint32_t off_lo = row_q + (((2 * q) ^ sw) << 4), off_hi = row_q + (((2 * q + 1) ^ sw) << 4);
+        for (uint32_t i = grp; i < nkb; i += CONV_GROUPS) {
+            ok = wait_or_abort(bar_rfull + 8 * r, rph, abort_flag) && wait_or_abort(bar_empty + 8 * c, cph, abort_flag);
             if (!ok) break;
-            const uint32_t q = cid & 3;
+            if (gtid == 0) PROBE(1, i);
+            const uint32_t src = stage_raw(r), dst = stage_a(c);
 #pragma unroll
-            for (uint32_t p = 0; p < 512 / (32 * CONV_WARPS); p++) {
-                const uint32_t row = (cid >> 2) + (8 * CONV_WARPS) * p;
+            for (uint32_t p = 0; p < 512 / (32 * CONV_WPG); p++) {
                 uint4 raw;
-                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(stage_raw(r) + row * (64 * RAW_KB) + sub * 64 + q * 16));
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(src + (gtid + 32 * CONV_WPG * p) * 16));
                 uint4 lo, hi;
-                if (a.abl & 64) { lo = raw; hi = raw; } else {
                 cvt_i8x4(raw.x, lo.x, lo.y);
                 cvt_i8x4(raw.y, lo.z, lo.w);
                 cvt_i8x4(raw.z, hi.x, hi.y);
-                cvt_i8x4(raw.w, hi.z, hi.w); }
-                const uint32_t base = stage_a(c) + row * 128, sw = row & 7;
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q) ^ sw) << 4)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((2 * q + 1) ^ sw) << 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                cvt_i8x4(raw.w, hi.z, hi.w);
+                const uint32_t base = dst + p * (8 * CONV_WPG * 128);  // 32 CONV_WPG threads cover 8 CONV_WPG rows
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + off_lo), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + off_hi), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
             }
-            if (!(a.abl & 32)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
             __syncwarp();
-            if (lane == 0) {  // one arrival per warp: 256 arrivals per stage would serialise on the barrier
-                mbar_arrive(bar_afull + 8 * c);
-                if (sub == RAW_KB - 1 || i == nkb - 1) mbar_arrive(bar_rempty + 8 * r);  // the raw stage's last k block
+            if (gtid == 0) PROBE(2, i);
+            if (lane == 0) {  // one arrival per warp: an arrival per thread would serialise on the barrier
+                mbar_arrive(bar_full + 8 * c);
+                mbar_arrive(bar_rempty + 8 * r);
             }
+            for (r += CONV_GROUPS; r >= R; r -= R) rph ^= 1;
+            for (c += CONV_GROUPS; c >= C; c -= C) cph ^= 1;
         }
     }
 
@@ -349,9 +361,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     };
 
     if (warp >= FIRST_CONV) {
-        PROBE(3);
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
-        PROBE(4);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // Two warps share a quarter of the TMEM lanes (rows) and take alternate groups of 16 tokens.
@@ -376,10 +386,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    PROBE(5);
     if (splits > 1) {
         cluster_sync();  // every block's partial is in place
-        PROBE(6);
         // Each block finishes its share of the rows. First their sums over the cluster's partials, into a
         // second buffer: a warp reads a row's tokens, contiguous in the other block's shared memory, and
         // adds the ranks up in order (deterministic). Then a lane takes a row and emits 32 tokens at a time.
@@ -405,7 +413,6 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
                     if (32 * c + lane < n_pad) sums[(r - r_begin) * pitch + 32 * c + lane] = v[c];
             }
         }
-        PROBE(7);
         __syncthreads();
         if (warp >= FIRST_CONV && !*abort_flag) {
             const uint32_t chunks = n_pad / 16, n_rg = (r_end - r_begin + 31) / 32;
@@ -420,10 +427,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             }
         }
     }
-    PROBE(8);
     if (splits > 1) cluster_sync();  // nobody leaves while its shared memory may still be read
     __syncthreads();
-    PROBE(9);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
@@ -462,13 +467,13 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     auto it = cache.maps.find(key);
     if (it == cache.maps.end()) {
         gemm::Maps m;
-        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK * gemm::RAW_KB, gemm::BM, 1, false);
+        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 1, false);
         else make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 2, true);
         make_tensor_map_2d(m.b, a.Xb, a.k, n_pad, gemm::BK, n_pad, 2, true);
         it = cache.maps.emplace(key, m).first;
     }
     // Shared memory: operand stages of (16 KiB + n_pad x 128 B); for int8, raw stages of 8 KiB in front.
-    const uint32_t ab_bytes = gemm::BM * gemm::BK * 2 + n_pad * gemm::BK * 2, raw_bytes = gemm::BM * gemm::BK * gemm::RAW_KB;
+    const uint32_t ab_bytes = gemm::BM * gemm::BK * 2 + n_pad * gemm::BK * 2, raw_bytes = gemm::BM * gemm::BK;
     const uint32_t budget = 208 * 1024;
     uint32_t stages, raw_stages = 0;
     if (a.int8) {
@@ -478,7 +483,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
         stages = std::max(2u, std::min(8u, budget / ab_bytes));
     }
     const uint32_t ring = std::max(stages * ab_bytes + raw_stages * raw_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
-    const size_t smem = size_t(ring) + 1024 + (3 * stages + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4;
+    const size_t smem = size_t(ring) + 1024 + (2 * stages + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4;
     if (!configured) {
         for (int i8 = 0; i8 < 2; i8++)
             for (uint32_t epi = EPI_NORM; epi <= EPI_RAW; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -519,10 +524,6 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     g.tmem_cols = cols;
     g.splits = splits;
     g.err_flag = err_flag;
-    static unsigned long long* dbg = nullptr;
-    if (getenv("VLT_GEMM_DEBUG") && !dbg) { cudaMalloc(&dbg, 128); }
-    g.dbg = dbg;
-    g.abl = getenv("VLT_GEMM_ABL") ? atoi(getenv("VLT_GEMM_ABL")) : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * splits);
     cfg.blockDim = dim3(gemm::THREADS);
@@ -537,14 +538,18 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     cfg.numAttrs = splits > 1 ? 1 : 0;
     VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm_entry(a.int8, a.epi), it->second, g));
     launch_counter()++;
-    if (dbg) {
+#ifdef VLT_GEMM_PROBE
+    if (getenv("VLT_GEMM_PROBE")) {
         cudaStreamSynchronize(s);
-        unsigned long long h[16];
-        cudaMemcpy(h, dbg, 128, cudaMemcpyDeviceToHost);
-        fprintf(stderr, "  loop: before_ld %lld after_ld %lld after_emit0 %lld after_emit1 %lld\n", (long long)(h[11]-h[0]), (long long)(h[12]-h[0]), (long long)(h[13]-h[0]), (long long)(h[14]-h[0]));
-        fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u: tma_done %lld mma_done %lld conv_done %lld accum %lld dumped %lld csync %lld summed %lld stored %lld end %lld | setup took %lld (ns from setup)\n", a.m, a.k, a.n, splits,
-                (long long)(h[1]-h[0]), (long long)(h[2]-h[0]), (long long)(h[3]-h[0]), (long long)(h[4]-h[0]), (long long)(h[5]-h[0]), (long long)(h[6]-h[0]), (long long)(h[7]-h[0]), (long long)(h[8]-h[0]), (long long)(h[9]-h[0]), (long long)(h[0]-h[10]));
+        static unsigned long long h[8][64];
+        cudaMemcpyFromSymbol(h, gemm::g_probe, sizeof(h));
+        fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u stages=%u raw=%u\n", a.m, a.k, a.n, splits, stages, raw_stages);
+        const unsigned long long t0 = h[0][0];
+        for (uint32_t i = 0; i < std::min(64u, nkb / splits); i++)
+            fprintf(stderr, "kb %2u: tmaA %6lld convstart %6lld convdone %6lld tmaB %6lld afull %6lld bfull %6lld commit %6lld\n", i, (long long)(h[0][i] - t0),
+                    (long long)(h[1][i] - t0), (long long)(h[2][i] - t0), (long long)(h[3][i] - t0), (long long)(h[4][i] - t0), (long long)(h[5][i] - t0), (long long)(h[6][i] - t0));
     }
+#endif
 }
 
 }  // namespace vlt
