@@ -458,7 +458,7 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
         if (!(skip & 16)) matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), h, nullptr, EPI_RESID, h, nullptr);
         if (!(skip & 32)) {
             launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
-            matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), s.act.as<float>(), s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());
+            matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());  // the down GEMM reads the bf16 copy only
         }
         if (!(skip & 64)) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), h, nullptr, EPI_RESID, h, nullptr);
     } else {
@@ -679,7 +679,7 @@ void Engine::bench_matmul(const std::string& kind, uint32_t n, uint32_t variant,
                 if (gemm) {
                     if (kind == "qkv") matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>());
                     else if (kind == "o") matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), s.hfin_all.as<float>(), nullptr, EPI_RESID, s.h.as<float>(), nullptr);
-                    else if (kind == "gate_up") matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), s.act.as<float>(), s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());
+                    else if (kind == "gate_up") matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());  // the down GEMM reads the bf16 copy only
                     else matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), s.hfin_all.as<float>(), nullptr, EPI_RESID, s.h.as<float>(), nullptr);
                 } else {
                     if (kind == "qkv") matmul(l.qkv, n, s.h.as<float>(), s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());

@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
     }
 }
 
-// A 2-D tensor [rows][inner] with a box of [box_rows][box_inner], optionally 128-byte swizzled.
+// A 2-D tensor [rows][inner] with a box of [box_rows][box_inner], optionally 128- or 64-byte swizzled.
 struct TmaEncoder {
     typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                            CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -335,7 +335,7 @@ struct TmaEncoder {
 };
 
 void make_tensor_map_2d(void* out_map, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows, uint32_t elem_bytes,
-                        bool swizzle128) {
+                        bool swizzle128, bool swizzle64) {
     static TmaEncoder enc;
     const cuuint64_t dims[2] = {inner, rows};
     const cuuint64_t strides[1] = {inner * elem_bytes};
@@ -343,7 +343,7 @@ void make_tensor_map_2d(void* out_map, const void* base, uint64_t inner, uint64_
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const CUresult r = enc.fn(static_cast<CUtensorMap*>(out_map), dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw Error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
 }

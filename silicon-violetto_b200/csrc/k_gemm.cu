@@ -25,9 +25,9 @@ namespace vlt {
 namespace gemm {
 
 constexpr uint32_t BM = 128, BK = 64;
-constexpr uint32_t CONV_WARPS = 8;
+constexpr uint32_t CONV_WARPS = 16;
 constexpr uint32_t CONV_GROUPS = 4;                      // converter groups, each on its own k block
-constexpr uint32_t CONV_WPG = CONV_WARPS / CONV_GROUPS;  // warps per group
+constexpr uint32_t CONV_WPG = CONV_WARPS / CONV_GROUPS;  // warps per group: one per quarter of the TMEM lanes
 constexpr uint32_t FIRST_CONV = 3;
 constexpr uint32_t THREADS = 32 * (FIRST_CONV + CONV_WARPS);  // warp 0: weight TMA, warp 1: MMA, warp 2: activation TMA, the rest: conversion and epilogue
 constexpr uint32_t SPIN = 1u << 26;
@@ -68,6 +68,29 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d), "l"(adesc), "l"(bdesc),
                  "r"(idesc), "r"(accumulate)
                  : "memory");
+}
+// The same with A in tensor memory: lane = row, a 32-bit column = two consecutive k.
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc),
+                 "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// 32 columns of this warp's 32 lanes from registers (thread = lane, register j = column j).
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
+        "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+        "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// One lane of a converged warp (the same one every time).
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
+    return pred;
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -116,9 +139,11 @@ struct Maps {
 struct Args {
     MatArgs m;
     uint32_t n_pad;     // tokens rounded up to 16: the MMA's N
-    uint32_t stages;      // operand stages (A bf16 | B)
-    uint32_t raw_stages;  // int8 only: raw weight stages in front of them
-    uint32_t tmem_cols; // power of two >= max(32, n_pad)
+    uint32_t stages_a;    // A stages: in shared memory (bf16 weights) or in tensor memory (int8 weights)
+    uint32_t stages_b;    // B stages in shared memory
+    uint32_t raw_stages;  // int8 only: raw weight stages in front of the A stages
+    uint32_t tmem_cols; // power of two >= 32 holding the accumulator and, for int8, the A stages
+    uint32_t tmem_a0;   // int8: the first A stage's column (32 columns per stage)
     uint32_t splits;    // blocks of a cluster that share a weight tile, each over a slice of k
     uint32_t* err_flag;
 };
@@ -169,24 +194,26 @@ template <bool INT8, uint32_t EPI>
 __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    // Two rings. `C` operand stages of (A bf16 16 KiB | B n_pad x 128 B) feed the MMA; for int8 weights `R`
-    // raw stages of 8 KiB sit in front of them, deep enough to keep this SM's share of HBM bandwidth in
-    // flight (a converted stage carries 36 KiB of shared memory for 8 KiB of HBM traffic; a raw one 8 for 8).
-    const uint32_t n_pad = a.n_pad, C = a.stages, R = INT8 ? a.raw_stages : 0, splits = a.splits;
+    // Three rings, each as deep as its own latency asks. B stages (n_pad x 128 B) in shared memory cover
+    // an L2 round trip. A stages: bf16 weights land in shared memory (16 KiB a stage); int8 weights are
+    // converted into tensor memory (32 columns a stage, behind the accumulator), so shared memory carries
+    // a weight byte once, not five times. In front of those, int8 weights have `R` raw stages of 8 KiB:
+    // the bytes in flight that cover the latency of HBM.
+    const uint32_t n_pad = a.n_pad, CA = a.stages_a, CB = a.stages_b, R = INT8 ? a.raw_stages : 0, splits = a.splits;
     const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = BM * BK;
-    const uint32_t ab_bytes = a_bytes + b_bytes;
-    const uint32_t ring_bytes = max(C * ab_bytes + R * raw_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the rings
+    const uint32_t a_region = INT8 ? 0 : CA * a_bytes;
+    const uint32_t ring_bytes = max(a_region + CB * b_bytes + R * raw_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the rings
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes);
-    // full[C] (both operands of a stage), empty[C], raw_full[R], raw_empty[R], then the accumulator's barrier
-    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * C, bar_rfull = bar_empty + 8 * C, bar_rempty = bar_rfull + 8 * R,
-                   bar_accum = bar_rempty + 8 * R;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * C + 2 * R + 1);
+    // a_full[CA], a_empty[CA], b_full[CB], b_empty[CB], raw_full[R], raw_empty[R], then the accumulator's barrier
+    const uint32_t bar_afull = smem_u32(bars), bar_aempty = bar_afull + 8 * CA, bar_bfull = bar_aempty + 8 * CA, bar_bempty = bar_bfull + 8 * CB,
+                   bar_rfull = bar_bempty + 8 * CB, bar_rempty = bar_rfull + 8 * R, bar_accum = bar_rempty + 8 * R;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * CA + 2 * CB + 2 * R + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* inv_s = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);  // 1/rms per token
     const uint32_t smem_base = smem_u32(smem);
-    auto stage_a = [&](uint32_t c) { return smem_base + c * ab_bytes; };
-    auto stage_b = [&](uint32_t c) { return smem_base + c * ab_bytes + a_bytes; };
-    auto stage_raw = [&](uint32_t r) { return smem_base + C * ab_bytes + r * raw_bytes; };
+    auto stage_a = [&](uint32_t c) { return smem_base + c * a_bytes; };
+    auto stage_b = [&](uint32_t c) { return smem_base + a_region + c * b_bytes; };
+    auto stage_raw = [&](uint32_t r) { return smem_base + a_region + CB * b_bytes + r * raw_bytes; };
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t rank = splits > 1 ? cluster_rank() : 0, tile = blockIdx.x / splits;
@@ -196,9 +223,13 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     const uint32_t nkb = nkb_all / splits + (rank < nkb_all % splits ? 1 : 0);
 
     if (tid == 0) {
-        for (uint32_t c = 0; c < C; c++) {
-            mbar_init(bar_full + 8 * c, (INT8 ? CONV_WPG : 1) + 1);  // the weights' side (converter warps, or the loader's expect_tx) + the activations' loader
-            mbar_init(bar_empty + 8 * c, 1);
+        for (uint32_t c = 0; c < CA; c++) {
+            mbar_init(bar_afull + 8 * c, INT8 ? CONV_WPG : 1);  // a group's converter warps, or the loader's expect_tx
+            mbar_init(bar_aempty + 8 * c, 1);
+        }
+        for (uint32_t c = 0; c < CB; c++) {
+            mbar_init(bar_bfull + 8 * c, 1);
+            mbar_init(bar_bempty + 8 * c, 1);
         }
         for (uint32_t r = 0; r < R; r++) {
             mbar_init(bar_rfull + 8 * r, 1);
@@ -226,8 +257,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     if (warp == 0) {
         // The weights' loader: raw int8 tiles into the deep ring, or bf16 tiles straight into the operand ring.
         if (lane == 0) {
-            const uint32_t n_st = INT8 ? R : C, bar_e = INT8 ? bar_rempty : bar_empty, bar_f = INT8 ? bar_rfull : bar_full;
-            const uint32_t dst0 = INT8 ? stage_raw(0) : stage_a(0), step = INT8 ? raw_bytes : ab_bytes, bytes = INT8 ? raw_bytes : a_bytes;
+            const uint32_t n_st = INT8 ? R : CA, bar_e = INT8 ? bar_rempty : bar_aempty, bar_f = INT8 ? bar_rfull : bar_afull;
+            const uint32_t dst0 = INT8 ? stage_raw(0) : stage_a(0), step = INT8 ? raw_bytes : a_bytes, bytes = step;
             uint32_t st = 0, ph = 1;
             for (uint32_t i = 0; i < nkb; i++) {
                 ok = wait_or_abort(bar_e + 8 * st, ph, abort_flag);
@@ -244,74 +275,86 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         if (lane == 0) {
             uint32_t c = 0, ph = 1;
             for (uint32_t i = 0; i < nkb; i++) {
-                ok = wait_or_abort(bar_empty + 8 * c, ph, abort_flag);
+                ok = wait_or_abort(bar_bempty + 8 * c, ph, abort_flag);
                 if (!ok) break;
                 PROBE(3, i);
-                mbar_expect_tx(bar_full + 8 * c, b_bytes);
-                tma_load_2d(stage_b(c), &maps.b, int((kb_begin + i) * BK), 0, bar_full + 8 * c);
-                if (++c == C) { c = 0; ph ^= 1; }
+                mbar_expect_tx(bar_bfull + 8 * c, b_bytes);
+                tma_load_2d(stage_b(c), &maps.b, int((kb_begin + i) * BK), 0, bar_bfull + 8 * c);
+                if (++c == CB) { c = 0; ph ^= 1; }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = instr_desc(BM, n_pad);
-            // A descriptor's low word holds (address >> 4); the stages and the four 32-byte k steps of a
-            // stage differ only there.
-            const uint64_t da0 = smem_desc(stage_a(0)), db0 = smem_desc(stage_b(0));
-            const uint32_t hi_a = uint32_t(da0 >> 32), hi_b = uint32_t(db0 >> 32), lo_a0 = uint32_t(da0), lo_b0 = uint32_t(db0), lo_step = ab_bytes >> 4;
-            uint32_t c = 0, ph = 0;
-            for (uint32_t i = 0; i < nkb; i++) {
-                ok = wait_or_abort(bar_full + 8 * c, ph, abort_flag);
-                if (!ok) break;
-                PROBE(5, i);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t lo_a = lo_a0 + c * lo_step, lo_b = lo_b0 + c * lo_step;
+        // The MMA issuer. The whole warp runs the loop and one elected lane issues: descriptors and
+        // addresses then stay warp-uniform values instead of being moved over for every instruction.
+        const uint32_t leader = elect_one();
+        const uint32_t idesc = instr_desc(BM, n_pad);
+        // A descriptor's low word holds (address >> 4); the stages and the four 32-byte k steps of a
+        // stage differ only there.
+        const uint64_t da0 = smem_desc(stage_a(0)), db0 = smem_desc(stage_b(0));
+        const uint32_t hi_a = uint32_t(da0 >> 32), hi_b = uint32_t(db0 >> 32), lo_a0 = uint32_t(da0), lo_b0 = uint32_t(db0);
+        const uint32_t ta0 = tmem_base + a.tmem_a0;
+        uint32_t ca = 0, pa = 0, cb = 0, pb = 0;
+        for (uint32_t i = 0; i < nkb; i++) {
+            ok = wait_or_abort(bar_afull + 8 * ca, pa, abort_flag);
+            if (leader) PROBE(4, i);
+            ok = ok && wait_or_abort(bar_bfull + 8 * cb, pb, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (leader) PROBE(5, i);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lo_a = lo_a0 + ca * (a_bytes >> 4), lo_b = lo_b0 + cb * (b_bytes >> 4), ta = ta0 + 32 * ca;
+            if (leader) {
 #pragma unroll
-                for (uint32_t k4 = 0; k4 < BK / 16; k4++)
-                    mma_f16(tmem_base, (uint64_t(hi_a) << 32) | (lo_a + 2 * k4), (uint64_t(hi_b) << 32) | (lo_b + 2 * k4), idesc, (i | k4) != 0 ? 1u : 0u);
-                mma_commit(bar_empty + 8 * c);  // arrives once these MMAs have read the stage
+                for (uint32_t k4 = 0; k4 < BK / 16; k4++) {
+                    if (INT8) mma_f16_ts(tmem_base, ta + 8 * k4, (uint64_t(hi_b) << 32) | (lo_b + 2 * k4), idesc, (i | k4) != 0 ? 1u : 0u);
+                    else mma_f16(tmem_base, (uint64_t(hi_a) << 32) | (lo_a + 2 * k4), (uint64_t(hi_b) << 32) | (lo_b + 2 * k4), idesc, (i | k4) != 0 ? 1u : 0u);
+                }
+                mma_commit(bar_aempty + 8 * ca);  // arrive once these MMAs have read the stages
+                mma_commit(bar_bempty + 8 * cb);
                 PROBE(6, i);
-                if (++c == C) { c = 0; ph ^= 1; }
             }
-            if (ok) mma_commit(bar_accum);
+            __syncwarp();
+            if (++ca == CA) { ca = 0; pa ^= 1; }
+            if (++cb == CB) { cb = 0; pb ^= 1; }
         }
+        if (ok && leader) mma_commit(bar_accum);
         __syncwarp();
     } else if (INT8) {
-        // Raw int8 [128][64] to bf16 in the swizzled layout, 16 bytes of a row at a time. The warps work
-        // in CONV_GROUPS groups that take k blocks in turn: a k block's wait -> load -> convert -> store ->
-        // fence -> arrive chain is long, and with every warp on the same k block nothing would overlap it.
-        const uint32_t grp = (warp - FIRST_CONV) / CONV_WPG, gtid = tid - (FIRST_CONV + grp * CONV_WPG) * 32;
-        uint32_t r = grp % R, rph = (grp / R) & 1, c = grp % C, cph = ((grp / C) & 1) ^ 1;
-        const uint32_t row_q = (gtid >> 2) * 128, q = gtid & 3, sw = (gtid >> 2) & 7;  // a thread's rows are 16 apart: the same swizzle phase
-        const uint32_t off_lo = row_q + (((2 * q) ^ sw) << 4), off_hi = row_q + (((2 * q + 1) ^ sw) << 4);
+        // Raw int8 [128][64] to bf16 in tensor memory. A thread owns a row (the TMEM lane its warp can reach:
+        // 32 (warp % 4) + lane), converts its 64 bytes exactly and stores 32 columns of bf16 pairs. The raw
+        // tile was swizzled by the TMA (64-byte mode: 16-byte chunk ^= (row >> 1) & 3), which keeps the
+        // row-per-thread loads off each other's banks. Groups of four warps take k blocks in turn: a k
+        // block's wait -> load -> convert -> store -> arrive chain is long, and this overlaps several of them.
+        const uint32_t grp = (warp - FIRST_CONV) / CONV_WPG, quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t row_off = row * 64, sw = (row >> 1) & 3, lane_base = tmem_base + ((quarter * 32) << 16) + a.tmem_a0;
+        uint32_t r = grp % R, rph = (grp / R) & 1, c = grp % CA, cph = ((grp / CA) & 1) ^ 1;
         for (uint32_t i = grp; i < nkb; i += CONV_GROUPS) {
-            ok = wait_or_abort(bar_rfull + 8 * r, rph, abort_flag) && wait_or_abort(bar_empty + 8 * c, cph, abort_flag);
+            ok = wait_or_abort(bar_rfull + 8 * r, rph, abort_flag) && wait_or_abort(bar_aempty + 8 * c, cph, abort_flag);
             if (!ok) break;
-            if (gtid == 0) PROBE(1, i);
-            const uint32_t src = stage_raw(r), dst = stage_a(c);
+            if (lane == 0 && quarter == 3) PROBE(1, i);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the MMAs that read this stage last are done
+            const uint32_t src = stage_raw(r) + row_off;
+            uint32_t v[32];
 #pragma unroll
-            for (uint32_t p = 0; p < 512 / (32 * CONV_WPG); p++) {
+            for (uint32_t j = 0; j < 4; j++) {
                 uint4 raw;
-                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(src + (gtid + 32 * CONV_WPG * p) * 16));
-                uint4 lo, hi;
-                cvt_i8x4(raw.x, lo.x, lo.y);
-                cvt_i8x4(raw.y, lo.z, lo.w);
-                cvt_i8x4(raw.z, hi.x, hi.y);
-                cvt_i8x4(raw.w, hi.z, hi.w);
-                const uint32_t base = dst + p * (8 * CONV_WPG * 128);  // 32 CONV_WPG threads cover 8 CONV_WPG rows
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + off_lo), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(base + off_hi), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(src + ((j ^ sw) << 4)));
+                cvt_i8x4(raw.x, v[8 * j + 0], v[8 * j + 1]);
+                cvt_i8x4(raw.y, v[8 * j + 2], v[8 * j + 3]);
+                cvt_i8x4(raw.z, v[8 * j + 4], v[8 * j + 5]);
+                cvt_i8x4(raw.w, v[8 * j + 6], v[8 * j + 7]);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+            tmem_st32(lane_base + 32 * c, v);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (gtid == 0) PROBE(2, i);
+            if (lane == 0 && quarter == 3) PROBE(2, i);
             if (lane == 0) {  // one arrival per warp: an arrival per thread would serialise on the barrier
-                mbar_arrive(bar_full + 8 * c);
+                mbar_arrive(bar_afull + 8 * c);
                 mbar_arrive(bar_rempty + 8 * r);
             }
             for (r += CONV_GROUPS; r >= R; r -= R) rph ^= 1;
-            for (c += CONV_GROUPS; c >= C; c -= C) cph ^= 1;
+            for (c += CONV_GROUPS; c >= CA; c -= CA) cph ^= 1;
         }
     }
 
@@ -354,7 +397,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             for (uint32_t j = 0; j < 16; j++)
                 if (t0 + j < m.n) {
                     const size_t o = size_t(t0 + j) * out_w + out_r;
-                    m.Y[o] = y[j];
+                    if (m.Y) m.Y[o] = y[j];
                     if (m.Yb) m.Yb[o] = f32_to_bf16(y[j]);
                 }
         }
@@ -364,11 +407,11 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // Two warps share a quarter of the TMEM lanes (rows) and take alternate groups of 16 tokens.
+            // The warps that share a quarter of the TMEM lanes (rows) take groups of 16 tokens in turn.
             const uint32_t quarter = warp & 3, half = ew >> 2, r = quarter * 32 + lane;
             const float scale = INT8 ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
             float* part = reinterpret_cast<float*>(smem) + size_t(r) * pitch;
-            for (uint32_t c0 = 16 * half; c0 < n_pad; c0 += 32) {
+            for (uint32_t c0 = 16 * half; c0 < n_pad; c0 += 16 * (CONV_WARPS / 4)) {
                 float acc[16];
                 tmem_ld16(tmem_base + ((quarter * 32) << 16) + c0, acc);
                 if (splits == 1) {
@@ -467,23 +510,28 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     auto it = cache.maps.find(key);
     if (it == cache.maps.end()) {
         gemm::Maps m;
-        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 1, false);
+        if (a.int8) make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 1, false, true);
         else make_tensor_map_2d(m.a, a.W, a.k, a.m, gemm::BK, gemm::BM, 2, true);
         make_tensor_map_2d(m.b, a.Xb, a.k, n_pad, gemm::BK, n_pad, 2, true);
         it = cache.maps.emplace(key, m).first;
     }
-    // Shared memory: operand stages of (16 KiB + n_pad x 128 B); for int8, raw stages of 8 KiB in front.
-    const uint32_t ab_bytes = gemm::BM * gemm::BK * 2 + n_pad * gemm::BK * 2, raw_bytes = gemm::BM * gemm::BK;
+    // Shared memory: B stages of n_pad x 128 B; bf16 weights, as many A stages of 16 KiB; int8 weights, A
+    // stages in tensor memory behind the accumulator and raw stages of 8 KiB in the shared memory left.
+    const uint32_t a_bytes = gemm::BM * gemm::BK * 2, b_bytes = n_pad * gemm::BK * 2, raw_bytes = gemm::BM * gemm::BK;
     const uint32_t budget = 208 * 1024;
-    uint32_t stages, raw_stages = 0;
+    const uint32_t tmem_a0 = (n_pad + 31) / 32 * 32;
+    uint32_t stages_a, stages_b, raw_stages = 0;
     if (a.int8) {
-        stages = std::max(2u, std::min(4u, (budget - 8 * raw_bytes) / ab_bytes));
-        raw_stages = std::max(2u, std::min(12u, (budget - stages * ab_bytes) / raw_bytes));
+        stages_a = std::min(8u, (512 - tmem_a0) / 32);
+        stages_b = std::max(2u, std::min(4u, (budget - 4 * raw_bytes) / b_bytes));
+        raw_stages = std::max(2u, std::min(16u, (budget - stages_b * b_bytes) / raw_bytes));
     } else {
-        stages = std::max(2u, std::min(8u, budget / ab_bytes));
+        stages_a = stages_b = std::max(2u, std::min(8u, budget / (a_bytes + b_bytes)));
     }
-    const uint32_t ring = std::max(stages * ab_bytes + raw_stages * raw_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
-    const size_t smem = size_t(ring) + 1024 + (2 * stages + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4;
+    const uint32_t ring = std::max((a.int8 ? 0 : stages_a * a_bytes) + stages_b * b_bytes + raw_stages * raw_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
+    // At least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
+    // behind another one (blocks of different clusters waiting on each other's SMs could deadlock).
+    const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4, 116 * 1024);
     if (!configured) {
         for (int i8 = 0; i8 < 2; i8++)
             for (uint32_t epi = EPI_NORM; epi <= EPI_RAW; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -517,11 +565,13 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     gemm::Args g;
     g.m = a;
     g.n_pad = n_pad;
-    g.stages = stages;
+    g.stages_a = stages_a;
+    g.stages_b = stages_b;
     g.raw_stages = raw_stages;
     uint32_t cols = 32;
-    while (cols < n_pad) cols *= 2;
+    while (cols < (a.int8 ? tmem_a0 + 32 * stages_a : n_pad)) cols *= 2;
     g.tmem_cols = cols;
+    g.tmem_a0 = tmem_a0;
     g.splits = splits;
     g.err_flag = err_flag;
     cudaLaunchConfig_t cfg = {};
@@ -543,7 +593,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
         cudaStreamSynchronize(s);
         static unsigned long long h[8][64];
         cudaMemcpyFromSymbol(h, gemm::g_probe, sizeof(h));
-        fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u stages=%u raw=%u\n", a.m, a.k, a.n, splits, stages, raw_stages);
+        fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u stages a %u b %u raw %u\n", a.m, a.k, a.n, splits, stages_a, stages_b, raw_stages);
         const unsigned long long t0 = h[0][0];
         for (uint32_t i = 0; i < std::min(64u, nkb / splits); i++)
             fprintf(stderr, "kb %2u: tmaA %6lld convstart %6lld convdone %6lld tmaB %6lld afull %6lld bfull %6lld commit %6lld\n", i, (long long)(h[0][i] - t0),

@@ -43,7 +43,7 @@ struct alignas(64) AttnMaps {
 };
 void attn_maps_init(AttnMaps* m, const uint16_t* k_cache, const uint16_t* v_cache, uint64_t total_rows);
 void make_tensor_map_2d(void* out_map, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows, uint32_t elem_bytes,
-                        bool swizzle128);
+                        bool swizzle128, bool swizzle64 = false);
 struct AttnArgs {
     const AttnMaps* maps;  // host pointer
     uint32_t* err_flag;    // device word set if a bounded wait ran out
