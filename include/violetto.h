@@ -143,6 +143,22 @@ int vlt_sample_logits(VltEngine* e, const float* logits, const VltSampling* rows
  * time, best of reps. */
 int vlt_spec_accept(VltEngine* e, const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature,
                     const uint64_t* seeds, const uint32_t* pos0, uint32_t reps, uint32_t* accepted, uint32_t* token, uint32_t* rollback, double* gpu_seconds);
+/* The same acceptance step for a caller that cannot allocate device memory at that point (all of it
+ * is in the caller's own pools, or an allocation's device-wide synchronisation is not acceptable
+ * inside the decode loop). No counterpart in the reference. It allocates nothing, on the device or
+ * (when it succeeds) on the host: its scratch is a pair of static device arrays of fixed size, so
+ * streams * (2 k + 1) may be at most vlt_spec_accept_static_max_rows() (2048); beyond that it fails
+ * with a message and vlt_spec_accept is the call to use. Every pointer is device memory of the
+ * current device; the kernels are queued on cuda_stream (a cudaStream_t; NULL: the default stream)
+ * and the call does not wait for them. A draft id >= vocab is read as 0. The first call made with a
+ * given device current looks up the arrays' addresses: that call is set-up and should come before
+ * the caller begins any stream capture. All calls on one device share the arrays; nothing in them
+ * needs clearing between calls, but two calls whose kernels overlap in time (two streams, two
+ * threads) race on them. */
+int vlt_spec_accept_static(const uint16_t* p_dev, const uint16_t* q_dev, const uint32_t* drafts_dev, uint32_t streams, uint32_t k, uint32_t vocab,
+                           float temperature, const uint64_t* seeds_dev, const uint32_t* pos0_dev, uint32_t* accepted_dev, uint32_t* token_dev,
+                           uint32_t* rollback_dev, void* cuda_stream);
+uint32_t vlt_spec_accept_static_max_rows(void);
 /* set_profile_skip, hooks.rs:9-26: leave kernel groups out (results are then wrong). */
 enum { VLT_SKIP_QKV = 1, VLT_SKIP_POST = 2, VLT_SKIP_ATTN = 4, VLT_SKIP_REDUCE = 8, VLT_SKIP_O = 16, VLT_SKIP_GATE_UP = 32, VLT_SKIP_DOWN = 64, VLT_SKIP_HEAD = 256 };
 void vlt_set_profile_skip(VltEngine* e, uint32_t mask);

@@ -168,6 +168,18 @@ int vlt_spec_accept(VltEngine* e, const uint16_t* p, const uint16_t* q, const ui
     });
 }
 
+int vlt_spec_accept_static(const uint16_t* p_dev, const uint16_t* q_dev, const uint32_t* drafts_dev, uint32_t streams, uint32_t k, uint32_t vocab,
+                           float temperature, const uint64_t* seeds_dev, const uint32_t* pos0_dev, uint32_t* accepted_dev, uint32_t* token_dev,
+                           uint32_t* rollback_dev, void* cuda_stream) {
+    // No guard(): nothing on this path throws, and the success path allocates nothing on host or device.
+    const char* err = launch_spec_accept_static(p_dev, q_dev, drafts_dev, streams, k, vocab, temperature, seeds_dev, pos0_dev, accepted_dev, token_dev,
+                                                rollback_dev, static_cast<cudaStream_t>(cuda_stream));
+    if (!err) return 0;
+    g_error = err;
+    return 1;
+}
+uint32_t vlt_spec_accept_static_max_rows(void) { return spec_accept_static_max_rows(); }
+
 void vlt_set_profile_skip(VltEngine* e, uint32_t mask) { if (e && e->e) e->e->skip = mask; }
 
 int vlt_bench_matmul(VltEngine* e, const char* kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes) {

@@ -14,6 +14,8 @@
 // over the logits from HBM -- then one block per stream that decides and draws (its two rows
 // come from L2).
 #include <cfloat>
+#include <cmath>
+#include <mutex>
 
 #include "kernels.h"
 
@@ -176,6 +178,78 @@ void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* dr
     spec::decide_kernel<<<streams, spec::THREADS, 0, s>>>(p, q, drafts, static_cast<const spec::RowStats*>(stats), streams, k, vocab, c, seeds, pos0, accepted,
                                                           token, rollback);
     launch_counter()++;
+}
+
+// ------------------------------------------------ the same, with nothing allocated
+// A variant for callers that cannot allocate device memory when they need an acceptance step:
+// a serving loop that has handed every byte of the device to its own pools, or one that must not
+// pay the device-wide synchronisation an allocation or a free can imply in the middle of decoding.
+// Its scratch (the per-row statistics, and a bounds-checked copy of the draft ids) lives in
+// file-scope device arrays of a fixed size, so a step may cover at most STATIC_MAX_ROWS rows of
+// logits. The arrays' addresses are looked up once per device, on the first call made with that
+// device current; that first call is set-up and belongs before the caller starts any stream
+// capture. All calls on a device share the arrays: nothing in them has to start at zero (the first
+// kernel overwrites every word the later ones read), but two calls in flight at once on one
+// device race on them.
+namespace spec {
+
+constexpr uint32_t STATIC_MAX_ROWS = 2048;  // streams * (2 k + 1) rows of logits a call may cover
+static __device__ __align__(256) RowStats static_stats[STATIC_MAX_ROWS];
+static __device__ __align__(256) uint32_t static_drafts[STATIC_MAX_ROWS];
+
+// The caller's draft ids cannot be checked on the host here; an id past the vocabulary is read as 0
+// instead of indexing out of the logits (that stream's result then means nothing).
+__global__ void copy_drafts_kernel(const uint32_t* __restrict__ drafts, uint32_t n, uint32_t vocab, uint32_t* out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = drafts[i] < vocab ? drafts[i] : 0u;
+}
+
+struct StaticScratch {
+    RowStats* stats;
+    uint32_t* drafts;
+};
+
+// The arrays' addresses on the current device; looked up (cudaGetSymbolAddress) on the first call per device.
+static const char* static_scratch(StaticScratch* out) {
+    constexpr int MAX_DEVICES = 64;
+    static StaticScratch table[MAX_DEVICES] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return "spec_accept_static: no usable current device";
+    std::lock_guard<std::mutex> lock(mu);
+    if (!table[dev].stats) {
+        void* ps = nullptr;
+        void* pd = nullptr;
+        if (cudaGetSymbolAddress(&ps, static_stats) != cudaSuccess || !ps) return "spec_accept_static: cudaGetSymbolAddress failed for the statistics array";
+        if (cudaGetSymbolAddress(&pd, static_drafts) != cudaSuccess || !pd) return "spec_accept_static: cudaGetSymbolAddress failed for the draft array";
+        table[dev].drafts = static_cast<uint32_t*>(pd);
+        table[dev].stats = static_cast<RowStats*>(ps);
+    }
+    *out = table[dev];
+    return nullptr;
+}
+
+}  // namespace spec
+
+uint32_t spec_accept_static_max_rows() { return spec::STATIC_MAX_ROWS; }
+
+// Every pointer is device memory of the current device. Returns NULL, or a message (a string literal:
+// this path does not allocate on the host either).
+const char* launch_spec_accept_static(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab,
+                                      float temperature, const uint64_t* seeds, const uint32_t* pos0, uint32_t* accepted, uint32_t* token,
+                                      uint32_t* rollback, cudaStream_t s) {
+    if (!p || !q || !drafts || !seeds || !pos0 || !accepted || !token || !rollback) return "spec_accept_static: null pointer";
+    if (streams == 0 || k == 0 || k > 15 || vocab == 0) return "spec_accept_static: needs at least one stream, 1..15 drafts and a vocabulary";
+    if (!(std::isnormal(temperature) && temperature > 0.0f)) return "spec_accept_static: needs a normal positive temperature";
+    if (uint64_t(streams) * (2 * k + 1) > spec::STATIC_MAX_ROWS)
+        return "spec_accept_static: streams * (2 k + 1) exceeds the 2048 rows the static scratch holds; use vlt_spec_accept";
+    spec::StaticScratch sc{};
+    if (const char* e = spec::static_scratch(&sc)) return e;
+    const uint32_t n = streams * k;
+    spec::copy_drafts_kernel<<<(n + 255) / 256, 256, 0, s>>>(drafts, n, vocab, sc.drafts);
+    launch_counter()++;
+    launch_spec_accept(p, q, sc.drafts, streams, k, vocab, temperature, seeds, pos0, sc.stats, accepted, token, rollback, s);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "spec_accept_static: kernel launch failed";
 }
 
 }  // namespace vlt

@@ -87,6 +87,12 @@ void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed
 // Rejection-sampling acceptance over bf16 draft and target logits on the device (k_spec.cu).
 void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab, float temperature,
                         const uint64_t* seeds, const uint32_t* pos0, void* stats, uint32_t* accepted, uint32_t* token, uint32_t* rollback, cudaStream_t s);
+// The same with its scratch in static device arrays: allocates nothing; device pointers throughout.
+// Returns NULL or an error message (a literal).
+uint32_t spec_accept_static_max_rows();
+const char* launch_spec_accept_static(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab,
+                                      float temperature, const uint64_t* seeds, const uint32_t* pos0, uint32_t* accepted, uint32_t* token,
+                                      uint32_t* rollback, cudaStream_t s);
 void launch_kv_fill(uint16_t* k_cache, uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t n_layers, uint32_t slot, uint32_t from,
                     uint32_t to, uint32_t seed, cudaStream_t s);
 

@@ -385,6 +385,23 @@ class Engine:
         return a.value, b.value
 
 
+def spec_accept_static(p_dev: int, q_dev: int, drafts_dev: int, streams: int, k: int, vocab: int, temperature: float, seeds_dev: int, pos0_dev: int,
+                       accepted_dev: int, token_dev: int, rollback_dev: int, cuda_stream: int = 0) -> None:
+    """vlt_spec_accept_static: the acceptance step on device pointers (integers) of the current device,
+    with static scratch -- nothing is allocated. Queues the kernels on `cuda_stream` and returns."""
+    fn = lib().vlt_spec_accept_static
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                   C.c_void_p, C.c_void_p]
+    fn.restype = C.c_int
+    _check(fn(p_dev, q_dev, drafts_dev, streams, k, vocab, temperature, seeds_dev, pos0_dev, accepted_dev, token_dev, rollback_dev, cuda_stream or None))
+
+
+def spec_accept_static_max_rows() -> int:
+    fn = lib().vlt_spec_accept_static_max_rows
+    fn.restype = C.c_uint32
+    return int(fn())
+
+
 class Draft:
     """engine/src/engine/generate.rs:24-42."""
     NONE, REPLAY, MODEL = 0, 1, 2
