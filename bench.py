@@ -103,7 +103,7 @@ def make_engine(E, path, streams, ctx, steps_total, device, attn_keys=0):
 def fill(eng, streams, ctx, rank):
     seqs = [eng.new_seq() for _ in range(streams)]
     for j, s in enumerate(seqs):
-        eng.bench_fill(s, ctx, seed=1000 * rank + 7 + j)  # the reference seeds stream j's prompt with 7 + j (cli/src/bench.rs:165)
+        eng.bench_fill(s, ctx, seed=stream_seeds(rank, j)[0])
     return seqs
 
 
@@ -126,7 +126,7 @@ def run_replica(args, rank, world, barrier, device, eng, mistakes):
     """One timed pass: `warmup` + `steps` verify steps of every stream, drafts from the replay drafter."""
     from silicon_violetto_b200 import engine as E
     total_steps = args.warmup + args.steps + 6
-    sampling = lambda j: E.Sampling(args.temperature, 0.95, 1 + 1000 * rank + j)
+    sampling = lambda j: E.Sampling(args.temperature, 0.95, stream_seeds(rank, j)[1])
     n_rec = ROWS * total_steps + 8
     recorded = record_plain(E, eng, args.streams, args.ctx, n_rec, rank, sampling) if mistakes < 1.0 else [[0] * n_rec] * args.streams
     seqs = fill(eng, args.streams, args.ctx, rank)
@@ -167,13 +167,13 @@ def run_replica(args, rank, world, barrier, device, eng, mistakes):
                 mean_len=mean_len, h2d=h2d, d2h=d2h, clocks=clocks.summary(), tokens_per_step=[s["tokens"] for s in timed])
 
 
-def cpu_reference(args, streams, steps, threads_note=True):
+def cpu_reference(args, streams, steps, warmup=1):
     """The CPU restatement of the path (the oracle) timed on this machine's cores, on a bounded
     sample of the workload: `streams` streams at the full context, `steps` verify steps of 5 rows."""
     _package()
     import oracle
     path = model_file("1b", not args.bf16, 0)
-    room = ROWS * (steps + 2) + 32
+    room = ROWS * (steps + warmup + 2) + 32
     eng = oracle.Engine(path, max_seqs=streams, max_step_tokens=streams * ROWS, max_chunk=16, kv_tokens=streams * (args.ctx + room + 16),
                         max_seq_len=args.ctx + room, max_head_rows=streams * ROWS)
     seqs = [eng.new_seq() for _ in range(streams)]
@@ -183,17 +183,36 @@ def cpu_reference(args, streams, steps, threads_note=True):
         eng.write("feed", s * 16, [100 + j, 1, 2, 3, 4])
     runs = [(s, [oracle.FEED_ROW + i for i in range(ROWS)], oracle.ROWS_LAST, True) for s in seqs]
     times, emitted = [], []
-    for i in range(steps + 1):
+    for i in range(steps + warmup):
         t0 = time.perf_counter()
         eng.step(runs)
         dt = time.perf_counter() - t0
         em = eng.array("emitted")[:streams]
         for j, s in enumerate(seqs):  # what `collect` does: give back the rows that were not accepted
             eng.settle(s, ROWS - int(em[j]))
-        if i > 0:
+        if i >= warmup:
             times.append(dt)
             emitted.append(int(em.sum()))
     return float(np.median(times)), os.cpu_count(), float(np.mean(emitted))
+
+
+def reduce_over_ranks(dev_ms, wall_s, emitted, launches, world, device):
+    """What the replicas share after the timed region: the slowest rank's times (MAX) and the whole job's
+    emitted tokens and kernel launches (SUM). The only collective of the bench; none on the data path."""
+    import torch
+    import torch.distributed as dist
+    vals = torch.tensor([dev_ms, wall_s], dtype=torch.float64, device=device)
+    sums = torch.tensor([float(emitted), float(launches)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    return vals.tolist(), sums.tolist()
+
+
+def stream_seeds(rank: int, stream: int):
+    """(context seed, sampling seed) of stream `stream` on replica `rank`: distinct over the whole job.
+    Rank 0 keeps the reference's 7 + j (cli/src/bench.rs:165)."""
+    return 1000 * rank + 7 + stream, 1 + 1000 * rank + stream
 
 
 def main():
@@ -208,8 +227,8 @@ def main():
     ap.add_argument("--mistakes", type=float, default=1.0, help="share of positions drafted wrong in the headline pass (1: every draft wrong, what a random-init drafter gives)")
     ap.add_argument("--replay-mistakes", type=float, default=0.3, help="a second pass with the replay drafter at this mistake rate (cli/src/bench_spec.rs:26-28); 1: skip")
     ap.add_argument("--bf16", action="store_true", help="bf16 weights instead of int8")
-    ap.add_argument("--cpu-streams", type=int, default=2)
-    ap.add_argument("--cpu-steps", type=int, default=2)
+    ap.add_argument("--cpu-streams", type=int, default=8, help="streams of the CPU sample")
+    ap.add_argument("--cpu-steps", type=int, default=10, help="timed verify steps of the CPU sample (the reference arm takes --steps, at most 20)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
@@ -227,14 +246,15 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)
+        ref_steps = max(1, min(args.steps, 20))
+        t_step, cores, em = cpu_reference(args, args.cpu_streams, ref_steps, warmup=min(args.warmup, 3))
         v = em / t_step
         print(json.dumps({"impl": "reference", "metric": "decode tokens/s at 8k context", "value": v, "unit": "tokens/s",
                           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
                           "vs_baseline": None, "dtype": "bf16 activations, int8 weights" if not args.bf16 else "bf16", "data": "synthetic",
                           "config": {"workload": workload, "streams_timed": args.cpu_streams, "drafter": "every draft wrong", "mean_accepted_len": em / args.cpu_streams},
                           "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                           "sample": f"{args.cpu_streams} streams x {args.cpu_steps} verify steps of 5 rows at ctx {args.ctx}; the reference has no CPU path, this is the C++ restatement of its shader math"},
+                                           "sample": f"{args.cpu_streams} streams x {ref_steps} verify steps of 5 rows at ctx {args.ctx}; the reference has no CPU path, this is the C++ restatement of its shader math"},
                           "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
@@ -255,17 +275,13 @@ def main():
     eng, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
     r = run_replica(args, rank, world, barrier, local, eng, args.mistakes)
     extra = run_replica(args, rank, world, barrier, local, eng, args.replay_mistakes) if args.replay_mistakes < 1.0 else None
-    vals = torch.tensor([r["dev_ms"], r["wall"]], dtype=torch.float64, device=f"cuda:{local}")
-    sums = torch.tensor([float(r["emitted"]), float(r["launches"])], dtype=torch.float64, device=f"cuda:{local}")
-    if world > 1:
-        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    vals, sums = reduce_over_ranks(r["dev_ms"], r["wall"], r["emitted"], r["launches"], world, f"cuda:{local}")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    dev_s, wall_s = vals[0].item() * 1e-3, vals[1].item()
-    emitted = sums[0].item()
+    dev_s, wall_s = vals[0] * 1e-3, vals[1]
+    emitted = sums[0]
     steps = args.steps
     tau = emitted / (steps * args.streams * world)
     # Roofline of the dominant kernel (the paged attention at 32 streams): algorithmic bytes of one
@@ -283,7 +299,7 @@ def main():
                    "kv": "filled without computing it (timing does not depend on KV values)", "l2": "per-step traffic (weights 1.2 GB + KV) exceeds the 126 MB L2",
                    "parallelism": f"{world} replica(s), streams sharded, no collective"},
         "e2e": {"value": emitted / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
-        "gpu_launches": int(sums[1].item()),
+        "gpu_launches": int(sums[1]),
         "clocks": r["clocks"],
         "roofline": {"bound": "hbm", "kernel": "attn_mma_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
                      "traffic": None, "step_frac": step_bytes / (dev_s / steps) / 1e9 / hbm_peak},
