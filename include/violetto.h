@@ -238,6 +238,8 @@ int vlt_debug_set_trace(VltEngine* e, uint32_t slot, const uint32_t* trace, uint
  * head, sampling, acceptance; the reference times its step with GPUEndTime - GPUStartTime,
  * engine/src/gpu.rs:147-154, and kernel groups by leaving them out, cli/src/profile.rs:44-104);
  * the bytes one step uploads and downloads. */
+/* vlt_debug_step then runs the loaded drafter for this many rows after the step (0: not). */
+void vlt_debug_set_draft_rows(VltEngine* e, uint32_t rows);
 int vlt_debug_mark(VltEngine* e, uint32_t which);
 int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms);
 uint64_t vlt_debug_launches(void);

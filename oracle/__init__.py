@@ -288,14 +288,18 @@ class Engine:
     def set_replay(self, rate: float, seed: int):
         lib().orc_set_replay(self.h, C.c_float(rate), C.c_uint32(seed))
 
-    def step(self, runs, hidden=ROWS_NONE, plan_only=False, replay=False):
-        """runs: list of (seq, tokens, head Rows, verify bool)."""
+    def load_drafter(self, path):
+        if lib().orc_load_drafter(self.h, str(path).encode()):
+            raise RuntimeError(_err())
+
+    def step(self, runs, hidden=ROWS_NONE, plan_only=False, replay=False, draft_rows=0):
+        """runs: list of (seq, tokens, head Rows, verify bool). draft_rows: the chain drafter proposes for that many rows."""
         seq = np.asarray([r[0] for r in runs], np.uint32)
         count = np.asarray([len(r[1]) for r in runs], np.uint32)
         heads = np.asarray([r[2] for r in runs], np.uint32)
         verify = np.asarray([1 if r[3] else 0 for r in runs], np.uint32)
         toks = np.concatenate([np.asarray(r[1], np.uint32) for r in runs]) if runs else np.zeros(0, np.uint32)
-        mode = (1 if plan_only else 0) | (2 if replay else 0)
+        mode = (1 if plan_only else 0) | (2 if replay else 0) | (int(draft_rows) << 8)
         if lib().orc_step(self.h, C.c_uint32(len(runs)), _p(seq), _p(count), _p(verify), _p(heads), _p(toks), C.c_uint32(hidden), C.c_uint32(mode)):
             raise RuntimeError(_err())
 
@@ -304,8 +308,8 @@ class Engine:
         if lib().orc_array_write(self.h, name.encode(), C.c_uint64(index), _p(d), C.c_uint64(d.size)):
             raise RuntimeError(_err())
 
-    _F32 = ("logits", "hidden_out", "taps", "draft_logits")
-    _U16 = ("k_cache", "v_cache")
+    _F32 = ("logits", "hidden_out", "taps", "draft_logits", "carry")
+    _U16 = ("k_cache", "v_cache", "draft_k_cache", "draft_v_cache")
 
     def array(self, name: str) -> np.ndarray:
         ptr = C.c_void_p()

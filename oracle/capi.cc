@@ -141,6 +141,7 @@ void orc_set_trace(void* h, uint32_t slot, const uint32_t* trace, uint32_t n) {
     std::copy_n(trace, n, e->trace.begin() + size_t(slot) * e->cfg.max_seq_len);
     e->trace_len[slot] = n;
 }
+int orc_load_drafter(void* h, const char* path) { try { static_cast<Engine*>(h)->load_drafter(path); return 0; } catch (const std::exception& e) { return fail(e); } }
 void orc_set_replay(void* h, float rate, uint32_t seed) {
     Engine* e = static_cast<Engine*>(h);
     e->replay = ReplayArgs{e->cfg.max_seq_len, seed, rate, e->md.vocab_real};
@@ -148,7 +149,7 @@ void orc_set_replay(void* h, float rate, uint32_t seed) {
 
 // One step. Runs are (seq, count, verify) with their tokens concatenated in `tokens`;
 // `head` and `hidden` are Rows values; mode bit 0: plan only (no forward), bit 1: run the
-// replay drafter after the step.
+// replay drafter after the step; bits 8..11: run the chain drafter for that many rows.
 int orc_step(void* h, uint32_t n_runs, const uint32_t* seq, const uint32_t* count, const uint32_t* verify, const uint32_t* heads, const uint32_t* tokens,
              uint32_t hidden, uint32_t mode) {
     try {
@@ -162,6 +163,7 @@ int orc_step(void* h, uint32_t n_runs, const uint32_t* seq, const uint32_t* coun
         Plan p = e->plan(runs, Rows(hidden));
         if (mode & 1) return 0;
         e->forward(p);
+        if ((mode >> 8) & 15) e->draft(p, (mode >> 8) & 15);
         if (mode & 2) e->run_replay(p);
         return 0;
     } catch (const std::exception& e) { return fail(e); }
@@ -176,6 +178,9 @@ uint64_t orc_array(void* h, const char* name, const void** ptr) {
     ARR(tokens) ARR(tin) ARR(vis) ARR(head_rows) ARR(hidden_rows) ARR(out_ids) ARR(tiles) ARR(emitted) ARR(meta)
     ARR(logits) ARR(hidden_out) ARR(taps) ARR(k_cache) ARR(v_cache) ARR(draft_logits)
 #undef ARR
+    if (n == "draft_k_cache" && e->drafter) { *ptr = e->drafter->k_cache.data(); return e->drafter->k_cache.size(); }
+    if (n == "draft_v_cache" && e->drafter) { *ptr = e->drafter->v_cache.data(); return e->drafter->v_cache.size(); }
+    if (n == "carry" && e->drafter) { *ptr = e->drafter->carry.data(); return e->drafter->carry.size(); }
     if (n == "gen") { *ptr = e->gen.data(); return e->gen.size() * sizeof(GenState) / 4; }
     if (n == "runs") { *ptr = e->runs.data(); return e->runs.size() * 6; }
     if (n == "sample_rows") { *ptr = e->sample_rows.data(); return e->sample_rows.size() * 6; }

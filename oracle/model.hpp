@@ -183,7 +183,8 @@ struct Engine {
     std::vector<float> logits, hidden_out, taps;  // taps: bf16(rms_norm(last layer's output)) as fp32, [n][d]
     ReplayArgs replay{0, 0, 0.0f, 0};
     std::unique_ptr<Drafter> drafter;
-    std::vector<float> draft_logits;  // the drafter's last pass, [rows][v]
+    std::vector<float> draft_logits;  // the drafter's passes, [rows - 1][runs][v]; rows of runs that did not draft stay 0
+    std::vector<uint32_t> write_mask;  // per step token: does its K/V go to the cache (empty: all do)
 
     Engine(const std::string& file_path, const EngineConfig& c) : file(VltFile::load(file_path)), cfg(c) {
         std::vector<float> m = file.f32s("meta");
@@ -291,7 +292,8 @@ struct Engine {
             Seq& s = seq(id);
             const uint32_t new_len = s.len + count;
             if (new_len > cfg.max_seq_len) throw std::runtime_error("sequence would reach " + std::to_string(new_len) + " tokens (max " + std::to_string(cfg.max_seq_len) + ")");
-            reserve(id, s.pages, new_len);
+            // With a drafter loaded the draft passes write their own K/V up to VERIFY_T positions past the step.
+            reserve(id, s.pages, drafter ? std::min(new_len + VERIFY_T, cfg.max_seq_len) : new_len);
             const uint32_t first_row = uint32_t(tokens.size());
             tokens.insert(tokens.end(), run.tokens.begin(), run.tokens.end());
             for (uint32_t row = 0; row < count; row++) {
@@ -341,6 +343,7 @@ struct Engine {
         for (uint32_t t = 0; t < n; t++) {
             const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1];
             const uint32_t cpos = meta[2 * (t - row) + 1] + row;  // kernels.metal:74-77 `cache_pos`
+            if (!write_mask.empty() && !write_mask[t]) continue;  // the drafter's passes write the rows that count only
             for (uint32_t g = 0; g < md.n_kv; g++) {
                 std::vector<float> k(qkv + size_t(t) * QW + koff + g * hd, qkv + size_t(t) * QW + koff + (g + 1) * hd);
                 rope_head(k.data(), pos);
@@ -480,6 +483,108 @@ struct Engine {
                         std::copy_n(vc + src, md.hd, vc + dst);
                     }
         }
+    }
+
+    // ---- the chain drafter (a benchmark extension, see `Drafter`)
+    void load_drafter(const std::string& path) {
+        auto dr = std::make_unique<Drafter>();
+        dr->file = VltFile::load(path);
+        const std::vector<float> m = dr->file.f32s("meta");
+        if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw std::runtime_error(path + ": meta is not a version-1 one-layer chain drafter");
+        const uint32_t v = uint32_t(m[3]), d = md.d;
+        if (md.ffn < 2 * d) throw std::runtime_error(path + ": the chain drafter needs ffn >= 2 d_model");
+        dr->fc = load_matrix(dr->file, "fc", d, 2 * d);
+        dr->layer.qkv = load_matrix(dr->file, "D00.qkv", md.qkv_w(), d);
+        dr->layer.o = load_matrix(dr->file, "D00.o", d, md.n_heads * md.hd);
+        dr->layer.gate_up = load_matrix(dr->file, "D00.gate_up", 2 * md.ffn, d);
+        dr->layer.down = load_matrix(dr->file, "D00.down", d, md.ffn);
+        dr->head = load_matrix(dr->file, "head", v, d);
+        for (float id : dr->file.f32s("vocab")) dr->vocab.push_back(uint32_t(id));
+        if (dr->vocab.size() != v) throw std::runtime_error(path + ": vocab has " + std::to_string(dr->vocab.size()) + " ids for a head of " + std::to_string(v));
+        for (uint32_t id : dr->vocab)
+            if (id >= md.vocab) throw std::runtime_error(path + ": draft vocabulary id out of the target's range");
+        const size_t pool = size_t(n_pages) * md.n_kv * md.page * md.hd;
+        dr->k_cache.assign(pool, 0);
+        dr->v_cache.assign(pool, 0);
+        dr->carry.assign(size_t(cfg.max_seqs) * d, 0.0f);
+        drafter = std::move(dr);
+    }
+
+    // The drafter's part of a step, after `forward`: (1) a catch-up pass over the step's own tokens -- input
+    // fc([feature of the position before ; embedding]), the feature being the target's tap of the row before
+    // (the slot's carried tap for a run's first row, zero at position 0) -- that writes the drafter's K/V for
+    // the rows on the accepted path only; (2) rows - 1 draft passes of one row per run: pass i stands at
+    // position lens[slot] + i - 1 on token feed[slot][i - 1], its feature the tap of the path's last row
+    // (i = 1) or the drafter's own normed output of the pass before, and writes feed[slot][i] = the draft
+    // vocabulary's argmax (ties to the lowest index) and tree[slot][i] = chain_node(i).
+    void draft(const Plan& p, uint32_t rows) {
+        if (!drafter) throw std::runtime_error("no drafter loaded");
+        if (rows < 1 || rows > VERIFY_T) throw std::runtime_error("the chain drafter proposes for 1.." + std::to_string(VERIFY_T) + " rows");
+        Drafter& dr = *drafter;
+        const uint32_t d = md.d, n = p.n, nr = p.n_runs, v = dr.head.m;
+        auto feature_in = [&](float* x, const float* feat, uint32_t tok) {
+            for (uint32_t i = 0; i < d; i++) x[i] = feat ? feat[i] : 0.0f;
+            for (uint32_t i = 0; i < d; i++) x[d + i] = bf16_to_f32(embed[size_t(tok) * d + i]);
+        };
+        // (1) catch-up on the step's layout (meta, tin, vis and tiles are still the step's).
+        {
+            std::vector<float> x(size_t(n) * 2 * d), h(size_t(n) * d);
+            for (uint32_t t = 0; t < n; t++) {
+                const uint32_t slot = tin[2 * t], row = tin[2 * t + 1], pos = meta[2 * t + 1];
+                const float* feat = row ? taps.data() + size_t(t - 1) * d : pos ? dr.carry.data() + size_t(slot) * d : nullptr;
+                feature_in(x.data() + size_t(t) * 2 * d, feat, tokens[t]);
+            }
+            matmul_raw(dr.fc, x.data(), n, h.data());
+            write_mask.assign(on_path.begin(), on_path.end());
+            layer_forward(dr.layer, 0, dr.k_cache.data(), dr.v_cache.data(), h.data(), n, p.n_tiles);
+            write_mask.clear();
+        }
+        // The runs that draft: those that emitted this step. Every run with rows on the path carries its last tap over.
+        std::vector<uint32_t> last(nr, NO_TOK);
+        for (uint32_t r = 0; r < nr; r++) {
+            const RunIn& ru = runs[r];
+            if (ru.verify) { if (path_len[r]) last[r] = ru.first + path[r * FEED_W + path_len[r] - 1]; }
+            else if (on_path[ru.first]) last[r] = ru.first + ru.count - 1;
+        }
+        // (2) draft passes on a layout of their own: one row per run.
+        const std::vector<uint32_t> s_meta = meta, s_tin = tin, s_vis = vis, s_tiles = tiles;
+        draft_logits.assign(size_t(rows - 1) * nr * v, 0.0f);
+        std::vector<float> feat(size_t(nr) * d, 0.0f), x(size_t(nr) * 2 * d), h(size_t(nr) * d), inv(nr), lg(size_t(nr) * v);
+        std::vector<uint8_t> live(nr, 0);
+        for (uint32_t i = 1; i < rows; i++) {
+            meta.assign(2 * nr, 0); tin.assign(2 * nr, 0); vis.assign(nr, 1); tiles.clear(); write_mask.assign(nr, 0);
+            for (uint32_t r = 0; r < nr; r++) {
+                const uint32_t slot = runs[r].slot, pos = lens[slot] + i - 1;
+                live[r] = last[r] != NO_TOK && emitted[r] > 0 && pos < cfg.max_seq_len;
+                meta[2 * r] = slot; meta[2 * r + 1] = live[r] ? pos : 0;
+                tin[2 * r] = slot;
+                tiles.push_back(r); tiles.push_back(1);
+                write_mask[r] = live[r];
+                const float* f = i == 1 ? (last[r] != NO_TOK ? taps.data() + size_t(last[r]) * d : nullptr) : feat.data() + size_t(r) * d;
+                feature_in(x.data() + size_t(r) * 2 * d, f, live[r] ? feed[slot * FEED_W + i - 1] : 0);
+            }
+            matmul_raw(dr.fc, x.data(), nr, h.data());
+            layer_forward(dr.layer, 0, dr.k_cache.data(), dr.v_cache.data(), h.data(), nr, nr);
+            inv_rms(h.data(), nr, d, md.eps, inv.data());
+            matmul_raw(dr.head, h.data(), nr, lg.data());
+            for (uint32_t r = 0; r < nr; r++) {
+                float* row = lg.data() + size_t(r) * v;
+                for (uint32_t j = 0; j < v; j++) row[j] *= inv[r];  // EPI_HEAD
+                for (uint32_t j = 0; j < d; j++) feat[size_t(r) * d + j] = round_bf16(h[size_t(r) * d + j] * inv[r]);
+                if (!live[r]) continue;
+                uint32_t best = 0;
+                for (uint32_t j = 1; j < v; j++)
+                    if (row[j] > row[best]) best = j;
+                const uint32_t slot = runs[r].slot;
+                feed[slot * FEED_W + i] = dr.vocab[best];
+                tree[slot * FEED_W + i] = chain_node(i);
+                std::copy_n(row, v, draft_logits.data() + (size_t(i - 1) * nr + r) * v);
+            }
+        }
+        write_mask.clear();
+        meta = s_meta; tin = s_tin; vis = s_vis; tiles = s_tiles;
+        for (uint32_t r = 0; r < nr; r++)
+            if (last[r] != NO_TOK) std::copy_n(taps.data() + size_t(last[r]) * d, d, dr.carry.data() + size_t(runs[r].slot) * d);
     }
 
     // encode.rs:439-451 `encode_replay`.

@@ -288,6 +288,8 @@ int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, con
     });
 }
 
+void vlt_debug_set_draft_rows(VltEngine* e, uint32_t rows) { if (e && e->e) e->e->debug_draft_rows = rows; }
+
 int vlt_debug_mark(VltEngine* e, uint32_t which) { return guard([&] { eng(e).mark(int(which)); }); }
 int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms) { return guard([&] { *ms = eng(e).mark_elapsed_ms(); }); }
 uint64_t vlt_debug_launches(void) { return launch_counter(); }

@@ -289,7 +289,8 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
         Seq& sq = *seqs[id];
         const uint32_t new_len = sq.len + count;
         if (new_len > cfg.max_seq_len) throw Error("sequence would reach " + std::to_string(new_len) + " tokens (max " + std::to_string(cfg.max_seq_len) + ")");
-        kv.reserve(id, sq.pages, new_len);
+        // With a drafter loaded the draft passes write their own K/V up to VERIFY_T positions past the step.
+        kv.reserve(id, sq.pages, drafter ? std::min(new_len + VERIFY_T, cfg.max_seq_len) : new_len);
         const uint32_t first_row = uint32_t(tokens.size());
         tokens.insert(tokens.end(), run.tokens, run.tokens + count);
         for (uint32_t row = 0; row < count; row++) {
@@ -332,6 +333,7 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
     p.n_runs = uint32_t(runs.size());
     p.tiles = uint32_t(tiles.size() / 2);
     p.max_run = max_count;
+    p.max_keys = max_keys;
     attention_split(p, max_keys, p.tiles);
     last_plan_n = n;
     return p;
@@ -340,7 +342,7 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
 // Y = epilogue(W . X) for n tokens: steps of at most 8 tokens stream the weights through the
 // tensor cores from registers; larger ones go in token blocks of 8 (the weights of one matrix
 // stay in L2 between blocks).
-void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out) {
+void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real) {
     MatArgs a{};
     a.W = w.w;
     a.scales = w.scales;
@@ -349,7 +351,7 @@ void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint3
     a.group = w.group;
     a.int8 = w.int8;
     a.epi = epi;
-    a.vocab_real = model.md.vocab_real;
+    a.vocab_real = vocab_real ? vocab_real : model.md.vocab_real;
     a.eps = model.md.eps;
     const uint32_t out_w = epi == EPI_SWIGLU ? w.m / 2 : w.m;
     for (uint32_t t0 = 0; t0 < n; t0 += 8) {
@@ -370,7 +372,8 @@ bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
     return n >= min_rows && n <= 256 && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
 }
 
-void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv) {
+void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
+                         uint32_t vocab_real) {
     MatArgs a{};
     a.W = w.w;
     a.scales = w.scales;
@@ -385,7 +388,7 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
     a.group = w.group;
     a.int8 = w.int8;
     a.epi = epi;
-    a.vocab_real = model.md.vocab_real;
+    a.vocab_real = vocab_real ? vocab_real : model.md.vocab_real;
     a.eps = model.md.eps;
     if (!gemm_supported(a)) throw Error("internal: GEMM asked for an unsupported shape");
     launch_gemm(a, sm_count, s.err_flag.as<uint32_t>(), stream);
@@ -393,10 +396,29 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
 
 // engine/src/engine/encode.rs:142-192 `encode_layer`, a plain decoder's.
 void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
-    const Layer& l = model.layers[li];
-    const ModelDesc& md = model.md;
     StepSet& st = sets[set];
-    const uint32_t n = p.n;
+    LayerIO io{};
+    io.l = &model.layers[li];
+    io.n = p.n;
+    io.meta = s.meta.as<uint32_t>();
+    io.tin = st.in<uint32_t>(st.o_tin);
+    io.tiles = st.in<uint32_t>(st.o_tiles);
+    io.vis = st.in<uint32_t>(st.o_vis);
+    io.n_tiles = p.tiles;
+    io.k_cache = kv.k.as<uint16_t>();
+    io.v_cache = kv.v.as<uint16_t>();
+    io.maps = &attn_maps;
+    io.layer = li;
+    io.keys_per_split = p.keys_per_split;
+    io.max_splits = p.max_splits;
+    encode_layer_io(io);
+}
+
+// The layer on any step layout, weights and cache: the target's layers and the drafter's one.
+void Engine::encode_layer_io(const LayerIO& io) {
+    const Layer& l = *io.l;
+    const ModelDesc& md = model.md;
+    const uint32_t n = io.n, li = io.layer;
     float* h = s.h.as<float>();
     // Steps of 16 tokens or more multiply on tcgen05: activations go in as bf16 copies and 1/rms
     // comes from a row pass, since the GEMM does not see whole rows of X.
@@ -415,33 +437,32 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
     sp = span_begin(G_SMALL);
     if (!(skip & 2))
-        launch_qkv_post(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tin), rope_tab.as<float>(), kv.k.as<uint16_t>(), kv.v.as<uint16_t>(),
-                        kv.page_table.as<uint32_t>(), kva, li, n, md.n_heads, scale_log2, tuning.plain_attention ? nullptr : s.q_b.as<uint16_t>(), stream);
+        launch_qkv_post(s.qkv.as<float>(), io.meta, io.tin, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva, li, n,
+                        md.n_heads, scale_log2, tuning.plain_attention ? nullptr : s.q_b.as<uint16_t>(), io.cpos, stream);
     span_end(sp);
     if (tuning.plain_attention) {
         if (!(skip & 4))
-            launch_attn_plain(s.qkv.as<float>(), s.meta.as<uint32_t>(), st.in<uint32_t>(st.o_tiles), st.in<uint32_t>(st.o_vis), rope_tab.as<float>(),
-                              kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kva, li, p.tiles, md.n_heads, scale_log2,
-                              s.attn.as<float>(), stream);
+            launch_attn_plain(s.qkv.as<float>(), io.meta, io.tiles, io.vis, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva,
+                              li, io.n_tiles, md.n_heads, scale_log2, s.attn.as<float>(), stream);
         if (big) launch_prep_rows(s.attn.as<float>(), nullptr, n, md.n_heads * md.hd, md.eps, nullptr, s.attn_b.as<uint16_t>(), nullptr, false, false, stream);
     } else {
         AttnArgs a{};
-        a.maps = &attn_maps;
+        a.maps = io.maps;
         a.err_flag = s.err_flag.as<uint32_t>();
         a.q_b = s.q_b.as<uint16_t>();
-        a.meta = s.meta.as<uint32_t>();
-        a.tiles = st.in<uint32_t>(st.o_tiles);
-        a.vis = st.in<uint32_t>(st.o_vis);
-        a.k_cache = kv.k.as<uint16_t>();
-        a.v_cache = kv.v.as<uint16_t>();
+        a.meta = io.meta;
+        a.tiles = io.tiles;
+        a.vis = io.vis;
+        a.k_cache = io.k_cache;
+        a.v_cache = io.v_cache;
         a.page_table = kv.page_table.as<uint32_t>();
         a.kv = kva;
         a.layer = li;
-        a.n_tiles = p.tiles;
+        a.n_tiles = io.n_tiles;
         a.n_heads = md.n_heads;
         a.scale_log2 = scale_log2;
-        a.keys_per_split = p.keys_per_split;
-        a.max_splits = p.max_splits;
+        a.keys_per_split = io.keys_per_split;
+        a.max_splits = io.max_splits;
         a.part = s.part.as<float>();
         a.out = s.attn.as<float>();
         a.out_b = big ? s.attn_b.as<uint16_t>() : nullptr;
@@ -556,13 +577,138 @@ void Engine::upload_set(uint32_t set) {
     VLT_CUDA(cudaStreamSynchronize(stream));
 }
 
-void Engine::load_drafter(const std::string& path) { throw Error(path + ": the model drafter is not built yet"); }
-bool Engine::has_drafter() const { return false; }
-void Engine::encode_drafter(uint32_t, const Plan&) {}
+// engine/src/engine.rs:381-389 `load_drafter`, for the chain drafter (see Engine::Drafter).
+void Engine::load_drafter(const std::string& path) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it cannot hold a drafter");
+    for (const auto& q : seqs)
+        if (q) throw Error("load the drafter before the first sequence (it changes how many pages a step reserves)");
+    auto dr = std::make_unique<Drafter>();
+    const ModelDesc& md = model.md;
+    dr->w.load(path, false);
+    const std::vector<float> m = dr->w.f32s("meta");
+    if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw Error(path + ": `meta` is not a version-1 one-layer chain drafter");
+    const uint32_t v = uint32_t(m[3]), d = md.d;
+    if (md.ffn < 2 * d) throw Error(path + ": the chain drafter needs ffn >= 2 d_model");
+    dr->v = v;
+    dr->fc = load_matrix(dr->w, "fc", d, 2 * d);
+    dr->layer.qkv = load_matrix(dr->w, "D00.qkv", md.qkv_w(), d);
+    dr->layer.o = load_matrix(dr->w, "D00.o", d, md.n_heads * md.hd);
+    dr->layer.gate_up = load_matrix(dr->w, "D00.gate_up", 2 * md.ffn, d);
+    dr->layer.down = load_matrix(dr->w, "D00.down", d, md.ffn);
+    dr->head = load_matrix(dr->w, "head", v, d);
+    const std::vector<float> idf = dr->w.f32s("vocab");
+    if (idf.size() != v) throw Error(path + ": `vocab` has " + std::to_string(idf.size()) + " ids for a head of " + std::to_string(v));
+    std::vector<uint32_t> ids(v);
+    for (uint32_t i = 0; i < v; i++) {
+        ids[i] = uint32_t(idf[i]);
+        if (ids[i] >= md.vocab) throw Error(path + ": draft vocabulary id out of the target's range");
+    }
+    const size_t ms = cfg.max_seqs, ms16 = (ms + 15) / 16 * 16, n = cfg.max_step_tokens;
+    dr->vocab_ids.alloc(size_t(v) * 4, false);
+    dr->vocab_ids.write(0, ids.data(), size_t(v) * 4);
+    const size_t pool = size_t(kv.n_pages) * md.n_kv * kv.page * md.hd * 2;  // one layer
+    dr->k.alloc(pool, false);
+    dr->v_cache.alloc(pool, false);
+    attn_maps_init(&dr->maps, dr->k.as<uint16_t>(), dr->v_cache.as<uint16_t>(), uint64_t(kv.n_pages) * md.n_kv * kv.page);
+    dr->carry.alloc(ms * d * 4, false);
+    dr->dfeat.alloc(ms * d * 4, false);
+    dr->dmeta.alloc(ms * 8, false);
+    dr->dtin.alloc(ms * 8, false);
+    dr->dvis.alloc(ms * 4, false);
+    dr->dcpos.alloc(ms * 4, false);
+    dr->live.alloc(ms * 4, false);
+    dr->cpos.alloc(n * 4, false);
+    dr->logits.alloc(size_t(VERIFY_T - 1) * ms * v * 4, false);
+    dr->hfin.alloc(ms * d * 4, false);
+    dr->hfin_b.alloc(ms16 * d * 2, false);
+    dr->inv.alloc(ms * 4, false);
+    std::vector<uint32_t> tiles(2 * ms);
+    for (uint32_t r = 0; r < ms; r++) { tiles[2 * r] = r; tiles[2 * r + 1] = 1; }
+    dr->dtiles.alloc(ms * 8, false);
+    dr->dtiles.write(0, tiles.data(), ms * 8);
+    drafter = std::move(dr);
+    taps_on = true;  // the drafter reads the target's tapped hidden states
+}
+bool Engine::has_drafter() const { return drafter != nullptr; }
+
+// The drafter's part of a step (the reference queues its drafter at the same point,
+// engine/src/engine/generate.rs:427-430): a catch-up pass over the step's own tokens that writes the
+// drafter's K/V for the rows on the accepted path, then rows - 1 draft passes of one row per run.
+void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
+    if (!drafter) throw Error("no drafter loaded");
+    if (rows < 1 || rows > VERIFY_T) throw Error("the chain drafter proposes for 1.." + std::to_string(VERIFY_T) + " rows");
+    Drafter& dr = *drafter;
+    StepSet& st = sets[set];
+    const ModelDesc& md = model.md;
+    const uint32_t d = md.d, n = p.n, nr = p.n_runs;
+    const int sp = span_begin(G_TAIL);
+    float* x = s.act.as<float>();
+    uint16_t* xb = s.act_b.as<uint16_t>();
+    float* h = s.h.as<float>();
+    const RunIn* runs = st.in<RunIn>(st.o_runs);
+    auto fc = [&](uint32_t rows_in) {
+        if (use_gemm(dr.fc, rows_in)) matmul_gemm(dr.fc, rows_in, xb, h, nullptr, EPI_RAW, nullptr, nullptr);
+        else matmul(dr.fc, rows_in, x, h, EPI_RAW, nullptr, nullptr);
+    };
+    LayerIO io{};
+    io.l = &dr.layer;
+    io.layer = 0;
+    io.k_cache = dr.k.as<uint16_t>();
+    io.v_cache = dr.v_cache.as<uint16_t>();
+    io.maps = &dr.maps;
+    // (1) catch-up, on the step's own layout.
+    launch_draft_catchup_in(st.in<uint32_t>(st.o_tokens), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), s.taps.as<float>(),
+                            dr.carry.as<float>(), model.embed, n, d, x, xb, dr.cpos.as<uint32_t>(), stream);
+    fc(n);
+    io.n = n;
+    io.meta = s.meta.as<uint32_t>();
+    io.tin = st.in<uint32_t>(st.o_tin);
+    io.tiles = st.in<uint32_t>(st.o_tiles);
+    io.vis = st.in<uint32_t>(st.o_vis);
+    io.n_tiles = p.tiles;
+    io.cpos = dr.cpos.as<uint32_t>();
+    io.keys_per_split = p.keys_per_split;
+    io.max_splits = p.max_splits;
+    encode_layer_io(io);
+    // (2) the draft passes, one row per run.
+    Plan dp;
+    dp.n = nr;
+    attention_split(dp, std::min(p.max_keys + VERIFY_T, cfg.max_seq_len), nr);
+    io.n = nr;
+    io.meta = dr.dmeta.as<uint32_t>();
+    io.tin = dr.dtin.as<uint32_t>();
+    io.tiles = dr.dtiles.as<uint32_t>();
+    io.vis = dr.dvis.as<uint32_t>();
+    io.n_tiles = nr;
+    io.cpos = dr.dcpos.as<uint32_t>();
+    io.keys_per_split = dp.keys_per_split;
+    io.max_splits = dp.max_splits;
+    for (uint32_t i = 1; i < rows; i++) {
+        launch_draft_pass_in(runs, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(),
+                             st.out<uint32_t>(st.o_emitted), s.taps.as<float>(), dr.dfeat.as<float>(), model.embed, nr, d, i, cfg.max_seq_len, x, xb,
+                             dr.dmeta.as<uint32_t>(), dr.dtin.as<uint32_t>(), dr.dvis.as<uint32_t>(), dr.dcpos.as<uint32_t>(), dr.live.as<uint32_t>(), stream);
+        fc(nr);
+        encode_layer_io(io);
+        // The pass's normed output is the next pass's feature (rounded like a tap); the head reads the raw rows and 1/rms.
+        launch_prep_rows(h, nullptr, nr, d, md.eps, dr.dfeat.as<float>(), nullptr, nullptr, true, true, stream);
+        float* lg = dr.logits.as<float>() + size_t(i - 1) * cfg.max_seqs * dr.v;
+        if (use_gemm(dr.head, nr)) {
+            launch_prep_rows(h, nullptr, nr, d, md.eps, nullptr, dr.hfin_b.as<uint16_t>(), dr.inv.as<float>(), false, false, stream);
+            matmul_gemm(dr.head, nr, dr.hfin_b.as<uint16_t>(), lg, nullptr, EPI_HEAD, nullptr, dr.inv.as<float>(), dr.v);
+        } else {
+            launch_prep_rows(h, nullptr, nr, d, md.eps, dr.hfin.as<float>(), nullptr, nullptr, false, false, stream);
+            matmul(dr.head, nr, dr.hfin.as<float>(), lg, EPI_HEAD, nullptr, nullptr, dr.v);
+        }
+        launch_draft_pick(lg, dr.v, dr.vocab_ids.as<uint32_t>(), runs, dr.live.as<uint32_t>(), nr, i, s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), stream);
+    }
+    launch_draft_carry(runs, s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(), s.taps.as<float>(), nr, d, dr.carry.as<float>(), stream);
+    span_end(sp);
+}
 
 StepOutput Engine::step_runs(const std::vector<PlanRun>& runs, const StepOptions& opts, const ReplayArgs* replay) {
     Plan p = plan(0, runs, opts.hidden);
     encode_forward(0, p);
+    if (debug_draft_rows && drafter) encode_drafter(0, p, debug_draft_rows);
     if (replay) encode_replay(0, p, *replay);
     commit(0);
     StepOutput out;
@@ -775,6 +921,13 @@ std::vector<uint32_t> Engine::debug_read(const std::string& name) {
     if (name == "meta") return whole(s.meta, 2 * size_t(last_plan_n));
     if (name == "page_table") return whole(kv.page_table, ms * kv.max_pages);
     if (name == "free_pages") return kv.free_pages;
+    if (drafter) {
+        const size_t pool = size_t(kv.n_pages) * model.md.n_kv * kv.page * model.md.hd;
+        if (name == "draft_logits") return whole(drafter->logits, size_t(VERIFY_T - 1) * ms * drafter->v);  // [pass][run slot][v] f32
+        if (name == "carry") return whole(drafter->carry, ms * model.md.d);
+        if (name == "draft_k_cache") return whole(drafter->k, pool / 2);  // bf16 pairs
+        if (name == "draft_v_cache") return whole(drafter->v_cache, pool / 2);
+    }
     const StepSet& st = sets[0];
     auto in = [&](size_t off, size_t words) {
         std::vector<uint32_t> v(words);

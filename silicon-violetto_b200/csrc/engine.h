@@ -52,6 +52,7 @@ struct Plan {
     uint32_t n = 0, n_head = 0, n_hidden = 0, n_runs = 0, tiles = 0, max_run = 0;
     bool branches = false;
     uint32_t keys_per_split = 0, max_splits = 1;  // the attention's key split
+    uint32_t max_keys = 0;                        // the longest run's keys
 };
 
 struct Seq {
@@ -118,7 +119,8 @@ class Engine {
     void upload_set(uint32_t set);
     void load_drafter(const std::string& path);
     bool has_drafter() const;
-    void encode_drafter(uint32_t set, const Plan& p);
+    void encode_drafter(uint32_t set, const Plan& p, uint32_t rows);  // after encode_forward: catch-up, then rows - 1 draft passes
+    uint32_t debug_draft_rows = 0;  // step_runs runs the drafter for this many rows (tests)
     void set_taps(bool on);
     void bench_fill(uint32_t id, uint32_t len, uint32_t seed);
     std::vector<uint32_t> sample_logits(const float* logits, const std::vector<std::pair<Sampling, uint32_t>>& rows);
@@ -168,14 +170,37 @@ class Engine {
     Buffer rope_tab;
     Buffer spec_p, spec_q, spec_small;  // spec_accept's device copies, grown on demand
     AttnMaps attn_maps;
+    // The chain drafter (a benchmark extension; the reference's drafter.rs is a block drafter): fc over
+    // (feature ; embedding), one decoder layer with a cache of its own on the target's page table, a head
+    // over a draft vocabulary.
+    struct Drafter {
+        Weights w;
+        Matrix fc, head;
+        Layer layer;
+        uint32_t v = 0;
+        Buffer vocab_ids, k, v_cache, carry, dfeat, dmeta, dtin, dvis, dcpos, dtiles, live, cpos, logits, hfin, hfin_b, inv;
+        AttnMaps maps;
+    };
+    std::unique_ptr<Drafter> drafter;
 
   private:
     KvArgs kv_args() const;
-    void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out);
+    void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real = 0);
     // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
-    void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv);
+    void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
+                     uint32_t vocab_real = 0);
     bool use_gemm(const Matrix& w, uint32_t n) const;
+    // What a decoder layer runs on: its weights, the step layout (device arrays), the cache it writes and reads.
+    struct LayerIO {
+        const Layer* l;
+        uint32_t n, n_tiles, layer, keys_per_split, max_splits;
+        const uint32_t *meta, *tin, *tiles, *vis;
+        const uint32_t* cpos;  // optional, per token: the cache position its K/V go to (NO_TOK: nowhere); NULL: its run's first position + its row
+        uint16_t *k_cache, *v_cache;
+        const AttnMaps* maps;
+    };
     void encode_layer(uint32_t set, const Plan& p, uint32_t li);
+    void encode_layer_io(const LayerIO& io);
     void encode_tail(uint32_t set, const Plan& p);
     void encode_sample(uint32_t set, uint32_t rows);
     void attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const;

@@ -214,7 +214,12 @@ std::optional<Generator::InFlight> Generator::encode_next() {
     const Plan plan = eng.plan(set, runs, Rows::None);
     const auto t0 = std::chrono::steady_clock::now();
     eng.encode_forward(set, plan);
-    if (modeled) eng.encode_drafter(set, plan);
+    if (modeled) {
+        uint32_t drows = 1;
+        for (const Active& a : active)
+            if (a.model) drows = std::max(drows, std::min(a.rows, VERIFY_T));
+        eng.encode_drafter(set, plan, drows);
+    }
     if (replay) eng.encode_replay(set, plan, ReplayArgs{cfg.max_seq_len, replay_seed, replay_rate, eng.model.md.vocab_real});
     eng.commit(set);
     f.set = set;

@@ -1,0 +1,128 @@
+// The chain drafter's own kernels (its matmuls, attention and K/V writes are the target's).
+// Not in the reference, whose drafter is a block drafter with a draft tree
+// (engine/src/engine/drafter.rs:278-447); this one keeps that drafter's interface: it reads the
+// tapped hidden states of the rows on the accepted path (kernels.metal:133-148), `lens` and
+// `feed[slot][0]` after `accept`, and writes its drafts to `feed[slot][1..]` and chain nodes to
+// `tree[slot][1..]` (kernels.metal:51-60), all on the device, in the same step.
+#include <cfloat>
+
+#include "kernels.h"
+
+namespace vlt {
+
+// One input row of the drafter: [feature (d) ; embedding of `tok` (d)], as fp32 and as bf16 (both exact:
+// features and embeddings are bf16 values).
+__device__ __forceinline__ void draft_row_in(const float* feat, const uint16_t* emb, uint32_t d, float* x, uint16_t* xb) {
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float f = feat ? feat[i] : 0.0f;
+        x[i] = f;
+        xb[i] = f32_to_bf16(f);
+        x[d + i] = bf16_to_f32(emb[i]);
+        xb[d + i] = emb[i];
+    }
+}
+
+// The catch-up pass's inputs, one block per step token: the feature of the position before is the tap
+// of the row before, or for a run's first row the slot's carried tap (zero at position 0). Rows off the
+// accepted path keep their K/V out of the drafter's cache (cpos = NO_TOK).
+__global__ void draft_catchup_in_kernel(const uint32_t* __restrict__ tokens, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ meta,
+                                        const uint32_t* __restrict__ on_path, const float* __restrict__ taps, const float* __restrict__ carry,
+                                        const uint16_t* __restrict__ embed, uint32_t d, float* x, uint16_t* xb, uint32_t* cpos) {
+    const uint32_t t = blockIdx.x, slot = tin[2 * t], row = tin[2 * t + 1], pos = meta[2 * t + 1];
+    const float* feat = row ? taps + size_t(t - 1) * d : pos ? carry + size_t(slot) * d : nullptr;
+    draft_row_in(feat, embed + size_t(tokens[t]) * d, d, x + size_t(t) * 2 * d, xb + size_t(t) * 2 * d);
+    if (threadIdx.x == 0) cpos[t] = on_path[t] ? pos : NO_TOK;
+}
+
+// The last row of run r on the accepted path (NO_TOK: none): a verify run's path end, any other run's last row.
+__device__ __forceinline__ uint32_t draft_last_row(const RunIn& ru, uint32_t r, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path) {
+    if (ru.verify) return path_len[r] ? ru.first + path[r * FEED_W + path_len[r] - 1] : NO_TOK;
+    return on_path[ru.first] ? ru.first + ru.count - 1 : NO_TOK;
+}
+
+// Draft pass i (1-based), one block per run: the row stands at position lens[slot] + i - 1 on token
+// feed[slot][i - 1]; its feature is the tap of the path's last row (i = 1) or the drafter's own normed
+// output of the pass before. Writes the pass's step layout (meta, tin, vis, cpos) and whether the run drafts.
+__global__ void draft_pass_in_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ lens, const uint32_t* __restrict__ feed,
+                                     const uint32_t* __restrict__ path, const uint32_t* __restrict__ path_len, const uint32_t* __restrict__ on_path,
+                                     const uint32_t* __restrict__ emitted, const float* __restrict__ taps, const float* __restrict__ dfeat,
+                                     const uint16_t* __restrict__ embed, uint32_t d, uint32_t i, uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta,
+                                     uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live) {
+    const uint32_t r = blockIdx.x;
+    const RunIn ru = runs[r];
+    const uint32_t last = draft_last_row(ru, r, path, path_len, on_path);
+    const uint32_t pos = lens[ru.slot] + i - 1;
+    const bool lv = last != NO_TOK && emitted[r] > 0 && pos < max_seq_len;
+    const float* feat = i == 1 ? (last != NO_TOK ? taps + size_t(last) * d : nullptr) : dfeat + size_t(r) * d;
+    const uint32_t tok = lv ? feed[ru.slot * FEED_W + i - 1] : 0u;
+    draft_row_in(feat, embed + size_t(tok) * d, d, x + size_t(r) * 2 * d, xb + size_t(r) * 2 * d);
+    if (threadIdx.x == 0) {
+        dmeta[2 * r] = ru.slot;
+        dmeta[2 * r + 1] = lv ? pos : 0u;
+        dtin[2 * r] = ru.slot;
+        dtin[2 * r + 1] = 0;
+        dvis[r] = 1;
+        dcpos[r] = lv ? pos : NO_TOK;
+        live[r] = lv ? 1u : 0u;
+    }
+}
+
+// The slot's carried tap for the next step's catch-up: the tap of the path's last row.
+__global__ void draft_carry_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ path, const uint32_t* __restrict__ path_len,
+                                   const uint32_t* __restrict__ on_path, const float* __restrict__ taps, uint32_t d, float* carry) {
+    const uint32_t r = blockIdx.x;
+    const RunIn ru = runs[r];
+    const uint32_t last = draft_last_row(ru, r, path, path_len, on_path);
+    if (last == NO_TOK) return;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) carry[size_t(ru.slot) * d + i] = taps[size_t(last) * d + i];
+}
+
+// The pass's drafts, one block per run: the draft vocabulary's argmax (ties to the lowest index), mapped
+// to the target's id, into feed[slot][i]; tree[slot][i] = chain_node(i).
+__global__ void __launch_bounds__(256) draft_pick_kernel(const float* __restrict__ logits, uint32_t v, const uint32_t* __restrict__ vocab_ids,
+                                                         const RunIn* __restrict__ runs, const uint32_t* __restrict__ live, uint32_t i, uint32_t* feed,
+                                                         uint32_t* tree) {
+    __shared__ float bv[8];
+    __shared__ uint32_t bi[8];
+    const uint32_t r = blockIdx.x, tid = threadIdx.x;
+    if (!live[r]) return;
+    const float* row = logits + size_t(r) * v;
+    float mx = -FLT_MAX;
+    uint32_t am = 0xffffffffu;
+    for (uint32_t j = tid; j < v; j += 256) better(mx, am, row[j], j);
+    warp_best(mx, am);
+    if (tid % 32 == 0) { bv[tid / 32] = mx; bi[tid / 32] = am; }
+    __syncthreads();
+    if (tid == 0) {
+        for (uint32_t w = 1; w < 8; w++) better(mx, am, bv[w], bi[w]);
+        const uint32_t slot = runs[r].slot;
+        feed[slot * FEED_W + i] = vocab_ids[am < v ? am : 0];
+        tree[slot * FEED_W + i] = d_chain_node(i);
+    }
+}
+
+void launch_draft_catchup_in(const uint32_t* tokens, const uint32_t* tin, const uint32_t* meta, const uint32_t* on_path, const float* taps, const float* carry,
+                             const uint16_t* embed, uint32_t n, uint32_t d, float* x, uint16_t* xb, uint32_t* cpos, cudaStream_t s) {
+    draft_catchup_in_kernel<<<n, 256, 0, s>>>(tokens, tin, meta, on_path, taps, carry, embed, d, x, xb, cpos);
+    launch_counter()++;
+}
+void launch_draft_pass_in(const RunIn* runs, const uint32_t* lens, const uint32_t* feed, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path,
+                          const uint32_t* emitted, const float* taps, const float* dfeat, const uint16_t* embed, uint32_t n_runs, uint32_t d, uint32_t i,
+                          uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live,
+                          cudaStream_t s) {
+    draft_pass_in_kernel<<<n_runs, 256, 0, s>>>(runs, lens, feed, path, path_len, on_path, emitted, taps, dfeat, embed, d, i, max_seq_len, x, xb, dmeta, dtin,
+                                                dvis, dcpos, live);
+    launch_counter()++;
+}
+void launch_draft_carry(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path, const float* taps, uint32_t n_runs,
+                        uint32_t d, float* carry, cudaStream_t s) {
+    draft_carry_kernel<<<n_runs, 256, 0, s>>>(runs, path, path_len, on_path, taps, d, carry);
+    launch_counter()++;
+}
+void launch_draft_pick(const float* logits, uint32_t v, const uint32_t* vocab_ids, const RunIn* runs, const uint32_t* live, uint32_t n_runs, uint32_t i,
+                       uint32_t* feed, uint32_t* tree, cudaStream_t s) {
+    draft_pick_kernel<<<n_runs, 256, 0, s>>>(logits, v, vocab_ids, runs, live, i, feed, tree);
+    launch_counter()++;
+}
+
+}  // namespace vlt

@@ -54,10 +54,10 @@ void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uin
 // folded in, rounded to bf16 (kernels.metal:776-789 does this for q in the same kernel).
 __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin,
                                 const float* __restrict__ rope, uint16_t* k_cache, uint16_t* v_cache, const uint32_t* __restrict__ page_table,
-                                KvArgs kv, uint32_t layer, uint32_t n_heads, float scale_log2, uint32_t* __restrict__ q_b) {
+                                KvArgs kv, uint32_t layer, uint32_t n_heads, float scale_log2, uint32_t* __restrict__ q_b, const uint32_t* __restrict__ cpos_in) {
     const uint32_t t = blockIdx.x, g = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1];
-    const uint32_t cpos = meta[2 * (t - row) + 1] + row;
+    const uint32_t cpos = cpos_in ? cpos_in[t] : meta[2 * (t - row) + 1] + row;
     const uint32_t qw = (n_heads + 2 * kv.n_kv) * kv.hd;
     const float* kp = qkv + size_t(t) * qw + size_t(n_heads) * kv.hd + g * kv.hd;
     const float* vp = kp + size_t(kv.n_kv) * kv.hd;
@@ -66,9 +66,11 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* _
     const float2 v = reinterpret_cast<const float2*>(vp)[lane];
     const float r0 = __fadd_rn(__fmul_rn(cs.x, k.x), __fmul_rn(cs.y, k.y));
     const float r1 = __fsub_rn(__fmul_rn(cs.x, k.y), __fmul_rn(cs.y, k.x));
-    const size_t at = kv_row(kv, layer, page_table, slot, g, cpos);
-    reinterpret_cast<uint32_t*>(k_cache + at)[lane] = pack_bf16(r0, r1);
-    reinterpret_cast<uint32_t*>(v_cache + at)[lane] = pack_bf16(v.x, v.y);
+    if (cpos != NO_TOK) {  // (the drafter's passes leave out the rows that are not on the accepted path)
+        const size_t at = kv_row(kv, layer, page_table, slot, g, cpos);
+        reinterpret_cast<uint32_t*>(k_cache + at)[lane] = pack_bf16(r0, r1);
+        reinterpret_cast<uint32_t*>(v_cache + at)[lane] = pack_bf16(v.x, v.y);
+    }
     if (q_b) {
         for (uint32_t h = g; h < n_heads; h += kv.n_kv) {
             const float2 q = reinterpret_cast<const float2*>(qkv + size_t(t) * qw + h * kv.hd)[lane];
@@ -80,8 +82,8 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* _
 }
 
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
-                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, cudaStream_t s) {
-    { qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads, scale_log2, reinterpret_cast<uint32_t*>(q_b)); launch_counter()++; }
+                     const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, const uint32_t* cpos, cudaStream_t s) {
+    { qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads, scale_log2, reinterpret_cast<uint32_t*>(q_b), cpos); launch_counter()++; }
 }
 
 // ----------------------------------------------- scalar attention (cross-check)

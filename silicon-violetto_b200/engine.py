@@ -223,6 +223,10 @@ class Engine:
     def load_drafter(self, path) -> None:
         _check(lib().vlt_load_drafter(self.h, str(path).encode()))
 
+    def set_draft_rows(self, rows: int) -> None:
+        """debug_step then runs the loaded drafter for `rows` rows (rows - 1 drafts) after each step; 0: not."""
+        lib().vlt_debug_set_draft_rows(self.h, C.c_uint32(rows))
+
     def has_drafter(self) -> bool:
         return bool(lib().vlt_has_drafter(self.h))
 
