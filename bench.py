@@ -93,6 +93,19 @@ KV_BYTES_PER_TOKEN_LAYER = 8 * 64 * 2 * 2  # 8 kv heads x 64 dims x bf16 x (K, V
 WEIGHT_PARAMS = 16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048
 
 
+def drafter_file(rank: int) -> Path:
+    """The chain drafter of the 1B target (fc, one layer, a head over 16384 draft ids), int8 per row, random-init."""
+    from silicon_violetto_b200 import synth
+    path = CACHE / "1b_drafter_int8row.vlt"
+    done = path.with_suffix(".ok")
+    if rank == 0 and not done.exists():
+        synth.write_drafter(path, "1b", seed=100, int8_group=0, draft_vocab=16384)
+        done.write_text("ok")
+    while not done.exists():
+        time.sleep(0.5)
+    return path
+
+
 def make_engine(E, path, streams, ctx, steps_total, device, attn_keys=0):
     room = ROWS * (steps_total + 8) + 64
     cfg = E.EngineConfig(max_seqs=streams, max_step_tokens=max(streams * ROWS, 64), max_chunk=16, global_kv_tokens=streams * (ctx + room + 16),
@@ -122,17 +135,21 @@ def record_plain(E, eng, streams, ctx, n_tokens, rank, sampling):
     return out
 
 
-def run_replica(args, rank, world, barrier, device, eng, mistakes):
-    """One timed pass: `warmup` + `steps` verify steps of every stream, drafts from the replay drafter."""
+def run_replica(args, rank, world, barrier, device, eng, mistakes, model_drafter=False):
+    """One timed pass: `warmup` + `steps` verify steps of every stream, drafts from the replay drafter
+    (or, with `model_drafter`, from the loaded chain drafter)."""
     from silicon_violetto_b200 import engine as E
     total_steps = args.warmup + args.steps + 6
     sampling = lambda j: E.Sampling(args.temperature, 0.95, stream_seeds(rank, j)[1])
     n_rec = ROWS * total_steps + 8
-    recorded = record_plain(E, eng, args.streams, args.ctx, n_rec, rank, sampling) if mistakes < 1.0 else [[0] * n_rec] * args.streams
+    recorded = record_plain(E, eng, args.streams, args.ctx, n_rec, rank, sampling) if mistakes < 1.0 and not model_drafter else [[0] * n_rec] * args.streams
     seqs = fill(eng, args.streams, args.ctx, rank)
     g = eng.generator()
     g.set_replay_mistakes(mistakes, 1)
     for j, s in enumerate(seqs):
+        if model_drafter:
+            g.submit(E.Request(("resume", s, 100 + j), n_rec - 2, sampling=sampling(j), draft=E.Draft.MODEL, rows=ROWS))
+            continue
         trace = [0] * args.ctx + [100 + j] + recorded[j]
         g.submit(E.Request(("resume", s, 100 + j), n_rec - 2, sampling=sampling(j), draft=E.Draft.REPLAY, rows=ROWS, trace=trace))
     with Clocks(device) as clocks:  # nvidia-smi needs a moment to start: it samples from the warm-up on
@@ -230,6 +247,8 @@ def main():
     ap.add_argument("--cpu-streams", type=int, default=8, help="streams of the CPU sample")
     ap.add_argument("--cpu-steps", type=int, default=10, help="timed verify steps of the CPU sample (the reference arm takes --steps, at most 20)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--also-streams", default="1", help="comma list: extra passes at these stream counts on rank 0's engine (BASELINE quotes 1 and 32 streams); empty: none")
+    ap.add_argument("--no-model-drafter", action="store_true", help="skip the pass with the chain drafter loaded")
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
     args = ap.parse_args()
@@ -308,6 +327,32 @@ def main():
     if extra is not None:
         out["replay_pass"] = {"mistakes": args.replay_mistakes, "value": extra["emitted"] / (extra["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)",
                               "mean_accepted_len": extra["emitted"] / (steps * args.streams), "ms_per_step": extra["dev_ms"] / steps}
+    import copy
+    if not args.layers:
+        for n_s in [int(x) for x in args.also_streams.split(",") if x.strip()]:
+            if n_s >= args.streams:
+                continue
+            a2 = copy.copy(args)
+            a2.streams = n_s
+            e2, _ = make_engine(E, path, n_s, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
+            r2 = run_replica(a2, rank, 1, lambda: torch.cuda.synchronize(local), local, e2, args.replay_mistakes)
+            r1 = run_replica(a2, rank, 1, lambda: torch.cuda.synchronize(local), local, e2, 1.0)
+            out[f"streams_{n_s}"] = {"value": r1["emitted"] / (r1["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r1["dev_ms"] / steps,
+                                     "e2e": r1["emitted"] / r1["wall"], "mean_accepted_len": r1["emitted"] / (steps * n_s),
+                                     "replay_pass": {"mistakes": args.replay_mistakes, "value": r2["emitted"] / (r2["dev_ms"] * 1e-3),
+                                                     "mean_accepted_len": r2["emitted"] / (steps * n_s), "ms_per_step": r2["dev_ms"] / steps},
+                                     "kernel_groups_ms_per_step": {k: v["ms"] / r1["prof_steps"] for k, v in r1["prof"].items()}}
+            e2.close()
+    if not args.layers and not args.no_model_drafter and not args.bf16:
+        eng.close()
+        e3, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
+        e3.load_drafter(drafter_file(0))
+        r3 = run_replica(args, rank, 1, lambda: torch.cuda.synchronize(local), local, e3, 1.0, model_drafter=True)
+        out["model_drafter_pass"] = {"value": r3["emitted"] / (r3["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r3["dev_ms"] / steps,
+                                     "mean_accepted_len": r3["emitted"] / (steps * args.streams),
+                                     "drafter": "chain drafter, 1 layer + fc + head over 16384 draft ids, int8, random-init (its drafts are never right)",
+                                     "kernel_groups_ms_per_step": {k: v["ms"] / r3["prof_steps"] for k, v in r3["prof"].items()}}
+        e3.close()
     if world == 1 and not args.no_cpu:
         eng.close()
         t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)

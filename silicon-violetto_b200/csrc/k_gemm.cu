@@ -240,8 +240,6 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (tid >= FIRST_CONV * 32)
-        for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -251,6 +249,11 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    // Programmatic dependent launch: the kernel queued behind this one may start its own set-up and weight
+    // loads now; and this one, if it was started that way, has touched nothing yet that the kernel before it
+    // writes -- the weights' loader, the converters and the MMA issuer never do, the activations' loader and
+    // the epilogue warps wait for that kernel first (griddepcontrol.wait).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // The loops below keep their stage index and phase bit by increment: a thread that feeds the tensor
     // core runs alone in its warp, and every division or descriptor rebuilt per k block is on the critical path.
@@ -273,6 +276,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     } else if (warp == 2) {
         // The activations' loader (they come from L2: every block reads the same rows).
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t c = 0, ph = 1;
             for (uint32_t i = 0; i < nkb; i++) {
                 ok = wait_or_abort(bar_bempty + 8 * c, ph, abort_flag);
@@ -404,6 +408,9 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     };
 
     if (warp >= FIRST_CONV) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * CONV_WARPS) : "memory");  // the epilogue warps only
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -579,13 +586,15 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     cfg.blockDim = dim3(gemm::THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the kernel before it drains
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = splits > 1 ? 1 : 0;
+    cfg.numAttrs = splits > 1 ? 2 : 1;
     VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm_entry(a.int8, a.epi), it->second, g));
     launch_counter()++;
 #ifdef VLT_GEMM_PROBE

@@ -177,6 +177,7 @@ void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* t
 // One block of 64 threads per (token, head).
 // Splits past a tile's keys hold m = -inf (the attention kernel writes every slot).
 __global__ void attn_combine_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out, uint16_t* out_b) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a GEMM queued behind may start loading its weights
     const uint32_t t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const float* pp = part + (size_t(t) * n_heads + h) * max_splits * ATTN_PART;
     float mm = -INFINITY;
@@ -205,6 +206,7 @@ void launch_attn_combine(const AttnArgs& a, cudaStream_t s) {
 __global__ void prep_rows_kernel(const float* __restrict__ in, const uint32_t* __restrict__ rows, uint32_t k, float eps, float* out_f32,
                                  uint16_t* out_bf16, float* inv, bool normalize, bool round_out) {
     __shared__ float red[8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a GEMM queued behind may start loading its weights
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
     const float* x = in + size_t(rows ? rows[r] : r) * k;
     float ss = 0.0f;
