@@ -128,4 +128,24 @@ struct Buffer {
     }
 };
 
+#ifdef __CUDACC__
+// A launch with programmatic stream serialization: the kernel may be scheduled while the one before it
+// still runs; it must call pdl_start() before touching anything (every kernel launched this way does).
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VLT_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    launch_counter()++;
+}
+#endif
+
 }  // namespace vlt

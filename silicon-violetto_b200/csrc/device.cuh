@@ -62,6 +62,13 @@ constexpr float LOG2E = 1.44269504088896340736f;
 
 // kernels.metal:64-72.
 __device__ __forceinline__ uint32_t d_tree_node(uint32_t depth, uint32_t parent, uint32_t sees) { return depth | parent << 8 | sees << 16; }
+// Programmatic dependent launch, first thing in a kernel started that way: let the kernel queued behind
+// this one be scheduled early (it waits in turn), then wait for the kernel before this one to complete.
+// From here on everything is ordered as if the kernels ran one after another; only launch latency overlaps.
+__device__ __forceinline__ void pdl_start() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ uint32_t d_chain_node(uint32_t row) { return d_tree_node(row, row == 0 ? 0xffu : row - 1, (2u << row) - 1u); }
 __device__ __forceinline__ uint32_t d_dead_node(uint32_t row) { return d_tree_node(1, 0xffu, 1u | 1u << row); }
 __device__ __forceinline__ uint32_t node_depth(uint32_t n) { return n & 0xffu; }

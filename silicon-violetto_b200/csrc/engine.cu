@@ -237,13 +237,13 @@ KvArgs Engine::kv_args() const {
 }
 
 // How the cached keys are split across attention blocks (the reference's decode_splits,
-// engine/src/engine/plan.rs:153-163, re-derived for this GPU): blocks of 4 warps, three per SM.
+// engine/src/engine/plan.rs:153-163, re-derived for this GPU): blocks of 4 warps, four per SM.
 // A block costs its warps' pages plus a fixed part (loading q, merging and writing the partial)
 // worth about six pages; the split count with the lowest waves x block cost wins.
 void Engine::attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const {
     const uint32_t page = model.md.page, unit = 4 * page;  // a block's four warps take a page each
     const uint32_t cap = std::min<uint32_t>(std::max<uint32_t>(cfg.max_step_tokens * 16 / std::max(p.n, 1u), 1u), 64u);  // plan.rs:127
-    const uint32_t slots = 3 * sm_count, base = std::max(n_tiles * model.md.n_kv, 1u);
+    const uint32_t slots = 4 * sm_count, base = std::max(n_tiles * model.md.n_kv, 1u);
     uint32_t best = 1;
     if (tuning.attn_keys_per_cta) {
         best = std::max(1u, (max_keys + tuning.attn_keys_per_cta - 1) / tuning.attn_keys_per_cta);

@@ -12,7 +12,7 @@
 //     scores, kernels.metal:803-806), and partials carry (m, l, o[64]);
 //   - the step's own rows are already in the cache (written by qkv_post), so they are read like
 //     any other key and only the pages at or past the run's first position are masked.
-// grid (splits, kv heads, tiles), 4 warps; warp w takes pages w, w + 4, ... of its split.
+// grid (kv heads, splits, tiles), 4 warps; warp w takes pages w, w + 4, ... of its split.
 #include <cuda.h>
 
 #include "kernels.h"
@@ -20,7 +20,7 @@
 namespace vlt {
 
 static constexpr int ATTN_WARPS = 4;
-static constexpr int ATTN_STAGES = 4;
+static constexpr int ATTN_STAGES = 3;
 static constexpr uint32_t PAGE = 16, HD = 64;
 static constexpr uint32_t STAGE_BYTES = 2 * PAGE * HD * 2;  // K then V
 static constexpr uint32_t SPIN_LIMIT = 1u << 24;
@@ -66,14 +66,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // MT: m16 tiles of query columns (T * G <= 16 MT).
 template <int MT>
-__global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
+__global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
+    pdl_start();
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4..9.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t bars[ATTN_WARPS][ATTN_STAGES];
-    __shared__ uint4 qs[MT * 16 * 8];
+    __shared__ __align__(128) uint4 qs[MT * 16 * 8];  // 128-byte aligned: fragment addresses below differ by an XOR of address bits 5..6
 
-    const uint32_t split = blockIdx.x, kvh = blockIdx.y, tile = blockIdx.z;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, tile = blockIdx.z;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const uint32_t G = a.n_heads / a.kv.n_kv;
     const uint32_t t0 = a.tiles[2 * tile], T = a.tiles[2 * tile + 1];
@@ -145,22 +146,20 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
     };
     for (uint32_t i = 0; i < min(my_pages, uint32_t(ATTN_STAGES)); i++) issue(i);
 
-    // Q as A operands (a0: rows g, dims lo; a1: rows g + 8, lo; a2: g, hi; a3: g + 8, hi), and
-    // the visibility masks of this lane's rows g and g + 8.
+    // Q as A operands (a0: rows g, dims lo; a1: rows g + 8, lo; a2: g, hi; a3: g + 8, hi) are read from
+    // shared memory for every page (keeping the 8 MT fragments in registers would cost a block per SM), and
+    // the visibility masks of this lane's rows g and g + 8 stay in registers.
     const uint32_t lm = lane >> 3, lr = lane & 7;  // ldmatrix: lane -> (matrix, row)
-    uint32_t qf[MT][4][4];
+    uint32_t q_addr[MT];  // fragment (mt, ks) is at q_addr[mt] ^ (ks << 5): the swizzle is an XOR of the 16-byte chunk index
     uint32_t vmask[MT][2];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            const uint32_t p = mt * 16 + 8 * (lm & 1) + lr, chunk = 2 * ks + (lm >> 1);
-            ldmatrix_x4(qf[mt][ks], smem_u32(&qs[p * 8 + (chunk ^ (p & 7))]));
-        }
+        const uint32_t p = mt * 16 + 8 * (lm & 1) + lr;
+        q_addr[mt] = smem_u32(&qs[p * 8 + ((lm >> 1) ^ (p & 7))]);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-            const uint32_t p = mt * 16 + g + 8 * half;
-            vmask[mt][half] = p < n_cols ? a.vis[t0 + p / G] : 0xffffffffu;
+            const uint32_t pr = mt * 16 + g + 8 * half;
+            vmask[mt][half] = pr < n_cols ? a.vis[t0 + pr / G] : 0xffffffffu;
         }
     }
 
@@ -176,6 +175,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
         l_run[mt][0] = l_run[mt][1] = 0.0f;
     }
 
+    // This lane's ldmatrix row within a page (stages are 1024-byte aligned, rows 128 bytes: the swizzled
+    // 16-byte chunk index is address bits 4..6, so the k step / dim pair is an XOR away).
+    const uint32_t k_off = (8 * (lm >> 1) + lr) * 128 + (((lm & 1) ^ lr) << 4);
+    const uint32_t v_off = (8 * (lm & 1) + lr) * 128 + (((lm >> 1) ^ lr) << 4);
     bool failed = false;
     for (uint32_t i = 0; i < my_pages; i++) {
         const uint32_t st = i % ATTN_STAGES, parity = (i / ATTN_STAGES) & 1;
@@ -194,12 +197,13 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
 #pragma unroll
         for (int ks = 0; ks < 4; ks++) {
             uint32_t kb[4];  // b0, b1 of nt 0, then of nt 1
-            const uint32_t key = 8 * (lm >> 1) + lr, chunk = 2 * ks + (lm & 1);
-            ldmatrix_x4(kb, kbase + key * 128 + ((chunk ^ (key & 7)) << 4));
+            ldmatrix_x4(kb, (kbase + k_off) ^ (uint32_t(ks) << 5));  // chunk 2 ks + (lm & 1), swizzled: an XOR of address bits 5..6
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
-                mma16816(sacc[mt][0], qf[mt][ks], kb[0], kb[1]);
-                mma16816(sacc[mt][1], qf[mt][ks], kb[2], kb[3]);
+                uint32_t qf[4];
+                ldmatrix_x4(qf, q_addr[mt] ^ (uint32_t(ks) << 5));
+                mma16816(sacc[mt][0], qf, kb[0], kb[1]);
+                mma16816(sacc[mt][1], qf, kb[2], kb[3]);
             }
         }
         // Visibility: keys below p0 are seen by every row; key p0 + j by the rows whose mask has
@@ -219,6 +223,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
         }
         // Online softmax; a row's statistics are shared by the four lanes of its quad.
         uint32_t pa[MT][4];
+        float corr[MT][2];
+        bool rescale = false;
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
@@ -228,28 +234,32 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_mma_kernel(AttnArgs a, c
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m_run[mt][half], mx);
                 const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-                const float corr = fast_exp2(m_run[mt][half] - m_use);
+                corr[mt][half] = fast_exp2(m_run[mt][half] - m_use);
+                rescale = rescale || corr[mt][half] != 1.0f;
                 m_run[mt][half] = m_new;
                 const float p00 = fast_exp2(sacc[mt][0][2 * half] - m_use), p01 = fast_exp2(sacc[mt][0][2 * half + 1] - m_use);
                 const float p10 = fast_exp2(sacc[mt][1][2 * half] - m_use), p11 = fast_exp2(sacc[mt][1][2 * half + 1] - m_use);
-                l_run[mt][half] = l_run[mt][half] * corr + (p00 + p01 + p10 + p11);
+                l_run[mt][half] = l_run[mt][half] * corr[mt][half] + (p00 + p01 + p10 + p11);
                 pa[mt][half] = pack_bf16(p00, p01);      // a0 / a1: keys 2t, 2t + 1
                 pa[mt][half + 2] = pack_bf16(p10, p11);  // a2 / a3: keys 8 + 2t, 9 + 2t
-                if (corr != 1.0f) {
-#pragma unroll
-                    for (int dn = 0; dn < 8; dn++) {
-                        oacc[mt][dn][2 * half] *= corr;
-                        oacc[mt][dn][2 * half + 1] *= corr;
-                    }
-                }
             }
+        }
+        if (__any_sync(0xffffffffu, rescale)) {  // a maximum moved somewhere in the warp: rare after the first pages
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int dn = 0; dn < 8; dn++) {
+                    oacc[mt][dn][0] *= corr[mt][0];
+                    oacc[mt][dn][1] *= corr[mt][0];
+                    oacc[mt][dn][2] *= corr[mt][1];
+                    oacc[mt][dn][3] *= corr[mt][1];
+                }
         }
         // O += P V: n-tile dn = dims 8 dn .. 8 dn + 7.
 #pragma unroll
         for (int dp = 0; dp < 4; dp++) {
             uint32_t vb[4];  // b0, b1 of dn = 2 dp, then of dn = 2 dp + 1
-            const uint32_t key = 8 * (lm & 1) + lr, chunk = 2 * dp + (lm >> 1);
-            ldmatrix_x4_trans(vb, vbase + key * 128 + ((chunk ^ (key & 7)) << 4));
+            ldmatrix_x4_trans(vb, (vbase + v_off) ^ (uint32_t(dp) << 5));  // chunk 2 dp + (lm >> 1), swizzled
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 mma16816(oacc[mt][2 * dp], pa[mt], vb[0], vb[1]);
@@ -358,15 +368,16 @@ void attn_maps_init(AttnMaps* m, const uint16_t* k_cache, const uint16_t* v_cach
 void launch_attn_mma(const AttnArgs& a, cudaStream_t s) {
     const uint32_t G = a.n_heads / a.kv.n_kv;
     const size_t smem = size_t(ATTN_WARPS) * ATTN_STAGES * STAGE_BYTES + 1024;
-    const dim3 grid(a.max_splits, a.kv.n_kv, a.n_tiles);
+    // kv heads fastest: the blocks that start together read neighbouring 2 KiB slabs of the same pages.
+    const dim3 grid(a.kv.n_kv, a.max_splits, a.n_tiles);
     static bool configured = false;
     if (!configured) {
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         configured = true;
     }
-    if (VERIFY_T * G <= 16) { attn_mma_kernel<1><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps); launch_counter()++; }
-    else { attn_mma_kernel<2><<<grid, ATTN_WARPS * 32, smem, s>>>(a, *a.maps); launch_counter()++; }
+    if (VERIFY_T * G <= 16) launch_pdl(attn_mma_kernel<1>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
+    else launch_pdl(attn_mma_kernel<2>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
 }
 
 }  // namespace vlt

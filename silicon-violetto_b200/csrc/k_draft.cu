@@ -28,6 +28,7 @@ __device__ __forceinline__ void draft_row_in(const float* feat, const uint16_t* 
 __global__ void draft_catchup_in_kernel(const uint32_t* __restrict__ tokens, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ meta,
                                         const uint32_t* __restrict__ on_path, const float* __restrict__ taps, const float* __restrict__ carry,
                                         const uint16_t* __restrict__ embed, uint32_t d, float* x, uint16_t* xb, uint32_t* cpos) {
+    pdl_start();
     const uint32_t t = blockIdx.x, slot = tin[2 * t], row = tin[2 * t + 1], pos = meta[2 * t + 1];
     const float* feat = row ? taps + size_t(t - 1) * d : pos ? carry + size_t(slot) * d : nullptr;
     draft_row_in(feat, embed + size_t(tokens[t]) * d, d, x + size_t(t) * 2 * d, xb + size_t(t) * 2 * d);
@@ -48,6 +49,7 @@ __global__ void draft_pass_in_kernel(const RunIn* __restrict__ runs, const uint3
                                      const uint32_t* __restrict__ emitted, const float* __restrict__ taps, const float* __restrict__ dfeat,
                                      const uint16_t* __restrict__ embed, uint32_t d, uint32_t i, uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta,
                                      uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live) {
+    pdl_start();
     const uint32_t r = blockIdx.x;
     const RunIn ru = runs[r];
     const uint32_t last = draft_last_row(ru, r, path, path_len, on_path);
@@ -70,6 +72,7 @@ __global__ void draft_pass_in_kernel(const RunIn* __restrict__ runs, const uint3
 // The slot's carried tap for the next step's catch-up: the tap of the path's last row.
 __global__ void draft_carry_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ path, const uint32_t* __restrict__ path_len,
                                    const uint32_t* __restrict__ on_path, const float* __restrict__ taps, uint32_t d, float* carry) {
+    pdl_start();
     const uint32_t r = blockIdx.x;
     const RunIn ru = runs[r];
     const uint32_t last = draft_last_row(ru, r, path, path_len, on_path);
@@ -82,6 +85,7 @@ __global__ void draft_carry_kernel(const RunIn* __restrict__ runs, const uint32_
 __global__ void __launch_bounds__(256) draft_pick_kernel(const float* __restrict__ logits, uint32_t v, const uint32_t* __restrict__ vocab_ids,
                                                          const RunIn* __restrict__ runs, const uint32_t* __restrict__ live, uint32_t i, uint32_t* feed,
                                                          uint32_t* tree) {
+    pdl_start();
     __shared__ float bv[8];
     __shared__ uint32_t bi[8];
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
@@ -103,26 +107,22 @@ __global__ void __launch_bounds__(256) draft_pick_kernel(const float* __restrict
 
 void launch_draft_catchup_in(const uint32_t* tokens, const uint32_t* tin, const uint32_t* meta, const uint32_t* on_path, const float* taps, const float* carry,
                              const uint16_t* embed, uint32_t n, uint32_t d, float* x, uint16_t* xb, uint32_t* cpos, cudaStream_t s) {
-    draft_catchup_in_kernel<<<n, 256, 0, s>>>(tokens, tin, meta, on_path, taps, carry, embed, d, x, xb, cpos);
-    launch_counter()++;
+    launch_pdl(draft_catchup_in_kernel, n, 256, 0, s, tokens, tin, meta, on_path, taps, carry, embed, d, x, xb, cpos);
 }
 void launch_draft_pass_in(const RunIn* runs, const uint32_t* lens, const uint32_t* feed, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path,
                           const uint32_t* emitted, const float* taps, const float* dfeat, const uint16_t* embed, uint32_t n_runs, uint32_t d, uint32_t i,
                           uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live,
                           cudaStream_t s) {
-    draft_pass_in_kernel<<<n_runs, 256, 0, s>>>(runs, lens, feed, path, path_len, on_path, emitted, taps, dfeat, embed, d, i, max_seq_len, x, xb, dmeta, dtin,
-                                                dvis, dcpos, live);
-    launch_counter()++;
+    launch_pdl(draft_pass_in_kernel, n_runs, 256, 0, s, runs, lens, feed, path, path_len, on_path, emitted, taps, dfeat, embed, d, i, max_seq_len, x, xb, dmeta,
+               dtin, dvis, dcpos, live);
 }
 void launch_draft_carry(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path, const float* taps, uint32_t n_runs,
                         uint32_t d, float* carry, cudaStream_t s) {
-    draft_carry_kernel<<<n_runs, 256, 0, s>>>(runs, path, path_len, on_path, taps, d, carry);
-    launch_counter()++;
+    launch_pdl(draft_carry_kernel, n_runs, 256, 0, s, runs, path, path_len, on_path, taps, d, carry);
 }
 void launch_draft_pick(const float* logits, uint32_t v, const uint32_t* vocab_ids, const RunIn* runs, const uint32_t* live, uint32_t n_runs, uint32_t i,
                        uint32_t* feed, uint32_t* tree, cudaStream_t s) {
-    draft_pick_kernel<<<n_runs, 256, 0, s>>>(logits, v, vocab_ids, runs, live, i, feed, tree);
-    launch_counter()++;
+    launch_pdl(draft_pick_kernel, n_runs, 256, 0, s, logits, v, vocab_ids, runs, live, i, feed, tree);
 }
 
 }  // namespace vlt

@@ -123,6 +123,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 // 2t+9) of successive mma steps for A and B alike, so every load is contiguous.
 template <bool INT8, int MT>
 __global__ void __launch_bounds__(512) matmul_stream_kernel(MatArgs a) {
+    pdl_start();
     constexpr int NW = 16;
     constexpr int E = INT8 ? 16 : 8;  // weights per 16-byte load
     constexpr int KT = 4 * E;         // k per tile
@@ -253,7 +254,7 @@ void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
     if (a.m % 32 == 0 && a.m / 32 >= 2 * sm_count) mt = 2;
     if (a.m % 64 == 0 && a.m / 64 >= 2 * sm_count) mt = 4;
     const uint32_t grid = a.m / (16 * mt);
-#define VLT_STREAM(I8, MT) { matmul_stream_kernel<I8, MT><<<grid, 512, 0, s>>>(a); launch_counter()++; }
+#define VLT_STREAM(I8, MT) { launch_pdl(matmul_stream_kernel<I8, MT>, grid, 512, 0, s, a); }
     if (a.int8) {
         if (mt == 1) VLT_STREAM(true, 1) else if (mt == 2) VLT_STREAM(true, 2) else VLT_STREAM(true, 4)
     } else {

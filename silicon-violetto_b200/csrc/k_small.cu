@@ -14,6 +14,7 @@ namespace vlt {
 __global__ void embed_kernel(const uint16_t* __restrict__ table, uint32_t* tokens, float* __restrict__ out, const uint32_t* __restrict__ tin,
                              uint32_t* meta, const uint32_t* __restrict__ lens, const uint32_t* __restrict__ feed, const uint32_t* __restrict__ tree,
                              uint32_t* vis, uint32_t d) {
+    pdl_start();
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
     const uint32_t slot = tin[2 * t];
     uint32_t tok = tokens[t], depth = tin[2 * t + 1];
@@ -42,7 +43,7 @@ __global__ void embed_kernel(const uint16_t* __restrict__ table, uint32_t* token
 
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
                   const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, cudaStream_t s) {
-    { embed_kernel<<<n, 128, 0, s>>>(table, tokens, out, tin, meta, lens, feed, tree, vis, d); launch_counter()++; }
+    launch_pdl(embed_kernel, n, 128, 0, s, table, tokens, out, tin, meta, lens, feed, tree, vis, d);
 }
 
 // ------------------------------------------------------- K/V into the cache
@@ -55,6 +56,7 @@ void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uin
 __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin,
                                 const float* __restrict__ rope, uint16_t* k_cache, uint16_t* v_cache, const uint32_t* __restrict__ page_table,
                                 KvArgs kv, uint32_t layer, uint32_t n_heads, float scale_log2, uint32_t* __restrict__ q_b, const uint32_t* __restrict__ cpos_in) {
+    pdl_start();
     const uint32_t t = blockIdx.x, g = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1];
     const uint32_t cpos = cpos_in ? cpos_in[t] : meta[2 * (t - row) + 1] + row;
@@ -83,7 +85,7 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const uint32_t* _
 
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
                      const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, const uint32_t* cpos, cudaStream_t s) {
-    { qkv_post_kernel<<<n, 32 * kv.n_kv, 0, s>>>(qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads, scale_log2, reinterpret_cast<uint32_t*>(q_b), cpos); launch_counter()++; }
+    launch_pdl(qkv_post_kernel, n, 32 * kv.n_kv, 0, s, qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads, scale_log2, reinterpret_cast<uint32_t*>(q_b), cpos);
 }
 
 // ----------------------------------------------- scalar attention (cross-check)
@@ -177,7 +179,7 @@ void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* t
 // One block of 64 threads per (token, head).
 // Splits past a tile's keys hold m = -inf (the attention kernel writes every slot).
 __global__ void attn_combine_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out, uint16_t* out_b) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a GEMM queued behind may start loading its weights
+    pdl_start();
     const uint32_t t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const float* pp = part + (size_t(t) * n_heads + h) * max_splits * ATTN_PART;
     float mm = -INFINITY;
@@ -197,7 +199,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part, uint32_t max
 }
 
 void launch_attn_combine(const AttnArgs& a, cudaStream_t s) {
-    { attn_combine_kernel<<<dim3(a.n, a.n_heads), 64, 0, s>>>(a.part, a.max_splits, a.n_heads, a.out, a.out_b); launch_counter()++; }
+    launch_pdl(attn_combine_kernel, dim3(a.n, a.n_heads), 64, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
 }
 
 // ------------------------------------------------------------- row preparation
@@ -205,8 +207,8 @@ void launch_attn_combine(const AttnArgs& a, cudaStream_t s) {
 // optionally rounded to bf16 and kept as fp32), a bf16 copy, and inv[r] = rsqrt(mean(x^2) + eps).
 __global__ void prep_rows_kernel(const float* __restrict__ in, const uint32_t* __restrict__ rows, uint32_t k, float eps, float* out_f32,
                                  uint16_t* out_bf16, float* inv, bool normalize, bool round_out) {
+    pdl_start();
     __shared__ float red[8];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a GEMM queued behind may start loading its weights
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
     const float* x = in + size_t(rows ? rows[r] : r) * k;
     float ss = 0.0f;
@@ -228,7 +230,7 @@ __global__ void prep_rows_kernel(const float* __restrict__ in, const uint32_t* _
 
 void launch_prep_rows(const float* in, const uint32_t* rows, uint32_t n, uint32_t k, float eps, float* out_f32, uint16_t* out_bf16, float* inv,
                       bool normalize, bool round_out, cudaStream_t s) {
-    if (n) { prep_rows_kernel<<<n, 256, 0, s>>>(in, rows, k, eps, out_f32, out_bf16, inv, normalize, round_out); launch_counter()++; }
+    if (n) launch_pdl(prep_rows_kernel, n, 256, 0, s, in, rows, k, eps, out_f32, out_bf16, inv, normalize, round_out);
 }
 
 // ------------------------------------------------------------------ sampling
@@ -272,6 +274,7 @@ __device__ void tg_scan(float v, float* ex, float* base, uint32_t tid) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits, const SampleRow* __restrict__ rows, uint32_t* out,
                                                                 const uint32_t* __restrict__ meta, uint32_t vocab) {
+    pdl_start();
     __shared__ float ex[SAMPLE_THREADS + SAMPLE_THREADS / 32 + 1];
     __shared__ float base[32];
     __shared__ float bvs[32];
@@ -334,7 +337,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 }
 
 void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s) {
-    if (n_rows) { sample_kernel<<<n_rows, SAMPLE_THREADS, 0, s>>>(logits, rows, out, meta, vocab); launch_counter()++; }
+    if (n_rows) launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, s, logits, rows, out, meta, vocab);
 }
 
 // ----------------------------------------------------------------- accepting
@@ -343,6 +346,7 @@ void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, co
 __global__ void accept_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ tokens, uint32_t* out, uint32_t* lens, uint32_t* feed,
                               GenState* gen, uint32_t* emitted, uint32_t nruns, const uint32_t* __restrict__ tree, uint32_t* path,
                               uint32_t* path_len, uint32_t* on_path) {
+    pdl_start();
     const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= nruns) return;
     const RunIn ru = runs[r];
@@ -387,7 +391,7 @@ __global__ void accept_kernel(const RunIn* __restrict__ runs, const uint32_t* __
 
 void launch_accept(const RunIn* runs, const uint32_t* tokens, uint32_t* out, uint32_t* lens, uint32_t* feed, GenState* gen, uint32_t* emitted,
                    uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s) {
-    if (n_runs) { accept_kernel<<<(n_runs + 63) / 64, 64, 0, s>>>(runs, tokens, out, lens, feed, gen, emitted, n_runs, tree, path, path_len, on_path); launch_counter()++; }
+    if (n_runs) launch_pdl(accept_kernel, (n_runs + 63) / 64, 64, 0, s, runs, tokens, out, lens, feed, gen, emitted, n_runs, tree, path, path_len, on_path);
 }
 
 // kernels.metal:1663-1693 `kv_compact`: the accepted path's K/V rows, on every layer, from
@@ -395,6 +399,7 @@ void launch_accept(const RunIn* runs, const uint32_t* tokens, uint32_t* out, uin
 __global__ void kv_compact_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ path, const uint32_t* __restrict__ path_len,
                                   const uint32_t* __restrict__ lens, uint16_t* k_cache, uint16_t* v_cache, const uint32_t* __restrict__ page_table,
                                   KvArgs kv) {
+    pdl_start();
     const uint32_t r = blockIdx.x, l = blockIdx.y, g = threadIdx.x / 32, lane = threadIdx.x % 32, k = path_len[r];
     const uint32_t slot = runs[r].slot, p0 = lens[slot] - k;
     for (uint32_t j = 1; j < k; j++) {
@@ -408,12 +413,13 @@ __global__ void kv_compact_kernel(const RunIn* __restrict__ runs, const uint32_t
 
 void launch_kv_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_cache, uint16_t* v_cache,
                        const uint32_t* page_table, KvArgs kv, uint32_t n_runs, uint32_t n_layers, cudaStream_t s) {
-    if (n_runs) { kv_compact_kernel<<<dim3(n_runs, n_layers), 32 * kv.n_kv, 0, s>>>(runs, path, path_len, lens, k_cache, v_cache, page_table, kv); launch_counter()++; }
+    if (n_runs) launch_pdl(kv_compact_kernel, dim3(n_runs, n_layers), 32 * kv.n_kv, 0, s, runs, path, path_len, lens, k_cache, v_cache, page_table, kv);
 }
 
 // kernels.metal:1705-1724 `replay_draft`. grid: runs blocks of FEED_W threads.
 __global__ void replay_draft_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ lens, uint32_t* feed, const uint32_t* __restrict__ trace,
                                     const uint32_t* __restrict__ trace_len, ReplayArgs ra, uint32_t nruns, uint32_t* tree) {
+    pdl_start();
     const uint32_t r = blockIdx.x, i = threadIdx.x;
     if (i == 0 || i >= FEED_W || r >= nruns || runs[r].nhead == 0) return;
     const uint32_t slot = runs[r].slot, n = trace_len[slot];
@@ -428,7 +434,7 @@ __global__ void replay_draft_kernel(const RunIn* __restrict__ runs, const uint32
 
 void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed, const uint32_t* trace, const uint32_t* trace_len, ReplayArgs ra,
                          uint32_t n_runs, uint32_t* tree, cudaStream_t s) {
-    if (n_runs) { replay_draft_kernel<<<n_runs, FEED_W, 0, s>>>(runs, lens, feed, trace, trace_len, ra, n_runs, tree); launch_counter()++; }
+    if (n_runs) launch_pdl(replay_draft_kernel, n_runs, FEED_W, 0, s, runs, lens, feed, trace, trace_len, ra, n_runs, tree);
 }
 
 // bench_fill's optional K/V values: small pseudo-random bf16 numbers (a hash of seed, layer,
