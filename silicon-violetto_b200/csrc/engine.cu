@@ -411,6 +411,7 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     io.layer = li;
     io.keys_per_split = p.keys_per_split;
     io.max_splits = p.max_splits;
+    io.max_rows = std::min(p.max_run, VERIFY_T);
     encode_layer_io(io);
 }
 
@@ -463,6 +464,7 @@ void Engine::encode_layer_io(const LayerIO& io) {
         a.scale_log2 = scale_log2;
         a.keys_per_split = io.keys_per_split;
         a.max_splits = io.max_splits;
+        a.max_rows = io.max_rows;
         a.part = s.part.as<float>();
         a.out = s.attn.as<float>();
         a.out_b = big ? s.attn_b.as<uint16_t>() : nullptr;
@@ -669,6 +671,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.cpos = dr.cpos.as<uint32_t>();
     io.keys_per_split = p.keys_per_split;
     io.max_splits = p.max_splits;
+    io.max_rows = std::min(p.max_run, VERIFY_T);
     encode_layer_io(io);
     // (2) the draft passes, one row per run.
     Plan dp;
@@ -683,6 +686,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.cpos = dr.dcpos.as<uint32_t>();
     io.keys_per_split = dp.keys_per_split;
     io.max_splits = dp.max_splits;
+    io.max_rows = 1;
     for (uint32_t i = 1; i < rows; i++) {
         launch_draft_pass_in(runs, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(),
                              st.out<uint32_t>(st.o_emitted), s.taps.as<float>(), dr.dfeat.as<float>(), model.embed, nr, d, i, cfg.max_seq_len, x, xb,

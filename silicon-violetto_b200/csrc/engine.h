@@ -193,7 +193,7 @@ class Engine {
     // What a decoder layer runs on: its weights, the step layout (device arrays), the cache it writes and reads.
     struct LayerIO {
         const Layer* l;
-        uint32_t n, n_tiles, layer, keys_per_split, max_splits;
+        uint32_t n, n_tiles, layer, keys_per_split, max_splits, max_rows;  // max_rows: the longest tile's rows
         const uint32_t *meta, *tin, *tiles, *vis;
         const uint32_t* cpos;  // optional, per token: the cache position its K/V go to (NO_TOK: nowhere); NULL: its run's first position + its row
         uint16_t *k_cache, *v_cache;

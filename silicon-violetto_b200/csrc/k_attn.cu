@@ -15,6 +15,8 @@
 // grid (kv heads, splits, tiles), 4 warps; warp w takes pages w, w + 4, ... of its split.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "kernels.h"
 
 namespace vlt {
@@ -64,22 +66,34 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// MT: m16 tiles of query columns (T * G <= 16 MT).
-template <int MT>
-__global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
+// An 8 x 8 b16 matrix held one row per quad (thread (g, t): row g, columns 2t, 2t + 1), transposed.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// NT: n8 tiles of query columns (column p = G i + h is token i, head h of this kv head; T * G <= 8 NT).
+// The keys are the MMAs' M side: S^T = K Q^T per page (16 keys x 8 NT columns), O^T += V^T P^T
+// (64 dims x 8 NT columns), so a page costs 8 NT MMAs whatever the number of query rows, the
+// statistics of a column live in the lanes that hold it, and P^T reaches the second MMA through
+// movmatrix. ATTN_CTAS blocks of 4 warps per SM.
+template <int NT>
+__global__ void __launch_bounds__(ATTN_WARPS * 32, NT <= 3 ? 4 : 3) attn_mma_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
     pdl_start();
+    constexpr int NTP = (NT + 1) / 2 * 2, NC = 8 * NT;  // q rows in shared memory: whole ldmatrix.x4 pairs of n-tiles
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4..9.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t bars[ATTN_WARPS][ATTN_STAGES];
-    __shared__ __align__(128) uint4 qs[MT * 16 * 8];  // 128-byte aligned: fragment addresses below differ by an XOR of address bits 5..6
+    __shared__ __align__(128) uint4 qs[NTP * 8 * 8];  // 128-byte aligned: fragment addresses below differ by an XOR of address bits 5..6
 
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, tile = blockIdx.z;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const uint32_t G = a.n_heads / a.kv.n_kv;
     const uint32_t t0 = a.tiles[2 * tile], T = a.tiles[2 * tile + 1];
     const uint32_t slot = a.meta[2 * t0], p0 = a.meta[2 * t0 + 1];
-    const uint32_t n_keys = p0 + T, n_cols = T * G;
+    const uint32_t n_keys = p0 + T, n_cols = min(T * G, uint32_t(NC));
     const uint32_t k_begin = split * a.keys_per_split;
     const uint32_t k_end = min(k_begin + a.keys_per_split, n_keys);
 
@@ -110,11 +124,11 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a
     };
     uint32_t ids0 = load_ids(0), ids1 = load_ids(1), cur_batch = 0;
 
-    // Q (bf16, RoPE and the softmax scale already applied) into shared memory as [row p][64 dims],
-    // 16-byte chunks XOR-swizzled by the row; row p = G i + h is token i, head h of this kv head.
+    // Q (bf16, RoPE and the softmax scale already applied) into shared memory as [column p][64 dims],
+    // 16-byte chunks XOR-swizzled by the row.
     {
         const uint4* qg = reinterpret_cast<const uint4*>(a.q_b);
-        for (uint32_t c = threadIdx.x; c < MT * 16 * 8; c += ATTN_WARPS * 32) {
+        for (uint32_t c = threadIdx.x; c < NTP * 8 * 8; c += ATTN_WARPS * 32) {
             const uint32_t p = c / 8, chunk = c % 8;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (p < n_cols) v = qg[(size_t(t0 + p / G) * a.n_heads + kvh * G + p % G) * 8 + chunk];
@@ -146,39 +160,37 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a
     };
     for (uint32_t i = 0; i < min(my_pages, uint32_t(ATTN_STAGES)); i++) issue(i);
 
-    // Q as A operands (a0: rows g, dims lo; a1: rows g + 8, lo; a2: g, hi; a3: g + 8, hi) are read from
-    // shared memory for every page (keeping the 8 MT fragments in registers would cost a block per SM), and
-    // the visibility masks of this lane's rows g and g + 8 stay in registers.
-    const uint32_t lm = lane >> 3, lr = lane & 7;  // ldmatrix: lane -> (matrix, row)
-    uint32_t q_addr[MT];  // fragment (mt, ks) is at q_addr[mt] ^ (ks << 5): the swizzle is an XOR of the 16-byte chunk index
-    uint32_t vmask[MT][2];
+    // ldmatrix lane roles: lane -> (matrix lm, row lr). Rows are 128 bytes and tiles 1024-byte aligned, so the
+    // swizzled 16-byte chunk index is address bits 4..6 and a k step / dim pair is an XOR of bits 5..6 away.
+    const uint32_t lm = lane >> 3, lr = lane & 7;
+    // K as A (keys x dims, straight) and V^T as A (dims x keys, .trans): key 8 (lm & 1) + lr / 8 (lm >> 1) + lr.
+    const uint32_t k_off = (8 * (lm & 1) + lr) * 128 + (((lm >> 1) ^ lr) << 4);
+    const uint32_t v_off = (8 * (lm >> 1) + lr) * 128 + (((lm & 1) ^ lr) << 4);
+    // Q^T as B: n-tile pair jp covers columns 16 jp ..; matrix lm -> n-tile 2 jp + (lm >> 1), chunk 2 ks + (lm & 1).
+    const uint32_t q_off = smem_u32(qs) + (8 * (lm >> 1) + lr) * 128 + (((lm & 1) ^ lr) << 4);
+
+    // This lane's columns: 8 j + 2 t and 8 j + 2 t + 1 of every n-tile j; their visibility masks.
+    uint32_t vmask[NT][2];
 #pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
-        const uint32_t p = mt * 16 + 8 * (lm & 1) + lr;
-        q_addr[mt] = smem_u32(&qs[p * 8 + ((lm >> 1) ^ (p & 7))]);
+    for (int j = 0; j < NT; j++)
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const uint32_t pr = mt * 16 + g + 8 * half;
-            vmask[mt][half] = pr < n_cols ? a.vis[t0 + pr / G] : 0xffffffffu;
+        for (int e = 0; e < 2; e++) {
+            const uint32_t p = 8 * j + 2 * t + e;
+            vmask[j][e] = p < n_cols ? a.vis[t0 + p / G] : 0xffffffffu;
         }
+
+    float oacc[4][NT][4];  // O^T: [dims 16 dm + g (+ 8)][columns 8 j + 2 t (+ 1)]
+    float m_run[NT][2], l_run[NT][2];  // per column; l is this lane's share (its keys g and g + 8)
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+#pragma unroll
+        for (int dm = 0; dm < 4; dm++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) oacc[dm][j][e] = 0.0f;
+        m_run[j][0] = m_run[j][1] = -INFINITY;
+        l_run[j][0] = l_run[j][1] = 0.0f;
     }
 
-    float oacc[MT][8][4];
-    float m_run[MT][2], l_run[MT][2];
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
-#pragma unroll
-        for (int dn = 0; dn < 8; dn++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) oacc[mt][dn][i] = 0.0f;
-        m_run[mt][0] = m_run[mt][1] = -INFINITY;
-        l_run[mt][0] = l_run[mt][1] = 0.0f;
-    }
-
-    // This lane's ldmatrix row within a page (stages are 1024-byte aligned, rows 128 bytes: the swizzled
-    // 16-byte chunk index is address bits 4..6, so the k step / dim pair is an XOR away).
-    const uint32_t k_off = (8 * (lm >> 1) + lr) * 128 + (((lm & 1) ^ lr) << 4);
-    const uint32_t v_off = (8 * (lm & 1) + lr) * 128 + (((lm >> 1) ^ lr) << 4);
     bool failed = false;
     for (uint32_t i = 0; i < my_pages; i++) {
         const uint32_t st = i % ATTN_STAGES, parity = (i / ATTN_STAGES) & 1;
@@ -186,85 +198,82 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a
         const uint32_t kbase = smem_u32(wbuf + st * STAGE_BYTES), vbase = kbase + PAGE * HD * 2;
         const uint32_t key0 = (page_begin + warp + i * ATTN_WARPS) * PAGE;
 
-        // S = Q K^T: n-tile nt = keys 8 nt .. 8 nt + 7 of the page.
-        float sacc[MT][2][4];
+        // S^T = K Q^T: rows = the page's keys g and g + 8, columns = this lane's.
+        float sacc[NT][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
+        for (int j = 0; j < NT; j++)
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) sacc[mt][nt][e] = 0.0f;
+            for (int e = 0; e < 4; e++) sacc[j][e] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < 4; ks++) {
-            uint32_t kb[4];  // b0, b1 of nt 0, then of nt 1
-            ldmatrix_x4(kb, (kbase + k_off) ^ (uint32_t(ks) << 5));  // chunk 2 ks + (lm & 1), swizzled: an XOR of address bits 5..6
+            uint32_t ka[4];
+            ldmatrix_x4(ka, (kbase + k_off) ^ (uint32_t(ks) << 5));
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++) {
-                uint32_t qf[4];
-                ldmatrix_x4(qf, q_addr[mt] ^ (uint32_t(ks) << 5));
-                mma16816(sacc[mt][0], qf, kb[0], kb[1]);
-                mma16816(sacc[mt][1], qf, kb[2], kb[3]);
+            for (int jp = 0; jp < NTP / 2; jp++) {
+                uint32_t qb[4];  // b0, b1 of n-tile 2 jp, then of 2 jp + 1
+                ldmatrix_x4(qb, (q_off + jp * 2048) ^ (uint32_t(ks) << 5));
+                mma16816(sacc[2 * jp], ka, qb[0], qb[1]);
+                if (2 * jp + 1 < NT) mma16816(sacc[2 * jp + 1 < NT ? 2 * jp + 1 : 0], ka, qb[2], qb[3]);
             }
         }
-        // Visibility: keys below p0 are seen by every row; key p0 + j by the rows whose mask has
-        // bit j; keys from p0 + T on by none.
+        // Visibility: keys below p0 are seen by every column; key p0 + r by the columns whose mask has
+        // bit r; keys from p0 + T on by none.
         if (key0 + PAGE > p0) {
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++)
+            for (int j = 0; j < NT; j++)
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const uint32_t key = key0 + 8 * nt + 2 * t + (e & 1);
-                        const uint32_t mask = vmask[mt][e >> 1];
-                        const bool seen = key < p0 || (key < n_keys && ((mask >> (key - p0)) & 1u));
-                        if (!seen) sacc[mt][nt][e] = -INFINITY;
-                    }
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t key = key0 + g + 8 * (e >> 1);
+                    const uint32_t mask = vmask[j][e & 1];
+                    const bool seen = key < p0 || (key < n_keys && ((mask >> (key - p0)) & 1u));
+                    if (!seen) sacc[j][e] = -INFINITY;
+                }
         }
-        // Online softmax; a row's statistics are shared by the four lanes of its quad.
-        uint32_t pa[MT][4];
-        float corr[MT][2];
+        // Online softmax: a column's maximum over the page's 16 keys = over its two rows here and the eight
+        // lanes that share t.
+        uint32_t pb[NT][2];  // P^T as B operands: b0 keys 2t, 2t + 1; b1 keys 8 + 2t, 9 + 2t; column g of the n-tile
+        float corr[NT][2];
         bool rescale = false;
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) {
+        for (int j = 0; j < NT; j++) {
+            float mx[2], m_use[2];
 #pragma unroll
-            for (int half = 0; half < 2; half++) {
-                float mx = fmaxf(fmaxf(sacc[mt][0][2 * half], sacc[mt][0][2 * half + 1]), fmaxf(sacc[mt][1][2 * half], sacc[mt][1][2 * half + 1]));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m_run[mt][half], mx);
-                const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-                corr[mt][half] = fast_exp2(m_run[mt][half] - m_use);
-                rescale = rescale || corr[mt][half] != 1.0f;
-                m_run[mt][half] = m_new;
-                const float p00 = fast_exp2(sacc[mt][0][2 * half] - m_use), p01 = fast_exp2(sacc[mt][0][2 * half + 1] - m_use);
-                const float p10 = fast_exp2(sacc[mt][1][2 * half] - m_use), p11 = fast_exp2(sacc[mt][1][2 * half + 1] - m_use);
-                l_run[mt][half] = l_run[mt][half] * corr[mt][half] + (p00 + p01 + p10 + p11);
-                pa[mt][half] = pack_bf16(p00, p01);      // a0 / a1: keys 2t, 2t + 1
-                pa[mt][half + 2] = pack_bf16(p10, p11);  // a2 / a3: keys 8 + 2t, 9 + 2t
+            for (int e = 0; e < 2; e++) {
+                mx[e] = fmaxf(sacc[j][e], sacc[j][e + 2]);
+                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 4));
+                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 8));
+                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 16));
+                const float m_new = fmaxf(m_run[j][e], mx[e]);
+                m_use[e] = m_new == -INFINITY ? 0.0f : m_new;
+                corr[j][e] = fast_exp2(m_run[j][e] - m_use[e]);
+                rescale = rescale || corr[j][e] != 1.0f;
+                m_run[j][e] = m_new;
             }
+            const float p0a = fast_exp2(sacc[j][0] - m_use[0]), p0b = fast_exp2(sacc[j][1] - m_use[1]);  // key g
+            const float p1a = fast_exp2(sacc[j][2] - m_use[0]), p1b = fast_exp2(sacc[j][3] - m_use[1]);  // key g + 8
+            l_run[j][0] = l_run[j][0] * corr[j][0] + (p0a + p1a);
+            l_run[j][1] = l_run[j][1] * corr[j][1] + (p0b + p1b);
+            pb[j][0] = movmatrix_trans(pack_bf16(p0a, p0b));
+            pb[j][1] = movmatrix_trans(pack_bf16(p1a, p1b));
         }
         if (__any_sync(0xffffffffu, rescale)) {  // a maximum moved somewhere in the warp: rare after the first pages
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++)
+            for (int dm = 0; dm < 4; dm++)
 #pragma unroll
-                for (int dn = 0; dn < 8; dn++) {
-                    oacc[mt][dn][0] *= corr[mt][0];
-                    oacc[mt][dn][1] *= corr[mt][0];
-                    oacc[mt][dn][2] *= corr[mt][1];
-                    oacc[mt][dn][3] *= corr[mt][1];
+                for (int j = 0; j < NT; j++) {
+                    oacc[dm][j][0] *= corr[j][0];
+                    oacc[dm][j][1] *= corr[j][1];
+                    oacc[dm][j][2] *= corr[j][0];
+                    oacc[dm][j][3] *= corr[j][1];
                 }
         }
-        // O += P V: n-tile dn = dims 8 dn .. 8 dn + 7.
+        // O^T += V^T P^T: m-tile dm = dims 16 dm .. 16 dm + 15, one k step of 16 keys.
 #pragma unroll
-        for (int dp = 0; dp < 4; dp++) {
-            uint32_t vb[4];  // b0, b1 of dn = 2 dp, then of dn = 2 dp + 1
-            ldmatrix_x4_trans(vb, (vbase + v_off) ^ (uint32_t(dp) << 5));  // chunk 2 dp + (lm >> 1), swizzled
+        for (int dm = 0; dm < 4; dm++) {
+            uint32_t va[4];
+            ldmatrix_x4_trans(va, (vbase + v_off) ^ (uint32_t(dm) << 5));
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++) {
-                mma16816(oacc[mt][2 * dp], pa[mt], vb[0], vb[1]);
-                mma16816(oacc[mt][2 * dp + 1], pa[mt], vb[2], vb[3]);
-            }
+            for (int j = 0; j < NT; j++) mma16816(oacc[dm][j], va, pb[j][0], pb[j][1]);
         }
         __syncwarp();
         if (i + ATTN_STAGES < my_pages) issue(i + ATTN_STAGES);
@@ -279,35 +288,39 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a
     }
 
     // Merge the four warps through shared memory (the stage ring is free now): every warp scales
-    // its rows to the block's maximum, the block adds them up and writes the partial.
+    // its columns to the block's maximum, the block adds them up and writes the partial.
     __syncthreads();
-    constexpr int ROWS = MT * 16, OS = HD + 8;        // the row stride keeps the float2 stores off each other's banks
-    float* ms = reinterpret_cast<float*>(smem);      // [warp][row]
-    float* ls = ms + ATTN_WARPS * ROWS;              // [warp][row], scaled
-    float* os = ls + ATTN_WARPS * ROWS;              // [warp][row][OS], scaled
+    constexpr int OS = HD + 4;                       // the row stride keeps a quad's stores off each other's banks
+    float* ms = reinterpret_cast<float*>(smem);      // [warp][column]
+    float* ls = ms + ATTN_WARPS * NC;                // [warp][column], scaled
+    float* os = ls + ATTN_WARPS * NC;                // [warp][column][OS], scaled
+    if (g == 0) {
 #pragma unroll
-    for (int mt = 0; mt < MT; mt++)
+        for (int j = 0; j < NT; j++)
 #pragma unroll
-        for (int half = 0; half < 2; half++)
-            if (t == 0) ms[warp * ROWS + mt * 16 + g + 8 * half] = m_run[mt][half];
+            for (int e = 0; e < 2; e++) ms[warp * NC + 8 * j + 2 * t + e] = m_run[j][e];
+    }
     __syncthreads();
 #pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
+    for (int j = 0; j < NT; j++) {
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const uint32_t row = mt * 16 + g + 8 * half;
-            float mm = ms[row];
+        for (int e = 0; e < 2; e++) {
+            const uint32_t col = 8 * j + 2 * t + e;
+            float mm = ms[col];
 #pragma unroll
-            for (int w = 1; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * ROWS + row]);
-            const float wgt = m_run[mt][half] == -INFINITY ? 0.0f : fast_exp2(m_run[mt][half] - mm);
-            float l = l_run[mt][half];
-            l += __shfl_xor_sync(0xffffffffu, l, 1);
-            l += __shfl_xor_sync(0xffffffffu, l, 2);
-            if (t == 0) ls[warp * ROWS + row] = l * wgt;
+            for (int w = 1; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * NC + col]);
+            const float wgt = m_run[j][e] == -INFINITY ? 0.0f : fast_exp2(m_run[j][e] - mm);
+            float l = l_run[j][e];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            if (g == 0) ls[warp * NC + col] = l * wgt;
 #pragma unroll
-            for (int dn = 0; dn < 8; dn++)
-                *reinterpret_cast<float2*>(os + (size_t(warp) * ROWS + row) * OS + 8 * dn + 2 * t) =
-                    make_float2(oacc[mt][dn][2 * half] * wgt, oacc[mt][dn][2 * half + 1] * wgt);
+            for (int dm = 0; dm < 4; dm++) {
+                float* o = os + (size_t(warp) * NC + col) * OS + 16 * dm + g;
+                o[0] = oacc[dm][j][e] * wgt;
+                o[8] = oacc[dm][j][e + 2] * wgt;
+            }
         }
     }
     __syncthreads();
@@ -315,14 +328,14 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_mma_kernel(AttnArgs a
         const uint32_t p = idx / HD, d = idx % HD;
         float oo = 0.0f;
 #pragma unroll
-        for (int w = 0; w < ATTN_WARPS; w++) oo += os[(size_t(w) * ROWS + p) * OS + d];
+        for (int w = 0; w < ATTN_WARPS; w++) oo += os[(size_t(w) * NC + p) * OS + d];
         float* pp = part_of(p);
         if (d == 0) {
             float mm = ms[p], ll = 0.0f;
 #pragma unroll
-            for (int w = 1; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * ROWS + p]);
+            for (int w = 1; w < ATTN_WARPS; w++) mm = fmaxf(mm, ms[w * NC + p]);
 #pragma unroll
-            for (int w = 0; w < ATTN_WARPS; w++) ll += ls[w * ROWS + p];
+            for (int w = 0; w < ATTN_WARPS; w++) ll += ls[w * NC + p];
             pp[0] = mm;
             pp[1] = ll;
         }
@@ -374,10 +387,16 @@ void launch_attn_mma(const AttnArgs& a, cudaStream_t s) {
     if (!configured) {
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         configured = true;
     }
-    if (VERIFY_T * G <= 16) launch_pdl(attn_mma_kernel<1>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
-    else launch_pdl(attn_mma_kernel<2>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
+    // n8 tiles of query columns the step's longest tile needs (at most VERIFY_T rows x G heads).
+    const uint32_t rows = a.max_rows ? std::min(a.max_rows, VERIFY_T) : VERIFY_T, nt = (rows * G + 7) / 8;
+    if (nt <= 1) launch_pdl(attn_mma_kernel<1>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
+    else if (nt == 2) launch_pdl(attn_mma_kernel<2>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
+    else if (nt == 3) launch_pdl(attn_mma_kernel<3>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
+    else launch_pdl(attn_mma_kernel<4>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);
 }
 
 }  // namespace vlt

@@ -58,6 +58,7 @@ struct AttnArgs {
     uint32_t layer, n_tiles, n_heads;
     float scale_log2;
     uint32_t keys_per_split, max_splits;
+    uint32_t max_rows;  // the longest tile's rows in this launch (0: unknown, VERIFY_T)
     float* part;  // [token][head][max_splits][PART]
     float* out;   // [n][n_heads * hd]
     uint16_t* out_b;  // optional bf16 copy
