@@ -189,6 +189,7 @@ def cpu_reference(args, streams, steps, warmup=1):
     sample of the workload: `streams` streams at the full context, `steps` verify steps of 5 rows."""
     _package()
     import oracle
+    threads = oracle.set_threads(os.cpu_count() or 1)  # torchrun sets OMP_NUM_THREADS=1 for its workers: take the machine's cores anyway
     path = model_file("1b", not args.bf16, 0)
     room = ROWS * (steps + warmup + 2) + 32
     eng = oracle.Engine(path, max_seqs=streams, max_step_tokens=streams * ROWS, max_chunk=16, kv_tokens=streams * (args.ctx + room + 16),
@@ -210,7 +211,7 @@ def cpu_reference(args, streams, steps, warmup=1):
         if i >= warmup:
             times.append(dt)
             emitted.append(int(em.sum()))
-    return float(np.median(times)), os.cpu_count(), float(np.mean(emitted))
+    return float(np.median(times)), threads, float(np.mean(emitted))
 
 
 def reduce_over_ranks(dev_ms, wall_s, emitted, launches, world, device):

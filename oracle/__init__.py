@@ -227,6 +227,12 @@ def draw_drafts(q, temperature, seeds, pos0):
     return out
 
 
+def set_threads(n: int) -> int:
+    """OpenMP threads the oracle uses from now on; returns the number in effect."""
+    lib().orc_set_threads(C.c_int(int(n)))
+    return int(lib().orc_max_threads())
+
+
 class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("max_seqs", "max_step_tokens", "max_chunk", "kv_tokens", "max_seq_len", "max_head_rows")]
 

@@ -1,6 +1,8 @@
 // CPU oracle (test infrastructure only, parity unpinned: see bits.hpp): C entry points for
 // the tests' ctypes binding and for the benchmark's CPU-baseline leg.
 #include <cstdio>
+#include <omp.h>
+
 #include <cstring>
 #include <string>
 
@@ -111,6 +113,10 @@ void orc_draw_drafts(const uint16_t* q, uint32_t streams, uint32_t k, uint32_t v
         for (int64_t i = 0; i < int64_t(k); i++)
             drafts[s * k + i] = draw_draft(q + (uint64_t(s) * k + i) * vocab, vocab, temperature, uint32_t(seeds[s]), uint32_t(seeds[s] >> 32), pos0[s] + uint32_t(i));
 }
+
+// OpenMP threads of the calls below (a launcher may have set OMP_NUM_THREADS=1 for its workers).
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int orc_max_threads() { return omp_get_max_threads(); }
 
 // ---- the engine
 struct OrcConfig { uint32_t max_seqs, max_step_tokens, max_chunk, kv_tokens, max_seq_len, max_head_rows; };
