@@ -89,6 +89,7 @@ class Clocks:
 
 
 ROWS = 5           # k = 4 drafts + the bonus row
+ATTN_TRAFFIC_RATIO = 542.4 / 537.6  # DRAM traffic / algorithmic bytes of the attention launch, from its ncu capture
 KV_BYTES_PER_TOKEN_LAYER = 8 * 64 * 2 * 2  # 8 kv heads x 64 dims x bf16 x (K, V)
 WEIGHT_PARAMS = 16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048
 
@@ -322,7 +323,10 @@ def main():
         "gpu_launches": int(sums[1]),
         "clocks": r["clocks"],
         "roofline": {"bound": "hbm", "kernel": "attn_mma_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
-                     "traffic": None, "step_frac": step_bytes / (dev_s / steps) / 1e9 / hbm_peak},
+                     # dram__bytes_read + dram__bytes_write of one launch of this very shape under ncu: 1.009 x the algorithmic
+                     # bytes (profiles/attn_mma_kernel_32streams_8k.md); scaled to this run's key count.
+                     "traffic": att_bytes * ATTN_TRAFFIC_RATIO, "traffic_source": "ncu capture of the same launch shape, scaled by keys",
+                     "step_frac": step_bytes / (dev_s / steps) / 1e9 / hbm_peak},
         "kernel_groups_ms_per_step": {k: v["ms"] / r["prof_steps"] for k, v in r["prof"].items()},
     }
     if extra is not None:
