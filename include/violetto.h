@@ -143,6 +143,15 @@ int vlt_sample_logits(VltEngine* e, const float* logits, const VltSampling* rows
  * time, best of reps. */
 int vlt_spec_accept(VltEngine* e, const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature,
                     const uint64_t* seeds, const uint32_t* pos0, uint32_t reps, uint32_t* accepted, uint32_t* token, uint32_t* rollback, double* gpu_seconds);
+/* The reference drafter's candidate kernels on caller-supplied draft logits [n_rows][nv] (host memory): `draft_top`
+ * (kernels.metal:1846-1889: the ncand <= 4 best entries of each row, mapped through vocab_ids if not NULL, with their
+ * probabilities at temperature 1 / inv_t -> cand, cand_q [n_rows][4]; rows whose tin[2r + 1] is 0 -- a block's first row, the
+ * bonus token's own -- are skipped, tin NULL: none are) and `draft_tree` (kernels.metal:1896-1934: per block
+ * b of blocks[2b + 1] <= 8 rows starting at row blocks[2b], the draft tree of slot slots[b] grown by path probability).
+ * feed and tree receive the engine's whole [max_seqs][16] arrays afterwards. The reference runs them inside its drafter
+ * (drafter.rs:420-447). */
+int vlt_draft_trees(VltEngine* e, const float* logits, uint32_t n_rows, uint32_t nv, const uint32_t* vocab_ids, const uint32_t* tin, const uint32_t* blocks, const uint32_t* slots,
+                    uint32_t n_blocks, float inv_t, uint32_t ncand, uint32_t* cand, float* cand_q, uint32_t* feed, uint32_t* tree);
 /* The same acceptance step for a caller that cannot allocate device memory at that point (all of it
  * is in the caller's own pools, or an allocation's device-wide synchronisation is not acceptable
  * inside the decode loop). No counterpart in the reference. It allocates nothing, on the device or

@@ -164,7 +164,9 @@ inline void replay_draft_run(uint32_t r, const RunIn* runs, const uint32_t* lens
 // and their probabilities at temperature 1/inv_t. z's sum: thread t of 1024 adds ids
 // t, t+1024, ... in turn; the reference then adds the threads' sums in simdgroup order
 // (tg_sum, kernels.metal:40-48), which Metal's simd_sum leaves unpinned: here lanes are added
-// left to right within a group of 32, then the 32 groups left to right.
+// left to right within a group of 32, then the 32 groups left to right. exp(x) is the shared
+// soft_exp2(x * log2e), every operation a single IEEE one, so that the CUDA kernel can agree
+// with this bit for bit (the reference's own tests pin the integers: candidates and tree).
 constexpr uint32_t CANDS = 4;
 inline void draft_top_row(const float* row, uint32_t nv, const uint32_t* vocab_ids, float inv_t, uint32_t ncand,
                           uint32_t* cand, float* cand_q) {
@@ -186,7 +188,7 @@ inline void draft_top_row(const float* row, uint32_t nv, const uint32_t* vocab_i
         float acc = 0.0f;
         for (uint32_t l = 0; l < 32; l++) {
             float zt = 0.0f;
-            for (uint32_t j = g * 32 + l; j < nv; j += 1024) zt += std::exp((row[j] - top_v[0]) * inv_t);
+            for (uint32_t j = g * 32 + l; j < nv; j += 1024) zt += soft_exp2(((row[j] - top_v[0]) * inv_t) * LOG2E);
             acc += zt;
         }
         groups[g] = acc;
@@ -195,7 +197,7 @@ inline void draft_top_row(const float* row, uint32_t nv, const uint32_t* vocab_i
     for (uint32_t g = 0; g < 32; g++) z += groups[g];
     for (uint32_t c = 0; c < ncand; c++) {
         cand[c] = vocab_ids ? vocab_ids[top_i[c]] : top_i[c];
-        cand_q[c] = std::exp((top_v[c] - top_v[0]) * inv_t) / z;
+        cand_q[c] = soft_exp2(((top_v[c] - top_v[0]) * inv_t) * LOG2E) / z;
     }
 }
 

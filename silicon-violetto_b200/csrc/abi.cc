@@ -168,6 +168,11 @@ int vlt_spec_accept(VltEngine* e, const uint16_t* p, const uint16_t* q, const ui
     });
 }
 
+int vlt_draft_trees(VltEngine* e, const float* logits, uint32_t n_rows, uint32_t nv, const uint32_t* vocab_ids, const uint32_t* tin, const uint32_t* blocks, const uint32_t* slots,
+                    uint32_t n_blocks, float inv_t, uint32_t ncand, uint32_t* cand, float* cand_q, uint32_t* feed, uint32_t* tree) {
+    return guard([&] { eng(e).draft_trees(logits, n_rows, nv, vocab_ids, tin, blocks, slots, n_blocks, inv_t, ncand, cand, cand_q, feed, tree); });
+}
+
 int vlt_spec_accept_static(const uint16_t* p_dev, const uint16_t* q_dev, const uint32_t* drafts_dev, uint32_t streams, uint32_t k, uint32_t vocab,
                            float temperature, const uint64_t* seeds_dev, const uint32_t* pos0_dev, uint32_t* accepted_dev, uint32_t* token_dev,
                            uint32_t* rollback_dev, void* cuda_stream) {

@@ -807,6 +807,41 @@ double Engine::spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t*
     return best;
 }
 
+// drafter.rs:420-447 runs draft_top and draft_tree on its block's logits; here they run on logits the caller supplies.
+void Engine::draft_trees(const float* logits, uint32_t n_rows, uint32_t nv, const uint32_t* vocab_ids, const uint32_t* tin, const uint32_t* blocks, const uint32_t* slots,
+                         uint32_t n_blocks, float inv_t, uint32_t ncand, uint32_t* cand, float* cand_q, uint32_t* feed, uint32_t* tree) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");
+    if (n_rows == 0 || nv == 0 || ncand == 0 || ncand > 4) throw Error("draft_trees: needs rows, a vocabulary and 1..4 candidates");
+    for (uint32_t b = 0; b < n_blocks; b++) {
+        if (slots[b] >= cfg.max_seqs) throw Error("draft_trees: slot out of range");
+        if (blocks[2 * b + 1] == 0 || blocks[2 * b + 1] > VERIFY_T || blocks[2 * b] + blocks[2 * b + 1] > n_rows) throw Error("draft_trees: block out of the rows given");
+    }
+    Buffer d_logits, d_ids, d_tin, d_blocks, d_slots, d_cand, d_q;
+    if (tin) { d_tin.alloc(size_t(n_rows) * 8, false); d_tin.write(0, tin, size_t(n_rows) * 8); }
+    d_logits.alloc(size_t(n_rows) * nv * 4, false);
+    d_logits.write(0, logits, size_t(n_rows) * nv * 4);
+    if (vocab_ids) { d_ids.alloc(size_t(nv) * 4, false); d_ids.write(0, vocab_ids, size_t(nv) * 4); }
+    d_cand.alloc(size_t(n_rows) * 16, false);
+    d_q.alloc(size_t(n_rows) * 16, false);
+    VLT_CUDA(cudaMemsetAsync(d_cand.dev, 0, size_t(n_rows) * 16, stream));
+    VLT_CUDA(cudaMemsetAsync(d_q.dev, 0, size_t(n_rows) * 16, stream));
+    launch_draft_top(d_logits.as<float>(), n_rows, nv, vocab_ids ? d_ids.as<uint32_t>() : nullptr, tin ? d_tin.as<uint32_t>() : nullptr, inv_t, ncand,
+                     d_cand.as<uint32_t>(), d_q.as<float>(), stream);
+    if (n_blocks) {
+        d_blocks.alloc(size_t(n_blocks) * 8, false);
+        d_blocks.write(0, blocks, size_t(n_blocks) * 8);
+        d_slots.alloc(size_t(n_blocks) * 4, false);
+        d_slots.write(0, slots, size_t(n_blocks) * 4);
+        launch_draft_tree(d_blocks.as<uint32_t>(), d_slots.as<uint32_t>(), n_blocks, d_cand.as<uint32_t>(), d_q.as<float>(), ncand, s.feed.as<uint32_t>(),
+                          s.tree.as<uint32_t>(), stream);
+    }
+    VLT_CUDA(cudaStreamSynchronize(stream));
+    d_cand.read(0, cand, size_t(n_rows) * 16);
+    d_q.read(0, cand_q, size_t(n_rows) * 16);
+    s.feed.read(0, feed, size_t(cfg.max_seqs) * FEED_W * 4);
+    s.tree.read(0, tree, size_t(cfg.max_seqs) * FEED_W * 4);
+}
+
 // engine/src/engine/hooks.rs:56-111 `bench_matmul`.
 void Engine::bench_matmul(const std::string& kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes) {
     if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");

@@ -128,6 +128,11 @@ class Engine {
     // (accepted, token, rollback). Returns the kernels' GPU seconds (best of reps).
     double spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, float temperature, const uint64_t* seeds,
                        const uint32_t* pos0, uint32_t reps, uint32_t* out);
+    // The reference drafter's draft_top + draft_tree on caller-supplied draft logits [n_rows][nv] (host pointers; a test hook
+    // like sample_logits): candidates [n_rows][4] and their probabilities, and per block (first row, rows, slot) the slot's
+    // feed[16] / tree[16] rows, which start as the engine's current ones.
+    void draft_trees(const float* logits, uint32_t n_rows, uint32_t nv, const uint32_t* vocab_ids, const uint32_t* tin, const uint32_t* blocks, const uint32_t* slots,
+                     uint32_t n_blocks, float inv_t, uint32_t ncand, uint32_t* cand, float* cand_q, uint32_t* feed, uint32_t* tree);
     void bench_matmul(const std::string& kind, uint32_t n, uint32_t variant, uint32_t reps, double* seconds, uint64_t* bytes);
 
     // The generator's building blocks (engine/src/engine/generate.rs uses the same ones).

@@ -105,6 +105,110 @@ __global__ void __launch_bounds__(256) draft_pick_kernel(const float* __restrict
     }
 }
 
+// ---------------------------------------------------------------- the reference drafter's candidate kernels
+// kernels.metal:1846-1889 `draft_top`: one block of 1024 threads per row of draft logits; the `ncand` (<= 4)
+// best draft-vocabulary entries (ties to the lowest index), mapped to target ids, and their probabilities
+// at temperature 1 / inv_t. The normaliser's sum: thread t adds entries t, t + 1024, ... in turn, lanes are
+// added left to right within a warp and the warps left to right (the reference's simd_sum order is not
+// pinned); exp is soft_exp2(x log2 e), every operation a single IEEE one, as in the CPU restatement.
+constexpr uint32_t DRAFT_CANDS = 4;
+__global__ void __launch_bounds__(1024) draft_top_kernel(const float* __restrict__ logits, uint32_t nv, const uint32_t* __restrict__ vocab_ids,
+                                                         const uint32_t* __restrict__ tin, float inv_t, uint32_t ncand, uint32_t* cand, float* cand_q) {
+    pdl_start();
+    if (tin && tin[2 * blockIdx.x + 1] == 0) return;  // kernels.metal:1862: a block's row 0 is the bonus token's own
+    __shared__ float bv[32];
+    __shared__ uint32_t bi[32];
+    __shared__ float top_v[DRAFT_CANDS];
+    __shared__ uint32_t top_i[DRAFT_CANDS];
+    __shared__ float zs[1024];
+    __shared__ float groups[32];
+    __shared__ float z_s;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+    const float* row = logits + size_t(r) * nv;
+    for (uint32_t c = 0; c < ncand; c++) {
+        float mx = -FLT_MAX;
+        uint32_t am = 0xffffffffu;
+        for (uint32_t j = tid; j < nv; j += 1024) {
+            bool taken = false;
+            for (uint32_t m = 0; m < c; m++) taken = taken || top_i[m] == j;
+            if (!taken) better(mx, am, row[j], j);
+        }
+        warp_best(mx, am);
+        if (lane == 0) { bv[warp] = mx; bi[warp] = am; }
+        __syncthreads();
+        if (tid == 0) {
+            for (uint32_t w = 1; w < 32; w++) better(mx, am, bv[w], bi[w]);
+            top_v[c] = mx;
+            top_i[c] = am;
+        }
+        __syncthreads();
+    }
+    const float t0 = top_v[0];
+    float zt = 0.0f;
+    for (uint32_t j = tid; j < nv; j += 1024) zt = __fadd_rn(zt, soft_exp2(__fmul_rn(__fmul_rn(__fsub_rn(row[j], t0), inv_t), LOG2E)));
+    zs[tid] = zt;
+    __syncthreads();
+    if (lane == 0) {
+        float acc = 0.0f;
+        for (uint32_t l = 0; l < 32; l++) acc = __fadd_rn(acc, zs[warp * 32 + l]);
+        groups[warp] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float z = 0.0f;
+        for (uint32_t w = 0; w < 32; w++) z = __fadd_rn(z, groups[w]);
+        z_s = z;
+    }
+    __syncthreads();
+    if (tid < ncand) {
+        cand[r * DRAFT_CANDS + tid] = vocab_ids ? vocab_ids[top_i[tid]] : top_i[tid];
+        cand_q[r * DRAFT_CANDS + tid] = __fdiv_rn(soft_exp2(__fmul_rn(__fmul_rn(__fsub_rn(top_v[tid], t0), inv_t), LOG2E)), z_s);
+    }
+}
+
+// kernels.metal:1896-1934 `draft_tree`: one thread per block of `rows` rows starting at step row `first`
+// (blocks[2 b], blocks[2 b + 1]) of slot slots[b]: grows the tree greedily by path probability -- the node
+// with the best score x next candidate's probability gets a child -- parents before children, then dead
+// nodes up to FEED_W.
+__global__ void draft_tree_kernel(const uint32_t* __restrict__ blocks, const uint32_t* __restrict__ slots, uint32_t n_blocks, const uint32_t* __restrict__ cand,
+                                  const float* __restrict__ cand_q, uint32_t ncand, uint32_t* feed, uint32_t* tree) {
+    pdl_start();
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint32_t first = blocks[2 * b], rows = min(blocks[2 * b + 1], VERIFY_T), slot = slots[b];
+    float score[8] = {1.0f, 0, 0, 0, 0, 0, 0, 0};
+    uint32_t depth[8] = {0, 0, 0, 0, 0, 0, 0, 0}, taken[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sees[8] = {1, 0, 0, 0, 0, 0, 0, 0};
+    uint32_t n = 1;
+    for (; n < rows; n++) {
+        float best = -1.0f;
+        uint32_t p = 0;
+        for (uint32_t i = 0; i < n; i++) {
+            if (depth[i] + 1 == rows || taken[i] == ncand) continue;
+            const float sc = __fmul_rn(score[i], cand_q[(first + depth[i] + 1) * DRAFT_CANDS + taken[i]]);
+            if (sc > best) { best = sc; p = i; }
+        }
+        if (best < 0.0f) break;
+        const uint32_t d = depth[p] + 1;
+        feed[slot * FEED_W + n] = cand[(first + d) * DRAFT_CANDS + taken[p]];
+        taken[p]++;
+        score[n] = best;
+        depth[n] = d;
+        taken[n] = 0;
+        sees[n] = sees[p] | 1u << n;
+        tree[slot * FEED_W + n] = d_tree_node(d, p, sees[n]);
+    }
+    for (; n < FEED_W; n++) tree[slot * FEED_W + n] = d_dead_node(n);
+}
+
+void launch_draft_top(const float* logits, uint32_t n_rows, uint32_t nv, const uint32_t* vocab_ids, const uint32_t* tin, float inv_t, uint32_t ncand, uint32_t* cand,
+                      float* cand_q, cudaStream_t s) {
+    if (n_rows) launch_pdl(draft_top_kernel, n_rows, 1024, 0, s, logits, nv, vocab_ids, tin, inv_t, ncand, cand, cand_q);
+}
+void launch_draft_tree(const uint32_t* blocks, const uint32_t* slots, uint32_t n_blocks, const uint32_t* cand, const float* cand_q, uint32_t ncand, uint32_t* feed,
+                       uint32_t* tree, cudaStream_t s) {
+    if (n_blocks) launch_pdl(draft_tree_kernel, (n_blocks + 31) / 32, 32, 0, s, blocks, slots, n_blocks, cand, cand_q, ncand, feed, tree);
+}
+
 void launch_draft_catchup_in(const uint32_t* tokens, const uint32_t* tin, const uint32_t* meta, const uint32_t* on_path, const float* taps, const float* carry,
                              const uint16_t* embed, uint32_t n, uint32_t d, float* x, uint16_t* xb, uint32_t* cpos, cudaStream_t s) {
     launch_pdl(draft_catchup_in_kernel, n, 256, 0, s, tokens, tin, meta, on_path, taps, carry, embed, d, x, xb, cpos);

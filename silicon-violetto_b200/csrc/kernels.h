@@ -81,6 +81,13 @@ void launch_draft_carry(const RunIn* runs, const uint32_t* path, const uint32_t*
 void launch_draft_pick(const float* logits, uint32_t v, const uint32_t* vocab_ids, const RunIn* runs, const uint32_t* live, uint32_t n_runs, uint32_t i,
                        uint32_t* feed, uint32_t* tree, cudaStream_t s);
 
+// The reference drafter's candidate kernels (kernels.metal:1846-1934): the best `ncand` (<= 4) entries of each row of draft
+// logits with their probabilities, then a draft tree per block of rows grown by path probability.
+void launch_draft_top(const float* logits, uint32_t n_rows, uint32_t nv, const uint32_t* vocab_ids, const uint32_t* tin, float inv_t, uint32_t ncand, uint32_t* cand,
+                      float* cand_q, cudaStream_t s);  // tin (optional): (slot, row) per row; rows numbered 0 are skipped
+void launch_draft_tree(const uint32_t* blocks, const uint32_t* slots, uint32_t n_blocks, const uint32_t* cand, const float* cand_q, uint32_t ncand, uint32_t* feed,
+                       uint32_t* tree, cudaStream_t s);
+
 // The tcgen05 GEMM for 16..256 tokens: needs Xb (bf16 X, rows padded to 16), inv_in for the
 // normed epilogues, m a multiple of 128, one int8 scale per row.
 bool gemm_supported(const MatArgs& a);

@@ -298,6 +298,21 @@ class Engine:
                                      _ptr(seeds, C.c_uint64), _ptr(pos0), C.c_uint32(reps), _ptr(acc), _ptr(tok), _ptr(rb), C.byref(secs)))
         return acc, tok, rb, secs.value
 
+    def draft_trees(self, logits, vocab_ids, blocks, slots, inv_t: float, ncand: int, tin=None):
+        """draft_top + draft_tree on draft logits [rows][nv]; blocks: (first row, rows) pairs, one slot each.
+        Returns (cand [rows][4], cand_q [rows][4], feed [max_seqs][16], tree [max_seqs][16])."""
+        logits = np.ascontiguousarray(logits, np.float32)
+        rows, nv = logits.shape
+        ids = None if vocab_ids is None else _u32(vocab_ids)
+        blocks, slots = _u32(blocks), _u32(slots)
+        tin = None if tin is None else _u32(tin)
+        cand, cand_q = np.zeros((rows, 4), np.uint32), np.zeros((rows, 4), np.float32)
+        feed, tree = np.zeros((self.cfg.max_seqs, 16), np.uint32), np.zeros((self.cfg.max_seqs, 16), np.uint32)
+        _check(lib().vlt_draft_trees(self.h, _ptr(logits, C.c_float), C.c_uint32(rows), C.c_uint32(nv), None if ids is None else _ptr(ids), None if tin is None else _ptr(tin),
+                                     _ptr(blocks),                                     _ptr(slots), C.c_uint32(len(slots)), C.c_float(inv_t), C.c_uint32(ncand), _ptr(cand), _ptr(cand_q, C.c_float), _ptr(feed),
+                                     _ptr(tree)))
+        return cand, cand_q, feed, tree
+
     def set_profile_skip(self, mask: int) -> None:
         lib().vlt_set_profile_skip(self.h, C.c_uint32(mask))
 
