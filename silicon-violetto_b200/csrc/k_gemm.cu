@@ -411,7 +411,9 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         asm volatile("griddepcontrol.wait;" ::: "memory");
         for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
         asm volatile("bar.sync 1, %0;" ::"n"(32 * CONV_WARPS) : "memory");  // the epilogue warps only
+        if (tid == FIRST_CONV * 32) PROBE(7, 0);
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
+        if (tid == FIRST_CONV * 32) PROBE(7, 1);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // The warps that share a quarter of the TMEM lanes (rows) take groups of 16 tokens in turn.
@@ -436,8 +438,10 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tid == FIRST_CONV * 32) PROBE(7, 2);
     if (splits > 1) {
         cluster_sync();  // every block's partial is in place
+        if (tid == FIRST_CONV * 32) PROBE(7, 3);
         // Each block finishes its share of the rows. First their sums over the cluster's partials, into a
         // second buffer: a warp reads a row's tokens, contiguous in the other block's shared memory, and
         // adds the ranks up in order (deterministic). Then a lane takes a row and emits 32 tokens at a time.
@@ -464,6 +468,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             }
         }
         __syncthreads();
+        if (tid == FIRST_CONV * 32) PROBE(7, 4);
         if (warp >= FIRST_CONV && !*abort_flag) {
             const uint32_t chunks = n_pad / 16, n_rg = (r_end - r_begin + 31) / 32;
             for (uint32_t item = ew; item < chunks * n_rg; item += CONV_WARPS) {
@@ -477,8 +482,10 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             }
         }
     }
+    if (tid == FIRST_CONV * 32) PROBE(7, 5);
     if (splits > 1) cluster_sync();  // nobody leaves while its shared memory may still be read
     __syncthreads();
+    if (tid == FIRST_CONV * 32) PROBE(7, 6);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
@@ -604,6 +611,8 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
         cudaMemcpyFromSymbol(h, gemm::g_probe, sizeof(h));
         fprintf(stderr, "gemm m=%u k=%u n=%u splits=%u stages a %u b %u raw %u\n", a.m, a.k, a.n, splits, stages_a, stages_b, raw_stages);
         const unsigned long long t0 = h[0][0];
+        fprintf(stderr, "epilogue (ns from the first weight load): starts %lld accumulator done %lld dumped %lld cluster barrier %lld summed %lld emitted %lld left %lld\n",
+                (long long)(h[7][0] - t0), (long long)(h[7][1] - t0), (long long)(h[7][2] - t0), (long long)(h[7][3] - t0), (long long)(h[7][4] - t0), (long long)(h[7][5] - t0), (long long)(h[7][6] - t0));
         for (uint32_t i = 0; i < std::min(64u, nkb / splits); i++)
             fprintf(stderr, "kb %2u: tmaA %6lld convstart %6lld convdone %6lld tmaB %6lld afull %6lld bfull %6lld commit %6lld\n", i, (long long)(h[0][i] - t0),
                     (long long)(h[1][i] - t0), (long long)(h[2][i] - t0), (long long)(h[3][i] - t0), (long long)(h[4][i] - t0), (long long)(h[5][i] - t0), (long long)(h[6][i] - t0));

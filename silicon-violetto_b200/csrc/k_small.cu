@@ -178,19 +178,35 @@ void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* t
 // (token, head) are (m, l, o[64]) per key split; out = sum(o_s 2^(m_s - M)) / sum(l_s 2^(m_s - M)).
 // One block of 64 threads per (token, head).
 // Splits past a tile's keys hold m = -inf (the attention kernel writes every slot).
-__global__ void attn_combine_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out, uint16_t* out_b) {
+__global__ void __launch_bounds__(64) attn_combine_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out, uint16_t* out_b) {
     pdl_start();
+    __shared__ float ws[64];   // the splits' weights 2^(m_s - M), 0 for an empty split
+    __shared__ float red[4];
     const uint32_t t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const float* pp = part + (size_t(t) * n_heads + h) * max_splits * ATTN_PART;
-    float mm = -INFINITY;
-    for (uint32_t s = 0; s < max_splits; s++) mm = fmaxf(mm, pp[s * ATTN_PART]);
+    // A thread per split for the statistics (at most 64 splits, engine.cu `attention_split`), then a thread
+    // per dim with the splits' loads independent of each other.
+    const bool has = d < max_splits;
+    const float ms = has ? pp[d * ATTN_PART] : -INFINITY;
+    const float ls = has ? pp[d * ATTN_PART + 1] : 0.0f;
+    float mm = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    if (d % 32 == 0) red[d / 32] = mm;
+    __syncthreads();
+    mm = fmaxf(red[0], red[1]);
+    const float w = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+    ws[d] = w;
+    float lw = ls * w;  // summed in split order below, so that the result does not depend on the warp layout
+    __shared__ float lws[64];
+    lws[d] = lw;
+    __syncthreads();
     float ll = 0.0f, oo = 0.0f;
+    for (uint32_t s = 0; s < max_splits; s++) ll += lws[s];
+#pragma unroll 8
     for (uint32_t s = 0; s < max_splits; s++) {
-        const float ms = pp[s * ATTN_PART];
-        if (ms == -INFINITY) continue;
-        const float w = exp2f(ms - mm);
-        ll += pp[s * ATTN_PART + 1] * w;
-        oo += pp[s * ATTN_PART + 4 + d] * w;
+        const float v = pp[s * ATTN_PART + 4 + d];  // an empty split's o was never written: whatever is there must not count
+        oo += ws[s] == 0.0f ? 0.0f : v * ws[s];
     }
     const float r = oo / ll;
     const size_t at = size_t(t) * n_heads * 64 + h * 64 + d;
@@ -286,7 +302,18 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     const float* x = logits + size_t(r) * vocab;
     float lmax = -FLT_MAX;
     uint32_t tok = 0xffffffffu;
-    for (uint32_t i = tid; i < vocab; i += SAMPLE_THREADS) better(lmax, tok, x[i], i);
+    // A thread's ids in batches of 8: the loads of a batch go out together (a row comes from L2, and one load
+    // at a time leaves the pass bound by its latency); the arithmetic keeps the id order.
+    constexpr uint32_t B = 8;
+    uint32_t i0 = tid;
+    for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+        float v[B];
+#pragma unroll
+        for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+        for (uint32_t k = 0; k < B; k++) better(lmax, tok, v[k], i0 + k * SAMPLE_THREADS);
+    }
+    for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) better(lmax, tok, x[i], i);
     warp_best(lmax, tok);
     if (lane == 0) { bvs[tid / 32] = lmax; bis[tid / 32] = tok; }
     __syncthreads();
@@ -296,7 +323,15 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     if (row.temperature > 0.0f) {
         const float c = __fdiv_rn(LOG2E, row.temperature);
         float s = 0.0f;
-        for (uint32_t i = tid; i < vocab; i += SAMPLE_THREADS) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(x[i], lmax), c)));
+        i0 = tid;
+        for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+            float v[B];
+#pragma unroll
+            for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+            for (uint32_t k = 0; k < B; k++) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+        }
+        for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(x[i], lmax), c)));
         tg_scan(s, ex, base, tid);
         const float z = ex[ex_at(SAMPLE_THREADS)];
         float low = -INFINITY;
@@ -324,7 +359,16 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
             const float xj = x[j];
             if (xj == lmax || row.top_p >= 1.0f) { tok = j; break; }
             float q = 0.0f;
-            for (uint32_t i = tid; i < vocab; i += SAMPLE_THREADS) {
+            i0 = tid;
+            for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+                float v[B];
+#pragma unroll
+                for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+                for (uint32_t k = 0; k < B; k++)
+                    if (v[k] > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+            }
+            for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) {
                 const float xi = x[i];
                 if (xi > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c)));
             }
@@ -336,8 +380,187 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     if (tid == 0) out[r] = tok;
 }
 
+// The same sampler spread over a cluster of 8 blocks: the 1024 "threads" of the reference's order are the
+// cluster's 8 x 128, so every sum keeps its order and its association (thread t still owns ids t, t + 1024,
+// ...; groups of 32 threads are warps; the 32 group totals are scanned left to right), while a row's passes
+// over the logits run on eight SMs instead of one. What one block needs from the others -- the best
+// (value, id) pairs, the group totals, the picked id -- crosses distributed shared memory around a cluster
+// barrier. Every block of a cluster takes the same branches (they hold the same values).
+constexpr uint32_t SC_CTAS = 8, SC_THREADS = SAMPLE_THREADS / SC_CTAS, SC_WARPS = SC_THREADS / 32;
+__device__ __forceinline__ void sc_cluster_sync() { asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t sc_remote(const void* p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(uint32_t(__cvta_generic_to_shared(p))), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ uint32_t sc_ld_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+struct ScExchange {
+    float tot[2][SC_WARPS];  // this block's group totals, double-buffered by scan
+    uint32_t pick[2];        // the id a thread of this block picked (NO_TOK: none), double-buffered by round
+    float bv;                // this block's best logit and its id
+    uint32_t bi;
+};
+
+// tg_scan over the cluster. v: this thread's sum. Returns ex[t] (lo), ex[t + 1] (hi) and ex[1024] (total).
+__device__ void sc_scan(float v, uint32_t buf, ScExchange* xc, float* vals, float* pre, float* tot_all, float* base, uint32_t rank, uint32_t tid, float& lo,
+                        float& hi, float& total) {
+    const uint32_t lane = tid % 32, warp = tid / 32;
+    vals[tid] = v;
+    __syncthreads();
+    if (tid < SC_WARPS) {  // a group's exclusive prefixes, left to right from 0
+        float acc = 0.0f;
+        for (uint32_t i = 32 * tid; i < 32 * tid + 32; i++) {
+            pre[i] = acc;
+            acc = __fadd_rn(acc, vals[i]);
+        }
+        xc->tot[buf][tid] = acc;
+    }
+    sc_cluster_sync();
+    if (tid < 32) tot_all[tid] = __uint_as_float(sc_ld_u32(sc_remote(&xc->tot[buf][tid % SC_WARPS], tid / SC_WARPS)));
+    __syncthreads();
+    if (tid == 0) {  // the group totals scanned left to right from 0
+        float acc = 0.0f;
+        for (uint32_t g = 0; g < 32; g++) {
+            base[g] = acc;
+            acc = __fadd_rn(acc, tot_all[g]);
+        }
+        base[32] = acc;
+    }
+    __syncthreads();
+    const uint32_t group = rank * SC_WARPS + warp;
+    lo = __fadd_rn(pre[tid], base[group]);
+    hi = __shfl_down_sync(0xffffffffu, lo, 1);
+    if (lane == 31) hi = base[group + 1];
+    total = base[32];
+}
+
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sample_cluster_kernel(const float* __restrict__ logits, const SampleRow* __restrict__ rows,
+                                                                                                 uint32_t* out, const uint32_t* __restrict__ meta, uint32_t vocab) {
+    pdl_start();
+    __shared__ ScExchange xc;
+    __shared__ float vals[SC_THREADS], pre[SC_THREADS], tot_all[32], base[33];
+    __shared__ float wbv[SC_WARPS];
+    __shared__ uint32_t wbi[SC_WARPS];
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const uint32_t r = blockIdx.x / SC_CTAS, tid = threadIdx.x, lane = tid % 32, vt = rank * SC_THREADS + tid;
+    const SampleRow row = rows[r];
+    const uint32_t pos = row.tok == NO_TOK ? row.pos : meta[2 * row.tok + 1] + 1;
+    const float* x = logits + size_t(r) * vocab;
+    constexpr uint32_t B = 8;  // a thread's ids in batches: the loads of a batch go out together, the arithmetic keeps the id order
+    float lmax = -FLT_MAX;
+    uint32_t tok = 0xffffffffu;
+    uint32_t i0 = vt;
+    for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+        float v[B];
+#pragma unroll
+        for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+        for (uint32_t k = 0; k < B; k++) better(lmax, tok, v[k], i0 + k * SAMPLE_THREADS);
+    }
+    for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) better(lmax, tok, x[i], i);
+    warp_best(lmax, tok);
+    if (lane == 0) { wbv[tid / 32] = lmax; wbi[tid / 32] = tok; }
+    if (tid == 0) { xc.pick[0] = NO_TOK; xc.pick[1] = NO_TOK; }
+    __syncthreads();
+    if (tid == 0) {
+        for (uint32_t w = 1; w < SC_WARPS; w++) better(lmax, tok, wbv[w], wbi[w]);
+        xc.bv = lmax;
+        xc.bi = tok;
+    }
+    sc_cluster_sync();
+    lmax = -FLT_MAX;
+    tok = 0xffffffffu;
+    for (uint32_t s = 0; s < SC_CTAS; s++)  // `better` is a total order on (value, id): any order of combination gives the same pair
+        better(lmax, tok, __uint_as_float(sc_ld_u32(sc_remote(&xc.bv, s))), sc_ld_u32(sc_remote(&xc.bi, s)));
+    if (row.temperature > 0.0f) {
+        const float c = __fdiv_rn(LOG2E, row.temperature);
+        float sum = 0.0f;
+        i0 = vt;
+        for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+            float v[B];
+#pragma unroll
+            for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+            for (uint32_t k = 0; k < B; k++) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+        }
+        for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(x[i], lmax), c)));
+        float lo, hi, total;
+        uint32_t scans = 0;
+        sc_scan(sum, scans++ & 1, &xc, vals, pre, tot_all, base, rank, tid, lo, hi, total);
+        const float z = total;
+        float low = -INFINITY;
+        for (uint32_t round = 0; round < SAMPLE_ROUNDS; round++) {
+            const float target = __fmul_rn(uniform01(row.seed_lo, row.seed_hi, pos, round), total);
+            const uint32_t pb = round & 1;
+            if (lo <= target && target < hi) {
+                float acc = 0.0f;
+                uint32_t j = 0xffffffffu;
+                for (uint32_t i = vt; i < vocab; i += SAMPLE_THREADS) {
+                    const float xi = x[i];
+                    if (!(xi > low)) continue;
+                    const float e = soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c));
+                    acc = __fadd_rn(acc, e);
+                    if (e > 0.0f) j = i;
+                    if (__fsub_rn(target, lo) < acc) break;
+                }
+                xc.pick[pb] = j;  // at most one thread of the cluster is here: the scan never decreases
+            }
+            sc_cluster_sync();
+            uint32_t j = NO_TOK;
+            for (uint32_t s = 0; s < SC_CTAS; s++) {
+                const uint32_t pj = sc_ld_u32(sc_remote(&xc.pick[pb], s));
+                if (pj != NO_TOK) j = pj;
+            }
+            if (j == NO_TOK) break;
+            __syncthreads();                       // every thread of this block has read this round's picks ...
+            if (tid == 0) xc.pick[pb ^ 1] = NO_TOK;  // ... of the buffer the round after next reuses; the next round's is cleared here
+            const float xj = x[j];
+            if (xj == lmax || row.top_p >= 1.0f) { tok = j; break; }
+            float q = 0.0f;
+            i0 = vt;
+            for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+                float v[B];
+#pragma unroll
+                for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+                for (uint32_t k = 0; k < B; k++)
+                    if (v[k] > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+            }
+            for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) {
+                const float xi = x[i];
+                if (xi > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c)));
+            }
+            sc_scan(q, scans++ & 1, &xc, vals, pre, tot_all, base, rank, tid, lo, hi, total);
+            if (total < __fmul_rn(row.top_p, z)) { tok = j; break; }
+            low = xj;
+        }
+    }
+    if (rank == 0 && tid == 0) out[r] = tok;
+    sc_cluster_sync();  // nobody leaves while another block may still read its shared memory
+}
+
 void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s) {
-    if (n_rows) launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, s, logits, rows, out, meta, vocab);
+    if (!n_rows) return;
+    // Enough rows to fill the SMs with one block each: the single-block form (at 160 rows the two take the same time,
+    // bound by instruction issue); fewer: a cluster of 8 blocks per row (one stream's 5 rows: 95 -> about 25 us).
+    if (n_rows > 96) { launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, s, logits, rows, out, meta, vocab); return; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_rows * SC_CTAS);
+    cfg.blockDim = dim3(SC_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, rows, out, meta, vocab));
+    launch_counter()++;
 }
 
 // ----------------------------------------------------------------- accepting

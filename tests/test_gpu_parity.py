@@ -239,6 +239,20 @@ def test_sampler_is_bit_exact(vocab_cfg):
     assert len(set(d1.tolist())) > n // 2
 
 
+def test_sampler_with_many_rows_takes_the_one_block_form_and_stays_bit_exact():
+    """More than 96 rows go through the one-block-per-row kernel, fewer through the cluster of 8 blocks per row: same tokens."""
+    eng = E.Engine(util.weights("micro"), E.EngineConfig(max_seqs=2, max_step_tokens=128, max_chunk=8, global_kv_tokens=64, max_seq_len=64, max_head_rows=128))
+    v = eng.desc.vocab
+    rng = np.random.default_rng(17)
+    n = 128
+    logits = (rng.standard_normal((n, v)) * 3.0).astype(np.float32)
+    rows = _rows(n, rng, [0.0, 0.6, 1.0, 3.0], [1.0, 0.95, 0.5, 0.05])
+    many = eng.sample_logits(logits, rows)
+    assert np.array_equal(many, oracle.sample(logits, _oracle_rows(rows)))
+    few = np.concatenate([eng.sample_logits(logits[i:i + 64], rows[i:i + 64]) for i in (0, 64)])
+    assert np.array_equal(few, many)
+
+
 def test_generator_reproduces_plain_decoding():
     """Continuous batching with replay drafts, greedy: every request's tokens are what the oracle
     decodes one token at a time (the reference's own check, cli/src/bench_spec.rs:133-139)."""
