@@ -188,8 +188,9 @@ __device__ __forceinline__ float ld_cluster(uint32_t addr) {
 }
 
 // grid: (m / 128) * splits blocks in clusters of `splits`. A cluster owns a 128-row weight tile;
-// its blocks each stream a slice of k into their own TMEM accumulator, put it in shared memory,
-// and each then adds up, over distributed shared memory and in rank order, the rows it owns.
+// its blocks each stream a slice of k into their own TMEM accumulator, send every group of 16 tokens
+// to the block that finishes it (stores into its shared memory), and each then adds up, in rank
+// order, the groups it owns.
 template <bool INT8, uint32_t EPI>
 __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
     extern __shared__ uint8_t smem_raw[];
@@ -202,7 +203,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     const uint32_t n_pad = a.n_pad, CA = a.stages_a, CB = a.stages_b, R = INT8 ? a.raw_stages : 0, splits = a.splits;
     const uint32_t a_bytes = BM * BK * 2, b_bytes = n_pad * BK * 2, raw_bytes = BM * BK;
     const uint32_t a_region = INT8 ? 0 : CA * a_bytes;
-    const uint32_t ring_bytes = max(a_region + CB * b_bytes + R * raw_bytes, (BM + BM / 2) * (n_pad + 1) * 4);  // the partial tile and the sums reuse the rings
+    // The split-k exchange buffer reuses the rings: [splits][groups of 16 tokens a block finishes][16][128] floats.
+    const uint32_t ring_bytes = max(a_region + CB * b_bytes + R * raw_bytes, splits * ((n_pad / 16) / splits + 1) * 16 * BM * 4);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes);
     // a_full[CA], a_empty[CA], b_full[CB], b_empty[CB], raw_full[R], raw_empty[R], then the accumulator's barrier
     const uint32_t bar_afull = smem_u32(bars), bar_aempty = bar_afull + 8 * CA, bar_bfull = bar_aempty + 8 * CA, bar_bempty = bar_bfull + 8 * CB,
@@ -362,10 +364,6 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         }
     }
 
-    // Rows this block finishes: an even share of the tile's 64 row pairs (a gate/up pair stays together).
-    const uint32_t u_begin = rank * (64 / splits) + min(rank, 64 % splits), u_count = 64 / splits + (rank < 64 % splits ? 1 : 0);
-    const uint32_t r_begin = 2 * u_begin, r_end = r_begin + 2 * u_count;
-    const uint32_t pitch = n_pad + 1;
     const MatArgs& m = a.m;
     const uint32_t ew = warp - FIRST_CONV;
 
@@ -373,17 +371,18 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     // code of a fat, fully unrolled epilogue does not stay in the instruction cache). The residual's
     // loads go out together before the first store (it may alias the output); 1/rms comes from
     // shared memory.
-    auto emit = [&](uint32_t r, bool valid, uint32_t t0, float scale, float (&v)[16]) {
+    auto emit = [&](uint32_t r, bool valid, uint32_t t0, float scale, auto& v) {  // v: 16 or 8 consecutive tokens of row r
+        constexpr uint32_t NTOK = sizeof(v) / sizeof(float);
         const uint32_t row = row0 + r;
-        // Loads first, then the arithmetic, then the stores: in that order the 16 tokens overlap.
-        float base[16], inv[16], y[16];
+        // Loads first, then the arithmetic, then the stores: in that order the tokens overlap.
+        float base[NTOK], inv[NTOK], y[NTOK];
 #pragma unroll
-        for (uint32_t j = 0; j < 16; j++) {
+        for (uint32_t j = 0; j < NTOK; j++) {
             inv[j] = inv_s[t0 + j];
             base[j] = (EPI == EPI_RESID && valid && t0 + j < m.n) ? m.base[size_t(t0 + j) * m.m + row] : 0.0f;
         }
 #pragma unroll
-        for (uint32_t j = 0; j < 16; j++) {
+        for (uint32_t j = 0; j < NTOK; j++) {
             const float x = v[j] * scale;
             if (EPI == EPI_SWIGLU) {
                 const float other = __shfl_xor_sync(0xffffffffu, x, 1);
@@ -398,7 +397,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         const uint32_t out_w = EPI == EPI_SWIGLU ? m.m / 2 : m.m, out_r = EPI == EPI_SWIGLU ? row / 2 : row;
         if (writes) {
 #pragma unroll
-            for (uint32_t j = 0; j < 16; j++)
+            for (uint32_t j = 0; j < NTOK; j++)
                 if (t0 + j < m.n) {
                     const size_t o = size_t(t0 + j) * out_w + out_r;
                     if (m.Y) m.Y[o] = y[j];
@@ -419,15 +418,11 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             // The warps that share a quarter of the TMEM lanes (rows) take groups of 16 tokens in turn.
             const uint32_t quarter = warp & 3, half = ew >> 2, r = quarter * 32 + lane;
             const float scale = INT8 ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
-            float* part = reinterpret_cast<float*>(smem) + size_t(r) * pitch;
-            for (uint32_t c0 = 16 * half; c0 < n_pad; c0 += 16 * (CONV_WARPS / 4)) {
-                float acc[16];
-                tmem_ld16(tmem_base + ((quarter * 32) << 16) + c0, acc);
-                if (splits == 1) {
-                    emit(r, true, c0, scale, acc);  // no other block adds to this tile: straight out
-                } else {
-#pragma unroll
-                    for (uint32_t j = 0; j < 16; j++) part[c0 + j] = acc[j];  // fp32 [128][n_pad + 1]: the ring is free once the MMAs are done
+            if (splits == 1) {  // no other block adds to this tile: straight out
+                for (uint32_t c0 = 16 * half; c0 < n_pad; c0 += 16 * (CONV_WARPS / 4)) {
+                    float acc[16];
+                    tmem_ld16(tmem_base + ((quarter * 32) << 16) + c0, acc);
+                    emit(r, true, c0, scale, acc);
                 }
             }
         }
@@ -440,50 +435,51 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     __syncthreads();
     if (tid == FIRST_CONV * 32) PROBE(7, 2);
     if (splits > 1) {
-        cluster_sync();  // every block's partial is in place
+        // Split k: the cluster's blocks share out the tile's groups of 16 tokens. Every block sends each group
+        // of its partial tile to the block that finishes it -- stores into that block's shared memory, which
+        // unlike loads from it wait for no round trip, 128 contiguous bytes per warp (a lane is a row, the
+        // buffer is [source rank][group][token][row]) -- and then adds up, in rank order (deterministic), what
+        // it was sent. The buffer reuses the rings, so the first cluster barrier says "my MMAs are done, my
+        // rings may be written"; after the second nobody touches another block's shared memory again.
+        const uint32_t chunks = n_pad / 16, qc = chunks / splits, remc = chunks % splits, slot = qc + 1;
+        cluster_sync();
         if (tid == FIRST_CONV * 32) PROBE(7, 3);
-        // Each block finishes its share of the rows. First their sums over the cluster's partials, into a
-        // second buffer: a warp reads a row's tokens, contiguous in the other block's shared memory, and
-        // adds the ranks up in order (deterministic). Then a lane takes a row and emits 32 tokens at a time.
-        float* sums = reinterpret_cast<float*>(smem) + size_t(BM) * pitch;
         if (warp >= FIRST_CONV && !*abort_flag) {
-            uint32_t remote[8];
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t quarter = warp & 3, half = ew >> 2, r = quarter * 32 + lane;
+            for (uint32_t ch = half; ch < chunks; ch += CONV_WARPS / 4) {
+                float acc[16];
+                tmem_ld16(tmem_base + ((quarter * 32) << 16) + 16 * ch, acc);
+                uint32_t owner, lc;
+                if (ch < remc * (qc + 1)) { owner = ch / (qc + 1); lc = ch % (qc + 1); }
+                else { owner = remc + (ch - remc * (qc + 1)) / qc; lc = (ch - remc * (qc + 1)) % qc; }
+                const uint32_t dst = map_to_rank(smem_base + (((rank * slot + lc) * 16) * BM + r) * 4, owner);
 #pragma unroll
-            for (uint32_t s = 0; s < 8; s++) remote[s] = s < splits ? map_to_rank(smem_base, s) : 0;  // (also orders the loads below after the barrier)
-            // A row at a time: all of its tokens' loads from every rank go out together (n_pad <= 256: 8 chunks of 32).
-            for (uint32_t r = r_begin + ew; r < r_end; r += CONV_WARPS) {
-                float v[8];
-#pragma unroll
-                for (uint32_t c = 0; c < 8; c++) v[c] = 0.0f;
-#pragma unroll
-                for (uint32_t s = 0; s < 8; s++)
-                    if (s < splits) {
-#pragma unroll
-                        for (uint32_t c = 0; c < 8; c++)
-                            if (32 * c + lane < n_pad) v[c] += ld_cluster(remote[s] + (r * pitch + 32 * c + lane) * 4);
-                    }
-#pragma unroll
-                for (uint32_t c = 0; c < 8; c++)
-                    if (32 * c + lane < n_pad) sums[(r - r_begin) * pitch + 32 * c + lane] = v[c];
+                for (uint32_t j = 0; j < 16; j++) asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + j * BM * 4), "f"(acc[j]) : "memory");
             }
         }
-        __syncthreads();
         if (tid == FIRST_CONV * 32) PROBE(7, 4);
+        cluster_sync();  // every partial is where it will be added up
         if (warp >= FIRST_CONV && !*abort_flag) {
-            const uint32_t chunks = n_pad / 16, n_rg = (r_end - r_begin + 31) / 32;
-            for (uint32_t item = ew; item < chunks * n_rg; item += CONV_WARPS) {
-                const uint32_t r = r_begin + 32 * (item / chunks) + lane, c0 = 16 * (item % chunks);
-                const bool valid = r < r_end;
-                const float scale = (INT8 && valid) ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
-                float v[16];
+            const float* buf = reinterpret_cast<const float*>(smem);
+            const uint32_t ch_begin = rank * qc + min(rank, remc), ch_count = qc + (rank < remc ? 1 : 0);
+            // An item: 32 rows x 8 tokens (half a group), so that two groups a block already keep all its warps busy.
+            for (uint32_t item = ew; item < ch_count * 2 * (BM / 32); item += CONV_WARPS) {
+                const uint32_t lc = item / (2 * (BM / 32)), hf = (item / (BM / 32)) & 1, r = 32 * (item % (BM / 32)) + lane;
+                const float scale = INT8 ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
+                float v[8];
 #pragma unroll
-                for (uint32_t j = 0; j < 16; j++) v[j] = valid ? sums[(r - r_begin) * pitch + c0 + j] : 0.0f;
-                emit(r, valid, c0, scale, v);
+                for (uint32_t j = 0; j < 8; j++) v[j] = 0.0f;
+                for (uint32_t sr = 0; sr < splits; sr++) {
+                    const float* src = buf + size_t((sr * slot + lc) * 16 + 8 * hf) * BM + r;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; j++) v[j] += src[j * BM];
+                }
+                emit(r, true, 16 * (ch_begin + lc) + 8 * hf, scale, v);
             }
         }
     }
     if (tid == FIRST_CONV * 32) PROBE(7, 5);
-    if (splits > 1) cluster_sync();  // nobody leaves while its shared memory may still be read
     __syncthreads();
     if (tid == FIRST_CONV * 32) PROBE(7, 6);
     if (warp == 1) {
@@ -542,7 +538,8 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     } else {
         stages_a = stages_b = std::max(2u, std::min(8u, budget / (a_bytes + b_bytes)));
     }
-    const uint32_t ring = std::max((a.int8 ? 0 : stages_a * a_bytes) + stages_b * b_bytes + raw_stages * raw_bytes, (gemm::BM + gemm::BM / 2) * (n_pad + 1) * 4);
+    const uint32_t ring = std::max((a.int8 ? 0 : stages_a * a_bytes) + stages_b * b_bytes + raw_stages * raw_bytes,
+                                   (n_pad / 16 + 8) * 16 * gemm::BM * 4);  // the split-k exchange buffer at its largest (8 splits)
     // At least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
     // behind another one (blocks of different clusters waiting on each other's SMs could deadlock).
     const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4, 116 * 1024);
