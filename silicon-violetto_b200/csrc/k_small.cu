@@ -176,14 +176,20 @@ void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* t
 // ------------------------------------------------------------ split merge
 // kernels.metal:1314-1362 `attn_dec_reduce`, with a running maximum: the partials of a
 // (token, head) are (m, l, o[64]) per key split; out = sum(o_s 2^(m_s - M)) / sum(l_s 2^(m_s - M)).
-// One block of 64 threads per (token, head).
+// One block per token and four heads, 64 threads a head.
 // Splits past a tile's keys hold m = -inf (the attention kernel writes every slot).
-__global__ void __launch_bounds__(64) attn_combine_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out, uint16_t* out_b) {
+// COMBINE_HEADS heads per block, 64 threads each: four when there are blocks enough to fill the GPU anyway (fewer,
+// fatter blocks schedule faster), one otherwise.
+template <uint32_t COMBINE_HEADS>
+__global__ void __launch_bounds__(64 * COMBINE_HEADS) attn_combine_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out,
+                                                                          uint16_t* out_b) {
     pdl_start();
-    __shared__ float ws[64];   // the splits' weights 2^(m_s - M), 0 for an empty split
-    __shared__ float red[4];
-    const uint32_t t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    const float* pp = part + (size_t(t) * n_heads + h) * max_splits * ATTN_PART;
+    __shared__ float ws[COMBINE_HEADS][64];   // the splits' weights 2^(m_s - M), 0 for an empty split
+    __shared__ float lws[COMBINE_HEADS][64];  // l_s times that
+    __shared__ float red[COMBINE_HEADS][2];
+    const uint32_t t = blockIdx.x, hl = threadIdx.x / 64, h = blockIdx.y * COMBINE_HEADS + hl, d = threadIdx.x % 64;
+    const bool live = h < n_heads;
+    const float* pp = part + (size_t(t) * n_heads + (live ? h : 0)) * max_splits * ATTN_PART;
     // A thread per split for the statistics (at most 64 splits, engine.cu `attention_split`), then a thread
     // per dim with the splits' loads independent of each other.
     const bool has = d < max_splits;
@@ -192,22 +198,21 @@ __global__ void __launch_bounds__(64) attn_combine_kernel(const float* __restric
     float mm = ms;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
-    if (d % 32 == 0) red[d / 32] = mm;
+    if (d % 32 == 0) red[hl][d / 32] = mm;
     __syncthreads();
-    mm = fmaxf(red[0], red[1]);
+    mm = fmaxf(red[hl][0], red[hl][1]);
     const float w = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
-    ws[d] = w;
-    float lw = ls * w;  // summed in split order below, so that the result does not depend on the warp layout
-    __shared__ float lws[64];
-    lws[d] = lw;
+    ws[hl][d] = w;
+    lws[hl][d] = ls * w;  // summed in split order below, so that the result does not depend on the warp layout
     __syncthreads();
     float ll = 0.0f, oo = 0.0f;
-    for (uint32_t s = 0; s < max_splits; s++) ll += lws[s];
+    for (uint32_t s = 0; s < max_splits; s++) ll += lws[hl][s];
 #pragma unroll 8
     for (uint32_t s = 0; s < max_splits; s++) {
         const float v = pp[s * ATTN_PART + 4 + d];  // an empty split's o was never written: whatever is there must not count
-        oo += ws[s] == 0.0f ? 0.0f : v * ws[s];
+        oo += ws[hl][s] == 0.0f ? 0.0f : v * ws[hl][s];
     }
+    if (!live) return;
     const float r = oo / ll;
     const size_t at = size_t(t) * n_heads * 64 + h * 64 + d;
     out[at] = r;
@@ -215,7 +220,8 @@ __global__ void __launch_bounds__(64) attn_combine_kernel(const float* __restric
 }
 
 void launch_attn_combine(const AttnArgs& a, cudaStream_t s) {
-    launch_pdl(attn_combine_kernel, dim3(a.n, a.n_heads), 64, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
+    if (a.n * a.n_heads >= 2048) launch_pdl(attn_combine_kernel<4>, dim3(a.n, (a.n_heads + 3) / 4), 256, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
+    else launch_pdl(attn_combine_kernel<1>, dim3(a.n, a.n_heads), 64, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
 }
 
 // ------------------------------------------------------------- row preparation
