@@ -86,6 +86,30 @@ def test_forward_logits_match_the_oracle(name, int8_group):
     print(f"{name} int8_group={int8_group}: worst logits error {worst:.2e}")
 
 
+@pytest.mark.parametrize("int8_group", [None, 0])
+def test_full_width_steps_match_the_oracle(int8_group):
+    """The benchmark's step shapes through the tensor-core GEMM: 32 sequences x 8 tokens = 256 tokens in one step
+    (the GEMM's widest N), then verify-shaped steps of 32 x 5 = 160 rows with every row through the head."""
+    prod, orc = pair("micro", int8_group, max_seqs=32, max_step_tokens=256, max_chunk=16, global_kv_tokens=32 * 64, max_seq_len=64, max_head_rows=160)
+    rng = np.random.default_rng(23)
+    seqs = [prod.new_seq() for _ in range(32)]
+    assert [orc.new_seq() for _ in range(32)] == seqs
+    vocab = prod.desc.vocab
+    prompts = [rng.integers(0, vocab, 8).astype(np.uint32) for _ in seqs]
+    both_step(prod, orc, [(s, p, E.Rows.NONE if i % 4 else E.Rows.LAST, False) for i, (s, p) in enumerate(zip(seqs, prompts))], TOL[int8_group])
+    same_state(prod, orc, 32, 256)
+    for step in range(2):
+        runs = [(s, rng.integers(0, vocab, 5).astype(np.uint32), E.Rows.ALL, False) for s in seqs]
+        out, want, err = both_step(prod, orc, runs, TOL[int8_group])
+        assert want.shape[0] == 160
+        top2 = np.sort(want, axis=1)[:, -2:]
+        clear = top2[:, 1] - top2[:, 0] > 1e-2
+        assert np.array_equal(out.ids[clear], orc.array("out_ids")[clear]) and clear.mean() > 0.5
+        for name_ in ("lens", "page_table", "free_pages", "meta"):
+            assert np.array_equal(prod.debug_read(name_)[:len(orc.array(name_))], orc.array(name_)), name_
+        print(f"160-row step, int8_group={int8_group}: logits error {err:.2e}")
+
+
 def test_kv_cache_matches_the_oracle_after_prefill():
     prod, orc = pair("micro")
     a, b = prod.new_seq(), orc.new_seq()
