@@ -67,7 +67,7 @@ inline Matrix load_matrix(const VltFile& f, const std::string& name, uint32_t m,
     const Tensor& s = f.tensor(name + ".scale");
     const uint32_t groups = s.shape.size() > 1 ? s.shape[1] : 0;
     const uint32_t group = k / std::max(groups, 1u);
-    if (group < 8 || (group & (group - 1)) || group * groups != k) throw std::runtime_error(name + ".scale: bad group count");
+    if (group < 8 || (groups > 1 && (group & (group - 1))) || group * groups != k) throw std::runtime_error(name + ".scale: bad group count");
     out.scales = reinterpret_cast<const uint16_t*>(f.ptr(f.get(name + ".scale", BF16, {m, groups})));
     out.group = group;
     out.int8 = true;

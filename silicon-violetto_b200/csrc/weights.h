@@ -127,7 +127,8 @@ inline Matrix load_matrix(const Weights& w, const std::string& name, uint32_t m,
     const Tensor& st = w.tensor(sn);
     const uint32_t groups = st.shape.size() > 1 ? st.shape[1] : 0;
     const uint32_t group = k / std::max(groups, 1u);
-    if (group < 8 || (group & (group - 1)) || group * groups != k) throw Error(sn + ": " + std::to_string(groups) + " groups per row of " + std::to_string(k));
+    // Groups of a power of two, or one scale per row whatever k is.
+    if (group < 8 || (groups > 1 && (group & (group - 1))) || group * groups != k) throw Error(sn + ": " + std::to_string(groups) + " groups per row of " + std::to_string(k));
     out.scales = reinterpret_cast<const uint16_t*>(base + w.get(sn, DType::Bf16, {m, groups}).offset);
     out.group = group;
     out.int8 = true;

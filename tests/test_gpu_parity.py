@@ -110,6 +110,28 @@ def test_full_width_steps_match_the_oracle(int8_group):
         print(f"160-row step, int8_group={int8_group}: logits error {err:.2e}")
 
 
+@pytest.mark.parametrize("int8_group", [None, 0])
+def test_wide_matrices_take_the_unsplit_gemm_path(int8_group):
+    """gate_up with 80 and a head with 96 tiles of 128 rows: more than half the SMs, so the GEMM keeps a tile's
+    whole k in one block and its epilogue goes straight from tensor memory to global memory (SwiGLU and head);
+    the narrow matrices of the same model still split k over clusters."""
+    cfg = dict(util.MICRO, n_layers=1, ffn=5120, vocab=12288)
+    w = util.weights_custom("wide_ffn", cfg, int8_group)
+    kw = dict(max_seqs=8, max_step_tokens=64, max_chunk=16, max_seq_len=64, max_head_rows=64)
+    prod = E.Engine(w, E.EngineConfig(global_kv_tokens=8 * 64, **kw))
+    orc = oracle.Engine(w, kv_tokens=8 * 64, **kw)
+    rng = np.random.default_rng(29)
+    seqs = [prod.new_seq() for _ in range(8)]
+    assert [orc.new_seq() for _ in range(8)] == seqs
+    for count in (8, 5, 3):  # 64, 40 and 24 tokens a step, every row through the head
+        runs = [(s, rng.integers(0, cfg["vocab"], count).astype(np.uint32), E.Rows.ALL, False) for s in seqs]
+        out, want, err = both_step(prod, orc, runs, TOL[int8_group])
+        top2 = np.sort(want, axis=1)[:, -2:]
+        clear = top2[:, 1] - top2[:, 0] > 1e-2
+        assert np.array_equal(out.ids[clear], orc.array("out_ids")[clear]) and clear.mean() > 0.5
+        print(f"{8 * count}-token step over wide matrices, int8_group={int8_group}: logits error {err:.2e}")
+
+
 def test_kv_cache_matches_the_oracle_after_prefill():
     prod, orc = pair("micro")
     a, b = prod.new_seq(), orc.new_seq()
