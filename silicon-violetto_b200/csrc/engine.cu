@@ -373,7 +373,7 @@ bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
 }
 
 void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
-                         uint32_t vocab_real) {
+                         uint32_t vocab_real, const QkvEpilogue* q) {
     MatArgs a{};
     a.W = w.w;
     a.scales = w.scales;
@@ -390,6 +390,7 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
     a.epi = epi;
     a.vocab_real = vocab_real ? vocab_real : model.md.vocab_real;
     a.eps = model.md.eps;
+    if (q) a.q = *q;
     if (!gemm_supported(a)) throw Error("internal: GEMM asked for an unsupported shape");
     launch_gemm(a, sm_count, s.err_flag.as<uint32_t>(), stream);
 }
@@ -424,20 +425,40 @@ void Engine::encode_layer_io(const LayerIO& io) {
     // Steps of 16 tokens or more multiply on tcgen05: activations go in as bf16 copies and 1/rms
     // comes from a row pass, since the GEMM does not see whole rows of X.
     const bool big = use_gemm(l.qkv, n) && use_gemm(l.o, n) && use_gemm(l.gate_up, n) && use_gemm(l.down, n);
+    const KvArgs kva = kv_args();
+    const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
+    // With the tensor-core GEMM the qkv projection's epilogue does what qkv_post does (RoPE, q for the attention,
+    // K/V into the cache); the scalar attention reads fp32 q, so that path keeps the separate kernel.
+    const bool fused_post = big && !tuning.plain_attention;
     int sp = span_begin(G_MATMUL);
     if (!(skip & 1)) {
         if (big) {
             launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
-            matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>());
+            if (fused_post) {
+                QkvEpilogue q{};
+                q.meta = io.meta;
+                q.tin = io.tin;
+                q.cpos = io.cpos;
+                q.rope = rope_tab.as<float>();
+                q.page_table = kv.page_table.as<uint32_t>();
+                q.kv = kva;
+                q.layer = li;
+                q.n_heads = md.n_heads;
+                q.scale_log2 = scale_log2;
+                q.q_b = s.q_b.as<uint16_t>();
+                q.k_cache = io.k_cache;
+                q.v_cache = io.v_cache;
+                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), nullptr, nullptr, EPI_QKV, nullptr, s.inv.as<float>(), 0, &q);
+            } else {
+                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>());
+            }
         } else {
             matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
         }
     }
     span_end(sp);
-    const KvArgs kva = kv_args();
-    const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
     sp = span_begin(G_SMALL);
-    if (!(skip & 2))
+    if (!(skip & 2) && !fused_post)
         launch_qkv_post(s.qkv.as<float>(), io.meta, io.tin, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva, li, n,
                         md.n_heads, scale_log2, tuning.plain_attention ? nullptr : s.q_b.as<uint16_t>(), io.cpos, stream);
     span_end(sp);

@@ -193,7 +193,7 @@ class Engine {
     void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real = 0);
     // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
     void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
-                     uint32_t vocab_real = 0);
+                     uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr);
     bool use_gemm(const Matrix& w, uint32_t n) const;
     // What a decoder layer runs on: its weights, the step layout (device arrays), the cache it writes and reads.
     struct LayerIO {

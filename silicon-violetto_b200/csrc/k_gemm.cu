@@ -212,6 +212,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * CA + 2 * CB + 2 * R + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* inv_s = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);  // 1/rms per token
+    uint32_t* pos_s = reinterpret_cast<uint32_t*>(inv_s + n_pad);                    // EPI_QKV: the token's position ...
+    uint32_t* kvrow_s = pos_s + n_pad;  // ... and the cache row (of 64 elements) of its kv head 0, NO_TOK if it writes none
     const uint32_t smem_base = smem_u32(smem);
     auto stage_a = [&](uint32_t c) { return smem_base + c * a_bytes; };
     auto stage_b = [&](uint32_t c) { return smem_base + a_region + c * b_bytes; };
@@ -374,6 +376,42 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     auto emit = [&](uint32_t r, bool valid, uint32_t t0, float scale, auto& v) {  // v: 16 or 8 consecutive tokens of row r
         constexpr uint32_t NTOK = sizeof(v) / sizeof(float);
         const uint32_t row = row0 + r;
+        if constexpr (EPI == EPI_QKV) {
+            // The row is feature `row` of the qkv projection: dim d of a q, k or v head (whole heads per 64 rows, so
+            // a warp's 32 rows are of one kind). RoPE pairs are neighbouring rows, i.e. neighbouring lanes.
+            const QkvEpilogue& qe = m.q;
+            const uint32_t head = row / 64, d = row % 64, odd = lane & 1;
+            const uint32_t kind = head < qe.n_heads ? 0u : head < qe.n_heads + qe.kv.n_kv ? 1u : 2u;  // q, k, v
+            const uint32_t psize = 1u << qe.kv.page_shift;
+            float x[NTOK];
+            float2 cs[NTOK];
+#pragma unroll
+            for (uint32_t j = 0; j < NTOK; j++) {
+                x[j] = (v[j] * scale) * inv_s[t0 + j];
+                cs[j] = kind < 2 ? reinterpret_cast<const float2*>(qe.rope)[size_t(pos_s[t0 + j]) * 32 + d / 2] : make_float2(1.0f, 0.0f);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < NTOK; j++) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[j], 1);
+                float y = x[j];
+                if (kind < 2) {  // (cos a + sin b, cos b - sin a) for the pair (a, b): kernels.metal:727-736
+                    const float mine = __fmul_rn(cs[j].x, x[j]), cross = __fmul_rn(cs[j].y, other);
+                    y = odd ? __fsub_rn(mine, cross) : __fadd_rn(mine, cross);
+                    if (kind == 0) y = __fmul_rn(y, qe.scale_log2);
+                }
+                const uint32_t bits = f32_to_bf16(y), pair = bits | (__shfl_xor_sync(0xffffffffu, bits, 1) << 16);
+                const uint32_t t = t0 + j;
+                if (!valid || odd || t >= m.n) continue;  // the even lane writes the pair
+                if (kind == 0) {
+                    *reinterpret_cast<uint32_t*>(qe.q_b + (size_t(t) * qe.n_heads + head) * 64 + d) = pair;
+                } else if (kvrow_s[t] != NO_TOK) {
+                    const uint32_t g = kind == 1 ? head - qe.n_heads : head - qe.n_heads - qe.kv.n_kv;
+                    uint16_t* cache = kind == 1 ? qe.k_cache : qe.v_cache;
+                    *reinterpret_cast<uint32_t*>(cache + (size_t(kvrow_s[t]) + size_t(g) * psize) * 64 + d) = pair;
+                }
+            }
+            return;
+        }
         // Loads first, then the arithmetic, then the stores: in that order the tokens overlap.
         float base[NTOK], inv[NTOK], y[NTOK];
 #pragma unroll
@@ -408,7 +446,24 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
 
     if (warp >= FIRST_CONV) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
+        for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) {
+            inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
+            if (EPI == EPI_QKV) {
+                const QkvEpilogue& qe = a.m.q;
+                uint32_t pos = 0, kvrow = NO_TOK;
+                if (t < a.m.n) {
+                    const uint32_t slot = qe.meta[2 * t], row = qe.tin[2 * t + 1];
+                    pos = qe.meta[2 * t + 1];
+                    const uint32_t cp = qe.cpos ? qe.cpos[t] : qe.meta[2 * (t - row) + 1] + row;  // kernels.metal:74-77 `cache_pos`
+                    if (cp != NO_TOK) {
+                        const uint32_t page = qe.page_table[size_t(slot) * qe.kv.max_pages + (cp >> qe.kv.page_shift)], psize = 1u << qe.kv.page_shift;
+                        kvrow = ((qe.layer * qe.kv.n_pages + page) * qe.kv.n_kv) * psize + (cp & (psize - 1));
+                    }
+                }
+                pos_s[t] = pos;
+                kvrow_s[t] = kvrow;
+            }
+        }
         asm volatile("bar.sync 1, %0;" ::"n"(32 * CONV_WARPS) : "memory");  // the epilogue warps only
         if (tid == FIRST_CONV * 32) PROBE(7, 0);
         if (ok) ok = wait_or_abort(bar_accum, 0, abort_flag);
@@ -502,6 +557,7 @@ static GemmEntry gemm_entry(bool int8, uint32_t epi) {
     case EPI_RESID: return int8 ? gemm::gemm_kernel<true, EPI_RESID> : gemm::gemm_kernel<false, EPI_RESID>;
     case EPI_SWIGLU: return int8 ? gemm::gemm_kernel<true, EPI_SWIGLU> : gemm::gemm_kernel<false, EPI_SWIGLU>;
     case EPI_HEAD: return int8 ? gemm::gemm_kernel<true, EPI_HEAD> : gemm::gemm_kernel<false, EPI_HEAD>;
+    case EPI_QKV: return int8 ? gemm::gemm_kernel<true, EPI_QKV> : gemm::gemm_kernel<false, EPI_QKV>;
     default: return int8 ? gemm::gemm_kernel<true, EPI_RAW> : gemm::gemm_kernel<false, EPI_RAW>;
     }
 }
@@ -542,10 +598,10 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
                                    (n_pad / 16 + 8) * 16 * gemm::BM * 4);  // the split-k exchange buffer at its largest (8 splits)
     // At least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
     // behind another one (blocks of different clusters waiting on each other's SMs could deadlock).
-    const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 4, 116 * 1024);
+    const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 12, 116 * 1024);
     if (!configured) {
         for (int i8 = 0; i8 < 2; i8++)
-            for (uint32_t epi = EPI_NORM; epi <= EPI_RAW; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            for (uint32_t epi = EPI_NORM; epi <= EPI_QKV; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
     // Split k over a cluster when the tiles alone cannot fill the SMs (the reference splits K the

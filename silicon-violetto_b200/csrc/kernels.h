@@ -9,7 +9,24 @@
 namespace vlt {
 
 // Epilogues of a matmul, engine/src/engine/kernels.rs:3-9 and kernels.metal:154-209.
-enum : uint32_t { EPI_NORM = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_HEAD = 4, EPI_RAW = 5 };
+enum : uint32_t { EPI_NORM = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_HEAD = 4, EPI_RAW = 5, EPI_QKV = 6 };
+
+// What the tensor-core GEMM's EPI_QKV epilogue needs to finish the qkv projection the way `qkv_post` does
+// (kernels.metal:749-801): RoPE on q and k, q scaled and rounded to bf16 for the attention, k and v rounded
+// into the paged cache at each token's position.
+struct QkvEpilogue {
+    const uint32_t* meta;        // (slot, position) per token
+    const uint32_t* tin;         // (slot, row in its run) per token
+    const uint32_t* cpos;        // optional: cache position per token (NO_TOK: no write); NULL: its run's first position + its row
+    const float* rope;           // [position][head_dim / 2] (cos, sin)
+    const uint32_t* page_table;
+    KvArgs kv;
+    uint32_t layer, n_heads;
+    float scale_log2;
+    uint16_t* q_b;               // [token][head][head_dim] bf16
+    uint16_t* k_cache;
+    uint16_t* v_cache;
+};
 
 // Y[t][row] = epilogue(W[row] . bf16(X[t])). X fp32 [n][k]; Y fp32 (SWIGLU: [n][m/2]).
 struct MatArgs {
@@ -26,6 +43,7 @@ struct MatArgs {
     uint32_t epi, vocab_real;
     float eps;
     bool int8;
+    QkvEpilogue q;  // EPI_QKV only
 };
 
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
