@@ -131,6 +131,7 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
         s.h_b.alloc(n16 * md.d * 2, false);
         s.attn_b.alloc(n16 * md.n_heads * md.hd * 2, false);
         s.q_b.alloc(n16 * md.n_heads * md.hd * 2, false);
+        s.ssq.alloc(size_t(md.d / 128 + 1) * n16 * 4, false);
         s.act_b.alloc(n16 * md.ffn * 2, false);
         s.hfin_b.alloc(hr16 * md.d * 2, false);
         f(s.inv_head, hr);
@@ -373,7 +374,7 @@ bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
 }
 
 void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
-                         uint32_t vocab_real, const QkvEpilogue* q) {
+                         uint32_t vocab_real, const QkvEpilogue* q, float* ssq_out, const float* ssq_in) {
     MatArgs a{};
     a.W = w.w;
     a.scales = w.scales;
@@ -391,6 +392,10 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
     a.vocab_real = vocab_real ? vocab_real : model.md.vocab_real;
     a.eps = model.md.eps;
     if (q) a.q = *q;
+    a.ssq_out = ssq_out;
+    a.ssq_in = ssq_in;
+    a.ssq_tiles = ssq_in ? w.k / 128 : 0;
+    a.ssq_stride = (cfg.max_step_tokens + 15) / 16 * 16;
     if (!gemm_supported(a)) throw Error("internal: GEMM asked for an unsupported shape");
     launch_gemm(a, sm_count, s.err_flag.as<uint32_t>(), stream);
 }
@@ -400,6 +405,7 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     StepSet& st = sets[set];
     LayerIO io{};
     io.l = &model.layers[li];
+    io.h_ready = li > 0;  // the layer before ended with the down GEMM (if the step is wide enough for the GEMM at all)
     io.n = p.n;
     io.meta = s.meta.as<uint32_t>();
     io.tin = st.in<uint32_t>(st.o_tin);
@@ -433,7 +439,11 @@ void Engine::encode_layer_io(const LayerIO& io) {
     int sp = span_begin(G_MATMUL);
     if (!(skip & 1)) {
         if (big) {
-            launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            // 1/rms of the rows: from the sums of squares the GEMM before left (o or down of the layer before), else a row pass.
+            const bool carried = io.h_ready && md.d % 128 == 0;
+            if (!carried) launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            const float* inv_in = carried ? nullptr : s.inv.as<float>();
+            const float* ssq_in = carried ? s.ssq.as<float>() : nullptr;
             if (fused_post) {
                 QkvEpilogue q{};
                 q.meta = io.meta;
@@ -448,9 +458,9 @@ void Engine::encode_layer_io(const LayerIO& io) {
                 q.q_b = s.q_b.as<uint16_t>();
                 q.k_cache = io.k_cache;
                 q.v_cache = io.v_cache;
-                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), nullptr, nullptr, EPI_QKV, nullptr, s.inv.as<float>(), 0, &q);
+                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), nullptr, nullptr, EPI_QKV, nullptr, inv_in, 0, &q, nullptr, ssq_in);
             } else {
-                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>());
+                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, inv_in, 0, nullptr, nullptr, ssq_in);
             }
         } else {
             matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
@@ -499,12 +509,18 @@ void Engine::encode_layer_io(const LayerIO& io) {
     }
     sp = span_begin(G_MATMUL);
     if (big) {
-        if (!(skip & 16)) matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), h, nullptr, EPI_RESID, h, nullptr);
+        // The residual GEMMs leave bf16(h) and h's sums of squares per 128-row tile for the GEMM after them (gate_up here,
+        // the next layer's qkv after down): no row pass in between.
+        const bool carry = md.d % 128 == 0;
+        float* ssq = carry ? s.ssq.as<float>() : nullptr;
+        uint16_t* hb = carry ? s.h_b.as<uint16_t>() : nullptr;
+        if (!(skip & 16)) matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), h, hb, EPI_RESID, h, nullptr, 0, nullptr, ssq);
         if (!(skip & 32)) {
-            launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
-            matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, s.inv.as<float>());  // the down GEMM reads the bf16 copy only
+            if (!carry) launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, carry ? nullptr : s.inv.as<float>(), 0, nullptr,
+                        nullptr, ssq);  // the down GEMM reads the bf16 copy only
         }
-        if (!(skip & 64)) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), h, nullptr, EPI_RESID, h, nullptr);
+        if (!(skip & 64)) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), h, hb, EPI_RESID, h, nullptr, 0, nullptr, ssq);
     } else {
         if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr);
         if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);

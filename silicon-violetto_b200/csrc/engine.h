@@ -169,7 +169,7 @@ class Engine {
     // Activations (engine/src/engine/buffers.rs:14-118) and per-slot state on the GPU.
     struct Scratch {
         Buffer h, qkv, attn, act, part, hfin_head, hfin_all, logits, taps, inv, meta;
-        Buffer h_b, attn_b, act_b, hfin_b, inv_head, q_b;  // bf16 copies that feed the tensor-core GEMM, rows padded to 16
+        Buffer h_b, attn_b, act_b, hfin_b, inv_head, q_b, ssq;  // ssq: [d / 128][n] sums of squares of h per 128-row tile (see MatArgs)  // bf16 copies that feed the tensor-core GEMM, rows padded to 16
         Buffer lens, feed, tree, gen, path, path_len, on_path, trace, trace_len, err_flag;
     } s;
     Buffer rope_tab;
@@ -193,13 +193,14 @@ class Engine {
     void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real = 0);
     // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
     void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
-                     uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr);
+                     uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr, float* ssq_out = nullptr, const float* ssq_in = nullptr);
     bool use_gemm(const Matrix& w, uint32_t n) const;
     // What a decoder layer runs on: its weights, the step layout (device arrays), the cache it writes and reads.
     struct LayerIO {
         const Layer* l;
         uint32_t n, n_tiles, layer, keys_per_split, max_splits, max_rows;  // max_rows: the longest tile's rows
         const uint32_t *meta, *tin, *tiles, *vis;
+        bool h_ready;          // the GEMM before this layer left bf16(h) in h_b and its sums of squares in ssq: no row pass before qkv
         const uint32_t* cpos;  // optional, per token: the cache position its K/V go to (NO_TOK: nowhere); NULL: its run's first position + its row
         uint16_t *k_cache, *v_cache;
         const AttnMaps* maps;

@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
     float* inv_s = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);  // 1/rms per token
     uint32_t* pos_s = reinterpret_cast<uint32_t*>(inv_s + n_pad);                    // EPI_QKV: the token's position ...
     uint32_t* kvrow_s = pos_s + n_pad;  // ... and the cache row (of 64 elements) of its kv head 0, NO_TOK if it writes none
+    float* ssq_s = reinterpret_cast<float*>(kvrow_s + n_pad);  // EPI_RESID with ssq_out: [row group of 32][token] sums of y^2
     const uint32_t smem_base = smem_u32(smem);
     auto stage_a = [&](uint32_t c) { return smem_base + c * a_bytes; };
     auto stage_b = [&](uint32_t c) { return smem_base + a_region + c * b_bytes; };
@@ -431,6 +432,27 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
             else if (EPI == EPI_HEAD) y[j] = row < m.vocab_real ? x * inv[j] : -INFINITY;
             else y[j] = x;
         }
+        if (EPI == EPI_RESID && m.ssq_out) {
+            // sum(y^2) over the warp's 32 rows for each of the NTOK tokens: a halving butterfly (lanes trade the half of the
+            // tokens they give up), a fixed tree, so the sums are the same on every run; then the last two levels in place.
+            float w[NTOK];
+#pragma unroll
+            for (uint32_t j = 0; j < NTOK; j++) w[j] = valid ? y[j] * y[j] : 0.0f;
+            uint32_t tk = 0;  // the token (offset in the item) this lane ends up holding
+#pragma unroll
+            for (uint32_t width = NTOK / 2, bit = 16; width >= 1; width /= 2, bit /= 2) {
+                const bool upper = (lane & bit) != 0;
+#pragma unroll
+                for (uint32_t j = 0; j < width; j++) {
+                    const float give = upper ? w[j] : w[j + width], keep = upper ? w[j + width] : w[j];
+                    w[j] = keep + __shfl_xor_sync(0xffffffffu, give, bit);
+                }
+                tk = 2 * tk + (upper ? 1 : 0);
+            }
+#pragma unroll
+            for (uint32_t bit = 16 / NTOK; bit >= 1; bit /= 2) w[0] += __shfl_xor_sync(0xffffffffu, w[0], bit);
+            if ((lane & (32 / NTOK - 1)) == 0) ssq_s[(r / 32) * n_pad + t0 + tk] = w[0];
+        }
         const bool writes = valid && (EPI != EPI_SWIGLU || (lane & 1) == 0);
         const uint32_t out_w = EPI == EPI_SWIGLU ? m.m / 2 : m.m, out_r = EPI == EPI_SWIGLU ? row / 2 : row;
         if (writes) {
@@ -444,10 +466,27 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
         }
     };
 
+    // After a block's emits: its tokens' sums of y^2 over the tile's four row groups, added in order, to global memory.
+    auto write_ssq = [&](uint32_t t_lo, uint32_t t_hi) {
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * CONV_WARPS) : "memory");  // every epilogue warp, whatever happened before: the row groups' sums are in
+        if (*abort_flag) return;
+        for (uint32_t t = t_lo + tid - FIRST_CONV * 32; t < t_hi && t < m.n; t += 32 * CONV_WARPS)
+            m.ssq_out[size_t(tile) * m.ssq_stride + t] = ((ssq_s[t] + ssq_s[n_pad + t]) + ssq_s[2 * n_pad + t]) + ssq_s[3 * n_pad + t];
+    };
+
     if (warp >= FIRST_CONV) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         for (uint32_t t = tid - FIRST_CONV * 32; t < n_pad; t += 32 * CONV_WARPS) {
-            inv_s[t] = (a.m.inv_in && t < a.m.n) ? a.m.inv_in[t] : 1.0f;
+            float inv = 1.0f;
+            if (t < a.m.n) {
+                if (a.m.inv_in) inv = a.m.inv_in[t];
+                else if (a.m.ssq_in) {  // the tiles' sums in tile order
+                    float ss = 0.0f;
+                    for (uint32_t tl = 0; tl < a.m.ssq_tiles; tl++) ss += a.m.ssq_in[size_t(tl) * a.m.ssq_stride + t];
+                    inv = rsqrtf(ss / float(a.m.k) + a.m.eps);
+                }
+            }
+            inv_s[t] = inv;
             if (EPI == EPI_QKV) {
                 const QkvEpilogue& qe = a.m.q;
                 uint32_t pos = 0, kvrow = NO_TOK;
@@ -481,6 +520,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
                 }
             }
         }
+        if (EPI == EPI_RESID && m.ssq_out && splits == 1) write_ssq(0, n_pad);
     }
     if (!ok) {
         *abort_flag = 1;
@@ -533,6 +573,10 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
                 emit(r, true, 16 * (ch_begin + lc) + 8 * hf, scale, v);
             }
         }
+        if (EPI == EPI_RESID && m.ssq_out && warp >= FIRST_CONV) {
+            const uint32_t ch_begin = rank * qc + min(rank, remc), ch_count = qc + (rank < remc ? 1 : 0);
+            write_ssq(16 * ch_begin, 16 * (ch_begin + ch_count));
+        }
     }
     if (tid == FIRST_CONV * 32) PROBE(7, 5);
     __syncthreads();
@@ -565,7 +609,7 @@ static GemmEntry gemm_entry(bool int8, uint32_t epi) {
 bool gemm_supported(const MatArgs& a) {
     const bool grouped = a.int8 && a.group < a.k;
     return a.n >= 1 && a.n <= 256 && a.m % gemm::BM == 0 && a.k % gemm::BK == 0 && !grouped && a.Xb != nullptr &&
-           (a.epi == EPI_RESID || a.epi == EPI_RAW || a.inv_in != nullptr);
+           (a.epi == EPI_RESID || a.epi == EPI_RAW || a.inv_in != nullptr || a.ssq_in != nullptr);
 }
 
 void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s) {
@@ -598,7 +642,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
                                    (n_pad / 16 + 8) * 16 * gemm::BM * 4);  // the split-k exchange buffer at its largest (8 splits)
     // At least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
     // behind another one (blocks of different clusters waiting on each other's SMs could deadlock).
-    const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 12, 116 * 1024);
+    const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 28, 116 * 1024);
     if (!configured) {
         for (int i8 = 0; i8 < 2; i8++)
             for (uint32_t epi = EPI_NORM; epi <= EPI_QKV; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));

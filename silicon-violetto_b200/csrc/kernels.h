@@ -44,6 +44,12 @@ struct MatArgs {
     float eps;
     bool int8;
     QkvEpilogue q;  // EPI_QKV only
+    // The residual stream's sum of squares per token, kept by the tensor-core GEMMs themselves so that no row pass is
+    // needed between them: an EPI_RESID GEMM with ssq_out writes, per 128-row tile of its output, sum(y^2) over the
+    // tile's rows ([tile][ssq_stride]); a GEMM with ssq_in (and no inv_in) takes 1/rms = rsqrt(sum over ssq_tiles / k + eps).
+    float* ssq_out;
+    const float* ssq_in;
+    uint32_t ssq_tiles, ssq_stride;
 };
 
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
