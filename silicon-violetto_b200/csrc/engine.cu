@@ -567,7 +567,7 @@ void Engine::encode_forward(uint32_t set, const Plan& p) {
     VLT_CUDA(cudaEventRecord(st.start, stream));
     VLT_CUDA(cudaMemcpyAsync(st.dev_in.dev, st.host_in, st.in_bytes, cudaMemcpyHostToDevice, stream));
     launch_embed(model.embed, st.in<uint32_t>(st.o_tokens), s.h.as<float>(), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.lens.as<uint32_t>(),
-                 s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), st.in<uint32_t>(st.o_vis), p.n, model.md.d, stream);
+                 s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), st.in<uint32_t>(st.o_vis), p.n, model.md.d, model.md.vocab, stream);
     for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
     const int sp = span_begin(G_TAIL);
     encode_tail(set, p);
@@ -726,7 +726,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.max_rows = 1;
     for (uint32_t i = 1; i < rows; i++) {
         launch_draft_pass_in(runs, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(),
-                             st.out<uint32_t>(st.o_emitted), s.taps.as<float>(), dr.dfeat.as<float>(), model.embed, nr, d, i, cfg.max_seq_len, x, xb,
+                             st.out<uint32_t>(st.o_emitted), s.taps.as<float>(), dr.dfeat.as<float>(), model.embed, nr, d, md.vocab, i, cfg.max_seq_len, x, xb,
                              dr.dmeta.as<uint32_t>(), dr.dtin.as<uint32_t>(), dr.dvis.as<uint32_t>(), dr.dcpos.as<uint32_t>(), dr.live.as<uint32_t>(), stream);
         fc(nr);
         encode_layer_io(io);

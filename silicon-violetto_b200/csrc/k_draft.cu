@@ -47,8 +47,8 @@ __device__ __forceinline__ uint32_t draft_last_row(const RunIn& ru, uint32_t r, 
 __global__ void draft_pass_in_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ lens, const uint32_t* __restrict__ feed,
                                      const uint32_t* __restrict__ path, const uint32_t* __restrict__ path_len, const uint32_t* __restrict__ on_path,
                                      const uint32_t* __restrict__ emitted, const float* __restrict__ taps, const float* __restrict__ dfeat,
-                                     const uint16_t* __restrict__ embed, uint32_t d, uint32_t i, uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta,
-                                     uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live) {
+                                     const uint16_t* __restrict__ embed, uint32_t d, uint32_t vocab, uint32_t i, uint32_t max_seq_len, float* x, uint16_t* xb,
+                                     uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live) {
     pdl_start();
     const uint32_t r = blockIdx.x;
     const RunIn ru = runs[r];
@@ -56,7 +56,8 @@ __global__ void draft_pass_in_kernel(const RunIn* __restrict__ runs, const uint3
     const uint32_t pos = lens[ru.slot] + i - 1;
     const bool lv = last != NO_TOK && emitted[r] > 0 && pos < max_seq_len;
     const float* feat = i == 1 ? (last != NO_TOK ? taps + size_t(last) * d : nullptr) : dfeat + size_t(r) * d;
-    const uint32_t tok = lv ? feed[ru.slot * FEED_W + i - 1] : 0u;
+    uint32_t tok = lv ? feed[ru.slot * FEED_W + i - 1] : 0u;
+    if (tok >= vocab) tok = 0;  // (only a row of NaN logits can leave such an id in feed)
     draft_row_in(feat, embed + size_t(tok) * d, d, x + size_t(r) * 2 * d, xb + size_t(r) * 2 * d);
     if (threadIdx.x == 0) {
         dmeta[2 * r] = ru.slot;
@@ -214,10 +215,10 @@ void launch_draft_catchup_in(const uint32_t* tokens, const uint32_t* tin, const 
     launch_pdl(draft_catchup_in_kernel, n, 256, 0, s, tokens, tin, meta, on_path, taps, carry, embed, d, x, xb, cpos);
 }
 void launch_draft_pass_in(const RunIn* runs, const uint32_t* lens, const uint32_t* feed, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path,
-                          const uint32_t* emitted, const float* taps, const float* dfeat, const uint16_t* embed, uint32_t n_runs, uint32_t d, uint32_t i,
-                          uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live,
+                          const uint32_t* emitted, const float* taps, const float* dfeat, const uint16_t* embed, uint32_t n_runs, uint32_t d, uint32_t vocab,
+                          uint32_t i, uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live,
                           cudaStream_t s) {
-    launch_pdl(draft_pass_in_kernel, n_runs, 256, 0, s, runs, lens, feed, path, path_len, on_path, emitted, taps, dfeat, embed, d, i, max_seq_len, x, xb, dmeta,
+    launch_pdl(draft_pass_in_kernel, n_runs, 256, 0, s, runs, lens, feed, path, path_len, on_path, emitted, taps, dfeat, embed, d, vocab, i, max_seq_len, x, xb, dmeta,
                dtin, dvis, dcpos, live);
 }
 void launch_draft_carry(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path, const float* taps, uint32_t n_runs,

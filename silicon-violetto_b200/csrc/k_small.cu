@@ -13,7 +13,7 @@ namespace vlt {
 // it sees from the node. meta[t] = (slot, lens[slot] + depth). One block per token.
 __global__ void embed_kernel(const uint16_t* __restrict__ table, uint32_t* tokens, float* __restrict__ out, const uint32_t* __restrict__ tin,
                              uint32_t* meta, const uint32_t* __restrict__ lens, const uint32_t* __restrict__ feed, const uint32_t* __restrict__ tree,
-                             uint32_t* vis, uint32_t d) {
+                             uint32_t* vis, uint32_t d, uint32_t vocab) {
     pdl_start();
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
     const uint32_t slot = tin[2 * t];
@@ -26,6 +26,9 @@ __global__ void embed_kernel(const uint16_t* __restrict__ table, uint32_t* token
         tok = feed[slot * FEED_W + i];
         depth = node_depth(node);
     }
+    // An id past the vocabulary can only come from the device (a row of NaN logits has no argmax): read it as 0
+    // rather than index out of the table.
+    if (tok >= vocab) tok = 0;
     const uint32_t* row = reinterpret_cast<const uint32_t*>(table + size_t(tok) * d);
     float2* o = reinterpret_cast<float2*>(out + size_t(t) * d);
     for (uint32_t i = tid; i < d / 2; i += blockDim.x) {
@@ -42,8 +45,8 @@ __global__ void embed_kernel(const uint16_t* __restrict__ table, uint32_t* token
 }
 
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
-                  const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, cudaStream_t s) {
-    launch_pdl(embed_kernel, n, 128, 0, s, table, tokens, out, tin, meta, lens, feed, tree, vis, d);
+                  const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, uint32_t vocab, cudaStream_t s) {
+    launch_pdl(embed_kernel, n, 128, 0, s, table, tokens, out, tin, meta, lens, feed, tree, vis, d, vocab);
 }
 
 // ------------------------------------------------------- K/V into the cache

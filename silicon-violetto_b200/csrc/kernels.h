@@ -53,7 +53,7 @@ struct MatArgs {
 };
 
 void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uint32_t* tin, uint32_t* meta, const uint32_t* lens,
-                  const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, cudaStream_t s);
+                  const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, uint32_t vocab, cudaStream_t s);
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
                      const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, const uint32_t* cpos, cudaStream_t s);
 void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* tiles, const uint32_t* vis, const float* rope, const uint16_t* k_cache,
@@ -97,8 +97,8 @@ void launch_attn_combine(const AttnArgs& a, cudaStream_t s);
 void launch_draft_catchup_in(const uint32_t* tokens, const uint32_t* tin, const uint32_t* meta, const uint32_t* on_path, const float* taps, const float* carry,
                              const uint16_t* embed, uint32_t n, uint32_t d, float* x, uint16_t* xb, uint32_t* cpos, cudaStream_t s);
 void launch_draft_pass_in(const RunIn* runs, const uint32_t* lens, const uint32_t* feed, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path,
-                          const uint32_t* emitted, const float* taps, const float* dfeat, const uint16_t* embed, uint32_t n_runs, uint32_t d, uint32_t i,
-                          uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live,
+                          const uint32_t* emitted, const float* taps, const float* dfeat, const uint16_t* embed, uint32_t n_runs, uint32_t d, uint32_t vocab,
+                          uint32_t i, uint32_t max_seq_len, float* x, uint16_t* xb, uint32_t* dmeta, uint32_t* dtin, uint32_t* dvis, uint32_t* dcpos, uint32_t* live,
                           cudaStream_t s);
 void launch_draft_carry(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* on_path, const float* taps, uint32_t n_runs,
                         uint32_t d, float* carry, cudaStream_t s);
