@@ -291,6 +291,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, NT <= 3 ? 4 : 3) attn_mma_ker
     // its columns to the block's maximum, the block adds them up and writes the partial.
     __syncthreads();
     constexpr int OS = HD + 4;                       // the row stride keeps a quad's stores off each other's banks
+    static_assert(size_t(ATTN_WARPS) * NC * (OS + 2) * 4 <= size_t(ATTN_WARPS) * ATTN_STAGES * STAGE_BYTES, "the merge buffers must fit in the stage rings");
     float* ms = reinterpret_cast<float*>(smem);      // [warp][column]
     float* ls = ms + ATTN_WARPS * NC;                // [warp][column], scaled
     float* os = ls + ATTN_WARPS * NC;                // [warp][column][OS], scaled
