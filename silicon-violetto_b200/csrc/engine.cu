@@ -343,8 +343,10 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
 // Y = epilogue(W . X) for n tokens: steps of at most 8 tokens stream the weights through the
 // tensor cores from registers; larger ones go in token blocks of 8 (the weights of one matrix
 // stay in L2 between blocks).
-void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real) {
+void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real,
+                    const QkvEpilogue* q) {
     MatArgs a{};
+    if (q) a.q = *q;
     a.W = w.w;
     a.scales = w.scales;
     a.k = w.k;
@@ -357,12 +359,24 @@ void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint3
     const uint32_t out_w = epi == EPI_SWIGLU ? w.m / 2 : w.m;
     for (uint32_t t0 = 0; t0 < n; t0 += 8) {
         a.n = std::min(8u, n - t0);
+        a.t0 = t0;
         a.X = x + size_t(t0) * w.k;
-        a.Y = y + size_t(t0) * out_w;
+        a.Y = y ? y + size_t(t0) * out_w : nullptr;
         a.base = base ? base + size_t(t0) * out_w : nullptr;
         a.inv_out = inv_out ? inv_out + t0 : nullptr;
         launch_matmul_stream(a, sm_count, stream);
     }
+}
+
+// Whether the streamed kernel itself (not its scalar stand-in) takes this matrix.
+bool Engine::stream_fits(const Matrix& w) const {
+    MatArgs a{};
+    a.n = 1;
+    a.k = w.k;
+    a.m = w.m;
+    a.group = w.group;
+    a.int8 = w.int8;
+    return matmul_stream_fits(a);
 }
 
 // The matmul variant by step size (the reference's Matmul::for_tokens, encode.rs:33-44): the
@@ -433,9 +447,23 @@ void Engine::encode_layer_io(const LayerIO& io) {
     const bool big = use_gemm(l.qkv, n) && use_gemm(l.o, n) && use_gemm(l.gate_up, n) && use_gemm(l.down, n);
     const KvArgs kva = kv_args();
     const float scale_log2 = md.attn_scale * 1.44269504088896340736f;
-    // With the tensor-core GEMM the qkv projection's epilogue does what qkv_post does (RoPE, q for the attention,
-    // K/V into the cache); the scalar attention reads fp32 q, so that path keeps the separate kernel.
-    const bool fused_post = big && !tuning.plain_attention;
+    // The qkv projection's epilogue does what qkv_post does (RoPE, q for the attention, K/V into the cache), in the
+    // tensor-core GEMM and in the streamed matmul alike; the scalar attention reads fp32 q, and odd shapes go through
+    // the scalar matmul: those keep the separate kernel.
+    const bool fused_post = !tuning.plain_attention && (big || stream_fits(l.qkv));
+    QkvEpilogue q{};
+    q.meta = io.meta;
+    q.tin = io.tin;
+    q.cpos = io.cpos;
+    q.rope = rope_tab.as<float>();
+    q.page_table = kv.page_table.as<uint32_t>();
+    q.kv = kva;
+    q.layer = li;
+    q.n_heads = md.n_heads;
+    q.scale_log2 = scale_log2;
+    q.q_b = s.q_b.as<uint16_t>();
+    q.k_cache = io.k_cache;
+    q.v_cache = io.v_cache;
     int sp = span_begin(G_MATMUL);
     if (!(skip & 1)) {
         if (big) {
@@ -444,24 +472,10 @@ void Engine::encode_layer_io(const LayerIO& io) {
             if (!carried) launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
             const float* inv_in = carried ? nullptr : s.inv.as<float>();
             const float* ssq_in = carried ? s.ssq.as<float>() : nullptr;
-            if (fused_post) {
-                QkvEpilogue q{};
-                q.meta = io.meta;
-                q.tin = io.tin;
-                q.cpos = io.cpos;
-                q.rope = rope_tab.as<float>();
-                q.page_table = kv.page_table.as<uint32_t>();
-                q.kv = kva;
-                q.layer = li;
-                q.n_heads = md.n_heads;
-                q.scale_log2 = scale_log2;
-                q.q_b = s.q_b.as<uint16_t>();
-                q.k_cache = io.k_cache;
-                q.v_cache = io.v_cache;
-                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), nullptr, nullptr, EPI_QKV, nullptr, inv_in, 0, &q, nullptr, ssq_in);
-            } else {
-                matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, inv_in, 0, nullptr, nullptr, ssq_in);
-            }
+            if (fused_post) matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), nullptr, nullptr, EPI_QKV, nullptr, inv_in, 0, &q, nullptr, ssq_in);
+            else matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, inv_in, 0, nullptr, nullptr, ssq_in);
+        } else if (fused_post) {
+            matmul(l.qkv, n, h, nullptr, EPI_QKV, nullptr, s.inv.as<float>(), 0, &q);
         } else {
             matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
         }

@@ -7,10 +7,10 @@
 // and each threadgroup writes a partial per (token, head, split) that a second kernel merges.
 // This kernel keeps that decomposition and changes what B200 wants changed:
 //   - K and V pages (16 tokens x 64 dims, 2 KiB each) come in by TMA into 128-byte-swizzled
-//     shared memory, a four-stage ring per warp, and go to the MMAs through ldmatrix;
+//     shared memory, a three-stage ring per warp, and go to the MMAs through ldmatrix;
 //   - the softmax keeps a running maximum (a plain decoder has no q/k norm to bound the
 //     scores, kernels.metal:803-806), and partials carry (m, l, o[64]);
-//   - the step's own rows are already in the cache (written by qkv_post), so they are read like
+//   - the step's own rows are already in the cache (written by the qkv projection's epilogue or qkv_post), so they are read like
 //     any other key and only the pages at or past the run's first position are masked.
 // grid (kv heads, splits, tiles), 4 warps; warp w takes pages w, w + 4, ... of its split.
 #include <cuda.h>

@@ -32,6 +32,32 @@ __device__ __forceinline__ void store_swiglu(const MatArgs& a, uint32_t t, uint3
     if (a.Yb) a.Yb[o] = f32_to_bf16(y);
 }
 
+// kernels.metal:749-801 `qkv_post` on one (even, odd) pair of rows of the qkv projection of token t: RoPE on q and k
+// (interleaved pairs, the angle of the token's position), q scaled by scale * log2(e) and rounded to bf16 for the
+// attention, k and v rounded to bf16 into the token's cache row (its run's first position + its row). Every float
+// operation is a single rounded one, as in `qkv_post_kernel`, so both forms give the same bits.
+__device__ __forceinline__ void qkv_store_pair(const QkvEpilogue& q, uint32_t t, uint32_t row, float y0, float y1) {
+    const uint32_t hd = q.kv.hd, head = row / hd, pair = (row % hd) / 2;
+    const uint32_t slot = q.meta[2 * t], pos = q.meta[2 * t + 1];
+    if (head < q.n_heads + q.kv.n_kv) {
+        const float2 cs = reinterpret_cast<const float2*>(q.rope)[size_t(pos) * (hd / 2) + pair];
+        const float r0 = __fadd_rn(__fmul_rn(cs.x, y0), __fmul_rn(cs.y, y1));
+        const float r1 = __fsub_rn(__fmul_rn(cs.x, y1), __fmul_rn(cs.y, y0));
+        if (head < q.n_heads) {
+            reinterpret_cast<uint32_t*>(q.q_b)[(size_t(t) * q.n_heads + head) * (hd / 2) + pair] = pack_bf16(__fmul_rn(r0, q.scale_log2), __fmul_rn(r1, q.scale_log2));
+            return;
+        }
+        y0 = r0;
+        y1 = r1;
+    }
+    const uint32_t run_row = q.tin[2 * t + 1];
+    const uint32_t cpos = q.cpos ? q.cpos[t] : q.meta[2 * (t - run_row) + 1] + run_row;
+    if (cpos == NO_TOK) return;  // (the drafter's passes leave out the rows that are not on the accepted path)
+    const bool is_v = head >= q.n_heads + q.kv.n_kv;
+    const size_t at = kv_row(q.kv, q.layer, q.page_table, slot, head - q.n_heads - (is_v ? q.kv.n_kv : 0), cpos);
+    reinterpret_cast<uint32_t*>((is_v ? q.v_cache : q.k_cache) + at)[pair] = pack_bf16(y0, y1);
+}
+
 // ------------------------------------------------------------------ scalar
 // One warp per pair of rows (a gate/up pair under SWIGLU), all tokens in blocks of 8.
 __global__ void __launch_bounds__(256) matmul_rows_kernel(MatArgs a) {
@@ -146,7 +172,7 @@ __global__ void __launch_bounds__(512) matmul_stream_kernel(MatArgs a) {
     const bool has_x = g < a.n;
     const float* xrow = a.X + size_t(has_x ? g : 0) * a.k;
 
-#pragma unroll 2
+#pragma unroll(MT == 1 ? 4 : 2)  // loads in flight per lane: deep k (8 tiles a warp at k = 8192) would otherwise be four round trips
     for (uint32_t kt = warp; kt < n_tiles; kt += NW) {
         const uint32_t k0 = kt * KT + t * E;
         uint4 wl[MT], wh[MT];
@@ -235,6 +261,8 @@ __global__ void __launch_bounds__(512) matmul_stream_kernel(MatArgs a) {
         if (b < a.n) {
             if (a.epi == EPI_SWIGLU) {
                 if (r % 2 == 0) store_swiglu(a, b, row0 + r, fin[r][b], fin[r + 1][b], inv_s[b]);
+            } else if (a.epi == EPI_QKV) {
+                if (r % 2 == 0) qkv_store_pair(a.q, a.t0 + b, row0 + r, fin[r][b] * inv_s[b], fin[r + 1][b] * inv_s[b]);
             } else {
                 store_out(a, b, row0 + r, fin[r][b], inv_s[b]);
             }
@@ -242,10 +270,15 @@ __global__ void __launch_bounds__(512) matmul_stream_kernel(MatArgs a) {
     }
 }
 
-void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
+bool matmul_stream_fits(const MatArgs& a) {
     const uint32_t kt = a.int8 ? 64 : 32;
     const bool grouped = a.int8 && a.group < a.k;
-    if (a.n > 8 || a.k % kt || a.m % 16 || (grouped && a.group % kt)) {
+    return !(a.n > 8 || a.k % kt || a.m % 16 || (grouped && a.group % kt));
+}
+
+void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
+    if (!matmul_stream_fits(a)) {
+        if (a.epi == EPI_QKV) throw Error("internal: the qkv epilogue needs the streamed matmul's shapes");
         launch_matmul_rows(a, s);
         return;
     }

@@ -44,6 +44,7 @@ struct MatArgs {
     float eps;
     bool int8;
     QkvEpilogue q;  // EPI_QKV only
+    uint32_t t0;    // EPI_QKV in the streamed matmul: the step's token that this launch's token 0 is
     // The residual stream's sum of squares per token, kept by the tensor-core GEMMs themselves so that no row pass is
     // needed between them: an EPI_RESID GEMM with ssq_out writes, per 128-row tile of its output, sum(y^2) over the
     // tile's rows ([tile][ssq_stride]); a GEMM with ssq_in (and no inv_in) takes 1/rms = rsqrt(sum over ssq_tiles / k + eps).
@@ -117,6 +118,7 @@ void launch_draft_tree(const uint32_t* blocks, const uint32_t* slots, uint32_t n
 bool gemm_supported(const MatArgs& a);
 void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s);
 void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s);  // n <= 8, tensor cores fed from registers
+bool matmul_stream_fits(const MatArgs& a);                                      // else launch_matmul_stream falls back to the scalar kernel
 void launch_matmul_rows(const MatArgs& a, cudaStream_t s);                      // any n, scalar (cross-check, odd scale groups)
 // out[r] = in[rows ? rows[r] : r] as fp32 (and bf16); inv[r] = 1 / rms (kernels.metal:117-148).
 void launch_prep_rows(const float* in, const uint32_t* rows, uint32_t n, uint32_t k, float eps, float* out_f32, uint16_t* out_bf16, float* inv,

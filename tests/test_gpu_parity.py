@@ -144,13 +144,14 @@ def test_kv_cache_matches_the_oracle_after_prefill():
     assert np.array_equal(prod.debug_read("page_table")[:2], np.array([0, 1], np.uint32))
 
 
-def test_two_attention_kernels_agree_at_long_context():
-    """The tensor-core attention against the scalar one, 3000 cached keys with filled values, several splits."""
+@pytest.mark.parametrize("keys_per_block", [640, 128])
+def test_two_attention_kernels_agree_at_long_context(keys_per_block):
+    """The tensor-core attention against the scalar one, 3000 cached keys with filled values, 5 key splits and 24."""
     w = util.weights("micro4", 0)
     cfg = E.EngineConfig(max_seqs=3, max_step_tokens=32, max_chunk=8, global_kv_tokens=3 * 3200, max_seq_len=3200, max_head_rows=24)
     outs = []
     for plain in (False, True):
-        eng = E.Engine(w, cfg, E.Tuning(plain_attention=plain, attn_keys_per_cta=640))
+        eng = E.Engine(w, cfg, E.Tuning(plain_attention=plain, attn_keys_per_cta=keys_per_block))
         seqs = [eng.new_seq() for _ in range(3)]
         for i, s in enumerate(seqs):
             eng.bench_fill(s, [3000, 17, 1234][i], seed=5 + i)
