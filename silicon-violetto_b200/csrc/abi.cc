@@ -78,8 +78,14 @@ int vlt_engine_new(const char* weights_path, const VltEngineConfig* cfg, const V
     });
 }
 
+#ifdef VLT_STEP_PROBE
+extern "C" void vlt_sp_dump_all();
+#endif
 void vlt_engine_free(VltEngine* e) {
     if (!e) return;
+#ifdef VLT_STEP_PROBE
+    vlt_sp_dump_all();
+#endif
     if (e->generator) e->generator->g.reset();  // a generator must not outlive its engine
     delete e;
 }

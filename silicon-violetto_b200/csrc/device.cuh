@@ -65,10 +65,44 @@ __device__ __forceinline__ uint32_t d_tree_node(uint32_t depth, uint32_t parent,
 // Programmatic dependent launch, first thing in a kernel started that way: let the kernel queued behind
 // this one be scheduled early (it waits in turn), then wait for the kernel before this one to complete.
 // From here on everything is ordered as if the kernels ran one after another; only launch latency overlaps.
+#ifdef VLT_STEP_PROBE
+}  // namespace vlt
+#include <cstdio>
+#include <vector>
+namespace vlt {
+static __device__ unsigned long long sp_buf[4 * 16384];
+static __device__ unsigned int sp_n;
+__device__ __forceinline__ void sp_mark(unsigned tag) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned i = atomicAdd(&sp_n, 1u);
+    if (i < 16384) { sp_buf[4 * i] = t; sp_buf[4 * i + 1] = tag; sp_buf[4 * i + 2] = gridDim.x * gridDim.y * gridDim.z; sp_buf[4 * i + 3] = blockDim.x; }
+}
+__device__ __forceinline__ void pdl_start() {
+    const bool me = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+    if (me) sp_mark(1);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (me) sp_mark(2);
+}
+inline std::vector<void (*)()>& sp_registry() { static std::vector<void (*)()> v; return v; }
+static void sp_dump_tu() {
+    static unsigned long long h[4 * 16384];
+    unsigned n = 0;
+    cudaMemcpyFromSymbol(&n, sp_n, 4);
+    cudaMemcpyFromSymbol(h, sp_buf, sizeof(h));
+    if (n > 16384) n = 16384;
+    for (unsigned i = 0; i < n; i++) fprintf(stderr, "SP %llu %llu %llu %llu %s\n", h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3], __FILE__);
+}
+namespace { struct SpReg { SpReg() { sp_registry().push_back(&sp_dump_tu); } }; static SpReg sp_reg_instance; }
+#define SP_MARK(tag) sp_mark(tag)
+#else
+#define SP_MARK(tag) do { } while (0)
 __device__ __forceinline__ void pdl_start() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+#endif
 __device__ __forceinline__ uint32_t d_chain_node(uint32_t row) { return d_tree_node(row, row == 0 ? 0xffu : row - 1, (2u << row) - 1u); }
 __device__ __forceinline__ uint32_t d_dead_node(uint32_t row) { return d_tree_node(1, 0xffu, 1u | 1u << row); }
 __device__ __forceinline__ uint32_t node_depth(uint32_t n) { return n & 0xffu; }

@@ -76,6 +76,8 @@ void StepSet::init(const EngineConfig& cfg) {
         std::memset(host_out, 0, out_bytes);
         VLT_CUDA(cudaEventCreate(&start));
         VLT_CUDA(cudaEventCreate(&done));
+        VLT_CUDA(cudaEventCreateWithFlags(&uploaded, cudaEventDisableTiming));
+        VLT_CUDA(cudaEventCreateWithFlags(&computed, cudaEventDisableTiming));
     }
 }
 
@@ -85,6 +87,8 @@ void StepSet::release() {
         if (host_out) cudaFreeHost(host_out);
         if (start) cudaEventDestroy(start);
         if (done) cudaEventDestroy(done);
+        if (uploaded) cudaEventDestroy(uploaded);
+        if (computed) cudaEventDestroy(computed);
     }
     host_in = host_out = nullptr;
 }
@@ -103,6 +107,8 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
         if (prop.major < 10) throw Error(std::string(prop.name) + ": compute capability " + std::to_string(prop.major) + "." + std::to_string(prop.minor) + " (the kernels are built for sm_100a)");
         sm_count = tuning.sm_count ? tuning.sm_count : uint32_t(prop.multiProcessorCount);
         VLT_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        VLT_CUDA(cudaStreamCreateWithFlags(&copy_in, cudaStreamNonBlocking));
+        VLT_CUDA(cudaStreamCreateWithFlags(&copy_out, cudaStreamNonBlocking));
     } else if (tuning.sm_count) {
         sm_count = tuning.sm_count;
     }
@@ -174,7 +180,10 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
 Engine::~Engine() {
     if (stream) {
         cudaStreamSynchronize(stream);
+        cudaStreamSynchronize(copy_out);
         cudaStreamDestroy(stream);
+        cudaStreamDestroy(copy_in);
+        cudaStreamDestroy(copy_out);
     }
     for (auto& st : sets) st.release();
 }
@@ -347,6 +356,7 @@ void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint3
                     const QkvEpilogue* q) {
     MatArgs a{};
     if (q) a.q = *q;
+    a.err_flag = s.err_flag.as<uint32_t>();
     a.W = w.w;
     a.scales = w.scales;
     a.k = w.k;
@@ -578,8 +588,11 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
 void Engine::encode_forward(uint32_t set, const Plan& p) {
     if (cfg.host_only) throw Error("this engine was created host-only: it plans steps but cannot run them (no CPU path)");
     StepSet& st = sets[set];
+    // The set's device copy is free: the step that used it last has been collected (three sets, at most two steps queued).
+    VLT_CUDA(cudaMemcpyAsync(st.dev_in.dev, st.host_in, st.in_bytes, cudaMemcpyHostToDevice, copy_in));
+    VLT_CUDA(cudaEventRecord(st.uploaded, copy_in));
     VLT_CUDA(cudaEventRecord(st.start, stream));
-    VLT_CUDA(cudaMemcpyAsync(st.dev_in.dev, st.host_in, st.in_bytes, cudaMemcpyHostToDevice, stream));
+    VLT_CUDA(cudaStreamWaitEvent(stream, st.uploaded, 0));
     launch_embed(model.embed, st.in<uint32_t>(st.o_tokens), s.h.as<float>(), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.lens.as<uint32_t>(),
                  s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), st.in<uint32_t>(st.o_vis), p.n, model.md.d, model.md.vocab, stream);
     for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
@@ -597,8 +610,10 @@ void Engine::encode_replay(uint32_t set, const Plan& p, const ReplayArgs& ra) {
 
 void Engine::commit(uint32_t set) {
     StepSet& st = sets[set];
-    VLT_CUDA(cudaMemcpyAsync(st.host_out, st.dev_out.dev, st.out_bytes, cudaMemcpyDeviceToHost, stream));
-    VLT_CUDA(cudaEventRecord(st.done, stream));
+    VLT_CUDA(cudaEventRecord(st.computed, stream));
+    VLT_CUDA(cudaStreamWaitEvent(copy_out, st.computed, 0));
+    VLT_CUDA(cudaMemcpyAsync(st.host_out, st.dev_out.dev, st.out_bytes, cudaMemcpyDeviceToHost, copy_out));
+    VLT_CUDA(cudaEventRecord(st.done, copy_out));
     VLT_CUDA(cudaGetLastError());
 }
 
@@ -1047,3 +1062,7 @@ void Engine::debug_write(const std::string& name, size_t index, const uint32_t* 
 }
 
 }  // namespace vlt
+
+#ifdef VLT_STEP_PROBE
+extern "C" void vlt_sp_dump_all() { cudaDeviceSynchronize(); for (auto f : vlt::sp_registry()) f(); }
+#endif

@@ -80,7 +80,8 @@ struct StepSet {
     size_t in_bytes = 0, out_bytes = 0;
     size_t o_tokens = 0, o_tin = 0, o_vis = 0, o_head_rows = 0, o_hidden_rows = 0, o_sample_rows = 0, o_tiles = 0, o_runs = 0;  // byte offsets in *_in
     size_t o_out_ids = 0, o_emitted = 0;                                                                                       // in *_out
-    cudaEvent_t start = nullptr, done = nullptr;
+    cudaEvent_t start = nullptr, done = nullptr;        // around the step on the engine's stream / after its results reached the host
+    cudaEvent_t uploaded = nullptr, computed = nullptr;  // the step's inputs are on the device / its last kernel has run
     bool host_only = false;
     void init(const EngineConfig& cfg);
     void release();
@@ -165,6 +166,9 @@ class Engine {
     uint32_t skip = 0;
     bool taps_on = false;
     cudaStream_t stream = nullptr;
+    // A step's inputs go up and its results come down on streams of their own, so that neither copy sits between the
+    // last kernel of one step and the first of the next (the next step is queued while this one runs).
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
 
     // Activations (engine/src/engine/buffers.rs:14-118) and per-slot state on the GPU.
     struct Scratch {

@@ -5,6 +5,9 @@
 // Y[t][row] = epilogue(W[row] . bf16(X[t])), W [m][k] row-major bf16 or int8 with bf16 scales
 // per group of consecutive k, X fp32 [n][k]. 1/rms(X[t]) is accumulated in the same pass
 // (kernels.metal:239-251,286), so a folded RMSNorm costs no extra kernel.
+#include <algorithm>
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace vlt {
@@ -142,138 +145,221 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// A block takes 16 MT rows and all of k; its 16 warps take k tiles in turn and add up their
-// sums through shared memory in warp order. Per tile a lane loads 16 bytes of row g and of row
-// g + 8 of each m16 tile (g = lane / 4) and 16 or 8 floats of token g; since the contraction
-// index may be permuted freely, lane t's consecutive k are used as k-slots (2t, 2t+1, 2t+8,
-// 2t+9) of successive mma steps for A and B alike, so every load is contiguous.
-template <bool INT8, int MT>
-__global__ void __launch_bounds__(512) matmul_stream_kernel(MatArgs a) {
-    pdl_start();
+// ---- shared-memory pipeline pieces (bounded waits: a copy that never lands sets the error word instead of hanging)
+__device__ __forceinline__ uint32_t st_smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void st_mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void st_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool st_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void st_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// One resident block of 16 warps per `slot` walks over tiles of 16 weight rows (tile = block, + grid, ...). A row
+// tile is cut along k into slices of at most 2 KiB per row; a (row tile, slice) is one item of the block's pipeline:
+// its 16 row pieces come by bulk copy into a stage of shared memory (rows 64 bytes apart from a multiple of 128, so
+// that the eight rows a quarter-warp reads fall in different banks), `n_stages` items ahead of the multiplication,
+// and the first of them before the kernel waits for its predecessor (weights do not depend on it): HBM latency is
+// paid once per launch, and the warps' meeting after each row tile does not stop the stream.
+// Within a slice the 64-byte k tiles go to the warps in turn. A lane reads 16 bytes of row g and of row g + 8
+// (g = lane / 4); since the contraction index may be permuted freely, lane t's consecutive k are used as k-slots
+// (2t, 2t+1, 2t+8, 2t+9) of successive mma steps for A and B alike. The warps' sums meet in shared memory in warp order.
+// The activations are staged once per block as bf16 ([n tokens][k], rows padded by 16 bytes against bank conflicts),
+// their sums of squares for the folded RMSNorm taken in the same pass.
+constexpr uint32_t STREAM_SLICE = 2048;                      // bytes of a weight row per item
+constexpr uint32_t STREAM_ROW = STREAM_SLICE + 64;           // a stage's row stride
+constexpr uint32_t STREAM_STAGE = 16 * STREAM_ROW;
+constexpr uint32_t STREAM_MAX_STAGES = 6;
+
+template <bool INT8>
+__global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32_t n_stages) {
     constexpr int NW = 16;
     constexpr int E = INT8 ? 16 : 8;  // weights per 16-byte load
-    constexpr int KT = 4 * E;         // k per tile
-    constexpr int KS = E / 4;         // mma steps per tile
-    __shared__ float red[NW][MT * 16][8];
-    __shared__ float ss_red[NW][8];
-    __shared__ float fin[MT * 16][8];
+    constexpr int KS = E / 4;         // mma steps per 64-byte tile
+    constexpr uint32_t WB = INT8 ? 1 : 2;
+    extern __shared__ __align__(128) uint8_t stream_smem[];
+    __shared__ uint64_t bars[STREAM_MAX_STAGES];
+    __shared__ float ss_part[NW][8];
     __shared__ float inv_s[8];
-    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
-    const uint32_t row0 = blockIdx.x * (16 * MT);
-    const uint32_t n_tiles = a.k / KT;
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane >> 2, t = lane & 3;
+    const uint32_t xrs = a.k * 2 + 16;                                         // bytes per staged activation row
+    uint8_t* stages = stream_smem;                                             // [n_stages][16][STREAM_ROW]
+    float* red = reinterpret_cast<float*>(stream_smem + n_stages * STREAM_STAGE);  // [2][NW][16 rows][8 tokens]
+    uint8_t* xs = reinterpret_cast<uint8_t*>(red + 2 * NW * 128);              // [n][xrs]
+    const uint32_t row_bytes = a.k * WB, n_tiles = row_bytes / 64, n_row_tiles = a.m / 16;
+    const uint32_t slices = (n_tiles + 31) / 32;
+    const uint32_t my_row_tiles = (n_row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const uint32_t n_items = my_row_tiles * slices;
     const bool grouped = INT8 && a.group < a.k;
     const uint32_t ng = INT8 ? a.k / a.group : 1;
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc[mt][i] = 0.0f;
-    float ss = 0.0f;
-    const bool has_x = g < a.n;
-    const float* xrow = a.X + size_t(has_x ? g : 0) * a.k;
 
-#pragma unroll(MT == 1 ? 4 : 2)  // loads in flight per lane: deep k (8 tiles a warp at k = 8192) would otherwise be four round trips
-    for (uint32_t kt = warp; kt < n_tiles; kt += NW) {
-        const uint32_t k0 = kt * KT + t * E;
-        uint4 wl[MT], wh[MT];
+    if (tid == 0) {
+        for (uint32_t i = 0; i < n_stages; i++) st_mbar_init(st_smem_u32(&bars[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // Warp 0 requests an item: lane 0 announces the bytes, lanes 0..15 copy a row piece each.
+    auto request = [&](uint32_t item) {
+        const uint32_t rt = blockIdx.x + (item / slices) * gridDim.x, sl = item % slices, st = item % n_stages;
+        const uint32_t bytes = (min(n_tiles - sl * 32, 32u)) * 64, bar = st_smem_u32(&bars[st]);
+        if (lane == 0) st_mbar_expect_tx(bar, bytes * 16);
+        __syncwarp();
+        if (lane < 16)
+            st_bulk_load(st_smem_u32(stages + size_t(st) * STREAM_STAGE + lane * STREAM_ROW), a.W + size_t(rt * 16 + lane) * row_bytes + size_t(sl) * STREAM_SLICE, bytes, bar);
+    };
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (warp == 0)
+        for (uint32_t i = 0; i < min(n_stages, n_items); i++) request(i);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // Activations: the [n][k] array in float4 steps over all threads, up to eight loads in flight each; bf16 into
+    // shared memory, and a sum of squares per token (a thread's step belongs to one token, found by division).
+    {
+        float ssb[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        const uint32_t n4 = a.k / 4, total = a.n * n4;
+        const float4* src = reinterpret_cast<const float4*>(a.X);
+        for (uint32_t i0 = tid; i0 < total; i0 += 512 * 8) {
+            float4 v[8];
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) {
-            const size_t e = size_t(row0 + mt * 16 + g) * a.k + k0;
-            const size_t bytes = INT8 ? 1 : 2;
-            wl[mt] = __ldg(reinterpret_cast<const uint4*>(a.W + e * bytes));
-            wh[mt] = __ldg(reinterpret_cast<const uint4*>(a.W + (e + size_t(8) * a.k) * bytes));
-        }
-        uint32_t xb[E / 2];
-        if (has_x) {
+            for (int q = 0; q < 8; q++) v[q] = i0 + 512 * q < total ? src[i0 + 512 * q] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-            for (int j = 0; j < E / 4; j++) {
-                const float4 v = *reinterpret_cast<const float4*>(xrow + k0 + 4 * j);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                xb[2 * j] = pack_bf16(v.x, v.y);
-                xb[2 * j + 1] = pack_bf16(v.z, v.w);
+            for (int q = 0; q < 8; q++) {
+                const uint32_t i = i0 + 512 * q;
+                if (i >= total) break;
+                const uint32_t tk = i / n4, c = i % n4;
+                const float sq = v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
+#pragma unroll
+                for (int b = 0; b < 8; b++) ssb[b] += tk == uint32_t(b) ? sq : 0.0f;
+                reinterpret_cast<uint2*>(xs + size_t(tk) * xrs)[c] = make_uint2(pack_bf16(v[q].x, v[q].y), pack_bf16(v[q].z, v[q].w));
             }
-        } else {
-#pragma unroll
-            for (int j = 0; j < E / 2; j++) xb[j] = 0u;
         }
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) {
+        for (int b = 0; b < 8; b++) {
+            float ss = ssb[b];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) ss_part[warp][b] = ss;
+        }
+    }
+    __syncthreads();
+    if (tid < 8) {
+        float block_ss = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) block_ss += ss_part[w][tid];
+        const float inv = a.inv_in ? (tid < a.n ? a.inv_in[tid] : 0.0f) : rsqrtf(block_ss / float(a.k) + a.eps);
+        inv_s[tid] = inv;
+        if (a.inv_out && blockIdx.x == 0 && tid < a.n) a.inv_out[tid] = inv;
+    }
+    __syncthreads();
+
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    uint32_t buf = 0;
+    const bool has_x = g < a.n;
+    for (uint32_t item = 0; item < n_items; item++) {
+        const uint32_t rt = blockIdx.x + (item / slices) * gridDim.x, sl = item % slices, st = item % n_stages, row0 = rt * 16;
+        const uint32_t count = min(n_tiles - sl * 32, 32u);  // 64-byte tiles in this slice
+        // One scale per row, applied once after the sum: asked for before the wait, so that it is there when needed.
+        float row_sl = 1.0f, row_sh = 1.0f;
+        if (INT8 && !grouped && sl + 1 == slices) {
+            row_sl = bf16_to_f32(a.scales[row0 + g]);
+            row_sh = bf16_to_f32(a.scales[row0 + g + 8]);
+        }
+        if (!st_mbar_wait(st_smem_u32(&bars[st]), (item / n_stages) & 1) && lane == 0 && a.err_flag) atomicExch(a.err_flag, 2u);
+        const uint8_t* sw = stages + size_t(st) * STREAM_STAGE;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t kt = warp + NW * u;  // tile within the slice
+            if (kt >= count) break;             // (the same for the whole warp)
+            const uint4 wl = *reinterpret_cast<const uint4*>(sw + g * STREAM_ROW + kt * 64 + t * 16);
+            const uint4 wh = *reinterpret_cast<const uint4*>(sw + (g + 8) * STREAM_ROW + kt * 64 + t * 16);
+            const uint32_t k0 = (sl * STREAM_SLICE + kt * 64 + t * 16) / WB;  // this lane's first weight of the tile
+            uint32_t xb[E / 2];
+            if (has_x) {
+                const uint4* xp = reinterpret_cast<const uint4*>(xs + size_t(g) * xrs + size_t(k0) * 2);
+#pragma unroll
+                for (int q = 0; q < E / 8; q++) {
+                    const uint4 v = xp[q];
+                    xb[4 * q] = v.x; xb[4 * q + 1] = v.y; xb[4 * q + 2] = v.z; xb[4 * q + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < E / 2; q++) xb[q] = 0u;
+            }
             uint32_t al[E / 2], ah[E / 2];  // rows g and g + 8 as bf16 pairs
             if (INT8) {
-                cvt_i8x4(wl[mt].x, al[0], al[1]); cvt_i8x4(wl[mt].y, al[2], al[3]); cvt_i8x4(wl[mt].z, al[4], al[5]); cvt_i8x4(wl[mt].w, al[6], al[7]);
-                cvt_i8x4(wh[mt].x, ah[0], ah[1]); cvt_i8x4(wh[mt].y, ah[2], ah[3]); cvt_i8x4(wh[mt].z, ah[4], ah[5]); cvt_i8x4(wh[mt].w, ah[6], ah[7]);
+                cvt_i8x4(wl.x, al[0], al[1]); cvt_i8x4(wl.y, al[2], al[3]); cvt_i8x4(wl.z, al[4], al[5]); cvt_i8x4(wl.w, al[6], al[7]);
+                cvt_i8x4(wh.x, ah[0], ah[1]); cvt_i8x4(wh.y, ah[2], ah[3]); cvt_i8x4(wh.z, ah[4], ah[5]); cvt_i8x4(wh.w, ah[6], ah[7]);
             } else {
-                al[0] = wl[mt].x; al[1] = wl[mt].y; al[2] = wl[mt].z; al[3] = wl[mt].w;
-                ah[0] = wh[mt].x; ah[1] = wh[mt].y; ah[2] = wh[mt].z; ah[3] = wh[mt].w;
+                al[0] = wl.x; al[1] = wl.y; al[2] = wl.z; al[3] = wl.w;
+                ah[0] = wh.x; ah[1] = wh.y; ah[2] = wh.z; ah[3] = wh.w;
             }
             if (grouped) {
                 float tmp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int ks = 0; ks < KS; ks++) mma_bf16(tmp, al[2 * ks], ah[2 * ks], al[2 * ks + 1], ah[2 * ks + 1], xb[2 * ks], xb[2 * ks + 1]);
-                const uint32_t gi = (kt * KT) / a.group;
-                const float sl = bf16_to_f32(a.scales[size_t(row0 + mt * 16 + g) * ng + gi]);
-                const float sh = bf16_to_f32(a.scales[size_t(row0 + mt * 16 + g + 8) * ng + gi]);
-                acc[mt][0] += tmp[0] * sl; acc[mt][1] += tmp[1] * sl; acc[mt][2] += tmp[2] * sh; acc[mt][3] += tmp[3] * sh;
+                const uint32_t gi = k0 / a.group;
+                const float sl_ = bf16_to_f32(a.scales[size_t(row0 + g) * ng + gi]);
+                const float sh_ = bf16_to_f32(a.scales[size_t(row0 + g + 8) * ng + gi]);
+                acc[0] += tmp[0] * sl_; acc[1] += tmp[1] * sl_; acc[2] += tmp[2] * sh_; acc[3] += tmp[3] * sh_;
             } else {
 #pragma unroll
-                for (int ks = 0; ks < KS; ks++) mma_bf16(acc[mt], al[2 * ks], ah[2 * ks], al[2 * ks + 1], ah[2 * ks + 1], xb[2 * ks], xb[2 * ks + 1]);
+                for (int ks = 0; ks < KS; ks++) mma_bf16(acc, al[2 * ks], ah[2 * ks], al[2 * ks + 1], ah[2 * ks + 1], xb[2 * ks], xb[2 * ks + 1]);
             }
         }
-    }
-    // One scale per row: applied once, after the sum.
-    if (INT8 && !grouped) {
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++) {
-            const float sl = bf16_to_f32(a.scales[row0 + mt * 16 + g]), sh = bf16_to_f32(a.scales[row0 + mt * 16 + g + 8]);
-            acc[mt][0] *= sl; acc[mt][1] *= sl; acc[mt][2] *= sh; acc[mt][3] *= sh;
+        if (sl + 1 == slices) {  // the row tile is complete: add up the warps and store
+            acc[0] *= row_sl; acc[1] *= row_sl; acc[2] *= row_sh; acc[3] *= row_sh;
+            float* rb = red + size_t(buf) * NW * 128 + warp * 128;  // [row][token]
+            rb[g * 8 + 2 * t] = acc[0];
+            rb[g * 8 + 2 * t + 1] = acc[1];
+            rb[(g + 8) * 8 + 2 * t] = acc[2];
+            rb[(g + 8) * 8 + 2 * t + 1] = acc[3];
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
         }
-    }
+        __syncthreads();  // every warp is done with the stage (and, after a row tile, has left its sums)
+        if (warp == 0 && item + n_stages < n_items) request(item + n_stages);
+        if (sl + 1 == slices) {
+            // Warps 0..3: thread (token b, row r), consecutive threads on consecutive rows of one token. The buffer
+            // alternates: a warp can be one row tile ahead of the four that are still adding up, never two.
+            if (tid < 128) {
+                const uint32_t r = tid % 16, b = tid / 16;
+                const float* rp = red + size_t(buf) * NW * 128 + r * 8 + b;
+                float sum = 0.0f;
 #pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
-        red[warp][mt * 16 + g][2 * t] = acc[mt][0];
-        red[warp][mt * 16 + g][2 * t + 1] = acc[mt][1];
-        red[warp][mt * 16 + g + 8][2 * t] = acc[mt][2];
-        red[warp][mt * 16 + g + 8][2 * t + 1] = acc[mt][3];
-    }
-    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-    if (t == 0) ss_red[warp][g] = ss;
-    __syncthreads();
-    const uint32_t tid = threadIdx.x;
-    if (tid < MT * 16 * 8) {
-        const uint32_t r = tid / 8, b = tid % 8;
-        float s = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NW; w++) s += red[w][r][b];
-        fin[r][b] = s;
-    }
-    if (tid < 8) {
-        float s = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NW; w++) s += ss_red[w][tid];
-        const float inv = a.inv_in ? (tid < a.n ? a.inv_in[tid] : 0.0f) : rsqrtf(s / float(a.k) + a.eps);
-        inv_s[tid] = inv;
-        if (a.inv_out && blockIdx.x == 0 && tid < a.n) a.inv_out[tid] = inv;
-    }
-    __syncthreads();
-    if (tid < MT * 16 * 8) {
-        const uint32_t b = tid / (MT * 16), r = tid % (MT * 16);  // consecutive threads: consecutive rows of one token
-        if (b < a.n) {
-            if (a.epi == EPI_SWIGLU) {
-                if (r % 2 == 0) store_swiglu(a, b, row0 + r, fin[r][b], fin[r + 1][b], inv_s[b]);
-            } else if (a.epi == EPI_QKV) {
-                if (r % 2 == 0) qkv_store_pair(a.q, a.t0 + b, row0 + r, fin[r][b] * inv_s[b], fin[r + 1][b] * inv_s[b]);
-            } else {
-                store_out(a, b, row0 + r, fin[r][b], inv_s[b]);
+                for (int w = 0; w < NW; w++) sum += rp[w * 128];
+                const float partner = __shfl_down_sync(0xffffffffu, sum, 1);  // row r + 1 of the same token (r is even where it is used)
+                if (b < a.n) {
+                    const float inv = inv_s[b];
+                    if (a.epi == EPI_SWIGLU) {
+                        if (r % 2 == 0) store_swiglu(a, b, row0 + r, sum, partner, inv);
+                    } else if (a.epi == EPI_QKV) {
+                        if (r % 2 == 0) qkv_store_pair(a.q, a.t0 + b, row0 + r, sum * inv, partner * inv);
+                    } else {
+                        store_out(a, b, row0 + r, sum, inv);
+                    }
+                }
             }
+            buf ^= 1;
         }
     }
 }
 
+// Shared memory of the streamed kernel besides its stages: two buffers for the warps' sums and the staged activations.
+static size_t stream_fixed_smem(const MatArgs& a) { return 2 * 16 * 128 * 4 + size_t(a.n) * (size_t(a.k) * 2 + 16); }
+
 bool matmul_stream_fits(const MatArgs& a) {
-    const uint32_t kt = a.int8 ? 64 : 32;
     const bool grouped = a.int8 && a.group < a.k;
-    return !(a.n > 8 || a.k % kt || a.m % 16 || (grouped && a.group % kt));
+    const uint32_t row_bytes = a.k * (a.int8 ? 1 : 2);
+    // (a scale group must cover whole 64-byte tiles: the four lanes of an mma row add up one tile's k)
+    return !(a.n > 8 || row_bytes % 64 || a.m % 16 || (grouped && a.group % 64) || stream_fixed_smem(a) + 2 * STREAM_STAGE > 220 * 1024);
 }
 
 void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
@@ -282,18 +368,25 @@ void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
         launch_matmul_rows(a, s);
         return;
     }
-    // Rows per block: as many as still leave about two blocks per SM.
-    int mt = 1;
-    if (a.m % 32 == 0 && a.m / 32 >= 2 * sm_count) mt = 2;
-    if (a.m % 64 == 0 && a.m / 64 >= 2 * sm_count) mt = 4;
-    const uint32_t grid = a.m / (16 * mt);
-#define VLT_STREAM(I8, MT) { launch_pdl(matmul_stream_kernel<I8, MT>, grid, 512, 0, s, a); }
-    if (a.int8) {
-        if (mt == 1) VLT_STREAM(true, 1) else if (mt == 2) VLT_STREAM(true, 2) else VLT_STREAM(true, 4)
-    } else {
-        if (mt == 1) VLT_STREAM(false, 1) else if (mt == 2) VLT_STREAM(false, 2) else VLT_STREAM(false, 4)
+    static bool configured = false;
+    if (!configured) {
+        VLT_CUDA(cudaFuncSetAttribute(matmul_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        VLT_CUDA(cudaFuncSetAttribute(matmul_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        configured = true;
     }
-#undef VLT_STREAM
+    // Two resident blocks per SM with two or three stages each where shared memory allows (their row-tile meetings
+    // then overlap), else one with up to six.
+    const size_t fixed = stream_fixed_smem(a), half = 110 * 1024, whole = 220 * 1024;
+    static const int force_bps = getenv("VLT_STREAM_BPS") ? atoi(getenv("VLT_STREAM_BPS")) : 0;
+    static const int force_stages = getenv("VLT_STREAM_STAGES") ? atoi(getenv("VLT_STREAM_STAGES")) : 0;
+    uint32_t per_sm = fixed + 2 * STREAM_STAGE <= half ? 2 : 1;
+    if (force_bps) per_sm = uint32_t(force_bps);
+    uint32_t n_stages = uint32_t(std::min<size_t>(((per_sm == 2 ? half : whole) - fixed) / STREAM_STAGE, per_sm == 2 ? 3 : STREAM_MAX_STAGES));
+    if (force_stages) n_stages = uint32_t(force_stages);
+    const uint32_t grid = std::min(a.m / 16, sm_count * per_sm);
+    const size_t smem = fixed + size_t(n_stages) * STREAM_STAGE;
+    if (a.int8) launch_pdl(matmul_stream_kernel<true>, grid, 512, smem, s, a, n_stages);
+    else launch_pdl(matmul_stream_kernel<false>, grid, 512, smem, s, a, n_stages);
 }
 
 }  // namespace vlt

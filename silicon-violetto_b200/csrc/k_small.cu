@@ -222,8 +222,55 @@ __global__ void __launch_bounds__(64 * COMBINE_HEADS) attn_combine_kernel(const 
     if (out_b) out_b[at] = f32_to_bf16(r);
 }
 
+// The same merge for many splits (a long context read by few streams): one block per (token, head), four groups of 64
+// threads that take every fourth split each, so that a thread has at most 16 loads and all of them in flight at once;
+// the groups' sums are added in group order.
+__global__ void __launch_bounds__(256) attn_combine_wide_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_heads, float* out, uint16_t* out_b) {
+    pdl_start();
+    __shared__ float ws[64], lws[64], red[8], og[4][64];
+    const uint32_t t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, grp = tid / 64, d = tid % 64;
+    const float* pp = part + (size_t(t) * n_heads + h) * max_splits * ATTN_PART;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {  // (asked for first: they do not depend on the statistics)
+        const uint32_t s = grp + 4 * i;
+        v[i] = s < max_splits ? pp[s * ATTN_PART + 4 + d] : 0.0f;
+    }
+    const bool has = tid < max_splits;  // at most 64 splits (engine.cu `attention_split`)
+    const float ms = has ? pp[tid * ATTN_PART] : -INFINITY;
+    const float ls = has ? pp[tid * ATTN_PART + 1] : 0.0f;
+    float mm = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    if (tid % 32 == 0) red[tid / 32] = mm;
+    __syncthreads();
+    mm = fmaxf(red[0], red[1]);
+    if (tid < 64) {
+        const float w = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+        ws[tid] = w;
+        lws[tid] = ls * w;
+    }
+    __syncthreads();
+    float oo = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const uint32_t s = grp + 4 * i;
+        if (s < max_splits && ws[s] != 0.0f) oo += v[i] * ws[s];  // an empty split's o was never written: whatever is there must not count
+    }
+    og[grp][d] = oo;
+    __syncthreads();
+    if (tid >= 64) return;
+    float ll = 0.0f;
+    for (uint32_t s = 0; s < max_splits; s++) ll += lws[s];
+    const float r = (((og[0][d] + og[1][d]) + og[2][d]) + og[3][d]) / ll;
+    const size_t at = size_t(t) * n_heads * 64 + h * 64 + d;
+    out[at] = r;
+    if (out_b) out_b[at] = f32_to_bf16(r);
+}
+
 void launch_attn_combine(const AttnArgs& a, cudaStream_t s) {
-    if (a.n * a.n_heads >= 2048) launch_pdl(attn_combine_kernel<4>, dim3(a.n, (a.n_heads + 3) / 4), 256, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
+    if (a.max_splits > 8) launch_pdl(attn_combine_wide_kernel, dim3(a.n, a.n_heads), 256, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
+    else if (a.n * a.n_heads >= 2048) launch_pdl(attn_combine_kernel<4>, dim3(a.n, (a.n_heads + 3) / 4), 256, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
     else launch_pdl(attn_combine_kernel<1>, dim3(a.n, a.n_heads), 64, 0, s, a.part, a.max_splits, a.n_heads, a.out, a.out_b);
 }
 

@@ -45,6 +45,7 @@ struct MatArgs {
     bool int8;
     QkvEpilogue q;  // EPI_QKV only
     uint32_t t0;    // EPI_QKV in the streamed matmul: the step's token that this launch's token 0 is
+    uint32_t* err_flag;  // streamed matmul: device word set if a bounded wait ran out (optional)
     // The residual stream's sum of squares per token, kept by the tensor-core GEMMs themselves so that no row pass is
     // needed between them: an EPI_RESID GEMM with ssq_out writes, per 128-row tile of its output, sum(y^2) over the
     // tile's rows ([tile][ssq_stride]); a GEMM with ssq_in (and no inv_in) takes 1/rms = rsqrt(sum over ssq_tiles / k + eps).
