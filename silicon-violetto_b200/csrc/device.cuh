@@ -65,6 +65,10 @@ __device__ __forceinline__ uint32_t d_tree_node(uint32_t depth, uint32_t parent,
 // Programmatic dependent launch, first thing in a kernel started that way: let the kernel queued behind
 // this one be scheduled early (it waits in turn), then wait for the kernel before this one to complete.
 // From here on everything is ordered as if the kernels ran one after another; only launch latency overlaps.
+// With -DVLT_STEP_PROBE (a developer's build, VLT_NVCC_FLAGS in build.py) every kernel that starts through pdl_start()
+// leaves two time stamps of its first block, before and after the wait for its predecessor (tags 1 and 2), and
+// SP_MARK(tag) leaves more (3 / 4: the first / last block's end, 5: its main loop's start); vlt_engine_free prints them
+// to stderr as "SP <ns> <tag> <blocks> <threads> <file>", which shows where a step's time goes between kernels.
 #ifdef VLT_STEP_PROBE
 }  // namespace vlt
 #include <cstdio>

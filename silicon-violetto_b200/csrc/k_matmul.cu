@@ -6,7 +6,6 @@
 // per group of consecutive k, X fp32 [n][k]. 1/rms(X[t]) is accumulated in the same pass
 // (kernels.metal:239-251,286), so a folded RMSNorm costs no extra kernel.
 #include <algorithm>
-#include <cstdlib>
 
 #include "kernels.h"
 
@@ -216,10 +215,12 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
         if (lane < 16)
             st_bulk_load(st_smem_u32(stages + size_t(st) * STREAM_STAGE + lane * STREAM_ROW), a.W + size_t(rt * 16 + lane) * row_bytes + size_t(sl) * STREAM_SLICE, bytes, bar);
     };
+    if (tid == 0 && blockIdx.x == 0) SP_MARK(1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (warp == 0)
         for (uint32_t i = 0; i < min(n_stages, n_items); i++) request(i);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0 && blockIdx.x == 0) SP_MARK(2);
 
     // Activations: the [n][k] array in float4 steps over all threads, up to eight loads in flight each; bf16 into
     // shared memory, and a sum of squares per token (a thread's step belongs to one token, found by division).
@@ -261,6 +262,7 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
     }
     __syncthreads();
 
+    if (tid == 0 && blockIdx.x == 0) SP_MARK(5);
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     uint32_t buf = 0;
     const bool has_x = g < a.n;
@@ -350,6 +352,7 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
             buf ^= 1;
         }
     }
+    if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) SP_MARK(blockIdx.x == 0 ? 3 : 4);
 }
 
 // Shared memory of the streamed kernel besides its stages: two buffers for the warps' sums and the staged activations.
@@ -377,12 +380,8 @@ void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
     // Two resident blocks per SM with two or three stages each where shared memory allows (their row-tile meetings
     // then overlap), else one with up to six.
     const size_t fixed = stream_fixed_smem(a), half = 110 * 1024, whole = 220 * 1024;
-    static const int force_bps = getenv("VLT_STREAM_BPS") ? atoi(getenv("VLT_STREAM_BPS")) : 0;
-    static const int force_stages = getenv("VLT_STREAM_STAGES") ? atoi(getenv("VLT_STREAM_STAGES")) : 0;
-    uint32_t per_sm = fixed + 2 * STREAM_STAGE <= half ? 2 : 1;
-    if (force_bps) per_sm = uint32_t(force_bps);
-    uint32_t n_stages = uint32_t(std::min<size_t>(((per_sm == 2 ? half : whole) - fixed) / STREAM_STAGE, per_sm == 2 ? 3 : STREAM_MAX_STAGES));
-    if (force_stages) n_stages = uint32_t(force_stages);
+    const uint32_t per_sm = fixed + 2 * STREAM_STAGE <= half ? 2 : 1;
+    const uint32_t n_stages = uint32_t(std::min<size_t>(((per_sm == 2 ? half : whole) - fixed) / STREAM_STAGE, per_sm == 2 ? 3 : STREAM_MAX_STAGES));
     const uint32_t grid = std::min(a.m / 16, sm_count * per_sm);
     const size_t smem = fixed + size_t(n_stages) * STREAM_STAGE;
     if (a.int8) launch_pdl(matmul_stream_kernel<true>, grid, 512, smem, s, a, n_stages);
