@@ -25,6 +25,11 @@ def _stale(obj: Path, src: Path) -> bool:
 def build(force: bool = False, verbose: bool = False) -> Path:
     objdir = HERE / "build"
     objdir.mkdir(exist_ok=True)
+    # Objects compiled with other extra flags (VLT_NVCC_FLAGS: the developer probes) are not reused.
+    extra, stamp = os.environ.get("VLT_NVCC_FLAGS", ""), objdir / "flags.txt"
+    if not stamp.exists() or stamp.read_text() != extra:
+        force = True
+        stamp.write_text(extra)
     jobs = []
     for name in SOURCES:
         src, obj = CSRC / name, objdir / (name + ".o")

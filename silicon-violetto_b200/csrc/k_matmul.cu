@@ -177,6 +177,7 @@ constexpr uint32_t STREAM_SLICE = 2048;                      // bytes of a weigh
 constexpr uint32_t STREAM_ROW = STREAM_SLICE + 64;           // a stage's row stride
 constexpr uint32_t STREAM_STAGE = 16 * STREAM_ROW;
 constexpr uint32_t STREAM_MAX_STAGES = 6;
+constexpr uint32_t STREAM_SCALE_TILES = 32;
 
 template <bool INT8>
 __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32_t n_stages) {
@@ -187,6 +188,7 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
     extern __shared__ __align__(128) uint8_t stream_smem[];
     __shared__ uint64_t bars[STREAM_MAX_STAGES];
     __shared__ float ss_part[NW][8];
+    __shared__ float row_scale[STREAM_SCALE_TILES * 16];  // one scale per row: the block's first row tiles' (the rest are read when needed)
     __shared__ float inv_s[8];
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane >> 2, t = lane & 3;
     const uint32_t xrs = a.k * 2 + 16;                                         // bytes per staged activation row
@@ -219,6 +221,10 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (warp == 0)
         for (uint32_t i = 0; i < min(n_stages, n_items); i++) request(i);
+    // The rows' scales are read once each, so every row tile would wait for HBM in its turn: all of them now.
+    if (INT8 && !grouped)
+        for (uint32_t i = tid; i < min(my_row_tiles, STREAM_SCALE_TILES) * 16; i += 512)
+            row_scale[i] = bf16_to_f32(a.scales[(blockIdx.x + (i / 16) * gridDim.x) * 16 + i % 16]);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0 && blockIdx.x == 0) SP_MARK(2);
 
@@ -269,9 +275,9 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
     for (uint32_t item = 0; item < n_items; item++) {
         const uint32_t rt = blockIdx.x + (item / slices) * gridDim.x, sl = item % slices, st = item % n_stages, row0 = rt * 16;
         const uint32_t count = min(n_tiles - sl * 32, 32u);  // 64-byte tiles in this slice
-        // One scale per row, applied once after the sum: asked for before the wait, so that it is there when needed.
+        // One scale per row, applied once after the sum (from shared memory; past its room, asked for before the wait).
         float row_sl = 1.0f, row_sh = 1.0f;
-        if (INT8 && !grouped && sl + 1 == slices) {
+        if (INT8 && !grouped && sl + 1 == slices && item / slices >= STREAM_SCALE_TILES) {
             row_sl = bf16_to_f32(a.scales[row0 + g]);
             row_sh = bf16_to_f32(a.scales[row0 + g + 8]);
         }
@@ -318,6 +324,10 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
             }
         }
         if (sl + 1 == slices) {  // the row tile is complete: add up the warps and store
+            if (INT8 && !grouped && item / slices < STREAM_SCALE_TILES) {
+                row_sl = row_scale[(item / slices) * 16 + g];
+                row_sh = row_scale[(item / slices) * 16 + g + 8];
+            }
             acc[0] *= row_sl; acc[1] *= row_sl; acc[2] *= row_sh; acc[3] *= row_sh;
             float* rb = red + size_t(buf) * NW * 128 + warp * 128;  // [row][token]
             rb[g * 8 + 2 * t] = acc[0];

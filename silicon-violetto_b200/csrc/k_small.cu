@@ -495,6 +495,10 @@ __device__ void sc_scan(float v, uint32_t buf, ScExchange* xc, float* vals, floa
     total = base[32];
 }
 
+// STAGED: the first pass leaves this block's share of the row in shared memory ([id / 1024][thread], 512 bytes per 1024
+// ids) and the later passes -- above all the one thread that walks its ids one by one to find the token -- read it there
+// instead of waiting for L2 at every step.
+template <bool STAGED>
 __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sample_cluster_kernel(const float* __restrict__ logits, const SampleRow* __restrict__ rows,
                                                                                                  uint32_t* out, const uint32_t* __restrict__ meta, uint32_t vocab) {
     pdl_start();
@@ -508,6 +512,8 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
     const SampleRow row = rows[r];
     const uint32_t pos = row.tok == NO_TOK ? row.pos : meta[2 * row.tok + 1] + 1;
     const float* x = logits + size_t(r) * vocab;
+    extern __shared__ float sc_row[];
+    auto own = [&](uint32_t i) { return STAGED ? sc_row[(i / SAMPLE_THREADS) * SC_THREADS + tid] : x[i]; };  // for this thread's ids only
     constexpr uint32_t B = 8;  // a thread's ids in batches: the loads of a batch go out together, the arithmetic keeps the id order
     float lmax = -FLT_MAX;
     uint32_t tok = 0xffffffffu;
@@ -517,9 +523,16 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
 #pragma unroll
         for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
 #pragma unroll
-        for (uint32_t k = 0; k < B; k++) better(lmax, tok, v[k], i0 + k * SAMPLE_THREADS);
+        for (uint32_t k = 0; k < B; k++) {
+            if (STAGED) sc_row[((i0 + k * SAMPLE_THREADS) / SAMPLE_THREADS) * SC_THREADS + tid] = v[k];
+            better(lmax, tok, v[k], i0 + k * SAMPLE_THREADS);
+        }
     }
-    for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) better(lmax, tok, x[i], i);
+    for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) {
+        const float xi = x[i];
+        if (STAGED) sc_row[(i / SAMPLE_THREADS) * SC_THREADS + tid] = xi;
+        better(lmax, tok, xi, i);
+    }
     warp_best(lmax, tok);
     if (lane == 0) { wbv[tid / 32] = lmax; wbi[tid / 32] = tok; }
     if (tid == 0) { xc.pick[0] = NO_TOK; xc.pick[1] = NO_TOK; }
@@ -541,11 +554,11 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
         for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
             float v[B];
 #pragma unroll
-            for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+            for (uint32_t k = 0; k < B; k++) v[k] = own(i0 + k * SAMPLE_THREADS);
 #pragma unroll
             for (uint32_t k = 0; k < B; k++) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
         }
-        for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(x[i], lmax), c)));
+        for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(own(i), lmax), c)));
         float lo, hi, total;
         uint32_t scans = 0;
         sc_scan(sum, scans++ & 1, &xc, vals, pre, tot_all, base, rank, tid, lo, hi, total);
@@ -558,7 +571,7 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
                 float acc = 0.0f;
                 uint32_t j = 0xffffffffu;
                 for (uint32_t i = vt; i < vocab; i += SAMPLE_THREADS) {
-                    const float xi = x[i];
+                    const float xi = own(i);
                     if (!(xi > low)) continue;
                     const float e = soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c));
                     acc = __fadd_rn(acc, e);
@@ -583,13 +596,13 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
             for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
                 float v[B];
 #pragma unroll
-                for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+                for (uint32_t k = 0; k < B; k++) v[k] = own(i0 + k * SAMPLE_THREADS);
 #pragma unroll
                 for (uint32_t k = 0; k < B; k++)
                     if (v[k] > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
             }
             for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) {
-                const float xi = x[i];
+                const float xi = own(i);
                 if (xi > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c)));
             }
             sc_scan(q, scans++ & 1, &xc, vals, pre, tot_all, base, rank, tid, lo, hi, total);
@@ -606,16 +619,26 @@ void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, co
     // Enough rows to fill the SMs with one block each: the single-block form (at 160 rows the two take the same time,
     // bound by instruction issue); fewer: a cluster of 8 blocks per row (one stream's 5 rows: 95 -> about 25 us).
     if (n_rows > 96) { launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, s, logits, rows, out, meta, vocab); return; }
+    // A block's share of a row in shared memory (512 bytes per 1024 ids), if it fits.
+    const size_t stage = size_t((vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS) * SC_THREADS * 4;
+    const bool staged = stage <= 200 * 1024;
+    static bool configured = false;
+    if (!configured) {
+        VLT_CUDA(cudaFuncSetAttribute(sample_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_rows * SC_CTAS);
     cfg.blockDim = dim3(SC_THREADS);
+    cfg.dynamicSmemBytes = staged ? stage : 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, rows, out, meta, vocab));
+    if (staged) VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<true>, logits, rows, out, meta, vocab));
+    else VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<false>, logits, rows, out, meta, vocab));
     launch_counter()++;
 }
 
