@@ -67,7 +67,7 @@ __device__ __forceinline__ uint32_t d_tree_node(uint32_t depth, uint32_t parent,
 // From here on everything is ordered as if the kernels ran one after another; only launch latency overlaps.
 // With -DVLT_STEP_PROBE (a developer's build, VLT_NVCC_FLAGS in build.py) every kernel that starts through pdl_start()
 // leaves two time stamps of its first block, before and after the wait for its predecessor (tags 1 and 2), and
-// SP_MARK(tag) leaves more (3 / 4: the first / last block's end, 5: its main loop's start); vlt_engine_free prints them
+// the streamed matmul leaves more (3 / 4: the first / last block's end, 5: its main loop's start); vlt_engine_free prints them
 // to stderr as "SP <ns> <tag> <blocks> <threads> <file>", which shows where a step's time goes between kernels.
 #ifdef VLT_STEP_PROBE
 }  // namespace vlt
@@ -76,18 +76,31 @@ __device__ __forceinline__ uint32_t d_tree_node(uint32_t depth, uint32_t parent,
 namespace vlt {
 static __device__ unsigned long long sp_buf[4 * 16384];
 static __device__ unsigned int sp_n;
-__device__ __forceinline__ void sp_mark(unsigned tag) {
+__device__ __forceinline__ unsigned long long sp_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const unsigned i = atomicAdd(&sp_n, 1u);
-    if (i < 16384) { sp_buf[4 * i] = t; sp_buf[4 * i + 1] = tag; sp_buf[4 * i + 2] = gridDim.x * gridDim.y * gridDim.z; sp_buf[4 * i + 3] = blockDim.x; }
+    return t;
+}
+// Time stamps are taken where they belong and written later, several at once (the slot comes from an atomic whose
+// round trip would otherwise sit in the measured path).
+__device__ __forceinline__ void sp_write(const unsigned long long* t, const unsigned* tags, unsigned n) {
+    const unsigned i0 = atomicAdd(&sp_n, n);
+    for (unsigned j = 0; j < n; j++) {
+        const unsigned i = i0 + j;
+        if (i < 16384) { sp_buf[4 * i] = t[j]; sp_buf[4 * i + 1] = tags[j]; sp_buf[4 * i + 2] = gridDim.x * gridDim.y * gridDim.z; sp_buf[4 * i + 3] = blockDim.x; }
+    }
 }
 __device__ __forceinline__ void pdl_start() {
     const bool me = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
-    if (me) sp_mark(1);
+    unsigned long long t[2];
+    if (me) t[0] = sp_now();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (me) sp_mark(2);
+    if (me) {
+        t[1] = sp_now();
+        const unsigned tags[2] = {1, 2};
+        sp_write(t, tags, 2);
+    }
 }
 inline std::vector<void (*)()>& sp_registry() { static std::vector<void (*)()> v; return v; }
 static void sp_dump_tu() {
@@ -99,9 +112,11 @@ static void sp_dump_tu() {
     for (unsigned i = 0; i < n; i++) fprintf(stderr, "SP %llu %llu %llu %llu %s\n", h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3], __FILE__);
 }
 namespace { struct SpReg { SpReg() { sp_registry().push_back(&sp_dump_tu); } }; static SpReg sp_reg_instance; }
-#define SP_MARK(tag) sp_mark(tag)
+#define SP_TIME(var) var = sp_now()
+#define SP_WRITE(t, tags, n) sp_write(t, tags, n)
 #else
-#define SP_MARK(tag) do { } while (0)
+#define SP_TIME(var) do { } while (0)
+#define SP_WRITE(t, tags, n) do { } while (0)
 __device__ __forceinline__ void pdl_start() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -353,7 +353,7 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
 // tensor cores from registers; larger ones go in token blocks of 8 (the weights of one matrix
 // stay in L2 between blocks).
 void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real,
-                    const QkvEpilogue* q) {
+                    const QkvEpilogue* q, const uint16_t* xb, uint16_t* yb) {
     MatArgs a{};
     if (q) a.q = *q;
     a.err_flag = s.err_flag.as<uint32_t>();
@@ -371,7 +371,9 @@ void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint3
         a.n = std::min(8u, n - t0);
         a.t0 = t0;
         a.X = x + size_t(t0) * w.k;
+        a.Xb = xb ? xb + size_t(t0) * w.k : nullptr;
         a.Y = y ? y + size_t(t0) * out_w : nullptr;
+        a.Yb = yb ? yb + size_t(t0) * out_w : nullptr;
         a.base = base ? base + size_t(t0) * out_w : nullptr;
         a.inv_out = inv_out ? inv_out + t0 : nullptr;
         launch_matmul_stream(a, sm_count, stream);
@@ -522,7 +524,7 @@ void Engine::encode_layer_io(const LayerIO& io) {
         a.max_rows = io.max_rows;
         a.part = s.part.as<float>();
         a.out = s.attn.as<float>();
-        a.out_b = big ? s.attn_b.as<uint16_t>() : nullptr;
+        a.out_b = s.attn_b.as<uint16_t>();  // the o projection reads the bf16 copy (GEMM and streamed matmul alike)
         a.n = n;
         sp = span_begin(G_ATTN);
         if (!(skip & 4)) launch_attn_mma(a, stream);
@@ -546,9 +548,10 @@ void Engine::encode_layer_io(const LayerIO& io) {
         }
         if (!(skip & 64)) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), h, hb, EPI_RESID, h, nullptr, 0, nullptr, ssq);
     } else {
-        if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr);
-        if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
-        if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr);
+        // o and down fold no RMSNorm: they take the bf16 copies their producers leave (a bulk copy instead of a conversion pass).
+        if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr, 0, nullptr, tuning.plain_attention ? nullptr : s.attn_b.as<uint16_t>());  // (the scalar attention leaves fp32 only)
+        if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr, 0, nullptr, nullptr, s.act_b.as<uint16_t>());
+        if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr, 0, nullptr, s.act_b.as<uint16_t>());
     }
     span_end(sp);
 }

@@ -194,7 +194,8 @@ class Engine {
 
   private:
     KvArgs kv_args() const;
-    void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr);
+    void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr,
+                const uint16_t* xb = nullptr, uint16_t* yb = nullptr);
     bool stream_fits(const Matrix& w) const;
     // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
     void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,

@@ -33,7 +33,7 @@ struct MatArgs {
     const uint8_t* W;
     const uint16_t* scales;  // int8: bf16 [m][k / group]
     const float* X;          // [n][k]
-    const uint16_t* Xb;      // bf16 copy of X [n_pad][k] (tensor-core GEMM only)
+    const uint16_t* Xb;      // bf16 copy of X [n_pad][k]: the tensor-core GEMM's input; the streamed matmul takes it instead of X if given (needs no 1/rms then)
     float* Y;
     const float* base;  // EPI_RESID: y = base + acc (may alias Y)
     float* inv_out;     // EPI_NORM / EPI_SWIGLU / EPI_HEAD: 1 / rms(X[t]) is computed here ...

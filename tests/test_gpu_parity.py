@@ -132,6 +132,31 @@ def test_wide_matrices_take_the_unsplit_gemm_path(int8_group):
         print(f"{8 * count}-token step over wide matrices, int8_group={int8_group}: logits error {err:.2e}")
 
 
+@pytest.mark.parametrize("std", [0.0005, 4.0])
+def test_small_steps_with_activations_far_from_one_match_the_oracle(std, tmp_path):
+    """int8 weights in steps of at most 8 tokens are multiplied as fp16, the activations scaled per token by a power of
+    two when their largest magnitude leaves [2^-6, 2^15): weights 40 times smaller than usual (attention output and
+    SwiGLU products far below 2^-6) and 200 times larger (a residual stream beyond fp16's range) take that path."""
+    from silicon_violetto_b200 import synth
+    w = tmp_path / f"micro_std{std}.vlt"
+    synth.write_target(w, util.MICRO, seed=3, int8_group=0, std=std)
+    kw = dict(max_seqs=2, max_step_tokens=16, max_chunk=8, max_seq_len=64, max_head_rows=16)
+    prod = E.Engine(w, E.EngineConfig(global_kv_tokens=2 * 64, **kw))
+    orc = oracle.Engine(w, kv_tokens=2 * 64, **kw)
+    rng = np.random.default_rng(31)
+    a, b = prod.new_seq(), orc.new_seq()
+    assert a == b
+    for count in (5, 1, 8, 1):
+        runs = [(a, rng.integers(0, 512, count).astype(np.uint32), E.Rows.ALL, False)]
+        out = prod.debug_step(runs, E.StepOptions(read_logits=True))
+        orc.step(runs)
+        want = orc.array("logits").reshape(-1, 512)
+        scale = max(1.0, float(np.abs(want).max()))
+        err = float(np.abs(out.logits - want).max()) / scale
+        assert np.isfinite(out.logits).all() and err < TOL[0], (std, count, err, scale)
+    prod.close()
+
+
 def test_kv_cache_matches_the_oracle_after_prefill():
     prod, orc = pair("micro")
     a, b = prod.new_seq(), orc.new_seq()
