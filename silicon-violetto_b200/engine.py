@@ -195,7 +195,10 @@ class Engine:
             self.h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:  # at interpreter shutdown the module's globals may already be gone
+            pass
 
     def device_name(self) -> str:
         buf = C.create_string_buffer(256)
