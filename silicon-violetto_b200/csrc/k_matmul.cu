@@ -140,13 +140,21 @@ __device__ __forceinline__ void st_mbar_init(uint32_t bar, uint32_t count) { asm
 __device__ __forceinline__ void st_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ bool st_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// The whole warp waits (call it converged): one lane polls, so that a waiting block leaves the issue slots to the block
+// it shares the SM with, then every lane observes the completed phase itself. False if the limit ran out.
 __device__ __forceinline__ bool st_mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); i++) {
-        uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
+    bool ok = true;
+    if (threadIdx.x % 32 == 0) {
+        ok = false;
+        for (uint32_t i = 0; i < (1u << 22) && !ok; i++) ok = st_mbar_try(bar, parity);
     }
-    return false;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok && st_mbar_try(bar, parity);
 }
 __device__ __forceinline__ void st_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
