@@ -249,7 +249,7 @@ def main():
     ap.add_argument("--cpu-streams", type=int, default=8, help="streams of the CPU sample")
     ap.add_argument("--cpu-steps", type=int, default=10, help="timed verify steps of the CPU sample (the reference arm takes --steps, at most 20)")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--also-streams", default="1", help="comma list: extra passes at these stream counts on rank 0's engine (BASELINE quotes 1 and 32 streams); empty: none")
+    ap.add_argument("--also-streams", default="1", help="comma list: extra passes at these stream counts on rank 0's engine (the headline metric is quoted at 1 and 32 streams); empty: none")
     ap.add_argument("--no-model-drafter", action="store_true", help="skip the pass with the chain drafter loaded")
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")

@@ -19,9 +19,9 @@ import torch
 from . import vlt
 
 CONFIGS = {
-    # BASELINE configs[0]: the plumbing check.
+    # Benchmark configuration 0: the plumbing check.
     "tiny": dict(n_layers=2, d=256, n_heads=4, n_kv=2, hd=64, ffn=1024, vocab=4096, eps=1e-5, theta=500000.0, page=16),
-    # BASELINE configs[2..4]: the 1B target.
+    # Benchmark configurations 2 to 4: the 1B target.
     "1b": dict(n_layers=16, d=2048, n_heads=32, n_kv=8, hd=64, ffn=8192, vocab=128256, eps=1e-5, theta=500000.0, page=16),
 }
 META_VERSION = 1.0

@@ -1,5 +1,5 @@
 """The rejection-sampling acceptance kernel against the oracle: accepted lengths, replacement / bonus
-tokens and rollback offsets, bit for bit (BASELINE's single-kernel configuration: 32 streams, k = 4,
+tokens and rollback offsets, bit for bit (the benchmark's single-kernel configuration: 32 streams, k = 4,
 vocabulary 128256, bf16 logits drawn N(0, 3^2), temperature 1)."""
 import numpy as np
 import pytest

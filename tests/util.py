@@ -12,7 +12,7 @@ from silicon_violetto_b200 import synth
 
 _TMP = Path(tempfile.mkdtemp(prefix="vlt_tests_"))
 
-# A decoder smaller than BASELINE's plumbing config, for cases the CPU oracle must finish in a blink.
+# A decoder smaller than the benchmark's plumbing configuration, for cases the CPU oracle must finish in a blink.
 MICRO = dict(n_layers=2, d=256, n_heads=4, n_kv=2, hd=64, ffn=512, vocab=512, eps=1e-5, theta=500000.0, page=16)
 MICRO4 = dict(n_layers=1, d=256, n_heads=8, n_kv=2, hd=64, ffn=256, vocab=256, eps=1e-5, theta=500000.0, page=16)  # 4 query heads per kv head
 
