@@ -296,36 +296,31 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
         }
         if (INT8) {  // bf16 -> fp16 in place
             if (!st_mbar_wait(xbar, 0) && lane == 0 && a.err_flag) atomicExch(a.err_flag, 2u);
-            for (uint32_t i = tid; i < total; i += 512) {
-                const uint32_t tk = i / n4, c = i % n4;
-                const uint2 v = reinterpret_cast<const uint2*>(xs + size_t(tk) * xrs)[c];
-                const float mx = magnitude(v.x, v.y);
+            // (the token loop is unrolled, so a token's accumulators are registers and no index is divided)
+            for (uint32_t c = tid; c < n4; c += 512) {
 #pragma unroll
-                for (int b = 0; b < 8; b++) mxb[b] = tk == uint32_t(b) ? fmaxf(mxb[b], mx) : mxb[b];
-                put(tk, c, v.x, v.y, 1.0f);
+                for (int tk = 0; tk < 8; tk++) {
+                    if (uint32_t(tk) >= a.n) break;
+                    const uint2 v = reinterpret_cast<const uint2*>(xs + size_t(tk) * xrs)[c];
+                    mxb[tk] = fmaxf(mxb[tk], magnitude(v.x, v.y));
+                    put(tk, c, v.x, v.y, 1.0f);
+                }
             }
         }
     } else {
-        // fp32 [n][k] in float4 steps over all threads, up to eight loads in flight each; a sum of squares per token
-        // (a thread's step belongs to one token, found by division).
+        // fp32 [n][k]: a float4 of every token per thread and step, the tokens' loads in flight together; a sum of
+        // squares per token (the token loop is unrolled: a token's accumulators are registers).
         const float4* src = reinterpret_cast<const float4*>(a.X);
-        for (uint32_t i0 = tid; i0 < total; i0 += 512 * 8) {
+        for (uint32_t c = tid; c < n4; c += 512) {
             float4 v[8];
 #pragma unroll
-            for (int q = 0; q < 8; q++) v[q] = i0 + 512 * q < total ? src[i0 + 512 * q] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int tk = 0; tk < 8; tk++) v[tk] = uint32_t(tk) < a.n ? src[size_t(tk) * n4 + c] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const uint32_t i = i0 + 512 * q;
-                if (i >= total) break;
-                const uint32_t tk = i / n4, c = i % n4;
-                const float sq = v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
-                const uint32_t p0 = pack_bf16(v[q].x, v[q].y), p1 = pack_bf16(v[q].z, v[q].w);
-                const float mx = INT8 ? magnitude(p0, p1) : 0.0f;
-#pragma unroll
-                for (int b = 0; b < 8; b++) {
-                    ssb[b] += tk == uint32_t(b) ? sq : 0.0f;
-                    if (INT8) mxb[b] = tk == uint32_t(b) ? fmaxf(mxb[b], mx) : mxb[b];
-                }
+            for (int tk = 0; tk < 8; tk++) {
+                if (uint32_t(tk) >= a.n) break;
+                ssb[tk] += v[tk].x * v[tk].x + v[tk].y * v[tk].y + v[tk].z * v[tk].z + v[tk].w * v[tk].w;
+                const uint32_t p0 = pack_bf16(v[tk].x, v[tk].y), p1 = pack_bf16(v[tk].z, v[tk].w);
+                if (INT8) mxb[tk] = fmaxf(mxb[tk], magnitude(p0, p1));
                 put(tk, c, p0, p1, 1.0f);
             }
         }
@@ -333,10 +328,12 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
 #pragma unroll
     for (int b = 0; b < 8; b++) {
         float ss = ssb[b], mx = mxb[b];
+        if (uint32_t(b) < a.n) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (INT8) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            for (int o = 16; o > 0; o >>= 1) {
+                if (!a.Xb) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (INT8) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            }
         }
         if (lane == 0) { ss_part[warp][b] = ss; mx_part[warp][b] = mx; }
     }
