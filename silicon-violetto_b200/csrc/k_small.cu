@@ -517,7 +517,18 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
     constexpr uint32_t B = 8;  // a thread's ids in batches: the loads of a batch go out together, the arithmetic keeps the id order
     float lmax = -FLT_MAX;
     uint32_t tok = 0xffffffffu;
+    constexpr uint32_t B1 = STAGED ? 32 : B;  // the pass that reads global memory: few threads per row, so many loads each
     uint32_t i0 = vt;
+    for (; i0 + (B1 - 1) * SAMPLE_THREADS < vocab; i0 += B1 * SAMPLE_THREADS) {
+        float v[B1];
+#pragma unroll
+        for (uint32_t k = 0; k < B1; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
+#pragma unroll
+        for (uint32_t k = 0; k < B1; k++) {
+            if (STAGED) sc_row[((i0 + k * SAMPLE_THREADS) / SAMPLE_THREADS) * SC_THREADS + tid] = v[k];
+            better(lmax, tok, v[k], i0 + k * SAMPLE_THREADS);
+        }
+    }
     for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
         float v[B];
 #pragma unroll
