@@ -396,18 +396,36 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
             if (tid == 0) pick = 0xffffffffu;
             __syncthreads();
             const float lo = ex[ex_at(tid)];
-            if (lo <= target && target < ex[ex_at(tid + 1)]) {
+            // The one thread whose interval holds the target re-adds its terms in order until they pass it
+            // (kernels.metal:1540-1559). Its warp helps: the lanes fetch and exponentiate 32 of its ids at a time, and
+            // only the additions stay in the thread's order.
+            const bool mine = lo <= target && target < ex[ex_at(tid + 1)];
+            const uint32_t owners = __ballot_sync(0xffffffffu, mine);
+            if (owners) {
+                const int src = __ffs(owners) - 1;
+                const uint32_t first = __shfl_sync(0xffffffffu, tid, src);
+                const float rest = __fsub_rn(target, __shfl_sync(0xffffffffu, lo, src));
                 float acc = 0.0f;
                 uint32_t j = 0xffffffffu;
-                for (uint32_t i = tid; i < vocab; i += SAMPLE_THREADS) {
-                    const float xi = x[i];
-                    if (!(xi > low)) continue;
-                    const float e = soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c));
-                    acc = __fadd_rn(acc, e);
-                    if (e > 0.0f) j = i;
-                    if (__fsub_rn(target, lo) < acc) break;
+                bool done = false;
+                for (uint32_t i0w = first; i0w < vocab && !done; i0w += 32 * SAMPLE_THREADS) {
+                    const uint32_t i = i0w + lane * SAMPLE_THREADS;
+                    float e = 0.0f;
+                    bool live = false;
+                    if (i < vocab) {
+                        const float xi = x[i];
+                        if (xi > low) { e = soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c)); live = true; }
+                    }
+                    const uint32_t lives = __ballot_sync(0xffffffffu, live);
+                    for (uint32_t l = 0; l < 32 && !done; l++) {
+                        const float el = __shfl_sync(0xffffffffu, e, l);
+                        if (!((lives >> l) & 1u)) continue;
+                        acc = __fadd_rn(acc, el);
+                        if (el > 0.0f) j = i0w + l * SAMPLE_THREADS;
+                        if (rest < acc) done = true;
+                    }
                 }
-                pick = j;
+                if (int(lane) == src) pick = j;
             }
             __syncthreads();
             const uint32_t j = pick;
@@ -578,18 +596,34 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
         for (uint32_t round = 0; round < SAMPLE_ROUNDS; round++) {
             const float target = __fmul_rn(uniform01(row.seed_lo, row.seed_hi, pos, round), total);
             const uint32_t pb = round & 1;
-            if (lo <= target && target < hi) {
+            // At most one thread of the cluster owns the target (the scan never decreases); its warp helps it as in
+            // sample_kernel: 32 of its ids at a time, the additions in the thread's order.
+            const uint32_t owners = __ballot_sync(0xffffffffu, lo <= target && target < hi);
+            if (owners) {
+                const int src = __ffs(owners) - 1;
+                const uint32_t first = __shfl_sync(0xffffffffu, vt, src), col = __shfl_sync(0xffffffffu, tid, src);
+                const float rest = __fsub_rn(target, __shfl_sync(0xffffffffu, lo, src));
                 float acc = 0.0f;
                 uint32_t j = 0xffffffffu;
-                for (uint32_t i = vt; i < vocab; i += SAMPLE_THREADS) {
-                    const float xi = own(i);
-                    if (!(xi > low)) continue;
-                    const float e = soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c));
-                    acc = __fadd_rn(acc, e);
-                    if (e > 0.0f) j = i;
-                    if (__fsub_rn(target, lo) < acc) break;
+                bool done = false;
+                for (uint32_t i0w = first; i0w < vocab && !done; i0w += 32 * SAMPLE_THREADS) {
+                    const uint32_t i = i0w + lane * SAMPLE_THREADS;
+                    float e = 0.0f;
+                    bool live = false;
+                    if (i < vocab) {
+                        const float xi = STAGED ? sc_row[(i / SAMPLE_THREADS) * SC_THREADS + col] : x[i];
+                        if (xi > low) { e = soft_exp2(__fmul_rn(__fsub_rn(xi, lmax), c)); live = true; }
+                    }
+                    const uint32_t lives = __ballot_sync(0xffffffffu, live);
+                    for (uint32_t l = 0; l < 32 && !done; l++) {
+                        const float el = __shfl_sync(0xffffffffu, e, l);
+                        if (!((lives >> l) & 1u)) continue;
+                        acc = __fadd_rn(acc, el);
+                        if (el > 0.0f) j = i0w + l * SAMPLE_THREADS;
+                        if (rest < acc) done = true;
+                    }
                 }
-                xc.pick[pb] = j;  // at most one thread of the cluster is here: the scan never decreases
+                if (int(lane) == src) xc.pick[pb] = j;
             }
             sc_cluster_sync();
             uint32_t j = NO_TOK;

@@ -100,16 +100,30 @@ __device__ uint32_t inverse_cdf(uint32_t vocab, W w, float u, uint32_t fallback,
     if (tid == 0) *pick = 0xffffffffu;
     __syncthreads();
     const float lo = ex[ex_at(tid)];
-    if (lo <= target && target < ex[ex_at(tid + 1)]) {
+    // The one thread whose interval holds the target re-adds its terms in order until they pass it; its warp helps:
+    // the lanes evaluate 32 of its ids at a time, and only the additions stay in the thread's order.
+    const bool mine = lo <= target && target < ex[ex_at(tid + 1)];
+    const uint32_t owners = __ballot_sync(0xffffffffu, mine);
+    if (owners) {
+        const uint32_t lane = tid % 32;
+        const int src = __ffs(owners) - 1;
+        const uint32_t first = __shfl_sync(0xffffffffu, tid, src);
+        const float rest = __fsub_rn(target, __shfl_sync(0xffffffffu, lo, src));
         float acc = 0.0f;
         uint32_t j = 0xffffffffu;
-        for (uint32_t i = tid; i < vocab; i += THREADS) {
-            const float e = w(i);
-            acc = __fadd_rn(acc, e);
-            if (e > 0.0f) j = i;
-            if (__fsub_rn(target, lo) < acc) break;
+        bool done = false;
+        for (uint32_t i0 = first; i0 < vocab && !done; i0 += 32 * THREADS) {
+            const uint32_t i = i0 + lane * THREADS;
+            const float e = i < vocab ? w(i) : 0.0f;
+            const uint32_t n_live = min(32u, (vocab - i0 + THREADS - 1) / THREADS);
+            for (uint32_t l = 0; l < n_live && !done; l++) {
+                const float el = __shfl_sync(0xffffffffu, e, l);
+                acc = __fadd_rn(acc, el);
+                if (el > 0.0f) j = i0 + l * THREADS;
+                if (rest < acc) done = true;
+            }
         }
-        *pick = j;
+        if (int(lane) == src) *pick = j;
     }
     __syncthreads();
     const uint32_t j = *pick;
