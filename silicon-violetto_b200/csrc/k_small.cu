@@ -195,6 +195,11 @@ __global__ void __launch_bounds__(64 * COMBINE_HEADS) attn_combine_kernel(const 
     const float* pp = part + (size_t(t) * n_heads + (live ? h : 0)) * max_splits * ATTN_PART;
     // A thread per split for the statistics (at most 64 splits, engine.cu `attention_split`), then a thread
     // per dim with the splits' loads independent of each other.
+    // The first eight splits' values are asked for together with the statistics (they do not depend on them): one
+    // round trip to L2 instead of two.
+    float v8[8];
+#pragma unroll
+    for (uint32_t s = 0; s < 8; s++) v8[s] = s < max_splits ? pp[s * ATTN_PART + 4 + d] : 0.0f;
     const bool has = d < max_splits;
     const float ms = has ? pp[d * ATTN_PART] : -INFINITY;
     const float ls = has ? pp[d * ATTN_PART + 1] : 0.0f;
@@ -210,9 +215,12 @@ __global__ void __launch_bounds__(64 * COMBINE_HEADS) attn_combine_kernel(const 
     __syncthreads();
     float ll = 0.0f, oo = 0.0f;
     for (uint32_t s = 0; s < max_splits; s++) ll += lws[hl][s];
+#pragma unroll
+    for (uint32_t s = 0; s < 8; s++)  // an empty split's o was never written: whatever is there must not count
+        if (s < max_splits) oo += ws[hl][s] == 0.0f ? 0.0f : v8[s] * ws[hl][s];
 #pragma unroll 8
-    for (uint32_t s = 0; s < max_splits; s++) {
-        const float v = pp[s * ATTN_PART + 4 + d];  // an empty split's o was never written: whatever is there must not count
+    for (uint32_t s = 8; s < max_splits; s++) {
+        const float v = pp[s * ATTN_PART + 4 + d];
         oo += ws[hl][s] == 0.0f ? 0.0f : v * ws[hl][s];
     }
     if (!live) return;
