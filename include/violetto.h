@@ -60,7 +60,6 @@ typedef struct {
     uint32_t attn_keys_per_cta; /* keys one attention CTA takes; 0: sized to fill the SMs */
     uint32_t gemm_min_rows;     /* steps with at least this many tokens use the tensor-core GEMM; 0: default */
     uint32_t plain_attention;   /* 1: the scalar attention kernel (cross-check only) */
-    uint32_t use_graphs;        /* 1: replay decode steps as CUDA graphs */
 } VltTuning;
 
 /* engine/src/engine.rs:100-138 `Sampling`. */
@@ -224,7 +223,8 @@ void vlt_generator_set_replay_mistakes(VltGenerator* g, float rate, uint32_t see
 /* Inspection, for parity tests against the CPU oracle: copies a named engine array into `out`
  * (u32 words: "lens", "feed", "tree", "gen", "path", "path_len", "on_path", "page_table",
  * "free_pages", "tokens", "tin", "vis", "head_rows", "sample_rows", "runs", "out_ids",
- * "emitted", "meta", "tiles"). Returns the word count through n. */
+ * "emitted", "meta", "tiles"; "attn_split": the last plan's keys per attention split and its split count).
+ * Returns the word count through n. */
 int vlt_debug_read(VltEngine* e, const char* name, uint32_t* out, uint64_t cap, uint64_t* n);
 /* Plans a step without running it (Engine::plan, engine/src/engine/plan.rs:47-150); works on a host-only engine. */
 int vlt_debug_plan(VltEngine* e, const VltRun* runs, const uint32_t* verify, const uint32_t* heads, uint32_t n_runs, uint32_t hidden);

@@ -279,8 +279,10 @@ class Engine:
         if lib().orc_seq_set_sampling(self.h, C.c_uint32(s), C.c_float(temperature), C.c_float(top_p), C.c_uint64(seed)):
             raise RuntimeError(_err())
 
-    def bench_fill(self, s: int, n: int):
-        if lib().orc_bench_fill(self.h, C.c_uint32(s), C.c_uint32(n)):
+    def bench_fill(self, s: int, n: int, seed: int = 0):
+        """Advances a sequence without computing it; seed != 0 fills the new positions' K/V with the hashed values
+        the CUDA engine's bench_fill writes for the same seed."""
+        if lib().orc_bench_fill(self.h, C.c_uint32(s), C.c_uint32(n), C.c_uint32(seed)):
             raise RuntimeError(_err())
 
     def set_gen(self, slot: int, remaining: int, stop=()):

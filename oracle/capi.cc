@@ -136,7 +136,7 @@ int orc_seq_set_sampling(void* h, uint32_t id, float temperature, float top_p, u
 }
 // engine.rs:281-285 `settle`.
 void orc_seq_settle(void* h, uint32_t id, uint32_t unused) { Engine* e = static_cast<Engine*>(h); if (id < e->seqs.size() && e->seqs[id]) e->seqs[id]->len -= unused; }
-int orc_bench_fill(void* h, uint32_t id, uint32_t len) { try { static_cast<Engine*>(h)->bench_fill(id, len); return 0; } catch (const std::exception& e) { return fail(e); } }
+int orc_bench_fill(void* h, uint32_t id, uint32_t len, uint32_t seed) { try { static_cast<Engine*>(h)->bench_fill(id, len, seed); return 0; } catch (const std::exception& e) { return fail(e); } }
 void orc_set_gen(void* h, uint32_t slot, uint32_t remaining, const uint32_t* stop, uint32_t nstop) {
     GenState g{remaining, 0, nstop, 0, {0}};
     for (uint32_t i = 0; i < nstop && i < MAX_STOP; i++) g.stop[i] = stop[i];

@@ -266,12 +266,32 @@ struct Engine {
             pages.push_back(page);
         }
     }
-    // hooks.rs:28-36 `bench_fill`.
-    void bench_fill(uint32_t s, uint32_t len) {
+    // hooks.rs:28-36 `bench_fill`: the sequence advances without being computed. The reference leaves the new
+    // positions' K/V as allocated; with a seed they are filled with the same hashed values the CUDA engine's fill
+    // writes (Philox of (position, layer * 64 + kv head, pair of dims, slot) under the key (seed, 0x6b76): four
+    // words -> k pair, v pair, each (u >> 8) * 2^-24 mapped to [-1, 1) and rounded to bf16), so that a step over a
+    // filled context can be compared value for value.
+    void bench_fill(uint32_t s, uint32_t len, uint32_t seed = 0) {
         Seq& q = seq(s);
+        const uint32_t from = q.len;
         q.len += len;
         lens[s] = q.len;
         reserve(s, q.pages, q.len);
+        if (!seed) return;
+        auto val = [](uint32_t u) { return (float(u >> 8) * 0x1p-24f - 0.5f) * 2.0f; };
+#pragma omp parallel for schedule(static) collapse(2)
+        for (int64_t l = 0; l < int64_t(md.n_layers); l++)
+            for (int64_t pos = from; pos < int64_t(q.len); pos++)
+                for (uint32_t g = 0; g < md.n_kv; g++) {
+                    const size_t at = kv_row(uint32_t(l), s, g, uint32_t(pos));
+                    for (uint32_t d = 0; d < md.hd / 2; d++) {
+                        const U4 h = philox(U4{uint32_t(pos), uint32_t(l) * 64 + g, d, s}, seed, 0x6b76u);
+                        k_cache[at + 2 * d] = f32_to_bf16(val(h.x));
+                        k_cache[at + 2 * d + 1] = f32_to_bf16(val(h.y));
+                        v_cache[at + 2 * d] = f32_to_bf16(val(h.z));
+                        v_cache[at + 2 * d + 1] = f32_to_bf16(val(h.w));
+                    }
+                }
     }
 
     // ---- plan.rs:47-150 `plan` (the attention split heuristics are device-specific and left out).

@@ -33,13 +33,22 @@ static int guard(F&& f) {
         return 1;
     }
 }
+// Every entry that may touch the GPU makes the engine's device current first: one thread may hold engines on
+// several devices (one engine per GPU makes a replica), and a launch goes to whichever device is current.
 static Engine& eng(VltEngine* e) {
     if (!e || !e->e) throw Error("null engine");
+    e->e->make_current();
     return *e->e;
 }
 static Generator& gen(VltGenerator* g) {
     if (!g || !g->g) throw Error("null generator");
+    g->g->eng.make_current();
     return *g->g;
+}
+// The synchronous step entries use step set 0 and the engine's one stream of state: not while a generator has a step queued.
+static void no_step_in_flight(VltEngine* e) {
+    if (e->generator && e->generator->g && e->generator->g->has_step_in_flight())
+        throw Error("the engine's generator has a step in flight: collect it (vlt_generator_step until idle, or free the generator) before stepping the engine directly");
 }
 static Sampling sampling_of(const VltSampling& s) { return Sampling{s.temperature, s.top_p, s.seed}; }
 
@@ -70,7 +79,6 @@ int vlt_engine_new(const char* weights_path, const VltEngineConfig* cfg, const V
             t.attn_keys_per_cta = tuning->attn_keys_per_cta;
             t.gemm_min_rows = tuning->gemm_min_rows;
             t.plain_attention = tuning->plain_attention != 0;
-            t.use_graphs = tuning->use_graphs != 0;
         }
         auto h = std::make_unique<VltEngine>();
         h->e = std::make_unique<Engine>(weights_path, c, t);
@@ -86,6 +94,7 @@ void vlt_engine_free(VltEngine* e) {
 #ifdef VLT_STEP_PROBE
     vlt_sp_dump_all();
 #endif
+    if (e->e) e->e->make_current();
     if (e->generator) e->generator->g.reset();  // a generator must not outlive its engine
     delete e;
 }
@@ -108,7 +117,7 @@ int vlt_model_desc(VltEngine* e, VltModelDesc* out) {
 }
 
 int vlt_seq_new(VltEngine* e, uint32_t* seq) { return guard([&] { *seq = eng(e).new_seq(); }); }
-void vlt_seq_free(VltEngine* e, uint32_t seq) { if (e && e->e) e->e->free_seq(seq); }
+void vlt_seq_free(VltEngine* e, uint32_t seq) { if (e && e->e) { e->e->make_current(); e->e->free_seq(seq); } }
 uint32_t vlt_seq_len(VltEngine* e, uint32_t seq) { return e && e->e ? e->e->seq_len(seq) : 0; }
 int vlt_seq_set_sampling(VltEngine* e, uint32_t seq, const VltSampling* s) { return guard([&] { eng(e).set_sampling(seq, sampling_of(*s)); }); }
 
@@ -136,6 +145,7 @@ static void fill_output(Engine& en, const StepOutput& r, VltStepOutput* out) {
 int vlt_step(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOptions* opts, VltStepOutput* out) {
     return guard([&] {
         Engine& en = eng(e);
+        no_step_in_flight(e);
         std::vector<PlanRun> rs;
         for (uint32_t i = 0; i < n_runs; i++) {
             for (uint32_t j = 0; j < runs[i].n_tokens; j++)
@@ -212,6 +222,7 @@ int vlt_generator_new(VltEngine* e, VltGenerator** out) {
 
 void vlt_generator_free(VltGenerator* g) {
     if (!g) return;
+    if (g->g) g->g->eng.make_current();
     if (g->owner && g->owner->generator == g) g->owner->generator = nullptr;
     delete g;
 }
@@ -234,7 +245,7 @@ int vlt_generator_submit(VltGenerator* g, const VltRequest* r, uint32_t* req_id)
     });
 }
 
-void vlt_generator_cancel(VltGenerator* g, uint32_t req_id) { if (g && g->g) g->g->cancel(req_id); }
+void vlt_generator_cancel(VltGenerator* g, uint32_t req_id) { if (g && g->g) { g->g->eng.make_current(); g->g->cancel(req_id); } }
 
 int vlt_generator_step(VltGenerator* g, VltEvent* events, uint32_t cap, uint32_t* n_events) {
     return guard([&] {
@@ -280,6 +291,8 @@ int vlt_debug_write(VltEngine* e, const char* name, uint64_t index, const uint32
 
 int vlt_debug_plan(VltEngine* e, const VltRun* runs, const uint32_t* verify, const uint32_t* heads, uint32_t n_runs, uint32_t hidden) {
     return guard([&] {
+        eng(e);
+        no_step_in_flight(e);
         std::vector<PlanRun> rs;
         for (uint32_t i = 0; i < n_runs; i++) rs.push_back(PlanRun{runs[i].seq, runs[i].tokens, runs[i].n_tokens, Rows(heads[i]), verify[i] != 0});
         eng(e).plan(0, rs, Rows(hidden));
@@ -291,6 +304,7 @@ int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, con
                    uint32_t replay, float replay_rate, uint32_t replay_seed, VltStepOutput* out) {
     return guard([&] {
         Engine& en = eng(e);
+        no_step_in_flight(e);
         std::vector<PlanRun> rs;
         for (uint32_t i = 0; i < n_runs; i++) rs.push_back(PlanRun{runs[i].seq, runs[i].tokens, runs[i].n_tokens, Rows(heads[i]), verify[i] != 0});
         StepOptions o{Rows::None, Rows(opts->hidden), opts->read_logits != 0, opts->read_taps != 0};
@@ -314,6 +328,8 @@ void vlt_debug_settle(VltEngine* e, uint32_t seq, uint32_t unused) { if (e && e-
 
 int vlt_debug_set_gen(VltEngine* e, uint32_t slot, uint32_t remaining, const uint32_t* stop, uint32_t n_stop) {
     return guard([&] {
+        if (n_stop > MAX_STOP) throw Error(std::to_string(n_stop) + " stop tokens (max " + std::to_string(MAX_STOP) + ")");
+        if (slot >= eng(e).cfg.max_seqs) throw Error("slot out of range");
         GenState g = gen_open();
         g.remaining = remaining;
         g.nstop = n_stop;

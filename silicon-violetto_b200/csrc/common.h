@@ -2,10 +2,12 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
 #include <cstdio>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -24,10 +26,31 @@ struct Error : std::runtime_error {
     } while (0)
 
 // Kernels this library has launched (every launcher counts its own), for benchmarks to report.
-inline uint64_t& launch_counter() {
-    static uint64_t count = 0;
+// Atomic: engines on several threads and the engine-less entry points all count here.
+inline std::atomic<uint64_t>& launch_counter() {
+    static std::atomic<uint64_t> count{0};
     return count;
 }
+
+// Work that must happen once per CUDA device (cudaFuncSetAttribute applies to the current device only, and one
+// process may hold engines on several devices): `once(f)` runs f the first time it is called with a given device
+// current, under a lock, so that a second thread on the same device waits for the set-up instead of racing it.
+class PerDevice {
+  public:
+    template <typename F>
+    void once(F&& f) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+        std::lock_guard<std::mutex> lock(mu_);
+        if ((done_ >> dev) & 1ull) return;
+        f();
+        done_ |= 1ull << dev;
+    }
+
+  private:
+    std::mutex mu_;
+    uint64_t done_ = 0;
+};
 
 // engine/src/engine/kernels.rs:14-29.
 constexpr uint32_t FEED_ROW = 0xffff0000u;
@@ -69,10 +92,14 @@ struct ReplayArgs {
 
 // A buffer on the device, or on the host for a host-only (planning) engine. Written and read
 // through explicit copies; step inputs use the pinned mirror for asynchronous uploads.
+// `order`: the stream whose kernels use the buffer. With it set, write() and read() are copies on that stream
+// (ordered against the kernels before and after them; a pageable source is staged before the call returns, so
+// the caller may reuse it). Without it they are set-up copies that have landed when the call returns.
 struct Buffer {
     void* dev = nullptr;
     size_t bytes = 0;
     bool host_only = false;
+    cudaStream_t order = nullptr;
 
     Buffer() = default;
     Buffer(const Buffer&) = delete;
@@ -80,7 +107,7 @@ struct Buffer {
     Buffer(Buffer&& o) noexcept { *this = std::move(o); }
     Buffer& operator=(Buffer&& o) noexcept {
         release();
-        dev = o.dev; bytes = o.bytes; host_only = o.host_only;
+        dev = o.dev; bytes = o.bytes; host_only = o.host_only; order = o.order;
         o.dev = nullptr; o.bytes = 0;
         return *this;
     }
@@ -107,18 +134,33 @@ struct Buffer {
     }
     template <typename T> T* as() const { return static_cast<T*>(dev); }
 
-    // Synchronous copies (set-up and inspection paths).
     void write(size_t offset_bytes, const void* src, size_t n) const {
         if (n == 0) return;
         if (offset_bytes + n > bytes) throw Error("buffer write out of range");
-        if (host_only) std::memcpy(static_cast<char*>(dev) + offset_bytes, src, n);
-        else VLT_CUDA(cudaMemcpy(static_cast<char*>(dev) + offset_bytes, src, n, cudaMemcpyHostToDevice));
+        char* dst = static_cast<char*>(dev) + offset_bytes;
+        if (host_only) {
+            std::memcpy(dst, src, n);
+        } else if (order) {
+            VLT_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, order));
+        } else {
+            // A blocking copy from pageable memory may return once the bytes are staged, before the DMA lands, and
+            // the engine's streams do not wait for the legacy stream: wait for it here.
+            VLT_CUDA(cudaMemcpy(dst, src, n, cudaMemcpyHostToDevice));
+            VLT_CUDA(cudaStreamSynchronize(cudaStreamLegacy));
+        }
     }
     void read(size_t offset_bytes, void* dst, size_t n) const {
         if (n == 0) return;
         if (offset_bytes + n > bytes) throw Error("buffer read out of range");
-        if (host_only) std::memcpy(dst, static_cast<char*>(dev) + offset_bytes, n);
-        else VLT_CUDA(cudaMemcpy(dst, static_cast<char*>(dev) + offset_bytes, n, cudaMemcpyDeviceToHost));
+        const char* src = static_cast<const char*>(dev) + offset_bytes;
+        if (host_only) {
+            std::memcpy(dst, src, n);
+        } else if (order) {
+            VLT_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, order));
+            VLT_CUDA(cudaStreamSynchronize(order));
+        } else {
+            VLT_CUDA(cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost));
+        }
     }
     template <typename T> void write_vec(size_t index, const std::vector<T>& v) const { write(index * sizeof(T), v.data(), v.size() * sizeof(T)); }
     template <typename T> std::vector<T> read_vec(size_t index, size_t count) const {
@@ -144,7 +186,7 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     VLT_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
-    launch_counter()++;
+    launch_counter().fetch_add(1, std::memory_order_relaxed);
 }
 #endif
 

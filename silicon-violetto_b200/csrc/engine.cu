@@ -31,13 +31,19 @@ void KvCache::init(const EngineConfig& cfg, const ModelDesc& md, uint32_t n_laye
 
 // engine/src/engine/kv.rs:51-58.
 void KvCache::reserve(uint32_t slot, std::vector<uint32_t>& pages, uint32_t len) {
+    const size_t had = pages.size();
     while (size_t(pages.size()) * page < len) {
-        if (free_pages.empty()) throw Error("global KV pool exhausted");
-        const uint32_t pg = free_pages.back();
+        if (free_pages.empty()) {
+            // Nothing was written yet: give back what this call took, so that a failed reserve changes nothing.
+            while (pages.size() > had) { free_pages.push_back(pages.back()); pages.pop_back(); }
+            throw Error("global KV pool exhausted");
+        }
+        pages.push_back(free_pages.back());
         free_pages.pop_back();
-        page_table.write((size_t(slot) * max_pages + pages.size()) * 4, &pg, 4);
-        pages.push_back(pg);
     }
+    // A sequence's table entries are consecutive: the new ones go up in one copy, ordered on the engine's stream
+    // before the kernels of the step that reads them.
+    if (pages.size() > had) page_table.write((size_t(slot) * max_pages + had) * 4, pages.data() + had, (pages.size() - had) * 4);
 }
 
 // engine/src/engine/kv.rs:60-62.
@@ -63,6 +69,7 @@ void StepSet::init(const EngineConfig& cfg) {
     at = 0;
     o_out_ids = take(hr * 4);
     o_emitted = take(ms * 4);
+    o_err = take(4);
     out_bytes = at;
     dev_in.alloc(in_bytes, host_only);
     dev_out.alloc(out_bytes, host_only);
@@ -153,6 +160,9 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
     f(s.trace, ho ? 1 : ms * size_t(cfg.max_seq_len));
     f(s.trace_len, ms);
     f(s.err_flag, 1);
+    // Per-slot state and the page table are written while steps are queued (admission, page reservation): those
+    // copies go on the engine's stream, ordered between the steps' kernels.
+    for (Buffer* b : {&s.lens, &s.feed, &s.tree, &s.gen, &s.path, &s.path_len, &s.on_path, &s.trace, &s.trace_len, &s.err_flag, &s.meta, &kv.page_table}) b->order = stream;
     std::vector<uint32_t> chains(ms * FEED_W);
     for (size_t i = 0; i < chains.size(); i++) chains[i] = chain_node(uint32_t(i % FEED_W));  // buffers.rs:112-113
     s.tree.write_vec(0, chains);
@@ -186,6 +196,10 @@ Engine::~Engine() {
         cudaStreamDestroy(copy_out);
     }
     for (auto& st : sets) st.release();
+}
+
+void Engine::make_current() const {
+    if (!cfg.host_only) VLT_CUDA(cudaSetDevice(cfg.device));
 }
 
 std::string Engine::device_name() const {
@@ -288,6 +302,8 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
         const PlanRun& run = runs[ri];
         const uint32_t id = run.seq, count = run.count;
         if (count == 0 || count > cfg.max_chunk) throw Error(std::to_string(count) + " tokens for one sequence in a step (max_chunk " + std::to_string(cfg.max_chunk) + ")");
+        // A verify run is one attention tile and one slot's feed/tree rows (engine/src/engine/kernels.rs:28-29, generate.rs:216-220).
+        if (run.verify && count > VERIFY_T) throw Error("a verify run takes at most " + std::to_string(VERIFY_T) + " rows, not " + std::to_string(count));
         for (uint32_t i = 0; i < count; i++) {
             const uint32_t tk = run.tokens[i];
             if (tk >= FEED_ROW && tk - FEED_ROW >= FEED_W) throw Error("only " + std::to_string(FEED_W) + " GPU-fed tokens per slot");
@@ -346,6 +362,8 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
     p.max_keys = max_keys;
     attention_split(p, max_keys, p.tiles);
     last_plan_n = n;
+    last_split[0] = p.keys_per_split;
+    last_split[1] = p.max_splits;
     return p;
 }
 
@@ -613,6 +631,7 @@ void Engine::encode_replay(uint32_t set, const Plan& p, const ReplayArgs& ra) {
 
 void Engine::commit(uint32_t set) {
     StepSet& st = sets[set];
+    VLT_CUDA(cudaMemcpyAsync(st.out<uint32_t>(st.o_err), s.err_flag.dev, 4, cudaMemcpyDeviceToDevice, stream));
     VLT_CUDA(cudaEventRecord(st.computed, stream));
     VLT_CUDA(cudaStreamWaitEvent(copy_out, st.computed, 0));
     VLT_CUDA(cudaMemcpyAsync(st.host_out, st.dev_out.dev, st.out_bytes, cudaMemcpyDeviceToHost, copy_out));
@@ -628,13 +647,14 @@ double Engine::wait(uint32_t set) {
     return double(ms) * 1e-3;
 }
 
-void Engine::check_device_error() {
-    uint32_t flag = 0;
-    s.err_flag.read(0, &flag, 4);
+// The device error word of a collected step (it came down with the step's results: no copy of its own).
+void Engine::check_device_error(uint32_t set) {
+    const StepSet& st = sets[set];
+    const uint32_t flag = *st.hout<uint32_t>(st.o_err);
     if (flag) {
-        const uint32_t zero = 0;
-        s.err_flag.write(0, &zero, 4);
-        throw Error("a kernel's bounded wait ran out (device error flag " + std::to_string(flag) + ")");
+        VLT_CUDA(cudaMemsetAsync(s.err_flag.dev, 0, 4, stream));
+        *st.hout<uint32_t>(st.o_err) = 0;
+        throw Error("a kernel's bounded wait ran out (device error flag " + std::to_string(flag) + "): the step's results are not valid");
     }
 }
 
@@ -650,12 +670,11 @@ void Engine::upload_set(uint32_t set) {
 
 // engine/src/engine.rs:381-389 `load_drafter`, for the chain drafter (see Engine::Drafter).
 void Engine::load_drafter(const std::string& path) {
-    if (cfg.host_only) throw Error("this engine was created host-only: it cannot hold a drafter");
     for (const auto& q : seqs)
         if (q) throw Error("load the drafter before the first sequence (it changes how many pages a step reserves)");
     auto dr = std::make_unique<Drafter>();
     const ModelDesc& md = model.md;
-    dr->w.load(path, false);
+    dr->w.load(path, cfg.host_only);
     const std::vector<float> m = dr->w.f32s("meta");
     if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw Error(path + ": `meta` is not a version-1 one-layer chain drafter");
     const uint32_t v = uint32_t(m[3]), d = md.d;
@@ -673,6 +692,10 @@ void Engine::load_drafter(const std::string& path) {
     for (uint32_t i = 0; i < v; i++) {
         ids[i] = uint32_t(idf[i]);
         if (ids[i] >= md.vocab) throw Error(path + ": draft vocabulary id out of the target's range");
+    }
+    if (cfg.host_only) {  // a planning engine keeps the drafter's effect on page reservation and admission, nothing else
+        drafter = std::move(dr);
+        return;
     }
     const size_t ms = cfg.max_seqs, ms16 = (ms + 15) / 16 * 16, n = cfg.max_step_tokens;
     dr->vocab_ids.alloc(size_t(v) * 4, false);
@@ -786,7 +809,7 @@ StepOutput Engine::step_runs(const std::vector<PlanRun>& runs, const StepOptions
     commit(0);
     StepOutput out;
     out.gpu_seconds = wait(0);
-    check_device_error();
+    check_device_error(0);
     const StepSet& st = sets[0];
     out.ids.assign(st.hout<uint32_t>(st.o_out_ids), st.hout<uint32_t>(st.o_out_ids) + p.n_head);
     if (opts.read_logits) out.logits = s.logits.read_vec<float>(0, size_t(p.n_head) * model.md.vocab);
@@ -1029,6 +1052,7 @@ std::vector<uint32_t> Engine::debug_read(const std::string& name) {
     if (name == "meta") return whole(s.meta, 2 * size_t(last_plan_n));
     if (name == "page_table") return whole(kv.page_table, ms * kv.max_pages);
     if (name == "free_pages") return kv.free_pages;
+    if (name == "attn_split") return {last_split[0], last_split[1]};
     if (drafter) {
         const size_t pool = size_t(kv.n_pages) * model.md.n_kv * kv.page * model.md.hd;
         if (name == "draft_logits") return whole(drafter->logits, size_t(VERIFY_T - 1) * ms * drafter->v);  // [pass][run slot][v] f32

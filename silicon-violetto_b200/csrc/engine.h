@@ -24,7 +24,7 @@ struct EngineConfig {
 struct Tuning {
     uint32_t spec_tokens = 32, spec_tokens_short = 8, spec_kv = 24576, spec_rows_long = 4;
     uint32_t sm_count = 0, attn_keys_per_cta = 0, gemm_min_rows = 0;
-    bool plain_attention = false, use_graphs = false;
+    bool plain_attention = false;
 };
 
 // engine/src/engine.rs:100-138.
@@ -79,7 +79,7 @@ struct StepSet {
     uint8_t* host_out = nullptr;  // pinned
     size_t in_bytes = 0, out_bytes = 0;
     size_t o_tokens = 0, o_tin = 0, o_vis = 0, o_head_rows = 0, o_hidden_rows = 0, o_sample_rows = 0, o_tiles = 0, o_runs = 0;  // byte offsets in *_in
-    size_t o_out_ids = 0, o_emitted = 0;                                                                                       // in *_out
+    size_t o_out_ids = 0, o_emitted = 0, o_err = 0;  // in *_out; o_err: the device error word as it stood when the step ended
     cudaEvent_t start = nullptr, done = nullptr;        // around the step on the engine's stream / after its results reached the host
     cudaEvent_t uploaded = nullptr, computed = nullptr;  // the step's inputs are on the device / its last kernel has run
     bool host_only = false;
@@ -109,6 +109,7 @@ class Engine {
     Engine(const Engine&) = delete;
 
     std::string device_name() const;
+    void make_current() const;  // the engine's device becomes the calling thread's current one
     uint32_t new_seq();
     void free_seq(uint32_t id);
     uint32_t seq_len(uint32_t id) const;
@@ -146,7 +147,7 @@ class Engine {
     void set_trace(uint32_t slot, const uint32_t* trace, uint32_t n);
     std::vector<uint32_t> debug_read(const std::string& name);
     void debug_write(const std::string& name, size_t index, const uint32_t* data, size_t n);
-    void check_device_error();
+    void check_device_error(uint32_t set);
 
     // Measurement: two stream marks (GPU time between them), and, while `profile` is on, the GPU
     // time of each kernel group of the queued steps (cuda events around the group's launches).
@@ -217,7 +218,7 @@ class Engine {
     void encode_sample(uint32_t set, uint32_t rows);
     void attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const;
     const Buffer* named(const std::string& name, uint32_t* set_off, size_t* words) const;
-    uint32_t last_plan_n = 0;
+    uint32_t last_plan_n = 0, last_split[2] = {0, 1};  // the last plan's tokens, keys per attention split and split count
     cudaEvent_t marks[2] = {nullptr, nullptr};
     struct Span { cudaEvent_t a, b; int group; uint32_t launches; };
     std::vector<Span> spans;

@@ -58,10 +58,14 @@ uint32_t Generator::submit(const Request& req) {
     if (req.max_tokens == 0) throw Error("max_tokens is 0");
     const uint64_t kv_len = uint64_t(len) + req.max_tokens - 1;
     const uint32_t page = eng.kv.page;
-    if (kv_len > c.max_seq_len || (kv_len + page - 1) / page > eng.kv.n_pages)
+    // With a drafter loaded a step reserves pages VERIFY_T positions past itself (the draft passes write their own
+    // K/V there, Engine::plan), so the pool is budgeted for that reach; the reference reserves to the step's end
+    // only (plan.rs:75) and budgets kv_len (generate.rs:237).
+    const uint64_t reach = eng.has_drafter() ? std::min<uint64_t>(kv_len + VERIFY_T, c.max_seq_len) : kv_len;
+    if (kv_len > c.max_seq_len || (reach + page - 1) / page > eng.kv.n_pages)
         throw Error("a request reaching " + std::to_string(kv_len) + " positions doesn't fit max_seq_len or the KV pool");
     const uint32_t id = submitted++;
-    queue.push_back(Queued{id, req, uint32_t(kv_len)});
+    queue.push_back(Queued{id, req, uint32_t(reach)});
     return id;
 }
 
@@ -234,7 +238,7 @@ std::optional<Generator::InFlight> Generator::encode_next() {
 // engine/src/engine/generate.rs:446-487 `collect`.
 void Generator::collect(const InFlight& f, std::vector<Event>& events) {
     const double gpu_seconds = eng.wait(f.set);
-    eng.check_device_error();
+    eng.check_device_error(f.set);
     const size_t before = events.size();
     collected = f.step;
     const StepSet& st = eng.sets[f.set];

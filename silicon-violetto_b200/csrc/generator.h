@@ -50,13 +50,15 @@ class Generator {
     void cancel(uint32_t id);
     std::vector<Event> step();
     bool is_idle() const { return queue.empty() && active.empty() && !in_flight; }
+    bool has_step_in_flight() const { return in_flight.has_value(); }
     void counts(uint32_t* queued, uint32_t* running) const { *queued = uint32_t(queue.size()); *running = uint32_t(active.size()); }
     void set_replay_mistakes(float rate, uint32_t seed) { replay_rate = rate; replay_seed = seed; }
     std::vector<StepStats> stats;
     bool hold = false;
+    Engine& eng;
 
   private:
-    struct Queued { uint32_t id; Request req; uint32_t kv_len; };
+    struct Queued { uint32_t id; Request req; uint32_t kv_len; };  // kv_len: the furthest position the request's steps reserve pages for
     struct Active {
         uint32_t id, seq;
         std::vector<uint32_t> feed;  // tokens the CPU feeds: the prompt, or the resumed token
@@ -76,7 +78,6 @@ class Generator {
     void collect(const InFlight& f, std::vector<Event>& events);
     void release();
 
-    Engine& eng;
     std::deque<Queued> queue;
     std::vector<Active> active;
     std::optional<InFlight> in_flight;

@@ -384,14 +384,13 @@ void launch_attn_mma(const AttnArgs& a, cudaStream_t s) {
     const size_t smem = size_t(ATTN_WARPS) * ATTN_STAGES * STAGE_BYTES + 1024;
     // kv heads fastest: the blocks that start together read neighbouring 2 KiB slabs of the same pages.
     const dim3 grid(a.kv.n_kv, a.max_splits, a.n_tiles);
-    static bool configured = false;
-    if (!configured) {
+    static PerDevice configured;
+    configured.once([smem] {
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         VLT_CUDA(cudaFuncSetAttribute(attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        configured = true;
-    }
+    });
     // n8 tiles of query columns the step's longest tile needs (at most VERIFY_T rows x G heads).
     const uint32_t rows = a.max_rows ? std::min(a.max_rows, VERIFY_T) : VERIFY_T, nt = (rows * G + 7) / 8;
     if (nt <= 1) launch_pdl(attn_mma_kernel<1>, grid, ATTN_WARPS * 32, smem, s, a, *a.maps);

@@ -6,9 +6,9 @@
 //     weight is read from HBM once whatever the number of streams;
 //   - operands come in by TMA (no multicast) into 128-byte-swizzled shared memory, a ring of
 //     stages guarded by mbarriers; tcgen05.mma, issued by one thread, accumulates fp32 in TMEM;
-//   - int8 weights arrive as raw bytes in a ring of their own; eight warps, in four groups that
-//     take k blocks in turn, turn each into bf16 (exactly) in the swizzled layout the MMA reads;
-//     the scale per output row is applied in the epilogue;
+//   - int8 weights arrive as raw bytes in a ring of their own; sixteen warps, in four groups that
+//     take k blocks in turn, turn each into bf16 (exactly) and store it into tensor memory, where
+//     the MMA takes its A operand from; the scale per output row is applied in the epilogue;
 //   - the epilogue warps read TMEM with tcgen05.ld and apply the fused epilogues (RMSNorm scale,
 //     residual add, SwiGLU on interleaved gate/up rows, head) before the coalesced store.
 // Every wait is bounded: on a time-out the kernel sets the error flag, frees its TMEM and returns.
@@ -614,7 +614,7 @@ bool gemm_supported(const MatArgs& a) {
 
 void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s) {
     static thread_local GemmMapCache cache;
-    static bool configured = false;
+    static PerDevice configured;
     const uint32_t n_pad = (a.n + 15) / 16 * 16;
     auto key = std::make_tuple(static_cast<const void*>(a.W), static_cast<const void*>(a.Xb), a.m, a.k, n_pad);
     auto it = cache.maps.find(key);
@@ -643,11 +643,10 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     // At least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
     // behind another one (blocks of different clusters waiting on each other's SMs could deadlock).
     const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 28, 116 * 1024);
-    if (!configured) {
+    configured.once([] {
         for (int i8 = 0; i8 < 2; i8++)
             for (uint32_t epi = EPI_NORM; epi <= EPI_QKV; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    });
     // Split k over a cluster when the tiles alone cannot fill the SMs (the reference splits K the
     // same way when a GEMM has few tiles, encode.rs:545-553).
     const uint32_t tiles = a.m / gemm::BM, nkb = a.k / gemm::BK;

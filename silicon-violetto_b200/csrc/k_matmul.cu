@@ -527,12 +527,11 @@ void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s) {
         launch_matmul_rows(a, s);
         return;
     }
-    static bool configured = false;
-    if (!configured) {
+    static PerDevice configured;
+    configured.once([] {
         VLT_CUDA(cudaFuncSetAttribute(matmul_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STREAM_SMEM_MAX)));
         VLT_CUDA(cudaFuncSetAttribute(matmul_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STREAM_SMEM_MAX)));
-        configured = true;
-    }
+    });
     // Two resident blocks per SM with two or three stages each where shared memory allows (their row-tile meetings
     // then overlap), else one with up to six.
     const size_t fixed = stream_fixed_smem(a), half = 108 * 1024, whole = STREAM_SMEM_MAX;

@@ -675,11 +675,8 @@ void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, co
     // A block's share of a row in shared memory (512 bytes per 1024 ids), if it fits.
     const size_t stage = size_t((vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS) * SC_THREADS * 4;
     const bool staged = stage <= 200 * 1024;
-    static bool configured = false;
-    if (!configured) {
-        VLT_CUDA(cudaFuncSetAttribute(sample_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
-    }
+    static PerDevice configured;
+    configured.once([] { VLT_CUDA(cudaFuncSetAttribute(sample_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); });
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_rows * SC_CTAS);
     cfg.blockDim = dim3(SC_THREADS);

@@ -39,7 +39,7 @@ class _Config(C.Structure):
 
 class _Tuning(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("spec_tokens", "spec_tokens_short", "spec_kv", "spec_rows_long", "spec_policy_off", "sm_count",
-                                          "attn_keys_per_cta", "gemm_min_rows", "plain_attention", "use_graphs")]
+                                          "attn_keys_per_cta", "gemm_min_rows", "plain_attention")]
 
 
 class _Sampling(C.Structure):
@@ -132,7 +132,6 @@ class Tuning:
     attn_keys_per_cta: int = 0
     gemm_min_rows: int = 0
     plain_attention: bool = False
-    use_graphs: bool = False
 
 
 @dataclass
@@ -181,7 +180,7 @@ class Engine:
         c = _Config(cfg.max_seqs, cfg.max_step_tokens, cfg.max_chunk, cfg.global_kv_tokens, cfg.max_seq_len, cfg.max_head_rows, cfg.device_ordinal,
                     FLAG_HOST_ONLY if cfg.host_only else 0)
         ct = _Tuning(t.spec_tokens, t.spec_tokens_short, t.spec_kv, t.spec_rows_long, int(t.spec_policy_off), t.sm_count, t.attn_keys_per_cta,
-                     t.gemm_min_rows, int(t.plain_attention), int(t.use_graphs))
+                     t.gemm_min_rows, int(t.plain_attention))
         self.h = C.c_void_p()
         self.cfg = cfg
         _check(lib().vlt_engine_new(str(weights).encode(), C.byref(c), C.byref(ct), C.byref(self.h)))

@@ -198,3 +198,48 @@ def test_sampling_is_checked():
         with pytest.raises(E.EngineError, match="needs a temperature of 0 or a normal positive one"):
             prod.set_sampling(s, bad)
     prod.set_sampling(s, E.Sampling(0.6, 0.95, 7))
+
+
+def test_inputs_that_would_overrun_device_arrays_are_refused_on_the_host():
+    """A verify run longer than one attention tile, more stop tokens than a slot's state holds, a slot past the
+    table: refused before any kernel could index out of its arrays."""
+    eng = E.Engine(util.weights("micro"), E.EngineConfig(host_only=True, max_seqs=2, max_step_tokens=64, max_chunk=32, max_seq_len=256, global_kv_tokens=256))
+    s = eng.new_seq()
+    with pytest.raises(E.EngineError, match="a verify run takes at most 8 rows"):
+        eng.debug_plan([(s, [E.FEED_ROW + i for i in range(9)], E.Rows.LAST, True)])
+    eng.debug_plan([(s, list(range(9)), E.Rows.LAST, False)])  # a plain run of the same length is fine
+    with pytest.raises(E.EngineError, match="9 stop tokens"):
+        eng.set_gen(s, 5, stop=list(range(9)))
+    with pytest.raises(E.EngineError, match="slot out of range"):
+        eng.set_gen(7, 5)
+    eng.set_gen(s, 5, stop=list(range(8)))
+
+
+def test_a_failed_page_reservation_changes_nothing():
+    """A step that does not fit the pool fails as a whole: the pages it had taken go back, in order."""
+    eng = E.Engine(util.weights("micro"), E.EngineConfig(host_only=True, max_seqs=2, max_step_tokens=64, max_chunk=64, max_seq_len=256, global_kv_tokens=48))
+    s = eng.new_seq()
+    before = eng.debug_read("free_pages").copy()
+    with pytest.raises(E.EngineError, match="global KV pool exhausted"):
+        eng.debug_plan([(s, list(range(50)), E.Rows.LAST, False)])
+    assert np.array_equal(eng.debug_read("free_pages"), before)
+
+
+def test_admission_budgets_the_drafters_reach(tmp_path):
+    """With a drafter loaded a step reserves pages 8 positions past itself; submit() budgets the pool for that reach,
+    so a request the pool holds only without the margin is refused up front instead of failing inside a step."""
+    from silicon_violetto_b200 import synth
+    d = tmp_path / "drafter.vlt"
+    synth.write_drafter(d, util.MICRO, seed=100, draft_vocab=64)
+    # 20 prompt tokens + 13 new ones reach 32 positions: exactly two pages.
+    cfg = E.EngineConfig(host_only=True, max_seqs=2, max_step_tokens=64, max_chunk=32, max_seq_len=256, global_kv_tokens=32, max_head_rows=8)
+    plain = E.Engine(util.weights("micro"), cfg)
+    with plain.generator() as g:
+        g.submit(E.Request(list(range(20)), 13))
+    drafted = E.Engine(util.weights("micro"), cfg)
+    drafted.load_drafter(d)
+    assert drafted.has_drafter()
+    with drafted.generator() as g:
+        with pytest.raises(E.EngineError, match="doesn't fit max_seq_len or the KV pool"):
+            g.submit(E.Request(list(range(20)), 13))
+        g.submit(E.Request(list(range(20)), 5))  # reaches 24 + 8 = 32 positions: fits
