@@ -90,9 +90,10 @@ typedef struct {
     float* hidden; /* [n_hidden][d_model]: final normed hidden state per hidden row */
     uint64_t hidden_cap;
     uint32_t n_hidden;
-    uint16_t* taps; /* [n_tokens][d_model] bf16(rms_norm(last layer's output)) if read_taps */
+    uint16_t* taps; /* [tap][n_tokens][d_model] bf16(rms_norm(a tapped layer's output)) if read_taps (see vlt_set_taps) */
     uint64_t taps_cap;
     double gpu_seconds;
+    uint32_t n_taps; /* tapped layers read back */
 } VltStepOutput;
 
 /* New: what the weight file's `meta` tensor describes (the reference hard-codes its model,
@@ -119,11 +120,35 @@ uint32_t vlt_seq_len(VltEngine* e, uint32_t seq);
 int vlt_seq_set_sampling(VltEngine* e, uint32_t seq, const VltSampling* s);
 /* Engine::step, engine.rs:310-314: one synchronous step of CPU-fed runs. */
 int vlt_step(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOptions* opts, VltStepOutput* out);
-/* Engine::set_taps / load_drafter / has_drafter, engine.rs:381-389, engine/drafter.rs:250-262.
- * The plain decoder taps its last layer only, so set_taps takes a switch. */
-int vlt_set_taps(VltEngine* e, uint32_t on);
+/* Engine::step_capture, engine.rs:318-355, with LayerCapture, engine.rs:175-188: a synchronous step that stops after
+ * every layer and hands that layer's intermediates (host memory, valid during the call) to `fn`: n rows each of
+ * resid_in [d_model] (the residual stream entering the layer), attn_in [d_model] (its RMS-normed rows), qkv [qkv_width]
+ * (q | k | v after the folded norm and RoPE, fp32: before the rounding to bf16 and q's softmax scale), sdpa_out
+ * [attn_width] (the attention's output), attn_out [d_model] (the o projection's output before the residual add), mlp_in
+ * [d_model] (the RMS-normed stream after attention), mlp_out [d_model] (the down projection's output before the residual
+ * add); resid_base is the reference's MUDD base (NULL for a plain decoder). */
+typedef struct {
+    uint32_t layer, n, d_model, qkv_width, attn_width;
+    const float *resid_in, *attn_in, *qkv, *sdpa_out, *attn_out, *mlp_in, *mlp_out, *resid_base;
+} VltLayerCapture;
+typedef void (*VltCaptureFn)(const VltLayerCapture* layer, void* user);
+int vlt_step_capture(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOptions* opts, VltCaptureFn fn, void* user, VltStepOutput* out);
+/* Engine::set_taps, engine.rs:381-389: taps these layers' outputs -- bf16(rms_norm(output)), kernels.metal:133-148 -- from the
+ * next step on, for VltStepOptions.read_taps ([tap][token][d_model], in the order given; with a drafter loaded the last layer
+ * stays tapped and comes last if it was not named). Engine::load_drafter / has_drafter, engine.rs:381-389, engine/drafter.rs:250-262. */
+int vlt_set_taps(VltEngine* e, const uint32_t* layers, uint32_t n_layers);
 int vlt_load_drafter(VltEngine* e, const char* path);
 int vlt_has_drafter(VltEngine* e);
+/* Which rule accepts drafts. VLT_ACCEPT_MATCH is the reference's `accept` (kernels.metal:1578-1657): every verify row
+ * draws the target's token, a draft is accepted if it equals the token drawn on its parent row. VLT_ACCEPT_REJECTION has
+ * no counterpart in the reference: a verify run whose drafts the chain drafter drew from its own distribution q at the
+ * sequence's temperature (top_p = 1, temperature > 0) is decided by speculative sampling -- draft i accepted with
+ * probability min(1, P(x) / Q(x)), the first rejected one replaced by a draw from the normalised max(0, P - Q), a bonus
+ * token from the last row if all pass -- inside the step, and committed through the same `accept` state (lens, feed,
+ * path, on_path, gen, emitted): rejected rows are rolled back by the sequence advancing only by what was accepted.
+ * Runs the rule does not fit (greedy or top-p sequences, replay drafts, draft trees) keep the reference's rule. */
+enum { VLT_ACCEPT_MATCH = 0, VLT_ACCEPT_REJECTION = 1 };
+int vlt_set_acceptance(VltEngine* e, uint32_t rule);
 
 /* Hooks, engine/src/engine/hooks.rs. */
 /* bench_fill, hooks.rs:28-36: advance a sequence without computing it. `seed` != 0 also fills
@@ -249,6 +274,10 @@ int vlt_debug_set_trace(VltEngine* e, uint32_t slot, const uint32_t* trace, uint
  * the bytes one step uploads and downloads. */
 /* vlt_debug_step then runs the loaded drafter for this many rows after the step (0: not). */
 void vlt_debug_set_draft_rows(VltEngine* e, uint32_t rows);
+/* The next vlt_debug_step replaces the logits its head computed ([head rows][vocab]) and the logits of its drafter's
+ * passes ([pass][run][draft vocabulary]) by these (either may be NULL / 0) before the sampler, the acceptance and the
+ * drafter's pick read them: the integer tail of a step on inputs identical to the oracle's. One step only. */
+int vlt_debug_force_logits(VltEngine* e, const float* logits, uint64_t n_logits, const float* draft_logits, uint64_t n_draft);
 int vlt_debug_mark(VltEngine* e, uint32_t which);
 int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms);
 uint64_t vlt_debug_launches(void);

@@ -296,6 +296,19 @@ class Engine:
     def set_replay(self, rate: float, seed: int):
         lib().orc_set_replay(self.h, C.c_float(rate), C.c_uint32(seed))
 
+    def set_capture(self, on: bool):
+        """Keep every layer's intermediates of the next steps (arrays cap_resid_in, cap_attn_in, cap_qkv, cap_sdpa_out,
+        cap_attn_out, cap_mlp_in, cap_mlp_out: [layer][n][width])."""
+        lib().orc_set_capture(self.h, C.c_uint32(int(on)))
+
+    def set_taps(self, layers):
+        a = np.ascontiguousarray(list(layers), np.uint32)
+        lib().orc_set_taps(self.h, _p(a), C.c_uint32(a.size))
+
+    def set_acceptance(self, rule: int):
+        """0: the reference's sample-then-match; 1: rejection sampling where a run's drafts came with their q rows."""
+        lib().orc_set_acceptance(self.h, C.c_uint32(rule))
+
     def load_drafter(self, path):
         if lib().orc_load_drafter(self.h, str(path).encode()):
             raise RuntimeError(_err())
@@ -316,7 +329,8 @@ class Engine:
         if lib().orc_array_write(self.h, name.encode(), C.c_uint64(index), _p(d), C.c_uint64(d.size)):
             raise RuntimeError(_err())
 
-    _F32 = ("logits", "hidden_out", "taps", "draft_logits", "carry")
+    _F32 = ("logits", "hidden_out", "taps", "draft_logits", "carry", "q_keep", "taps_all", "cap_resid_in", "cap_attn_in", "cap_qkv", "cap_sdpa_out", "cap_attn_out",
+            "cap_mlp_in", "cap_mlp_out")
     _U16 = ("k_cache", "v_cache", "draft_k_cache", "draft_v_cache")
 
     def array(self, name: str) -> np.ndarray:

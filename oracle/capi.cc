@@ -148,6 +148,10 @@ void orc_set_trace(void* h, uint32_t slot, const uint32_t* trace, uint32_t n) {
     e->trace_len[slot] = n;
 }
 int orc_load_drafter(void* h, const char* path) { try { static_cast<Engine*>(h)->load_drafter(path); return 0; } catch (const std::exception& e) { return fail(e); } }
+// 0: the reference's acceptance (sample, then match); 1: rejection sampling for runs whose drafts came with their q rows.
+void orc_set_acceptance(void* h, uint32_t rule) { static_cast<Engine*>(h)->accept_rule = rule; }
+void orc_set_capture(void* h, uint32_t on) { static_cast<Engine*>(h)->capture = on != 0; }
+void orc_set_taps(void* h, const uint32_t* layers, uint32_t n) { static_cast<Engine*>(h)->tap_layers.assign(layers, layers + n); }
 void orc_set_replay(void* h, float rate, uint32_t seed) {
     Engine* e = static_cast<Engine*>(h);
     e->replay = ReplayArgs{e->cfg.max_seq_len, seed, rate, e->md.vocab_real};
@@ -182,11 +186,14 @@ uint64_t orc_array(void* h, const char* name, const void** ptr) {
 #define ARR(x) if (n == #x) { *ptr = e->x.data(); return e->x.size(); }
     ARR(lens) ARR(feed) ARR(tree) ARR(path) ARR(path_len) ARR(on_path) ARR(trace_len) ARR(page_table) ARR(free_pages)
     ARR(tokens) ARR(tin) ARR(vis) ARR(head_rows) ARR(hidden_rows) ARR(out_ids) ARR(tiles) ARR(emitted) ARR(meta)
-    ARR(logits) ARR(hidden_out) ARR(taps) ARR(k_cache) ARR(v_cache) ARR(draft_logits)
+    ARR(logits) ARR(hidden_out) ARR(taps) ARR(k_cache) ARR(v_cache) ARR(draft_logits) ARR(taps_all)
+    ARR(cap_resid_in) ARR(cap_attn_in) ARR(cap_qkv) ARR(cap_sdpa_out) ARR(cap_attn_out) ARR(cap_mlp_in) ARR(cap_mlp_out)
 #undef ARR
     if (n == "draft_k_cache" && e->drafter) { *ptr = e->drafter->k_cache.data(); return e->drafter->k_cache.size(); }
     if (n == "draft_v_cache" && e->drafter) { *ptr = e->drafter->v_cache.data(); return e->drafter->v_cache.size(); }
     if (n == "carry" && e->drafter) { *ptr = e->drafter->carry.data(); return e->drafter->carry.size(); }
+    if (n == "q_rows" && e->drafter) { *ptr = e->drafter->q_rows.data(); return e->drafter->q_rows.size(); }
+    if (n == "q_keep" && e->drafter) { *ptr = e->drafter->q_keep.data(); return e->drafter->q_keep.size(); }
     if (n == "gen") { *ptr = e->gen.data(); return e->gen.size() * sizeof(GenState) / 4; }
     if (n == "runs") { *ptr = e->runs.data(); return e->runs.size() * 6; }
     if (n == "sample_rows") { *ptr = e->sample_rows.data(); return e->sample_rows.size() * 6; }

@@ -158,6 +158,10 @@ struct Drafter {
     std::vector<uint32_t> vocab;
     std::vector<uint16_t> k_cache, v_cache;  // [n_pages][n_kv][page][hd]
     std::vector<float> carry;                // [max_seqs][d]: the tap of each slot's last position
+    // For the rejection-sampling rule: the draft rows a slot's drafts were drawn from ([max_seqs][VERIFY_T - 1][v]),
+    // how many of them are current (0 once a step has used them), and the draft vocabulary's inverse map.
+    std::vector<float> q_keep;
+    std::vector<uint32_t> q_rows, index_of;
 };
 
 struct Engine {
@@ -185,6 +189,13 @@ struct Engine {
     std::unique_ptr<Drafter> drafter;
     std::vector<float> draft_logits;  // the drafter's passes, [rows - 1][runs][v]; rows of runs that did not draft stay 0
     std::vector<uint32_t> write_mask;  // per step token: does its K/V go to the cache (empty: all do)
+    // engine.rs:175-188 `LayerCapture`: with `capture` set, `forward` keeps every target layer's intermediates, [layer][n][width].
+    bool capture = false;
+    std::vector<float> cap_resid_in, cap_attn_in, cap_qkv, cap_sdpa_out, cap_attn_out, cap_mlp_in, cap_mlp_out;
+    // engine.rs:381-389 `set_taps`: bf16(rms_norm(output)) of these layers, [tap][n][d] (`taps` is the last layer's, always kept).
+    std::vector<uint32_t> tap_layers;
+    std::vector<float> taps_all;
+    uint32_t accept_rule = 0;  // 0: the reference's sample-then-match; 1: rejection sampling where a run's drafts came with their q rows
 
     Engine(const std::string& file_path, const EngineConfig& c) : file(VltFile::load(file_path)), cfg(c) {
         std::vector<float> m = file.f32s("meta");
@@ -242,6 +253,7 @@ struct Engine {
                 lens[s] = 0;
                 trace_len[s] = 0;
                 gen[s] = GenState{0xffffffffu, 0, 0, 0, {0}};
+                if (drafter) drafter->q_rows[s] = 0;
                 return s;
             }
         throw std::runtime_error("no free sequence slot");
@@ -414,17 +426,34 @@ struct Engine {
 
     // One decoder layer on x [n][d] in place: encode.rs:142-192 with the plain decoder's
     // parameters (scales and lambdas 1, no MUDD, gates, XSA or value embeddings).
-    void layer_forward(const Layer& L, uint32_t li, uint16_t* kc, uint16_t* vc, float* x, uint32_t n, uint32_t n_tiles) {
+    void layer_forward(const Layer& L, uint32_t li, uint16_t* kc, uint16_t* vc, float* x, uint32_t n, uint32_t n_tiles, bool keep = false) {
         const uint32_t d = md.d, QW = md.qkv_w();
         std::vector<float> inv(n), qkv(size_t(n) * QW), attn(size_t(n) * md.n_heads * md.hd), acc(size_t(n) * std::max(2 * md.ffn, QW)), act(size_t(n) * md.ffn);
+        auto put = [&](std::vector<float>& dst, const float* src, size_t width) { if (keep) dst.insert(dst.end(), src, src + size_t(n) * width); };
+        auto put_normed = [&](std::vector<float>& dst) {
+            if (!keep) return;
+            for (uint32_t t = 0; t < n; t++)
+                for (uint32_t j = 0; j < d; j++) dst.push_back(x[size_t(t) * d + j] * inv[t]);
+        };
+        put(cap_resid_in, x, d);
         inv_rms(x, n, d, md.eps, inv.data());
+        put_normed(cap_attn_in);
         matmul_raw(L.qkv, x, n, qkv.data());
         for (uint32_t t = 0; t < n; t++)
             for (uint32_t j = 0; j < QW; j++) qkv[size_t(t) * QW + j] *= inv[t];  // EPI_NORM
+        if (keep) {  // q | k | v with RoPE on the q and k heads, before the rounding and q's scale
+            std::vector<float> r = qkv;
+            for (uint32_t t = 0; t < n; t++)
+                for (uint32_t hh = 0; hh < md.n_heads + md.n_kv; hh++) rope_head(r.data() + size_t(t) * QW + hh * md.hd, meta[2 * t + 1]);
+            put(cap_qkv, r.data(), QW);
+        }
         attention(li, kc, vc, qkv.data(), n, n_tiles, attn.data());
+        put(cap_sdpa_out, attn.data(), md.n_heads * md.hd);
         matmul_raw(L.o, attn.data(), n, acc.data());
+        put(cap_attn_out, acc.data(), d);
         for (size_t i = 0; i < size_t(n) * d; i++) x[i] += acc[i];  // EPI_RESID: mixed
         inv_rms(x, n, d, md.eps, inv.data());
+        put_normed(cap_mlp_in);
         matmul_raw(L.gate_up, x, n, acc.data());
         for (uint32_t t = 0; t < n; t++)
             for (uint32_t j = 0; j < md.ffn; j++) {  // EPI_SWIGLU, kernels.metal:204-209
@@ -432,6 +461,7 @@ struct Engine {
                 act[size_t(t) * md.ffn + j] = g * (1.0f / (1.0f + std::exp(-g))) * u;
             }
         matmul_raw(L.down, act.data(), n, acc.data());
+        put(cap_mlp_out, acc.data(), d);
         for (size_t i = 0; i < size_t(n) * d; i++) x[i] += acc[i];
     }
 
@@ -454,8 +484,18 @@ struct Engine {
             meta[2 * t + 1] = lens[slot] + depth;
             for (uint32_t i = 0; i < d; i++) x[size_t(t) * d + i] = bf16_to_f32(embed[size_t(tok) * d + i]);
         }
-        for (uint32_t li = 0; li < md.n_layers; li++)
-            layer_forward(layers[li], li, k_cache.data(), v_cache.data(), x.data(), n, p.n_tiles);
+        for (std::vector<float>* c : {&cap_resid_in, &cap_attn_in, &cap_qkv, &cap_sdpa_out, &cap_attn_out, &cap_mlp_in, &cap_mlp_out}) c->clear();
+        taps_all.assign(tap_layers.size() * size_t(n) * d, 0.0f);
+        for (uint32_t li = 0; li < md.n_layers; li++) {
+            layer_forward(layers[li], li, k_cache.data(), v_cache.data(), x.data(), n, p.n_tiles, capture);
+            for (size_t ti = 0; ti < tap_layers.size(); ti++) {
+                if (tap_layers[ti] != li) continue;
+                std::vector<float> tinv(n);
+                inv_rms(x.data(), n, d, md.eps, tinv.data());
+                for (uint32_t t = 0; t < n; t++)
+                    for (uint32_t i = 0; i < d; i++) taps_all[(ti * n + t) * d + i] = round_bf16(x[size_t(t) * d + i] * tinv[t]);
+            }
+        }
         std::vector<float> inv(n);
         inv_rms(x.data(), n, d, md.eps, inv.data());
         taps.resize(size_t(n) * d);  // kernels.metal:133-148 `tap_rows`
@@ -484,9 +524,38 @@ struct Engine {
         }
         emitted.assign(p.n_runs, 0);
         on_path.assign(n, 0);
+        std::vector<uint32_t> decided(p.n_runs, 0);
+        if (accept_rule == 1 && drafter) {
+            for (uint32_t r = 0; r < p.n_runs; r++) {
+                if (spec_applies(r)) decided[r] = spec_decide(r);
+                drafter->q_rows[runs[r].slot] = 0;  // a slot's kept rows serve one step
+            }
+        }
         for (uint32_t r = 0; r < p.n_runs; r++)
-            accept_run(r, runs.data(), tokens.data(), out_ids.data(), lens.data(), feed.data(), gen.data(), emitted.data(), tree.data(), path.data(), path_len.data(), on_path.data());
+            accept_run(r, runs.data(), tokens.data(), out_ids.data(), lens.data(), feed.data(), gen.data(), emitted.data(), tree.data(), path.data(), path_len.data(), on_path.data(), decided[r]);
         if (p.branches) kv_compact(p, k_cache.data(), v_cache.data(), md.n_layers);
+    }
+
+    // Whether run r is decided by the rejection rule: a verify run of a sequence that samples (temperature > 0, no
+    // top-p cut), whose rows are a plain chain and whose drafts all came with a kept q row from the step before.
+    bool spec_applies(uint32_t r) const {
+        const RunIn& ru = runs[r];
+        if (!ru.verify || ru.count < 2 || ru.nhead != ru.count) return false;
+        const SampleRow& sr = sample_rows[ru.head0];
+        if (!(sr.temperature > 0.0f) || sr.top_p < 1.0f) return false;
+        if (drafter->q_rows[ru.slot] + 1 < ru.count) return false;
+        for (uint32_t c2 = 1; c2 < ru.count; c2++)
+            if (tree[ru.slot * FEED_W + c2] != chain_node(c2)) return false;
+        return true;
+    }
+    uint32_t spec_decide(uint32_t r) {
+        const RunIn& ru = runs[r];
+        const SampleRow& sr = sample_rows[ru.head0];
+        const uint32_t v = drafter->head.m;
+        uint32_t pos[FEED_W];
+        for (uint32_t i = 0; i < ru.count; i++) pos[i] = meta[2 * (ru.first + i) + 1];
+        return spec_step_run(logits.data() + size_t(ru.head0) * md.vocab, md.vocab, drafter->q_keep.data() + size_t(ru.slot) * (VERIFY_T - 1) * v, v,
+                             drafter->index_of.data(), tokens.data() + ru.first, pos, ru.count, sr.temperature, sr.seed_lo, sr.seed_hi, out_ids.data() + ru.head0);
     }
 
     // kernels.metal:1663-1693 `kv_compact` over `nl` layers of a cache with the pool's layout.
@@ -527,6 +596,10 @@ struct Engine {
         dr->k_cache.assign(pool, 0);
         dr->v_cache.assign(pool, 0);
         dr->carry.assign(size_t(cfg.max_seqs) * d, 0.0f);
+        dr->q_keep.assign(size_t(cfg.max_seqs) * (VERIFY_T - 1) * v, 0.0f);
+        dr->q_rows.assign(cfg.max_seqs, 0);
+        dr->index_of.assign(md.vocab, NO_TOK);
+        for (uint32_t j = 0; j < v; j++) dr->index_of[dr->vocab[j]] = j;
         drafter = std::move(dr);
     }
 
@@ -596,6 +669,16 @@ struct Engine {
                 for (uint32_t j = 1; j < v; j++)
                     if (row[j] > row[best]) best = j;
                 const uint32_t slot = runs[r].slot;
+                // Under the rejection rule a sampling sequence's draft is drawn from softmax(q / T) and its row is kept
+                // for the next step's test; otherwise the argmax, and nothing kept.
+                const SampleRow& sr = sample_rows[runs[r].head0];
+                if (accept_rule == 1 && sr.temperature > 0.0f && sr.top_p >= 1.0f) {
+                    best = draw_draft_index(row, v, sr.temperature, sr.seed_lo, sr.seed_hi, lens[slot] + i);
+                    std::copy_n(row, v, dr.q_keep.data() + (size_t(slot) * (VERIFY_T - 1) + i - 1) * v);
+                    dr.q_rows[slot] = i;
+                } else if (i == 1) {
+                    dr.q_rows[slot] = 0;
+                }
                 feed[slot * FEED_W + i] = dr.vocab[best];
                 tree[slot * FEED_W + i] = chain_node(i);
                 std::copy_n(row, v, draft_logits.data() + (size_t(i - 1) * nr + r) * v);

@@ -101,9 +101,12 @@ inline uint32_t sample_row(const float* x, uint32_t vocab, const SampleRow& row,
 }
 
 // kernels.metal:1605-1657 `accept`, one run. Arrays are the whole step's / engine's.
+// `decided` (not in the reference): if not 0, a verify run's candidates were settled before this by the
+// rejection-sampling rule (see spec_step_run): rows 0 .. decided - 1 are the path and out[head0 ..] already
+// holds their tokens; everything from the stop-token scan on is the reference's.
 inline void accept_run(uint32_t r, const RunIn* runs, const uint32_t* tokens, uint32_t* out, uint32_t* lens,
                        uint32_t* feed, GenState* gen, uint32_t* emitted, const uint32_t* tree, uint32_t* path,
-                       uint32_t* path_len, uint32_t* on_path) {
+                       uint32_t* path_len, uint32_t* on_path, uint32_t decided = 0) {
     const RunIn ru = runs[r];
     GenState& gs = gen[ru.slot];
     path_len[r] = 0;
@@ -114,7 +117,11 @@ inline void accept_run(uint32_t r, const RunIn* runs, const uint32_t* tokens, ui
     uint32_t first = ru.head0 + ru.nhead - 1, e = 1;
     uint32_t walk[FEED_W];
     walk[0] = 0;
-    if (ru.verify) {
+    if (ru.verify && decided) {
+        e = decided;
+        for (uint32_t j = 0; j < e; j++) walk[j] = j;
+        first = ru.head0;
+    } else if (ru.verify) {
         const uint32_t* node = tree + ru.slot * FEED_W;
         for (uint32_t c = 1, at = 0; c < ru.count; c++) {
             if (node_parent(node[c]) == at && tokens[ru.first + c] == out[ru.head0 + at]) walk[e++] = at = c;
@@ -246,14 +253,17 @@ inline void draft_tree_block(uint32_t first, uint32_t rows, uint32_t slot, const
 //   with all k accepted the bonus token is drawn from P_{k+1} the same way, round 0 of
 //   position pos0 + k.
 // Outputs: accepted (0..k), the token that follows the accepted drafts, rollback = k - accepted.
-inline void softmax_stats(const uint16_t* x, uint32_t vocab, float c, float& lmax, uint32_t& amax, float& z) {
+inline float logit_of(uint16_t x) { return bf16_to_f32(x); }
+inline float logit_of(float x) { return x; }
+template <typename T>
+inline void softmax_stats(const T* x, uint32_t vocab, float c, float& lmax, uint32_t& amax, float& z) {
     lmax = -FLT_MAX;
     amax = 0xffffffffu;
-    for (uint32_t i = 0; i < vocab; i++) better(lmax, amax, bf16_to_f32(x[i]), i);
+    for (uint32_t i = 0; i < vocab; i++) better(lmax, amax, logit_of(x[i]), i);
     std::vector<float> s(SAMPLE_THREADS), ex(SAMPLE_THREADS + 1);
     for (uint32_t t = 0; t < SAMPLE_THREADS; t++) {
         float a = 0.0f;
-        for (uint32_t i = t; i < vocab; i += SAMPLE_THREADS) a += soft_exp2((bf16_to_f32(x[i]) - lmax) * c);
+        for (uint32_t i = t; i < vocab; i += SAMPLE_THREADS) a += soft_exp2((logit_of(x[i]) - lmax) * c);
         s[t] = a;
     }
     tg_scan(s.data(), ex.data());
@@ -334,6 +344,63 @@ inline uint32_t draw_draft(const uint16_t* q, uint32_t vocab, float temperature,
     softmax_stats(q, vocab, c, qm, qa, zq);
     auto w = [&](uint32_t j) { return soft_exp2((bf16_to_f32(q[j]) - qm) * c); };
     return inverse_cdf(vocab, w, uniform01(seed_lo, seed_hi, pos, 2), qa);
+}
+
+// ---------------------------------------------------------------------------------------
+// The same rule inside the engine's step (NOT in the reference either), for a verify run whose drafts the chain
+// drafter drew in the step before. What differs from spec_accept_stream: the target's rows are the step's fp32
+// logits over the whole vocabulary; a draft row q_i is fp32 over the draft vocabulary of `v` ids (id_of[index],
+// index_of[id] or NO_TOK), its statistics and the draft's own draw taken in the sampler's order over draft
+// indices, and Q is 0 for an id outside that vocabulary (such a draft is rejected); the uniforms are keyed by the
+// position of the token they decide (pos[i] for draft i: round 0 the test, round 1 the replacement; the bonus
+// token's position is pos[count - 1] + 1, round 0). p: rows 0 .. count - 1 (row i - 1 scores draft i);
+// q: rows 1 .. count - 1 at q + (i - 1) * v; x: the run's tokens (x[i] is draft i). Returns the number of
+// candidates e = accepted + 1 and leaves them in out[0 .. e): the accepted drafts, then the drawn token.
+inline uint32_t spec_step_run(const float* p, uint32_t vocab, const float* q, uint32_t v, const uint32_t* index_of, const uint32_t* x, const uint32_t* pos,
+                              uint32_t count, float temperature, uint32_t seed_lo, uint32_t seed_hi, uint32_t* out) {
+    const float c = LOG2E / temperature;
+    for (uint32_t i = 1; i < count; i++) {
+        const float* pi = p + uint64_t(i - 1) * vocab;
+        const float* qi = q + uint64_t(i - 1) * v;
+        float pm, qm, zp, zq;
+        uint32_t pa, qa;
+        softmax_stats(pi, vocab, c, pm, pa, zp);
+        softmax_stats(qi, v, c, qm, qa, zq);
+        const uint32_t tok = x[i], idx = tok < vocab ? index_of[tok] : NO_TOK;
+        bool ok = false;
+        if (idx != NO_TOK) {
+            const float ep = soft_exp2((pi[tok] - pm) * c), eq = soft_exp2((qi[idx] - qm) * c);
+            const float u = uniform01(seed_lo, seed_hi, pos[i], 0);
+            ok = (u * eq) * zp < ep * zq;
+        }
+        if (ok) { out[i - 1] = tok; continue; }
+        auto resid = [&](uint32_t j) {
+            const float a = soft_exp2((pi[j] - pm) * c) * zq;
+            const float b = index_of[j] == NO_TOK ? 0.0f : soft_exp2((qi[index_of[j]] - qm) * c) * zp;
+            const float d = a - b;
+            return d > 0.0f ? d : 0.0f;
+        };
+        out[i - 1] = inverse_cdf(vocab, resid, uniform01(seed_lo, seed_hi, pos[i], 1), pa);
+        return i;
+    }
+    const float* pk = p + uint64_t(count - 1) * vocab;
+    float pm, zp;
+    uint32_t pa;
+    softmax_stats(pk, vocab, c, pm, pa, zp);
+    auto w = [&](uint32_t j) { return soft_exp2((pk[j] - pm) * c); };
+    out[count - 1] = inverse_cdf(vocab, w, uniform01(seed_lo, seed_hi, pos[count - 1] + 1, 0), pa);
+    return count;
+}
+
+// The chain drafter's draw for that rule: draft index from softmax(q / T) over the draft vocabulary by the same
+// inverse CDF, round 2 of the drafted token's position.
+inline uint32_t draw_draft_index(const float* q, uint32_t v, float temperature, uint32_t seed_lo, uint32_t seed_hi, uint32_t pos) {
+    const float c = LOG2E / temperature;
+    float qm, zq;
+    uint32_t qa;
+    softmax_stats(q, v, c, qm, qa, zq);
+    auto w = [&](uint32_t j) { return soft_exp2((q[j] - qm) * c); };
+    return inverse_cdf(v, w, uniform01(seed_lo, seed_hi, pos, 2), qa);
 }
 
 }  // namespace orc

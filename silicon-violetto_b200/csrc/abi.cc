@@ -135,9 +135,11 @@ static void fill_output(Engine& en, const StepOutput& r, VltStepOutput* out) {
         if (!out->hidden || r.hidden.size() > out->hidden_cap) throw Error("hidden buffer too small");
         std::memcpy(out->hidden, r.hidden.data(), r.hidden.size() * 4);
     }
+    out->n_taps = 0;
     if (!r.taps.empty()) {
         if (!out->taps || r.taps.size() > out->taps_cap) throw Error("taps buffer too small");
         std::memcpy(out->taps, r.taps.data(), r.taps.size() * 2);
+        out->n_taps = uint32_t(en.tap_layers.size());
     }
     out->gpu_seconds = r.gpu_seconds;
 }
@@ -157,7 +159,30 @@ int vlt_step(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOpt
     });
 }
 
-int vlt_set_taps(VltEngine* e, uint32_t on) { return guard([&] { eng(e).set_taps(on != 0); }); }
+int vlt_set_taps(VltEngine* e, const uint32_t* layers, uint32_t n_layers) {
+    return guard([&] { eng(e).set_taps(std::vector<uint32_t>(layers, layers + (layers ? n_layers : 0))); });
+}
+
+int vlt_step_capture(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOptions* opts, VltCaptureFn fn, void* user, VltStepOutput* out) {
+    return guard([&] {
+        Engine& en = eng(e);
+        no_step_in_flight(e);
+        if (!fn) throw Error("vlt_step_capture: no callback");
+        std::vector<PlanRun> rs;
+        for (uint32_t i = 0; i < n_runs; i++) {
+            for (uint32_t j = 0; j < runs[i].n_tokens; j++)
+                if (runs[i].tokens[j] >= en.model.md.vocab) throw Error("token id out of range");  // engine.rs:346-348
+            rs.push_back(PlanRun{runs[i].seq, runs[i].tokens, runs[i].n_tokens, Rows(opts->head), false});
+        }
+        StepOptions o{Rows(opts->head), Rows(opts->hidden), opts->read_logits != 0, opts->read_taps != 0};
+        const ModelDesc& md = en.model.md;
+        fill_output(en, en.step_capture(rs, o, [&](const LayerCapture& c) {
+            const VltLayerCapture v{c.layer, c.n, md.d, md.qkv_w(), md.n_heads * md.hd, c.resid_in, c.attn_in, c.qkv, c.sdpa_out, c.attn_out, c.mlp_in, c.mlp_out, nullptr};
+            fn(&v, user);
+        }), out);
+    });
+}
+int vlt_set_acceptance(VltEngine* e, uint32_t rule) { return guard([&] { eng(e).set_acceptance(rule); }); }
 int vlt_load_drafter(VltEngine* e, const char* path) { return guard([&] { eng(e).load_drafter(path); }); }
 int vlt_has_drafter(VltEngine* e) { return e && e->e && e->e->has_drafter() ? 1 : 0; }
 
@@ -314,6 +339,14 @@ int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, con
 }
 
 void vlt_debug_set_draft_rows(VltEngine* e, uint32_t rows) { if (e && e->e) e->e->debug_draft_rows = rows; }
+
+int vlt_debug_force_logits(VltEngine* e, const float* logits, uint64_t n_logits, const float* draft_logits, uint64_t n_draft) {
+    return guard([&] {
+        Engine& en = eng(e);
+        en.forced_logits.assign(logits, logits + (logits ? n_logits : 0));
+        en.forced_draft_logits.assign(draft_logits, draft_logits + (draft_logits ? n_draft : 0));
+    });
+}
 
 int vlt_debug_mark(VltEngine* e, uint32_t which) { return guard([&] { eng(e).mark(int(which)); }); }
 int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms) { return guard([&] { *ms = eng(e).mark_elapsed_ms(); }); }

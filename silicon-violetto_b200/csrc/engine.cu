@@ -138,7 +138,6 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
         f(s.hfin_head, hr * md.d);
         f(s.hfin_all, n * md.d);
         f(s.logits, hr * md.vocab);
-        f(s.taps, n * md.d);
         f(s.inv, n);
         const size_t n16 = (n + 15) / 16 * 16, hr16 = (hr + 15) / 16 * 16;
         s.h_b.alloc(n16 * md.d * 2, false);
@@ -217,6 +216,7 @@ uint32_t Engine::new_seq() {
             const uint32_t zero = 0;
             s.lens.write(slot * 4, &zero, 4);
             s.trace_len.write(slot * 4, &zero, 4);
+            if (drafter && !cfg.host_only) drafter->q_rows.write(slot * 4, &zero, 4);
             set_gen(slot, gen_open());
             return slot;
         }
@@ -252,7 +252,36 @@ void Engine::free_seq(uint32_t id) {
 
 uint32_t Engine::seq_len(uint32_t id) const { return id < seqs.size() && seqs[id] ? seqs[id]->len : 0; }
 
-void Engine::set_taps(bool on) { taps_on = on; }
+void Engine::set_taps(const std::vector<uint32_t>& layers) {
+    std::vector<uint32_t> want = layers;
+    const uint32_t last = model.md.n_layers - 1;
+    // The chain drafter's features are the last layer's tap: it stays tapped while a drafter is loaded.
+    if (drafter && std::find(want.begin(), want.end(), last) == want.end()) want.push_back(last);
+    for (size_t i = 0; i < want.size(); i++) {
+        if (want[i] >= model.md.n_layers) throw Error("taps: layer " + std::to_string(want[i]) + " of " + std::to_string(model.md.n_layers));
+        if (std::find(want.begin(), want.begin() + i, want[i]) != want.begin() + i) throw Error("taps: layer " + std::to_string(want[i]) + " named twice");
+    }
+    if (!cfg.host_only) VLT_CUDA(cudaStreamSynchronize(stream));  // no queued step writes the buffers that go away
+    std::vector<Buffer> bufs(want.size());
+    for (size_t i = 0; i < want.size(); i++) {
+        auto old = std::find(tap_layers.begin(), tap_layers.end(), want[i]);
+        if (old != tap_layers.end()) bufs[i] = std::move(tap_bufs[old - tap_layers.begin()]);
+        else bufs[i].alloc(size_t(cfg.max_step_tokens) * model.md.d * 4, cfg.host_only);
+    }
+    tap_layers = std::move(want);
+    tap_bufs = std::move(bufs);
+}
+
+float* Engine::last_tap() const {
+    auto it = std::find(tap_layers.begin(), tap_layers.end(), model.md.n_layers - 1);
+    if (it == tap_layers.end()) throw Error("internal: the last layer is not tapped");
+    return tap_bufs[it - tap_layers.begin()].as<float>();
+}
+
+void Engine::set_acceptance(uint32_t rule) {
+    if (rule > 1) throw Error("acceptance rule " + std::to_string(rule) + ": 0 (sample, then match) or 1 (rejection sampling)");
+    accept_rule = rule;
+}
 
 KvArgs Engine::kv_args() const {
     uint32_t shift = 0;
@@ -445,7 +474,7 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
 }
 
 // engine/src/engine/encode.rs:142-192 `encode_layer`, a plain decoder's.
-void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
+void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li, bool capture) {
     StepSet& st = sets[set];
     LayerIO io{};
     io.l = &model.layers[li];
@@ -463,11 +492,18 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li) {
     io.keys_per_split = p.keys_per_split;
     io.max_splits = p.max_splits;
     io.max_rows = std::min(p.max_run, VERIFY_T);
-    encode_layer_io(io);
+    encode_layer_io(io, capture);
+    // kernels.metal:133-148 `tap_rows`: bf16(rms_norm(the layer's output)), kept as fp32.
+    auto tap = std::find(tap_layers.begin(), tap_layers.end(), li);
+    if (tap != tap_layers.end())
+        launch_prep_rows(s.h.as<float>(), nullptr, p.n, model.md.d, model.md.eps, tap_bufs[tap - tap_layers.begin()].as<float>(), nullptr, nullptr, true, true, stream);
 }
 
 // The layer on any step layout, weights and cache: the target's layers and the drafter's one.
-void Engine::encode_layer_io(const LayerIO& io) {
+// With `capture`, the layer also leaves the intermediates step_capture hands out: the normed inputs by row passes, q | k | v
+// by a second qkv projection with the plain norm epilogue and a RoPE pass, the o and down projections' own outputs by
+// second launches with the raw epilogue (the same kernels on the same inputs: the same sums), all beside the normal work.
+void Engine::encode_layer_io(const LayerIO& io, bool capture) {
     const Layer& l = *io.l;
     const ModelDesc& md = model.md;
     const uint32_t n = io.n, li = io.layer;
@@ -494,6 +530,10 @@ void Engine::encode_layer_io(const LayerIO& io) {
     q.q_b = s.q_b.as<uint16_t>();
     q.k_cache = io.k_cache;
     q.v_cache = io.v_cache;
+    if (capture) {
+        VLT_CUDA(cudaMemcpyAsync(cap->resid_in.dev, h, size_t(n) * md.d * 4, cudaMemcpyDeviceToDevice, stream));
+        launch_prep_rows(h, nullptr, n, md.d, md.eps, cap->attn_in.as<float>(), nullptr, nullptr, true, false, stream);
+    }
     int sp = span_begin(G_MATMUL);
     if (!(skip & 1)) {
         if (big) {
@@ -504,11 +544,14 @@ void Engine::encode_layer_io(const LayerIO& io) {
             const float* ssq_in = carried ? s.ssq.as<float>() : nullptr;
             if (fused_post) matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), nullptr, nullptr, EPI_QKV, nullptr, inv_in, 0, &q, nullptr, ssq_in);
             else matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, inv_in, 0, nullptr, nullptr, ssq_in);
+            if (capture && fused_post) matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, inv_in, 0, nullptr, nullptr, ssq_in);
         } else if (fused_post) {
             matmul(l.qkv, n, h, nullptr, EPI_QKV, nullptr, s.inv.as<float>(), 0, &q);
+            if (capture) matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
         } else {
             matmul(l.qkv, n, h, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>());
         }
+        if (capture) launch_qkv_capture(s.qkv.as<float>(), io.meta, rope_tab.as<float>(), n, md.n_heads, kva, cap->qkv.as<float>(), stream);
     }
     span_end(sp);
     sp = span_begin(G_SMALL);
@@ -558,17 +601,24 @@ void Engine::encode_layer_io(const LayerIO& io) {
         const bool carry = md.d % 128 == 0;
         float* ssq = carry ? s.ssq.as<float>() : nullptr;
         uint16_t* hb = carry ? s.h_b.as<uint16_t>() : nullptr;
+        if (capture) matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), cap->attn_out.as<float>(), nullptr, EPI_RAW, nullptr, nullptr);
         if (!(skip & 16)) matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), h, hb, EPI_RESID, h, nullptr, 0, nullptr, ssq);
+        if (capture) launch_prep_rows(h, nullptr, n, md.d, md.eps, cap->mlp_in.as<float>(), nullptr, nullptr, true, false, stream);
         if (!(skip & 32)) {
             if (!carry) launch_prep_rows(h, nullptr, n, md.d, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
             matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, carry ? nullptr : s.inv.as<float>(), 0, nullptr,
                         nullptr, ssq);  // the down GEMM reads the bf16 copy only
         }
+        if (capture) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), cap->mlp_out.as<float>(), nullptr, EPI_RAW, nullptr, nullptr);
         if (!(skip & 64)) matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), h, hb, EPI_RESID, h, nullptr, 0, nullptr, ssq);
     } else {
         // o and down fold no RMSNorm: they take the bf16 copies their producers leave (a bulk copy instead of a conversion pass).
-        if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr, 0, nullptr, tuning.plain_attention ? nullptr : s.attn_b.as<uint16_t>());  // (the scalar attention leaves fp32 only)
+        const uint16_t* attn_b = tuning.plain_attention ? nullptr : s.attn_b.as<uint16_t>();  // (the scalar attention leaves fp32 only)
+        if (capture) matmul(l.o, n, s.attn.as<float>(), cap->attn_out.as<float>(), EPI_RAW, nullptr, nullptr, 0, nullptr, attn_b);
+        if (!(skip & 16)) matmul(l.o, n, s.attn.as<float>(), h, EPI_RESID, h, nullptr, 0, nullptr, attn_b);
+        if (capture) launch_prep_rows(h, nullptr, n, md.d, md.eps, cap->mlp_in.as<float>(), nullptr, nullptr, true, false, stream);
         if (!(skip & 32)) matmul(l.gate_up, n, h, s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr, 0, nullptr, nullptr, s.act_b.as<uint16_t>());
+        if (capture) matmul(l.down, n, s.act.as<float>(), cap->mlp_out.as<float>(), EPI_RAW, nullptr, nullptr, 0, nullptr, s.act_b.as<uint16_t>());
         if (!(skip & 64)) matmul(l.down, n, s.act.as<float>(), h, EPI_RESID, h, nullptr, 0, nullptr, s.act_b.as<uint16_t>());
     }
     span_end(sp);
@@ -585,7 +635,8 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
     StepSet& st = sets[set];
     const ModelDesc& md = model.md;
     const float* h = s.h.as<float>();
-    if (taps_on) launch_prep_rows(h, nullptr, p.n, md.d, md.eps, s.taps.as<float>(), nullptr, nullptr, true, true, stream);
+    bool spec = false;
+    SpecStepArgs sa{};
     if (p.n_hidden) launch_prep_rows(h, st.in<uint32_t>(st.o_hidden_rows), p.n_hidden, md.d, md.eps, s.hfin_all.as<float>(), nullptr, nullptr, true, false, stream);
     if (p.n_head && !(skip & 256)) {
         if (use_gemm(model.head, p.n_head)) {
@@ -595,11 +646,43 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
             launch_prep_rows(h, st.in<uint32_t>(st.o_head_rows), p.n_head, md.d, md.eps, s.hfin_head.as<float>(), nullptr, nullptr, false, false, stream);
             matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD, nullptr, nullptr);
         }
-        encode_sample(set, p.n_head);
+        // Under the rejection rule the runs whose drafts came with their q rows are decided by k_spec.cu's kernels: row
+        // statistics first (they also tell the sampler which rows to leave alone), the sampler for the other rows, then
+        // the decisions; accept commits either kind of run.
+        if (!forced_logits.empty()) {
+            if (forced_logits.size() != size_t(p.n_head) * md.vocab) throw Error("forced logits: " + std::to_string(forced_logits.size()) + " values for " + std::to_string(p.n_head) + " head rows");
+            VLT_CUDA(cudaMemcpyAsync(s.logits.dev, forced_logits.data(), forced_logits.size() * 4, cudaMemcpyHostToDevice, stream));
+        }
+        spec = accept_rule == 1 && drafter;
+        if (spec) {
+            Drafter& dr = *drafter;
+            sa.runs = st.in<RunIn>(st.o_runs);
+            sa.n_runs = p.n_runs;
+            sa.n_head = p.n_head;
+            sa.max_head_rows = cfg.max_head_rows;
+            sa.samples = st.in<SampleRow>(st.o_sample_rows);
+            sa.tokens = st.in<uint32_t>(st.o_tokens);
+            sa.meta = s.meta.as<uint32_t>();
+            sa.tree = s.tree.as<uint32_t>();
+            sa.logits = s.logits.as<float>();
+            sa.vocab = md.vocab;
+            sa.q_keep = dr.q_keep.as<float>();
+            sa.v = dr.v;
+            sa.q_rows = dr.q_rows.as<uint32_t>();
+            sa.index_of = dr.index_of.as<uint32_t>();
+            sa.stats = dr.spec_stats.as<SpecRowStats>();
+            sa.row_skip = dr.row_skip.as<uint32_t>();
+            sa.spec_e = dr.spec_e.as<uint32_t>();
+            sa.out = st.out<uint32_t>(st.o_out_ids);
+            launch_spec_step_stats(sa, stream);
+        }
+        launch_sample(s.logits.as<float>(), st.in<SampleRow>(st.o_sample_rows), st.out<uint32_t>(st.o_out_ids), s.meta.as<uint32_t>(), p.n_head, md.vocab, stream,
+                      spec ? sa.row_skip : nullptr);
+        if (spec) launch_spec_step_decide(sa, stream);
     }
     launch_accept(st.in<RunIn>(st.o_runs), st.in<uint32_t>(st.o_tokens), st.out<uint32_t>(st.o_out_ids), s.lens.as<uint32_t>(), s.feed.as<uint32_t>(),
                   s.gen.as<GenState>(), st.out<uint32_t>(st.o_emitted), p.n_runs, s.tree.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(),
-                  s.on_path.as<uint32_t>(), stream);
+                  s.on_path.as<uint32_t>(), stream, spec ? sa.spec_e : nullptr);
     if (p.branches)
         launch_kv_compact(st.in<RunIn>(st.o_runs), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.lens.as<uint32_t>(), kv.k.as<uint16_t>(),
                           kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kv_args(), p.n_runs, md.n_layers, stream);
@@ -607,6 +690,14 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
 
 // engine/src/engine/encode.rs:99-105 `encode_forward`, after the step set's upload.
 void Engine::encode_forward(uint32_t set, const Plan& p) {
+    begin_step(set, p);
+    for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
+    const int sp = span_begin(G_TAIL);
+    encode_tail(set, p);
+    span_end(sp);
+}
+
+void Engine::begin_step(uint32_t set, const Plan& p) {
     if (cfg.host_only) throw Error("this engine was created host-only: it plans steps but cannot run them (no CPU path)");
     StepSet& st = sets[set];
     // The set's device copy is free: the step that used it last has been collected (three sets, at most two steps queued).
@@ -616,10 +707,6 @@ void Engine::encode_forward(uint32_t set, const Plan& p) {
     VLT_CUDA(cudaStreamWaitEvent(stream, st.uploaded, 0));
     launch_embed(model.embed, st.in<uint32_t>(st.o_tokens), s.h.as<float>(), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.lens.as<uint32_t>(),
                  s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), st.in<uint32_t>(st.o_vis), p.n, model.md.d, model.md.vocab, stream);
-    for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
-    const int sp = span_begin(G_TAIL);
-    encode_tail(set, p);
-    span_end(sp);
 }
 
 // engine/src/engine/encode.rs:439-451 `encode_replay`.
@@ -716,12 +803,22 @@ void Engine::load_drafter(const std::string& path) {
     dr->hfin.alloc(ms * d * 4, false);
     dr->hfin_b.alloc(ms16 * d * 2, false);
     dr->inv.alloc(ms * 4, false);
+    dr->q_keep.alloc(ms * (VERIFY_T - 1) * size_t(v) * 4, false);
+    dr->q_rows.alloc(ms * 4, false);
+    dr->q_rows.order = stream;
+    std::vector<uint32_t> inverse(md.vocab, NO_TOK);
+    for (uint32_t i = 0; i < v; i++) inverse[ids[i]] = i;
+    dr->index_of.alloc(size_t(md.vocab) * 4, false);
+    dr->index_of.write(0, inverse.data(), size_t(md.vocab) * 4);
+    dr->spec_stats.alloc((size_t(cfg.max_head_rows) + ms * (VERIFY_T - 1)) * sizeof(SpecRowStats), false);
+    dr->row_skip.alloc(size_t(cfg.max_head_rows) * 4, false);
+    dr->spec_e.alloc(ms * 4, false);
     std::vector<uint32_t> tiles(2 * ms);
     for (uint32_t r = 0; r < ms; r++) { tiles[2 * r] = r; tiles[2 * r + 1] = 1; }
     dr->dtiles.alloc(ms * 8, false);
     dr->dtiles.write(0, tiles.data(), ms * 8);
     drafter = std::move(dr);
-    taps_on = true;  // the drafter reads the target's tapped hidden states
+    set_taps(tap_layers);  // the drafter reads the last layer's tapped hidden states: it is tapped from now on
 }
 bool Engine::has_drafter() const { return drafter != nullptr; }
 
@@ -751,7 +848,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.v_cache = dr.v_cache.as<uint16_t>();
     io.maps = &dr.maps;
     // (1) catch-up, on the step's own layout.
-    launch_draft_catchup_in(st.in<uint32_t>(st.o_tokens), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), s.taps.as<float>(),
+    launch_draft_catchup_in(st.in<uint32_t>(st.o_tokens), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), last_tap(),
                             dr.carry.as<float>(), model.embed, n, d, x, xb, dr.cpos.as<uint32_t>(), stream);
     fc(n);
     io.n = n;
@@ -781,7 +878,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.max_rows = 1;
     for (uint32_t i = 1; i < rows; i++) {
         launch_draft_pass_in(runs, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(),
-                             st.out<uint32_t>(st.o_emitted), s.taps.as<float>(), dr.dfeat.as<float>(), model.embed, nr, d, md.vocab, i, cfg.max_seq_len, x, xb,
+                             st.out<uint32_t>(st.o_emitted), last_tap(), dr.dfeat.as<float>(), model.embed, nr, d, md.vocab, i, cfg.max_seq_len, x, xb,
                              dr.dmeta.as<uint32_t>(), dr.dtin.as<uint32_t>(), dr.dvis.as<uint32_t>(), dr.dcpos.as<uint32_t>(), dr.live.as<uint32_t>(), stream);
         fc(nr);
         encode_layer_io(io);
@@ -795,9 +892,14 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
             launch_prep_rows(h, nullptr, nr, d, md.eps, dr.hfin.as<float>(), nullptr, nullptr, false, false, stream);
             matmul(dr.head, nr, dr.hfin.as<float>(), lg, EPI_HEAD, nullptr, nullptr, dr.v);
         }
-        launch_draft_pick(lg, dr.v, dr.vocab_ids.as<uint32_t>(), runs, dr.live.as<uint32_t>(), nr, i, s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), stream);
+        if (!forced_draft_logits.empty()) {
+            if (forced_draft_logits.size() != size_t(rows - 1) * nr * dr.v) throw Error("forced draft logits: wrong size");
+            VLT_CUDA(cudaMemcpyAsync(lg, forced_draft_logits.data() + size_t(i - 1) * nr * dr.v, size_t(nr) * dr.v * 4, cudaMemcpyHostToDevice, stream));
+        }
+        launch_draft_draw(lg, dr.v, dr.vocab_ids.as<uint32_t>(), runs, st.in<SampleRow>(st.o_sample_rows), dr.live.as<uint32_t>(), s.lens.as<uint32_t>(), nr, i, accept_rule,
+                          s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), dr.q_keep.as<float>(), dr.q_rows.as<uint32_t>(), stream);
     }
-    launch_draft_carry(runs, s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(), s.taps.as<float>(), nr, d, dr.carry.as<float>(), stream);
+    launch_draft_carry(runs, s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(), last_tap(), nr, d, dr.carry.as<float>(), stream);
     span_end(sp);
 }
 
@@ -807,19 +909,57 @@ StepOutput Engine::step_runs(const std::vector<PlanRun>& runs, const StepOptions
     if (debug_draft_rows && drafter) encode_drafter(0, p, debug_draft_rows);
     if (replay) encode_replay(0, p, *replay);
     commit(0);
-    StepOutput out;
-    out.gpu_seconds = wait(0);
+    const double secs = wait(0);
+    forced_logits.clear();
+    forced_draft_logits.clear();
     check_device_error(0);
+    return read_output(p, opts, secs);
+}
+
+// engine/src/engine.rs:357-371 `read_output`.
+StepOutput Engine::read_output(const Plan& p, const StepOptions& opts, double gpu_seconds) {
+    StepOutput out;
+    out.gpu_seconds = gpu_seconds;
     const StepSet& st = sets[0];
     out.ids.assign(st.hout<uint32_t>(st.o_out_ids), st.hout<uint32_t>(st.o_out_ids) + p.n_head);
     if (opts.read_logits) out.logits = s.logits.read_vec<float>(0, size_t(p.n_head) * model.md.vocab);
     out.hidden = s.hfin_all.read_vec<float>(0, size_t(p.n_hidden) * model.md.d);
-    if (opts.read_taps && taps_on) {
-        std::vector<float> tf = s.taps.read_vec<float>(0, size_t(p.n) * model.md.d);
-        out.taps.resize(tf.size());
-        for (size_t i = 0; i < tf.size(); i++) { uint32_t u; std::memcpy(&u, &tf[i], 4); out.taps[i] = uint16_t(u >> 16); }  // bf16 values held as f32
+    if (opts.read_taps) {
+        for (const Buffer& b : tap_bufs) {
+            const std::vector<float> tf = b.read_vec<float>(0, size_t(p.n) * model.md.d);
+            for (float v : tf) { uint32_t u; std::memcpy(&u, &v, 4); out.taps.push_back(uint16_t(u >> 16)); }  // bf16 values held as f32
+        }
     }
     return out;
+}
+
+// engine/src/engine.rs:318-355 `step_capture`.
+StepOutput Engine::step_capture(const std::vector<PlanRun>& runs, const StepOptions& opts, const std::function<void(const LayerCapture&)>& f) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it plans steps but cannot run them (no CPU path)");
+    const ModelDesc& md = model.md;
+    if (!cap) {
+        cap = std::make_unique<CaptureBufs>();
+        const size_t n = cfg.max_step_tokens;
+        for (Buffer* b : {&cap->resid_in, &cap->attn_in, &cap->attn_out, &cap->mlp_in, &cap->mlp_out}) b->alloc(n * md.d * 4, false);
+        cap->qkv.alloc(n * md.qkv_w() * 4, false);
+    }
+    Plan p = plan(0, runs, opts.hidden);
+    begin_step(0, p);
+    const size_t n = p.n;
+    for (uint32_t li = 0; li < md.n_layers; li++) {
+        encode_layer(0, p, li, true);
+        VLT_CUDA(cudaStreamSynchronize(stream));
+        const std::vector<float> resid_in = cap->resid_in.read_vec<float>(0, n * md.d), attn_in = cap->attn_in.read_vec<float>(0, n * md.d),
+                                 qkv = cap->qkv.read_vec<float>(0, n * md.qkv_w()), sdpa = s.attn.read_vec<float>(0, n * md.n_heads * md.hd),
+                                 attn_out = cap->attn_out.read_vec<float>(0, n * md.d), mlp_in = cap->mlp_in.read_vec<float>(0, n * md.d),
+                                 mlp_out = cap->mlp_out.read_vec<float>(0, n * md.d);
+        f(LayerCapture{li, p.n, resid_in.data(), attn_in.data(), qkv.data(), sdpa.data(), attn_out.data(), mlp_in.data(), mlp_out.data()});
+    }
+    encode_tail(0, p);
+    commit(0);
+    const double secs = wait(0);
+    check_device_error(0);
+    return read_output(p, opts, secs);
 }
 
 // engine/src/engine/hooks.rs:28-36 `bench_fill`.
@@ -1057,6 +1197,8 @@ std::vector<uint32_t> Engine::debug_read(const std::string& name) {
         const size_t pool = size_t(kv.n_pages) * model.md.n_kv * kv.page * model.md.hd;
         if (name == "draft_logits") return whole(drafter->logits, size_t(VERIFY_T - 1) * ms * drafter->v);  // [pass][run slot][v] f32
         if (name == "carry") return whole(drafter->carry, ms * model.md.d);
+        if (name == "q_rows") return whole(drafter->q_rows, ms);
+        if (name == "q_keep") return whole(drafter->q_keep, ms * (VERIFY_T - 1) * size_t(drafter->v));
         if (name == "draft_k_cache") return whole(drafter->k, pool / 2);  // bf16 pairs
         if (name == "draft_v_cache") return whole(drafter->v_cache, pool / 2);
     }

@@ -2,6 +2,7 @@
 // Mirrors the reference's `Engine` (engine/src/engine.rs) with CUDA underneath.
 #pragma once
 #include <array>
+#include <functional>
 #include <memory>
 #include <optional>
 #include <string>
@@ -98,8 +99,18 @@ struct StepOptions {
 struct StepOutput {
     std::vector<uint32_t> ids;
     std::vector<float> logits, hidden;
-    std::vector<uint16_t> taps;
+    std::vector<uint16_t> taps;  // [tap][token][d]
     double gpu_seconds = 0;
+};
+
+// engine/src/engine.rs:175-188 `LayerCapture`: one layer's intermediates over a step, n rows each (host memory, valid
+// during the callback). For the plain decoder: resid_in the residual stream entering the layer; attn_in its RMS-normed
+// rows; qkv = q | k | v after the folded norm and RoPE (fp32, before the rounding to bf16 and q's softmax scale);
+// sdpa_out the attention's output; attn_out the o projection's output before the residual add; mlp_in the RMS-normed
+// residual stream after attention; mlp_out the down projection's output before the residual add.
+struct LayerCapture {
+    uint32_t layer, n;
+    const float *resid_in, *attn_in, *qkv, *sdpa_out, *attn_out, *mlp_in, *mlp_out;
 };
 
 class Engine {
@@ -123,7 +134,17 @@ class Engine {
     bool has_drafter() const;
     void encode_drafter(uint32_t set, const Plan& p, uint32_t rows);  // after encode_forward: catch-up, then rows - 1 draft passes
     uint32_t debug_draft_rows = 0;  // step_runs runs the drafter for this many rows (tests)
-    void set_taps(bool on);
+    // Tests of the integer tail on identical inputs: the next step_runs replaces the head's logits ([head rows][vocab]) and
+    // the drafter's per-pass logits ([pass][run][v]) by these before anything reads them. Cleared after that step.
+    std::vector<float> forced_logits, forced_draft_logits;
+    // engine/src/engine.rs:381-389: taps these layers' outputs (bf16(rms_norm(output)), kernels.metal:133-148) from the next step on.
+    void set_taps(const std::vector<uint32_t>& layers);
+    // engine/src/engine.rs:318-355: a step that stops after every layer and hands its intermediates to `f`.
+    StepOutput step_capture(const std::vector<PlanRun>& runs, const StepOptions& opts, const std::function<void(const LayerCapture&)>& f);
+    // 0: the reference's acceptance (every row draws the target's token, a draft is accepted if it equals its parent
+    // row's draw); 1: rejection sampling for verify runs whose drafts the chain drafter drew from its own distribution.
+    void set_acceptance(uint32_t rule);
+    uint32_t accept_rule = 0;
     void bench_fill(uint32_t id, uint32_t len, uint32_t seed);
     std::vector<uint32_t> sample_logits(const float* logits, const std::vector<std::pair<Sampling, uint32_t>>& rows);
     // Rejection-sampling acceptance on caller-supplied logits (host pointers); out: 3 x streams words
@@ -165,7 +186,8 @@ class Engine {
     std::vector<std::optional<Seq>> seqs;
     std::array<StepSet, 3> sets;  // three rotate, so the CPU prepares step t+1 while the GPU runs step t
     uint32_t skip = 0;
-    bool taps_on = false;
+    std::vector<uint32_t> tap_layers;
+    std::vector<Buffer> tap_bufs;  // [max_step_tokens][d] fp32 holding bf16 values, one per tapped layer
     cudaStream_t stream = nullptr;
     // A step's inputs go up and its results come down on streams of their own, so that neither copy sits between the
     // last kernel of one step and the first of the next (the next step is queued while this one runs).
@@ -173,7 +195,7 @@ class Engine {
 
     // Activations (engine/src/engine/buffers.rs:14-118) and per-slot state on the GPU.
     struct Scratch {
-        Buffer h, qkv, attn, act, part, hfin_head, hfin_all, logits, taps, inv, meta;
+        Buffer h, qkv, attn, act, part, hfin_head, hfin_all, logits, inv, meta;
         Buffer h_b, attn_b, act_b, hfin_b, inv_head, q_b, ssq;  // ssq: [d / 128][n] sums of squares of h per 128-row tile (see MatArgs)  // bf16 copies that feed the tensor-core GEMM, rows padded to 16
         Buffer lens, feed, tree, gen, path, path_len, on_path, trace, trace_len, err_flag;
     } s;
@@ -189,6 +211,9 @@ class Engine {
         Layer layer;
         uint32_t v = 0;
         Buffer vocab_ids, k, v_cache, carry, dfeat, dmeta, dtin, dvis, dcpos, dtiles, live, cpos, logits, hfin, hfin_b, inv;
+        // The rejection-sampling rule's state: the q rows a slot's drafts were drawn from, how many are current, the
+        // draft vocabulary's inverse map, and the step's scratch (row statistics, sampler skips, settled candidates).
+        Buffer q_keep, q_rows, index_of, spec_stats, row_skip, spec_e;
         AttnMaps maps;
     };
     std::unique_ptr<Drafter> drafter;
@@ -212,8 +237,14 @@ class Engine {
         uint16_t *k_cache, *v_cache;
         const AttnMaps* maps;
     };
-    void encode_layer(uint32_t set, const Plan& p, uint32_t li);
-    void encode_layer_io(const LayerIO& io);
+    // Device buffers a capturing step fills beside its normal work (allocated by the first step_capture).
+    struct CaptureBufs { Buffer resid_in, attn_in, qkv, attn_out, mlp_in, mlp_out; };
+    std::unique_ptr<CaptureBufs> cap;
+    float* last_tap() const;  // the last layer's tap (the chain drafter's features)
+    void begin_step(uint32_t set, const Plan& p);  // upload, start event, embedding
+    void encode_layer(uint32_t set, const Plan& p, uint32_t li, bool capture = false);
+    void encode_layer_io(const LayerIO& io, bool capture = false);
+    StepOutput read_output(const Plan& p, const StepOptions& opts, double gpu_seconds);
     void encode_tail(uint32_t set, const Plan& p);
     void encode_sample(uint32_t set, uint32_t rows);
     void attention_split(Plan& p, uint32_t max_keys, uint32_t n_tiles) const;

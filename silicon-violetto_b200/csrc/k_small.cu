@@ -91,6 +91,29 @@ void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin
     launch_pdl(qkv_post_kernel, n, 32 * kv.n_kv, 0, s, qkv, meta, tin, rope, k_cache, v_cache, page_table, kv, layer, n_heads, scale_log2, reinterpret_cast<uint32_t*>(q_b), cpos);
 }
 
+// q | k | v of every token with RoPE applied to the q and k heads, in fp32 and unscaled: what engine.rs:183's `qkv`
+// capture holds ("after the norms, RoPE and value embeddings"). One block per token, a thread per pair of dims.
+__global__ void qkv_capture_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const float* __restrict__ rope, uint32_t n_heads, KvArgs kv,
+                                   float* out) {
+    const uint32_t t = blockIdx.x, pos = meta[2 * t + 1], half = kv.hd / 2, qw = (n_heads + 2 * kv.n_kv) * kv.hd;
+    for (uint32_t i = threadIdx.x; i < qw / 2; i += blockDim.x) {
+        const uint32_t head = i / half, pr = i % half;
+        const float2 x = reinterpret_cast<const float2*>(qkv + size_t(t) * qw)[i];
+        float2 y = x;
+        if (head < n_heads + kv.n_kv) {
+            const float2 cs = reinterpret_cast<const float2*>(rope)[size_t(pos) * half + pr];
+            y.x = __fadd_rn(__fmul_rn(cs.x, x.x), __fmul_rn(cs.y, x.y));
+            y.y = __fsub_rn(__fmul_rn(cs.x, x.y), __fmul_rn(cs.y, x.x));
+        }
+        reinterpret_cast<float2*>(out + size_t(t) * qw)[i] = y;
+    }
+}
+void launch_qkv_capture(const float* qkv, const uint32_t* meta, const float* rope, uint32_t n, uint32_t n_heads, KvArgs kv, float* out, cudaStream_t s) {
+    if (!n) return;
+    qkv_capture_kernel<<<n, 256, 0, s>>>(qkv, meta, rope, n_heads, kv, out);
+    launch_counter()++;
+}
+
 // ----------------------------------------------- scalar attention (cross-check)
 // One block of 128 threads per (token, head): every thread takes keys tid, tid + 128, ... of the
 // token's visible keys -- the cache below its tile's first position, then the tile's rows its
@@ -353,8 +376,9 @@ __device__ void tg_scan(float v, float* ex, float* base, uint32_t tid) {
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits, const SampleRow* __restrict__ rows, uint32_t* out,
-                                                                const uint32_t* __restrict__ meta, uint32_t vocab) {
+                                                                const uint32_t* __restrict__ meta, uint32_t vocab, const uint32_t* __restrict__ row_skip) {
     pdl_start();
+    if (row_skip && row_skip[blockIdx.x]) return;
     __shared__ float ex[SAMPLE_THREADS + SAMPLE_THREADS / 32 + 1];
     __shared__ float base[32];
     __shared__ float bvs[32];
@@ -526,8 +550,9 @@ __device__ void sc_scan(float v, uint32_t buf, ScExchange* xc, float* vals, floa
 // instead of waiting for L2 at every step.
 template <bool STAGED>
 __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sample_cluster_kernel(const float* __restrict__ logits, const SampleRow* __restrict__ rows,
-                                                                                                 uint32_t* out, const uint32_t* __restrict__ meta, uint32_t vocab) {
+                                                                                                 uint32_t* out, const uint32_t* __restrict__ meta, uint32_t vocab, const uint32_t* __restrict__ row_skip) {
     pdl_start();
+    if (row_skip && row_skip[blockIdx.x / SC_CTAS]) return;  // the whole cluster leaves: no cluster barrier has been entered
     __shared__ ScExchange xc;
     __shared__ float vals[SC_THREADS], pre[SC_THREADS], tot_all[32], base[33];
     __shared__ float wbv[SC_WARPS];
@@ -667,11 +692,12 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
     sc_cluster_sync();  // nobody leaves while another block may still read its shared memory
 }
 
-void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s) {
+void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s,
+                   const uint32_t* row_skip) {
     if (!n_rows) return;
     // Enough rows to fill the SMs with one block each: the single-block form (at 160 rows the two take the same time,
     // bound by instruction issue); fewer: a cluster of 8 blocks per row (one stream's 5 rows: 95 -> about 25 us).
-    if (n_rows > 96) { launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, s, logits, rows, out, meta, vocab); return; }
+    if (n_rows > 96) { launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, s, logits, rows, out, meta, vocab, row_skip); return; }
     // A block's share of a row in shared memory (512 bytes per 1024 ids), if it fits.
     const size_t stage = size_t((vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS) * SC_THREADS * 4;
     const bool staged = stage <= 200 * 1024;
@@ -687,8 +713,8 @@ void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (staged) VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<true>, logits, rows, out, meta, vocab));
-    else VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<false>, logits, rows, out, meta, vocab));
+    if (staged) VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<true>, logits, rows, out, meta, vocab, row_skip));
+    else VLT_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<false>, logits, rows, out, meta, vocab, row_skip));
     launch_counter()++;
 }
 
@@ -697,7 +723,7 @@ void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, co
 // One thread per run.
 __global__ void accept_kernel(const RunIn* __restrict__ runs, const uint32_t* __restrict__ tokens, uint32_t* out, uint32_t* lens, uint32_t* feed,
                               GenState* gen, uint32_t* emitted, uint32_t nruns, const uint32_t* __restrict__ tree, uint32_t* path,
-                              uint32_t* path_len, uint32_t* on_path) {
+                              uint32_t* path_len, uint32_t* on_path, const uint32_t* __restrict__ spec_e) {
     pdl_start();
     const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= nruns) return;
@@ -711,7 +737,13 @@ __global__ void accept_kernel(const RunIn* __restrict__ runs, const uint32_t* __
     uint32_t first = ru.head0 + ru.nhead - 1, e = 1;
     uint32_t walk[FEED_W];
     walk[0] = 0;
-    if (ru.verify) {
+    const uint32_t decided = ru.verify && spec_e ? min(spec_e[r], ru.count) : 0u;
+    if (decided) {
+        // The rejection-sampling rule settled this run's candidates (k_spec.cu): rows 0 .. decided - 1 are the path.
+        e = decided;
+        for (uint32_t j = 0; j < e; j++) walk[j] = j;
+        first = ru.head0;
+    } else if (ru.verify) {
         // Children come after their parents, so one pass over the rows finds the path.
         const uint32_t* node = tree + ru.slot * FEED_W;
         for (uint32_t c = 1, at = 0; c < ru.count; c++) {
@@ -742,8 +774,8 @@ __global__ void accept_kernel(const RunIn* __restrict__ runs, const uint32_t* __
 }
 
 void launch_accept(const RunIn* runs, const uint32_t* tokens, uint32_t* out, uint32_t* lens, uint32_t* feed, GenState* gen, uint32_t* emitted,
-                   uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s) {
-    if (n_runs) launch_pdl(accept_kernel, (n_runs + 63) / 64, 64, 0, s, runs, tokens, out, lens, feed, gen, emitted, n_runs, tree, path, path_len, on_path);
+                   uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s, const uint32_t* spec_e) {
+    if (n_runs) launch_pdl(accept_kernel, (n_runs + 63) / 64, 64, 0, s, runs, tokens, out, lens, feed, gen, emitted, n_runs, tree, path, path_len, on_path, spec_e);
 }
 
 // kernels.metal:1663-1693 `kv_compact`: the accepted path's K/V rows, on every layer, from

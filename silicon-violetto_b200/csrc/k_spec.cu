@@ -54,12 +54,8 @@ __device__ void tg_scan(float v, float* ex, float* base, uint32_t tid) {
     __syncthreads();
 }
 
-struct RowStats {
-    float max;
-    uint32_t argmax;
-    float z;
-    uint32_t pad;
-};
+using vlt::SpecRowStats;
+typedef SpecRowStats RowStats;
 
 __device__ __forceinline__ float e_of(uint16_t x, float mx, float c) { return soft_exp2(__fmul_rn(__fsub_rn(bf16_to_f32(x), mx), c)); }
 
@@ -192,6 +188,197 @@ void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* dr
     spec::decide_kernel<<<streams, spec::THREADS, 0, s>>>(p, q, drafts, static_cast<const spec::RowStats*>(stats), streams, k, vocab, c, seeds, pos0, accepted,
                                                           token, rollback);
     launch_counter()++;
+}
+
+// ------------------------------------------------ the rule inside the engine's step
+// A verify run whose drafts the chain drafter drew (from softmax(q / T), keeping the q rows) in the step before is
+// decided by the rule above instead of the reference's sample-then-match. What differs from the stand-alone form:
+// the target's rows are the step's fp32 logits over the whole vocabulary; a q row is fp32 over the draft vocabulary
+// (v ids, `index_of` maps a target id to its index or NO_TOK), its statistics taken in the sampler's order over
+// draft indices, Q being 0 for an id outside it (such a draft is rejected); the uniforms are keyed by the position
+// of the token they decide (round 0 the test, round 1 the replacement; the bonus token at the last row's position
+// + 1, round 0). The kernels leave the run's candidates -- the accepted drafts, then the drawn token -- in
+// out[head0 ..] and their number in spec_e[run]; `accept_kernel` then commits them exactly as it commits a walk
+// of the reference's rule (lens, feed, path, on_path, gen, emitted), so rejected rows are rolled back the same
+// way: the sequence advances by what was accepted and the K/V past it is overwritten by the next step.
+namespace spec {
+
+// Whether run r is decided by this rule: a verify run of a sequence that samples (temperature > 0, no top-p cut),
+// whose rows are a plain chain and whose drafts all came with a kept q row. Uniform over a block.
+__device__ bool step_applies(const SpecStepArgs& a, uint32_t r) {
+    const RunIn ru = a.runs[r];
+    if (!ru.verify || ru.count < 2 || ru.nhead != ru.count || ru.count > VERIFY_T) return false;
+    const SampleRow sr = a.samples[ru.head0];
+    if (!(sr.temperature > 0.0f) || sr.top_p < 1.0f) return false;
+    if (a.q_rows[ru.slot] + 1 < ru.count) return false;
+    for (uint32_t c = 1; c < ru.count; c++)
+        if (a.tree[ru.slot * FEED_W + c] != d_chain_node(c)) return false;
+    return true;
+}
+
+// One block per row: the step's head rows first, then VERIFY_T - 1 q rows per run. Rows of runs the rule does
+// not decide are left alone (and marked for the sampler: row_skip 0); the others get (max, argmax, Z).
+__global__ void __launch_bounds__(THREADS) step_stats_kernel(const SpecStepArgs a) {
+    pdl_start();
+    __shared__ float ex[THREADS + THREADS / 32 + 1];
+    __shared__ float base[32];
+    __shared__ float bvs[32];
+    __shared__ uint32_t bis[32];
+    const uint32_t b = blockIdx.x, tid = threadIdx.x, lane = tid % 32;
+    const float* x;
+    uint32_t n, r;
+    RowStats* out;
+    if (b < a.n_head) {
+        for (r = 0; r < a.n_runs; r++)
+            if (b >= a.runs[r].head0 && b < a.runs[r].head0 + a.runs[r].nhead) break;
+        const bool on = r < a.n_runs && step_applies(a, r);
+        if (tid == 0) a.row_skip[b] = on ? 1u : 0u;
+        if (!on) return;
+        x = a.logits + size_t(b) * a.vocab;
+        n = a.vocab;
+        out = a.stats + b;
+    } else {
+        r = (b - a.n_head) / (VERIFY_T - 1);
+        const uint32_t i = (b - a.n_head) % (VERIFY_T - 1) + 1;
+        if (!step_applies(a, r) || i >= a.runs[r].count) return;
+        x = a.q_keep + (size_t(a.runs[r].slot) * (VERIFY_T - 1) + i - 1) * a.v;
+        n = a.v;
+        out = a.stats + a.max_head_rows + r * (VERIFY_T - 1) + i - 1;
+    }
+    const float c = __fdiv_rn(LOG2E, a.samples[a.runs[r].head0].temperature);
+    float mx = -FLT_MAX;
+    uint32_t am = 0xffffffffu;
+    for (uint32_t i = tid; i < n; i += THREADS) better(mx, am, x[i], i);
+    warp_best(mx, am);
+    if (lane == 0) { bvs[tid / 32] = mx; bis[tid / 32] = am; }
+    __syncthreads();
+    mx = bvs[0];
+    am = bis[0];
+    for (uint32_t i = 1; i < 32; i++) better(mx, am, bvs[i], bis[i]);
+    float s = 0.0f;
+    for (uint32_t i = tid; i < n; i += THREADS) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(x[i], mx), c)));
+    tg_scan(s, ex, base, tid);
+    if (tid == 0) *out = RowStats{mx, am, ex[ex_at(THREADS)], 0};
+}
+
+// One block per run: the tests in order (one thread), then the replacement or the bonus token (the block).
+__global__ void __launch_bounds__(THREADS) step_decide_kernel(const SpecStepArgs a) {
+    pdl_start();
+    __shared__ float ex[THREADS + THREADS / 32 + 1];
+    __shared__ float base[32];
+    __shared__ uint32_t pick, first_reject;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x;
+    const RunIn ru = a.runs[r];
+    const bool on = step_applies(a, r);
+    __syncthreads();  // every thread has read q_rows
+    if (tid == 0) {
+        a.q_rows[ru.slot] = 0;  // a slot's kept rows serve one step
+        if (!on) a.spec_e[r] = 0;
+    }
+    if (!on) return;
+    const SampleRow sr = a.samples[ru.head0];
+    const float c = __fdiv_rn(LOG2E, sr.temperature);
+    const RowStats* ps = a.stats + ru.head0;
+    const RowStats* qs = a.stats + a.max_head_rows + r * (VERIFY_T - 1);
+    const float* pp = a.logits + size_t(ru.head0) * a.vocab;
+    const float* qq = a.q_keep + size_t(ru.slot) * (VERIFY_T - 1) * a.v;
+    auto e_of = [&](float x, float mx) { return soft_exp2(__fmul_rn(__fsub_rn(x, mx), c)); };
+    if (tid == 0) {
+        uint32_t i = 1;
+        for (; i < ru.count; i++) {
+            const uint32_t tok = a.tokens[ru.first + i], idx = tok < a.vocab ? a.index_of[tok] : NO_TOK;
+            if (idx == NO_TOK) break;
+            const float ep = e_of(pp[size_t(i - 1) * a.vocab + tok], ps[i - 1].max), eq = e_of(qq[size_t(i - 1) * a.v + idx], qs[i - 1].max);
+            const float u = uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 0);
+            const float lhs = __fmul_rn(__fmul_rn(u, eq), ps[i - 1].z), rhs = __fmul_rn(ep, qs[i - 1].z);
+            if (!(lhs < rhs)) break;
+        }
+        first_reject = i;
+    }
+    __syncthreads();
+    const uint32_t i = first_reject;
+    uint32_t tok;
+    if (i < ru.count) {
+        const float* pi = pp + size_t(i - 1) * a.vocab;
+        const float* qi = qq + size_t(i - 1) * a.v;
+        const float pm = ps[i - 1].max, qm = qs[i - 1].max, zp = ps[i - 1].z, zq = qs[i - 1].z;
+        const uint32_t* index_of = a.index_of;
+        auto resid = [&](uint32_t j) {
+            const uint32_t idx = index_of[j];
+            const float ea = __fmul_rn(e_of(pi[j], pm), zq), eb = idx == NO_TOK ? 0.0f : __fmul_rn(e_of(qi[idx], qm), zp);
+            const float d = __fsub_rn(ea, eb);
+            return d > 0.0f ? d : 0.0f;
+        };
+        tok = inverse_cdf(a.vocab, resid, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 1), ps[i - 1].argmax, ex, base, &pick, tid);
+    } else {
+        const float* pk = pp + size_t(ru.count - 1) * a.vocab;
+        const float pm = ps[ru.count - 1].max;
+        auto w = [&](uint32_t j) { return e_of(pk[j], pm); };
+        tok = inverse_cdf(a.vocab, w, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + ru.count - 1) + 1] + 1, 0), ps[ru.count - 1].argmax, ex, base, &pick, tid);
+    }
+    if (tid == 0) {
+        for (uint32_t j = 0; j + 1 < i; j++) a.out[ru.head0 + j] = a.tokens[ru.first + j + 1];
+        a.out[ru.head0 + i - 1] = tok;
+        a.spec_e[r] = i;
+    }
+}
+
+// The chain drafter's pick for pass i, one block per run: the draft vocabulary's argmax (ties to the lowest
+// index), or -- under the rule, for a sequence that samples -- a draw from softmax(q / T) by the sampler's
+// inverse CDF at round 2 of the drafted token's position, the row kept for the next step's test.
+__global__ void __launch_bounds__(THREADS) draft_draw_kernel(const float* __restrict__ logits, uint32_t v, const uint32_t* __restrict__ vocab_ids,
+                                                             const RunIn* __restrict__ runs, const SampleRow* __restrict__ samples,
+                                                             const uint32_t* __restrict__ live, const uint32_t* __restrict__ lens, uint32_t i, uint32_t rule,
+                                                             uint32_t* feed, uint32_t* tree, float* q_keep, uint32_t* q_rows) {
+    pdl_start();
+    __shared__ float ex[THREADS + THREADS / 32 + 1];
+    __shared__ float base[32];
+    __shared__ float bvs[32];
+    __shared__ uint32_t bis[32];
+    __shared__ uint32_t pick;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid % 32;
+    if (!live[r]) return;
+    const RunIn ru = runs[r];
+    const float* row = logits + size_t(r) * v;
+    float mx = -FLT_MAX;
+    uint32_t am = 0xffffffffu;
+    for (uint32_t j = tid; j < v; j += THREADS) better(mx, am, row[j], j);
+    warp_best(mx, am);
+    if (lane == 0) { bvs[tid / 32] = mx; bis[tid / 32] = am; }
+    __syncthreads();
+    mx = bvs[0];
+    am = bis[0];
+    for (uint32_t j = 1; j < 32; j++) better(mx, am, bvs[j], bis[j]);
+    const SampleRow sr = samples[ru.head0];
+    const bool draws = rule == 1 && sr.temperature > 0.0f && sr.top_p >= 1.0f;
+    uint32_t idx = am;
+    if (draws) {
+        const float c = __fdiv_rn(LOG2E, sr.temperature);
+        auto w = [&](uint32_t j) { return soft_exp2(__fmul_rn(__fsub_rn(row[j], mx), c)); };
+        idx = inverse_cdf(v, w, uniform01(sr.seed_lo, sr.seed_hi, lens[ru.slot] + i, 2), am, ex, base, &pick, tid);
+        float* keep = q_keep + (size_t(ru.slot) * (VERIFY_T - 1) + i - 1) * v;
+        for (uint32_t j = tid; j < v; j += THREADS) keep[j] = row[j];
+    }
+    if (tid == 0) {
+        feed[ru.slot * FEED_W + i] = vocab_ids[idx < v ? idx : 0];
+        tree[ru.slot * FEED_W + i] = d_chain_node(i);
+        if (draws) q_rows[ru.slot] = i;
+        else if (i == 1) q_rows[ru.slot] = 0;
+    }
+}
+
+}  // namespace spec
+
+void launch_spec_step_stats(const SpecStepArgs& a, cudaStream_t s) {
+    launch_pdl(spec::step_stats_kernel, a.n_head + a.n_runs * (VERIFY_T - 1), spec::THREADS, 0, s, a);
+}
+void launch_spec_step_decide(const SpecStepArgs& a, cudaStream_t s) {
+    launch_pdl(spec::step_decide_kernel, a.n_runs, spec::THREADS, 0, s, a);
+}
+void launch_draft_draw(const float* logits, uint32_t v, const uint32_t* vocab_ids, const RunIn* runs, const SampleRow* samples, const uint32_t* live,
+                       const uint32_t* lens, uint32_t n_runs, uint32_t i, uint32_t rule, uint32_t* feed, uint32_t* tree, float* q_keep, uint32_t* q_rows,
+                       cudaStream_t s) {
+    launch_pdl(spec::draft_draw_kernel, n_runs, spec::THREADS, 0, s, logits, v, vocab_ids, runs, samples, live, lens, i, rule, feed, tree, q_keep, q_rows);
 }
 
 // ------------------------------------------------ the same, with nothing allocated

@@ -58,6 +58,8 @@ void launch_embed(const uint16_t* table, uint32_t* tokens, float* out, const uin
                   const uint32_t* feed, const uint32_t* tree, uint32_t* vis, uint32_t n, uint32_t d, uint32_t vocab, cudaStream_t s);
 void launch_qkv_post(const float* qkv, const uint32_t* meta, const uint32_t* tin, const float* rope, uint16_t* k_cache, uint16_t* v_cache,
                      const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n, uint32_t n_heads, float scale_log2, uint16_t* q_b, const uint32_t* cpos, cudaStream_t s);
+// q | k | v rows as the attention sees them before rounding (RoPE on q and k, kernels.metal:727-736), for step_capture.
+void launch_qkv_capture(const float* qkv, const uint32_t* meta, const float* rope, uint32_t n, uint32_t n_heads, KvArgs kv, float* out, cudaStream_t s);
 void launch_attn_plain(const float* qkv, const uint32_t* meta, const uint32_t* tiles, const uint32_t* vis, const float* rope, const uint16_t* k_cache,
                        const uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t layer, uint32_t n_tiles, uint32_t n_heads,
                        float scale_log2, float* out, cudaStream_t s);
@@ -125,13 +127,49 @@ void launch_matmul_rows(const MatArgs& a, cudaStream_t s);                      
 void launch_prep_rows(const float* in, const uint32_t* rows, uint32_t n, uint32_t k, float eps, float* out_f32, uint16_t* out_bf16, float* inv,
                       bool normalize, bool round_out, cudaStream_t s);
 
-void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s);
+// row_skip (optional): rows marked 1 are left untouched (another rule decides them).
+void launch_sample(const float* logits, const SampleRow* rows, uint32_t* out, const uint32_t* meta, uint32_t n_rows, uint32_t vocab, cudaStream_t s,
+                   const uint32_t* row_skip = nullptr);
+// spec_e (optional): a run with spec_e[run] != 0 has that many candidates already settled in out[head0 ..], its path rows 0 .. spec_e - 1.
 void launch_accept(const RunIn* runs, const uint32_t* tokens, uint32_t* out, uint32_t* lens, uint32_t* feed, GenState* gen, uint32_t* emitted,
-                   uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s);
+                   uint32_t n_runs, const uint32_t* tree, uint32_t* path, uint32_t* path_len, uint32_t* on_path, cudaStream_t s, const uint32_t* spec_e = nullptr);
 void launch_kv_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_cache, uint16_t* v_cache,
                        const uint32_t* page_table, KvArgs kv, uint32_t n_runs, uint32_t n_layers, cudaStream_t s);
 void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed, const uint32_t* trace, const uint32_t* trace_len, ReplayArgs ra,
                          uint32_t n_runs, uint32_t* tree, cudaStream_t s);
+// A row of logits' statistics for the rejection-sampling rule: maximum, argmax (ties to the lowest id), and the sum
+// of 2^((x - max) log2(e) / T) in the sampler's order.
+struct SpecRowStats {
+    float max;
+    uint32_t argmax;
+    float z;
+    uint32_t pad;
+};
+// The rule inside the engine's step (k_spec.cu), device pointers throughout.
+struct SpecStepArgs {
+    const RunIn* runs;
+    uint32_t n_runs, n_head, max_head_rows;
+    const SampleRow* samples;  // per head row
+    const uint32_t* tokens;    // the step's tokens, resolved
+    const uint32_t* meta;      // (slot, position) per token
+    const uint32_t* tree;      // [slot][FEED_W]
+    const float* logits;       // [head row][vocab]
+    uint32_t vocab;
+    const float* q_keep;       // [slot][VERIFY_T - 1][v]: the rows the slot's drafts were drawn from
+    uint32_t v;
+    uint32_t* q_rows;          // [slot]: how many of them are current
+    const uint32_t* index_of;  // [vocab]: a target id's index in the draft vocabulary, or NO_TOK
+    SpecRowStats* stats;       // [max_head_rows + max_seqs (VERIFY_T - 1)]
+    uint32_t* row_skip;        // [head row]: 1 if the sampler is to leave the row to this rule
+    uint32_t* spec_e;          // [run]: the candidates this rule settled (0: the run is not its)
+    uint32_t* out;             // out_ids
+};
+void launch_spec_step_stats(const SpecStepArgs& a, cudaStream_t s);
+void launch_spec_step_decide(const SpecStepArgs& a, cudaStream_t s);
+// The chain drafter's pick of pass i: argmax, or (rule 1, a sampling sequence) a draw from softmax(q / T) with the row kept.
+void launch_draft_draw(const float* logits, uint32_t v, const uint32_t* vocab_ids, const RunIn* runs, const SampleRow* samples, const uint32_t* live,
+                       const uint32_t* lens, uint32_t n_runs, uint32_t i, uint32_t rule, uint32_t* feed, uint32_t* tree, float* q_keep, uint32_t* q_rows,
+                       cudaStream_t s);
 // Rejection-sampling acceptance over bf16 draft and target logits on the device (k_spec.cu).
 void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab, float temperature,
                         const uint64_t* seeds, const uint32_t* pos0, void* stats, uint32_t* accepted, uint32_t* token, uint32_t* rollback, cudaStream_t s);

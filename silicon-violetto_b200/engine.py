@@ -57,7 +57,15 @@ class _StepOptions(C.Structure):
 class _StepOutput(C.Structure):
     _fields_ = [("ids", C.POINTER(C.c_uint32)), ("ids_cap", C.c_uint32), ("n_ids", C.c_uint32), ("logits", C.POINTER(C.c_float)), ("logits_cap", C.c_uint64),
                 ("hidden", C.POINTER(C.c_float)), ("hidden_cap", C.c_uint64), ("n_hidden", C.c_uint32), ("taps", C.POINTER(C.c_uint16)),
-                ("taps_cap", C.c_uint64), ("gpu_seconds", C.c_double)]
+                ("taps_cap", C.c_uint64), ("gpu_seconds", C.c_double), ("n_taps", C.c_uint32)]
+
+
+class _LayerCapture(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("layer", "n", "d_model", "qkv_width", "attn_width")] + \
+               [(n, C.POINTER(C.c_float)) for n in ("resid_in", "attn_in", "qkv", "sdpa_out", "attn_out", "mlp_in", "mlp_out", "resid_base")]
+
+
+_CAPTURE_FN = C.CFUNCTYPE(None, C.POINTER(_LayerCapture), C.c_void_p)
 
 
 class _ModelDesc(C.Structure):
@@ -219,8 +227,15 @@ class Engine:
         cs = s.c()
         _check(lib().vlt_seq_set_sampling(self.h, C.c_uint32(seq), C.byref(cs)))
 
-    def set_taps(self, on: bool) -> None:
-        _check(lib().vlt_set_taps(self.h, C.c_uint32(int(on))))
+    def set_taps(self, layers) -> None:
+        """engine.rs:381-389: tap these layers' outputs from the next step on (StepOptions.read_taps)."""
+        a = _u32(list(layers))
+        _check(lib().vlt_set_taps(self.h, _ptr(a), C.c_uint32(a.size)))
+        self._taps = [int(x) for x in a]
+
+    def set_acceptance(self, rule: int) -> None:
+        """0: the reference's sample-then-match `accept`; 1: rejection sampling for runs whose drafts the chain drafter drew."""
+        _check(lib().vlt_set_acceptance(self.h, C.c_uint32(rule)))
 
     def load_drafter(self, path) -> None:
         _check(lib().vlt_load_drafter(self.h, str(path).encode()))
@@ -228,6 +243,13 @@ class Engine:
     def set_draft_rows(self, rows: int) -> None:
         """debug_step then runs the loaded drafter for `rows` rows (rows - 1 drafts) after each step; 0: not."""
         lib().vlt_debug_set_draft_rows(self.h, C.c_uint32(rows))
+
+    def force_logits(self, logits=None, draft_logits=None) -> None:
+        """The next debug_step's sampler / acceptance / drafter pick read these instead of the logits it computed."""
+        a = None if logits is None else np.ascontiguousarray(logits, np.float32)
+        b = None if draft_logits is None else np.ascontiguousarray(draft_logits, np.float32)
+        _check(lib().vlt_debug_force_logits(self.h, None if a is None else _ptr(a, C.c_float), C.c_uint64(0 if a is None else a.size),
+                                            None if b is None else _ptr(b, C.c_float), C.c_uint64(0 if b is None else b.size)))
 
     def has_drafter(self) -> bool:
         return bool(lib().vlt_has_drafter(self.h))
@@ -245,15 +267,16 @@ class Engine:
         ids = np.zeros(rows, np.uint32)
         logits = np.zeros(rows * d.vocab if opts.read_logits else 0, np.float32)
         hidden = np.zeros(n_tokens * d.d_model if opts.hidden != Rows.NONE else 0, np.float32)
-        taps = np.zeros(n_tokens * d.d_model if opts.read_taps else 0, np.uint16)
-        out = _StepOutput(_ptr(ids), rows, 0, _ptr(logits, C.c_float), logits.size, _ptr(hidden, C.c_float), hidden.size, 0, _ptr(taps, C.c_uint16), taps.size, 0.0)
+        n_taps = len(getattr(self, "_taps", [])) + 1  # (+1: a loaded drafter keeps the last layer tapped)
+        taps = np.zeros(n_taps * n_tokens * d.d_model if opts.read_taps else 0, np.uint16)
+        out = _StepOutput(_ptr(ids), rows, 0, _ptr(logits, C.c_float), logits.size, _ptr(hidden, C.c_float), hidden.size, 0, _ptr(taps, C.c_uint16), taps.size, 0.0, 0)
         return out, (ids, logits, hidden, taps)
 
     def _result(self, out, bufs, n_tokens, opts) -> StepOutput:
         ids, logits, hidden, taps = bufs
         d = self.desc
         return StepOutput(ids[:out.n_ids].copy(), logits[:out.n_ids * d.vocab].reshape(-1, d.vocab) if opts.read_logits else logits,
-                          hidden[:out.n_hidden * d.d_model].reshape(-1, d.d_model), taps.reshape(-1, d.d_model) if taps.size else taps, out.gpu_seconds)
+                          hidden[:out.n_hidden * d.d_model].reshape(-1, d.d_model), taps[:out.n_taps * n_tokens * d.d_model].reshape(out.n_taps, n_tokens, d.d_model) if taps.size else taps, out.gpu_seconds)
 
     def step(self, runs, opts: StepOptions | None = None) -> StepOutput:
         """engine.rs:310-314: one synchronous step of CPU-fed runs."""
@@ -264,6 +287,25 @@ class Engine:
         out, bufs = self._out(n, opts)
         _check(lib().vlt_step(self.h, arr, C.c_uint32(len(runs)), C.byref(co), C.byref(out)))
         return self._result(out, bufs, n, opts)
+
+    def step_capture(self, runs, opts: StepOptions | None = None):
+        """engine.rs:318-355: a step that hands every layer's intermediates back. Returns (StepOutput, [layer dicts]) with
+        each dict's arrays shaped [n][width]."""
+        opts = opts or StepOptions()
+        arr, keep = self._runs(runs)
+        n = sum(len(k) for k in keep)
+        co = _StepOptions(opts.head, opts.hidden, int(opts.read_logits), int(opts.read_taps))
+        out, bufs = self._out(n, opts)
+        layers = []
+
+        def take(pc, _user):
+            c = pc.contents
+            widths = dict(resid_in=c.d_model, attn_in=c.d_model, qkv=c.qkv_width, sdpa_out=c.attn_width, attn_out=c.d_model, mlp_in=c.d_model, mlp_out=c.d_model)
+            layers.append({"layer": c.layer, **{k: np.ctypeslib.as_array(getattr(c, k), shape=(c.n, w)).copy() for k, w in widths.items()}})
+
+        cb = _CAPTURE_FN(take)
+        _check(lib().vlt_step_capture(self.h, arr, C.c_uint32(len(runs)), C.byref(co), cb, None, C.byref(out)))
+        return self._result(out, bufs, n, opts), layers
 
     def bench_fill(self, seq: int, n: int, seed: int = 0) -> None:
         _check(lib().vlt_bench_fill(self.h, C.c_uint32(seq), C.c_uint32(n), C.c_uint32(seed)))
