@@ -4,12 +4,16 @@
 
 One rank per GPU (torchrun for N > 1): each rank is an independent replica with its own
 streams -- no collective on the data path; ranks only meet at the timing barriers. A "step"
-is one verify step of every stream on the rank: k = 4 drafts + 1 row per stream through the
-target, sampling at T = 0.6 / top-p 0.95, acceptance and KV commit. Prints one JSON line.
+is one decode step of every stream on the rank: the chain drafter's catch-up and k = 4 draft passes,
+k + 1 rows per stream through the int8 target, acceptance at T = 0.6 (rejection sampling against the
+drafter's distribution) and KV commit. Further passes in the same JSON line: the target alone behind the
+replay drafter, 1 and 8 streams, bf16 at one stream, the 64k context, the acceptance kernel alone, and
+the CPU restatement's sample. Prints one JSON line.
 """
 from __future__ import annotations
 
 import argparse
+import copy
 import importlib.util
 import json
 import os
@@ -141,7 +145,7 @@ def run_replica(args, rank, world, barrier, device, eng, mistakes, model_drafter
     (or, with `model_drafter`, from the loaded chain drafter)."""
     from silicon_violetto_b200 import engine as E
     total_steps = args.warmup + args.steps + 6
-    sampling = lambda j: E.Sampling(args.temperature, 0.95, stream_seeds(rank, j)[1])
+    sampling = lambda j: E.Sampling(args.temperature, args.top_p, stream_seeds(rank, j)[1])
     n_rec = ROWS * total_steps + 8
     recorded = record_plain(E, eng, args.streams, args.ctx, n_rec, rank, sampling) if mistakes < 1.0 and not model_drafter else [[0] * n_rec] * args.streams
     seqs = fill(eng, args.streams, args.ctx, rank)
@@ -197,7 +201,7 @@ def cpu_reference(args, streams, steps, warmup=1):
                         max_seq_len=args.ctx + room, max_head_rows=streams * ROWS)
     seqs = [eng.new_seq() for _ in range(streams)]
     for j, s in enumerate(seqs):
-        eng.set_sampling(s, args.temperature, 0.95, 1 + j)
+        eng.set_sampling(s, args.temperature, 0.95, 1 + j)  # (the reference's sample-then-match acceptance: the target's verify step alone)
         eng.bench_fill(s, args.ctx)
         eng.write("feed", s * 16, [100 + j, 1, 2, 3, 4])
     runs = [(s, [oracle.FEED_ROW + i for i in range(ROWS)], oracle.ROWS_LAST, True) for s in seqs]
@@ -234,6 +238,28 @@ def stream_seeds(rank: int, stream: int):
     return 1000 * rank + 7 + stream, 1 + 1000 * rank + stream
 
 
+def spec_accept_figure(E, eng, hbm_peak):
+    """BASELINE configuration 1: the stand-alone acceptance step on 32 streams x (5 target + 4 draft) rows of bf16
+    logits N(0, 3^2) over 128 256 ids at temperature 1; drafts drawn from softmax(q) (numpy, seed 1), uniforms keyed by
+    seed 2. Algorithmic bytes: p and q read once."""
+    rng = np.random.default_rng(0)
+    streams, k, v = 32, 4, eng.desc.vocab
+    from silicon_violetto_b200 import vlt
+    p = vlt.to_bf16((rng.standard_normal((streams, k + 1, v)) * 3.0).astype(np.float32))
+    q = vlt.to_bf16((rng.standard_normal((streams, k, v)) * 3.0).astype(np.float32))
+    qf = vlt.from_bf16(q).astype(np.float64)
+    pr = np.exp(qf - qf.max(axis=2, keepdims=True))
+    pr /= pr.sum(axis=2, keepdims=True)
+    r1 = np.random.default_rng(1)
+    drafts = np.array([[r1.choice(v, p=pr[s_, i]) for i in range(k)] for s_ in range(streams)], np.uint32)
+    seeds = np.arange(streams, dtype=np.uint64) + np.uint64(2)
+    pos0 = np.full(streams, 8192, np.uint32)
+    acc, tok, rb, secs = eng.spec_accept(p, q, drafts, 1.0, seeds, pos0, reps=10)
+    nbytes = p.nbytes + q.nbytes
+    return {"workload": "32 streams, k=4, 128256 ids, bf16 logits N(0, 3^2), T=1", "us": secs * 1e6, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / secs / 1e9,
+            "frac_of_hbm_peak": nbytes / secs / 1e9 / hbm_peak, "mean_accepted": float(acc.mean())}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -243,14 +269,18 @@ def main():
     ap.add_argument("--streams", type=int, default=32, help="streams per GPU")
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--temperature", type=float, default=0.6)
-    ap.add_argument("--mistakes", type=float, default=1.0, help="share of positions drafted wrong in the headline pass (1: every draft wrong, what a random-init drafter gives)")
+    ap.add_argument("--top-p", type=float, default=1.0, help="1: the rejection-sampling acceptance decides the drafted runs (BASELINE configurations 3 and 4); below 1 the reference's sample-then-match does")
+    ap.add_argument("--mistakes", type=float, default=1.0, help="share of positions drafted wrong in the replay-drafter passes' first one (1: every draft wrong, what a random-init drafter gives)")
     ap.add_argument("--replay-mistakes", type=float, default=0.3, help="a second pass with the replay drafter at this mistake rate (cli/src/bench_spec.rs:26-28); 1: skip")
-    ap.add_argument("--bf16", action="store_true", help="bf16 weights instead of int8")
+    ap.add_argument("--bf16", action="store_true", help="bf16 weights instead of int8 (no drafter pass)")
     ap.add_argument("--cpu-streams", type=int, default=8, help="streams of the CPU sample")
     ap.add_argument("--cpu-steps", type=int, default=10, help="timed verify steps of the CPU sample (the reference arm takes --steps, at most 20)")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--also-streams", default="1", help="comma list: extra passes at these stream counts on rank 0's engine (the headline metric is quoted at 1 and 32 streams); empty: none")
-    ap.add_argument("--no-model-drafter", action="store_true", help="skip the pass with the chain drafter loaded")
+    ap.add_argument("--also-streams", default="1,8", help="comma list: extra passes at these stream counts on rank 0's engine (the headline metric is quoted at 1, 8 and 32 streams); empty: none")
+    ap.add_argument("--no-model-drafter", action="store_true", help="the headline pass without the chain drafter (replay drafter, every draft wrong)")
+    ap.add_argument("--no-extras", action="store_true", help="only the headline pass (no replay, stream-count, bf16, long-context or acceptance-kernel passes)")
+    ap.add_argument("--long-ctx", type=int, default=65536, help="context of the long-context pass every rank runs after the headline one (BASELINE configuration 4); 0: skip")
+    ap.add_argument("--long-steps", type=int, default=20)
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
     args = ap.parse_args()
@@ -260,22 +290,27 @@ def main():
     if (ROOT / "MEASURED_PEAKS.json").exists():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
     hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
-    workload = f"1B llama-style target, {'bf16' if args.bf16 else 'int8 per-row'} weights, {args.streams} streams/GPU, ctx {args.ctx}, k=4 (5 rows), T={args.temperature} top-p 0.95"
+    with_drafter = not (args.no_model_drafter or args.bf16 or args.layers)
+    workload = (f"1B llama-style target{' + chain drafter' if with_drafter else ''}, {'bf16' if args.bf16 else 'int8 per-row'} weights, {args.streams} streams/GPU, ctx {args.ctx}, "
+                f"k=4 (5 rows), T={args.temperature} top-p {args.top_p}")
     if args.layers:
         workload += f" -- CUT TO {args.layers} LAYERS (profiler-size case)"
 
     if args.impl == "reference":
+        # The reference has no CPU implementation of this path (its arithmetic is Metal shaders); what runs here is the C++
+        # restatement of that shader math on this machine's cores, on the main arm's stream count, a bounded number of steps.
         if rank != 0:
             return
         ref_steps = max(1, min(args.steps, 20))
-        t_step, cores, em = cpu_reference(args, args.cpu_streams, ref_steps, warmup=min(args.warmup, 3))
+        t_step, cores, em = cpu_reference(args, args.streams, ref_steps, warmup=1)
         v = em / t_step
         print(json.dumps({"impl": "reference", "metric": "decode tokens/s at 8k context", "value": v, "unit": "tokens/s",
                           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
                           "vs_baseline": None, "dtype": "bf16 activations, int8 weights" if not args.bf16 else "bf16", "data": "synthetic",
-                          "config": {"workload": workload, "streams_timed": args.cpu_streams, "drafter": "every draft wrong", "mean_accepted_len": em / args.cpu_streams},
+                          "config": {"workload": workload, "streams_timed": args.streams, "steps_timed": ref_steps, "drafter": "every draft wrong (the target's verify step alone)",
+                                     "mean_accepted_len": em / args.streams},
                           "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                           "sample": f"{args.cpu_streams} streams x {ref_steps} verify steps of 5 rows at ctx {args.ctx}; the reference has no CPU path, this is the C++ restatement of its shader math"},
+                                           "sample": f"{args.streams} streams x {ref_steps} verify steps of 5 rows at ctx {args.ctx}; the reference has no CPU path, this is the C++ restatement of its shader math"},
                           "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
@@ -290,13 +325,37 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(local)
 
+    solo = lambda: torch.cuda.synchronize(local)
     _package()
     from silicon_violetto_b200 import engine as E
     path = model_file("1b", not args.bf16, rank, args.layers)
-    eng, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
-    r = run_replica(args, rank, world, barrier, local, eng, args.mistakes)
-    extra = run_replica(args, rank, world, barrier, local, eng, args.replay_mistakes) if args.replay_mistakes < 1.0 else None
+    total = args.warmup + args.steps + 6
+    # The headline pass, on every rank: the int8 target with the chain drafter loaded (1 layer + fc + a head over 16 384 draft
+    # ids, random-init), drafts drawn from its distribution, the rejection-sampling rule deciding them in the step.
+    eng, _ = make_engine(E, path, args.streams, args.ctx, total, local, args.attn_keys)
+    if with_drafter:
+        eng.load_drafter(drafter_file(rank))
+        eng.set_acceptance(1 if args.top_p >= 1.0 else 0)
+    r = run_replica(args, rank, world, barrier, local, eng, args.mistakes, model_drafter=with_drafter)
     vals, sums = reduce_over_ranks(r["dev_ms"], r["wall"], r["emitted"], r["launches"], world, f"cuda:{local}")
+    eng.close()
+    # The long-context pass (BASELINE configuration 4's share of one GPU), on every rank as well.
+    long_pass = None
+    if args.long_ctx and not args.no_extras and not args.layers:
+        a4 = copy.copy(args)
+        a4.ctx, a4.steps = args.long_ctx, args.long_steps
+        e4, _ = make_engine(E, path, args.streams, a4.ctx, a4.warmup + a4.steps + 6, local, args.attn_keys)
+        if with_drafter:
+            e4.load_drafter(drafter_file(rank))
+            e4.set_acceptance(1 if args.top_p >= 1.0 else 0)
+        r4 = run_replica(a4, rank, world, barrier, local, e4, 1.0, model_drafter=with_drafter)
+        v4, s4 = reduce_over_ranks(r4["dev_ms"], r4["wall"], r4["emitted"], r4["launches"], world, f"cuda:{local}")
+        e4.close()
+        kv4 = args.streams * (r4["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER * 16
+        long_pass = {"workload": f"{args.streams} streams/GPU at ctx {a4.ctx}, {a4.steps} steps", "value": s4[0] / (v4[0] * 1e-3), "unit": "tokens/s (all ranks)",
+                     "ms_per_step": v4[0] / a4.steps, "e2e": s4[0] / v4[1], "mean_accepted_len": s4[0] / (a4.steps * args.streams * world),
+                     "step_frac": (WEIGHT_PARAMS + kv4) / (v4[0] * 1e-3 / a4.steps) / 1e9 / hbm_peak,
+                     "kernel_groups_ms_per_step": {k: v["ms"] / r4["prof_steps"] for k, v in r4["prof"].items()}}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -312,11 +371,13 @@ def main():
     att_bytes = args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER
     achieved = att_bytes / (att_ms * 1e-3) / 1e9 if att_ms > 0 else 0.0
     step_bytes = WEIGHT_PARAMS * (2 if args.bf16 else 1) + args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER * (args.layers or 16)
+    drafter_note = ("chain drafter (1 layer + fc + head over 16384 draft ids, int8, random-init: its drafts are practically never accepted), drafts drawn from its own "
+                    "distribution, rejection-sampling acceptance in the step" if with_drafter else f"replay drafter, {args.mistakes:.2f} of positions drafted wrong")
     out = {
         "metric": "decode tokens/s at 8k context", "value": emitted / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
         "ms_per_step": dev_s * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.bf16 else "bf16 activations x int8 weights, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": workload, "drafter": f"replay drafter, {args.mistakes:.2f} of positions drafted wrong", "mean_accepted_len": tau,
+        "config": {"workload": workload, "drafter": drafter_note, "mean_accepted_len": tau,
                    "kv": "filled without computing it (timing does not depend on KV values)", "l2": "per-step traffic (weights 1.2 GB + KV) exceeds the 126 MB L2",
                    "parallelism": f"{world} replica(s), streams sharded, no collective"},
         "e2e": {"value": emitted / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
@@ -326,47 +387,73 @@ def main():
                      # dram__bytes_read + dram__bytes_write of one launch of this very shape under ncu: 1.009 x the algorithmic
                      # bytes (profiles/attn_mma_kernel_32streams_8k.md); scaled to this run's key count.
                      "traffic": att_bytes * ATTN_TRAFFIC_RATIO, "traffic_source": "ncu capture of the same launch shape, scaled by keys",
+                     # the target's verify step alone (weights + K/V once) against the whole step's time, drafter included
                      "step_frac": step_bytes / (dev_s / steps) / 1e9 / hbm_peak},
         "kernel_groups_ms_per_step": {k: v["ms"] / r["prof_steps"] for k, v in r["prof"].items()},
     }
-    if extra is not None:
-        out["replay_pass"] = {"mistakes": args.replay_mistakes, "value": extra["emitted"] / (extra["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)",
-                              "mean_accepted_len": extra["emitted"] / (steps * args.streams), "ms_per_step": extra["dev_ms"] / steps,
-                              # Chains that stop at the first wrong draft accept 1 + 0.7 + 0.7^2 + ... = 2.77 of 5 rows at 0.30. The drafts
-                              # replay a recording of one-row decoding; a stream whose sampled token once differs from it (sums in another
-                              # order, a random-init model's flat distributions: a near-tie of the draw) drafts wrong from then on.
-                              "note": "expected 2.77 at 0.30 mistakes; streams that leave their recorded continuation (sampling near-ties) draft wrong afterwards"}
-    import copy
-    if not args.layers:
+    if long_pass is not None:
+        out["long_context_pass"] = long_pass
+    if not args.no_extras and not args.layers:
+        # The target's verify step alone, drafts from the replay drafter: every one wrong, then at the reference's mistake rate.
+        a0 = copy.copy(args)
+        a0.top_p = 0.95
+        e0, _ = make_engine(E, path, args.streams, args.ctx, total, local, args.attn_keys)
+        r0 = run_replica(a0, rank, 1, solo, local, e0, 1.0)
+        p0 = r0["prof"]
+        out["replay_pass_all_wrong"] = {"value": r0["emitted"] / (r0["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r0["dev_ms"] / steps, "e2e": r0["emitted"] / r0["wall"],
+                                        "mean_accepted_len": r0["emitted"] / (steps * args.streams), "sampling": "T as above, top-p 0.95 (the reference's sample-then-match acceptance)",
+                                        "step_frac": step_bytes / (r0["dev_ms"] * 1e-3 / steps) / 1e9 / hbm_peak,
+                                        "verify_attention_frac": step_bytes / ((p0["matmul"]["ms"] + p0["attention"]["ms"]) / r0["prof_steps"] * 1e-3) / 1e9 / hbm_peak,
+                                        "kernel_groups_ms_per_step": {k: v["ms"] / r0["prof_steps"] for k, v in p0.items()}}
+        if args.replay_mistakes < 1.0:
+            extra = run_replica(a0, rank, 1, solo, local, e0, args.replay_mistakes)
+            out["replay_pass"] = {"mistakes": args.replay_mistakes, "value": extra["emitted"] / (extra["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)",
+                                  "mean_accepted_len": extra["emitted"] / (steps * args.streams), "ms_per_step": extra["dev_ms"] / steps,
+                                  # Chains that stop at the first wrong draft accept 1 + 0.7 + 0.7^2 + ... = 2.77 of 5 rows at 0.30. The drafts
+                                  # replay a recording of one-row decoding; a stream whose sampled token once differs from it (sums in another
+                                  # order, a random-init model's flat distributions: a near-tie of the draw) drafts wrong from then on.
+                                  "note": "expected 2.77 at 0.30 mistakes; streams that leave their recorded continuation (sampling near-ties) draft wrong afterwards"}
+        out["acceptance_kernel"] = spec_accept_figure(E, e0, hbm_peak)
+        e0.close()
         for n_s in [int(x) for x in args.also_streams.split(",") if x.strip()]:
             if n_s >= args.streams:
                 continue
-            a2 = copy.copy(args)
+            a2 = copy.copy(a0)
             a2.streams = n_s
-            e2, _ = make_engine(E, path, n_s, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
-            r2 = run_replica(a2, rank, 1, lambda: torch.cuda.synchronize(local), local, e2, args.replay_mistakes)
-            r1 = run_replica(a2, rank, 1, lambda: torch.cuda.synchronize(local), local, e2, 1.0)
-            out[f"streams_{n_s}"] = {"value": r1["emitted"] / (r1["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r1["dev_ms"] / steps,
-                                     "e2e": r1["emitted"] / r1["wall"], "mean_accepted_len": r1["emitted"] / (steps * n_s),
-                                     "replay_pass": {"mistakes": args.replay_mistakes, "value": r2["emitted"] / (r2["dev_ms"] * 1e-3),
-                                                     "mean_accepted_len": r2["emitted"] / (steps * n_s), "ms_per_step": r2["dev_ms"] / steps},
-                                     "kernel_groups_ms_per_step": {k: v["ms"] / r1["prof_steps"] for k, v in r1["prof"].items()}}
+            e2, _ = make_engine(E, path, n_s, args.ctx, total, local, args.attn_keys)
+            r2 = run_replica(a2, rank, 1, solo, local, e2, args.replay_mistakes)
+            r1 = run_replica(a2, rank, 1, solo, local, e2, 1.0)
             e2.close()
-    if not args.layers and not args.no_model_drafter and not args.bf16:
-        eng.close()
-        e3, _ = make_engine(E, path, args.streams, args.ctx, args.warmup + args.steps + 6, local, args.attn_keys)
-        e3.load_drafter(drafter_file(0))
-        r3 = run_replica(args, rank, 1, lambda: torch.cuda.synchronize(local), local, e3, 1.0, model_drafter=True)
-        out["model_drafter_pass"] = {"value": r3["emitted"] / (r3["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r3["dev_ms"] / steps,
-                                     "mean_accepted_len": r3["emitted"] / (steps * args.streams),
-                                     "drafter": "chain drafter, 1 layer + fc + head over 16384 draft ids, int8, random-init (its drafts are never right)",
-                                     "kernel_groups_ms_per_step": {k: v["ms"] / r3["prof_steps"] for k, v in r3["prof"].items()}}
-        e3.close()
+            entry = {"value": r1["emitted"] / (r1["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r1["dev_ms"] / steps,
+                     "e2e": r1["emitted"] / r1["wall"], "mean_accepted_len": r1["emitted"] / (steps * n_s),
+                     "replay_pass": {"mistakes": args.replay_mistakes, "value": r2["emitted"] / (r2["dev_ms"] * 1e-3),
+                                     "mean_accepted_len": r2["emitted"] / (steps * n_s), "ms_per_step": r2["dev_ms"] / steps},
+                     "kernel_groups_ms_per_step": {k: v["ms"] / r1["prof_steps"] for k, v in r1["prof"].items()}}
+            if with_drafter:
+                a3 = copy.copy(args)
+                a3.streams = n_s
+                e3, _ = make_engine(E, path, n_s, args.ctx, total, local, args.attn_keys)
+                e3.load_drafter(drafter_file(0))
+                e3.set_acceptance(1 if args.top_p >= 1.0 else 0)
+                r3 = run_replica(a3, rank, 1, solo, local, e3, 1.0, model_drafter=True)
+                e3.close()
+                entry["with_chain_drafter"] = {"value": r3["emitted"] / (r3["dev_ms"] * 1e-3), "ms_per_step": r3["dev_ms"] / steps, "mean_accepted_len": r3["emitted"] / (steps * n_s)}
+            out[f"streams_{n_s}"] = entry
+        if not args.bf16:
+            # BASELINE configuration 2: the same target in bf16, one stream.
+            ab = copy.copy(a0)
+            ab.streams, ab.bf16 = 1, True
+            eb, _ = make_engine(E, model_file("1b", False, 0), 1, args.ctx, total, local, args.attn_keys)
+            rb = run_replica(ab, rank, 1, solo, local, eb, 1.0)
+            eb.close()
+            out["bf16_streams_1"] = {"value": rb["emitted"] / (rb["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": rb["dev_ms"] / steps, "e2e": rb["emitted"] / rb["wall"],
+                                     "mean_accepted_len": rb["emitted"] / steps}
     if world == 1 and not args.no_cpu:
-        eng.close()
         t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)
         out["cpu_baseline"] = {"value": em / t_step, "unit": "tokens/s", "cores": cores, "kind": "port",
                                "sample": f"{args.cpu_streams} streams x {args.cpu_steps} verify steps of 5 rows at ctx {args.ctx} ({t_step:.2f} s/step), every draft wrong"}
+        t1, _, em1 = cpu_reference(args, 1, args.cpu_steps)
+        out["cpu_baseline"]["one_stream"] = {"value": em1 / t1, "unit": "tokens/s", "sample": f"1 stream x {args.cpu_steps} verify steps of 5 rows at ctx {args.ctx} ({t1:.2f} s/step)"}
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
