@@ -218,7 +218,7 @@ typedef struct {
     uint32_t n_trace;
 } VltRequest;
 enum { VLT_EVENT_TOKEN = 0, VLT_EVENT_DONE = 1 };
-enum { VLT_FINISH_STOP = 0, VLT_FINISH_LENGTH = 1 };
+enum { VLT_FINISH_STOP = 0, VLT_FINISH_LENGTH = 1, VLT_FINISH_FAILED = 2 /* router only: no replica could take the request */ };
 typedef struct {
     uint32_t kind; /* VLT_EVENT_* */
     uint32_t req;
@@ -244,6 +244,37 @@ void vlt_generator_counts(VltGenerator* g, uint32_t* queued, uint32_t* running);
 int vlt_generator_stats(VltGenerator* g, VltStepStats* out, uint32_t cap, uint32_t* n);
 void vlt_generator_set_hold(VltGenerator* g, uint32_t hold);
 void vlt_generator_set_replay_mistakes(VltGenerator* g, float rate, uint32_t seed);
+
+/* Replicas. The model fits one GPU, so a machine's GPUs are used as independent replicas -- one engine and generator per
+ * device, no exchange between them -- and a router on the host shards the streams: a request goes to the live replica
+ * with the fewest requests, and when a replica's step fails, its unfinished requests are submitted again on the others,
+ * continued from the tokens they had emitted (a sequence's draws are keyed by seed and position, engine.rs:100-102, so
+ * the continuation is the one the failed replica would have produced). The reference has one engine on one device and
+ * exits when it fails (cli/src/serve.rs:147-150): this has no counterpart there. A replica is a table of the generator's
+ * calls (generate.rs:185-280), so that it can be a VltGenerator (vlt_replica_of_generator) or anything else that
+ * behaves like one; each must be called from the thread that owns it, i.e. the router's. */
+typedef struct {
+    void* ctx;
+    int (*submit)(void* ctx, const VltRequest* req, uint32_t* req_id);
+    int (*step)(void* ctx, VltEvent* events, uint32_t cap, uint32_t* n_events); /* non-zero: the replica has failed */
+    void (*cancel)(void* ctx, uint32_t req_id);                                 /* may be NULL */
+    int (*is_idle)(void* ctx);
+    void (*counts)(void* ctx, uint32_t* queued, uint32_t* running);
+} VltReplicaOps;
+typedef struct VltRouter VltRouter;
+void vlt_replica_of_generator(VltGenerator* g, VltReplicaOps* out);
+int vlt_router_new(const VltReplicaOps* replicas, uint32_t n_replicas, VltRouter** out);
+void vlt_router_free(VltRouter* r);
+/* Token prompts only (a resumed sequence lives on one replica's engine). */
+int vlt_router_submit(VltRouter* r, const VltRequest* req, uint32_t* req_id);
+void vlt_router_cancel(VltRouter* r, uint32_t req_id);
+/* One step of every live replica; events carry the router's request ids. A request that no replica can take after a
+ * failure ends with VLT_EVENT_DONE / VLT_FINISH_FAILED; with no replica left and requests pending the call fails. */
+int vlt_router_step(VltRouter* r, VltEvent* events, uint32_t cap, uint32_t* n_events);
+int vlt_router_is_idle(VltRouter* r);
+uint32_t vlt_router_alive(VltRouter* r);
+/* The replica a pending request is on (VLT_NO_TOK: finished or unknown). */
+uint32_t vlt_router_replica_of(VltRouter* r, uint32_t req_id);
 
 /* Inspection, for parity tests against the CPU oracle: copies a named engine array into `out`
  * (u32 words: "lens", "feed", "tree", "gen", "path", "path_len", "on_path", "page_table",

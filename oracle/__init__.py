@@ -296,11 +296,6 @@ class Engine:
     def set_replay(self, rate: float, seed: int):
         lib().orc_set_replay(self.h, C.c_float(rate), C.c_uint32(seed))
 
-    def set_p_bf16(self, on: bool):
-        """Round the attention's probabilities to bf16 before P.V (a bf16 tensor-core product's convention) instead of the
-        reference's fp32 ones."""
-        lib().orc_set_p_bf16(self.h, C.c_uint32(int(on)))
-
     def set_capture(self, on: bool):
         """Keep every layer's intermediates of the next steps (arrays cap_resid_in, cap_attn_in, cap_qkv, cap_sdpa_out,
         cap_attn_out, cap_mlp_in, cap_mlp_out: [layer][n][width])."""

@@ -150,7 +150,6 @@ void orc_set_trace(void* h, uint32_t slot, const uint32_t* trace, uint32_t n) {
 int orc_load_drafter(void* h, const char* path) { try { static_cast<Engine*>(h)->load_drafter(path); return 0; } catch (const std::exception& e) { return fail(e); } }
 // 0: the reference's acceptance (sample, then match); 1: rejection sampling for runs whose drafts came with their q rows.
 void orc_set_acceptance(void* h, uint32_t rule) { static_cast<Engine*>(h)->accept_rule = rule; }
-void orc_set_p_bf16(void* h, uint32_t on) { static_cast<Engine*>(h)->p_bf16 = on != 0; }
 void orc_set_capture(void* h, uint32_t on) { static_cast<Engine*>(h)->capture = on != 0; }
 void orc_set_taps(void* h, const uint32_t* layers, uint32_t n) { static_cast<Engine*>(h)->tap_layers.assign(layers, layers + n); }
 void orc_set_replay(void* h, float rate, uint32_t seed) {

@@ -195,11 +195,6 @@ struct Engine {
     // engine.rs:381-389 `set_taps`: bf16(rms_norm(output)) of these layers, [tap][n][d] (`taps` is the last layer's, always kept).
     std::vector<uint32_t> tap_layers;
     std::vector<float> taps_all;
-    // Off (the default): the attention's probabilities stay fp32 in P.V, as in the reference. On: they are rounded to bf16
-    // first, which is what a bf16 tensor-core P.V does. Over a handful of keys that rounding is the largest single term of
-    // the CUDA path's deviation from the reference's arithmetic (it averages out over a long context); a test that wants to
-    // see everything else at full resolution on short sequences switches it on and says so.
-    bool p_bf16 = false;
     uint32_t accept_rule = 0;  // 0: the reference's sample-then-match; 1: rejection sampling where a run's drafts came with their q rows
 
     Engine(const std::string& file_path, const EngineConfig& c) : file(VltFile::load(file_path)), cfg(c) {
@@ -420,11 +415,8 @@ struct Engine {
                         if (sc[kp] == -INFINITY) continue;
                         const float pz = std::exp2(sc[kp] - mx);
                         l += pz;
-                        // The reference multiplies fp32 probabilities (kernels.metal:1075-1110); with p_bf16 they are rounded like every
-                        // other input of a bf16 tensor-core product (the sum l keeps the unrounded ones), see `p_bf16`.
-                        const float pv = p_bf16 ? round_bf16(pz) : pz;
                         const uint16_t* vr = vc + kv_row(layer, slot, g, kp);
-                        for (uint32_t d = 0; d < hd; d++) o[d] += pv * bf16_to_f32(vr[d]);
+                        for (uint32_t d = 0; d < hd; d++) o[d] += pz * bf16_to_f32(vr[d]);
                     }
                     for (uint32_t d = 0; d < hd; d++) out[size_t(t) * md.n_heads * hd + h * hd + d] = o[d] / l;
                 }

@@ -6,6 +6,7 @@
 #include "../../include/violetto.h"
 #include "engine.h"
 #include "generator.h"
+#include "router.h"
 
 using namespace vlt;
 
@@ -16,6 +17,10 @@ struct VltEngine {
 struct VltGenerator {
     std::unique_ptr<Generator> g;
     VltEngine* owner = nullptr;
+};
+
+struct VltRouter {
+    std::unique_ptr<Router> r;
 };
 
 static thread_local std::string g_error;
@@ -299,6 +304,44 @@ int vlt_generator_stats(VltGenerator* g, VltStepStats* out, uint32_t cap, uint32
 
 void vlt_generator_set_hold(VltGenerator* g, uint32_t hold) { if (g && g->g) g->g->hold = hold != 0; }
 void vlt_generator_set_replay_mistakes(VltGenerator* g, float rate, uint32_t seed) { if (g && g->g) g->g->set_replay_mistakes(rate, seed); }
+
+// ---- replicas
+static int rep_submit(void* ctx, const VltRequest* req, uint32_t* id) { return vlt_generator_submit(static_cast<VltGenerator*>(ctx), req, id); }
+static int rep_step(void* ctx, VltEvent* ev, uint32_t cap, uint32_t* n) { return vlt_generator_step(static_cast<VltGenerator*>(ctx), ev, cap, n); }
+static void rep_cancel(void* ctx, uint32_t id) { vlt_generator_cancel(static_cast<VltGenerator*>(ctx), id); }
+static int rep_idle(void* ctx) { return vlt_generator_is_idle(static_cast<VltGenerator*>(ctx)); }
+static void rep_counts(void* ctx, uint32_t* q, uint32_t* r) { *q = *r = 0; vlt_generator_counts(static_cast<VltGenerator*>(ctx), q, r); }
+
+void vlt_replica_of_generator(VltGenerator* g, VltReplicaOps* out) {
+    if (out) *out = VltReplicaOps{g, rep_submit, rep_step, rep_cancel, rep_idle, rep_counts};
+}
+
+int vlt_router_new(const VltReplicaOps* replicas, uint32_t n_replicas, VltRouter** out) {
+    return guard([&] {
+        if (!replicas || !out) throw Error("vlt_router_new: null argument");
+        auto h = std::make_unique<VltRouter>();
+        h->r = std::make_unique<Router>(std::vector<VltReplicaOps>(replicas, replicas + n_replicas));
+        *out = h.release();
+    });
+}
+void vlt_router_free(VltRouter* r) { delete r; }
+static Router& router(VltRouter* r) {
+    if (!r || !r->r) throw Error("null router");
+    return *r->r;
+}
+int vlt_router_submit(VltRouter* r, const VltRequest* req, uint32_t* req_id) { return guard([&] { *req_id = router(r).submit(*req); }); }
+void vlt_router_cancel(VltRouter* r, uint32_t req_id) { if (r && r->r) r->r->cancel(req_id); }
+int vlt_router_step(VltRouter* r, VltEvent* events, uint32_t cap, uint32_t* n_events) {
+    return guard([&] {
+        const std::vector<VltEvent> ev = router(r).step();
+        if (ev.size() > cap) throw Error("event buffer too small: " + std::to_string(ev.size()) + " events");
+        for (size_t i = 0; i < ev.size(); i++) events[i] = ev[i];
+        *n_events = uint32_t(ev.size());
+    });
+}
+int vlt_router_is_idle(VltRouter* r) { return r && r->r && r->r->is_idle() ? 1 : 0; }
+uint32_t vlt_router_alive(VltRouter* r) { return r && r->r ? r->r->alive() : 0; }
+uint32_t vlt_router_replica_of(VltRouter* r, uint32_t req_id) { return r && r->r ? r->r->replica_of(req_id) : NO_TOK; }
 
 // ---- inspection
 int vlt_debug_read(VltEngine* e, const char* name, uint32_t* out, uint64_t cap, uint64_t* n) {

@@ -471,7 +471,7 @@ class Draft:
 
 
 class Finish:
-    STOP, LENGTH = 0, 1
+    STOP, LENGTH, FAILED = 0, 1, 2
 
 
 @dataclass
@@ -566,3 +566,111 @@ class Generator:
 
     def set_replay_mistakes(self, rate: float, seed: int) -> None:
         lib().vlt_generator_set_replay_mistakes(self.h, C.c_float(rate), C.c_uint32(seed))
+
+
+class _ReplicaOps(C.Structure):
+    _fields_ = [("ctx", C.c_void_p),
+                ("submit", C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(_Request), C.POINTER(C.c_uint32))),
+                ("step", C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(_Event), C.c_uint32, C.POINTER(C.c_uint32))),
+                ("cancel", C.CFUNCTYPE(None, C.c_void_p, C.c_uint32)),
+                ("is_idle", C.CFUNCTYPE(C.c_int, C.c_void_p)),
+                ("counts", C.CFUNCTYPE(None, C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)))]
+
+
+class Router:
+    """Streams sharded over replicas, a failed replica's streams re-queued on the others (vlt_router_*). `replicas` are
+    Generators of this module, or objects with the same submit / step / cancel / is_idle / counts methods (stand-ins on
+    the host: their step may raise to play a failed replica)."""
+
+    def __init__(self, replicas):
+        self.replicas = list(replicas)
+        self._keep = []
+        ops = (_ReplicaOps * len(self.replicas))()
+        for i, r in enumerate(self.replicas):
+            if isinstance(r, Generator):
+                lib().vlt_replica_of_generator(r.h, C.byref(ops[i]))
+            else:
+                ops[i] = self._wrap(r)
+        self.h = C.c_void_p()
+        _check(lib().vlt_router_new(ops, C.c_uint32(len(self.replicas)), C.byref(self.h)))
+
+    def _wrap(self, rep) -> _ReplicaOps:
+        F = dict(_ReplicaOps._fields_)
+
+        def submit(_ctx, preq, pid):
+            q = preq.contents
+            try:
+                req = Request([q.prompt_tokens[i] for i in range(q.n_prompt)], q.max_tokens, [q.stop[i] for i in range(q.n_stop)],
+                              Sampling(q.sampling.temperature, q.sampling.top_p, q.sampling.seed), q.draft_kind, q.draft_rows, [q.trace[i] for i in range(q.n_trace)])
+                pid[0] = rep.submit(req)
+                return 0
+            except Exception:
+                return 1
+
+        def step(_ctx, pev, cap, pn):
+            try:
+                evs = rep.step()
+            except Exception:
+                return 1
+            for i, e in enumerate(evs[:cap]):
+                pev[i] = _Event(0 if e.kind == "token" else 1, e.req, e.value)
+            pn[0] = min(len(evs), cap)
+            return 0
+
+        def cancel(_ctx, rid):
+            rep.cancel(rid)
+
+        def is_idle(_ctx):
+            return int(rep.is_idle())
+
+        def counts(_ctx, pq, pr):
+            pq[0], pr[0] = rep.counts()
+
+        fns = [F["submit"](submit), F["step"](step), F["cancel"](cancel), F["is_idle"](is_idle), F["counts"](counts)]
+        self._keep.append(fns)
+        return _ReplicaOps(None, *fns)
+
+    def close(self) -> None:
+        if getattr(self, "h", None):
+            lib().vlt_router_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def submit(self, req: Request) -> int:
+        r = _Request()
+        p, st, tr = _u32(req.prompt), _u32(req.stop), _u32(req.trace)
+        r.prompt_kind, r.prompt_tokens, r.n_prompt = 0, _ptr(p), p.size
+        r.max_tokens, r.stop, r.n_stop = req.max_tokens, _ptr(st), st.size
+        r.sampling = req.sampling.c()
+        r.draft_kind, r.draft_rows, r.trace, r.n_trace = req.draft, req.rows, _ptr(tr), tr.size
+        rid = C.c_uint32()
+        _check(lib().vlt_router_submit(self.h, C.byref(r), C.byref(rid)))
+        return rid.value
+
+    def cancel(self, req: int) -> None:
+        lib().vlt_router_cancel(self.h, C.c_uint32(req))
+
+    def step(self) -> list:
+        cap = 8192
+        ev = (_Event * cap)()
+        n = C.c_uint32()
+        _check(lib().vlt_router_step(self.h, ev, C.c_uint32(cap), C.byref(n)))
+        return [Event("token" if ev[i].kind == 0 else "done", ev[i].req, ev[i].value) for i in range(n.value)]
+
+    def is_idle(self) -> bool:
+        return bool(lib().vlt_router_is_idle(self.h))
+
+    def alive(self) -> int:
+        f = lib().vlt_router_alive
+        f.restype = C.c_uint32
+        return int(f(self.h))
+
+    def replica_of(self, req: int) -> int:
+        f = lib().vlt_router_replica_of
+        f.restype = C.c_uint32
+        return int(f(self.h, C.c_uint32(req)))
