@@ -305,6 +305,11 @@ int vlt_debug_set_trace(VltEngine* e, uint32_t slot, const uint32_t* trace, uint
  * the bytes one step uploads and downloads. */
 /* vlt_debug_step then runs the loaded drafter for this many rows after the step (0: not). */
 void vlt_debug_set_draft_rows(VltEngine* e, uint32_t rows);
+/* Queues, on the engine's stream, a small kernel whose wait on a barrier runs out by design (nobody arrives; it gives up
+ * after 1024 polls, sets the device error word and returns -- nothing faults or hangs). Every kernel of a step bounds its
+ * waits the same way; this makes the report testable: the next step collected fails with "a kernel's bounded wait ran
+ * out", and the engine works on afterwards. */
+int vlt_debug_stalled_wait(VltEngine* e);
 /* The next vlt_debug_step replaces the logits its head computed ([head rows][vocab]) and the logits of its drafter's
  * passes ([pass][run][draft vocabulary]) by these (either may be NULL / 0) before the sampler, the acceptance and the
  * drafter's pick read them: the integer tail of a step on inputs identical to the oracle's. One step only. */

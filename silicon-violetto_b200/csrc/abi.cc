@@ -383,6 +383,8 @@ int vlt_debug_step(VltEngine* e, const VltRun* runs, const uint32_t* verify, con
 
 void vlt_debug_set_draft_rows(VltEngine* e, uint32_t rows) { if (e && e->e) e->e->debug_draft_rows = rows; }
 
+int vlt_debug_stalled_wait(VltEngine* e) { return guard([&] { eng(e).debug_stalled_wait(); }); }
+
 int vlt_debug_force_logits(VltEngine* e, const float* logits, uint64_t n_logits, const float* draft_logits, uint64_t n_draft) {
     return guard([&] {
         Engine& en = eng(e);

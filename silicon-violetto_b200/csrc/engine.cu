@@ -734,6 +734,11 @@ double Engine::wait(uint32_t set) {
     return double(ms) * 1e-3;
 }
 
+void Engine::debug_stalled_wait() {
+    if (cfg.host_only) throw Error("this engine was created host-only: it cannot run kernels");
+    launch_stalled_wait(s.err_flag.as<uint32_t>(), 1u << 10, 7u, stream);
+}
+
 // The device error word of a collected step (it came down with the step's results: no copy of its own).
 void Engine::check_device_error(uint32_t set) {
     const StepSet& st = sets[set];

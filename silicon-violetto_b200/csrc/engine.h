@@ -169,6 +169,7 @@ class Engine {
     std::vector<uint32_t> debug_read(const std::string& name);
     void debug_write(const std::string& name, size_t index, const uint32_t* data, size_t n);
     void check_device_error(uint32_t set);
+    void debug_stalled_wait();  // queues a kernel whose bounded wait runs out: the next collected step must report it
 
     // Measurement: two stream marks (GPU time between them), and, while `profile` is on, the GPU
     // time of each kernel group of the queued steps (cuda events around the group's launches).

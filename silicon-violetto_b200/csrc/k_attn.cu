@@ -229,43 +229,48 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, NT <= 3 ? 4 : 3) attn_mma_ker
                     if (!seen) sacc[j][e] = -INFINITY;
                 }
         }
-        // Online softmax: a column's maximum over the page's 16 keys = over its two rows here and the eight
-        // lanes that share t.
+        // Online softmax with a lazy maximum. A column's running maximum m only has to keep 2^(s - m) in range, not to be
+        // the maximum: it is moved (and the sums so far rescaled) only when some score of the page exceeds it by more than
+        // 8 -- one vote per page in place of a shuffle reduction per column -- which after a column's first pages is rare.
+        // Whatever m a partial ends with, (m, l, o) stay consistent (l = sum 2^(s - m), o = sum 2^(s - m) v), so the merge
+        // of warps and of key splits is unchanged. A column's eight lanes (same t) hold the same m: it changes only here,
+        // warp-uniformly, from a maximum reduced over those lanes.
         uint32_t pb[NT][2];  // P^T as B operands: b0 keys 2t, 2t + 1; b1 keys 8 + 2t, 9 + 2t; column g of the n-tile
-        float corr[NT][2];
-        bool rescale = false;
+        bool over = false;
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) over = over || fmaxf(sacc[j][e], sacc[j][e + 2]) > m_run[j][e] + 8.0f;
+        if (__any_sync(0xffffffffu, over)) {
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    float mx = fmaxf(sacc[j][e], sacc[j][e + 2]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    const float m_new = fmaxf(m_run[j][e], mx);
+                    const float corr = fast_exp2(m_run[j][e] - (m_new == -INFINITY ? 0.0f : m_new));  // 0 for a column's first keys, 1 if nothing moved
+                    m_run[j][e] = m_new;
+                    l_run[j][e] *= corr;
+#pragma unroll
+                    for (int dm = 0; dm < 4; dm++) {
+                        oacc[dm][j][e] *= corr;
+                        oacc[dm][j][e + 2] *= corr;
+                    }
+                }
+            }
+        }
 #pragma unroll
         for (int j = 0; j < NT; j++) {
-            float mx[2], m_use[2];
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                mx[e] = fmaxf(sacc[j][e], sacc[j][e + 2]);
-                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 4));
-                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 8));
-                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 16));
-                const float m_new = fmaxf(m_run[j][e], mx[e]);
-                m_use[e] = m_new == -INFINITY ? 0.0f : m_new;
-                corr[j][e] = fast_exp2(m_run[j][e] - m_use[e]);
-                rescale = rescale || corr[j][e] != 1.0f;
-                m_run[j][e] = m_new;
-            }
-            const float p0a = fast_exp2(sacc[j][0] - m_use[0]), p0b = fast_exp2(sacc[j][1] - m_use[1]);  // key g
-            const float p1a = fast_exp2(sacc[j][2] - m_use[0]), p1b = fast_exp2(sacc[j][3] - m_use[1]);  // key g + 8
-            l_run[j][0] = l_run[j][0] * corr[j][0] + (p0a + p1a);
-            l_run[j][1] = l_run[j][1] * corr[j][1] + (p0b + p1b);
+            const float m0 = m_run[j][0] == -INFINITY ? 0.0f : m_run[j][0], m1 = m_run[j][1] == -INFINITY ? 0.0f : m_run[j][1];
+            const float p0a = fast_exp2(sacc[j][0] - m0), p0b = fast_exp2(sacc[j][1] - m1);  // key g
+            const float p1a = fast_exp2(sacc[j][2] - m0), p1b = fast_exp2(sacc[j][3] - m1);  // key g + 8
+            l_run[j][0] += p0a + p1a;
+            l_run[j][1] += p0b + p1b;
             pb[j][0] = movmatrix_trans(pack_bf16(p0a, p0b));
             pb[j][1] = movmatrix_trans(pack_bf16(p1a, p1b));
-        }
-        if (__any_sync(0xffffffffu, rescale)) {  // a maximum moved somewhere in the warp: rare after the first pages
-#pragma unroll
-            for (int dm = 0; dm < 4; dm++)
-#pragma unroll
-                for (int j = 0; j < NT; j++) {
-                    oacc[dm][j][0] *= corr[j][0];
-                    oacc[dm][j][1] *= corr[j][1];
-                    oacc[dm][j][2] *= corr[j][0];
-                    oacc[dm][j][3] *= corr[j][1];
-                }
         }
         // O^T += V^T P^T: m-tile dm = dims 16 dm .. 16 dm + 15, one k step of 16 keys.
 #pragma unroll

@@ -821,6 +821,31 @@ void launch_replay_draft(const RunIn* runs, const uint32_t* lens, uint32_t* feed
     if (n_runs) launch_pdl(replay_draft_kernel, n_runs, FEED_W, 0, s, runs, lens, feed, trace, trace_len, ra, n_runs, tree);
 }
 
+// A wait that runs out, by design of the wait: one warp polls an mbarrier that expects an arrival nobody makes, gives up
+// after `polls` tries -- the same bounded wait every kernel here uses around its copies -- and reports it the same way, in
+// the device error word. Nothing faults or hangs; the kernel returns. Exists so that the reporting path (the error word
+// travelling down with a step's results, the step raising, the engine carrying on) can be tested.
+__global__ void stalled_wait_kernel(uint32_t* err_flag, uint32_t polls, uint32_t code) {
+    __shared__ uint64_t bar;
+    const uint32_t addr = uint32_t(__cvta_generic_to_shared(&bar));
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(1u));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    bool arrived = false;
+    for (uint32_t i = 0; i < polls && !arrived; i++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(addr), "r"(0u) : "memory");
+        arrived = ok != 0;
+    }
+    if (!arrived && threadIdx.x == 0) atomicExch(err_flag, code);
+}
+void launch_stalled_wait(uint32_t* err_flag, uint32_t polls, uint32_t code, cudaStream_t s) {
+    stalled_wait_kernel<<<1, 32, 0, s>>>(err_flag, polls, code);
+    launch_counter()++;
+}
+
 // bench_fill's optional K/V values: small pseudo-random bf16 numbers (a hash of seed, layer,
 // head, position and dim) at positions [from, to) of a slot, so that timing runs read finite data.
 __global__ void kv_fill_kernel(uint16_t* k_cache, uint16_t* v_cache, const uint32_t* __restrict__ page_table, KvArgs kv, uint32_t slot, uint32_t from,

@@ -179,6 +179,8 @@ uint32_t spec_accept_static_max_rows();
 const char* launch_spec_accept_static(const uint16_t* p, const uint16_t* q, const uint32_t* drafts, uint32_t streams, uint32_t k, uint32_t vocab,
                                       float temperature, const uint64_t* seeds, const uint32_t* pos0, uint32_t* accepted, uint32_t* token,
                                       uint32_t* rollback, cudaStream_t s);
+// A kernel whose (bounded) wait runs out on purpose and sets the error word to `code`: for testing how that is reported.
+void launch_stalled_wait(uint32_t* err_flag, uint32_t polls, uint32_t code, cudaStream_t s);
 void launch_kv_fill(uint16_t* k_cache, uint16_t* v_cache, const uint32_t* page_table, KvArgs kv, uint32_t n_layers, uint32_t slot, uint32_t from,
                     uint32_t to, uint32_t seed, cudaStream_t s);
 

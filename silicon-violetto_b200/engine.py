@@ -244,6 +244,10 @@ class Engine:
         """debug_step then runs the loaded drafter for `rows` rows (rows - 1 drafts) after each step; 0: not."""
         lib().vlt_debug_set_draft_rows(self.h, C.c_uint32(rows))
 
+    def debug_stalled_wait(self) -> None:
+        """Queues a kernel whose bounded wait runs out on purpose: the next collected step raises, the engine carries on."""
+        _check(lib().vlt_debug_stalled_wait(self.h))
+
     def force_logits(self, logits=None, draft_logits=None) -> None:
         """The next debug_step's sampler / acceptance / drafter pick read these instead of the logits it computed."""
         a = None if logits is None else np.ascontiguousarray(logits, np.float32)
