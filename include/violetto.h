@@ -279,7 +279,8 @@ uint32_t vlt_router_replica_of(VltRouter* r, uint32_t req_id);
 /* Inspection, for parity tests against the CPU oracle: copies a named engine array into `out`
  * (u32 words: "lens", "feed", "tree", "gen", "path", "path_len", "on_path", "page_table",
  * "free_pages", "tokens", "tin", "vis", "head_rows", "sample_rows", "runs", "out_ids",
- * "emitted", "meta", "tiles"; "attn_split": the last plan's keys per attention split and its split count).
+ * "emitted", "meta", "tiles"; "attn_split": the last plan's keys per attention split and its split count;
+ * "k_cache", "v_cache": the whole pools as bf16 pairs).
  * Returns the word count through n. */
 int vlt_debug_read(VltEngine* e, const char* name, uint32_t* out, uint64_t cap, uint64_t* n);
 /* Plans a step without running it (Engine::plan, engine/src/engine/plan.rs:47-150); works on a host-only engine. */

@@ -65,6 +65,7 @@ void StepSet::init(const EngineConfig& cfg) {
     o_sample_rows = take(hr * sizeof(SampleRow));
     o_tiles = take(2 * (n / 8 + ms + 1) * 4);
     o_runs = take(ms * sizeof(RunIn));
+    o_ctiles = take(2 * (n / 64 + ms + 1) * 4);
     in_bytes = at;
     at = 0;
     o_out_ids = take(hr * 4);
@@ -322,7 +323,7 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
     uint32_t n = 0;
     for (const PlanRun& r : runs) n += r.count;
     if (n == 0 || n > cfg.max_step_tokens) throw Error("step has " + std::to_string(n) + " tokens (max " + std::to_string(cfg.max_step_tokens) + ")");
-    std::vector<uint32_t> tokens, tin, vis, head_rows, hidden_rows, tiles;
+    std::vector<uint32_t> tokens, tin, vis, head_rows, hidden_rows, tiles, ctiles;
     std::vector<SampleRow> samples;
     std::vector<RunIn> run_in;
     uint32_t max_keys = 0, max_count = 0;
@@ -366,6 +367,10 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
             tiles.push_back(first_row + i);
             tiles.push_back(std::min(count - i, 8u));
         }
+        for (uint32_t i = 0; i < count; i += 64) {
+            ctiles.push_back(first_row + i);
+            ctiles.push_back(std::min(count - i, 64u));
+        }
         max_keys = std::max(max_keys, new_len);
         max_count = std::max(max_count, count);
         p.branches = p.branches || (run.verify && count > 2);
@@ -382,12 +387,15 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
     put(st.o_sample_rows, samples.data(), samples.size() * sizeof(SampleRow));
     put(st.o_tiles, tiles.data(), tiles.size() * 4);
     put(st.o_runs, run_in.data(), run_in.size() * sizeof(RunIn));
+    put(st.o_ctiles, ctiles.data(), ctiles.size() * 4);
+    p.ctiles = uint32_t(ctiles.size() / 2);
     p.n = n;
     p.n_head = uint32_t(head_rows.size());
     p.n_hidden = uint32_t(hidden_rows.size());
     p.n_runs = uint32_t(runs.size());
     p.tiles = uint32_t(tiles.size() / 2);
     p.max_run = max_count;
+    p.chunked = max_count > VERIFY_T;
     p.max_keys = max_keys;
     attention_split(p, max_keys, p.tiles);
     last_plan_n = n;
@@ -443,7 +451,7 @@ bool Engine::stream_fits(const Matrix& w) const {
 bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
     const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 16;
     const bool grouped = w.int8 && w.group < w.k;
-    return n >= min_rows && n <= 256 && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
+    return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
 }
 
 void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
@@ -469,8 +477,29 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
     a.ssq_in = ssq_in;
     a.ssq_tiles = ssq_in ? w.k / 128 : 0;
     a.ssq_stride = (cfg.max_step_tokens + 15) / 16 * 16;
-    if (!gemm_supported(a)) throw Error("internal: GEMM asked for an unsupported shape");
-    launch_gemm(a, sm_count, s.err_flag.as<uint32_t>(), stream);
+    // The kernel's N is at most 256 tokens: a longer step (a prompt chunk) goes in blocks of 256, the weights read once per
+    // block (the reference's tiled GEMM loops its token tiles the same way, kernels.metal:319-514). Everything indexed by
+    // token moves along with the block.
+    const uint32_t out_w = epi == EPI_SWIGLU ? w.m / 2 : w.m;
+    for (uint32_t t0 = 0; t0 < n; t0 += 256) {
+        MatArgs b = a;
+        b.n = std::min(256u, n - t0);
+        b.Xb = xb + size_t(t0) * w.k;
+        b.Y = y ? y + size_t(t0) * out_w : nullptr;
+        b.Yb = yb ? yb + size_t(t0) * out_w : nullptr;
+        b.base = base ? base + size_t(t0) * out_w : nullptr;
+        b.inv_in = inv ? inv + t0 : nullptr;
+        b.ssq_out = ssq_out ? ssq_out + t0 : nullptr;
+        b.ssq_in = ssq_in ? ssq_in + t0 : nullptr;
+        if (q) {
+            b.q.meta = q->meta + 2 * size_t(t0);
+            b.q.tin = q->tin + 2 * size_t(t0);
+            b.q.cpos = q->cpos ? q->cpos + t0 : nullptr;
+            b.q.q_b = q->q_b + size_t(t0) * q->n_heads * model.md.hd;
+        }
+        if (!gemm_supported(b)) throw Error("internal: GEMM asked for an unsupported shape");
+        launch_gemm(b, sm_count, s.err_flag.as<uint32_t>(), stream);
+    }
 }
 
 // engine/src/engine/encode.rs:142-192 `encode_layer`, a plain decoder's.
@@ -485,6 +514,8 @@ void Engine::encode_layer(uint32_t set, const Plan& p, uint32_t li, bool capture
     io.tiles = st.in<uint32_t>(st.o_tiles);
     io.vis = st.in<uint32_t>(st.o_vis);
     io.n_tiles = p.tiles;
+    io.ctiles = st.in<uint32_t>(st.o_ctiles);
+    io.n_ctiles = p.chunked ? p.ctiles : 0;
     io.k_cache = kv.k.as<uint16_t>();
     io.v_cache = kv.v.as<uint16_t>();
     io.maps = &attn_maps;
@@ -564,6 +595,26 @@ void Engine::encode_layer_io(const LayerIO& io, bool capture) {
             launch_attn_plain(s.qkv.as<float>(), io.meta, io.tiles, io.vis, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva,
                               li, io.n_tiles, md.n_heads, scale_log2, s.attn.as<float>(), stream);
         if (big) launch_prep_rows(s.attn.as<float>(), nullptr, n, md.n_heads * md.hd, md.eps, nullptr, s.attn_b.as<uint16_t>(), nullptr, false, false, stream);
+    } else if (io.n_ctiles) {
+        // A step with a prompt chunk: rows as the MMA's M side, the keys read once per 64 rows, no key split and no merge.
+        ChunkAttnArgs c{};
+        c.maps = io.maps;
+        c.err_flag = s.err_flag.as<uint32_t>();
+        c.q_b = s.q_b.as<uint16_t>();
+        c.meta = io.meta;
+        c.tin = io.tin;
+        c.ctiles = io.ctiles;
+        c.vis = io.vis;
+        c.page_table = kv.page_table.as<uint32_t>();
+        c.kv = kva;
+        c.layer = li;
+        c.n_ctiles = io.n_ctiles;
+        c.n_heads = md.n_heads;
+        c.out = s.attn.as<float>();
+        c.out_b = s.attn_b.as<uint16_t>();
+        sp = span_begin(G_ATTN);
+        if (!(skip & 4)) launch_attn_chunk(c, stream);
+        span_end(sp);
     } else {
         AttnArgs a{};
         a.maps = io.maps;
@@ -862,6 +913,8 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.tiles = st.in<uint32_t>(st.o_tiles);
     io.vis = st.in<uint32_t>(st.o_vis);
     io.n_tiles = p.tiles;
+    io.ctiles = st.in<uint32_t>(st.o_ctiles);
+    io.n_ctiles = p.chunked ? p.ctiles : 0;
     io.cpos = dr.cpos.as<uint32_t>();
     io.keys_per_split = p.keys_per_split;
     io.max_splits = p.max_splits;
@@ -877,6 +930,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.tiles = dr.dtiles.as<uint32_t>();
     io.vis = dr.dvis.as<uint32_t>();
     io.n_tiles = nr;
+    io.n_ctiles = 0;
     io.cpos = dr.dcpos.as<uint32_t>();
     io.keys_per_split = dp.keys_per_split;
     io.max_splits = dp.max_splits;
@@ -1198,6 +1252,8 @@ std::vector<uint32_t> Engine::debug_read(const std::string& name) {
     if (name == "page_table") return whole(kv.page_table, ms * kv.max_pages);
     if (name == "free_pages") return kv.free_pages;
     if (name == "attn_split") return {last_split[0], last_split[1]};
+    if (name == "k_cache") return whole(kv.k, kv.k.bytes / 4);  // bf16 pairs; small pools only
+    if (name == "v_cache") return whole(kv.v, kv.v.bytes / 4);
     if (drafter) {
         const size_t pool = size_t(kv.n_pages) * model.md.n_kv * kv.page * model.md.hd;
         if (name == "draft_logits") return whole(drafter->logits, size_t(VERIFY_T - 1) * ms * drafter->v);  // [pass][run slot][v] f32

@@ -52,6 +52,8 @@ struct PlanRun {
 struct Plan {
     uint32_t n = 0, n_head = 0, n_hidden = 0, n_runs = 0, tiles = 0, max_run = 0;
     bool branches = false;
+    uint32_t ctiles = 0;   // chunk tiles of at most 64 rows (the prefill attention's blocks)
+    bool chunked = false;  // some run is longer than VERIFY_T rows: the step's attention is the chunk kernel (encode.rs:299-355)
     uint32_t keys_per_split = 0, max_splits = 1;  // the attention's key split
     uint32_t max_keys = 0;                        // the longest run's keys
 };
@@ -79,7 +81,7 @@ struct StepSet {
     uint8_t* host_in = nullptr;   // pinned
     uint8_t* host_out = nullptr;  // pinned
     size_t in_bytes = 0, out_bytes = 0;
-    size_t o_tokens = 0, o_tin = 0, o_vis = 0, o_head_rows = 0, o_hidden_rows = 0, o_sample_rows = 0, o_tiles = 0, o_runs = 0;  // byte offsets in *_in
+    size_t o_tokens = 0, o_tin = 0, o_vis = 0, o_head_rows = 0, o_hidden_rows = 0, o_sample_rows = 0, o_tiles = 0, o_runs = 0, o_ctiles = 0;  // byte offsets in *_in
     size_t o_out_ids = 0, o_emitted = 0, o_err = 0;  // in *_out; o_err: the device error word as it stood when the step ended
     cudaEvent_t start = nullptr, done = nullptr;        // around the step on the engine's stream / after its results reached the host
     cudaEvent_t uploaded = nullptr, computed = nullptr;  // the step's inputs are on the device / its last kernel has run
@@ -233,6 +235,8 @@ class Engine {
         const Layer* l;
         uint32_t n, n_tiles, layer, keys_per_split, max_splits, max_rows;  // max_rows: the longest tile's rows
         const uint32_t *meta, *tin, *tiles, *vis;
+        const uint32_t* ctiles;  // chunk tiles, if the step's attention is the chunk kernel (n_ctiles > 0)
+        uint32_t n_ctiles;
         bool h_ready;          // the GEMM before this layer left bf16(h) in h_b and its sums of squares in ssq: no row pass before qkv
         const uint32_t* cpos;  // optional, per token: the cache position its K/V go to (NO_TOK: nowhere); NULL: its run's first position + its row
         uint16_t *k_cache, *v_cache;

@@ -493,7 +493,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ M
                 if (t < a.m.n) {
                     const uint32_t slot = qe.meta[2 * t], row = qe.tin[2 * t + 1];
                     pos = qe.meta[2 * t + 1];
-                    const uint32_t cp = qe.cpos ? qe.cpos[t] : qe.meta[2 * (t - row) + 1] + row;  // kernels.metal:74-77 `cache_pos`
+                    // (the run's first token may lie before this launch's block of tokens: a signed index)
+                    const uint32_t cp = qe.cpos ? qe.cpos[t] : qe.meta[2 * (int(t) - int(row)) + 1] + row;  // kernels.metal:74-77 `cache_pos`
                     if (cp != NO_TOK) {
                         const uint32_t page = qe.page_table[size_t(slot) * qe.kv.max_pages + (cp >> qe.kv.page_shift)], psize = 1u << qe.kv.page_shift;
                         kvrow = ((qe.layer * qe.kv.n_pages + page) * qe.kv.n_kv) * psize + (cp & (psize - 1));

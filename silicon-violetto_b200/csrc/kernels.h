@@ -96,6 +96,24 @@ constexpr uint32_t ATTN_PART = 68;  // floats per partial: m, l, 2 pad, o[64]
 void launch_attn_mma(const AttnArgs& a, cudaStream_t s);
 void launch_attn_combine(const AttnArgs& a, cudaStream_t s);
 
+// Chunk (prefill) attention, k_prefill.cu: blocks of 64 rows of one run x one query head over all the keys the rows see,
+// no key split; writes the normalised rows (fp32 and, optionally, bf16).
+struct ChunkAttnArgs {
+    const AttnMaps* maps;  // host pointer
+    uint32_t* err_flag;
+    const uint16_t* q_b;  // [token][head][64] bf16, rotated and scaled
+    const uint32_t* meta;
+    const uint32_t* tin;
+    const uint32_t* ctiles;  // (first token, rows <= 64) per chunk tile, never across runs
+    const uint32_t* vis;
+    const uint32_t* page_table;
+    KvArgs kv;
+    uint32_t layer, n_ctiles, n_heads;
+    float* out;
+    uint16_t* out_b;
+};
+void launch_attn_chunk(const ChunkAttnArgs& a, cudaStream_t s);
+
 // The chain drafter's own kernels (k_draft.cu): inputs of the catch-up pass and of a draft pass, the
 // carried tap, and the argmax pick into feed / tree.
 void launch_draft_catchup_in(const uint32_t* tokens, const uint32_t* tin, const uint32_t* meta, const uint32_t* on_path, const float* taps, const float* carry,

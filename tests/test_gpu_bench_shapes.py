@@ -160,7 +160,6 @@ def _agree_at_scale(prod, orc, runs, tol):
     return err, rms
 
 
-@pytest.mark.parametrize("filled", [True, False], ids=["filled-contexts", "empty-sequences"])
 def _same_but_feed(prod, orc, n_runs, n_tokens):
     """Every integer of the step's state but `feed`, whose first entry per slot is a greedy token: that one is compared
     where the oracle's margin is clear (inside _agree_at_scale), and the product is put on the oracle's token for the next step."""
@@ -168,6 +167,7 @@ def _same_but_feed(prod, orc, n_runs, n_tokens):
     prod.debug_write("feed", 0, orc.array("feed"))
 
 
+@pytest.mark.parametrize("filled", [True, False], ids=["filled-contexts", "empty-sequences"])
 def test_one_layer_at_the_1b_dimensions_matches_the_oracle(one_layer_1b, filled):
     """32 sequences, with 600 to 900 filled positions each (a short version of the benchmark's contexts; several key
     splits) or empty (every row attends to at most 14 keys, where the bf16 rounding of the attention's probabilities in the
