@@ -58,7 +58,7 @@ typedef struct {
     uint32_t spec_policy_off;   /* 1: rows as requested (the reference's spec_tokens = 0) */
     uint32_t sm_count;          /* SMs to size grids for; 0: the device's */
     uint32_t attn_keys_per_cta; /* keys one attention CTA takes; 0: sized to fill the SMs */
-    uint32_t gemm_min_rows;     /* steps with at least this many tokens use the tensor-core GEMM; 0: default */
+    uint32_t gemm_min_rows;     /* steps with at least this many tokens use the tensor-core GEMM; 0: default (9) */
     uint32_t plain_attention;   /* 1: the scalar attention kernel (cross-check only) */
 } VltTuning;
 

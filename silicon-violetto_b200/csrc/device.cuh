@@ -64,6 +64,30 @@ __device__ __forceinline__ float soft_exp2(float x) {
     return __int_as_float(__float_as_int(p) + (n << 23));
 }
 
+// Two at once, on the packed fp32 instructions of sm_100 (add / mul / fma .f32x2: each half is the scalar IEEE operation, so
+// each half's result is soft_exp2's, bit for bit). The samplers are bound by instruction issue, and this is most of it.
+__device__ __forceinline__ float2 soft_exp2_x2(float2 x) {
+    const bool zero0 = !(x.x > -125.5f), zero1 = !(x.y > -125.5f);
+    x.x = fminf(x.x, 126.0f);
+    x.y = fminf(x.y, 126.0f);
+    const float2 magic = make_float2(12582912.0f, 12582912.0f), minus_magic = make_float2(-12582912.0f, -12582912.0f), minus_one = make_float2(-1.0f, -1.0f);
+    const float2 t = __fadd2_rn(x, magic);
+    const int n0 = __float_as_int(t.x) - 0x4B400000, n1 = __float_as_int(t.y) - 0x4B400000;
+    const float2 f = __ffma2_rn(__fadd2_rn(t, minus_magic), minus_one, x);  // x - (t - magic): the product by -1 is exact, one rounding as in the subtraction
+    float2 p = make_float2(0.00015403530393381608f, 0.00015403530393381608f);
+    p = __ffma2_rn(p, f, make_float2(0.0013333558146428443f, 0.0013333558146428443f));
+    p = __ffma2_rn(p, f, make_float2(0.009618129107628477f, 0.009618129107628477f));
+    p = __ffma2_rn(p, f, make_float2(0.05550410866482158f, 0.05550410866482158f));
+    p = __ffma2_rn(p, f, make_float2(0.2402265069591007f, 0.2402265069591007f));
+    p = __ffma2_rn(p, f, make_float2(0.6931471805599453f, 0.6931471805599453f));
+    p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
+    return make_float2(zero0 ? 0.0f : __int_as_float(__float_as_int(p.x) + (n0 << 23)), zero1 ? 0.0f : __int_as_float(__float_as_int(p.y) + (n1 << 23)));
+}
+// e(x) = 2^((x - mx) c) for two logits, as the scalar soft_exp2(__fmul_rn(__fsub_rn(x, mx), c)) twice.
+__device__ __forceinline__ float2 soft_exp2_scaled_x2(float x0, float x1, float mx, float c) {
+    return soft_exp2_x2(__fmul2_rn(__fadd2_rn(make_float2(x0, x1), make_float2(-mx, -mx)), make_float2(c, c)));
+}
+
 constexpr float LOG2E = 1.44269504088896340736f;
 
 // kernels.metal:64-72.

@@ -447,9 +447,9 @@ bool Engine::stream_fits(const Matrix& w) const {
 }
 
 // The matmul variant by step size (the reference's Matmul::for_tokens, encode.rs:33-44): the
-// tcgen05 GEMM from gemm_min_rows tokens (default 16), the streamed kernel below.
+// tcgen05 GEMM from gemm_min_rows tokens (default 9), the streamed kernel below.
 bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
-    const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 16;
+    const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 9;  // up to 8 tokens the streamed kernel; 9..15 would take it twice over the weights
     const bool grouped = w.int8 && w.group < w.k;
     return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
 }
@@ -585,11 +585,13 @@ void Engine::encode_layer_io(const LayerIO& io, bool capture) {
         if (capture) launch_qkv_capture(s.qkv.as<float>(), io.meta, rope_tab.as<float>(), n, md.n_heads, kva, cap->qkv.as<float>(), stream);
     }
     span_end(sp);
+    if (io.kv_only && fused_post && !capture) return;
     sp = span_begin(G_SMALL);
     if (!(skip & 2) && !fused_post)
         launch_qkv_post(s.qkv.as<float>(), io.meta, io.tin, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva, li, n,
                         md.n_heads, scale_log2, tuning.plain_attention ? nullptr : s.q_b.as<uint16_t>(), io.cpos, stream);
     span_end(sp);
+    if (io.kv_only && !capture) return;
     if (tuning.plain_attention) {
         if (!(skip & 4))
             launch_attn_plain(s.qkv.as<float>(), io.meta, io.tiles, io.vis, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva,
@@ -903,7 +905,9 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.k_cache = dr.k.as<uint16_t>();
     io.v_cache = dr.v_cache.as<uint16_t>();
     io.maps = &dr.maps;
-    // (1) catch-up, on the step's own layout.
+    // (1) catch-up, on the step's own layout. Only its K/V matter (the passes below take their features from the target's
+    // taps, not from this pass's output), and a one-layer drafter's K/V depend on fc and the qkv projection alone: the
+    // pass stops there, without attention, o projection or MLP.
     launch_draft_catchup_in(st.in<uint32_t>(st.o_tokens), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), last_tap(),
                             dr.carry.as<float>(), model.embed, n, d, x, xb, dr.cpos.as<uint32_t>(), stream);
     fc(n);
@@ -919,7 +923,9 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.keys_per_split = p.keys_per_split;
     io.max_splits = p.max_splits;
     io.max_rows = std::min(p.max_run, VERIFY_T);
+    io.kv_only = true;
     encode_layer_io(io);
+    io.kv_only = false;
     // (2) the draft passes, one row per run.
     Plan dp;
     dp.n = nr;

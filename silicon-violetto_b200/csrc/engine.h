@@ -237,6 +237,7 @@ class Engine {
         const uint32_t *meta, *tin, *tiles, *vis;
         const uint32_t* ctiles;  // chunk tiles, if the step's attention is the chunk kernel (n_ctiles > 0)
         uint32_t n_ctiles;
+        bool kv_only;          // stop after the qkv projection has written K/V into the cache (the drafter's catch-up pass: a one-layer drafter's K/V depend on nothing after it)
         bool h_ready;          // the GEMM before this layer left bf16(h) in h_b and its sums of squares in ssq: no row pass before qkv
         const uint32_t* cpos;  // optional, per token: the cache position its K/V go to (NO_TOK: nowhere); NULL: its run's first position + its row
         uint16_t *k_cache, *v_cache;

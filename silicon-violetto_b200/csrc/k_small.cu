@@ -4,6 +4,7 @@
 #include <cfloat>
 
 #include "kernels.h"
+#include "sampling.cuh"
 
 namespace vlt {
 
@@ -342,9 +343,7 @@ void launch_prep_rows(const float* in, const uint32_t* rows, uint32_t n, uint32_
 // by inverting the CDF of e_i = 2^((x_i - max) log2(e) / T) over a fixed order: thread t of
 // 1024 owns ids t, t + 1024, ...; threads in turn. Every float operation below is a single IEEE
 // operation in a fixed order, so the token is a pure function of (logit bits, seed, position).
-constexpr uint32_t SAMPLE_THREADS = 1024;
 constexpr uint32_t SAMPLE_ROUNDS = 8;
-__device__ __forceinline__ uint32_t ex_at(uint32_t t) { return t + t / 32; }
 
 // kernels.metal:1482-1501 `tg_scan`: ex[ex_at(t)] = sum of v over threads before t,
 // ex[ex_at(1024)] = the total; 32 groups of 32 threads summed left to right, then the groups.
@@ -417,7 +416,10 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 #pragma unroll
             for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
 #pragma unroll
-            for (uint32_t k = 0; k < B; k++) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+            for (uint32_t k = 0; k < B; k += 2) {  // the exponentials two at a time, the additions in id order
+                const float2 e = soft_exp2_scaled_x2(v[k], v[k + 1], lmax, c);
+                s = __fadd_rn(__fadd_rn(s, e.x), e.y);
+            }
         }
         for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(x[i], lmax), c)));
         tg_scan(s, ex, base, tid);
@@ -471,8 +473,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 #pragma unroll
                 for (uint32_t k = 0; k < B; k++) v[k] = x[i0 + k * SAMPLE_THREADS];
 #pragma unroll
-                for (uint32_t k = 0; k < B; k++)
-                    if (v[k] > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+                for (uint32_t k = 0; k < B; k += 2) {
+                    const float2 e = soft_exp2_scaled_x2(v[k], v[k + 1], lmax, c);
+                    if (v[k] > xj) q = __fadd_rn(q, e.x);
+                    if (v[k + 1] > xj) q = __fadd_rn(q, e.y);
+                }
             }
             for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) {
                 const float xi = x[i];
@@ -492,59 +497,6 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 // over the logits run on eight SMs instead of one. What one block needs from the others -- the best
 // (value, id) pairs, the group totals, the picked id -- crosses distributed shared memory around a cluster
 // barrier. Every block of a cluster takes the same branches (they hold the same values).
-constexpr uint32_t SC_CTAS = 8, SC_THREADS = SAMPLE_THREADS / SC_CTAS, SC_WARPS = SC_THREADS / 32;
-__device__ __forceinline__ void sc_cluster_sync() { asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ uint32_t sc_remote(const void* p, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(uint32_t(__cvta_generic_to_shared(p))), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ uint32_t sc_ld_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-
-struct ScExchange {
-    float tot[2][SC_WARPS];  // this block's group totals, double-buffered by scan
-    uint32_t pick[2];        // the id a thread of this block picked (NO_TOK: none), double-buffered by round
-    float bv;                // this block's best logit and its id
-    uint32_t bi;
-};
-
-// tg_scan over the cluster. v: this thread's sum. Returns ex[t] (lo), ex[t + 1] (hi) and ex[1024] (total).
-__device__ void sc_scan(float v, uint32_t buf, ScExchange* xc, float* vals, float* pre, float* tot_all, float* base, uint32_t rank, uint32_t tid, float& lo,
-                        float& hi, float& total) {
-    const uint32_t lane = tid % 32, warp = tid / 32;
-    vals[tid] = v;
-    __syncthreads();
-    if (tid < SC_WARPS) {  // a group's exclusive prefixes, left to right from 0
-        float acc = 0.0f;
-        for (uint32_t i = 32 * tid; i < 32 * tid + 32; i++) {
-            pre[i] = acc;
-            acc = __fadd_rn(acc, vals[i]);
-        }
-        xc->tot[buf][tid] = acc;
-    }
-    sc_cluster_sync();
-    if (tid < 32) tot_all[tid] = __uint_as_float(sc_ld_u32(sc_remote(&xc->tot[buf][tid % SC_WARPS], tid / SC_WARPS)));
-    __syncthreads();
-    if (tid == 0) {  // the group totals scanned left to right from 0
-        float acc = 0.0f;
-        for (uint32_t g = 0; g < 32; g++) {
-            base[g] = acc;
-            acc = __fadd_rn(acc, tot_all[g]);
-        }
-        base[32] = acc;
-    }
-    __syncthreads();
-    const uint32_t group = rank * SC_WARPS + warp;
-    lo = __fadd_rn(pre[tid], base[group]);
-    hi = __shfl_down_sync(0xffffffffu, lo, 1);
-    if (lane == 31) hi = base[group + 1];
-    total = base[32];
-}
-
 // STAGED: the first pass leaves this block's share of the row in shared memory ([id / 1024][thread], 512 bytes per 1024
 // ids) and the later passes -- above all the one thread that walks its ids one by one to find the token -- read it there
 // instead of waiting for L2 at every step.
@@ -618,7 +570,10 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
 #pragma unroll
             for (uint32_t k = 0; k < B; k++) v[k] = own(i0 + k * SAMPLE_THREADS);
 #pragma unroll
-            for (uint32_t k = 0; k < B; k++) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+            for (uint32_t k = 0; k < B; k += 2) {
+                const float2 e = soft_exp2_scaled_x2(v[k], v[k + 1], lmax, c);
+                sum = __fadd_rn(__fadd_rn(sum, e.x), e.y);
+            }
         }
         for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) sum = __fadd_rn(sum, soft_exp2(__fmul_rn(__fsub_rn(own(i), lmax), c)));
         float lo, hi, total;
@@ -676,8 +631,11 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) sa
 #pragma unroll
                 for (uint32_t k = 0; k < B; k++) v[k] = own(i0 + k * SAMPLE_THREADS);
 #pragma unroll
-                for (uint32_t k = 0; k < B; k++)
-                    if (v[k] > xj) q = __fadd_rn(q, soft_exp2(__fmul_rn(__fsub_rn(v[k], lmax), c)));
+                for (uint32_t k = 0; k < B; k += 2) {
+                    const float2 e = soft_exp2_scaled_x2(v[k], v[k + 1], lmax, c);
+                    if (v[k] > xj) q = __fadd_rn(q, e.x);
+                    if (v[k + 1] > xj) q = __fadd_rn(q, e.y);
+                }
             }
             for (uint32_t i = i0; i < vocab; i += SAMPLE_THREADS) {
                 const float xi = own(i);

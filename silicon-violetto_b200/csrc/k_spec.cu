@@ -11,13 +11,14 @@
 //   inverse CDF at uniform01(seed, pos0 + i, 1); with all accepted, the bonus token from p_k at
 //   uniform01(seed, pos0 + k, 0). Outputs: accepted count, that token, rollback = k - accepted.
 // Two kernels: per-row statistics (max, argmax, Z) for all S (2k + 1) rows at once -- one pass
-// over the logits from HBM -- then one block per stream that decides and draws (its two rows
+// over the logits from HBM -- then a cluster of 8 blocks per stream that decides and draws (its two rows
 // come from L2).
 #include <cfloat>
 #include <cmath>
 #include <mutex>
 
 #include "kernels.h"
+#include "sampling.cuh"
 
 namespace vlt {
 
@@ -70,7 +71,17 @@ __global__ void __launch_bounds__(THREADS) stats_kernel(const uint16_t* __restri
     const uint16_t* x = r < p_rows ? p + size_t(r) * vocab : q + size_t(r - p_rows) * vocab;
     float mx = -FLT_MAX;
     uint32_t am = 0xffffffffu;
-    for (uint32_t i = tid; i < vocab; i += THREADS) better(mx, am, bf16_to_f32(x[i]), i);
+    {
+        uint32_t i0 = tid;
+        for (; i0 + 7 * THREADS < vocab; i0 += 8 * THREADS) {
+            uint16_t v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = x[i0 + u * THREADS];
+#pragma unroll
+            for (int u = 0; u < 8; u++) better(mx, am, bf16_to_f32(v[u]), i0 + u * THREADS);
+        }
+        for (; i0 < vocab; i0 += THREADS) better(mx, am, bf16_to_f32(x[i0]), i0);
+    }
     warp_best(mx, am);
     if (lane == 0) { bvs[tid / 32] = mx; bis[tid / 32] = am; }
     __syncthreads();
@@ -78,7 +89,15 @@ __global__ void __launch_bounds__(THREADS) stats_kernel(const uint16_t* __restri
     am = bis[0];
     for (uint32_t i = 1; i < 32; i++) better(mx, am, bvs[i], bis[i]);
     float s = 0.0f;
-    for (uint32_t i = tid; i < vocab; i += THREADS) s = __fadd_rn(s, e_of(x[i], mx, c));
+    uint32_t i0 = tid;
+    for (; i0 + 7 * THREADS < vocab; i0 += 8 * THREADS) {  // eight loads in flight, the additions in id order
+        uint16_t v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = x[i0 + u * THREADS];
+#pragma unroll
+        for (int u = 0; u < 8; u++) s = __fadd_rn(s, e_of(v[u], mx, c));
+    }
+    for (; i0 < vocab; i0 += THREADS) s = __fadd_rn(s, e_of(x[i0], mx, c));
     tg_scan(s, ex, base, tid);
     if (tid == 0) out[r] = RowStats{mx, am, ex[ex_at(THREADS)], 0};
 }
@@ -126,21 +145,26 @@ __device__ uint32_t inverse_cdf(uint32_t vocab, W w, float u, uint32_t fallback,
     return j == 0xffffffffu ? fallback : j;
 }
 
-// One block per stream.
-__global__ void __launch_bounds__(THREADS) decide_kernel(const uint16_t* __restrict__ p, const uint16_t* __restrict__ q, const uint32_t* __restrict__ drafts,
-                                                         const RowStats* __restrict__ stats, uint32_t streams, uint32_t k, uint32_t vocab, float c,
-                                                         const uint64_t* __restrict__ seeds, const uint32_t* __restrict__ pos0, uint32_t* accepted,
-                                                         uint32_t* token, uint32_t* rollback) {
-    __shared__ float ex[THREADS + THREADS / 32 + 1];
-    __shared__ float base[32];
-    __shared__ uint32_t pick, first_reject;
-    const uint32_t s = blockIdx.x, tid = threadIdx.x;
+// The decision, a cluster of 8 blocks per stream: the 1024 "threads" of the sampler's order are the cluster's 8 x 128 (as
+// in the sampler's cluster form), so every sum keeps its order and association while a stream's pass over its two rows
+// runs on eight SMs (one block per stream left 116 of 148 SMs idle at 32 streams).
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) decide_cluster_kernel(const uint16_t* __restrict__ p, const uint16_t* __restrict__ q,
+                                                                                                 const uint32_t* __restrict__ drafts, const RowStats* __restrict__ stats,
+                                                                                                 uint32_t streams, uint32_t k, uint32_t vocab, float c,
+                                                                                                 const uint64_t* __restrict__ seeds, const uint32_t* __restrict__ pos0,
+                                                                                                 uint32_t* accepted, uint32_t* token, uint32_t* rollback) {
+    __shared__ ScExchange xc;
+    __shared__ float vals[SC_THREADS], pre[SC_THREADS], tot_all[32], base[33];
+    __shared__ uint32_t first_reject;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const uint32_t s = blockIdx.x / SC_CTAS, tid = threadIdx.x;
     const uint32_t seed_lo = uint32_t(seeds[s]), seed_hi = uint32_t(seeds[s] >> 32);
     const RowStats* ps = stats + size_t(s) * (k + 1);
     const RowStats* qs = stats + size_t(streams) * (k + 1) + size_t(s) * k;
     const uint16_t* pp = p + size_t(s) * (k + 1) * vocab;
     const uint16_t* qq = q + size_t(s) * k * vocab;
-    if (tid == 0) {
+    if (tid == 0) {  // every block runs the few tests itself: cheaper than sending the result round
         uint32_t i = 0;
         for (; i < k; i++) {
             const uint32_t x = drafts[s * k + i];
@@ -150,6 +174,8 @@ __global__ void __launch_bounds__(THREADS) decide_kernel(const uint16_t* __restr
             if (!(lhs < rhs)) break;
         }
         first_reject = i;
+        xc.pick[0] = 0xffffffffu;
+        xc.pick[1] = 0xffffffffu;
     }
     __syncthreads();
     const uint32_t i = first_reject;
@@ -163,18 +189,19 @@ __global__ void __launch_bounds__(THREADS) decide_kernel(const uint16_t* __restr
             const float d = __fsub_rn(a, b);
             return d > 0.0f ? d : 0.0f;
         };
-        tok = inverse_cdf(vocab, resid, uniform01(seed_lo, seed_hi, pos0[s] + i, 1), ps[i].argmax, ex, base, &pick, tid);
+        tok = sc_inverse_cdf(vocab, resid, uniform01(seed_lo, seed_hi, pos0[s] + i, 1), ps[i].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
     } else {
         const uint16_t* pk = pp + size_t(k) * vocab;
         const float pm = ps[k].max;
         auto w = [&](uint32_t j) { return e_of(pk[j], pm, c); };
-        tok = inverse_cdf(vocab, w, uniform01(seed_lo, seed_hi, pos0[s] + k, 0), ps[k].argmax, ex, base, &pick, tid);
+        tok = sc_inverse_cdf(vocab, w, uniform01(seed_lo, seed_hi, pos0[s] + k, 0), ps[k].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
     }
-    if (tid == 0) {
+    if (rank == 0 && tid == 0) {
         accepted[s] = i;
         token[s] = tok;
         rollback[s] = k - i;
     }
+    sc_cluster_sync();  // nobody leaves while another block may still read its shared memory
 }
 
 }  // namespace spec
@@ -185,8 +212,8 @@ void launch_spec_accept(const uint16_t* p, const uint16_t* q, const uint32_t* dr
     const float c = LOG2E / temperature;  // the same IEEE division as the device's __fdiv_rn
     spec::stats_kernel<<<streams * (2 * k + 1), spec::THREADS, 0, s>>>(p, q, streams * (k + 1), vocab, c, static_cast<spec::RowStats*>(stats));
     launch_counter()++;
-    spec::decide_kernel<<<streams, spec::THREADS, 0, s>>>(p, q, drafts, static_cast<const spec::RowStats*>(stats), streams, k, vocab, c, seeds, pos0, accepted,
-                                                          token, rollback);
+    spec::decide_cluster_kernel<<<streams * SC_CTAS, SC_THREADS, 0, s>>>(p, q, drafts, static_cast<const spec::RowStats*>(stats), streams, k, vocab, c, seeds, pos0,
+                                                                        accepted, token, rollback);
     launch_counter()++;
 }
 
@@ -256,26 +283,37 @@ __global__ void __launch_bounds__(THREADS) step_stats_kernel(const SpecStepArgs 
     am = bis[0];
     for (uint32_t i = 1; i < 32; i++) better(mx, am, bvs[i], bis[i]);
     float s = 0.0f;
-    for (uint32_t i = tid; i < n; i += THREADS) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(x[i], mx), c)));
+    uint32_t i0 = tid;
+    for (; i0 + 7 * THREADS < n; i0 += 8 * THREADS) {  // eight loads in flight, the additions in id order
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = x[i0 + u * THREADS];
+#pragma unroll
+        for (int u = 0; u < 8; u++) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(v[u], mx), c)));
+    }
+    for (; i0 < n; i0 += THREADS) s = __fadd_rn(s, soft_exp2(__fmul_rn(__fsub_rn(x[i0], mx), c)));
     tg_scan(s, ex, base, tid);
     if (tid == 0) *out = RowStats{mx, am, ex[ex_at(THREADS)], 0};
 }
 
-// One block per run: the tests in order (one thread), then the replacement or the bonus token (the block).
-__global__ void __launch_bounds__(THREADS) step_decide_kernel(const SpecStepArgs a) {
+// A cluster of 8 blocks per run (the sampler's 1024 threads, see decide_cluster_kernel): the tests in order (one thread
+// of every block), then the replacement or the bonus token (the cluster).
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) step_decide_kernel(const SpecStepArgs a) {
     pdl_start();
-    __shared__ float ex[THREADS + THREADS / 32 + 1];
-    __shared__ float base[32];
-    __shared__ uint32_t pick, first_reject;
-    const uint32_t r = blockIdx.x, tid = threadIdx.x;
+    __shared__ ScExchange xc;
+    __shared__ float vals[SC_THREADS], pre[SC_THREADS], tot_all[32], base[33];
+    __shared__ uint32_t first_reject;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const uint32_t r = blockIdx.x / SC_CTAS, tid = threadIdx.x;
     const RunIn ru = a.runs[r];
     const bool on = step_applies(a, r);
-    __syncthreads();  // every thread has read q_rows
-    if (tid == 0) {
+    sc_cluster_sync();  // every thread of the cluster has read q_rows
+    if (rank == 0 && tid == 0) {
         a.q_rows[ru.slot] = 0;  // a slot's kept rows serve one step
         if (!on) a.spec_e[r] = 0;
     }
-    if (!on) return;
+    if (!on) return;  // the whole cluster leaves: no further cluster barrier
     const SampleRow sr = a.samples[ru.head0];
     const float c = __fdiv_rn(LOG2E, sr.temperature);
     const RowStats* ps = a.stats + ru.head0;
@@ -294,6 +332,8 @@ __global__ void __launch_bounds__(THREADS) step_decide_kernel(const SpecStepArgs
             if (!(lhs < rhs)) break;
         }
         first_reject = i;
+        xc.pick[0] = 0xffffffffu;
+        xc.pick[1] = 0xffffffffu;
     }
     __syncthreads();
     const uint32_t i = first_reject;
@@ -309,18 +349,19 @@ __global__ void __launch_bounds__(THREADS) step_decide_kernel(const SpecStepArgs
             const float d = __fsub_rn(ea, eb);
             return d > 0.0f ? d : 0.0f;
         };
-        tok = inverse_cdf(a.vocab, resid, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 1), ps[i - 1].argmax, ex, base, &pick, tid);
+        tok = sc_inverse_cdf(a.vocab, resid, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 1), ps[i - 1].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
     } else {
         const float* pk = pp + size_t(ru.count - 1) * a.vocab;
         const float pm = ps[ru.count - 1].max;
         auto w = [&](uint32_t j) { return e_of(pk[j], pm); };
-        tok = inverse_cdf(a.vocab, w, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + ru.count - 1) + 1] + 1, 0), ps[ru.count - 1].argmax, ex, base, &pick, tid);
+        tok = sc_inverse_cdf(a.vocab, w, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + ru.count - 1) + 1] + 1, 0), ps[ru.count - 1].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
     }
-    if (tid == 0) {
+    if (rank == 0 && tid == 0) {
         for (uint32_t j = 0; j + 1 < i; j++) a.out[ru.head0 + j] = a.tokens[ru.first + j + 1];
         a.out[ru.head0 + i - 1] = tok;
         a.spec_e[r] = i;
     }
+    sc_cluster_sync();  // nobody leaves while another block may still read its shared memory
 }
 
 // The chain drafter's pick for pass i, one block per run: the draft vocabulary's argmax (ties to the lowest
@@ -373,7 +414,7 @@ void launch_spec_step_stats(const SpecStepArgs& a, cudaStream_t s) {
     launch_pdl(spec::step_stats_kernel, a.n_head + a.n_runs * (VERIFY_T - 1), spec::THREADS, 0, s, a);
 }
 void launch_spec_step_decide(const SpecStepArgs& a, cudaStream_t s) {
-    launch_pdl(spec::step_decide_kernel, a.n_runs, spec::THREADS, 0, s, a);
+    launch_pdl(spec::step_decide_kernel, a.n_runs * SC_CTAS, SC_THREADS, 0, s, a);
 }
 void launch_draft_draw(const float* logits, uint32_t v, const uint32_t* vocab_ids, const RunIn* runs, const SampleRow* samples, const uint32_t* live,
                        const uint32_t* lens, uint32_t n_runs, uint32_t i, uint32_t rule, uint32_t* feed, uint32_t* tree, float* q_keep, uint32_t* q_rows,
