@@ -306,6 +306,7 @@ def main():
     ap.add_argument("--long-steps", type=int, default=20)
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
+    ap.add_argument("--only", default="", help="'prefill' or 'acceptance': run that one pass alone and print its figure (a profiler-size command, not the bench line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -313,7 +314,7 @@ def main():
     if (ROOT / "MEASURED_PEAKS.json").exists():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
     hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
-    with_drafter = not (args.no_model_drafter or args.bf16 or args.layers)
+    with_drafter = not (args.no_model_drafter or args.bf16)
     workload = (f"1B llama-style target{' + chain drafter' if with_drafter else ''}, {'bf16' if args.bf16 else 'int8 per-row'} weights, {args.streams} streams/GPU, ctx {args.ctx}, "
                 f"k=4 (5 rows), T={args.temperature} top-p {args.top_p}")
     if args.layers:
@@ -352,6 +353,15 @@ def main():
     _package()
     from silicon_violetto_b200 import engine as E
     path = model_file("1b", not args.bf16, rank, args.layers)
+    if args.only:
+        if args.only == "prefill":
+            print(json.dumps(prefill_figure(E, path, args.ctx, local)))
+        elif args.only == "acceptance":
+            e1, _ = make_engine(E, path, 2, 64, 8, local)
+            print(json.dumps(spec_accept_figure(E, e1, hbm_peak)))
+        else:
+            raise SystemExit(f"--only {args.only}: 'prefill' or 'acceptance'")
+        return
     total = args.warmup + args.steps + 6
     # The headline pass, on every rank: the int8 target with the chain drafter loaded (1 layer + fc + a head over 16 384 draft
     # ids, random-init), drafts drawn from its distribution, the rejection-sampling rule deciding them in the step.
