@@ -98,13 +98,15 @@ KV_BYTES_PER_TOKEN_LAYER = 8 * 64 * 2 * 2  # 8 kv heads x 64 dims x bf16 x (K, V
 WEIGHT_PARAMS = 16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048
 
 
-def drafter_file(rank: int) -> Path:
-    """The chain drafter of the 1B target (fc, one layer, a head over 16384 draft ids), int8 per row, random-init."""
+def drafter_file(rank: int, window: int) -> Path:
+    """The chain drafter of the 1B target (fc, one layer, a head over 16384 draft ids), int8 per row, random-init; its
+    draft passes attend to the last `window` positions (0: all), as the reference's drafter layers attend to 1024
+    (tools/spec/drafter.py:17)."""
     from silicon_violetto_b200 import synth
-    path = CACHE / "1b_drafter_int8row.vlt"
+    path = CACHE / f"1b_drafter_int8row_w{window}.vlt"
     done = path.with_suffix(".ok")
     if rank == 0 and not done.exists():
-        synth.write_drafter(path, "1b", seed=100, int8_group=0, draft_vocab=16384)
+        synth.write_drafter(path, "1b", seed=100, int8_group=0, draft_vocab=16384, window=window)
         done.write_text("ok")
     while not done.exists():
         time.sleep(0.5)
@@ -300,6 +302,7 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=10, help="timed verify steps of the CPU sample (the reference arm takes --steps, at most 20)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--also-streams", default="1,8", help="comma list: extra passes at these stream counts on rank 0's engine (the headline metric is quoted at 1, 8 and 32 streams); empty: none")
+    ap.add_argument("--drafter-window", type=int, default=1024, help="the chain drafter's attention window in positions (the reference's drafter: 1024); 0: the whole context")
     ap.add_argument("--no-model-drafter", action="store_true", help="the headline pass without the chain drafter (replay drafter, every draft wrong)")
     ap.add_argument("--no-extras", action="store_true", help="only the headline pass (no replay, stream-count, bf16, long-context or acceptance-kernel passes)")
     ap.add_argument("--long-ctx", type=int, default=65536, help="context of the long-context pass every rank runs after the headline one (BASELINE configuration 4); 0: skip")
@@ -367,7 +370,7 @@ def main():
     # ids, random-init), drafts drawn from its distribution, the rejection-sampling rule deciding them in the step.
     eng, _ = make_engine(E, path, args.streams, args.ctx, total, local, args.attn_keys)
     if with_drafter:
-        eng.load_drafter(drafter_file(rank))
+        eng.load_drafter(drafter_file(rank, args.drafter_window))
         eng.set_acceptance(1 if args.top_p >= 1.0 else 0)
     r = run_replica(args, rank, world, barrier, local, eng, args.mistakes, model_drafter=with_drafter)
     vals, sums = reduce_over_ranks(r["dev_ms"], r["wall"], r["emitted"], r["launches"], world, f"cuda:{local}")
@@ -379,7 +382,7 @@ def main():
         a4.ctx, a4.steps = args.long_ctx, args.long_steps
         e4, _ = make_engine(E, path, args.streams, a4.ctx, a4.warmup + a4.steps + 6, local, args.attn_keys)
         if with_drafter:
-            e4.load_drafter(drafter_file(rank))
+            e4.load_drafter(drafter_file(rank, args.drafter_window))
             e4.set_acceptance(1 if args.top_p >= 1.0 else 0)
         r4 = run_replica(a4, rank, world, barrier, local, e4, 1.0, model_drafter=with_drafter)
         v4, s4 = reduce_over_ranks(r4["dev_ms"], r4["wall"], r4["emitted"], r4["launches"], world, f"cuda:{local}")
@@ -404,7 +407,7 @@ def main():
     att_bytes = args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER
     achieved = att_bytes / (att_ms * 1e-3) / 1e9 if att_ms > 0 else 0.0
     step_bytes = WEIGHT_PARAMS * (2 if args.bf16 else 1) + args.streams * (r["mean_len"] + ROWS) * KV_BYTES_PER_TOKEN_LAYER * (args.layers or 16)
-    drafter_note = ("chain drafter (1 layer + fc + head over 16384 draft ids, int8, random-init: its drafts are practically never accepted), drafts drawn from its own "
+    drafter_note = (f"chain drafter (1 layer + fc + head over 16384 draft ids, int8, attention window {args.drafter_window or 'none'}, random-init: its drafts are practically never accepted), drafts drawn from its own "
                     "distribution, rejection-sampling acceptance in the step" if with_drafter else f"replay drafter, {args.mistakes:.2f} of positions drafted wrong")
     out = {
         "metric": "decode tokens/s at 8k context", "value": emitted / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
@@ -448,6 +451,16 @@ def main():
                                   "note": "expected 2.77 at 0.30 mistakes; streams that leave their recorded continuation (sampling near-ties) draft wrong afterwards"}
         out["acceptance_kernel"] = spec_accept_figure(E, e0, hbm_peak)
         e0.close()
+        if with_drafter and args.drafter_window:
+            # The headline pass again with a chain drafter that attends to its whole context (four more reads of a layer's K/V a step).
+            e5, _ = make_engine(E, path, args.streams, args.ctx, total, local, args.attn_keys)
+            e5.load_drafter(drafter_file(0, 0))
+            e5.set_acceptance(1 if args.top_p >= 1.0 else 0)
+            r5 = run_replica(args, rank, 1, solo, local, e5, 1.0, model_drafter=True)
+            e5.close()
+            out["full_context_drafter_pass"] = {"value": r5["emitted"] / (r5["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": r5["dev_ms"] / steps,
+                                                "mean_accepted_len": r5["emitted"] / (steps * args.streams),
+                                                "kernel_groups_ms_per_step": {k: v["ms"] / r5["prof_steps"] for k, v in r5["prof"].items()}}
         out["prefill_pass"] = prefill_figure(E, path, args.ctx, local)
         for n_s in [int(x) for x in args.also_streams.split(",") if x.strip()]:
             if n_s >= args.streams:
@@ -467,7 +480,7 @@ def main():
                 a3 = copy.copy(args)
                 a3.streams = n_s
                 e3, _ = make_engine(E, path, n_s, args.ctx, total, local, args.attn_keys)
-                e3.load_drafter(drafter_file(0))
+                e3.load_drafter(drafter_file(0, args.drafter_window))
                 e3.set_acceptance(1 if args.top_p >= 1.0 else 0)
                 r3 = run_replica(a3, rank, 1, solo, local, e3, 1.0, model_drafter=True)
                 e3.close()

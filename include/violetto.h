@@ -60,6 +60,7 @@ typedef struct {
     uint32_t attn_keys_per_cta; /* keys one attention CTA takes; 0: sized to fill the SMs */
     uint32_t gemm_min_rows;     /* steps with at least this many tokens use the tensor-core GEMM; 0: default (9) */
     uint32_t plain_attention;   /* 1: the scalar attention kernel (cross-check only) */
+    uint32_t gemm_unpaired;     /* 1: the head GEMM as one block per SM, like the others (cross-check only; results are the same bit for bit) */
 } VltTuning;
 
 /* engine/src/engine.rs:100-138 `Sampling`. */
@@ -300,8 +301,8 @@ int vlt_debug_set_trace(VltEngine* e, uint32_t slot, const uint32_t* trace, uint
 
 /* Measurement. Two marks on the engine's stream and the GPU time between them; the number of
  * kernels this library has launched so far; per-group GPU time of the steps queued while
- * profiling is on (groups: 0 matmuls, 1 attention, 2 K/V write and split merge, 3 the tail:
- * head, sampling, acceptance; the reference times its step with GPUEndTime - GPUStartTime,
+ * profiling is on (groups: the target layers' 0 matmuls, 1 attention, 2 K/V write and split merge; 3 the tail:
+ * head, sampling, acceptance; 4 the drafter, everything it launches; the reference times its step with GPUEndTime - GPUStartTime,
  * engine/src/gpu.rs:147-154, and kernel groups by leaving them out, cli/src/profile.rs:44-104);
  * the bytes one step uploads and downloads. */
 /* vlt_debug_step then runs the loaded drafter for this many rows after the step (0: not). */
@@ -319,7 +320,7 @@ int vlt_debug_mark(VltEngine* e, uint32_t which);
 int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms);
 uint64_t vlt_debug_launches(void);
 int vlt_debug_profile(VltEngine* e, uint32_t on);
-int vlt_debug_profile_read(VltEngine* e, double* ms4, uint32_t* launches4);
+int vlt_debug_profile_read(VltEngine* e, double* ms5, uint32_t* launches5);
 int vlt_debug_step_bytes(VltEngine* e, uint64_t* h2d, uint64_t* d2h);
 
 #ifdef __cplusplus

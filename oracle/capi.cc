@@ -204,6 +204,12 @@ uint64_t orc_array(void* h, const char* name, const void** ptr) {
 int orc_array_write(void* h, const char* name, uint64_t index, const uint32_t* data, uint64_t n) {
     Engine* e = static_cast<Engine*>(h);
     const std::string nm = name;
+    if ((nm == "draft_k_cache" || nm == "draft_v_cache") && e->drafter) {  // one cache element (bf16 bits) per word
+        std::vector<uint16_t>& c = nm == "draft_k_cache" ? e->drafter->k_cache : e->drafter->v_cache;
+        if (index + n > c.size()) { g_err = "orc_array_write: " + nm; return 1; }
+        for (uint64_t i = 0; i < n; i++) c[index + i] = uint16_t(data[i]);
+        return 0;
+    }
     std::vector<uint32_t>* v = nm == "lens" ? &e->lens : nm == "feed" ? &e->feed : nm == "tree" ? &e->tree : nullptr;
     if (!v || index + n > v->size()) { g_err = "orc_array_write: " + nm; return 1; }
     std::copy_n(data, n, v->begin() + index);

@@ -156,6 +156,10 @@ struct Drafter {
     Layer layer;
     Matrix head;  // [v][d]
     std::vector<uint32_t> vocab;
+    // The draft passes' attention window (meta[4]; 0 or absent: the whole context): a row sees the last `window` keys of
+    // its context, extended down to the start of the page that holds the first of them. The reference's drafter layers
+    // are sliding-window layers too (tools/spec/drafter.py:17, 1024 positions).
+    uint32_t window = 0;
     std::vector<uint16_t> k_cache, v_cache;  // [n_pages][n_kv][page][hd]
     std::vector<float> carry;                // [max_seqs][d]: the tap of each slot's last position
     // For the rejection-sampling rule: the draft rows a slot's drafts were drawn from ([max_seqs][VERIFY_T - 1][v]),
@@ -195,6 +199,7 @@ struct Engine {
     // engine.rs:381-389 `set_taps`: bf16(rms_norm(output)) of these layers, [tap][n][d] (`taps` is the last layer's, always kept).
     std::vector<uint32_t> tap_layers;
     std::vector<float> taps_all;
+    uint32_t attn_window = 0;  // set around the drafter's passes: see Drafter::window
     uint32_t accept_rule = 0;  // 0: the reference's sample-then-match; 1: rejection sampling where a run's drafts came with their q rows
 
     Engine(const std::string& file_path, const EngineConfig& c) : file(VltFile::load(file_path)), cfg(c) {
@@ -392,6 +397,7 @@ struct Engine {
             for (int64_t h = 0; h < int64_t(md.n_heads); h++) {
                 const uint32_t t0 = tiles[2 * ti], T = tiles[2 * ti + 1], g = uint32_t(h) / G;
                 const uint32_t slot = meta[2 * t0], p0 = meta[2 * t0 + 1];
+                const uint32_t lo = attn_window && p0 + T > attn_window ? (p0 + T - attn_window) / md.page * md.page : 0;
                 std::vector<float> sc(p0 + T), q(hd), o(hd);
                 for (uint32_t i = 0; i < T; i++) {
                     const uint32_t t = t0 + i;
@@ -399,7 +405,7 @@ struct Engine {
                     rope_head(q.data(), meta[2 * t + 1]);
                     for (uint32_t d = 0; d < hd; d++) q[d] = round_bf16(q[d] * sl2);
                     float mx = -INFINITY;
-                    for (uint32_t kp = 0; kp < p0 + T; kp++) {
+                    for (uint32_t kp = lo; kp < p0 + T; kp++) {
                         const bool seen = kp < p0 || ((vis[t] >> (kp - p0)) & 1u);
                         if (!seen) { sc[kp] = -INFINITY; continue; }
                         const uint16_t* kr = kc + kv_row(layer, slot, g, kp);
@@ -411,7 +417,7 @@ struct Engine {
                     }
                     float l = 0.0f;
                     std::fill(o.begin(), o.end(), 0.0f);
-                    for (uint32_t kp = 0; kp < p0 + T; kp++) {
+                    for (uint32_t kp = lo; kp < p0 + T; kp++) {
                         if (sc[kp] == -INFINITY) continue;
                         const float pz = std::exp2(sc[kp] - mx);
                         l += pz;
@@ -581,6 +587,7 @@ struct Engine {
         const std::vector<float> m = dr->file.f32s("meta");
         if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw std::runtime_error(path + ": meta is not a version-1 one-layer chain drafter");
         const uint32_t v = uint32_t(m[3]), d = md.d;
+        dr->window = m.size() > 4 ? uint32_t(m[4]) : 0;
         if (md.ffn < 2 * d) throw std::runtime_error(path + ": the chain drafter needs ffn >= 2 d_model");
         dr->fc = load_matrix(dr->file, "fc", d, 2 * d);
         dr->layer.qkv = load_matrix(dr->file, "D00.qkv", md.qkv_w(), d);
@@ -657,7 +664,9 @@ struct Engine {
                 feature_in(x.data() + size_t(r) * 2 * d, f, live[r] ? feed[slot * FEED_W + i - 1] : 0);
             }
             matmul_raw(dr.fc, x.data(), nr, h.data());
+            attn_window = dr.window;
             layer_forward(dr.layer, 0, dr.k_cache.data(), dr.v_cache.data(), h.data(), nr, nr);
+            attn_window = 0;
             inv_rms(h.data(), nr, d, md.eps, inv.data());
             matmul_raw(dr.head, h.data(), nr, lg.data());
             for (uint32_t r = 0; r < nr; r++) {

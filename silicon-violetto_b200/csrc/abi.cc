@@ -84,6 +84,7 @@ int vlt_engine_new(const char* weights_path, const VltEngineConfig* cfg, const V
             t.attn_keys_per_cta = tuning->attn_keys_per_cta;
             t.gemm_min_rows = tuning->gemm_min_rows;
             t.plain_attention = tuning->plain_attention != 0;
+            t.gemm_unpaired = tuning->gemm_unpaired != 0;
         }
         auto h = std::make_unique<VltEngine>();
         h->e = std::make_unique<Engine>(weights_path, c, t);
@@ -397,7 +398,7 @@ int vlt_debug_mark(VltEngine* e, uint32_t which) { return guard([&] { eng(e).mar
 int vlt_debug_mark_elapsed_ms(VltEngine* e, double* ms) { return guard([&] { *ms = eng(e).mark_elapsed_ms(); }); }
 uint64_t vlt_debug_launches(void) { return launch_counter(); }
 int vlt_debug_profile(VltEngine* e, uint32_t on) { return guard([&] { eng(e).profile = on != 0; }); }
-int vlt_debug_profile_read(VltEngine* e, double* ms4, uint32_t* launches4) { return guard([&] { eng(e).profile_read(ms4, launches4); }); }
+int vlt_debug_profile_read(VltEngine* e, double* ms5, uint32_t* launches5) { return guard([&] { eng(e).profile_read(ms5, launches5); }); }
 int vlt_debug_step_bytes(VltEngine* e, uint64_t* h2d, uint64_t* d2h) {
     return guard([&] { *h2d = eng(e).sets[0].in_bytes; *d2h = eng(e).sets[0].out_bytes; });
 }

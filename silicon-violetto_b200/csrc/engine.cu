@@ -498,7 +498,7 @@ void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float*
             b.q.q_b = q->q_b + size_t(t0) * q->n_heads * model.md.hd;
         }
         if (!gemm_supported(b)) throw Error("internal: GEMM asked for an unsupported shape");
-        launch_gemm(b, sm_count, s.err_flag.as<uint32_t>(), stream);
+        launch_gemm(b, sm_count, s.err_flag.as<uint32_t>(), stream, !tuning.gemm_unpaired);
     }
 }
 
@@ -592,6 +592,7 @@ void Engine::encode_layer_io(const LayerIO& io, bool capture) {
                         md.n_heads, scale_log2, tuning.plain_attention ? nullptr : s.q_b.as<uint16_t>(), io.cpos, stream);
     span_end(sp);
     if (io.kv_only && !capture) return;
+    if (io.window && (tuning.plain_attention || io.n_ctiles)) throw Error("only the split attention kernel takes a window");
     if (tuning.plain_attention) {
         if (!(skip & 4))
             launch_attn_plain(s.qkv.as<float>(), io.meta, io.tiles, io.vis, rope_tab.as<float>(), io.k_cache, io.v_cache, kv.page_table.as<uint32_t>(), kva,
@@ -636,6 +637,7 @@ void Engine::encode_layer_io(const LayerIO& io, bool capture) {
         a.keys_per_split = io.keys_per_split;
         a.max_splits = io.max_splits;
         a.max_rows = io.max_rows;
+        a.window = io.window;
         a.part = s.part.as<float>();
         a.out = s.attn.as<float>();
         a.out_b = s.attn_b.as<uint16_t>();  // the o projection reads the bf16 copy (GEMM and streamed matmul alike)
@@ -823,6 +825,7 @@ void Engine::load_drafter(const std::string& path) {
     const std::vector<float> m = dr->w.f32s("meta");
     if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw Error(path + ": `meta` is not a version-1 one-layer chain drafter");
     const uint32_t v = uint32_t(m[3]), d = md.d;
+    dr->window = m.size() > 4 ? uint32_t(m[4]) : 0;
     if (md.ffn < 2 * d) throw Error(path + ": the chain drafter needs ffn >= 2 d_model");
     dr->v = v;
     dr->fc = load_matrix(dr->w, "fc", d, 2 * d);
@@ -890,7 +893,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     StepSet& st = sets[set];
     const ModelDesc& md = model.md;
     const uint32_t d = md.d, n = p.n, nr = p.n_runs;
-    const int sp = span_begin(G_TAIL);
+    const int sp = span_begin(G_DRAFTER);
     float* x = s.act.as<float>();
     uint16_t* xb = s.act_b.as<uint16_t>();
     float* h = s.h.as<float>();
@@ -929,7 +932,8 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     // (2) the draft passes, one row per run.
     Plan dp;
     dp.n = nr;
-    attention_split(dp, std::min(p.max_keys + VERIFY_T, cfg.max_seq_len), nr);
+    const uint32_t reach = std::min(p.max_keys + VERIFY_T, cfg.max_seq_len);
+    attention_split(dp, dr.window ? std::min(reach, dr.window + md.page) : reach, nr);
     io.n = nr;
     io.meta = dr.dmeta.as<uint32_t>();
     io.tin = dr.dtin.as<uint32_t>();
@@ -941,6 +945,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     io.keys_per_split = dp.keys_per_split;
     io.max_splits = dp.max_splits;
     io.max_rows = 1;
+    io.window = dr.window;
     for (uint32_t i = 1; i < rows; i++) {
         launch_draft_pass_in(runs, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(),
                              st.out<uint32_t>(st.o_emitted), last_tap(), dr.dfeat.as<float>(), model.embed, nr, d, md.vocab, i, cfg.max_seq_len, x, xb,
@@ -1199,7 +1204,8 @@ cudaEvent_t Engine::pooled_event() {
 }
 
 int Engine::span_begin(int group) {
-    if (!profile) return -1;
+    if (!profile || span_open_outer) return -1;
+    if (group == G_DRAFTER) span_open_outer = true;
     Span sp{pooled_event(), pooled_event(), group, uint32_t(launch_counter())};
     VLT_CUDA(cudaEventRecord(sp.a, stream));
     spans.push_back(sp);
@@ -1209,6 +1215,7 @@ int Engine::span_begin(int group) {
 void Engine::span_end(int idx) {
     if (idx < 0) return;
     Span& sp = spans[idx];
+    if (sp.group == G_DRAFTER) span_open_outer = false;
     VLT_CUDA(cudaEventRecord(sp.b, stream));
     sp.launches = uint32_t(launch_counter()) - sp.launches;
 }
@@ -1225,6 +1232,7 @@ void Engine::profile_read(double* ms, uint32_t* launches) {
         event_pool.push_back(sp.b);
     }
     spans.clear();
+    span_open_outer = false;
 }
 
 void Engine::mark(int which) {

@@ -26,6 +26,7 @@ struct Tuning {
     uint32_t spec_tokens = 32, spec_tokens_short = 8, spec_kv = 24576, spec_rows_long = 4;
     uint32_t sm_count = 0, attn_keys_per_cta = 0, gemm_min_rows = 0;
     bool plain_attention = false;
+    bool gemm_unpaired = false;  // the many-tile head GEMM as one block per SM (default: two smaller blocks per SM)
 };
 
 // engine/src/engine.rs:100-138.
@@ -174,11 +175,14 @@ class Engine {
     void debug_stalled_wait();  // queues a kernel whose bounded wait runs out: the next collected step must report it
 
     // Measurement: two stream marks (GPU time between them), and, while `profile` is on, the GPU
-    // time of each kernel group of the queued steps (cuda events around the group's launches).
-    enum Group : int { G_MATMUL = 0, G_ATTN = 1, G_SMALL = 2, G_TAIL = 3, G_COUNT = 4 };
+    // time of each kernel group of the queued steps (cuda events around the group's launches). The groups are disjoint:
+    // the first three are the target's layers, G_TAIL its head, sampling and acceptance, G_DRAFTER everything the
+    // drafter runs (its own projections and attention included).
+    enum Group : int { G_MATMUL = 0, G_ATTN = 1, G_SMALL = 2, G_TAIL = 3, G_DRAFTER = 4, G_COUNT = 5 };
     void mark(int which);
     double mark_elapsed_ms();
     bool profile = false;
+    bool span_open_outer = false;  // a G_DRAFTER span is open: the spans inside it are not recorded
     void profile_read(double* ms, uint32_t* launches);
 
     Model model;
@@ -213,6 +217,7 @@ class Engine {
         Matrix fc, head;
         Layer layer;
         uint32_t v = 0;
+        uint32_t window = 0;  // the draft passes' attention window in keys (0: the whole context)
         Buffer vocab_ids, k, v_cache, carry, dfeat, dmeta, dtin, dvis, dcpos, dtiles, live, cpos, logits, hfin, hfin_b, inv;
         // The rejection-sampling rule's state: the q rows a slot's drafts were drawn from, how many are current, the
         // draft vocabulary's inverse map, and the step's scratch (row statistics, sampler skips, settled candidates).
@@ -234,6 +239,7 @@ class Engine {
     struct LayerIO {
         const Layer* l;
         uint32_t n, n_tiles, layer, keys_per_split, max_splits, max_rows;  // max_rows: the longest tile's rows
+        uint32_t window;       // 0: every key; else the tiles' last `window` keys, extended down to a page boundary (the split kernel only)
         const uint32_t *meta, *tin, *tiles, *vis;
         const uint32_t* ctiles;  // chunk tiles, if the step's attention is the chunk kernel (n_ctiles > 0)
         uint32_t n_ctiles;

@@ -94,7 +94,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, NT <= 3 ? 4 : 3) attn_mma_ker
     const uint32_t t0 = a.tiles[2 * tile], T = a.tiles[2 * tile + 1];
     const uint32_t slot = a.meta[2 * t0], p0 = a.meta[2 * t0 + 1];
     const uint32_t n_keys = p0 + T, n_cols = min(T * G, uint32_t(NC));
-    const uint32_t k_begin = split * a.keys_per_split;
+    // A windowed layer starts at the page that holds the first key of the tile's last `window`.
+    const uint32_t k_lo = a.window && n_keys > a.window ? (n_keys - a.window) / PAGE * PAGE : 0;
+    const uint32_t k_begin = k_lo + split * a.keys_per_split;
     const uint32_t k_end = min(k_begin + a.keys_per_split, n_keys);
 
     auto part_of = [&](uint32_t p) {  // column p's partial for this split

@@ -25,11 +25,13 @@ namespace vlt {
 namespace gemm {
 
 constexpr uint32_t BM = 128, BK = 64;
-constexpr uint32_t CONV_WARPS = 16;
-constexpr uint32_t CONV_GROUPS = 4;                      // converter groups, each on its own k block
-constexpr uint32_t CONV_WPG = CONV_WARPS / CONV_GROUPS;  // warps per group: one per quarter of the TMEM lanes
+constexpr uint32_t CONV_WPG = 4;  // converter warps per group: one per quarter of the TMEM lanes
 constexpr uint32_t FIRST_CONV = 3;
-constexpr uint32_t THREADS = 32 * (FIRST_CONV + CONV_WARPS);  // warp 0: weight TMA, warp 1: MMA, warp 2: activation TMA, the rest: conversion and epilogue
+// warp 0: weight TMA, warp 1: MMA, warp 2: activation TMA, the rest (CW of them, in groups that each take their own k
+// block): conversion and epilogue. Sixteen normally, one block per SM. Eight -- two blocks per SM, each with half the
+// shared and tensor memory -- for a GEMM of several waves of tiles (the head over the vocabulary): one block's fill and
+// epilogue then run under the other's main loop.
+constexpr uint32_t threads_of(uint32_t cw) { return 32 * (FIRST_CONV + cw); }
 constexpr uint32_t SPIN = 1u << 26;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -191,8 +193,9 @@ __device__ __forceinline__ float ld_cluster(uint32_t addr) {
 // its blocks each stream a slice of k into their own TMEM accumulator, send every group of 16 tokens
 // to the block that finishes it (stores into its shared memory), and each then adds up, in rank
 // order, the groups it owns.
-template <bool INT8, uint32_t EPI>
-__global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
+template <bool INT8, uint32_t EPI, uint32_t CONV_WARPS = 16>
+__global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 : 2) gemm_kernel(const __grid_constant__ Maps maps, const Args a) {
+    constexpr uint32_t CONV_GROUPS = CONV_WARPS / CONV_WPG;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // Three rings, each as deep as its own latency asks. B stages (n_pad x 128 B) in shared memory cover
@@ -596,7 +599,8 @@ struct GemmMapCache {
 };
 
 typedef void (*GemmEntry)(const gemm::Maps, const gemm::Args);
-static GemmEntry gemm_entry(bool int8, uint32_t epi) {
+static GemmEntry gemm_entry(bool int8, uint32_t epi, bool paired = false) {
+    if (paired) return gemm::gemm_kernel<true, EPI_HEAD, 8>;  // the only shape that runs in waves
     switch (epi) {
     case EPI_NORM: return int8 ? gemm::gemm_kernel<true, EPI_NORM> : gemm::gemm_kernel<false, EPI_NORM>;
     case EPI_RESID: return int8 ? gemm::gemm_kernel<true, EPI_RESID> : gemm::gemm_kernel<false, EPI_RESID>;
@@ -613,7 +617,7 @@ bool gemm_supported(const MatArgs& a) {
            (a.epi == EPI_RESID || a.epi == EPI_RAW || a.inv_in != nullptr || a.ssq_in != nullptr);
 }
 
-void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s) {
+void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s, bool allow_paired) {
     static thread_local GemmMapCache cache;
     static PerDevice configured;
     const uint32_t n_pad = (a.n + 15) / 16 * 16;
@@ -629,37 +633,45 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     // Shared memory: B stages of n_pad x 128 B; bf16 weights, as many A stages of 16 KiB; int8 weights, A
     // stages in tensor memory behind the accumulator and raw stages of 8 KiB in the shared memory left.
     const uint32_t a_bytes = gemm::BM * gemm::BK * 2, b_bytes = n_pad * gemm::BK * 2, raw_bytes = gemm::BM * gemm::BK;
-    const uint32_t budget = 208 * 1024;
+    const uint32_t tiles = a.m / gemm::BM, nkb = a.k / gemm::BK;
     const uint32_t tmem_a0 = (n_pad + 31) / 32 * 32;
+    // Several waves of tiles (the head over the vocabulary): two smaller blocks per SM, see threads_of. Each gets half the
+    // tensor memory (the accumulator and three A stages in 256 columns) and half the shared memory.
+    const bool paired = a.int8 && a.epi == EPI_HEAD && tiles > sm_count && tmem_a0 + 3 * 32 <= 256 && allow_paired;
+    const uint32_t budget = paired ? 100 * 1024 : 208 * 1024;
     uint32_t stages_a, stages_b, raw_stages = 0;
     if (a.int8) {
-        stages_a = std::min(8u, (512 - tmem_a0) / 32);
-        stages_b = std::max(2u, std::min(4u, (budget - 4 * raw_bytes) / b_bytes));
+        stages_a = paired ? 3u : std::min(8u, (512 - tmem_a0) / 32);
+        stages_b = paired ? 2u : std::max(2u, std::min(4u, (budget - 4 * raw_bytes) / b_bytes));
         raw_stages = std::max(2u, std::min(16u, (budget - stages_b * b_bytes) / raw_bytes));
     } else {
         stages_a = stages_b = std::max(2u, std::min(8u, budget / (a_bytes + b_bytes)));
     }
-    const uint32_t ring = std::max((a.int8 ? 0 : stages_a * a_bytes) + stages_b * b_bytes + raw_stages * raw_bytes,
-                                   (n_pad / 16 + 8) * 16 * gemm::BM * 4);  // the split-k exchange buffer at its largest (8 splits)
-    // At least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
-    // behind another one (blocks of different clusters waiting on each other's SMs could deadlock).
-    const size_t smem = std::max<size_t>(size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 28, 116 * 1024);
+    const uint32_t ring = paired ? stages_b * b_bytes + raw_stages * raw_bytes
+                                 : std::max((a.int8 ? 0 : stages_a * a_bytes) + stages_b * b_bytes + raw_stages * raw_bytes,
+                                            (n_pad / 16 + 8) * 16 * gemm::BM * 4);  // the split-k exchange buffer at its largest (8 splits)
+    // Unpaired, at least half an SM's shared memory: one block per SM, so that a block never waits for tensor memory
+    // behind another one (blocks of different clusters waiting on each other's SMs could deadlock). Paired blocks are in
+    // no cluster, and two of them hold exactly an SM's tensor memory.
+    const size_t need = size_t(ring) + 1024 + (2 * stages_a + 2 * stages_b + 2 * raw_stages + 1) * 8 + 16 + n_pad * 28;
+    const size_t smem = paired ? need : std::max<size_t>(need, 116 * 1024);
     configured.once([] {
         for (int i8 = 0; i8 < 2; i8++)
             for (uint32_t epi = EPI_NORM; epi <= EPI_QKV; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        VLT_CUDA(cudaFuncSetAttribute(gemm_entry(true, EPI_HEAD, true), cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
+        VLT_CUDA(cudaFuncSetAttribute(gemm_entry(true, EPI_HEAD, true), cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     });
     // Split k over a cluster when the tiles alone cannot fill the SMs (the reference splits K the
     // same way when a GEMM has few tiles, encode.rs:545-553).
-    const uint32_t tiles = a.m / gemm::BM, nkb = a.k / gemm::BK;
     static thread_local std::map<std::tuple<bool, uint32_t, uint32_t>, uint32_t> wave;  // (int8, smem, cluster size) -> clusters one wave holds
-    uint32_t splits = std::max(1u, std::min(8u, std::min(sm_count / tiles, nkb)));
+    uint32_t splits = std::max(1u, std::min(8u, std::min(sm_count / tiles, nkb)));  // (1 for a paired launch: more tiles than SMs)
     for (; splits > 1; splits--) {
         auto wk = std::make_tuple(a.int8, uint32_t(smem) * 8 + a.epi, splits);
         auto w = wave.find(wk);
         if (w == wave.end()) {
             cudaLaunchConfig_t q = {};
             q.gridDim = dim3(tiles * splits);
-            q.blockDim = dim3(gemm::THREADS);
+            q.blockDim = dim3(gemm::threads_of(16));
             q.dynamicSmemBytes = smem;
             cudaLaunchAttribute qa[1];
             qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -687,7 +699,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     g.err_flag = err_flag;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * splits);
-    cfg.blockDim = dim3(gemm::THREADS);
+    cfg.blockDim = dim3(gemm::threads_of(paired ? 8 : 16));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
@@ -699,7 +711,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = splits > 1 ? 2 : 1;
-    VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm_entry(a.int8, a.epi), it->second, g));
+    VLT_CUDA(cudaLaunchKernelEx(&cfg, gemm_entry(a.int8, a.epi, paired), it->second, g));
     launch_counter()++;
 #ifdef VLT_GEMM_PROBE
     if (getenv("VLT_GEMM_PROBE")) {

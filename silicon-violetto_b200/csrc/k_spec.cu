@@ -296,8 +296,8 @@ __global__ void __launch_bounds__(THREADS) step_stats_kernel(const SpecStepArgs 
     if (tid == 0) *out = RowStats{mx, am, ex[ex_at(THREADS)], 0};
 }
 
-// A cluster of 8 blocks per run (the sampler's 1024 threads, see decide_cluster_kernel): the tests in order (one thread
-// of every block), then the replacement or the bonus token (the cluster).
+// A cluster of 8 blocks per run (the sampler's 1024 threads, see decide_cluster_kernel): the tests (a lane each, in
+// every block), then the replacement or the bonus token (the cluster).
 __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) step_decide_kernel(const SpecStepArgs a) {
     pdl_start();
     __shared__ ScExchange xc;
@@ -321,19 +321,27 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) st
     const float* pp = a.logits + size_t(ru.head0) * a.vocab;
     const float* qq = a.q_keep + size_t(ru.slot) * (VERIFY_T - 1) * a.v;
     auto e_of = [&](float x, float mx) { return soft_exp2(__fmul_rn(__fsub_rn(x, mx), c)); };
-    if (tid == 0) {
-        uint32_t i = 1;
-        for (; i < ru.count; i++) {
+    // The tests, one lane each (every block of the cluster does them), so that the loads of all of them are in flight at
+    // once; the first that fails, or whose draft is outside the draft vocabulary, is where the run stops.
+    if (tid < 32) {
+        bool fails = false;  // a lane without a test does not fail
+        if (tid + 1 < ru.count) {
+            const uint32_t i = tid + 1;
             const uint32_t tok = a.tokens[ru.first + i], idx = tok < a.vocab ? a.index_of[tok] : NO_TOK;
-            if (idx == NO_TOK) break;
-            const float ep = e_of(pp[size_t(i - 1) * a.vocab + tok], ps[i - 1].max), eq = e_of(qq[size_t(i - 1) * a.v + idx], qs[i - 1].max);
-            const float u = uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 0);
-            const float lhs = __fmul_rn(__fmul_rn(u, eq), ps[i - 1].z), rhs = __fmul_rn(ep, qs[i - 1].z);
-            if (!(lhs < rhs)) break;
+            fails = true;
+            if (idx != NO_TOK) {
+                const float ep = e_of(pp[size_t(i - 1) * a.vocab + tok], ps[i - 1].max), eq = e_of(qq[size_t(i - 1) * a.v + idx], qs[i - 1].max);
+                const float u = uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 0);
+                const float lhs = __fmul_rn(__fmul_rn(u, eq), ps[i - 1].z), rhs = __fmul_rn(ep, qs[i - 1].z);
+                fails = !(lhs < rhs);
+            }
         }
-        first_reject = i;
-        xc.pick[0] = 0xffffffffu;
-        xc.pick[1] = 0xffffffffu;
+        const uint32_t failed = __ballot_sync(0xffffffffu, fails);  // lane t holds test t + 1
+        if (tid == 0) {
+            first_reject = failed ? uint32_t(__ffs(failed)) : ru.count;
+            xc.pick[0] = 0xffffffffu;
+            xc.pick[1] = 0xffffffffu;
+        }
     }
     __syncthreads();
     const uint32_t i = first_reject;
@@ -345,16 +353,37 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS) st
         const uint32_t* index_of = a.index_of;
         auto resid = [&](uint32_t j) {
             const uint32_t idx = index_of[j];
-            const float ea = __fmul_rn(e_of(pi[j], pm), zq), eb = idx == NO_TOK ? 0.0f : __fmul_rn(e_of(qi[idx], qm), zp);
+            const float qv = qi[idx == NO_TOK ? 0u : idx];  // an unconditional load: a batch's loads all go out before the arithmetic
+            const float ea = __fmul_rn(e_of(pi[j], pm), zq), eb = idx == NO_TOK ? 0.0f : __fmul_rn(e_of(qv, qm), zp);
             const float d = __fsub_rn(ea, eb);
             return d > 0.0f ? d : 0.0f;
         };
-        tok = sc_inverse_cdf(a.vocab, resid, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 1), ps[i - 1].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
+        // A batch in three rounds of loads (draft index and p; q through the index), then the arithmetic.
+        constexpr int B = 16;
+        auto resid_batch = [&](uint32_t i0, float (&e)[B]) {
+            uint32_t idx[B];
+            float pv[B], qv[B];
+#pragma unroll
+            for (int u = 0; u < B; u++) {
+                idx[u] = index_of[i0 + u * SAMPLE_THREADS];
+                pv[u] = pi[i0 + u * SAMPLE_THREADS];
+            }
+#pragma unroll
+            for (int u = 0; u < B; u++) qv[u] = qi[idx[u] == NO_TOK ? 0u : idx[u]];
+#pragma unroll
+            for (int u = 0; u < B; u++) {
+                const float ea = __fmul_rn(e_of(pv[u], pm), zq), eb = idx[u] == NO_TOK ? 0.0f : __fmul_rn(e_of(qv[u], qm), zp);
+                const float d = __fsub_rn(ea, eb);
+                e[u] = d > 0.0f ? d : 0.0f;
+            }
+        };
+        tok = sc_inverse_cdf_batched<B>(a.vocab, resid, resid_batch, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + i) + 1], 1), ps[i - 1].argmax, &xc, 0, 0, vals, pre,
+                                        tot_all, base, rank, tid);
     } else {
         const float* pk = pp + size_t(ru.count - 1) * a.vocab;
         const float pm = ps[ru.count - 1].max;
         auto w = [&](uint32_t j) { return e_of(pk[j], pm); };
-        tok = sc_inverse_cdf(a.vocab, w, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + ru.count - 1) + 1] + 1, 0), ps[ru.count - 1].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
+        tok = sc_inverse_cdf<16>(a.vocab, w, uniform01(sr.seed_lo, sr.seed_hi, a.meta[2 * (ru.first + ru.count - 1) + 1] + 1, 0), ps[ru.count - 1].argmax, &xc, 0, 0, vals, pre, tot_all, base, rank, tid);
     }
     if (rank == 0 && tid == 0) {
         for (uint32_t j = 0; j + 1 < i; j++) a.out[ru.head0 + j] = a.tokens[ru.first + j + 1];

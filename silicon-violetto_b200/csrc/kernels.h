@@ -87,6 +87,7 @@ struct AttnArgs {
     float scale_log2;
     uint32_t keys_per_split, max_splits;
     uint32_t max_rows;  // the longest tile's rows in this launch (0: unknown, VERIFY_T)
+    uint32_t window;    // 0: every key; else a tile sees its last `window` keys, extended down to a page boundary
     float* part;  // [token][head][max_splits][PART]
     float* out;   // [n][n_heads * hd]
     uint16_t* out_b;  // optional bf16 copy
@@ -137,7 +138,7 @@ void launch_draft_tree(const uint32_t* blocks, const uint32_t* slots, uint32_t n
 // The tcgen05 GEMM for 16..256 tokens: needs Xb (bf16 X, rows padded to 16), inv_in for the
 // normed epilogues, m a multiple of 128, one int8 scale per row.
 bool gemm_supported(const MatArgs& a);
-void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s);
+void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s, bool allow_paired = true);
 void launch_matmul_stream(const MatArgs& a, uint32_t sm_count, cudaStream_t s);  // n <= 8, tensor cores fed from registers
 bool matmul_stream_fits(const MatArgs& a);                                      // else launch_matmul_stream falls back to the scalar kernel
 void launch_matmul_rows(const MatArgs& a, cudaStream_t s);                      // any n, scalar (cross-check, odd scale groups)

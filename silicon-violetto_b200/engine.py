@@ -39,7 +39,7 @@ class _Config(C.Structure):
 
 class _Tuning(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("spec_tokens", "spec_tokens_short", "spec_kv", "spec_rows_long", "spec_policy_off", "sm_count",
-                                          "attn_keys_per_cta", "gemm_min_rows", "plain_attention")]
+                                          "attn_keys_per_cta", "gemm_min_rows", "plain_attention", "gemm_unpaired")]
 
 
 class _Sampling(C.Structure):
@@ -140,6 +140,7 @@ class Tuning:
     attn_keys_per_cta: int = 0
     gemm_min_rows: int = 0
     plain_attention: bool = False
+    gemm_unpaired: bool = False
 
 
 @dataclass
@@ -188,7 +189,7 @@ class Engine:
         c = _Config(cfg.max_seqs, cfg.max_step_tokens, cfg.max_chunk, cfg.global_kv_tokens, cfg.max_seq_len, cfg.max_head_rows, cfg.device_ordinal,
                     FLAG_HOST_ONLY if cfg.host_only else 0)
         ct = _Tuning(t.spec_tokens, t.spec_tokens_short, t.spec_kv, t.spec_rows_long, int(t.spec_policy_off), t.sm_count, t.attn_keys_per_cta,
-                     t.gemm_min_rows, int(t.plain_attention))
+                     t.gemm_min_rows, int(t.plain_attention), int(t.gemm_unpaired))
         self.h = C.c_void_p()
         self.cfg = cfg
         _check(lib().vlt_engine_new(str(weights).encode(), C.byref(c), C.byref(ct), C.byref(self.h)))
@@ -440,10 +441,10 @@ class Engine:
         _check(lib().vlt_debug_profile(self.h, C.c_uint32(int(on))))
 
     def profile_read(self) -> dict:
-        ms = (C.c_double * 4)()
-        n = (C.c_uint32 * 4)()
+        ms = (C.c_double * 5)()
+        n = (C.c_uint32 * 5)()
         _check(lib().vlt_debug_profile_read(self.h, ms, n))
-        names = ("matmul", "attention", "small", "tail")
+        names = ("matmul", "attention", "small", "tail", "drafter")
         return {k: dict(ms=ms[i], launches=int(n[i])) for i, k in enumerate(names)}
 
     def step_bytes(self):

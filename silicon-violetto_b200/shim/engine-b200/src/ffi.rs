@@ -46,6 +46,7 @@ pub struct VltTuning {
     pub attn_keys_per_cta: u32,
     pub gemm_min_rows: u32,
     pub plain_attention: u32,
+    pub gemm_unpaired: u32,
 }
 #[repr(C)]
 #[derive(Clone, Copy)]

@@ -161,6 +161,7 @@ impl Engine {
             attn_keys_per_cta: tuning.attn_keys_per_cta as u32,
             gemm_min_rows: tuning.gemm_min_rows as u32,
             plain_attention: 0,
+            gemm_unpaired: 0,
         };
         let mut h = std::ptr::null_mut();
         check(unsafe { ffi::vlt_engine_new(path.as_ptr(), &c, &t, &mut h) })?;

@@ -79,15 +79,19 @@ def write_target(path, config: str | dict, seed: int = 0, int8_group: int | None
     return c
 
 
-def write_drafter(path, config: str | dict, seed: int = 100, int8_group: int | None = None, draft_vocab: int | None = None, std: float = 0.02) -> None:
+def write_drafter(path, config: str | dict, seed: int = 100, int8_group: int | None = None, draft_vocab: int | None = None, std: float = 0.02,
+                  window: int = 0) -> None:
     """The chain drafter: fc [d][2d] over (tapped hidden ; token embedding), one decoder layer
     `D00.*`, a head over a draft vocabulary of `draft_vocab` ids (`vocab`, ascending target
-    ids stored as f32 like the reference's drafter file, tools/spec/export.py:51)."""
+    ids stored as f32 like the reference's drafter file, tools/spec/export.py:51). With `window`,
+    a draft pass attends to the last `window` keys of its context (down to a page boundary), as the
+    reference's drafter layers attend to 1024 positions (tools/spec/drafter.py:17); the descriptor
+    then has a fifth field."""
     c = CONFIGS[config] if isinstance(config, str) else config
     gen = torch.Generator().manual_seed(seed)
     d, qkv_w = c["d"], (c["n_heads"] + 2 * c["n_kv"]) * c["hd"]
     v = draft_vocab or c["vocab"]
-    out: dict = {"meta": np.array([META_VERSION, DRAFTER_KIND_CHAIN, 1, v], dtype=np.float32)}
+    out: dict = {"meta": np.array([META_VERSION, DRAFTER_KIND_CHAIN, 1, v] + ([window] if window else []), dtype=np.float32)}
     _put(out, "fc", _randn(gen, d, 2 * d, std), int8_group)
     _put(out, "D00.qkv", _randn(gen, qkv_w, d, std), int8_group)
     _put(out, "D00.o", _randn(gen, d, c["n_heads"] * c["hd"], std), int8_group)

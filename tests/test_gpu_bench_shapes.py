@@ -202,6 +202,29 @@ def test_one_layer_at_the_1b_dimensions_matches_the_oracle(one_layer_1b, filled)
     prod.close()
 
 
+def test_head_gemm_in_paired_blocks_gives_the_one_block_per_sm_logits_bit_for_bit(one_layer_1b):
+    """The head over 128 256 ids is 1002 tiles: by default two half-size blocks share an SM (one's fill and epilogue under
+    the other's main loop). A tile's arithmetic and its order are the same either way, so the logits must be the same bits
+    as with one block per SM (gemm_unpaired), at 160 rows and at 40."""
+    path, int8_group = one_layer_1b
+    if int8_group is None:
+        pytest.skip("bf16 weights have no converter warps to halve: one block per SM always")
+    kw = dict(max_seqs=32, max_step_tokens=160, max_chunk=8, global_kv_tokens=32 * 64, max_seq_len=64, max_head_rows=160)
+    got = []
+    for unpaired in (False, True):
+        eng = E.Engine(path, E.EngineConfig(**kw), E.Tuning(gemm_unpaired=unpaired))
+        seqs = [eng.new_seq() for _ in range(32)]
+        rng = np.random.default_rng(8)
+        vocab = eng.desc.vocab
+        a = eng.debug_step([(s, rng.integers(0, vocab, 5).astype(np.uint32), E.Rows.ALL, False) for s in seqs], E.StepOptions(read_logits=True))
+        b = eng.debug_step([(s, rng.integers(0, vocab, 5).astype(np.uint32), E.Rows.ALL, False) for s in seqs[:8]], E.StepOptions(read_logits=True))
+        got.append((a.logits.copy(), b.logits.copy(), a.ids.copy(), b.ids.copy()))
+        eng.close()
+    assert got[0][0].shape == (160, 128256) and got[0][1].shape == (40, 128256)
+    for x, y in zip(got[0], got[1]):
+        assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+
 # ---------------------------------------------------------------- the plumbing configuration as stated
 def _plain_decode(w, prompt, n_tokens):
     """The oracle's one-token-at-a-time greedy decoding with each token's top-2 logit margin."""

@@ -19,10 +19,12 @@ def built():
     build.build()
 
 
-@pytest.fixture(scope="module")
-def drafter_file(tmp_path_factory):
+@pytest.fixture(scope="module", params=[0, 16], ids=["full", "window16"])
+def drafter_file(request, tmp_path_factory):
+    """The chain drafter over the whole context, and with a window of one page (the steps below reach 50 positions:
+    the passes start at key 0, 16 or 32)."""
     path = tmp_path_factory.mktemp("drafter") / "micro_drafter.vlt"
-    synth.write_drafter(path, util.MICRO, seed=100, draft_vocab=DRAFT_V)
+    synth.write_drafter(path, util.MICRO, seed=100, draft_vocab=DRAFT_V, window=request.param)
     return path
 
 
@@ -117,6 +119,36 @@ def test_chain_drafter_matches_the_oracle(drafter_file):
             prod.settle(s, ROWS - int(e))
             orc.settle(s, ROWS - int(e))
         assert prod.seq_len(a) == orc.seq_len(a) and prod.seq_len(b) == orc.seq_len(b)
+
+
+def test_windowed_drafter_over_a_long_context_and_two_key_splits(tmp_path):
+    """A window of 64 keys at 150 to 190 positions, the kernel's key split forced to 64 keys per block: the draft passes
+    run two splits from the window's page-aligned start. The oracle's draft logits must differ from a full-context
+    drafter's (the window is in effect) and the product must follow the windowed ones."""
+    ids = None
+    logits = {}
+    for window in (64, 0):
+        path = tmp_path / f"d{window}.vlt"
+        synth.write_drafter(path, util.MICRO, seed=100, draft_vocab=DRAFT_V, window=window)
+        ids = vlt.read(path)["vocab"].astype(np.uint32)
+        cfg = dict(max_seqs=2, max_step_tokens=256, max_chunk=256, global_kv_tokens=16 * 40, max_seq_len=256, max_head_rows=16)
+        w = util.weights("micro")
+        prod = E.Engine(w, E.EngineConfig(**cfg), E.Tuning(attn_keys_per_cta=64))
+        orc = oracle.Engine(w, max_seqs=2, max_step_tokens=256, max_chunk=256, kv_tokens=16 * 40, max_seq_len=256, max_head_rows=16)
+        prod.load_drafter(path)
+        orc.load_drafter(path)
+        prod.set_draft_rows(ROWS)
+        rng = np.random.default_rng(77)
+        a, b = prod.new_seq(), prod.new_seq()
+        assert (orc.new_seq(), orc.new_seq()) == (a, b)
+        _step(prod, orc, [(a, rng.integers(0, 512, 150).astype(np.uint32), E.Rows.LAST, False), (b, rng.integers(0, 512, 71).astype(np.uint32), E.Rows.LAST, False)], cfg, ids)
+        for _ in range(3):
+            _step(prod, orc, [(s, [E.FEED_ROW + i for i in range(ROWS)], E.Rows.LAST, True) for s in (a, b)], cfg, ids)
+            for s, e in zip((a, b), orc.array("emitted")[:2]):
+                prod.settle(s, ROWS - int(e))
+                orc.settle(s, ROWS - int(e))
+        logits[window] = orc.array("draft_logits").copy()
+    assert np.abs(logits[64] - logits[0]).max() > 1e-3
 
 
 def test_generator_with_the_model_drafter_decodes_like_plain_decoding(drafter_file):

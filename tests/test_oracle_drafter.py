@@ -67,3 +67,34 @@ def test_drafts_are_chain_nodes_from_the_draft_vocabulary_and_rows_of_one_draft_
         assert tree[i] == (i | ((i - 1) << 8) | (((2 << i) - 1) << 16))  # depth i, parent i - 1, sees rows 0..i
     # Reserving for the draft passes: 8 positions past the step (bounded by max_seq_len).
     assert len(e.array("free_pages")) == 512 // 16 - -(-(e.seq_len(s) + 8) // 16)
+
+
+def test_a_window_that_covers_the_context_changes_nothing_and_a_shorter_one_starts_on_a_page(tmp_path):
+    """meta[4] = window: a pass at position p sees keys from 16 * ((p + 1 - window) // 16) on. With the window past the
+    context the draft logits are the full drafter's bit for bit; with a shorter one they equal those of a drafter whose
+    cache below the window's start has been overwritten (nothing below it is read)."""
+    from silicon_violetto_b200 import vlt
+    prompt = np.random.default_rng(9).integers(0, 512, 45).astype(np.uint32)
+
+    def run(window, scribble=False):
+        d = tmp_path / f"w{window}.vlt"
+        synth.write_drafter(d, util.MICRO, seed=100, draft_vocab=128, window=window)
+        assert len(vlt.read(d)["meta"]) == (5 if window else 4)
+        e = oracle.Engine(util.weights("micro"), max_seqs=1, max_step_tokens=64, max_chunk=64, kv_tokens=256, max_seq_len=256, max_head_rows=16)
+        e.load_drafter(d)
+        s = e.new_seq()
+        e.step([(s, prompt, LAST, False)], draft_rows=1)
+        if scribble:  # positions 0..15 (page 0 of the slot) of the drafter's cache
+            junk = np.full(util.MICRO["n_kv"] * 16 * 64, 0x4120, np.uint16)  # bf16 10.0
+            page = int(e.array("page_table")[0])
+            e.write("draft_k_cache", page * len(junk), junk)
+            e.write("draft_v_cache", page * len(junk), junk)
+        e.step([(s, [FEED_ROW], LAST, False)], draft_rows=ROWS)
+        return e.array("draft_logits").copy()
+
+    full = run(0)
+    assert np.array_equal(run(200), full)
+    short = run(20)  # passes at positions 45..48: keys from 16 on ((46 - 20) // 16 * 16 .. (49 - 20) // 16 * 16)
+    assert not np.array_equal(short, full)
+    assert np.array_equal(run(20, scribble=True), short)
+    assert not np.array_equal(run(0, scribble=True), full)
