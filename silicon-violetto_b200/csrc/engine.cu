@@ -391,6 +391,7 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
     p.ctiles = uint32_t(ctiles.size() / 2);
     p.n = n;
     p.n_head = uint32_t(head_rows.size());
+    p.head_all = p.n_head == n;  // (rows are listed in step order, each once)
     p.n_hidden = uint32_t(hidden_rows.size());
     p.n_runs = uint32_t(runs.size());
     p.tiles = uint32_t(tiles.size() / 2);
@@ -452,6 +453,10 @@ bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
     const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 9;  // up to 8 tokens the streamed kernel; 9..15 would take it twice over the weights
     const bool grouped = w.int8 && w.group < w.k;
     return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
+}
+
+bool Engine::layer_carries(const Layer& l, uint32_t n) const {
+    return use_gemm(l.qkv, n) && use_gemm(l.o, n) && use_gemm(l.gate_up, n) && use_gemm(l.down, n) && model.md.d % 128 == 0;
 }
 
 void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
@@ -694,7 +699,10 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
     SpecStepArgs sa{};
     if (p.n_hidden) launch_prep_rows(h, st.in<uint32_t>(st.o_hidden_rows), p.n_hidden, md.d, md.eps, s.hfin_all.as<float>(), nullptr, nullptr, true, false, stream);
     if (p.n_head && !(skip & 256)) {
-        if (use_gemm(model.head, p.n_head)) {
+        if (use_gemm(model.head, p.n_head) && p.head_all && !(skip & 64) && layer_carries(model.layers.back(), p.n)) {
+            // Every row goes through the head (a verify step): the last down projection left bf16(h) and the sums of squares.
+            matmul_gemm(model.head, p.n_head, s.h_b.as<uint16_t>(), s.logits.as<float>(), nullptr, EPI_HEAD, nullptr, nullptr, 0, nullptr, nullptr, s.ssq.as<float>());
+        } else if (use_gemm(model.head, p.n_head)) {
             launch_prep_rows(h, st.in<uint32_t>(st.o_head_rows), p.n_head, md.d, md.eps, nullptr, s.hfin_b.as<uint16_t>(), s.inv_head.as<float>(), false, false, stream);
             matmul_gemm(model.head, p.n_head, s.hfin_b.as<uint16_t>(), s.logits.as<float>(), nullptr, EPI_HEAD, nullptr, s.inv_head.as<float>());
         } else {
@@ -898,9 +906,14 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     uint16_t* xb = s.act_b.as<uint16_t>();
     float* h = s.h.as<float>();
     const RunIn* runs = st.in<RunIn>(st.o_runs);
+    // With the layer on the GEMM, fc leaves bf16(h) and h's sums of squares as a residual projection does (no base here):
+    // the qkv projection needs no row pass, nor does the head after the layer.
     auto fc = [&](uint32_t rows_in) {
-        if (use_gemm(dr.fc, rows_in)) matmul_gemm(dr.fc, rows_in, xb, h, nullptr, EPI_RAW, nullptr, nullptr);
+        const bool carries = use_gemm(dr.fc, rows_in) && layer_carries(dr.layer, rows_in);
+        if (carries) matmul_gemm(dr.fc, rows_in, xb, h, s.h_b.as<uint16_t>(), EPI_RESID, nullptr, nullptr, 0, nullptr, s.ssq.as<float>());
+        else if (use_gemm(dr.fc, rows_in)) matmul_gemm(dr.fc, rows_in, xb, h, nullptr, EPI_RAW, nullptr, nullptr);
         else matmul(dr.fc, rows_in, x, h, EPI_RAW, nullptr, nullptr);
+        return carries;
     };
     LayerIO io{};
     io.l = &dr.layer;
@@ -913,7 +926,7 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     // pass stops there, without attention, o projection or MLP.
     launch_draft_catchup_in(st.in<uint32_t>(st.o_tokens), st.in<uint32_t>(st.o_tin), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), last_tap(),
                             dr.carry.as<float>(), model.embed, n, d, x, xb, dr.cpos.as<uint32_t>(), stream);
-    fc(n);
+    io.h_ready = fc(n);
     io.n = n;
     io.meta = s.meta.as<uint32_t>();
     io.tin = st.in<uint32_t>(st.o_tin);
@@ -950,12 +963,14 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
         launch_draft_pass_in(runs, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(),
                              st.out<uint32_t>(st.o_emitted), last_tap(), dr.dfeat.as<float>(), model.embed, nr, d, md.vocab, i, cfg.max_seq_len, x, xb,
                              dr.dmeta.as<uint32_t>(), dr.dtin.as<uint32_t>(), dr.dvis.as<uint32_t>(), dr.dcpos.as<uint32_t>(), dr.live.as<uint32_t>(), stream);
-        fc(nr);
+        io.h_ready = fc(nr);
         encode_layer_io(io);
         // The pass's normed output is the next pass's feature (rounded like a tap); the head reads the raw rows and 1/rms.
         launch_prep_rows(h, nullptr, nr, d, md.eps, dr.dfeat.as<float>(), nullptr, nullptr, true, true, stream);
         float* lg = dr.logits.as<float>() + size_t(i - 1) * cfg.max_seqs * dr.v;
-        if (use_gemm(dr.head, nr)) {
+        if (use_gemm(dr.head, nr) && layer_carries(dr.layer, nr)) {
+            matmul_gemm(dr.head, nr, s.h_b.as<uint16_t>(), lg, nullptr, EPI_HEAD, nullptr, nullptr, dr.v, nullptr, nullptr, s.ssq.as<float>());
+        } else if (use_gemm(dr.head, nr)) {
             launch_prep_rows(h, nullptr, nr, d, md.eps, nullptr, dr.hfin_b.as<uint16_t>(), dr.inv.as<float>(), false, false, stream);
             matmul_gemm(dr.head, nr, dr.hfin_b.as<uint16_t>(), lg, nullptr, EPI_HEAD, nullptr, dr.inv.as<float>(), dr.v);
         } else {

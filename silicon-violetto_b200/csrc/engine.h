@@ -53,6 +53,7 @@ struct PlanRun {
 struct Plan {
     uint32_t n = 0, n_head = 0, n_hidden = 0, n_runs = 0, tiles = 0, max_run = 0;
     bool branches = false;
+    bool head_all = false;  // every row of the step goes through the head, in order
     uint32_t ctiles = 0;   // chunk tiles of at most 64 rows (the prefill attention's blocks)
     bool chunked = false;  // some run is longer than VERIFY_T rows: the step's attention is the chunk kernel (encode.rs:299-355)
     uint32_t keys_per_split = 0, max_splits = 1;  // the attention's key split
@@ -235,6 +236,8 @@ class Engine {
     void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
                      uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr, float* ssq_out = nullptr, const float* ssq_in = nullptr);
     bool use_gemm(const Matrix& w, uint32_t n) const;
+    // A layer of n tokens runs on the tensor-core GEMM and its last projection leaves bf16(h) in h_b and h's sums of squares in ssq.
+    bool layer_carries(const Layer& l, uint32_t n) const;
     // What a decoder layer runs on: its weights, the step layout (device arrays), the cache it writes and reads.
     struct LayerIO {
         const Layer* l;

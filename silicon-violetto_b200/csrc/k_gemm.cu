@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 :
 #pragma unroll
         for (uint32_t j = 0; j < NTOK; j++) {
             inv[j] = inv_s[t0 + j];
-            base[j] = (EPI == EPI_RESID && valid && t0 + j < m.n) ? m.base[size_t(t0 + j) * m.m + row] : 0.0f;
+            base[j] = (EPI == EPI_RESID && m.base && valid && t0 + j < m.n) ? m.base[size_t(t0 + j) * m.m + row] : 0.0f;  // (no base: the sum alone, for its bf16 copy and sums of squares)
         }
 #pragma unroll
         for (uint32_t j = 0; j < NTOK; j++) {
