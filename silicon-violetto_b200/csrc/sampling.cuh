@@ -67,19 +67,12 @@ __device__ inline void sc_scan(float v, uint32_t buf, ScExchange* xc, float* val
 // 1024 owns ids vt, vt + 1024, ...; the one thread whose interval holds the target re-adds its terms in order until they
 // pass it, its warp evaluating 32 of them at a time. `fallback` if the weights sum to 0 or the target falls past the last
 // term. xc->pick[pb] must hold NO_TOK in every block on entry. Every block of the cluster returns the same id.
-// `wb(i0, e)`: the B weights of ids i0, i0 + 1024, ... into e -- the caller's chance to issue a batch's loads together.
-template <int B, typename W, typename WB>
-__device__ inline uint32_t sc_inverse_cdf_batched(uint32_t vocab, W w, WB wb, float u, uint32_t fallback, ScExchange* xc, uint32_t buf, uint32_t pb, float* vals, float* pre,
-                                           float* tot_all, float* base, uint32_t rank, uint32_t tid) {
+// This is the part after a thread's whole batches (sc_inverse_cdf and sc_inverse_cdf_batched below): `a` is its sum so
+// far, `i0` its next id.
+template <typename W>
+__device__ inline uint32_t sc_inverse_cdf_rest(uint32_t vocab, W w, float a, uint32_t i0, float u, uint32_t fallback, ScExchange* xc, uint32_t buf, uint32_t pb, float* vals,
+                                        float* pre, float* tot_all, float* base, uint32_t rank, uint32_t tid) {
     const uint32_t lane = tid % 32, vt = rank * SC_THREADS + tid;
-    float a = 0.0f;
-    uint32_t i0 = vt;
-    for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {  // B weights' loads in flight, the additions in id order
-        float e[B];
-        wb(i0, e);
-#pragma unroll
-        for (int u = 0; u < B; u++) a = __fadd_rn(a, e[u]);
-    }
     for (; i0 < vocab; i0 += SAMPLE_THREADS) a = __fadd_rn(a, w(i0));
     float lo, hi, total;
     sc_scan(a, buf, xc, vals, pre, tot_all, base, rank, tid, lo, hi, total);
@@ -118,11 +111,32 @@ __device__ inline uint32_t sc_inverse_cdf_batched(uint32_t vocab, W w, WB wb, fl
 template <int B = 8, typename W>
 __device__ inline uint32_t sc_inverse_cdf(uint32_t vocab, W w, float u, uint32_t fallback, ScExchange* xc, uint32_t buf, uint32_t pb, float* vals, float* pre, float* tot_all,
                                    float* base, uint32_t rank, uint32_t tid) {
-    auto wb = [&](uint32_t i0, float (&e)[B]) {
+    float a = 0.0f;
+    uint32_t i0 = rank * SC_THREADS + tid;
+    for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {  // B weights' loads in flight, the additions in id order
+        float e[B];
 #pragma unroll
-        for (int u = 0; u < B; u++) e[u] = w(i0 + u * SAMPLE_THREADS);
-    };
-    return sc_inverse_cdf_batched<B>(vocab, w, wb, u, fallback, xc, buf, pb, vals, pre, tot_all, base, rank, tid);
+        for (int k = 0; k < B; k++) e[k] = w(i0 + k * SAMPLE_THREADS);
+#pragma unroll
+        for (int k = 0; k < B; k++) a = __fadd_rn(a, e[k]);
+    }
+    return sc_inverse_cdf_rest(vocab, w, a, i0, u, fallback, xc, buf, pb, vals, pre, tot_all, base, rank, tid);
+}
+
+// The same with the batches evaluated by `wb(i0, e)` -- the B weights of ids i0, i0 + 1024, ... into e -- which lets the
+// caller issue a batch's loads in rounds of its own (a weight that needs a load through another load's result).
+template <int B, typename W, typename WB>
+__device__ inline uint32_t sc_inverse_cdf_batched(uint32_t vocab, W w, WB wb, float u, uint32_t fallback, ScExchange* xc, uint32_t buf, uint32_t pb, float* vals, float* pre,
+                                           float* tot_all, float* base, uint32_t rank, uint32_t tid) {
+    float a = 0.0f;
+    uint32_t i0 = rank * SC_THREADS + tid;
+    for (; i0 + (B - 1) * SAMPLE_THREADS < vocab; i0 += B * SAMPLE_THREADS) {
+        float e[B];
+        wb(i0, e);
+#pragma unroll
+        for (int k = 0; k < B; k++) a = __fadd_rn(a, e[k]);
+    }
+    return sc_inverse_cdf_rest(vocab, w, a, i0, u, fallback, xc, buf, pb, vals, pre, tot_all, base, rank, tid);
 }
 
 }  // namespace vlt
