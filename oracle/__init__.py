@@ -340,3 +340,52 @@ class Engine:
             return np.zeros(0, np.uint32)
         dt = np.float32 if name in self._F32 else np.uint16 if name in self._U16 else np.uint32
         return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(n * np.dtype(dt).itemsize,)).view(dt).copy()
+
+
+class BlockDrafter:
+    """block_drafter.hpp stand-alone: the reference's block drafter (tools/spec/drafter.py as engine/src/engine/drafter.rs
+    runs it) on features and blocks the caller supplies."""
+    _U16 = ("k_ring", "v_ring")
+    _U32 = ("vocab",)
+
+    def __init__(self, path, eps: float, scale: float, rope_freq, max_seqs: int = 1, max_chunk: int = 64):
+        f = lib()
+        f.orc_block_new.restype = C.c_void_p
+        f.orc_block_array.restype = C.c_uint64
+        freq = np.ascontiguousarray(rope_freq, np.float32)
+        assert freq.size == 32
+        self.h = C.c_void_p(f.orc_block_new(str(path).encode(), C.c_float(eps), C.c_float(scale), _p(freq), C.c_uint32(max_seqs), C.c_uint32(max_chunk)))
+        if not self.h.value:
+            raise RuntimeError(_err())
+        d = np.zeros(8, np.uint32)
+        f.orc_block_desc(self.h, _p(d))
+        self.n_layers, self.n_taps, self.block, self.window, self.v, self.hidden, self.ffn, self.ring = (int(x) for x in d)
+
+    def close(self):
+        if self.h.value:
+            lib().orc_block_free(self.h)
+            self.h = C.c_void_p()
+
+    def context(self, taps, meta, on_path=None):
+        """taps [n_taps][n][hidden] fp32 holding bf16 values; meta [n][2] (slot, position)."""
+        taps = np.ascontiguousarray(taps, np.float32)
+        meta = np.ascontiguousarray(meta, np.uint32)
+        n = taps.shape[1]
+        op = None if on_path is None else np.ascontiguousarray(on_path, np.uint32)
+        if lib().orc_block_context(self.h, C.c_uint32(n), _p(taps), _p(meta), None if op is None else _p(op)):
+            raise RuntimeError(_err())
+
+    def run(self, slots, rows, p0, bonus_rows):
+        """Blocks (slot, rows, the bonus token's position) with the bonus tokens' embedding rows [blocks][hidden] as bf16 bits."""
+        slots, rows, p0 = (np.ascontiguousarray(x, np.uint32) for x in (slots, rows, p0))
+        bonus = np.ascontiguousarray(bonus_rows, np.uint16)
+        if lib().orc_block_run(self.h, C.c_uint32(len(slots)), _p(slots), _p(rows), _p(p0), _p(bonus)):
+            raise RuntimeError(_err())
+
+    def array(self, name: str) -> np.ndarray:
+        ptr = C.c_void_p()
+        n = lib().orc_block_array(self.h, name.encode(), C.byref(ptr))
+        if not ptr.value:
+            return np.zeros(0, np.float32)
+        dt = np.uint16 if name in self._U16 else np.uint32 if name in self._U32 else np.float32
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(n * np.dtype(dt).itemsize,)).view(dt).copy()

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <string>
 
+#include "block_drafter.hpp"
 #include "model.hpp"
 
 using namespace orc;
@@ -220,6 +221,53 @@ void orc_model_desc(void* h, uint32_t* out12) {
     const uint32_t v[12] = {m.n_layers, m.d, m.n_heads, m.n_kv, m.hd, m.ffn, m.vocab, m.vocab_real, m.page, f2u(m.eps), f2u(m.attn_scale),
                             static_cast<Engine*>(h)->n_pages};
     std::memcpy(out12, v, sizeof v);
+}
+
+// ---- the reference's block drafter, stand-alone (block_drafter.hpp)
+void* orc_block_new(const char* path, float eps, float scale, const float* freq32, uint32_t max_seqs, uint32_t max_chunk) {
+    try {
+        auto b = std::make_unique<BlockDrafter>(path, eps, scale, std::vector<float>(freq32, freq32 + 32));
+        b->init_state(max_seqs, max_chunk);
+        return b.release();
+    } catch (const std::exception& e) { fail(e); return nullptr; }
+}
+void orc_block_free(void* h) { delete static_cast<BlockDrafter*>(h); }
+void orc_block_desc(void* h, uint32_t* out8) {
+    const BlockDrafter* b = static_cast<BlockDrafter*>(h);
+    const uint32_t v[8] = {b->n_layers, b->n_taps, b->block, b->window, b->v, b->H, b->FFN, b->ring};
+    std::memcpy(out8, v, sizeof v);
+}
+// taps [n_taps][n][H] fp32 (bf16 values); meta [n][2] (slot, position); on_path [n] or NULL.
+int orc_block_context(void* h, uint32_t n, const float* taps, const uint32_t* meta, const uint32_t* on_path) {
+    try {
+        BlockDrafter* b = static_cast<BlockDrafter*>(h);
+        std::vector<const float*> rows;
+        for (uint32_t k = 0; k < b->n_taps; k++) rows.push_back(taps + size_t(k) * n * b->H);
+        b->context(n, rows, meta, on_path);
+        return 0;
+    } catch (const std::exception& e) { return fail(e); }
+}
+// Per block: slot, rows, the bonus token's position, its embedding row ([n_blocks][H] bf16).
+int orc_block_run(void* h, uint32_t n_blocks, const uint32_t* slots, const uint32_t* rows, const uint32_t* p0, const uint16_t* bonus_rows) {
+    try {
+        BlockDrafter* b = static_cast<BlockDrafter*>(h);
+        std::vector<BlockDrafter::Block> bl;
+        for (uint32_t i = 0; i < n_blocks; i++) bl.push_back(BlockDrafter::Block{slots[i], rows[i], p0[i], bonus_rows + size_t(i) * b->H});
+        b->blocks(bl);
+        return 0;
+    } catch (const std::exception& e) { return fail(e); }
+}
+uint64_t orc_block_array(void* h, const char* name, const void** ptr) {
+    BlockDrafter* b = static_cast<BlockDrafter*>(h);
+    const std::string n = name;
+    if (n == "hfin") { *ptr = b->hfin.data(); return b->hfin.size(); }
+    if (n == "logits") { *ptr = b->logits.data(); return b->logits.size(); }
+    if (n == "ctx_ring") { *ptr = b->ctx_ring.data(); return b->ctx_ring.size(); }
+    if (n == "k_ring") { *ptr = b->k_ring.data(); return b->k_ring.size(); }
+    if (n == "v_ring") { *ptr = b->v_ring.data(); return b->v_ring.size(); }
+    if (n == "vocab") { *ptr = b->vocab.data(); return b->vocab.size(); }
+    *ptr = nullptr;
+    return 0;
 }
 
 }  // extern "C"

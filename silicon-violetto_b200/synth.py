@@ -114,3 +114,92 @@ def lcg_ids(n: int, seed: int, vocab: int) -> np.ndarray:
         x = (x * a + c) & mask
         out[i] = (x >> 33) % vocab
     return out
+
+
+# ------------------------------------------------------------------ the reference's block drafter
+# tools/spec/drafter.py's model (fc over the tapped layers, inject, a mask embedding, layers with four two-tap
+# convolutions each, a head over a draft vocabulary) as the file tools/spec/export.py writes. The reference fixes the
+# shapes to its target's local layers (hidden 1280, 10 query / 2 kv heads of 128, FFN 3328); here the hidden width is
+# a parameter (it has to be the target's), heads stay 128 wide with 2 kv heads.
+BLOCK_HEAD_DIM, BLOCK_KV_HEADS, CONV_GROUP, CONV_ROWS = 128, 2, 16, 192
+
+
+def block_drafter_state(seed: int = 0, hidden: int = 1280, ffn: int = 3328, layers: int = 2, taps=(35, 47), draft_vocab: int = 16384,
+                        target_vocab: int = 151667) -> dict:
+    """A random drafter with nothing at its initial zero or identity, in values bf16 keeps exactly (the recipe of
+    tools/spec/check_engine.py:47-62 `random_drafter`, from numpy's generator), keyed like the reference module's
+    state_dict so that the same arrays load into tools/spec/drafter.py `Drafter`."""
+    rng = np.random.default_rng(seed)
+    nq = hidden // BLOCK_HEAD_DIM
+
+    def lin(m, k, std=None):  # nn.Linear's default range, halved, bf16-exact
+        bound = 1.0 / np.sqrt(k)
+        w = rng.uniform(-bound, bound, (m, k)) if std is None else rng.normal(0.0, std, (m, k))
+        return vlt.from_bf16(vlt.to_bf16((0.5 * w).astype(np.float32)))
+
+    def vec(x):
+        return vlt.from_bf16(vlt.to_bf16((0.5 * np.asarray(x)).astype(np.float32)))
+
+    sd = {"fc.weight": lin(hidden, len(taps) * hidden), "inject.weight": lin(hidden, hidden, 0.05), "mask_emb": vec(rng.normal(0.0, 0.02, hidden))}
+    for i in range(layers):
+        p = f"layers.{i}."
+        for c in range(4):
+            base = np.stack([np.ones(hidden), np.zeros(hidden)]) + rng.normal(0.0, 0.3, (2, hidden))
+            sd[f"{p}convs.{c}.base"] = vec(base)
+            sd[f"{p}convs.{c}.corr.weight"] = lin(2 * hidden // CONV_GROUP, hidden, 0.05)
+        sd[p + "wq.weight"] = lin(nq * BLOCK_HEAD_DIM, hidden)
+        sd[p + "wk.weight"] = lin(BLOCK_KV_HEADS * BLOCK_HEAD_DIM, hidden)
+        sd[p + "wv.weight"] = lin(BLOCK_KV_HEADS * BLOCK_HEAD_DIM, hidden)
+        sd[p + "wo.weight"] = lin(hidden, nq * BLOCK_HEAD_DIM)
+        sd[p + "wgu.weight"] = lin(2 * ffn, hidden)
+        sd[p + "wd.weight"] = lin(hidden, ffn)
+    sd["head.weight"] = lin(draft_vocab, hidden)
+    sd["out_gain"] = vec(rng.uniform(0.5, 1.5, hidden))
+    sd["vocab"] = np.sort(rng.permutation(target_vocab)[:draft_vocab]).astype(np.int64)
+    sd["_meta"] = dict(layers=layers, taps=tuple(taps), hidden=hidden, ffn=ffn)
+    return sd
+
+
+def write_block_drafter(path, sd: dict, int8: bool = False, block: int = 8, window: int = 1024) -> None:
+    """tools/spec/export.py:17-55: fc split per tap, the layers' q | k | v stacked, every layer's k | v rows again as
+    `kv_all` (the context goes through all of them at once), the convolutions' corrections padded to 192 rows, the
+    output gain folded into the head's columns, `vocab` and `meta` as f32; matrices bf16, or int8 in groups of 64 (the
+    head: 8)."""
+    m = sd["_meta"]
+    hidden, layers, taps = m["hidden"], m["layers"], m["taps"]
+    out: dict = {}
+
+    def matrix(name, w, group=64):
+        _put(out, name, np.ascontiguousarray(w, np.float32), group if int8 else None)
+
+    for k in range(len(taps)):
+        matrix(f"fc.{k}", sd["fc.weight"][:, k * hidden:(k + 1) * hidden])
+    out["mask_emb"] = np.ascontiguousarray(sd["mask_emb"], np.float32)
+    matrix("inject", sd["inject.weight"])
+    for i in range(layers):
+        p = f"layers.{i}."
+        matrix(f"D{i:02d}.qkv", np.concatenate([sd[p + "wq.weight"], sd[p + "wk.weight"], sd[p + "wv.weight"]]))
+        matrix(f"D{i:02d}.o", sd[p + "wo.weight"])
+        matrix(f"D{i:02d}.gate_up", sd[p + "wgu.weight"])
+        matrix(f"D{i:02d}.down", sd[p + "wd.weight"])
+        for c in range(4):
+            out[f"D{i:02d}.conv{c}.base"] = np.ascontiguousarray(sd[f"{p}convs.{c}.base"], np.float32)
+            corr = sd[f"{p}convs.{c}.corr.weight"]
+            matrix(f"D{i:02d}.conv{c}.corr", np.concatenate([corr, np.zeros((CONV_ROWS - len(corr), hidden), np.float32)]))
+    matrix("kv_all", np.concatenate([sd[f"layers.{i}.{w}.weight"] for i in range(layers) for w in ("wk", "wv")]))
+    matrix("head", sd["head.weight"] * sd["out_gain"][None], 8)
+    out["vocab"] = sd["vocab"].astype(np.float32)
+    out["meta"] = np.array([layers, len(taps), block, window, len(sd["vocab"]), *taps], dtype=np.float32)
+    vlt.write(path, out)
+
+
+def block_case_inputs(seed: int, n_ctx: int, hidden: int = 1280, n_taps: int = 2):
+    """Seeded inputs of one block-drafter case: the tapped features of `n_ctx` context positions
+    ([n_ctx][n_taps][hidden], rms-normed and rounded to bf16 as the target's taps are) and the bonus token's
+    embedding row ([hidden], bf16 values)."""
+    rng = np.random.default_rng(seed)
+    f = rng.normal(0.0, 1.0, (n_ctx, n_taps, hidden)).astype(np.float32)
+    f = f / np.sqrt((f * f).mean(axis=-1, keepdims=True) + np.float32(2.0 ** -23))
+    feat = vlt.from_bf16(vlt.to_bf16(f.astype(np.float32)))
+    emb = vlt.from_bf16(vlt.to_bf16(rng.normal(0.0, 0.02, hidden).astype(np.float32)))
+    return feat, emb
