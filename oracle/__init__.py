@@ -330,8 +330,8 @@ class Engine:
             raise RuntimeError(_err())
 
     _F32 = ("logits", "hidden_out", "taps", "draft_logits", "carry", "q_keep", "taps_all", "cap_resid_in", "cap_attn_in", "cap_qkv", "cap_sdpa_out", "cap_attn_out",
-            "cap_mlp_in", "cap_mlp_out")
-    _U16 = ("k_cache", "v_cache", "draft_k_cache", "draft_v_cache")
+            "cap_mlp_in", "cap_mlp_out", "block_logits", "block_hfin", "block_ctx_ring")
+    _U16 = ("k_cache", "v_cache", "draft_k_cache", "draft_v_cache", "block_k_ring", "block_v_ring")
 
     def array(self, name: str) -> np.ndarray:
         ptr = C.c_void_p()

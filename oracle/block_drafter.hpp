@@ -24,7 +24,7 @@
 #include <string>
 #include <vector>
 
-#include "model.hpp"
+#include "linear.hpp"
 
 namespace orc {
 

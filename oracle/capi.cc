@@ -195,6 +195,14 @@ uint64_t orc_array(void* h, const char* name, const void** ptr) {
     if (n == "carry" && e->drafter) { *ptr = e->drafter->carry.data(); return e->drafter->carry.size(); }
     if (n == "q_rows" && e->drafter) { *ptr = e->drafter->q_rows.data(); return e->drafter->q_rows.size(); }
     if (n == "q_keep" && e->drafter) { *ptr = e->drafter->q_keep.data(); return e->drafter->q_keep.size(); }
+    if (e->block_drafter) {
+        BlockDrafter& b = *e->block_drafter;
+        if (n == "block_logits") { *ptr = b.logits.data(); return b.logits.size(); }
+        if (n == "block_hfin") { *ptr = b.hfin.data(); return b.hfin.size(); }
+        if (n == "block_ctx_ring") { *ptr = b.ctx_ring.data(); return b.ctx_ring.size(); }
+        if (n == "block_k_ring") { *ptr = b.k_ring.data(); return b.k_ring.size(); }
+        if (n == "block_v_ring") { *ptr = b.v_ring.data(); return b.v_ring.size(); }
+    }
     if (n == "gen") { *ptr = e->gen.data(); return e->gen.size() * sizeof(GenState) / 4; }
     if (n == "runs") { *ptr = e->runs.data(); return e->runs.size() * 6; }
     if (n == "sample_rows") { *ptr = e->sample_rows.data(); return e->sample_rows.size() * 6; }

@@ -32,102 +32,12 @@
 #include <vector>
 
 #include "bits.hpp"
+#include "block_drafter.hpp"
+#include "linear.hpp"
 #include "sampling.hpp"
 #include "vlt.hpp"
 
 namespace orc {
-
-struct ModelDesc {
-    uint32_t n_layers, d, n_heads, n_kv, hd, ffn, vocab, vocab_real;
-    float eps;
-    uint32_t page;
-    float attn_scale;
-    uint32_t qkv_w() const { return (n_heads + 2 * n_kv) * hd; }
-};
-
-struct Matrix {
-    const uint8_t* w = nullptr;
-    const uint16_t* scales = nullptr;  // int8 only: [m][k / group]
-    uint32_t m = 0, k = 0, group = 0;
-    bool int8 = false;
-};
-
-// engine/src/model.rs:81-103 `matrix`: bf16, or int8 with `<name>.scale`. The reference accepts
-// groups of 8..256; a whole row per scale (group = k) is accepted here as well.
-inline Matrix load_matrix(const VltFile& f, const std::string& name, uint32_t m, uint32_t k) {
-    const Tensor& t = f.tensor(name);
-    Matrix out;
-    out.m = m;
-    out.k = k;
-    if (t.dtype != I8) {
-        out.w = f.ptr(f.get(name, BF16, {m, k}));
-        return out;
-    }
-    out.w = f.ptr(f.get(name, I8, {m, k}));
-    const Tensor& s = f.tensor(name + ".scale");
-    const uint32_t groups = s.shape.size() > 1 ? s.shape[1] : 0;
-    const uint32_t group = k / std::max(groups, 1u);
-    if (group < 8 || (groups > 1 && (group & (group - 1))) || group * groups != k) throw std::runtime_error(name + ".scale: bad group count");
-    out.scales = reinterpret_cast<const uint16_t*>(f.ptr(f.get(name + ".scale", BF16, {m, groups})));
-    out.group = group;
-    out.int8 = true;
-    return out;
-}
-
-// acc[t][row] = sum_k W[row][k] * bf16(X[t][k]), int8 groups scaled as they are added.
-inline void matmul_raw(const Matrix& W, const float* X, uint32_t n, float* acc) {
-    std::vector<float> xb(size_t(n) * W.k);
-    for (size_t i = 0; i < xb.size(); i++) xb[i] = round_bf16(X[i]);
-#pragma omp parallel
-    {
-        std::vector<float> wr(W.k);
-#pragma omp for schedule(static)
-        for (int64_t r = 0; r < int64_t(W.m); r++) {
-            if (W.int8) {
-                const int8_t* q = reinterpret_cast<const int8_t*>(W.w) + uint64_t(r) * W.k;
-                for (uint32_t i = 0; i < W.k; i++) wr[i] = float(q[i]);
-            } else {
-                const uint16_t* b = reinterpret_cast<const uint16_t*>(W.w) + uint64_t(r) * W.k;
-                for (uint32_t i = 0; i < W.k; i++) wr[i] = bf16_to_f32(b[i]);
-            }
-            const uint32_t group = W.int8 ? W.group : W.k, ng = W.k / group;
-            for (uint32_t t = 0; t < n; t++) {
-                const float* x = xb.data() + size_t(t) * W.k;
-                float total = 0.0f;
-                for (uint32_t g = 0; g < ng; g++) {
-                    float a = 0.0f;
-#pragma omp simd reduction(+ : a)
-                    for (uint32_t i = g * group; i < (g + 1) * group; i++) a += wr[i] * x[i];
-                    total += W.int8 ? a * bf16_to_f32(W.scales[uint64_t(r) * ng + g]) : a;
-                }
-                acc[size_t(t) * W.m + r] = total;
-            }
-        }
-    }
-}
-
-// engine.rs:392-409 `rope_table`: theta = float32(pos) * frequency; cos, sin rounded to bf16.
-inline void rope_cs(uint32_t pos, float freq, float& c, float& s) {
-    const float theta = float(pos) * freq;
-    c = round_bf16(std::cos(theta));
-    s = round_bf16(std::sin(theta));
-}
-// kernels.metal:727-736 `norm_rope` without the norm: interleaved pairs, in place; cs [hd/2][2].
-inline void rope_pairs(float* v, uint32_t hd, const float* cs) {
-    for (uint32_t i = 0; i < hd / 2; i++) {
-        const float c = cs[2 * i], s = cs[2 * i + 1], a0 = v[2 * i], a1 = v[2 * i + 1];
-        v[2 * i] = c * a0 + s * a1;
-        v[2 * i + 1] = c * a1 - s * a0;
-    }
-}
-
-inline void inv_rms(const float* X, uint32_t n, uint32_t k, float eps, float* inv) {
-    for (uint32_t t = 0; t < n; t++) {
-        float ss = 0.0f;
-        for (uint32_t i = 0; i < k; i++) ss += X[size_t(t) * k + i] * X[size_t(t) * k + i];
-        inv[t] = 1.0f / std::sqrt(ss / float(k) + eps);
-    }
-}
 
 struct EngineConfig {
     uint32_t max_seqs = 8, max_step_tokens = 512, max_chunk = 512, kv_tokens = 65536, max_seq_len = 131072,
@@ -191,6 +101,8 @@ struct Engine {
     std::vector<float> logits, hidden_out, taps;  // taps: bf16(rms_norm(last layer's output)) as fp32, [n][d]
     ReplayArgs replay{0, 0, 0.0f, 0};
     std::unique_ptr<Drafter> drafter;
+    std::unique_ptr<BlockDrafter> block_drafter;  // the reference's block drafter (block_drafter.hpp), if that is what was loaded
+    std::vector<float> rope_freq;
     std::vector<float> draft_logits;  // the drafter's passes, [rows - 1][runs][v]; rows of runs that did not draft stay 0
     std::vector<uint32_t> write_mask;  // per step token: does its K/V go to the cache (empty: all do)
     // engine.rs:175-188 `LayerCapture`: with `capture` set, `forward` keeps every target layer's intermediates, [layer][n][width].
@@ -224,6 +136,7 @@ struct Engine {
         }
         // engine.rs:392-421 `rope_table`: theta = float32(pos) * freq, cos and sin rounded to bf16.
         std::vector<float> freq = file.f32s("rope_freq");
+        rope_freq = freq;
         if (freq.size() != md.hd / 2) throw std::runtime_error("rope_freq: expected head_dim / 2 entries");
         const uint32_t npos = cfg.max_seq_len + FEED_W;
         rope.resize(size_t(npos) * md.hd);
@@ -584,6 +497,14 @@ struct Engine {
     void load_drafter(const std::string& path) {
         auto dr = std::make_unique<Drafter>();
         dr->file = VltFile::load(path);
+        if (BlockDrafter::is_block_drafter(dr->file)) {  // engine/src/engine.rs:381-389 with a file of tools/spec/export.py
+            if (md.hd != 64 || md.d % BlockDrafter::D) throw std::runtime_error(path + ": the block drafter needs a target of 64-wide heads whose hidden width is a multiple of 128");
+            block_drafter = std::make_unique<BlockDrafter>(path, md.eps, md.attn_scale, rope_freq);
+            if (block_drafter->H != md.d) throw std::runtime_error(path + ": hidden width " + std::to_string(block_drafter->H) + ", the target's is " + std::to_string(md.d));
+            block_drafter->init_state(cfg.max_seqs, cfg.max_chunk);
+            tap_layers = block_drafter->taps;
+            return;
+        }
         const std::vector<float> m = dr->file.f32s("meta");
         if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw std::runtime_error(path + ": meta is not a version-1 one-layer chain drafter");
         const uint32_t v = uint32_t(m[3]), d = md.d;
@@ -617,7 +538,36 @@ struct Engine {
     // position lens[slot] + i - 1 on token feed[slot][i - 1], its feature the tap of the path's last row
     // (i = 1) or the drafter's own normed output of the pass before, and writes feed[slot][i] = the draft
     // vocabulary's argmax (ties to the lowest index) and tree[slot][i] = chain_node(i).
+    // engine/src/engine/drafter.rs:278-447 `encode_drafter`: the context of the step's tokens (those on the accepted path
+    // reach the rings), a block of `rows` rows for every run with head rows, candidates and a draft tree per block.
+    void block_draft(const Plan& p, uint32_t rows) {
+        BlockDrafter& b = *block_drafter;
+        std::vector<const float*> tap_rows;
+        for (size_t k = 0; k < tap_layers.size(); k++) tap_rows.push_back(taps_all.data() + k * size_t(p.n) * md.d);
+        b.context(p.n, tap_rows, meta.data(), on_path.data());
+        std::vector<BlockDrafter::Block> bl;
+        std::vector<uint32_t> btin, first;
+        for (uint32_t r = 0; r < p.n_runs && rows > 1; r++) {
+            if (runs[r].nhead == 0) continue;
+            const uint32_t slot = runs[r].slot;
+            uint32_t tok = feed[slot * FEED_W];
+            if (tok >= md.vocab) tok = 0;
+            first.push_back(uint32_t(btin.size() / 2));
+            for (uint32_t i = 0; i < rows; i++) { btin.push_back(slot); btin.push_back(i); }
+            bl.push_back(BlockDrafter::Block{slot, rows, lens[slot], embed + size_t(tok) * md.d});
+        }
+        if (bl.empty()) { b.hfin.clear(); b.logits.clear(); return; }
+        b.blocks(bl);
+        const uint32_t R = uint32_t(btin.size() / 2), ncand = std::min(BlockDrafter::CANDS, rows - 1);
+        b.cand.assign(size_t(R) * CANDS, 0);
+        b.cand_q.assign(size_t(R) * CANDS, 0.0f);
+        for (uint32_t r = 0; r < R; r++)
+            if (btin[2 * r + 1]) draft_top_row(b.logits.data() + size_t(r) * b.v, b.v, b.vocab.data(), 1.0f / 0.6f, ncand, b.cand.data() + r * CANDS, b.cand_q.data() + r * CANDS);
+        for (size_t i = 0; i < bl.size(); i++) draft_tree_block(first[i], rows, bl[i].slot, b.cand.data(), b.cand_q.data(), ncand, feed.data(), tree.data());
+    }
+
     void draft(const Plan& p, uint32_t rows) {
+        if (block_drafter) { block_draft(p, rows); return; }
         if (!drafter) throw std::runtime_error("no drafter loaded");
         if (rows < 1 || rows > VERIFY_T) throw std::runtime_error("the chain drafter proposes for 1.." + std::to_string(VERIFY_T) + " rows");
         Drafter& dr = *drafter;

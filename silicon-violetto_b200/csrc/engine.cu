@@ -830,6 +830,11 @@ void Engine::load_drafter(const std::string& path) {
     auto dr = std::make_unique<Drafter>();
     const ModelDesc& md = model.md;
     dr->w.load(path, cfg.host_only);
+    if (dr->w.has("kv_all")) {  // the reference's block drafter (tools/spec/export.py), not the chain drafter
+        dr.reset();
+        load_block_drafter(path);
+        return;
+    }
     const std::vector<float> m = dr->w.f32s("meta");
     if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw Error(path + ": `meta` is not a version-1 one-layer chain drafter");
     const uint32_t v = uint32_t(m[3]), d = md.d;
@@ -889,12 +894,13 @@ void Engine::load_drafter(const std::string& path) {
     drafter = std::move(dr);
     set_taps(tap_layers);  // the drafter reads the last layer's tapped hidden states: it is tapped from now on
 }
-bool Engine::has_drafter() const { return drafter != nullptr; }
+bool Engine::has_drafter() const { return drafter != nullptr || block_drafter != nullptr; }
 
 // The drafter's part of a step (the reference queues its drafter at the same point,
 // engine/src/engine/generate.rs:427-430): a catch-up pass over the step's own tokens that writes the
 // drafter's K/V for the rows on the accepted path, then rows - 1 draft passes of one row per run.
 void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
+    if (block_drafter) { encode_block_drafter(set, p, rows); return; }
     if (!drafter) throw Error("no drafter loaded");
     if (rows < 1 || rows > VERIFY_T) throw Error("the chain drafter proposes for 1.." + std::to_string(VERIFY_T) + " rows");
     Drafter& dr = *drafter;
@@ -988,10 +994,174 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     span_end(sp);
 }
 
+// engine/src/engine/drafter.rs:131-240 `Drafter::load`, for a file of tools/spec/export.py's layout. The reference's
+// shapes are its target's constants; here the hidden width must be the target's, heads are 128 wide, and the file gives
+// the rest. The drafter turns 32 pairs with the engine's RoPE table, so the target's heads must be 64 wide.
+void Engine::load_block_drafter(const std::string& path) {
+    auto d = std::make_unique<BlockDrafter>();
+    const ModelDesc& md = model.md;
+    d->w.load(path, cfg.host_only);
+    const std::vector<float> m = d->w.f32s("meta");
+    if (m.size() < 5 || m.size() != 5 + size_t(m[1])) throw Error(path + ": `meta` is not a block drafter's");
+    const uint32_t n_layers = uint32_t(m[0]), n_taps = uint32_t(m[1]);
+    d->block = uint32_t(m[2]);
+    d->v = uint32_t(m[4]);
+    for (uint32_t k = 0; k < n_taps; k++) d->taps.push_back(uint32_t(m[5 + k]));
+    const uint32_t H = md.d, D = 128;
+    if (H % D || md.hd != 64) throw Error(path + ": the block drafter needs a target of 64-wide heads whose hidden width is a multiple of 128");
+    const uint32_t n_q = H / D, kv_rows = d->w.tensor("kv_all").shape.at(0), n_kv = kv_rows / (n_layers * 2 * D);
+    if (n_layers == 0 || n_kv == 0 || n_kv * n_layers * 2 * D != kv_rows || n_q % n_kv || n_q + n_kv > 32) throw Error(path + ": kv_all's rows do not fit the layers and heads");
+    d->ffn = d->w.tensor("D00.down").shape.at(1);
+    if (H / 16 * 2 > BLOCK_CONV_KC) throw Error(path + ": the convolutions' corrections do not fit 192 rows");
+    for (uint32_t k = 0; k < n_taps; k++) d->fc.push_back(load_matrix(d->w, "fc." + std::to_string(k), H, H));
+    d->kv_all = load_matrix(d->w, "kv_all", kv_rows, H);
+    d->inject = load_matrix(d->w, "inject", H, H);
+    d->head = load_matrix(d->w, "head", d->v, H);
+    const uint8_t* base = d->w.buffer.as<uint8_t>();
+    d->mask_emb = reinterpret_cast<const float*>(base + d->w.get("mask_emb", DType::F32, {H}).offset);
+    for (uint32_t i = 0; i < n_layers; i++) {
+        char nm[48];
+        auto name = [&](const std::string& k) { std::snprintf(nm, sizeof nm, "D%02u.%s", i, k.c_str()); return std::string(nm); };
+        BlockDrafter::DLayer l;
+        l.qkv = load_matrix(d->w, name("qkv"), (n_q + 2 * n_kv) * D, H);
+        l.o = load_matrix(d->w, name("o"), H, n_q * D);
+        l.gate_up = load_matrix(d->w, name("gate_up"), 2 * d->ffn, H);
+        l.down = load_matrix(d->w, name("down"), H, d->ffn);
+        for (uint32_t c = 0; c < 4; c++) {
+            l.conv_base[c] = reinterpret_cast<const float*>(base + d->w.get(name("conv" + std::to_string(c) + ".base"), DType::F32, {2, H}).offset);
+            l.conv_corr[c] = load_matrix(d->w, name("conv" + std::to_string(c) + ".corr"), BLOCK_CONV_KC, H);
+        }
+        d->layers.push_back(l);
+    }
+    const std::vector<float> idf = d->w.f32s("vocab");
+    if (idf.size() != d->v) throw Error(path + ": `vocab` has " + std::to_string(idf.size()) + " ids for a head of " + std::to_string(d->v));
+    std::vector<uint32_t> ids(d->v);
+    for (uint32_t i = 0; i < d->v; i++) {
+        ids[i] = uint32_t(idf[i]);
+        if (ids[i] >= md.vocab) throw Error(path + ": draft vocabulary id out of the target's range");
+    }
+    for (uint32_t t : d->taps)
+        if (t >= md.n_layers) throw Error(path + ": it reads layer " + std::to_string(t) + " of a target with " + std::to_string(md.n_layers));
+    BlockDrafterDims& bd = d->dims;
+    bd.hidden = H; bd.n_q = n_q; bd.n_kv = n_kv; bd.n_layers = n_layers;
+    bd.window = uint32_t(m[3]);
+    bd.ring = bd.window + cfg.max_chunk;  // drafter.rs:175: a step's run is at most max_chunk tokens, so its positions do not collide
+    bd.ctx_ring_len = cfg.max_chunk;
+    bd.max_seqs = cfg.max_seqs;
+    bd.eps = md.eps;
+    bd.scale = md.attn_scale;
+    if (!cfg.host_only) {
+        const size_t n = cfg.max_step_tokens, ms = cfg.max_seqs, rows = ms * VERIFY_T, ring_bytes = size_t(n_layers) * ms * n_kv * bd.ring * D * 2;
+        auto f = [&](Buffer& b, size_t floats) { b.alloc(floats * 4, false); };
+        d->vocab_ids.alloc(size_t(d->v) * 4, false);
+        d->vocab_ids.write(0, ids.data(), size_t(d->v) * 4);
+        d->k_ring.alloc(ring_bytes, false);
+        d->v_ring.alloc(ring_bytes, false);
+        f(d->ctx_ring, ms * bd.ctx_ring_len * H);
+        f(d->ctx, n * H);
+        f(d->ctx_inv, n);
+        f(d->kvp, n * kv_rows);
+        for (Buffer* b : {&d->x, &d->last, &d->cx, &d->co, &d->mixed, &d->hfin}) f(*b, rows * H);
+        f(d->qkv, rows * (n_q + 2 * n_kv) * D);
+        f(d->inv, rows);
+        f(d->attn, rows * n_q * D);
+        f(d->act, rows * d->ffn);
+        f(d->corr, rows * BLOCK_CONV_KC);
+        f(d->corr_inv, rows);
+        f(d->logits, rows * d->v);
+        f(d->cand, rows * 4);
+        f(d->cand_q, rows * 4);
+        f(d->meta, 2 * rows);
+        for (Buffer& b : d->layout) {
+            f(b, 3 * rows + 3 * ms);
+            b.order = stream;
+        }
+    }
+    block_drafter = std::move(d);
+    set_taps(block_drafter->taps);
+}
+
+// engine/src/engine/drafter.rs:278-447 `encode_drafter`: the context of all of the step's tokens (those on the accepted
+// path reach the rings), then a block of `rows` rows for every run of the step that has head rows, then the candidates
+// and a draft tree per block into feed / tree.
+void Engine::encode_block_drafter(uint32_t set, const Plan& p, uint32_t rows) {
+    if (cfg.host_only) throw Error("this engine was created host-only: it plans steps but cannot run them (no CPU path)");
+    if (rows < 1 || rows > VERIFY_T) throw Error("a block has 1.." + std::to_string(VERIFY_T) + " rows");
+    BlockDrafter& d = *block_drafter;
+    const BlockDrafterDims& bd = d.dims;
+    const ModelDesc& md = model.md;
+    StepSet& st = sets[set];
+    const int sp = span_begin(G_DRAFTER);
+    const uint32_t n = p.n, H = bd.hidden;
+    // 1. Context.
+    for (uint32_t k = 0; k < d.fc.size(); k++)
+        matmul(d.fc[k], n, tap_bufs[k].as<float>(), d.ctx.as<float>(), k ? EPI_RESID : EPI_RAW, k ? d.ctx.as<float>() : nullptr, nullptr);
+    matmul(d.kv_all, n, d.ctx.as<float>(), d.kvp.as<float>(), EPI_NORM, nullptr, d.ctx_inv.as<float>());
+    launch_block_context(d.kvp.as<float>(), d.ctx.as<float>(), d.ctx_inv.as<float>(), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), rope_tab.as<float>(), bd, n,
+                         d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), d.ctx_ring.as<float>(), stream);
+    // 2. The blocks' layout, from the step's runs (the host's copy of what the step uploaded).
+    const RunIn* runs = st.hin<RunIn>(st.o_runs);
+    const size_t max_rows = size_t(cfg.max_seqs) * VERIFY_T;
+    std::vector<uint32_t> lay(3 * max_rows + 3 * size_t(cfg.max_seqs), 0);
+    uint32_t* tin = lay.data();
+    uint32_t* rows_of = tin + 2 * max_rows;
+    uint32_t* blocks = rows_of + max_rows;
+    uint32_t* slots = blocks + 2 * cfg.max_seqs;
+    uint32_t R = 0, nb = 0;
+    for (uint32_t r = 0; r < p.n_runs && rows > 1; r++) {
+        if (runs[r].nhead == 0 || nb == cfg.max_seqs) continue;
+        blocks[2 * nb] = R;
+        blocks[2 * nb + 1] = rows;
+        slots[nb++] = runs[r].slot;
+        for (uint32_t i = 0; i < rows; i++, R++) {
+            tin[2 * R] = runs[r].slot;
+            tin[2 * R + 1] = i;
+            rows_of[R] = rows;
+        }
+    }
+    d.last_rows = R;
+    if (R == 0) { span_end(sp); return; }
+    Buffer& lb = d.layout[set];
+    lb.write(0, lay.data(), lay.size() * 4);
+    const uint32_t* d_tin = lb.as<uint32_t>();
+    const uint32_t* d_rows_of = d_tin + 2 * max_rows;
+    const uint32_t* d_blocks = d_rows_of + max_rows;
+    const uint32_t* d_slots = d_blocks + 2 * cfg.max_seqs;
+    float* x = d.x.as<float>();
+    launch_block_embed(model.embed, d_tin, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), d.mask_emb, d.ctx_ring.as<float>(), bd, md.vocab, R, x, d.last.as<float>(),
+                       d.meta.as<uint32_t>(), stream);
+    matmul(d.inject, R, d.last.as<float>(), x, EPI_RESID, x, nullptr);
+    // out = resid + conv(in) within each block (or conv(in) alone): the corrections through a matmul, then the two taps.
+    auto conv = [&](const BlockDrafter::DLayer& l, uint32_t c, const float* in, const float* resid, float* out) {
+        matmul(l.conv_corr[c], R, in, d.corr.as<float>(), EPI_NORM, nullptr, d.corr_inv.as<float>());
+        launch_block_conv(in, d.corr.as<float>(), l.conv_base[c], d_tin, resid, H, R, out, stream);
+    };
+    for (uint32_t li = 0; li < d.layers.size(); li++) {
+        const BlockDrafter::DLayer& l = d.layers[li];
+        conv(l, 0, x, nullptr, d.cx.as<float>());
+        matmul(l.qkv, R, d.cx.as<float>(), d.qkv.as<float>(), EPI_NORM, nullptr, d.inv.as<float>());
+        launch_block_qkv_post(d.qkv.as<float>(), d.meta.as<uint32_t>(), rope_tab.as<float>(), bd, li, R, d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), stream);
+        launch_block_attn(d.qkv.as<float>(), d.meta.as<uint32_t>(), d_tin, d_rows_of, d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), bd, li, R, d.attn.as<float>(), stream);
+        matmul(l.o, R, d.attn.as<float>(), d.co.as<float>(), EPI_RAW, nullptr, nullptr);
+        conv(l, 1, d.co.as<float>(), x, d.mixed.as<float>());
+        conv(l, 2, d.mixed.as<float>(), nullptr, d.cx.as<float>());
+        matmul(l.gate_up, R, d.cx.as<float>(), d.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+        matmul(l.down, R, d.act.as<float>(), d.co.as<float>(), EPI_RAW, nullptr, nullptr);
+        conv(l, 3, d.co.as<float>(), d.mixed.as<float>(), x);
+    }
+    // 3. Raw logits (drafter.rs:418-419: through the target's cap a trained drafter's largest would tie), candidates, trees.
+    launch_prep_rows(x, nullptr, R, H, md.eps, d.hfin.as<float>(), nullptr, nullptr, true, false, stream);
+    matmul(d.head, R, d.hfin.as<float>(), d.logits.as<float>(), EPI_RAW, nullptr, nullptr);
+    const uint32_t ncand = std::min(4u, rows - 1);
+    launch_draft_top(d.logits.as<float>(), R, d.v, d.vocab_ids.as<uint32_t>(), d_tin, 1.0f / 0.6f, ncand, d.cand.as<uint32_t>(), d.cand_q.as<float>(), stream);
+    launch_draft_tree(d_blocks, d_slots, nb, d.cand.as<uint32_t>(), d.cand_q.as<float>(), ncand, s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), stream);
+    span_end(sp);
+}
+
 StepOutput Engine::step_runs(const std::vector<PlanRun>& runs, const StepOptions& opts, const ReplayArgs* replay) {
     Plan p = plan(0, runs, opts.hidden);
     encode_forward(0, p);
-    if (debug_draft_rows && drafter) encode_drafter(0, p, debug_draft_rows);
+    if (debug_draft_rows && has_drafter()) encode_drafter(0, p, debug_draft_rows);
     if (replay) encode_replay(0, p, *replay);
     commit(0);
     const double secs = wait(0);
@@ -1291,6 +1461,14 @@ std::vector<uint32_t> Engine::debug_read(const std::string& name) {
         if (name == "q_keep") return whole(drafter->q_keep, ms * (VERIFY_T - 1) * size_t(drafter->v));
         if (name == "draft_k_cache") return whole(drafter->k, pool / 2);  // bf16 pairs
         if (name == "draft_v_cache") return whole(drafter->v_cache, pool / 2);
+    }
+    if (block_drafter) {
+        const BlockDrafter& b = *block_drafter;
+        if (name == "block_logits") return whole(b.logits, size_t(b.last_rows) * b.v);  // [block row][v] f32
+        if (name == "block_hfin") return whole(b.hfin, size_t(b.last_rows) * b.dims.hidden);
+        if (name == "block_ctx_ring") return whole(b.ctx_ring, b.ctx_ring.bytes / 4);
+        if (name == "block_k_ring") return whole(b.k_ring, b.k_ring.bytes / 4);  // bf16 pairs
+        if (name == "block_v_ring") return whole(b.v_ring, b.v_ring.bytes / 4);
     }
     const StepSet& st = sets[0];
     auto in = [&](size_t off, size_t words) {

@@ -226,6 +226,32 @@ class Engine {
         AttnMaps maps;
     };
     std::unique_ptr<Drafter> drafter;
+    // The reference's block drafter (engine/src/engine/drafter.rs:52-100): a file of tools/spec/export.py's layout, the
+    // context's keys and values in rings per (layer, slot), the normed context in a ring per slot, scratch for a step's
+    // context and for its block rows.
+    struct BlockDrafter {
+        Weights w;
+        std::vector<Matrix> fc;
+        Matrix kv_all, inject, head;
+        const float* mask_emb = nullptr;
+        struct DLayer {
+            Matrix qkv, o, gate_up, down;
+            const float* conv_base[4];
+            Matrix conv_corr[4];
+        };
+        std::vector<DLayer> layers;
+        std::vector<uint32_t> taps;
+        uint32_t v = 0, block = 0, ffn = 0;
+        BlockDrafterDims dims{};
+        Buffer vocab_ids, k_ring, v_ring, ctx_ring;
+        Buffer ctx, ctx_inv, kvp;                                                                 // per step token
+        Buffer x, last, cx, co, mixed, qkv, inv, attn, act, corr, corr_inv, hfin, logits, cand, cand_q, meta;  // per block row
+        Buffer layout[3];  // per step set: tin [rows][2] | rows_of [rows] | blocks [max_seqs][2] | slots [max_seqs]
+        uint32_t last_rows = 0;  // the last pass's block rows (debug reads)
+    };
+    std::unique_ptr<BlockDrafter> block_drafter;
+    void load_block_drafter(const std::string& path);
+    void encode_block_drafter(uint32_t set, const Plan& p, uint32_t rows);
 
   private:
     KvArgs kv_args() const;

@@ -135,6 +135,24 @@ void launch_draft_top(const float* logits, uint32_t n_rows, uint32_t nv, const u
 void launch_draft_tree(const uint32_t* blocks, const uint32_t* slots, uint32_t n_blocks, const uint32_t* cand, const float* cand_q, uint32_t ncand, uint32_t* feed,
                        uint32_t* tree, cudaStream_t s);
 
+// The reference's block drafter (k_block.cu): its shapes and state sizes, and its own kernels.
+struct BlockDrafterDims {
+    uint32_t hidden, n_q, n_kv, n_layers;  // heads are 128 wide
+    uint32_t ring, max_seqs, window, ctx_ring_len;
+    float eps, scale;
+};
+constexpr uint32_t BLOCK_CONV_KC = 192;  // a convolution's correction rows (2 * hidden / 16, padded; tools/spec/export.py:14)
+void launch_block_context(const float* kvp, const float* ctx, const float* ctx_inv, const uint32_t* meta, const uint32_t* on_path, const float* rope,
+                          const BlockDrafterDims& b, uint32_t n, uint16_t* k_ring, uint16_t* v_ring, float* ctx_ring, cudaStream_t s);
+void launch_block_embed(const uint16_t* table, const uint32_t* tin, const uint32_t* lens, const uint32_t* feed, const float* mask_emb, const float* ctx_ring,
+                        const BlockDrafterDims& b, uint32_t vocab, uint32_t rows, float* x, float* last, uint32_t* meta, cudaStream_t s);
+void launch_block_conv(const float* x, const float* corr, const float* base, const uint32_t* tin, const float* resid, uint32_t hidden, uint32_t rows, float* out,
+                       cudaStream_t s);
+void launch_block_qkv_post(float* qkv, const uint32_t* meta, const float* rope, const BlockDrafterDims& b, uint32_t layer, uint32_t rows, uint16_t* k_ring,
+                           uint16_t* v_ring, cudaStream_t s);
+void launch_block_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* rows_of, const uint16_t* k_ring, const uint16_t* v_ring,
+                       const BlockDrafterDims& b, uint32_t layer, uint32_t rows, float* out, cudaStream_t s);
+
 // The tcgen05 GEMM for 16..256 tokens: needs Xb (bf16 X, rows padded to 16), inv_in for the
 // normed epilogues, m a multiple of 128, one int8 scale per row.
 bool gemm_supported(const MatArgs& a);

@@ -31,10 +31,12 @@ DRAFTER_KIND_CHAIN = 1.0
 
 def meta_tensor(c: dict) -> np.ndarray:
     return np.array([META_VERSION, PRESET_LLAMA, c["n_layers"], c["d"], c["n_heads"], c["n_kv"], c["hd"], c["ffn"], c["vocab"],
-                     c.get("vocab_real", c["vocab"]), c["eps"], c["page"], c["theta"], 1.0 / np.sqrt(c["hd"])], dtype=np.float32)
+                     c.get("vocab_real", c["vocab"]), c["eps"], c["page"], c["theta"], c.get("attn_scale", 1.0 / np.sqrt(c["hd"]))], dtype=np.float32)
 
 
 def rope_freq(c: dict) -> np.ndarray:
+    if "rope_freq" in c:  # given outright (the reference's target: (1 / 1024) ^ linspace(0, 1, 32), tools/spec/drafter.py:27)
+        return np.asarray(c["rope_freq"], np.float32)
     i = np.arange(c["hd"] // 2, dtype=np.float64)
     return (c["theta"] ** (-2.0 * i / c["hd"])).astype(np.float32)
 
