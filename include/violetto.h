@@ -136,7 +136,11 @@ typedef void (*VltCaptureFn)(const VltLayerCapture* layer, void* user);
 int vlt_step_capture(VltEngine* e, const VltRun* runs, uint32_t n_runs, const VltStepOptions* opts, VltCaptureFn fn, void* user, VltStepOutput* out);
 /* Engine::set_taps, engine.rs:381-389: taps these layers' outputs -- bf16(rms_norm(output)), kernels.metal:133-148 -- from the
  * next step on, for VltStepOptions.read_taps ([tap][token][d_model], in the order given; with a drafter loaded the last layer
- * stays tapped and comes last if it was not named). Engine::load_drafter / has_drafter, engine.rs:381-389, engine/drafter.rs:250-262. */
+ * stays tapped and comes last if it was not named). Engine::load_drafter / has_drafter, engine.rs:381-389, engine/drafter.rs:250-262.
+ * Two kinds of file load: the reference's block drafter as tools/spec/export.py writes it (recognised by its `kv_all`
+ * tensor; engine/drafter.rs:131-240; it taps the layers its `meta` names, needs a target of 64-wide heads whose hidden width
+ * is the drafter's, and drafts a tree per step), and the benchmark's one-layer chain drafter (`meta` = [1, 1, 1, draft ids
+ * [, attention window]]). */
 int vlt_set_taps(VltEngine* e, const uint32_t* layers, uint32_t n_layers);
 int vlt_load_drafter(VltEngine* e, const char* path);
 int vlt_has_drafter(VltEngine* e);

@@ -126,3 +126,33 @@ def test_block_drafter_matches_the_oracle(files, window, rows):
     # exactly is asserted per step: the product's tree is the reference kernels' tree of the product's own logits.
     assert agree * 2 >= total, f"only {agree} of {total} trees equal the oracle's"
     prod.close()
+
+
+def test_generator_with_the_block_drafter_decodes_like_plain_decoding(files):
+    """Draft trees of a random drafter are rarely right; whatever they are, the tokens must be the plain decoding's
+    (greedy): tree verification, the accepted path and the cache compaction behind a drafter that draws trees."""
+    from tests.test_gpu_bench_shapes import _compare_stream, _plain_decode
+    target, drafters = files
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(0, 4096, n).astype(np.uint32) for n in (11, 40, 17)]
+    max_tokens = [24, 16, 12]
+    want = [_plain_decode(target, p, mt) for p, mt in zip(prompts, max_tokens)]
+    eng = E.Engine(target, E.EngineConfig(max_seqs=3, max_step_tokens=64, max_chunk=32, global_kv_tokens=16 * 24, max_seq_len=128, max_head_rows=24),
+                   E.Tuning(spec_policy_off=True))
+    eng.load_drafter(drafters[1024])
+    with eng.generator() as g:
+        ids = [g.submit(E.Request(list(p), mt, draft=[E.Draft.MODEL, E.Draft.MODEL, E.Draft.NONE][i], rows=[8, 4, 1][i])) for i, (p, mt) in enumerate(zip(prompts, max_tokens))]
+        got = {i: [] for i in ids}
+        for _ in range(400):
+            if g.is_idle():
+                break
+            for ev in g.step():
+                if ev.kind == "token":
+                    got[ev.req].append(ev.value)
+        assert g.is_idle()
+    for i, rid in enumerate(ids):
+        toks, margins = want[i]
+        assert _compare_stream(got[rid], toks, margins) >= 4, f"request {i}"
+        assert len(got[rid]) == max_tokens[i]
+    assert len(eng.debug_read("free_pages")) == 24
+    eng.close()
