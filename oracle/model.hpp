@@ -33,6 +33,7 @@
 
 #include "bits.hpp"
 #include "block_drafter.hpp"
+#include "limite.hpp"
 #include "linear.hpp"
 #include "sampling.hpp"
 #include "vlt.hpp"
@@ -78,6 +79,9 @@ struct Drafter {
     std::vector<uint32_t> q_rows, index_of;
 };
 
+struct Engine;
+void limite_forward(Engine& e, const Plan& p);  // limite_forward.hpp
+
 struct Engine {
     VltFile file;
     ModelDesc md{};
@@ -101,6 +105,8 @@ struct Engine {
     std::vector<float> logits, hidden_out, taps;  // taps: bf16(rms_norm(last layer's output)) as fp32, [n][d]
     ReplayArgs replay{0, 0, 0.0f, 0};
     std::unique_ptr<Drafter> drafter;
+    std::unique_ptr<Limite> lim;  // the reference's own architecture (limite.hpp), if the weight file is one of its converter's
+    uint32_t kv_layers = 0;       // layers of the paged pool: all of a plain decoder's, the global ones of a Limite model
     std::unique_ptr<BlockDrafter> block_drafter;  // the reference's block drafter (block_drafter.hpp), if that is what was loaded
     std::vector<float> rope_freq;
     std::vector<float> draft_logits;  // the drafter's passes, [rows - 1][runs][v]; rows of runs that did not draft stay 0
@@ -115,11 +121,29 @@ struct Engine {
     uint32_t accept_rule = 0;  // 0: the reference's sample-then-match; 1: rejection sampling where a run's drafts came with their q rows
 
     Engine(const std::string& file_path, const EngineConfig& c) : file(VltFile::load(file_path)), cfg(c) {
+        if (Limite::is_limite(file)) {
+            // engine/src/model.rs:6-20, read off the file instead of fixed: hidden width and vocabulary from `embed`, kv
+            // heads from the qkv projection's rows, FFN from `down`, layers by counting; an optional `limite_vocab_real`
+            // (f32[1]) names the first padding id, else the reference's 151 667 of 151 680.
+            lim = std::make_unique<Limite>();
+            const Tensor& et = file.tensor("embed");
+            md.vocab = et.shape.at(0); md.d = et.shape.at(1); md.hd = Limite::D;
+            if (md.d % Limite::D) throw std::runtime_error(file_path + ": hidden width is not a multiple of 128");
+            md.n_heads = md.d / Limite::D;
+            md.n_kv = (file.tensor("L00.qkv").shape.at(0) / Limite::D - md.n_heads) / 2;
+            md.ffn = file.tensor("L00.down").shape.at(1);
+            md.n_layers = 0;
+            while (file.has("L" + std::string(md.n_layers < 10 ? "0" : "") + std::to_string(md.n_layers) + ".qkv")) md.n_layers++;
+            md.vocab_real = file.has("limite_vocab_real") ? uint32_t(file.f32s("limite_vocab_real").at(0)) : md.vocab == 151680 ? 151667u : md.vocab;
+            md.eps = 0x1p-23f; md.page = Limite::PAGE; md.attn_scale = 0.1f;  // kernels.metal:13, kv.rs:6, model.rs:19
+            if (md.n_kv == 0 || md.n_heads % md.n_kv) throw std::runtime_error(file_path + ": the qkv projection's rows do not fit the heads");
+        } else {
         std::vector<float> m = file.f32s("meta");
         if (m.size() < 14 || m[0] != 1.0f || m[1] != 0.0f) throw std::runtime_error(file_path + ": meta is not a version-1 llama descriptor");
         md.n_layers = uint32_t(m[2]); md.d = uint32_t(m[3]); md.n_heads = uint32_t(m[4]); md.n_kv = uint32_t(m[5]);
         md.hd = uint32_t(m[6]); md.ffn = uint32_t(m[7]); md.vocab = uint32_t(m[8]); md.vocab_real = uint32_t(m[9]);
         md.eps = m[10]; md.page = uint32_t(m[11]); md.attn_scale = m[13];
+        }
         embed = reinterpret_cast<const uint16_t*>(file.ptr(file.get("embed", BF16, {md.vocab, md.d})));
         // engine/src/model.rs:139-140: the head is the embedding unless the file has one.
         if (file.has("head")) head = load_matrix(file, "head", md.vocab, md.d);
@@ -133,12 +157,31 @@ struct Engine {
             l.gate_up = load_matrix(file, name("gate_up"), 2 * md.ffn, md.d);
             l.down = load_matrix(file, name("down"), md.d, md.ffn);
             layers.push_back(l);
+            if (!lim) continue;
+            LimiteLayer x;  // model.rs:108-135
+            auto f32 = [&](const char* k, std::vector<uint32_t> shape) { return reinterpret_cast<const float*>(file.ptr(file.get(name(k), F32, shape))); };
+            x.global = i % 4 == 3;
+            x.kv_index = x.global ? lim->n_global++ : lim->n_local++;
+            x.attn_gate = f32("attn_gate", {md.n_heads, Limite::D});
+            if (i % 3 == 1) x.ve_gate = f32("ve_gate", {md.n_kv, 12});
+            x.xsa = f32("xsa", {md.n_heads});
+            const float* sc = f32("scalars", {8});
+            x.qkv_scale = sc[0]; x.o_scale = sc[1]; x.resid_attn = sc[2]; x.post_attn = sc[3]; x.resid_mlp = sc[4]; x.post_mlp = sc[5];
+            lim->layers.push_back(x);
+        }
+        if (lim) {
+            lim->value_embed = reinterpret_cast<const uint16_t*>(file.ptr(file.get("value_embed", BF16, {md.vocab, md.n_kv * Limite::D})));
+            lim->mudd_dense1 = reinterpret_cast<const float*>(file.ptr(file.get("mudd.dense1", F32, {32, md.d})));
+            lim->mudd_mix = reinterpret_cast<const float*>(file.ptr(file.get("mudd.mix", F32, {2, 2, 3, 33})));
+            if (lim->n_global == 0 || lim->n_local == 0) throw std::runtime_error(file_path + ": a Limite model has local and global layers (at least 4 layers)");
+            lim->init_state(cfg.max_seqs, cfg.max_chunk, md.n_kv);
         }
         // engine.rs:392-421 `rope_table`: theta = float32(pos) * freq, cos and sin rounded to bf16.
         std::vector<float> freq = file.f32s("rope_freq");
         rope_freq = freq;
-        if (freq.size() != md.hd / 2) throw std::runtime_error("rope_freq: expected head_dim / 2 entries");
-        const uint32_t npos = cfg.max_seq_len + FEED_W;
+        // (a Limite head of 128 turns its first 64 dims: 32 pairs, looked up as they are needed)
+        if (freq.size() != (lim ? 32 : md.hd / 2)) throw std::runtime_error("rope_freq: expected head_dim / 2 entries (32 for the reference's own model)");
+        const uint32_t npos = lim ? 0 : cfg.max_seq_len + FEED_W;
         rope.resize(size_t(npos) * md.hd);
         for (uint32_t p = 0; p < npos; p++)
             for (uint32_t i = 0; i < md.hd / 2; i++)
@@ -146,7 +189,8 @@ struct Engine {
         // kv.rs:23-48 `KvCache::new`.
         n_pages = (cfg.kv_tokens + md.page - 1) / md.page;
         max_pages = (cfg.max_seq_len + md.page - 1) / md.page;
-        const size_t kv = size_t(md.n_layers) * n_pages * md.n_kv * md.page * md.hd;
+        kv_layers = lim ? lim->n_global : md.n_layers;
+        const size_t kv = size_t(kv_layers) * n_pages * md.n_kv * md.page * md.hd;
         k_cache.assign(kv, 0);
         v_cache.assign(kv, 0);
         page_table.assign(size_t(cfg.max_seqs) * max_pages, 0);
@@ -208,6 +252,7 @@ struct Engine {
         lens[s] = q.len;
         reserve(s, q.pages, q.len);
         if (!seed) return;
+        if (lim) throw std::runtime_error("bench_fill with values is for the paged pool of a plain decoder");
         auto val = [](uint32_t u) { return (float(u >> 8) * 0x1p-24f - 0.5f) * 2.0f; };
 #pragma omp parallel for schedule(static) collapse(2)
         for (int64_t l = 0; l < int64_t(md.n_layers); l++)
@@ -278,6 +323,9 @@ struct Engine {
     }
 
     // Where kv head g's row for cache position pos starts (kernels.metal:704-711, global layers).
+    size_t limite_ring_row(uint32_t layer, uint32_t slot, uint32_t g, uint32_t pos) const {  // kernels.metal:710 `kv_row_of`, local
+        return ((size_t(layer) * lim->max_seqs + slot) * md.n_kv + g) * lim->ring * md.hd + size_t(pos % lim->ring) * md.hd;
+    }
     size_t kv_row(uint32_t layer, uint32_t slot, uint32_t g, uint32_t pos) const {
         const uint32_t page = page_table[size_t(slot) * max_pages + pos / md.page];
         return ((size_t(layer) * n_pages + page) * md.n_kv + g) * md.page * md.hd + size_t(pos % md.page) * md.hd;
@@ -386,6 +434,7 @@ struct Engine {
 
     // encode.rs:99-105 `encode_forward` + :383-412 `encode_tail`.
     void forward(const Plan& p) {
+        if (lim) { limite_forward(*this, p); return; }
         const uint32_t n = p.n, d = md.d;
         meta.assign(2 * n, 0);
         std::vector<float> x(size_t(n) * d);
@@ -434,6 +483,14 @@ struct Engine {
                     float& l = logits[size_t(r) * md.vocab + j];
                     l = j < md.vocab_real ? l * inv[head_rows[r]] : -INFINITY;
                 }
+        }
+        finish_step(p);
+    }
+
+    // encode.rs:395-412, from the logits on: each head row's token, `accept`, and the accepted paths' K/V into place.
+    void finish_step(const Plan& p) {
+        const uint32_t n = p.n;
+        if (p.n_head) {
 #pragma omp parallel for schedule(dynamic)
             for (int64_t r = 0; r < int64_t(p.n_head); r++) {
                 const SampleRow& sr = sample_rows[r];
@@ -452,7 +509,7 @@ struct Engine {
         }
         for (uint32_t r = 0; r < p.n_runs; r++)
             accept_run(r, runs.data(), tokens.data(), out_ids.data(), lens.data(), feed.data(), gen.data(), emitted.data(), tree.data(), path.data(), path_len.data(), on_path.data(), decided[r]);
-        if (p.branches) kv_compact(p, k_cache.data(), v_cache.data(), md.n_layers);
+        if (p.branches) kv_compact(p, k_cache.data(), v_cache.data(), kv_layers);
     }
 
     // Whether run r is decided by the rejection rule: a verify run of a sequence that samples (temperature > 0, no
@@ -481,6 +538,16 @@ struct Engine {
     void kv_compact(const Plan& p, uint16_t* kc, uint16_t* vc, uint32_t nl) {
         for (uint32_t r = 0; r < p.n_runs; r++) {
             const uint32_t k = path_len[r], slot = runs[r].slot, p0 = lens[slot] - k;
+            if (lim && kc == k_cache.data())  // the local layers' rings as well (kernels.metal:1663-1693 takes both kinds)
+                for (uint32_t l = 0; l < lim->n_local; l++)
+                    for (uint32_t g = 0; g < md.n_kv; g++)
+                        for (uint32_t j = 1; j < k; j++) {
+                            const uint32_t from = path[r * FEED_W + j];
+                            if (from == j) continue;
+                            const size_t src = limite_ring_row(l, slot, g, p0 + from), dst = limite_ring_row(l, slot, g, p0 + j);
+                            std::copy_n(lim->k_local.data() + src, md.hd, lim->k_local.data() + dst);
+                            std::copy_n(lim->v_local.data() + src, md.hd, lim->v_local.data() + dst);
+                        }
             for (uint32_t l = 0; l < nl; l++)
                 for (uint32_t g = 0; g < md.n_kv; g++)
                     for (uint32_t j = 1; j < k; j++) {
@@ -657,3 +724,5 @@ struct Engine {
 };
 
 }  // namespace orc
+
+#include "limite_forward.hpp"

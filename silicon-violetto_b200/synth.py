@@ -205,3 +205,46 @@ def block_case_inputs(seed: int, n_ctx: int, hidden: int = 1280, n_taps: int = 2
     feat = vlt.from_bf16(vlt.to_bf16(f.astype(np.float32)))
     emb = vlt.from_bf16(vlt.to_bf16(rng.normal(0.0, 0.02, hidden).astype(np.float32)))
     return feat, emb
+
+
+# ------------------------------------------------------------------ the reference's own architecture ("Limite")
+def write_limite(path, n_layers: int = 48, hidden: int = 1280, n_kv: int = 2, ffn: int = 3328, vocab: int = 4096, vocab_real: int | None = None,
+                 seed: int = 0, int8_group: int | None = None, std: float = 0.02) -> dict:
+    """A random-init weight file with the tensor set tools/convert.py:64-114 writes for the reference's own model (no
+    `meta`: the reference hard-codes the architecture, engine/src/model.rs:6-20): `embed`, `value_embed`, `rope_freq`
+    (32 frequencies, (1 / 1024) ^ linspace(0, 1, 32)), `mudd.dense1`, `mudd.mix`, and per layer the four projections
+    (gate_up interleaved) with `attn_gate`, `xsa` (tanh applied), `scalars` (qkv_scale, o_scale, the four residual
+    lambdas, two zeros) and, on layers with i % 3 == 1, `ve_gate`. Heads are 128 wide, hidden / 128 of them; the
+    reference's shapes are the defaults. `limite_vocab_real` (not in the reference's files, whose padding starts at
+    151 667) names the first padding id of a smaller vocabulary."""
+    gen = torch.Generator().manual_seed(seed)
+    rng = np.random.default_rng(seed)
+    d_head = 128
+    nq = hidden // d_head
+    qkv_w = (nq + 2 * n_kv) * d_head
+    out: dict = {}
+    embed = _randn(gen, vocab, hidden, std)
+    out["embed"] = vlt.Bf16.from_f32(embed)
+    out["value_embed"] = vlt.Bf16.from_f32(_randn(gen, vocab, n_kv * d_head, 0.5))
+    out["rope_freq"] = ((1.0 / 1024.0) ** np.linspace(0, 1, 32, dtype=np.float32)).astype(np.float32)
+    out["mudd.dense1"] = rng.normal(0.0, 0.05, (32, hidden)).astype(np.float32)
+    mix = rng.normal(0.0, 0.3, (2, 2, 3, 33)).astype(np.float32)
+    mix[:, :, :, 32] = np.array([0.1, 0.2, 0.9], np.float32) + rng.normal(0.0, 0.05, (2, 2, 3)).astype(np.float32)
+    out["mudd.mix"] = mix
+    for i in range(n_layers):
+        L = f"L{i:02d}."
+        _put(out, L + "qkv", _randn(gen, qkv_w, hidden, std), int8_group)
+        _put(out, L + "o", _randn(gen, hidden, hidden, std), int8_group)
+        _put(out, L + "gate_up", _randn(gen, 2 * ffn, hidden, std), int8_group)
+        _put(out, L + "down", _randn(gen, hidden, ffn, std), int8_group)
+        out[L + "attn_gate"] = rng.normal(0.0, 0.1, (nq, d_head)).astype(np.float32)
+        if i % 3 == 1:
+            out[L + "ve_gate"] = rng.normal(0.0, 0.3, (n_kv, 12)).astype(np.float32)
+        out[L + "xsa"] = np.tanh(rng.normal(0.0, 0.5, nq)).astype(np.float32)
+        out[L + "scalars"] = np.concatenate([rng.uniform(0.8, 1.2, 6), [0.0, 0.0]]).astype(np.float32)
+    if int8_group is not None:
+        _put(out, "head", embed, 8 if int8_group else 0)
+    if vocab_real is not None:
+        out["limite_vocab_real"] = np.array([vocab_real], np.float32)
+    vlt.write(path, out)
+    return dict(n_layers=n_layers, d=hidden, n_heads=nq, n_kv=n_kv, hd=d_head, ffn=ffn, vocab=vocab, vocab_real=vocab_real or vocab)
