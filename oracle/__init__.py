@@ -331,7 +331,7 @@ class Engine:
 
     _F32 = ("logits", "hidden_out", "taps", "draft_logits", "carry", "q_keep", "taps_all", "cap_resid_in", "cap_attn_in", "cap_qkv", "cap_sdpa_out", "cap_attn_out",
             "cap_mlp_in", "cap_mlp_out", "block_logits", "block_hfin", "block_ctx_ring")
-    _U16 = ("k_cache", "v_cache", "draft_k_cache", "draft_v_cache", "block_k_ring", "block_v_ring")
+    _U16 = ("k_cache", "v_cache", "draft_k_cache", "draft_v_cache", "block_k_ring", "block_v_ring", "limite_k_local", "limite_v_local")
 
     def array(self, name: str) -> np.ndarray:
         ptr = C.c_void_p()

@@ -195,6 +195,10 @@ uint64_t orc_array(void* h, const char* name, const void** ptr) {
     if (n == "carry" && e->drafter) { *ptr = e->drafter->carry.data(); return e->drafter->carry.size(); }
     if (n == "q_rows" && e->drafter) { *ptr = e->drafter->q_rows.data(); return e->drafter->q_rows.size(); }
     if (n == "q_keep" && e->drafter) { *ptr = e->drafter->q_keep.data(); return e->drafter->q_keep.size(); }
+    if (e->lim) {
+        if (n == "limite_k_local") { *ptr = e->lim->k_local.data(); return e->lim->k_local.size(); }
+        if (n == "limite_v_local") { *ptr = e->lim->v_local.data(); return e->lim->v_local.size(); }
+    }
     if (e->block_drafter) {
         BlockDrafter& b = *e->block_drafter;
         if (n == "block_logits") { *ptr = b.logits.data(); return b.logits.size(); }

@@ -565,7 +565,7 @@ struct Engine {
         auto dr = std::make_unique<Drafter>();
         dr->file = VltFile::load(path);
         if (BlockDrafter::is_block_drafter(dr->file)) {  // engine/src/engine.rs:381-389 with a file of tools/spec/export.py
-            if (md.hd != 64 || md.d % BlockDrafter::D) throw std::runtime_error(path + ": the block drafter needs a target of 64-wide heads whose hidden width is a multiple of 128");
+            if (rope_freq.size() != 32 || md.d % BlockDrafter::D) throw std::runtime_error(path + ": the block drafter needs a target whose hidden width is a multiple of 128 and whose RoPE table has 32 pairs");
             block_drafter = std::make_unique<BlockDrafter>(path, md.eps, md.attn_scale, rope_freq);
             if (block_drafter->H != md.d) throw std::runtime_error(path + ": hidden width " + std::to_string(block_drafter->H) + ", the target's is " + std::to_string(md.d));
             block_drafter->init_state(cfg.max_seqs, cfg.max_chunk);

@@ -123,7 +123,7 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
     if (cfg.max_seqs == 0 || cfg.max_step_tokens == 0 || cfg.max_chunk == 0 || cfg.max_head_rows == 0) throw Error("engine config: zero capacity");
     model.load(weights, cfg.host_only);
     const ModelDesc& md = model.md;
-    kv.init(cfg, md, md.n_layers, !cfg.host_only);
+    kv.init(cfg, md, model.limite ? model.n_global : md.n_layers, !cfg.host_only);  // (the reference's architecture pages its global layers only)
     seqs.resize(cfg.max_seqs);
     for (auto& st : sets) st.init(cfg);
 
@@ -171,7 +171,7 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
 
     if (!ho) {
         // engine.rs:392-421 `rope_table`: theta = float32(pos) * frequency, cos and sin rounded to bf16.
-        const uint32_t npos = cfg.max_seq_len + FEED_W, half = md.hd / 2;
+        const uint32_t npos = cfg.max_seq_len + FEED_W, half = uint32_t(model.rope_freq.size());  // hd / 2; 32 pairs for a head of 128 of the reference's architecture
         std::vector<float> tab(size_t(npos) * half * 2);
         auto rb = [](float x) { uint32_t u; std::memcpy(&u, &x, 4); u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u; std::memcpy(&x, &u, 4); return x; };
         for (uint32_t p = 0; p < npos; p++)
@@ -182,7 +182,17 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
             }
         rope_tab.alloc(tab.size() * 4, false);
         rope_tab.write_vec(0, tab);
-        attn_maps_init(&attn_maps, kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), uint64_t(md.n_layers) * kv.n_pages * md.n_kv * md.page);
+        if (!model.limite) attn_maps_init(&attn_maps, kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), uint64_t(md.n_layers) * kv.n_pages * md.n_kv * md.page);
+        if (model.limite) {
+            lim = std::make_unique<LimiteState>();
+            lim->ring = LIMITE_WINDOW + cfg.max_chunk;  // kv.rs:26-28: the window plus a whole chunk
+            const size_t n = cfg.max_step_tokens, ring_bytes = size_t(model.n_local) * cfg.max_seqs * md.n_kv * lim->ring * 128 * 2;
+            lim->k_local.alloc(ring_bytes, false);
+            lim->v_local.alloc(ring_bytes, false);
+            for (Buffer* b : {&lim->hist0, &lim->hist12, &lim->hist23, &lim->xattn, &lim->base, &lim->mixed}) b->alloc(n * md.d * 4, false);
+            lim->vdir.alloc(n * md.n_kv * 128 * 4, false);
+            lim->gates.alloc(n * md.n_heads * 4, false);
+        }
         VLT_CUDA(cudaDeviceSynchronize());
     }
 }
@@ -409,8 +419,11 @@ Plan Engine::plan(uint32_t set, const std::vector<PlanRun>& runs, Rows hidden) {
 // tensor cores from registers; larger ones go in token blocks of 8 (the weights of one matrix
 // stay in L2 between blocks).
 void Engine::matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real,
-                    const QkvEpilogue* q, const uint16_t* xb, uint16_t* yb) {
+                    const QkvEpilogue* q, const uint16_t* xb, uint16_t* yb, float scale, float ra, float rb) {
     MatArgs a{};
+    a.scale = scale;
+    a.ra = ra;
+    a.rb = rb;
     if (q) a.q = *q;
     a.err_flag = s.err_flag.as<uint32_t>();
     a.W = w.w;
@@ -452,7 +465,7 @@ bool Engine::stream_fits(const Matrix& w) const {
 bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
     const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 9;  // up to 8 tokens the streamed kernel; 9..15 would take it twice over the weights
     const bool grouped = w.int8 && w.group < w.k;
-    return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
+    return !model.limite && n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;  // (the GEMM has no matrix scales or residual lambdas)
 }
 
 bool Engine::layer_carries(const Layer& l, uint32_t n) const {
@@ -751,8 +764,93 @@ void Engine::encode_tail(uint32_t set, const Plan& p) {
                           kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kv_args(), p.n_runs, md.n_layers, stream);
 }
 
+// The reference's own architecture, encode.rs:99-192 `encode_forward` / `encode_layer` and :383-412 `encode_tail`: the
+// layers' extras are k_limite.cu's kernels, the projections the streamed matmul with the matrix scales and residual
+// lambdas in its epilogue. The residual stream moves through hist0 (the normed embedding), hist12 / hist23 (the outputs of
+// layers 11 and 22, which the MUDD sites at 24 and 47 mix back in) and h.
+LimiteKv Engine::limite_kv(const LimiteLayer& x) const {
+    uint32_t shift = 0;
+    while ((1u << shift) < model.md.page) shift++;
+    return LimiteKv{x.global ? 1u : 0u, x.kv_index, model.md.n_kv, lim->ring, cfg.max_seqs, kv.n_pages, kv.max_pages, shift, kv.page_table.as<uint32_t>()};
+}
+
+void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
+    const ModelDesc& md = model.md;
+    StepSet& st = sets[set];
+    LimiteState& L = *lim;
+    const uint32_t n = p.n, H = md.d;
+    if (p.chunked && p.max_run > cfg.max_chunk) throw Error("a run longer than max_chunk");
+    begin_step(set, p);  // upload, embedding rows into h
+    int sp = span_begin(G_SMALL);
+    launch_prep_rows(s.h.as<float>(), nullptr, n, H, md.eps, L.hist0.as<float>(), nullptr, nullptr, true, false, stream);  // kernels.metal:108-113: rms_norm(embedding)
+    span_end(sp);
+    const float* cur = L.hist0.as<float>();
+    const uint32_t* meta = s.meta.as<uint32_t>();
+    const uint32_t* tin = st.in<uint32_t>(st.o_tin);
+    for (uint32_t li = 0; li < md.n_layers; li++) {
+        const Layer& l = model.layers[li];
+        const LimiteLayer& x = model.lim[li];
+        const float* xa = cur;
+        const float* base = cur;
+        const int site = li == 24 ? 0 : li == 47 ? 1 : -1;  // model.rs:20 `MUDD_LAYERS`
+        if (site >= 0) {
+            sp = span_begin(G_SMALL);
+            launch_limite_mudd(cur, L.hist0.as<float>(), (site == 0 ? L.hist12 : L.hist23).as<float>(), model.mudd_dense1, model.mudd_mix + size_t(site) * 2 * 3 * 33, H, md.eps, n,
+                               L.xattn.as<float>(), L.base.as<float>(), stream);
+            span_end(sp);
+            xa = L.xattn.as<float>();
+            base = L.base.as<float>();
+        }
+        const LimiteKv kva = limite_kv(x);
+        uint16_t* kc = x.global ? kv.k.as<uint16_t>() : L.k_local.as<uint16_t>();
+        uint16_t* vc = x.global ? kv.v.as<uint16_t>() : L.v_local.as<uint16_t>();
+        sp = span_begin(G_MATMUL);
+        matmul(l.qkv, n, xa, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>(), 0, nullptr, nullptr, nullptr, x.qkv_scale);
+        span_end(sp);
+        sp = span_begin(G_SMALL);
+        launch_limite_qkv_post(s.qkv.as<float>(), xa, s.inv.as<float>(), meta, tin, st.in<uint32_t>(st.o_tokens), model.value_embed, x.ve_gate, x.attn_gate, rope_tab.as<float>(), kva,
+                               H, md.n_heads, md.eps, md.vocab, n, kc, vc, L.vdir.as<float>(), L.gates.as<float>(), stream);
+        span_end(sp);
+        sp = span_begin(G_ATTN);
+        launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
+                           n, s.attn.as<float>(), stream);
+        span_end(sp);
+        sp = span_begin(G_MATMUL);
+        float* out = li == 11 ? L.hist12.as<float>() : li == 22 ? L.hist23.as<float>() : s.h.as<float>();  // encode.rs:116-122 `resid_out`
+        matmul(l.o, n, s.attn.as<float>(), L.mixed.as<float>(), EPI_RESID, base, nullptr, 0, nullptr, nullptr, nullptr, x.o_scale, x.resid_attn, x.post_attn);
+        matmul(l.gate_up, n, L.mixed.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+        matmul(l.down, n, s.act.as<float>(), out, EPI_RESID, L.mixed.as<float>(), nullptr, 0, nullptr, nullptr, nullptr, 1.0f, x.resid_mlp, x.post_mlp);
+        span_end(sp);
+        cur = out;
+        auto tap = std::find(tap_layers.begin(), tap_layers.end(), li);
+        if (tap != tap_layers.end()) launch_prep_rows(out, nullptr, n, H, md.eps, tap_bufs[tap - tap_layers.begin()].as<float>(), nullptr, nullptr, true, true, stream);
+    }
+    // The tail: final norm of the hidden and head rows, the head with its cap, sampling, accept, compaction.
+    sp = span_begin(G_TAIL);
+    if (p.n_hidden) launch_prep_rows(cur, st.in<uint32_t>(st.o_hidden_rows), p.n_hidden, H, md.eps, s.hfin_all.as<float>(), nullptr, nullptr, true, false, stream);
+    if (p.n_head) {
+        launch_prep_rows(cur, st.in<uint32_t>(st.o_head_rows), p.n_head, H, md.eps, s.hfin_head.as<float>(), nullptr, nullptr, true, false, stream);
+        matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD_CAP, nullptr, nullptr);
+        if (!forced_logits.empty()) {
+            if (forced_logits.size() != size_t(p.n_head) * md.vocab) throw Error("forced logits: wrong size");
+            VLT_CUDA(cudaMemcpyAsync(s.logits.dev, forced_logits.data(), forced_logits.size() * 4, cudaMemcpyHostToDevice, stream));
+        }
+        launch_sample(s.logits.as<float>(), st.in<SampleRow>(st.o_sample_rows), st.out<uint32_t>(st.o_out_ids), s.meta.as<uint32_t>(), p.n_head, md.vocab, stream, nullptr);
+    }
+    launch_accept(st.in<RunIn>(st.o_runs), st.in<uint32_t>(st.o_tokens), st.out<uint32_t>(st.o_out_ids), s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), s.gen.as<GenState>(),
+                  st.out<uint32_t>(st.o_emitted), p.n_runs, s.tree.as<uint32_t>(), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.on_path.as<uint32_t>(), stream, nullptr);
+    if (p.branches) {
+        LimiteLayer any_local, any_global;
+        any_global.global = true;
+        launch_limite_compact(st.in<RunIn>(st.o_runs), s.path.as<uint32_t>(), s.path_len.as<uint32_t>(), s.lens.as<uint32_t>(), L.k_local.as<uint16_t>(), L.v_local.as<uint16_t>(),
+                              kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), limite_kv(any_local), limite_kv(any_global), model.n_local, model.n_global, p.n_runs, stream);
+    }
+    span_end(sp);
+}
+
 // engine/src/engine/encode.rs:99-105 `encode_forward`, after the step set's upload.
 void Engine::encode_forward(uint32_t set, const Plan& p) {
+    if (model.limite) { encode_forward_limite(set, p); return; }
     begin_step(set, p);
     for (uint32_t li = 0; li < model.md.n_layers; li++) encode_layer(set, p, li);
     const int sp = span_begin(G_TAIL);
@@ -835,6 +933,7 @@ void Engine::load_drafter(const std::string& path) {
         load_block_drafter(path);
         return;
     }
+    if (model.limite) throw Error(path + ": the chain drafter runs a plain decoder's layer; a target of the reference's own architecture takes the block drafter");
     const std::vector<float> m = dr->w.f32s("meta");
     if (m.size() < 4 || m[0] != 1.0f || m[1] != 1.0f || m[2] != 1.0f) throw Error(path + ": `meta` is not a version-1 one-layer chain drafter");
     const uint32_t v = uint32_t(m[3]), d = md.d;
@@ -996,7 +1095,8 @@ void Engine::encode_drafter(uint32_t set, const Plan& p, uint32_t rows) {
 
 // engine/src/engine/drafter.rs:131-240 `Drafter::load`, for a file of tools/spec/export.py's layout. The reference's
 // shapes are its target's constants; here the hidden width must be the target's, heads are 128 wide, and the file gives
-// the rest. The drafter turns 32 pairs with the engine's RoPE table, so the target's heads must be 64 wide.
+// the rest. The drafter turns 32 pairs with the engine's RoPE table: the target's heads are 64 wide, or the target is of the
+// reference's own architecture.
 void Engine::load_block_drafter(const std::string& path) {
     auto d = std::make_unique<BlockDrafter>();
     const ModelDesc& md = model.md;
@@ -1008,7 +1108,7 @@ void Engine::load_block_drafter(const std::string& path) {
     d->v = uint32_t(m[4]);
     for (uint32_t k = 0; k < n_taps; k++) d->taps.push_back(uint32_t(m[5 + k]));
     const uint32_t H = md.d, D = 128;
-    if (H % D || md.hd != 64) throw Error(path + ": the block drafter needs a target of 64-wide heads whose hidden width is a multiple of 128");
+    if (H % D || model.rope_freq.size() != 32) throw Error(path + ": the block drafter needs a target whose hidden width is a multiple of 128 and whose RoPE table has 32 pairs (heads of 64, or the reference's own architecture)");
     const uint32_t n_q = H / D, kv_rows = d->w.tensor("kv_all").shape.at(0), n_kv = kv_rows / (n_layers * 2 * D);
     if (n_layers == 0 || n_kv == 0 || n_kv * n_layers * 2 * D != kv_rows || n_q % n_kv || n_q + n_kv > 32) throw Error(path + ": kv_all's rows do not fit the layers and heads");
     d->ffn = d->w.tensor("D00.down").shape.at(1);
@@ -1191,6 +1291,7 @@ StepOutput Engine::read_output(const Plan& p, const StepOptions& opts, double gp
 // engine/src/engine.rs:318-355 `step_capture`.
 StepOutput Engine::step_capture(const std::vector<PlanRun>& runs, const StepOptions& opts, const std::function<void(const LayerCapture&)>& f) {
     if (cfg.host_only) throw Error("this engine was created host-only: it plans steps but cannot run them (no CPU path)");
+    if (model.limite) throw Error("step_capture is built for the plain decoder");
     const ModelDesc& md = model.md;
     if (!cap) {
         cap = std::make_unique<CaptureBufs>();
@@ -1226,6 +1327,7 @@ void Engine::bench_fill(uint32_t id, uint32_t len, uint32_t seed) {
     sq.len += len;
     s.lens.write(id * 4, &sq.len, 4);
     kv.reserve(id, sq.pages, sq.len);
+    if (seed && model.limite) throw Error("bench_fill with values fills a plain decoder's paged pool; a model of the reference's own architecture is filled by computing it");
     if (seed && !cfg.host_only) {
         launch_kv_fill(kv.k.as<uint16_t>(), kv.v.as<uint16_t>(), kv.page_table.as<uint32_t>(), kv_args(), model.md.n_layers, id, from, sq.len, seed, stream);
         VLT_CUDA(cudaStreamSynchronize(stream));
@@ -1461,6 +1563,10 @@ std::vector<uint32_t> Engine::debug_read(const std::string& name) {
         if (name == "q_keep") return whole(drafter->q_keep, ms * (VERIFY_T - 1) * size_t(drafter->v));
         if (name == "draft_k_cache") return whole(drafter->k, pool / 2);  // bf16 pairs
         if (name == "draft_v_cache") return whole(drafter->v_cache, pool / 2);
+    }
+    if (lim) {
+        if (name == "limite_k_local") return whole(lim->k_local, lim->k_local.bytes / 4);  // bf16 pairs
+        if (name == "limite_v_local") return whole(lim->v_local, lim->v_local.bytes / 4);
     }
     if (block_drafter) {
         const BlockDrafter& b = *block_drafter;

@@ -225,6 +225,17 @@ class Engine {
         Buffer q_keep, q_rows, index_of, spec_stats, row_skip, spec_e;
         AttnMaps maps;
     };
+    // The reference's own architecture (model.limite): the local layers' rings and the scratch its layers need beyond a
+    // plain decoder's (buffers.rs:14-40: hist0 / hist12 / hist23, the MUDD outputs, XSA directions, attention gates).
+    static constexpr uint32_t LIMITE_WINDOW = 1024;  // model.rs:18
+    struct LimiteState {
+        uint32_t ring = 0;
+        Buffer k_local, v_local;  // [local layer][slot][kv head][ring][128] bf16
+        Buffer hist0, hist12, hist23, xattn, base, mixed, vdir, gates;
+    };
+    std::unique_ptr<LimiteState> lim;
+    LimiteKv limite_kv(const LimiteLayer& x) const;
+    void encode_forward_limite(uint32_t set, const Plan& p);
     std::unique_ptr<Drafter> drafter;
     // The reference's block drafter (engine/src/engine/drafter.rs:52-100): a file of tools/spec/export.py's layout, the
     // context's keys and values in rings per (layer, slot), the normed context in a ring per slot, scratch for a step's
@@ -256,7 +267,7 @@ class Engine {
   private:
     KvArgs kv_args() const;
     void matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr,
-                const uint16_t* xb = nullptr, uint16_t* yb = nullptr);
+                const uint16_t* xb = nullptr, uint16_t* yb = nullptr, float scale = 1.0f, float ra = 1.0f, float rb = 1.0f);
     bool stream_fits(const Matrix& w) const;
     // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
     void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,

@@ -13,15 +13,16 @@
 
 namespace vlt {
 
-// kernels.metal:184-209 `epilogue`, `epilogue_swiglu`, for a plain decoder (scales and residual
-// lambdas are 1, the head has no softcap).
+// kernels.metal:184-209 `epilogue`, `epilogue_swiglu`. A plain decoder's scales and residual lambdas are 1 and its head has
+// no cap; the reference's own architecture sets them and takes EPI_HEAD_CAP.
 __device__ __forceinline__ void store_out(const MatArgs& a, uint32_t t, uint32_t row, float acc, float inv) {
     const size_t o = size_t(t) * a.m + row;
     float y;
     switch (a.epi) {
-    case EPI_NORM: y = acc * inv; break;
-    case EPI_RESID: y = a.base[o] + acc; break;
+    case EPI_NORM: y = acc * inv * a.scale; break;
+    case EPI_RESID: y = a.ra * a.base[o] + a.rb * (a.scale * acc); break;
     case EPI_HEAD: y = row < a.vocab_real ? acc * inv : -INFINITY; break;
+    case EPI_HEAD_CAP: y = row < a.vocab_real ? 23.0f * (1.0f / (1.0f + expf(-(acc + 5.0f) / 7.5f))) : -INFINITY; break;
     default: y = acc; break;
     }
     a.Y[o] = y;
@@ -492,7 +493,7 @@ __global__ void __launch_bounds__(512, 2) matmul_stream_kernel(MatArgs a, uint32
                         }
                     } else if (a.epi == EPI_RESID) {
                         const size_t o = size_t(b) * a.m + row0 + r;
-                        const float y = resid + sum;
+                        const float y = a.ra * resid + a.rb * (a.scale * sum);
                         a.Y[o] = y;
                         if (a.Yb) a.Yb[o] = f32_to_bf16(y);
                     } else {

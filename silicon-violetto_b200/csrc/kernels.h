@@ -9,7 +9,7 @@
 namespace vlt {
 
 // Epilogues of a matmul, engine/src/engine/kernels.rs:3-9 and kernels.metal:154-209.
-enum : uint32_t { EPI_NORM = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_HEAD = 4, EPI_RAW = 5, EPI_QKV = 6 };
+enum : uint32_t { EPI_NORM = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_HEAD = 4, EPI_RAW = 5, EPI_QKV = 6, EPI_HEAD_CAP = 7 };  // 7: 23 sigmoid((acc + 5) / 7.5), kernels.metal:196-199
 
 // What the tensor-core GEMM's EPI_QKV epilogue needs to finish the qkv projection the way `qkv_post` does
 // (kernels.metal:749-801): RoPE on q and k, q scaled and rounded to bf16 for the attention, k and v rounded
@@ -42,6 +42,9 @@ struct MatArgs {
     uint32_t n, k, m, group;  // group: 0 for bf16 weights
     uint32_t epi, vocab_real;
     float eps;
+    // kernels.metal:164-165,188-193: the matrix scale (qkv_scale, o_scale) and EPI_RESID's y = ra base + rb (scale acc). 1 for a
+    // plain decoder; honoured by the streamed and the scalar matmul, not by the tensor-core GEMM.
+    float scale = 1.0f, ra = 1.0f, rb = 1.0f;
     bool int8;
     QkvEpilogue q;  // EPI_QKV only
     uint32_t t0;    // EPI_QKV in the streamed matmul: the step's token that this launch's token 0 is
@@ -152,6 +155,26 @@ void launch_block_qkv_post(float* qkv, const uint32_t* meta, const float* rope, 
                            uint16_t* v_ring, cudaStream_t s);
 void launch_block_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* rows_of, const uint16_t* k_ring, const uint16_t* v_ring,
                        const BlockDrafterDims& b, uint32_t layer, uint32_t rows, float* out, cudaStream_t s);
+
+// The reference's own architecture (k_limite.cu). A layer's cache: a ring per (local layer, slot) or the paged pool of the
+// global layers (kernels.metal:692-715); heads are 128 wide.
+struct LimiteKv {
+    uint32_t is_global, layer;  // layer: its index among the local or among the global layers
+    uint32_t n_kv, ring, max_seqs;
+    uint32_t n_pages, max_pages, page_shift;
+    const uint32_t* page_table;
+};
+void launch_limite_mudd(const float* cur, const float* tap0, const float* tap1, const float* dense1, const float* mix, uint32_t hidden, float eps, uint32_t n,
+                        float* out_attn, float* out_base, cudaStream_t s);
+void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, const uint32_t* meta, const uint32_t* tin, const uint32_t* tokens, const uint16_t* ve_table,
+                            const float* ve_gate, const float* attn_gate, const float* rope, const LimiteKv& kv, uint32_t hidden, uint32_t n_q, float eps, uint32_t vocab,
+                            uint32_t n, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates, cudaStream_t s);
+void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
+                        const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n, float* out,
+                        cudaStream_t s);
+void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
+                           uint16_t* k_global, uint16_t* v_global, const LimiteKv& local, const LimiteKv& global, uint32_t n_local, uint32_t n_global, uint32_t n_runs,
+                           cudaStream_t s);
 
 // The tcgen05 GEMM for 16..256 tokens: needs Xb (bf16 X, rows padded to 16), inv_in for the
 // normed epilogues, m a multiple of 128, one int8 scale per row.

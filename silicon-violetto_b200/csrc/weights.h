@@ -146,7 +146,20 @@ struct Layer {
     Matrix qkv, o, gate_up, down;
 };
 
-// engine/src/model.rs:69-155 `Model`, for the plain decoder the file's `meta` describes.
+// What a layer of the reference's own architecture has beyond the four projections (engine/src/model.rs:49-67): device
+// pointers into the weight buffer, and the scalars of tools/convert.py:104.
+struct LimiteLayer {
+    const float* attn_gate = nullptr;  // [n_heads][128]
+    const float* ve_gate = nullptr;    // [n_kv][12]; layers with value embeddings only
+    const float* xsa = nullptr;        // [n_heads]
+    float qkv_scale = 1, o_scale = 1, resid_attn = 1, post_attn = 1, resid_mlp = 1, post_mlp = 1;
+    bool global = false;
+    uint32_t kv_index = 0;  // among the global or among the local layers
+};
+
+// engine/src/model.rs:69-155 `Model`: a plain decoder the file's `meta` describes, or -- a file of tools/convert.py, which
+// has no `meta` -- the reference's own architecture (`limite`), whose shapes the reference fixes (model.rs:6-20) and
+// which are read off the file here (heads stay 128 wide).
 struct Model {
     Weights w;
     ModelDesc md;
@@ -154,9 +167,31 @@ struct Model {
     Matrix head;                      // the embedding itself (tied) unless the file has a `head`
     std::vector<Layer> layers;
     std::vector<float> rope_freq;
+    bool limite = false;
+    std::vector<LimiteLayer> lim;
+    const uint16_t* value_embed = nullptr;  // [vocab][n_kv * 128] bf16
+    const float* mudd_dense1 = nullptr;     // [32][d]
+    const float* mudd_mix = nullptr;        // [2][2][3][33]
+    uint32_t n_local = 0, n_global = 0;
 
     void load(const std::string& path, bool host_only) {
         w.load(path, host_only);
+        limite = !w.has("meta") && w.has("L00.scalars");
+        if (limite) {
+            const Tensor& et = w.tensor("embed");
+            if (et.shape.size() != 2) throw Error(path + ": embed is not a matrix");
+            md.vocab = et.shape[0]; md.d = et.shape[1]; md.hd = 128;
+            if (md.d % 128) throw Error(path + ": hidden width is not a multiple of 128");
+            md.n_heads = md.d / 128;
+            md.n_kv = (w.tensor("L00.qkv").shape.at(0) / 128 - md.n_heads) / 2;
+            md.ffn = w.tensor("L00.down").shape.at(1);
+            md.n_layers = 0;
+            while (w.has("L" + std::string(md.n_layers < 10 ? "0" : "") + std::to_string(md.n_layers) + ".qkv")) md.n_layers++;
+            md.vocab_real = w.has("limite_vocab_real") ? uint32_t(w.f32s("limite_vocab_real").at(0)) : md.vocab == 151680 ? 151667u : md.vocab;
+            md.eps = 0x1p-23f; md.page = 128; md.attn_scale = 0.1f;  // kernels.metal:13, kv.rs:6, model.rs:19
+            if (md.n_kv == 0 || md.n_heads % md.n_kv || md.n_heads + md.n_kv > 32) throw Error(path + ": the qkv projection's rows do not fit the heads");
+            if (md.n_layers < 4) throw Error(path + ": a model of this architecture has local and global layers (at least 4 layers)");
+        } else {
         std::vector<float> m = w.f32s("meta");
         if (m.size() < 14 || m[0] != 1.0f || m[1] != 0.0f) throw Error(path + ": `meta` is not a version-1 plain-decoder descriptor");
         md.n_layers = uint32_t(m[2]); md.d = uint32_t(m[3]); md.n_heads = uint32_t(m[4]); md.n_kv = uint32_t(m[5]);
@@ -166,6 +201,7 @@ struct Model {
         if (md.page != 16) throw Error(path + ": page_size " + std::to_string(md.page) + " (the attention kernels are built for 16-token pages)");
         if (md.n_kv == 0 || md.n_heads % md.n_kv || md.group() > 4) throw Error(path + ": " + std::to_string(md.n_heads) + " query heads over " + std::to_string(md.n_kv) + " kv heads (at most 4 per kv head)");
         if (md.d % 256 || md.ffn % 256 || (md.n_heads * md.hd) % 256) throw Error(path + ": d_model, ffn and heads * head_dim must be multiples of 256");
+        }
         embed = reinterpret_cast<const uint16_t*>(w.buffer.as<uint8_t>() + w.get("embed", DType::Bf16, {md.vocab, md.d}).offset);
         if (w.has("head")) head = load_matrix(w, "head", md.vocab, md.d);
         else { head.w = reinterpret_cast<const uint8_t*>(embed); head.m = md.vocab; head.k = md.d; }
@@ -178,9 +214,29 @@ struct Model {
             l.gate_up = load_matrix(w, name("gate_up"), 2 * md.ffn, md.d);
             l.down = load_matrix(w, name("down"), md.d, md.ffn);
             layers.push_back(l);
+            if (!limite) continue;
+            const uint8_t* base = w.buffer.as<uint8_t>();
+            auto f32 = [&](const char* k, std::vector<uint32_t> shape) { return reinterpret_cast<const float*>(base + w.get(name(k), DType::F32, shape).offset); };
+            LimiteLayer x;  // model.rs:108-135
+            x.global = i % 4 == 3;
+            x.kv_index = x.global ? n_global++ : n_local++;
+            x.attn_gate = f32("attn_gate", {md.n_heads, 128});
+            if (i % 3 == 1) x.ve_gate = f32("ve_gate", {md.n_kv, 12});
+            x.xsa = f32("xsa", {md.n_heads});
+            f32("scalars", {8});
+            const std::vector<float> sc = w.f32s(name("scalars"));
+            x.qkv_scale = sc[0]; x.o_scale = sc[1]; x.resid_attn = sc[2]; x.post_attn = sc[3]; x.resid_mlp = sc[4]; x.post_mlp = sc[5];
+            lim.push_back(x);
+        }
+        if (limite) {
+            const uint8_t* base = w.buffer.as<uint8_t>();
+            value_embed = reinterpret_cast<const uint16_t*>(base + w.get("value_embed", DType::Bf16, {md.vocab, md.n_kv * 128}).offset);
+            mudd_dense1 = reinterpret_cast<const float*>(base + w.get("mudd.dense1", DType::F32, {32, md.d}).offset);
+            mudd_mix = reinterpret_cast<const float*>(base + w.get("mudd.mix", DType::F32, {2, 2, 3, 33}).offset);
         }
         rope_freq = w.f32s("rope_freq");
-        if (rope_freq.size() != md.hd / 2) throw Error("rope_freq: expected head_dim / 2 entries");
+        // (a head of 128 of the reference's architecture turns its first 64 dims: 32 pairs)
+        if (rope_freq.size() != (limite ? 32 : md.hd / 2)) throw Error("rope_freq: expected head_dim / 2 entries (32 for the reference's own architecture)");
     }
 };
 

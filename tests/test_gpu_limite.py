@@ -1,0 +1,114 @@
+"""The reference's own architecture on the GPU (k_limite.cu, Engine::encode_forward_limite) against the oracle's
+restatement of it (oracle/limite.hpp, limite_forward.hpp): synthetic files of tools/convert.py's tensor set. Local rings
+and the global pool, q/k norm, RoPE on local layers only, value embeddings, attention gates, XSA, matrix scales and
+residual lambdas, both MUDD sites, the capped head with masked padding ids; prompt chunks, decoding, tree verification
+with cache compaction; integer state bit for bit."""
+import numpy as np
+import pytest
+
+import oracle
+from silicon_violetto_b200 import build, engine as E, synth
+from tests.test_gpu_parity import STATE, same_state
+
+pytestmark = pytest.mark.gpu
+MODELS = {
+    "26 layers, hidden 256": dict(n_layers=26, hidden=256, n_kv=1, ffn=512, vocab=640, vocab_real=630),
+    "48 layers, hidden 256, int8": dict(n_layers=48, hidden=256, n_kv=1, ffn=512, vocab=640, vocab_real=630, int8_group=64),
+    "5 layers, the reference's widths": dict(n_layers=5, hidden=1280, n_kv=2, ffn=3328, vocab=1024),
+}
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    build.build()
+
+
+@pytest.fixture(scope="module", params=list(MODELS), ids=list(MODELS))
+def model(request, tmp_path_factory):
+    path = tmp_path_factory.mktemp("limite") / "limite.vlt"
+    desc = synth.write_limite(path, seed=5, **MODELS[request.param])
+    return path, desc
+
+
+def _pair(path, **kw):
+    cfg = dict(max_seqs=3, max_step_tokens=64, max_chunk=32, global_kv_tokens=128 * 8, max_seq_len=512, max_head_rows=32)
+    cfg.update(kw)
+    prod = E.Engine(path, E.EngineConfig(**cfg))
+    orc = oracle.Engine(path, max_seqs=cfg["max_seqs"], max_step_tokens=cfg["max_step_tokens"], max_chunk=cfg["max_chunk"], kv_tokens=cfg["global_kv_tokens"],
+                        max_seq_len=cfg["max_seq_len"], max_head_rows=cfg["max_head_rows"])
+    return prod, orc
+
+
+def _bf16(bits):
+    return (np.asarray(bits).astype(np.uint32) << 16).view(np.float32)
+
+
+def _step(prod, orc, runs, vocab_real, replay=None):
+    """One step on both engines. The logits are capped to (0, 23): 5e-2 absolute (int8: 1e-1); a sampled or greedy token may
+    differ from the oracle's only at a near-tie of its two best logits, and the product is then put on the oracle's token."""
+    out = prod.debug_step(runs, E.StepOptions(read_logits=True), replay=replay)
+    orc.step(runs, replay=replay)
+    nr, n = len(runs), sum(len(r[1]) for r in runs)
+    want = orc.array("logits").reshape(-1, prod.desc.vocab)
+    assert out.logits.shape == want.shape
+    assert np.isneginf(out.logits[:, vocab_real:]).all() and np.isneginf(want[:, vocab_real:]).all()
+    err = float(np.abs(out.logits[:, :vocab_real] - want[:, :vocab_real]).max())
+    assert err <= 1e-1, f"logits max-abs error {err}"
+    assert want[:, :vocab_real].min() > 0 and want[:, :vocab_real].max() < 23
+    same_state(prod, orc, nr, n, names=[x for x in STATE if x != "feed"])
+    top2 = np.sort(want[:, :vocab_real], axis=1)[:, -2:]
+    clear = top2[:, 1] - top2[:, 0] > 2 * max(err, 1e-3)
+    assert np.array_equal(out.ids[clear], orc.array("out_ids")[clear])
+    prod.debug_write("feed", 0, orc.array("feed"))
+    for name in ("limite_k_local", "limite_v_local", "k_cache", "v_cache"):
+        got, exp = _bf16(prod.debug_read(name).view(np.uint16)), _bf16(orc.array(name))
+        e = float(np.abs(got - exp[:len(got)]).max() / max(np.abs(exp).max(), 1e-6))
+        assert e <= 3e-2, f"{name}: {e} of the largest"
+    return err
+
+
+def test_limite_forward_matches_the_oracle(model):
+    path, desc = model
+    prod, orc = _pair(path)
+    assert (prod.desc.n_layers, prod.desc.d_model, prod.desc.head_dim, prod.desc.page_size) == (desc["n_layers"], desc["d"], 128, 128)
+    vr = desc["vocab_real"]
+    rng = np.random.default_rng(17)
+    a, b = prod.new_seq(), prod.new_seq()
+    assert (orc.new_seq(), orc.new_seq()) == (a, b)
+    pa, pb = rng.integers(0, vr, 21).astype(np.uint32), rng.integers(0, vr, 40).astype(np.uint32)
+    errs = [_step(prod, orc, [(a, pa, E.Rows.LAST, False), (b, pb[:30], E.Rows.NONE, False)], vr)]
+    errs.append(_step(prod, orc, [(b, pb[30:], E.Rows.ALL, False), (a, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    # Draft trees written by hand: a chain of wrong drafts for a; for b a tree whose second branch is b's own continuation
+    # (taken from a plain decoding of the same prompt), so that the accepted path 0 -> 2 -> 3 is not a prefix of the rows
+    # and the caches, rings and pages alike, are compacted.
+    o2 = oracle.Engine(path, max_seqs=1, max_step_tokens=64, max_chunk=32, kv_tokens=128 * 8, max_seq_len=512, max_head_rows=32)
+    q = o2.new_seq()
+    o2.step([(q, pb[:30], E.Rows.NONE, False)])
+    o2.step([(q, pb[30:], E.Rows.LAST, False)])
+    cont = []
+    for _ in range(3):
+        cont.append(int(o2.array("feed")[0]))
+        o2.step([(q, [E.FEED_ROW], E.Rows.LAST, False)])
+    feed = orc.array("feed").reshape(-1, 16).copy()
+    tree = orc.array("tree").reshape(-1, 16).copy()
+    assert feed[b][0] == cont[0]
+    node = lambda depth, parent, sees: depth | parent << 8 | sees << 16
+    wrong = lambda t: (t + 1) % vr
+    feed[a][1:4] = rng.integers(0, vr, 3)
+    tree[a][1:4] = [node(1, 0, 0b0011), node(2, 1, 0b0111), node(3, 2, 0b1111)]
+    feed[b][1:5] = [wrong(cont[1]), cont[1], cont[2], wrong(cont[2])]
+    tree[b][1:5] = [node(1, 0, 0b00011), node(1, 0, 0b00101), node(2, 2, 0b01101), node(2, 1, 0b10011)]
+    for eng, w in ((prod, prod.debug_write), (orc, orc.write)):
+        w("feed", 0, feed.reshape(-1))
+        w("tree", 0, tree.reshape(-1))
+    runs = [(a, [E.FEED_ROW + i for i in range(4)], E.Rows.LAST, True), (b, [E.FEED_ROW + i for i in range(5)], E.Rows.LAST, True)]
+    errs.append(_step(prod, orc, runs, vr))
+    assert list(orc.array("path").reshape(-1, 16)[1][:3]) == [0, 2, 3] and orc.array("emitted")[1] == 3
+    for s, e, rows in zip((a, b), orc.array("emitted")[:2], (4, 5)):
+        prod.settle(s, rows - int(e))
+        orc.settle(s, rows - int(e))
+    assert prod.seq_len(a) == orc.seq_len(a) and prod.seq_len(b) == orc.seq_len(b)
+    for _ in range(3):
+        errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    print(f"limite {desc['n_layers']} layers d {desc['d']}: logits max-abs errors {['%.1e' % e for e in errs]}")
+    prod.close()
