@@ -107,7 +107,9 @@ typedef struct {
 
 const char* vlt_last_error(void);
 
-/* Engine::new, engine/src/engine.rs:221-250. `tuning` may be NULL. */
+/* Engine::new, engine/src/engine.rs:221-250. `tuning` may be NULL. The weight file is a plain decoder's (its `meta` tensor
+ * describes it: the benchmark's models) or one of the reference's own architecture as tools/convert.py:64-114 writes it (no
+ * `meta`; engine/src/model.rs:6-20, with the shapes read off the file). */
 int vlt_engine_new(const char* weights_path, const VltEngineConfig* cfg, const VltTuning* tuning, VltEngine** out);
 /* Drop for Engine. */
 void vlt_engine_free(VltEngine* e);

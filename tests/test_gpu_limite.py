@@ -112,3 +112,56 @@ def test_limite_forward_matches_the_oracle(model):
         errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
     print(f"limite {desc['n_layers']} layers d {desc['d']}: logits max-abs errors {['%.1e' % e for e in errs]}")
     prod.close()
+
+
+def test_generator_on_the_reference_architecture_with_its_block_drafter(tmp_path):
+    """The reference's own pairing: a target of its architecture (5 layers at its widths here) and its block drafter
+    reading two of the target's layers, through the generator, beside a request behind the replay drafter and a plain
+    one. Greedy: whatever is drafted, the tokens are those of the oracle's one-token-at-a-time decoding."""
+    from tests.test_gpu_bench_shapes import _compare_stream
+    target = tmp_path / "limite.vlt"
+    synth.write_limite(target, n_layers=5, hidden=1280, n_kv=2, ffn=3328, vocab=1024, seed=8)
+    sd = synth.block_drafter_state(2, hidden=1280, ffn=3328, layers=2, taps=(1, 3), draft_vocab=512, target_vocab=1024)
+    drafter = tmp_path / "drafter.vlt"
+    synth.write_block_drafter(drafter, sd)
+    rng = np.random.default_rng(12)
+    prompts = [rng.integers(0, 1024, n).astype(np.uint32) for n in (19, 33, 9)]
+    max_tokens = [20, 14, 10]
+    want = []
+    for p, mt in zip(prompts, max_tokens):
+        o = oracle.Engine(target, max_seqs=1, max_step_tokens=64, max_chunk=32, kv_tokens=128 * 4, max_seq_len=256, max_head_rows=8)
+        q = o.new_seq()
+        o.step([(q, p[:32], E.Rows.LAST if len(p) <= 32 else E.Rows.NONE, False)])
+        if len(p) > 32:
+            o.step([(q, p[32:], E.Rows.LAST, False)])
+        toks, margins = [], []
+        for i in range(mt):
+            lg = np.sort(o.array("logits"))
+            toks.append(int(o.array("feed")[0]))
+            margins.append(float(lg[-1] - lg[-2]))
+            if i + 1 < mt:
+                o.step([(q, [E.FEED_ROW], E.Rows.LAST, False)])
+        want.append((toks, margins))
+    eng = E.Engine(target, E.EngineConfig(max_seqs=3, max_step_tokens=64, max_chunk=32, global_kv_tokens=128 * 6, max_seq_len=256, max_head_rows=24),
+                   E.Tuning(spec_policy_off=True))
+    eng.load_drafter(drafter)
+    with eng.generator() as g:
+        g.set_replay_mistakes(0.3, 4)
+        reqs = [E.Request(list(prompts[0]), max_tokens[0], draft=E.Draft.MODEL, rows=8),
+                E.Request(list(prompts[1]), max_tokens[1], draft=E.Draft.REPLAY, rows=5, trace=list(prompts[1]) + want[1][0]),
+                E.Request(list(prompts[2]), max_tokens[2])]
+        ids = [g.submit(r) for r in reqs]
+        got = {i: [] for i in ids}
+        for _ in range(400):
+            if g.is_idle():
+                break
+            for ev in g.step():
+                if ev.kind == "token":
+                    got[ev.req].append(ev.value)
+        assert g.is_idle()
+    for i, rid in enumerate(ids):
+        toks, margins = want[i]
+        assert _compare_stream(got[rid], toks, margins) >= 4, f"request {i}"
+        assert len(got[rid]) == max_tokens[i]
+    assert len(eng.debug_read("free_pages")) == 6
+    eng.close()
