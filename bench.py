@@ -262,6 +262,40 @@ def spec_accept_figure(E, eng, hbm_peak):
             "frac_of_hbm_peak": nbytes / secs / 1e9 / hbm_peak, "mean_accepted": float(acc.mean())}
 
 
+def limite_figure(E, local, ctx, steps=30):
+    """The reference's own architecture at its shapes (48 layers, hidden 1280, 10 query / 2 kv heads of 128, FFN 3328,
+    151 680 ids, bf16, random-init) through this library's parity path (small kernels, no tuning): decoding one token a step
+    at 1, 8 and 32 streams over contexts advanced without computing them. Not BASELINE's metric: a figure for the record."""
+    from silicon_violetto_b200 import synth
+    CACHE.mkdir(parents=True, exist_ok=True)
+    path = CACHE / "limite_48x1280_bf16.vlt"
+    done = path.with_suffix(".ok")
+    if not done.exists():
+        synth.write_limite(path, n_layers=48, hidden=1280, n_kv=2, ffn=3328, vocab=151680, seed=0)
+        done.write_text("ok")
+    out = {"workload": f"reference architecture 48 x 1280, bf16, ctx {ctx}, one token per stream and step"}
+    for n_s in (1, 8, 32):
+        cfg = E.EngineConfig(max_seqs=n_s, max_step_tokens=64, max_chunk=32, global_kv_tokens=n_s * (ctx + 256), max_seq_len=ctx + 256, max_head_rows=8 * n_s, device_ordinal=local)
+        eng = E.Engine(path, cfg, E.Tuning(spec_policy_off=True))
+        seqs = [eng.new_seq() for _ in range(n_s)]
+        for s_ in seqs:
+            eng.bench_fill(s_, ctx)
+        with eng.generator() as g:
+            for j, s_ in enumerate(seqs):
+                g.submit(E.Request(("resume", s_, 100 + j), steps + 16, sampling=E.Sampling(0.6, 0.95, 1 + j)))
+            for _ in range(4):
+                g.step()
+            eng.mark(0)
+            for _ in range(steps):
+                g.step()
+            eng.mark(1)
+            g.step()
+            ms = eng.mark_elapsed_ms() / steps
+        eng.close()
+        out[f"streams_{n_s}"] = {"ms_per_step": ms, "tokens_per_s": n_s / (ms * 1e-3)}
+    return out
+
+
 def prefill_figure(E, path, ctx, local, chunk=512):
     """A `ctx`-token prompt of the reference's LCG ids computed in chunks of `chunk` tokens through the generator (the
     tensor-core GEMM in blocks of 256 tokens, the chunk attention kernel), one stream; device time from the first chunk's
@@ -309,7 +343,7 @@ def main():
     ap.add_argument("--long-steps", type=int, default=20)
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
-    ap.add_argument("--only", default="", help="'prefill' or 'acceptance': run that one pass alone and print its figure (a profiler-size command, not the bench line)")
+    ap.add_argument("--only", default="", help="'prefill', 'acceptance' or 'limite' (the reference's own architecture at its shapes, decoding): run that one pass alone and print its figure (not the bench line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -362,8 +396,10 @@ def main():
         elif args.only == "acceptance":
             e1, _ = make_engine(E, path, 2, 64, 8, local)
             print(json.dumps(spec_accept_figure(E, e1, hbm_peak)))
+        elif args.only == "limite":
+            print(json.dumps(limite_figure(E, local, args.ctx)))
         else:
-            raise SystemExit(f"--only {args.only}: 'prefill' or 'acceptance'")
+            raise SystemExit(f"--only {args.only}: 'prefill', 'acceptance' or 'limite'")
         return
     total = args.warmup + args.steps + 6
     # The headline pass, on every rank: the int8 target with the chain drafter loaded (1 layer + fc + a head over 16 384 draft

@@ -192,6 +192,7 @@ Engine::Engine(const std::string& weights, const EngineConfig& c, const Tuning& 
             for (Buffer* b : {&lim->hist0, &lim->hist12, &lim->hist23, &lim->xattn, &lim->base, &lim->mixed}) b->alloc(n * md.d * 4, false);
             lim->vdir.alloc(n * md.n_kv * 128 * 4, false);
             lim->gates.alloc(n * md.n_heads * 4, false);
+            lim->part.alloc(n * md.n_heads * size_t(LIMITE_MAX_SPLITS) * LIMITE_PART * 4, false);
         }
         VLT_CUDA(cudaDeviceSynchronize());
     }
@@ -813,7 +814,7 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
         span_end(sp);
         sp = span_begin(G_ATTN);
         launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
-                           n, s.attn.as<float>(), stream);
+                           n, (x.global ? p.max_keys : std::min(p.max_keys, LIMITE_WINDOW)) + 8, L.part.as<float>(), s.attn.as<float>(), stream);
         span_end(sp);
         sp = span_begin(G_MATMUL);
         float* out = li == 11 ? L.hist12.as<float>() : li == 22 ? L.hist23.as<float>() : s.h.as<float>();  // encode.rs:116-122 `resid_out`

@@ -231,7 +231,7 @@ class Engine {
     struct LimiteState {
         uint32_t ring = 0;
         Buffer k_local, v_local;  // [local layer][slot][kv head][ring][128] bf16
-        Buffer hist0, hist12, hist23, xattn, base, mixed, vdir, gates;
+        Buffer hist0, hist12, hist23, xattn, base, mixed, vdir, gates, part;  // part: the attention's partials per (token, head, key split)
     };
     std::unique_ptr<LimiteState> lim;
     LimiteKv limite_kv(const LimiteLayer& x) const;
