@@ -286,22 +286,55 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
 }
 
 // The splits' partials of a (token, head) added up (an empty split has m = -inf), then XSA and the gate
-// (kernels.metal:1314-1362 `attn_dec_reduce`). grid (tokens, heads), one warp.
-__global__ void merge_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_q, uint32_t n_kv, const float* __restrict__ vdir,
-                             const float* __restrict__ gates, const float* __restrict__ xsa, float* out) {
+// (kernels.metal:1314-1362 `attn_dec_reduce`). grid (tokens, heads), four warps: warp w takes splits w, w + 4, ..., eight
+// at a time with their loads together (one after the other each is an L2 round trip, and there are up to 128); the warps'
+// sums meet in shared memory.
+__global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_q, uint32_t n_kv, const float* __restrict__ vdir,
+                                                    const float* __restrict__ gates, const float* __restrict__ xsa, float* out) {
     pdl_start();
-    const uint32_t t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, d0 = 4 * lane, g = h / (n_q / n_kv);
+    __shared__ float ms[4], ls[4];
+    __shared__ float os[4][D];
+    const uint32_t t = blockIdx.x, h = blockIdx.y, w = threadIdx.x / 32, lane = threadIdx.x % 32, d0 = 4 * lane, g = h / (n_q / n_kv);
     const float* pp = part + (size_t(t) * n_q + h) * max_splits * PART;
-    float mm = -INFINITY;
-    for (uint32_t s = 0; s < max_splits; s++) mm = fmaxf(mm, pp[s * PART]);
+    float m = -INFINITY, l = 0.0f;
+    float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint32_t s0 = w; s0 < max_splits; s0 += 32) {
+        float2 ml[8];
+        float4 ov[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8; u++) {
+            const uint32_t sp = s0 + 4 * u;
+            ml[u] = make_float2(-INFINITY, 0.0f);
+            ov[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (sp < max_splits) {
+                ml[u] = *reinterpret_cast<const float2*>(pp + sp * PART);
+                ov[u] = *reinterpret_cast<const float4*>(pp + sp * PART + 4 + d0);
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 8; u++) {
+            if (ml[u].x == -INFINITY) continue;  // (the same for the whole warp)
+            const float mn = fmaxf(m, ml[u].x), corr = __expf(m - mn), wk = __expf(ml[u].x - mn);
+            l = l * corr + ml[u].y * wk;
+            o.x = o.x * corr + ov[u].x * wk;
+            o.y = o.y * corr + ov[u].y * wk;
+            o.z = o.z * corr + ov[u].z * wk;
+            o.w = o.w * corr + ov[u].w * wk;
+            m = mn;
+        }
+    }
+    if (lane == 0) { ms[w] = m; ls[w] = l; }
+    *reinterpret_cast<float4*>(&os[w][d0]) = o;
+    __syncthreads();
+    if (w) return;
+    const float mm = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
     float ll = 0.0f;
     float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (uint32_t s = 0; s < max_splits; s++) {
-        const float ms = pp[s * PART];
-        if (ms == -INFINITY) continue;  // (the same for the whole warp)
-        const float wk = __expf(ms - mm);
-        const float4 ok = *reinterpret_cast<const float4*>(pp + s * PART + 4 + d0);
-        ll += pp[s * PART + 1] * wk;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float wk = ms[k] == -INFINITY ? 0.0f : __expf(ms[k] - mm);
+        const float4 ok = *reinterpret_cast<const float4*>(&os[k][d0]);
+        ll += ls[k] * wk;
         oo.x += ok.x * wk; oo.y += ok.y * wk; oo.z += ok.z * wk; oo.w += ok.w * wk;
     }
     oo.x /= ll; oo.y /= ll; oo.z /= ll; oo.w /= ll;
@@ -356,15 +389,15 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
         launch_pdl(limite::attn_kernel, dim3(n, n_q), 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, vdir, gates, xsa, out);
         return;
     }
-    // Blocks of at least 128 keys (a warp's eight batches), as many as fill the GPU a few times over, at most LIMITE_MAX_SPLITS.
-    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 127) / 128, 2048u / std::max(n * kv.n_kv, 1u)}));
+    // Blocks of at least 64 keys (four batches a warp), as many as fill the GPU a few times over, at most LIMITE_MAX_SPLITS.
+    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, 2048u / std::max(n * kv.n_kv, 1u)}));
     const uint32_t kps = ((max_keys + splits - 1) / splits + 15) / 16 * 16;
     splits = (max_keys + kps - 1) / kps;
     const dim3 grid(n, kv.n_kv, splits);
     if (G == 1) launch_pdl(limite::attn_split_kernel<1>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
     else if (G == 2) launch_pdl(limite::attn_split_kernel<2>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
     else launch_pdl(limite::attn_split_kernel<5>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
-    launch_pdl(limite::merge_kernel, dim3(n, n_q), 32, 0, s, part, splits, n_q, kv.n_kv, vdir, gates, xsa, out);
+    launch_pdl(limite::merge_kernel, dim3(n, n_q), 128, 0, s, part, splits, n_q, kv.n_kv, vdir, gates, xsa, out);
 }
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
                            uint16_t* k_global, uint16_t* v_global, const LimiteKv& local, const LimiteKv& global, uint32_t n_local, uint32_t n_global, uint32_t n_runs,
