@@ -466,7 +466,14 @@ bool Engine::stream_fits(const Matrix& w) const {
 bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
     const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 9;  // up to 8 tokens the streamed kernel; 9..15 would take it twice over the weights
     const bool grouped = w.int8 && w.group < w.k;
-    return !model.limite && n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;  // (the GEMM has no matrix scales or residual lambdas)
+    return !model.limite && n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;  // (the reference's architecture decides for itself: gemm_fits)
+}
+
+// Whether the tensor-core GEMM takes this matrix at n tokens (the plain decoder's rule, for the reference's architecture).
+bool Engine::gemm_fits(const Matrix& w, uint32_t n) const {
+    const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 9;
+    const bool grouped = w.int8 && w.group < w.k;
+    return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
 }
 
 bool Engine::layer_carries(const Layer& l, uint32_t n) const {
@@ -474,8 +481,11 @@ bool Engine::layer_carries(const Layer& l, uint32_t n) const {
 }
 
 void Engine::matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
-                         uint32_t vocab_real, const QkvEpilogue* q, float* ssq_out, const float* ssq_in) {
+                         uint32_t vocab_real, const QkvEpilogue* q, float* ssq_out, const float* ssq_in, float scale, float ra, float rb) {
     MatArgs a{};
+    a.scale = scale;
+    a.ra = ra;
+    a.rb = rb;
     a.W = w.w;
     a.scales = w.scales;
     a.Xb = xb;
@@ -805,8 +815,18 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
         const LimiteKv kva = limite_kv(x);
         uint16_t* kc = x.global ? kv.k.as<uint16_t>() : L.k_local.as<uint16_t>();
         uint16_t* vc = x.global ? kv.v.as<uint16_t>() : L.v_local.as<uint16_t>();
+        // From 9 tokens on, and if the projections' shapes and scales fit it (bf16, or int8 with one scale per row -- the
+        // reference's own int8 files have groups of 64 and stay on the streamed kernel), the tensor-core GEMM: activations go
+        // in as bf16 copies, 1 / rms from a row pass or from the sums of squares the GEMM before left.
+        const uint32_t G = md.n_heads / md.n_kv;
+        const bool big = gemm_fits(l.qkv, n) && gemm_fits(l.o, n) && gemm_fits(l.gate_up, n) && gemm_fits(l.down, n) && (G == 1 || G == 2 || G == 5) && md.d % 128 == 0;
         sp = span_begin(G_MATMUL);
-        matmul(l.qkv, n, xa, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>(), 0, nullptr, nullptr, nullptr, x.qkv_scale);
+        if (big) {
+            launch_prep_rows(xa, nullptr, n, H, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>(), 0, nullptr, nullptr, nullptr, x.qkv_scale);
+        } else {
+            matmul(l.qkv, n, xa, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>(), 0, nullptr, nullptr, nullptr, x.qkv_scale);
+        }
         span_end(sp);
         sp = span_begin(G_SMALL);
         launch_limite_qkv_post(s.qkv.as<float>(), xa, s.inv.as<float>(), meta, tin, st.in<uint32_t>(st.o_tokens), model.value_embed, x.ve_gate, x.attn_gate, rope_tab.as<float>(), kva,
@@ -814,13 +834,20 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
         span_end(sp);
         sp = span_begin(G_ATTN);
         launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
-                           n, (x.global ? p.max_keys : std::min(p.max_keys, LIMITE_WINDOW)) + 8, L.part.as<float>(), s.attn.as<float>(), stream);
+                           n, (x.global ? p.max_keys : std::min(p.max_keys, LIMITE_WINDOW)) + 8, L.part.as<float>(), s.attn.as<float>(), big ? s.attn_b.as<uint16_t>() : nullptr, stream);
         span_end(sp);
         sp = span_begin(G_MATMUL);
         float* out = li == 11 ? L.hist12.as<float>() : li == 22 ? L.hist23.as<float>() : s.h.as<float>();  // encode.rs:116-122 `resid_out`
-        matmul(l.o, n, s.attn.as<float>(), L.mixed.as<float>(), EPI_RESID, base, nullptr, 0, nullptr, nullptr, nullptr, x.o_scale, x.resid_attn, x.post_attn);
-        matmul(l.gate_up, n, L.mixed.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
-        matmul(l.down, n, s.act.as<float>(), out, EPI_RESID, L.mixed.as<float>(), nullptr, 0, nullptr, nullptr, nullptr, 1.0f, x.resid_mlp, x.post_mlp);
+        if (big) {
+            matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), L.mixed.as<float>(), s.h_b.as<uint16_t>(), EPI_RESID, base, nullptr, 0, nullptr, s.ssq.as<float>(), nullptr, x.o_scale,
+                        x.resid_attn, x.post_attn);
+            matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, nullptr, 0, nullptr, nullptr, s.ssq.as<float>());
+            matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), out, nullptr, EPI_RESID, L.mixed.as<float>(), nullptr, 0, nullptr, nullptr, nullptr, 1.0f, x.resid_mlp, x.post_mlp);
+        } else {
+            matmul(l.o, n, s.attn.as<float>(), L.mixed.as<float>(), EPI_RESID, base, nullptr, 0, nullptr, nullptr, nullptr, x.o_scale, x.resid_attn, x.post_attn);
+            matmul(l.gate_up, n, L.mixed.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
+            matmul(l.down, n, s.act.as<float>(), out, EPI_RESID, L.mixed.as<float>(), nullptr, 0, nullptr, nullptr, nullptr, 1.0f, x.resid_mlp, x.post_mlp);
+        }
         span_end(sp);
         cur = out;
         auto tap = std::find(tap_layers.begin(), tap_layers.end(), li);
@@ -830,8 +857,10 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
     sp = span_begin(G_TAIL);
     if (p.n_hidden) launch_prep_rows(cur, st.in<uint32_t>(st.o_hidden_rows), p.n_hidden, H, md.eps, s.hfin_all.as<float>(), nullptr, nullptr, true, false, stream);
     if (p.n_head) {
-        launch_prep_rows(cur, st.in<uint32_t>(st.o_head_rows), p.n_head, H, md.eps, s.hfin_head.as<float>(), nullptr, nullptr, true, false, stream);
-        matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD_CAP, nullptr, nullptr);
+        const bool big_head = gemm_fits(model.head, p.n_head);
+        launch_prep_rows(cur, st.in<uint32_t>(st.o_head_rows), p.n_head, H, md.eps, s.hfin_head.as<float>(), big_head ? s.hfin_b.as<uint16_t>() : nullptr, nullptr, true, false, stream);
+        if (big_head) matmul_gemm(model.head, p.n_head, s.hfin_b.as<uint16_t>(), s.logits.as<float>(), nullptr, EPI_HEAD_CAP, nullptr, nullptr);
+        else matmul(model.head, p.n_head, s.hfin_head.as<float>(), s.logits.as<float>(), EPI_HEAD_CAP, nullptr, nullptr);
         if (!forced_logits.empty()) {
             if (forced_logits.size() != size_t(p.n_head) * md.vocab) throw Error("forced logits: wrong size");
             VLT_CUDA(cudaMemcpyAsync(s.logits.dev, forced_logits.data(), forced_logits.size() * 4, cudaMemcpyHostToDevice, stream));

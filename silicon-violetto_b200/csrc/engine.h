@@ -271,8 +271,10 @@ class Engine {
     bool stream_fits(const Matrix& w) const;
     // The tensor-core GEMM: xb is x in bf16, inv the rows' 1/rms (normed epilogues), yb an optional bf16 copy of y.
     void matmul_gemm(const Matrix& w, uint32_t n, const uint16_t* xb, float* y, uint16_t* yb, uint32_t epi, const float* base, const float* inv,
-                     uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr, float* ssq_out = nullptr, const float* ssq_in = nullptr);
+                     uint32_t vocab_real = 0, const QkvEpilogue* q = nullptr, float* ssq_out = nullptr, const float* ssq_in = nullptr, float scale = 1.0f, float ra = 1.0f,
+                     float rb = 1.0f);
     bool use_gemm(const Matrix& w, uint32_t n) const;
+    bool gemm_fits(const Matrix& w, uint32_t n) const;
     // A layer of n tokens runs on the tensor-core GEMM and its last projection leaves bf16(h) in h_b and h's sums of squares in ssq.
     bool layer_carries(const Layer& l, uint32_t n) const;
     // What a decoder layer runs on: its weights, the step layout (device arrays), the cache it writes and reads.

@@ -430,9 +430,10 @@ __global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 :
                 const float other = __shfl_xor_sync(0xffffffffu, x, 1);
                 const float gt = x * inv[j], up = other * inv[j];
                 y[j] = gt * __fdividef(1.0f, 1.0f + __expf(-gt)) * up;
-            } else if (EPI == EPI_NORM) y[j] = x * inv[j];
-            else if (EPI == EPI_RESID) y[j] = base[j] + x;
+            } else if (EPI == EPI_NORM) y[j] = x * inv[j] * m.scale;
+            else if (EPI == EPI_RESID) y[j] = m.ra * base[j] + m.rb * (m.scale * x);  // (1, 1, 1 for a plain decoder: the same bits as base + x)
             else if (EPI == EPI_HEAD) y[j] = row < m.vocab_real ? x * inv[j] : -INFINITY;
+            else if (EPI == EPI_HEAD_CAP) y[j] = row < m.vocab_real ? 23.0f * (1.0f / (1.0f + __expf(-(x + 5.0f) / 7.5f))) : -INFINITY;  // kernels.metal:196-199
             else y[j] = x;
         }
         if (EPI == EPI_RESID && m.ssq_out) {
@@ -607,6 +608,7 @@ static GemmEntry gemm_entry(bool int8, uint32_t epi, bool paired = false) {
     case EPI_SWIGLU: return int8 ? gemm::gemm_kernel<true, EPI_SWIGLU> : gemm::gemm_kernel<false, EPI_SWIGLU>;
     case EPI_HEAD: return int8 ? gemm::gemm_kernel<true, EPI_HEAD> : gemm::gemm_kernel<false, EPI_HEAD>;
     case EPI_QKV: return int8 ? gemm::gemm_kernel<true, EPI_QKV> : gemm::gemm_kernel<false, EPI_QKV>;
+    case EPI_HEAD_CAP: return int8 ? gemm::gemm_kernel<true, EPI_HEAD_CAP> : gemm::gemm_kernel<false, EPI_HEAD_CAP>;
     default: return int8 ? gemm::gemm_kernel<true, EPI_RAW> : gemm::gemm_kernel<false, EPI_RAW>;
     }
 }
@@ -614,7 +616,7 @@ static GemmEntry gemm_entry(bool int8, uint32_t epi, bool paired = false) {
 bool gemm_supported(const MatArgs& a) {
     const bool grouped = a.int8 && a.group < a.k;
     return a.n >= 1 && a.n <= 256 && a.m % gemm::BM == 0 && a.k % gemm::BK == 0 && !grouped && a.Xb != nullptr &&
-           (a.epi == EPI_RESID || a.epi == EPI_RAW || a.inv_in != nullptr || a.ssq_in != nullptr);
+           (a.epi == EPI_RESID || a.epi == EPI_RAW || a.epi == EPI_HEAD_CAP || a.inv_in != nullptr || a.ssq_in != nullptr);
 }
 
 void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaStream_t s, bool allow_paired) {
@@ -657,7 +659,7 @@ void launch_gemm(const MatArgs& a, uint32_t sm_count, uint32_t* err_flag, cudaSt
     const size_t smem = paired ? need : std::max<size_t>(need, 116 * 1024);
     configured.once([] {
         for (int i8 = 0; i8 < 2; i8++)
-            for (uint32_t epi = EPI_NORM; epi <= EPI_QKV; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            for (uint32_t epi = EPI_NORM; epi <= EPI_HEAD_CAP; epi++) VLT_CUDA(cudaFuncSetAttribute(gemm_entry(i8 != 0, epi), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         VLT_CUDA(cudaFuncSetAttribute(gemm_entry(true, EPI_HEAD, true), cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
         VLT_CUDA(cudaFuncSetAttribute(gemm_entry(true, EPI_HEAD, true), cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     });

@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
 // at a time with their loads together (one after the other each is an L2 round trip, and there are up to 128); the warps'
 // sums meet in shared memory.
 __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ part, uint32_t max_splits, uint32_t n_q, uint32_t n_kv, const float* __restrict__ vdir,
-                                                    const float* __restrict__ gates, const float* __restrict__ xsa, float* out) {
+                                                    const float* __restrict__ gates, const float* __restrict__ xsa, float* out, uint16_t* out_b) {
     pdl_start();
     __shared__ float ms[4], ls[4];
     __shared__ float os[4][D];
@@ -341,7 +341,9 @@ __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pa
     const float4 vd = *reinterpret_cast<const float4*>(vdir + (size_t(t) * n_kv + g) * D + d0);
     const float pr = warp_sum(oo.x * vd.x + oo.y * vd.y + oo.z * vd.z + oo.w * vd.w);
     const float xs = xsa[h] * pr, gt = gates[size_t(t) * n_q + h];
-    *reinterpret_cast<float4*>(out + (size_t(t) * n_q + h) * D + d0) = make_float4((oo.x - xs * vd.x) * gt, (oo.y - xs * vd.y) * gt, (oo.z - xs * vd.z) * gt, (oo.w - xs * vd.w) * gt);
+    const float4 r = make_float4((oo.x - xs * vd.x) * gt, (oo.y - xs * vd.y) * gt, (oo.z - xs * vd.z) * gt, (oo.w - xs * vd.w) * gt);
+    *reinterpret_cast<float4*>(out + (size_t(t) * n_q + h) * D + d0) = r;
+    if (out_b) *reinterpret_cast<uint2*>(out_b + (size_t(t) * n_q + h) * D + d0) = make_uint2(pack_bf16(r.x, r.y), pack_bf16(r.z, r.w));  // for a tensor-core o projection
 }
 
 // kernels.metal:1663-1693 `kv_compact` over the local rings and the global pool. grid (runs, local + global layers), a warp
@@ -383,9 +385,10 @@ void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, co
 // one-block-per-(token, head) kernel.
 void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
                         const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
-                        uint32_t max_keys, float* part, float* out, cudaStream_t s) {
+                        uint32_t max_keys, float* part, float* out, uint16_t* out_b, cudaStream_t s) {
     const uint32_t G = n_q / kv.n_kv;
     if (G != 1 && G != 2 && G != 5) {
+        if (out_b) throw Error("internal: the one-block attention leaves no bf16 copy");
         launch_pdl(limite::attn_kernel, dim3(n, n_q), 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, vdir, gates, xsa, out);
         return;
     }
@@ -397,7 +400,7 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
     if (G == 1) launch_pdl(limite::attn_split_kernel<1>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
     else if (G == 2) launch_pdl(limite::attn_split_kernel<2>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
     else launch_pdl(limite::attn_split_kernel<5>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
-    launch_pdl(limite::merge_kernel, dim3(n, n_q), 128, 0, s, part, splits, n_q, kv.n_kv, vdir, gates, xsa, out);
+    launch_pdl(limite::merge_kernel, dim3(n, n_q), 128, 0, s, part, splits, n_q, kv.n_kv, vdir, gates, xsa, out, out_b);
 }
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
                            uint16_t* k_global, uint16_t* v_global, const LimiteKv& local, const LimiteKv& global, uint32_t n_local, uint32_t n_global, uint32_t n_runs,

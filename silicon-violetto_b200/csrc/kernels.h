@@ -43,7 +43,7 @@ struct MatArgs {
     uint32_t epi, vocab_real;
     float eps;
     // kernels.metal:164-165,188-193: the matrix scale (qkv_scale, o_scale) and EPI_RESID's y = ra base + rb (scale acc). 1 for a
-    // plain decoder; honoured by the streamed and the scalar matmul, not by the tensor-core GEMM.
+    // plain decoder.
     float scale = 1.0f, ra = 1.0f, rb = 1.0f;
     bool int8;
     QkvEpilogue q;  // EPI_QKV only
@@ -172,7 +172,7 @@ void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, co
 constexpr uint32_t LIMITE_MAX_SPLITS = 128, LIMITE_PART = 132;  // key splits a row's attention may take; floats per partial
 void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
                         const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
-                        uint32_t max_keys, float* part, float* out, cudaStream_t s);
+                        uint32_t max_keys, float* part, float* out, uint16_t* out_b, cudaStream_t s);  // out_b: optional bf16 copy (heads per kv head 1, 2 or 5)
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
                            uint16_t* k_global, uint16_t* v_global, const LimiteKv& local, const LimiteKv& global, uint32_t n_local, uint32_t n_global, uint32_t n_runs,
                            cudaStream_t s);
