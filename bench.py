@@ -7,8 +7,9 @@ streams -- no collective on the data path; ranks only meet at the timing barrier
 is one decode step of every stream on the rank: the chain drafter's catch-up and k = 4 draft passes,
 k + 1 rows per stream through the int8 target, acceptance at T = 0.6 (rejection sampling against the
 drafter's distribution) and KV commit. Further passes in the same JSON line: the target alone behind the
-replay drafter, 1 and 8 streams, bf16 at one stream, the 64k context, the acceptance kernel alone, and
-the CPU restatement's sample. Prints one JSON line.
+replay drafter, 1 and 8 streams, bf16 at one stream, the 64k context, the acceptance kernel alone, a drafter without
+its attention window, prefill, the reference's own architecture at its shapes (plain decoding), and the CPU
+restatement's sample. Prints one JSON line.
 """
 from __future__ import annotations
 
@@ -343,6 +344,7 @@ def main():
     ap.add_argument("--long-steps", type=int, default=20)
     ap.add_argument("--attn-keys", type=int, default=0, help="keys per attention block (0: the engine's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
+    ap.add_argument("--no-limite", action="store_true", help="skip the reference-architecture pass of the extras (it writes a 2 GB file first)")
     ap.add_argument("--limite-streams", default="1,8,32", help="stream counts of --only limite")
     ap.add_argument("--only", default="", help="'prefill', 'acceptance' or 'limite' (the reference's own architecture at its shapes, decoding): run that one pass alone and print its figure (not the bench line)")
     args = ap.parse_args()
@@ -532,6 +534,13 @@ def main():
             eb.close()
             out["bf16_streams_1"] = {"value": rb["emitted"] / (rb["dev_ms"] * 1e-3), "unit": "tokens/s (this rank)", "ms_per_step": rb["dev_ms"] / steps, "e2e": rb["emitted"] / rb["wall"],
                                      "mean_accepted_len": rb["emitted"] / steps}
+        if not args.no_limite:
+            # Not BASELINE's metric: the reference's own architecture at its shapes through this library, plain decoding. It
+            # needs a 2 GB random-init file written first; whatever goes wrong there is reported, not raised.
+            try:
+                out["reference_architecture_pass"] = limite_figure(E, local, args.ctx)
+            except Exception as e:  # noqa: BLE001
+                out["reference_architecture_pass"] = {"error": str(e)[:300]}
     if world == 1 and not args.no_cpu:
         t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)
         out["cpu_baseline"] = {"value": em / t_step, "unit": "tokens/s", "cores": cores, "kind": "port",
