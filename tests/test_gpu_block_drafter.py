@@ -30,7 +30,8 @@ def files(tmp_path_factory):
         sd = synth.block_drafter_state(1, hidden=1280, ffn=3328, layers=2, taps=(0, 1), draft_vocab=DRAFT_V, target_vocab=TARGET["vocab"])
         sd["out_gain"] = sd["out_gain"] * 16  # logits up to 10 instead of 0.6: a row's best candidates are then no near-ties
         paths[window] = d / f"drafter_w{window}.vlt"
-        synth.write_block_drafter(paths[window], sd, window=window)
+        # (the exporter's default is int8 in groups of 64, the head in groups of 8: the window-48 file is written that way)
+        synth.write_block_drafter(paths[window], sd, window=window, int8=window == 48)
     return d / "target.vlt", paths
 
 
