@@ -9,7 +9,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libvioletto_b200.so"
-SOURCES = ["abi.cc", "generator.cc", "router.cc", "engine.cu", "k_small.cu", "k_matmul.cu", "k_attn.cu", "k_gemm.cu", "k_spec.cu", "k_draft.cu", "k_prefill.cu", "k_block.cu", "k_limite.cu"]
+SOURCES = ["abi.cc", "generator.cc", "router.cc", "engine.cu", "k_small.cu", "k_matmul.cu", "k_attn.cu", "k_gemm.cu", "k_spec.cu", "k_draft.cu", "k_prefill.cu", "k_block.cu", "k_limite.cu", "k_limite_attn.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-x", "cu",
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]

@@ -3,10 +3,9 @@
 // scales and residual lambdas in its epilogue. Here: `mudd` (kernels.metal:1364-1407), the per-token work after the qkv
 // projection (`qkv_post` / `new_key`, :725-801,910-945: q/k RMS-norm per head of 128, RoPE on the first 64 dims of local
 // layers, gated value embeddings, K/V rounded into a ring per (local layer, slot) or into the paged pool of the global
-// layers, XSA directions, attention gates), the attention of a row over its window and its tile under `vis` with XSA and
-// the gate applied (`attn_verify` + `attn_dec_reduce`, :809-811,1019-1062,1314-1362), and the path compaction over both
-// kinds of cache (`kv_compact`, :1663-1693). One block per token or per (token, head): this path is built for parity with
-// the oracle's restatement, not yet for speed.
+// layers, XSA directions, attention gates), the merge of the attention's key splits with XSA and the gate applied
+// (`attn_dec_reduce`, :1314-1362; the attention itself is k_limite_attn.cu, and a one-block form of it here serves kv
+// heads with more than eight query heads), and the path compaction over both kinds of cache (`kv_compact`, :1663-1693).
 #include <algorithm>
 #include <cfloat>
 
@@ -199,91 +198,7 @@ __global__ void attn_kernel(const float* __restrict__ qkv, const uint32_t* __res
     *reinterpret_cast<float4*>(out + (size_t(t) * n_q + h) * D + d0) = make_float4((oo.x - xs * vd.x) * gt, (oo.y - xs * vd.y) * gt, (oo.z - xs * vd.z) * gt, (oo.w - xs * vd.w) * gt);
 }
 
-// The same attention for all the query heads of a kv head at once and with the keys split over blocks: grid (tokens, kv
-// heads, key splits), four warps. A block takes a contiguous share of the row's keys (the cached ones from its window start,
-// then its tile's eight slots under `vis`); a warp takes them four at a time with the loads of all four ahead of the
-// arithmetic, a lane four of the 128 dims, and every key is multiplied with the G query heads that share it. Partials
-// (m, l, o[128]) per (token, head, split) go to `part`; merge_kernel adds them up and applies XSA and the gate.
 constexpr uint32_t PART = 132;  // floats per partial: m, l, 2 pad, o[128] (kernels.metal:15)
-template <int G>
-__global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin,
-                                                         const uint32_t* __restrict__ vis, const uint16_t* __restrict__ k_cache, const uint16_t* __restrict__ v_cache,
-                                                         const LimiteKv kv, uint32_t n_q, uint32_t window, float scale, uint32_t keys_per_split, uint32_t max_splits,
-                                                         float* part) {
-    pdl_start();
-    __shared__ float ms[4][G], ls[4][G];
-    __shared__ float os[4][G][D];
-    const uint32_t t = blockIdx.x, g = blockIdx.y, sp = blockIdx.z, w = threadIdx.x / 32, lane = threadIdx.x % 32, d0 = 4 * lane;
-    const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1], mask = vis[t];
-    const uint32_t p0 = meta[2 * (t - row % 8) + 1], lo = kv.is_global ? 0u : (pos > window ? pos - window : 0u);
-    const uint32_t p_run = meta[2 * (t - row) + 1] + (row - row % 8), own = meta[2 * (t - row) + 1] + row;
-    const uint32_t n_old = p0 > lo ? p0 - lo : 0, total = n_old + 8;
-    const uint32_t begin = sp * keys_per_split, end = min(begin + keys_per_split, total);
-    const uint32_t qw = (n_q + 2 * kv.n_kv) * D;
-    float4 q[G];
-    float m[G], l[G];
-    float4 o[G];
-#pragma unroll
-    for (int h = 0; h < G; h++) {
-        q[h] = *reinterpret_cast<const float4*>(qkv + size_t(t) * qw + (g * G + h) * D + d0);
-        m[h] = -INFINITY;
-        l[h] = 0.0f;
-        o[h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    constexpr uint32_t B = 4;
-    for (uint32_t i0 = begin + w * B; i0 < end; i0 += 4 * B) {
-        uint2 kb[B], vb[B];
-        bool ok[B];
-#pragma unroll
-        for (uint32_t u = 0; u < B; u++) {
-            const uint32_t i = i0 + u;
-            ok[u] = i < end && (i < n_old || ((mask >> (i - n_old)) & 1u));
-            const uint32_t kp = !ok[u] ? own : i < n_old ? lo + i : p_run + (i - n_old);  // (an unseen slot reads the row's own key: a valid address, unused)
-            const size_t at = kv_row(kv, slot, g, kp) + d0;
-            kb[u] = *reinterpret_cast<const uint2*>(k_cache + at);
-            vb[u] = *reinterpret_cast<const uint2*>(v_cache + at);
-        }
-#pragma unroll
-        for (uint32_t u = 0; u < B; u++) {
-            if (!ok[u]) continue;  // (the same for the whole warp)
-            const float k0 = bf16lo(kb[u].x), k1 = bf16hi(kb[u].x), k2 = bf16lo(kb[u].y), k3 = bf16hi(kb[u].y);
-            const float v0 = bf16lo(vb[u].x), v1 = bf16hi(vb[u].x), v2 = bf16lo(vb[u].y), v3 = bf16hi(vb[u].y);
-#pragma unroll
-            for (int h = 0; h < G; h++) {
-                const float sc = warp_sum(q[h].x * k0 + q[h].y * k1 + q[h].z * k2 + q[h].w * k3) * scale;
-                const float mn = fmaxf(m[h], sc), corr = __expf(m[h] - mn), p = __expf(sc - mn);
-                l[h] = l[h] * corr + p;
-                o[h].x = o[h].x * corr + p * v0;
-                o[h].y = o[h].y * corr + p * v1;
-                o[h].z = o[h].z * corr + p * v2;
-                o[h].w = o[h].w * corr + p * v3;
-                m[h] = mn;
-            }
-        }
-    }
-#pragma unroll
-    for (int h = 0; h < G; h++) {
-        if (lane == 0) { ms[w][h] = m[h]; ls[w][h] = l[h]; }
-        *reinterpret_cast<float4*>(&os[w][h][d0]) = o[h];
-    }
-    __syncthreads();
-    // Warp w < G merges head w's four partials; with more heads than warps, in turns.
-    for (int h = w; h < G; h += 4) {
-        const float mm = fmaxf(fmaxf(ms[0][h], ms[1][h]), fmaxf(ms[2][h], ms[3][h]));
-        float ll = 0.0f;
-        float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const float wk = ms[k][h] == -INFINITY ? 0.0f : __expf(ms[k][h] - mm);
-            const float4 ok4 = *reinterpret_cast<const float4*>(&os[k][h][d0]);
-            ll += ls[k][h] * wk;
-            oo.x += ok4.x * wk; oo.y += ok4.y * wk; oo.z += ok4.z * wk; oo.w += ok4.w * wk;
-        }
-        float* pp = part + ((size_t(t) * n_q + g * G + h) * max_splits + sp) * PART;
-        if (lane == 0) { pp[0] = mm; pp[1] = ll; }
-        *reinterpret_cast<float4*>(pp + 4 + d0) = oo;
-    }
-}
 
 // The splits' partials of a (token, head) added up (an empty split has m = -inf), then XSA and the gate
 // (kernels.metal:1314-1362 `attn_dec_reduce`). grid (tokens, heads), four warps: warp w takes splits w, w + 4, ..., eight
@@ -387,19 +302,18 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
                         const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
                         uint32_t max_keys, float* part, float* out, uint16_t* out_b, cudaStream_t s) {
     const uint32_t G = n_q / kv.n_kv;
-    if (G != 1 && G != 2 && G != 5) {
+    if (G > 8) {
         if (out_b) throw Error("internal: the one-block attention leaves no bf16 copy");
         launch_pdl(limite::attn_kernel, dim3(n, n_q), 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, vdir, gates, xsa, out);
         return;
     }
-    // Blocks of at least 64 keys (four batches a warp), as many as fill the GPU a few times over, at most LIMITE_MAX_SPLITS.
-    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, 2048u / std::max(n * kv.n_kv, 1u)}));
-    const uint32_t kps = ((max_keys + splits - 1) / splits + 15) / 16 * 16;
+    // Enough blocks to fill the GPU twice over (three blocks of four warps an SM), of whole rounds of 64 keys (a tile of 16
+    // per warp), at most LIMITE_MAX_SPLITS.
+    const uint32_t want = (6 * 148 + n * kv.n_kv - 1) / std::max(n * kv.n_kv, 1u);  // (a B200's 148 SMs)
+    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, want}));
+    const uint32_t kps = ((max_keys + splits - 1) / splits + 63) / 64 * 64;
     splits = (max_keys + kps - 1) / kps;
-    const dim3 grid(n, kv.n_kv, splits);
-    if (G == 1) launch_pdl(limite::attn_split_kernel<1>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
-    else if (G == 2) launch_pdl(limite::attn_split_kernel<2>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
-    else launch_pdl(limite::attn_split_kernel<5>, grid, 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, kps, splits, part);
+    launch_limite_attn_mma(qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, n, kps, splits, part, s);
     launch_pdl(limite::merge_kernel, dim3(n, n_q), 128, 0, s, part, splits, n_q, kv.n_kv, vdir, gates, xsa, out, out_b);
 }
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
