@@ -798,12 +798,20 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
     const float* cur = L.hist0.as<float>();
     const uint32_t* meta = s.meta.as<uint32_t>();
     const uint32_t* tin = st.in<uint32_t>(st.o_tin);
+    // From 9 tokens on, and if the projections' shapes and scales fit it (bf16, or int8 with one scale per row -- the
+    // reference's own int8 files have groups of 64 and stay on the streamed kernel), a layer takes the tensor-core GEMM:
+    // activations go in as bf16 copies, 1 / rms from a row pass or from the sums of squares the GEMM before left.
+    auto big_of = [&](uint32_t li) {
+        const Layer& l = model.layers[li];
+        return gemm_fits(l.qkv, n) && gemm_fits(l.o, n) && gemm_fits(l.gate_up, n) && gemm_fits(l.down, n) && md.n_heads / md.n_kv <= 8 && md.d % 128 == 0;
+    };
+    auto mudd_site = [](uint32_t li) { return li == 24 ? 0 : li == 47 ? 1 : -1; };  // model.rs:20 `MUDD_LAYERS`
     for (uint32_t li = 0; li < md.n_layers; li++) {
         const Layer& l = model.layers[li];
         const LimiteLayer& x = model.lim[li];
         const float* xa = cur;
         const float* base = cur;
-        const int site = li == 24 ? 0 : li == 47 ? 1 : -1;  // model.rs:20 `MUDD_LAYERS`
+        const int site = mudd_site(li);
         if (site >= 0) {
             sp = span_begin(G_SMALL);
             launch_limite_mudd(cur, L.hist0.as<float>(), (site == 0 ? L.hist12 : L.hist23).as<float>(), model.mudd_dense1, model.mudd_mix + size_t(site) * 2 * 3 * 33, H, md.eps, n,
@@ -815,22 +823,22 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
         const LimiteKv kva = limite_kv(x);
         uint16_t* kc = x.global ? kv.k.as<uint16_t>() : L.k_local.as<uint16_t>();
         uint16_t* vc = x.global ? kv.v.as<uint16_t>() : L.v_local.as<uint16_t>();
-        // From 9 tokens on, and if the projections' shapes and scales fit it (bf16, or int8 with one scale per row -- the
-        // reference's own int8 files have groups of 64 and stay on the streamed kernel), the tensor-core GEMM: activations go
-        // in as bf16 copies, 1 / rms from a row pass or from the sums of squares the GEMM before left.
-        const uint32_t G = md.n_heads / md.n_kv;
-        const bool big = gemm_fits(l.qkv, n) && gemm_fits(l.o, n) && gemm_fits(l.gate_up, n) && gemm_fits(l.down, n) && (G == 1 || G == 2 || G == 5) && md.d % 128 == 0;
+        // The down projection before this layer left the bf16 copy and the sums of squares of this layer's input, unless
+        // a MUDD mix stands in between (or this is the first layer): then a row pass makes them.
+        const bool big = big_of(li), carried = big && li > 0 && site < 0 && big_of(li - 1);
+        const float* inv_in = carried ? nullptr : s.inv.as<float>();
+        const float* ssq_in = carried ? s.ssq.as<float>() : nullptr;
         sp = span_begin(G_MATMUL);
         if (big) {
-            launch_prep_rows(xa, nullptr, n, H, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
-            matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, s.inv.as<float>(), 0, nullptr, nullptr, nullptr, x.qkv_scale);
+            if (!carried) launch_prep_rows(xa, nullptr, n, H, md.eps, nullptr, s.h_b.as<uint16_t>(), s.inv.as<float>(), false, false, stream);
+            matmul_gemm(l.qkv, n, s.h_b.as<uint16_t>(), s.qkv.as<float>(), nullptr, EPI_NORM, nullptr, inv_in, 0, nullptr, nullptr, ssq_in, x.qkv_scale);
         } else {
             matmul(l.qkv, n, xa, s.qkv.as<float>(), EPI_NORM, nullptr, s.inv.as<float>(), 0, nullptr, nullptr, nullptr, x.qkv_scale);
         }
         span_end(sp);
         sp = span_begin(G_SMALL);
-        launch_limite_qkv_post(s.qkv.as<float>(), xa, s.inv.as<float>(), meta, tin, st.in<uint32_t>(st.o_tokens), model.value_embed, x.ve_gate, x.attn_gate, rope_tab.as<float>(), kva,
-                               H, md.n_heads, md.eps, md.vocab, n, kc, vc, L.vdir.as<float>(), L.gates.as<float>(), stream);
+        launch_limite_qkv_post(s.qkv.as<float>(), xa, inv_in, meta, tin, st.in<uint32_t>(st.o_tokens), model.value_embed, x.ve_gate, x.attn_gate, rope_tab.as<float>(), kva,
+                               H, md.n_heads, md.eps, md.vocab, n, kc, vc, L.vdir.as<float>(), L.gates.as<float>(), ssq_in, H / 128, (cfg.max_step_tokens + 15) / 16 * 16, stream);
         span_end(sp);
         sp = span_begin(G_ATTN);
         launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
@@ -842,7 +850,9 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
             matmul_gemm(l.o, n, s.attn_b.as<uint16_t>(), L.mixed.as<float>(), s.h_b.as<uint16_t>(), EPI_RESID, base, nullptr, 0, nullptr, s.ssq.as<float>(), nullptr, x.o_scale,
                         x.resid_attn, x.post_attn);
             matmul_gemm(l.gate_up, n, s.h_b.as<uint16_t>(), nullptr, s.act_b.as<uint16_t>(), EPI_SWIGLU, nullptr, nullptr, 0, nullptr, nullptr, s.ssq.as<float>());
-            matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), out, nullptr, EPI_RESID, L.mixed.as<float>(), nullptr, 0, nullptr, nullptr, nullptr, 1.0f, x.resid_mlp, x.post_mlp);
+            const bool carry = li + 1 < md.n_layers && big_of(li + 1) && mudd_site(li + 1) < 0;
+            matmul_gemm(l.down, n, s.act_b.as<uint16_t>(), out, carry ? s.h_b.as<uint16_t>() : nullptr, EPI_RESID, L.mixed.as<float>(), nullptr, 0, nullptr,
+                        carry ? s.ssq.as<float>() : nullptr, nullptr, 1.0f, x.resid_mlp, x.post_mlp);
         } else {
             matmul(l.o, n, s.attn.as<float>(), L.mixed.as<float>(), EPI_RESID, base, nullptr, 0, nullptr, nullptr, nullptr, x.o_scale, x.resid_attn, x.post_attn);
             matmul(l.gate_up, n, L.mixed.as<float>(), s.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);

@@ -92,15 +92,22 @@ __global__ void mudd_kernel(const float* __restrict__ cur, const float* __restri
 }
 
 // After the qkv projection, one block per token, a warp per head (query heads, then kv heads). x: the attention's input
-// before its norm, inv its 1 / rms.
+// before its norm; its 1 / rms from inv_rms, or (inv_rms null) from ssq.
 __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ x, const float* __restrict__ inv_rms, const uint32_t* __restrict__ meta,
                                 const uint32_t* __restrict__ tin, const uint32_t* __restrict__ tokens, const uint16_t* __restrict__ ve_table,
                                 const float* __restrict__ ve_gate, const float* __restrict__ attn_gate, const float* __restrict__ rope, const LimiteKv kv,
-                                uint32_t hidden, uint32_t n_q, float eps, uint32_t vocab, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates) {
+                                uint32_t hidden, uint32_t n_q, float eps, uint32_t vocab, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates,
+                                const float* __restrict__ ssq, uint32_t ssq_tiles, uint32_t ssq_stride) {
     pdl_start();
     const uint32_t t = blockIdx.x, w = threadIdx.x / 32, lane = threadIdx.x % 32, d0 = 4 * lane;
     const uint32_t slot = meta[2 * t], pos = meta[2 * t + 1], row = tin[2 * t + 1], qw = (n_q + 2 * kv.n_kv) * D;
-    const float inv = inv_rms[t];
+    float inv;
+    if (inv_rms) inv = inv_rms[t];
+    else {  // the sums of squares the GEMM before left per 128-row tile, as the qkv GEMM itself takes them
+        float ss = 0.0f;
+        for (uint32_t tl = 0; tl < ssq_tiles; tl++) ss += ssq[size_t(tl) * ssq_stride + t];
+        inv = rsqrtf(ss / float(hidden) + eps);
+    }
     const float* xt = x + size_t(t) * hidden;
     const float2* cs = reinterpret_cast<const float2*>(rope) + size_t(pos) * 32;
     const bool turn = !kv.is_global;  // encode.rs:227: global layers take no RoPE
@@ -291,9 +298,10 @@ void launch_limite_mudd(const float* cur, const float* tap0, const float* tap1, 
 }
 void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, const uint32_t* meta, const uint32_t* tin, const uint32_t* tokens, const uint16_t* ve_table,
                             const float* ve_gate, const float* attn_gate, const float* rope, const LimiteKv& kv, uint32_t hidden, uint32_t n_q, float eps, uint32_t vocab,
-                            uint32_t n, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates, cudaStream_t s) {
+                            uint32_t n, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates, const float* ssq, uint32_t ssq_tiles, uint32_t ssq_stride,
+                            cudaStream_t s) {
     launch_pdl(limite::qkv_post_kernel, n, 32 * (n_q + kv.n_kv), 0, s, qkv, x, inv_rms, meta, tin, tokens, ve_table, ve_gate, attn_gate, rope, kv, hidden, n_q, eps, vocab,
-               k_cache, v_cache, vdir, gates);
+               k_cache, v_cache, vdir, gates, ssq, ssq_tiles, ssq_stride);
 }
 // max_keys: the most keys a row of the step may see on this layer (its tile's eight slots included); part: room for
 // n * n_q * LIMITE_MAX_SPLITS partials of 132 floats. Heads per kv head other than 1, 2 and 5 (the reference's) take the

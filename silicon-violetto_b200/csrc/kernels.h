@@ -168,7 +168,8 @@ void launch_limite_mudd(const float* cur, const float* tap0, const float* tap1, 
                         float* out_attn, float* out_base, cudaStream_t s);
 void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, const uint32_t* meta, const uint32_t* tin, const uint32_t* tokens, const uint16_t* ve_table,
                             const float* ve_gate, const float* attn_gate, const float* rope, const LimiteKv& kv, uint32_t hidden, uint32_t n_q, float eps, uint32_t vocab,
-                            uint32_t n, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates, cudaStream_t s);
+                            uint32_t n, uint16_t* k_cache, uint16_t* v_cache, float* vdir, float* gates, const float* ssq, uint32_t ssq_tiles, uint32_t ssq_stride,
+                            cudaStream_t s);
 constexpr uint32_t LIMITE_MAX_SPLITS = 128, LIMITE_PART = 132;  // key splits a row's attention may take; floats per partial
 void launch_limite_attn_mma(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
                             const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, uint32_t n, uint32_t keys_per_split, uint32_t splits, float* part,
