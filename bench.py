@@ -263,7 +263,7 @@ def spec_accept_figure(E, eng, hbm_peak):
             "frac_of_hbm_peak": nbytes / secs / 1e9 / hbm_peak, "mean_accepted": float(acc.mean())}
 
 
-def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32)):
+def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_block=0):
     """The reference's own architecture at its shapes (48 layers, hidden 1280, 10 query / 2 kv heads of 128, FFN 3328,
     151 680 ids, bf16, random-init) through this library's parity path (small kernels, no tuning): decoding one token a step
     at 1, 8 and 32 streams over contexts advanced without computing them. Not BASELINE's metric: a figure for the record."""
@@ -277,7 +277,7 @@ def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32)):
     out = {"workload": f"reference architecture 48 x 1280, bf16, ctx {ctx}, one token per stream and step"}
     for n_s in stream_counts:
         cfg = E.EngineConfig(max_seqs=n_s, max_step_tokens=64, max_chunk=32, global_kv_tokens=n_s * (ctx + 256), max_seq_len=ctx + 256, max_head_rows=8 * n_s, device_ordinal=local)
-        eng = E.Engine(path, cfg, E.Tuning(spec_policy_off=True))
+        eng = E.Engine(path, cfg, E.Tuning(spec_policy_off=True, attn_keys_per_cta=keys_per_block))
         seqs = [eng.new_seq() for _ in range(n_s)]
         for s_ in seqs:
             eng.bench_fill(s_, ctx)
@@ -346,6 +346,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
     ap.add_argument("--no-limite", action="store_true", help="skip the reference-architecture pass of the extras (it writes a 2 GB file first)")
     ap.add_argument("--limite-streams", default="1,8,32", help="stream counts of --only limite")
+    ap.add_argument("--limite-keys", type=int, default=0, help="--only limite: keys per attention block (VltTuning.attn_keys_per_cta); 0 = the library's choice")
     ap.add_argument("--only", default="", help="'prefill', 'acceptance' or 'limite' (the reference's own architecture at its shapes, decoding): run that one pass alone and print its figure (not the bench line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -400,7 +401,7 @@ def main():
             e1, _ = make_engine(E, path, 2, 64, 8, local)
             print(json.dumps(spec_accept_figure(E, e1, hbm_peak)))
         elif args.only == "limite":
-            print(json.dumps(limite_figure(E, local, args.ctx, min(args.steps, 30), [int(x) for x in args.limite_streams.split(",")])))
+            print(json.dumps(limite_figure(E, local, args.ctx, min(args.steps, 30), [int(x) for x in args.limite_streams.split(",")], args.limite_keys)))
         else:
             raise SystemExit(f"--only {args.only}: 'prefill', 'acceptance' or 'limite'")
         return

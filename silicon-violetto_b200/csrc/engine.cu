@@ -842,7 +842,7 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
         span_end(sp);
         sp = span_begin(G_ATTN);
         launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
-                           n, (x.global ? p.max_keys : std::min(p.max_keys, LIMITE_WINDOW)) + 8, L.part.as<float>(), s.attn.as<float>(), big ? s.attn_b.as<uint16_t>() : nullptr, stream);
+                           n, (x.global ? p.max_keys : std::min(p.max_keys, LIMITE_WINDOW)) + 8, L.part.as<float>(), s.attn.as<float>(), big ? s.attn_b.as<uint16_t>() : nullptr, tuning.attn_keys_per_cta, stream);
         span_end(sp);
         sp = span_begin(G_MATMUL);
         float* out = li == 11 ? L.hist12.as<float>() : li == 22 ? L.hist23.as<float>() : s.h.as<float>();  // encode.rs:116-122 `resid_out`

@@ -308,7 +308,7 @@ void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, co
 // one-block-per-(token, head) kernel.
 void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
                         const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
-                        uint32_t max_keys, float* part, float* out, uint16_t* out_b, cudaStream_t s) {
+                        uint32_t max_keys, float* part, float* out, uint16_t* out_b, uint32_t keys_per_block, cudaStream_t s) {
     const uint32_t G = n_q / kv.n_kv;
     if (G > 8) {
         if (out_b) throw Error("internal: the one-block attention leaves no bf16 copy");
@@ -319,6 +319,7 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
     // per warp), at most LIMITE_MAX_SPLITS.
     const uint32_t want = (6 * 148 + n * kv.n_kv - 1) / std::max(n * kv.n_kv, 1u);  // (a B200's 148 SMs)
     uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, want}));
+    if (keys_per_block) splits = std::max(1u, std::min(LIMITE_MAX_SPLITS, (max_keys + keys_per_block - 1) / keys_per_block));  // (a tuning override)
     const uint32_t kps = ((max_keys + splits - 1) / splits + 63) / 64 * 64;
     splits = (max_keys + kps - 1) / kps;
     launch_limite_attn_mma(qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, n, kps, splits, part, s);

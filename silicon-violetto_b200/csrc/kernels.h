@@ -176,7 +176,7 @@ void launch_limite_attn_mma(const float* qkv, const uint32_t* meta, const uint32
                             cudaStream_t s);
 void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
                         const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
-                        uint32_t max_keys, float* part, float* out, uint16_t* out_b, cudaStream_t s);  // out_b: optional bf16 copy (heads per kv head 1, 2 or 5)
+                        uint32_t max_keys, float* part, float* out, uint16_t* out_b, uint32_t keys_per_block, cudaStream_t s);  // out_b: optional bf16 copy (heads per kv head 1, 2 or 5)
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
                            uint16_t* k_global, uint16_t* v_global, const LimiteKv& local, const LimiteKv& global, uint32_t n_local, uint32_t n_global, uint32_t n_runs,
                            cudaStream_t s);
