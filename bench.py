@@ -265,7 +265,7 @@ def spec_accept_figure(E, eng, hbm_peak):
 
 def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_block=0):
     """The reference's own architecture at its shapes (48 layers, hidden 1280, 10 query / 2 kv heads of 128, FFN 3328,
-    151 680 ids, bf16, random-init) through this library's parity path (small kernels, no tuning): decoding one token a step
+    151 680 ids, bf16, random-init): decoding one token a step
     at 1, 8 and 32 streams over contexts advanced without computing them. Not BASELINE's metric: a figure for the record."""
     from silicon_violetto_b200 import synth
     CACHE.mkdir(parents=True, exist_ok=True)
