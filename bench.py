@@ -263,10 +263,13 @@ def spec_accept_figure(E, eng, hbm_peak):
             "frac_of_hbm_peak": nbytes / secs / 1e9 / hbm_peak, "mean_accepted": float(acc.mean())}
 
 
-def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_block=0):
+def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_block=0, drafter=False):
     """The reference's own architecture at its shapes (48 layers, hidden 1280, 10 query / 2 kv heads of 128, FFN 3328,
     151 680 ids, bf16, random-init): decoding one token a step
-    at 1, 8 and 32 streams over contexts advanced without computing them. Not BASELINE's metric: a figure for the record."""
+    at 1, 8 and 32 streams over contexts advanced without computing them. With `drafter`, the reference's pairing: its
+    block drafter (tools/spec/drafter.py's shapes: 2 layers reading target layers 35 and 47, blocks of 8, window 1024, 16 384
+    draft ids; random-init, so next to nothing it drafts is accepted) drafts a tree of up to 8 rows per stream and step and
+    the target verifies it. Not BASELINE's metric: figures for the record."""
     from silicon_violetto_b200 import synth
     CACHE.mkdir(parents=True, exist_ok=True)
     path = CACHE / "limite_48x1280_bf16.vlt"
@@ -274,17 +277,26 @@ def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_bl
     if not done.exists():
         synth.write_limite(path, n_layers=48, hidden=1280, n_kv=2, ffn=3328, vocab=151680, seed=0)
         done.write_text("ok")
-    out = {"workload": f"reference architecture 48 x 1280, bf16, ctx {ctx}, one token per stream and step"}
+    dpath = CACHE / "block_drafter_1280_bf16.vlt"
+    if drafter and not dpath.with_suffix(".ok").exists():
+        synth.write_block_drafter(dpath, synth.block_drafter_state(1))
+        dpath.with_suffix(".ok").write_text("ok")
+    what = "the block drafter's tree of up to 8 rows verified per stream and step" if drafter else "one token per stream and step"
+    out = {"workload": f"reference architecture 48 x 1280, bf16, ctx {ctx}, {what}"}
     for n_s in stream_counts:
-        cfg = E.EngineConfig(max_seqs=n_s, max_step_tokens=64, max_chunk=32, global_kv_tokens=n_s * (ctx + 256), max_seq_len=ctx + 256, max_head_rows=8 * n_s, device_ordinal=local)
+        cfg = E.EngineConfig(max_seqs=n_s, max_step_tokens=max(64, 8 * n_s), max_chunk=32, global_kv_tokens=n_s * (ctx + 512), max_seq_len=ctx + 512, max_head_rows=8 * n_s,
+                             device_ordinal=local)
         eng = E.Engine(path, cfg, E.Tuning(spec_policy_off=True, attn_keys_per_cta=keys_per_block))
+        if drafter:
+            eng.load_drafter(dpath)
         seqs = [eng.new_seq() for _ in range(n_s)]
         for s_ in seqs:
             eng.bench_fill(s_, ctx)
         with eng.generator() as g:
             for j, s_ in enumerate(seqs):
-                g.submit(E.Request(("resume", s_, 100 + j), steps + 16, sampling=E.Sampling(0.6, 0.95, 1 + j)))
-            for _ in range(4):
+                g.submit(E.Request(("resume", s_, 100 + j), 8 * (steps + 16), sampling=E.Sampling(0.6, 0.95, 1 + j), draft=E.Draft.MODEL if drafter else E.Draft.NONE, rows=8 if drafter else 1))
+            warm = 4
+            for _ in range(warm):
                 g.step()
             eng.mark(0)
             for _ in range(steps):
@@ -292,8 +304,11 @@ def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_bl
             eng.mark(1)
             g.step()
             ms = eng.mark_elapsed_ms() / steps
+            timed = g.take_stats()[warm:warm + steps]
         eng.close()
-        out[f"streams_{n_s}"] = {"ms_per_step": ms, "tokens_per_s": n_s / (ms * 1e-3)}
+        emitted = sum(s_["emitted"] for s_ in timed)
+        out[f"streams_{n_s}"] = {"ms_per_step": ms, "tokens_per_s": emitted / (ms * steps * 1e-3), "mean_accepted_len": emitted / (steps * n_s),
+                                 "rows_per_step": float(np.mean([s_["tokens"] for s_ in timed]))}
     return out
 
 
@@ -346,6 +361,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers: a profiler-size case, not a bench value")
     ap.add_argument("--no-limite", action="store_true", help="skip the reference-architecture pass of the extras (it writes a 2 GB file first)")
     ap.add_argument("--limite-streams", default="1,8,32", help="stream counts of --only limite")
+    ap.add_argument("--limite-drafter", action="store_true", help="--only limite: with the reference's block drafter loaded (tree drafts of up to 8 rows)")
     ap.add_argument("--limite-keys", type=int, default=0, help="--only limite: keys per attention block (VltTuning.attn_keys_per_cta); 0 = the library's choice")
     ap.add_argument("--only", default="", help="'prefill', 'acceptance' or 'limite' (the reference's own architecture at its shapes, decoding): run that one pass alone and print its figure (not the bench line)")
     args = ap.parse_args()
@@ -401,7 +417,7 @@ def main():
             e1, _ = make_engine(E, path, 2, 64, 8, local)
             print(json.dumps(spec_accept_figure(E, e1, hbm_peak)))
         elif args.only == "limite":
-            print(json.dumps(limite_figure(E, local, args.ctx, min(args.steps, 30), [int(x) for x in args.limite_streams.split(",")], args.limite_keys)))
+            print(json.dumps(limite_figure(E, local, args.ctx, min(args.steps, 30), [int(x) for x in args.limite_streams.split(",")], args.limite_keys, args.limite_drafter)))
         else:
             raise SystemExit(f"--only {args.only}: 'prefill', 'acceptance' or 'limite'")
         return

@@ -841,7 +841,7 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
                                H, md.n_heads, md.eps, md.vocab, n, kc, vc, L.vdir.as<float>(), L.gates.as<float>(), ssq_in, H / 128, (cfg.max_step_tokens + 15) / 16 * 16, stream);
         span_end(sp);
         sp = span_begin(G_ATTN);
-        launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
+        launch_limite_attn(s.qkv.as<float>(), meta, tin, st.in<uint32_t>(st.o_vis), st.in<uint32_t>(st.o_tiles), p.tiles, kc, vc, kva, md.n_heads, LIMITE_WINDOW, md.attn_scale, L.vdir.as<float>(), L.gates.as<float>(), x.xsa,
                            n, (x.global ? p.max_keys : std::min(p.max_keys, LIMITE_WINDOW)) + 8, L.part.as<float>(), s.attn.as<float>(), big ? s.attn_b.as<uint16_t>() : nullptr, tuning.attn_keys_per_cta, stream);
         span_end(sp);
         sp = span_begin(G_MATMUL);
@@ -1206,19 +1206,53 @@ void Engine::load_block_drafter(const std::string& path) {
         f(d->inv, rows);
         f(d->attn, rows * n_q * D);
         f(d->act, rows * d->ffn);
-        f(d->corr, rows * BLOCK_CONV_KC);
+        // bf16 correction matrices also as copies of 256 rows (zero past the file's 192), which the GEMM's 128-row tiles take.
+        d->corr_stride = 2 * 128;
+        if (!d->layers.empty() && !d->layers[0].conv_corr[0].int8) {
+            const size_t one = size_t(d->corr_stride) * H * 2;
+            d->conv_pad.alloc(one * 4 * n_layers, false);  // (zeroed)
+            for (uint32_t i = 0; i < n_layers; i++)
+                for (uint32_t c = 0; c < 4; c++) {
+                    uint8_t* at = d->conv_pad.as<uint8_t>() + (size_t(i) * 4 + c) * one;
+                    const Matrix& src = d->layers[i].conv_corr[c];
+                    if (src.int8) continue;
+                    VLT_CUDA(cudaMemcpy(at, src.w, size_t(BLOCK_CONV_KC) * H * 2, cudaMemcpyDeviceToDevice));
+                    Matrix& g = d->layers[i].conv_corr_gemm[c];
+                    g.w = at;
+                    g.m = d->corr_stride;
+                    g.k = H;
+                }
+        }
+        f(d->corr, rows * d->corr_stride);
         f(d->corr_inv, rows);
+        d->xb.alloc((std::max(n, rows) + 16) * std::max<size_t>(H, d->ffn) * 2, false);  // (the GEMM's tensor maps cover whole groups of 16 rows)
+        d->act_b.alloc((rows + 16) * d->ffn * 2, false);
+        d->attn_b.alloc((rows + 16) * size_t(n_q) * D * 2, false);
+        // The attention's partials: a row's keys are at most window + 8, in splits of at least 64.
+        d->part.alloc(rows * n_q * size_t(std::min<uint32_t>(LIMITE_MAX_SPLITS, (bd.window + 8 + 63) / 64 + 1)) * LIMITE_PART * 4, false);
         f(d->logits, rows * d->v);
         f(d->cand, rows * 4);
         f(d->cand_q, rows * 4);
         f(d->meta, 2 * rows);
         for (Buffer& b : d->layout) {
-            f(b, 3 * rows + 3 * ms);
+            f(b, 4 * rows + 3 * ms);
             b.order = stream;
         }
     }
     block_drafter = std::move(d);
     set_taps(block_drafter->taps);
+}
+
+void Engine::drafter_matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, const uint16_t* xb, uint16_t* yb) {
+    if (!gemm_fits(w, n)) {
+        matmul(w, n, x, y, epi, base, inv_out, 0, nullptr, nullptr, yb);
+        return;
+    }
+    BlockDrafter& d = *block_drafter;
+    const bool norms = epi == EPI_NORM || epi == EPI_SWIGLU;
+    float* inv = norms ? (inv_out ? inv_out : d.inv.as<float>()) : nullptr;
+    if (!xb || norms) launch_prep_rows(x, nullptr, n, w.k, model.md.eps, nullptr, xb ? nullptr : d.xb.as<uint16_t>(), inv, false, false, stream);
+    matmul_gemm(w, n, xb ? xb : d.xb.as<uint16_t>(), y, yb, epi, base, inv);
 }
 
 // engine/src/engine/drafter.rs:278-447 `encode_drafter`: the context of all of the step's tokens (those on the accepted
@@ -1235,17 +1269,18 @@ void Engine::encode_block_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     const uint32_t n = p.n, H = bd.hidden;
     // 1. Context.
     for (uint32_t k = 0; k < d.fc.size(); k++)
-        matmul(d.fc[k], n, tap_bufs[k].as<float>(), d.ctx.as<float>(), k ? EPI_RESID : EPI_RAW, k ? d.ctx.as<float>() : nullptr, nullptr);
-    matmul(d.kv_all, n, d.ctx.as<float>(), d.kvp.as<float>(), EPI_NORM, nullptr, d.ctx_inv.as<float>());
+        drafter_matmul(d.fc[k], n, tap_bufs[k].as<float>(), d.ctx.as<float>(), k ? EPI_RESID : EPI_RAW, k ? d.ctx.as<float>() : nullptr, nullptr);
+    drafter_matmul(d.kv_all, n, d.ctx.as<float>(), d.kvp.as<float>(), EPI_NORM, nullptr, d.ctx_inv.as<float>());
     launch_block_context(d.kvp.as<float>(), d.ctx.as<float>(), d.ctx_inv.as<float>(), s.meta.as<uint32_t>(), s.on_path.as<uint32_t>(), rope_tab.as<float>(), bd, n,
                          d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), d.ctx_ring.as<float>(), stream);
     // 2. The blocks' layout, from the step's runs (the host's copy of what the step uploaded).
     const RunIn* runs = st.hin<RunIn>(st.o_runs);
     const size_t max_rows = size_t(cfg.max_seqs) * VERIFY_T;
-    std::vector<uint32_t> lay(3 * max_rows + 3 * size_t(cfg.max_seqs), 0);
+    std::vector<uint32_t> lay(4 * max_rows + 3 * size_t(cfg.max_seqs), 0);
     uint32_t* tin = lay.data();
     uint32_t* rows_of = tin + 2 * max_rows;
-    uint32_t* blocks = rows_of + max_rows;
+    uint32_t* sees = rows_of + max_rows;  // a block row sees every row of its block
+    uint32_t* blocks = sees + max_rows;
     uint32_t* slots = blocks + 2 * cfg.max_seqs;
     uint32_t R = 0, nb = 0;
     for (uint32_t r = 0; r < p.n_runs && rows > 1; r++) {
@@ -1257,6 +1292,7 @@ void Engine::encode_block_drafter(uint32_t set, const Plan& p, uint32_t rows) {
             tin[2 * R] = runs[r].slot;
             tin[2 * R + 1] = i;
             rows_of[R] = rows;
+            sees[R] = (1u << rows) - 1;
         }
     }
     d.last_rows = R;
@@ -1265,33 +1301,52 @@ void Engine::encode_block_drafter(uint32_t set, const Plan& p, uint32_t rows) {
     lb.write(0, lay.data(), lay.size() * 4);
     const uint32_t* d_tin = lb.as<uint32_t>();
     const uint32_t* d_rows_of = d_tin + 2 * max_rows;
-    const uint32_t* d_blocks = d_rows_of + max_rows;
+    const uint32_t* d_sees = d_rows_of + max_rows;
+    const uint32_t* d_blocks = d_sees + max_rows;
     const uint32_t* d_slots = d_blocks + 2 * cfg.max_seqs;
     float* x = d.x.as<float>();
     launch_block_embed(model.embed, d_tin, s.lens.as<uint32_t>(), s.feed.as<uint32_t>(), d.mask_emb, d.ctx_ring.as<float>(), bd, md.vocab, R, x, d.last.as<float>(),
                        d.meta.as<uint32_t>(), stream);
-    matmul(d.inject, R, d.last.as<float>(), x, EPI_RESID, x, nullptr);
+    drafter_matmul(d.inject, R, d.last.as<float>(), x, EPI_RESID, x, nullptr);
     // out = resid + conv(in) within each block (or conv(in) alone): the corrections through a matmul, then the two taps.
     auto conv = [&](const BlockDrafter::DLayer& l, uint32_t c, const float* in, const float* resid, float* out) {
-        matmul(l.conv_corr[c], R, in, d.corr.as<float>(), EPI_NORM, nullptr, d.corr_inv.as<float>());
-        launch_block_conv(in, d.corr.as<float>(), l.conv_base[c], d_tin, resid, H, R, out, stream);
+        const bool padded = l.conv_corr_gemm[c].m && gemm_fits(l.conv_corr_gemm[c], R);
+        drafter_matmul(padded ? l.conv_corr_gemm[c] : l.conv_corr[c], R, in, d.corr.as<float>(), EPI_NORM, nullptr, d.corr_inv.as<float>());
+        launch_block_conv(in, d.corr.as<float>(), padded ? d.corr_stride : BLOCK_CONV_KC, l.conv_base[c], d_tin, resid, H, R, out, stream);
     };
     for (uint32_t li = 0; li < d.layers.size(); li++) {
         const BlockDrafter::DLayer& l = d.layers[li];
         conv(l, 0, x, nullptr, d.cx.as<float>());
-        matmul(l.qkv, R, d.cx.as<float>(), d.qkv.as<float>(), EPI_NORM, nullptr, d.inv.as<float>());
+        drafter_matmul(l.qkv, R, d.cx.as<float>(), d.qkv.as<float>(), EPI_NORM, nullptr, d.inv.as<float>());
         launch_block_qkv_post(d.qkv.as<float>(), d.meta.as<uint32_t>(), rope_tab.as<float>(), bd, li, R, d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), stream);
-        launch_block_attn(d.qkv.as<float>(), d.meta.as<uint32_t>(), d_tin, d_rows_of, d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), bd, li, R, d.attn.as<float>(), stream);
-        matmul(l.o, R, d.attn.as<float>(), d.co.as<float>(), EPI_RAW, nullptr, nullptr);
+        // The attention: the reference architecture's tensor-core kernel over the layer's rings (a block's rows lie in the
+        // ring like a verified tile's, each seeing all of them; no XSA, no gate), which also leaves the o projection's bf16
+        // input; kv heads with more than eight query heads take the block kernel.
+        const bool mma_attn = bd.n_q / bd.n_kv <= 8;
+        if (mma_attn) {
+            LimiteKv ring{};
+            ring.layer = li;
+            ring.n_kv = bd.n_kv;
+            ring.ring = bd.ring;
+            ring.max_seqs = bd.max_seqs;
+            launch_limite_attn(d.qkv.as<float>(), d.meta.as<uint32_t>(), d_tin, d_sees, d_blocks, nb, d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), ring, bd.n_q, bd.window, bd.scale, nullptr,
+                               nullptr, nullptr, R, std::min(p.max_keys + VERIFY_T, bd.window) + 8, d.part.as<float>(), d.attn.as<float>(), d.attn_b.as<uint16_t>(),
+                               tuning.attn_keys_per_cta, stream);
+        } else {
+            launch_block_attn(d.qkv.as<float>(), d.meta.as<uint32_t>(), d_tin, d_rows_of, d.k_ring.as<uint16_t>(), d.v_ring.as<uint16_t>(), bd, li, R, d.attn.as<float>(), stream);
+        }
+        drafter_matmul(l.o, R, d.attn.as<float>(), d.co.as<float>(), EPI_RAW, nullptr, nullptr, mma_attn ? d.attn_b.as<uint16_t>() : nullptr);
         conv(l, 1, d.co.as<float>(), x, d.mixed.as<float>());
         conv(l, 2, d.mixed.as<float>(), nullptr, d.cx.as<float>());
-        matmul(l.gate_up, R, d.cx.as<float>(), d.act.as<float>(), EPI_SWIGLU, nullptr, nullptr);
-        matmul(l.down, R, d.act.as<float>(), d.co.as<float>(), EPI_RAW, nullptr, nullptr);
+        // The SwiGLU's bf16 output feeds the down projection's GEMM directly.
+        const bool chain = gemm_fits(l.gate_up, R) && gemm_fits(l.down, R);
+        drafter_matmul(l.gate_up, R, d.cx.as<float>(), chain ? nullptr : d.act.as<float>(), EPI_SWIGLU, nullptr, nullptr, nullptr, chain ? d.act_b.as<uint16_t>() : nullptr);
+        drafter_matmul(l.down, R, d.act.as<float>(), d.co.as<float>(), EPI_RAW, nullptr, nullptr, chain ? d.act_b.as<uint16_t>() : nullptr);
         conv(l, 3, d.co.as<float>(), d.mixed.as<float>(), x);
     }
     // 3. Raw logits (drafter.rs:418-419: through the target's cap a trained drafter's largest would tie), candidates, trees.
     launch_prep_rows(x, nullptr, R, H, md.eps, d.hfin.as<float>(), nullptr, nullptr, true, false, stream);
-    matmul(d.head, R, d.hfin.as<float>(), d.logits.as<float>(), EPI_RAW, nullptr, nullptr);
+    drafter_matmul(d.head, R, d.hfin.as<float>(), d.logits.as<float>(), EPI_RAW, nullptr, nullptr);
     const uint32_t ncand = std::min(4u, rows - 1);
     launch_draft_top(d.logits.as<float>(), R, d.v, d.vocab_ids.as<uint32_t>(), d_tin, 1.0f / 0.6f, ncand, d.cand.as<uint32_t>(), d.cand_q.as<float>(), stream);
     launch_draft_tree(d_blocks, d_slots, nb, d.cand.as<uint32_t>(), d.cand_q.as<float>(), ncand, s.feed.as<uint32_t>(), s.tree.as<uint32_t>(), stream);

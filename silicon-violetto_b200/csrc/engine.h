@@ -248,7 +248,8 @@ class Engine {
         struct DLayer {
             Matrix qkv, o, gate_up, down;
             const float* conv_base[4];
-            Matrix conv_corr[4];
+            Matrix conv_corr[4];       // [192][H] as the file holds them
+            Matrix conv_corr_gemm[4];  // bf16 files: copies padded with zero rows to the GEMM's 128-row tiles (m = 0: none)
         };
         std::vector<DLayer> layers;
         std::vector<uint32_t> taps;
@@ -257,12 +258,21 @@ class Engine {
         Buffer vocab_ids, k_ring, v_ring, ctx_ring;
         Buffer ctx, ctx_inv, kvp;                                                                 // per step token
         Buffer x, last, cx, co, mixed, qkv, inv, attn, act, corr, corr_inv, hfin, logits, cand, cand_q, meta;  // per block row
-        Buffer layout[3];  // per step set: tin [rows][2] | rows_of [rows] | blocks [max_seqs][2] | slots [max_seqs]
+        Buffer conv_pad;        // the padded correction matrices
+        Buffer xb, act_b, attn_b;  // bf16 inputs of the tensor-core GEMM: a row pass's copy of any input, the SwiGLU's and the attention's output
+        Buffer part;               // the attention's partials per (row, head, key split)
+        uint32_t corr_stride = BLOCK_CONV_KC;  // floats per row of `corr`
+        Buffer layout[3];  // per step set: tin [rows][2] | rows_of [rows] | sees [rows] | blocks [max_seqs][2] | slots [max_seqs]
         uint32_t last_rows = 0;  // the last pass's block rows (debug reads)
     };
     std::unique_ptr<BlockDrafter> block_drafter;
     void load_block_drafter(const std::string& path);
     void encode_block_drafter(uint32_t set, const Plan& p, uint32_t rows);
+    // A projection of the block drafter: the tensor-core GEMM where the matrix and the row count fit it (xb: the input's
+    // bf16 copy if something left one, else a row pass makes it -- and 1 / rms for the epilogues that norm), else the
+    // streamed kernel in blocks of 8 rows.
+    void drafter_matmul(const Matrix& w, uint32_t n, const float* x, float* y, uint32_t epi, const float* base, float* inv_out, const uint16_t* xb = nullptr,
+                        uint16_t* yb = nullptr);
 
   private:
     KvArgs kv_args() const;

@@ -107,13 +107,13 @@ __global__ void embed_kernel(const uint16_t* __restrict__ table, const uint32_t*
 
 // kernels.metal:1820-1840 `draft_conv` (tools/spec/drafter.py `Conv2`): out[t] = resid[t] (if any) + k0 x[t] + k1 x[t - 1]
 // within a block, no predecessor for its row 0; the kernels are base [2][H] plus the row's corrections per 16 channels
-// (k0's, then k1's; [rows][192], already times 1 / rms of the row). out must not be x.
-__global__ void conv_kernel(const float* __restrict__ x, const float* __restrict__ corr, const float* __restrict__ base, const uint32_t* __restrict__ tin,
-                            const float* __restrict__ resid, uint32_t hidden, float* out) {
+// (k0's, then k1's; [rows][corr_stride], already times 1 / rms of the row). out must not be x.
+__global__ void conv_kernel(const float* __restrict__ x, const float* __restrict__ corr, uint32_t corr_stride, const float* __restrict__ base,
+                            const uint32_t* __restrict__ tin, const float* __restrict__ resid, uint32_t hidden, float* out) {
     pdl_start();
     const uint32_t t = blockIdx.x;
     const bool prev = tin[2 * t + 1] > 0;
-    const float* c = corr + size_t(t) * BLOCK_CONV_KC;
+    const float* c = corr + size_t(t) * corr_stride;
     for (uint32_t d = threadIdx.x; d < hidden; d += blockDim.x) {
         const size_t at = size_t(t) * hidden + d;
         float y = (base[d] + c[d / 16]) * x[at];
@@ -197,9 +197,9 @@ void launch_block_embed(const uint16_t* table, const uint32_t* tin, const uint32
                         const BlockDrafterDims& b, uint32_t vocab, uint32_t rows, float* x, float* last, uint32_t* meta, cudaStream_t s) {
     launch_pdl(block::embed_kernel, rows, 256, 0, s, table, tin, lens, feed, mask_emb, ctx_ring, b, vocab, x, last, meta);
 }
-void launch_block_conv(const float* x, const float* corr, const float* base, const uint32_t* tin, const float* resid, uint32_t hidden, uint32_t rows, float* out,
-                       cudaStream_t s) {
-    launch_pdl(block::conv_kernel, rows, 256, 0, s, x, corr, base, tin, resid, hidden, out);
+void launch_block_conv(const float* x, const float* corr, uint32_t corr_stride, const float* base, const uint32_t* tin, const float* resid, uint32_t hidden,
+                       uint32_t rows, float* out, cudaStream_t s) {
+    launch_pdl(block::conv_kernel, rows, 256, 0, s, x, corr, corr_stride, base, tin, resid, hidden, out);
 }
 void launch_block_qkv_post(float* qkv, const uint32_t* meta, const float* rope, const BlockDrafterDims& b, uint32_t layer, uint32_t rows, uint16_t* k_ring,
                            uint16_t* v_ring, cudaStream_t s) {

@@ -260,10 +260,13 @@ __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pa
         oo.x += ok.x * wk; oo.y += ok.y * wk; oo.z += ok.z * wk; oo.w += ok.w * wk;
     }
     oo.x /= ll; oo.y /= ll; oo.z /= ll; oo.w /= ll;
-    const float4 vd = *reinterpret_cast<const float4*>(vdir + (size_t(t) * n_kv + g) * D + d0);
-    const float pr = warp_sum(oo.x * vd.x + oo.y * vd.y + oo.z * vd.z + oo.w * vd.w);
-    const float xs = xsa[h] * pr, gt = gates[size_t(t) * n_q + h];
-    const float4 r = make_float4((oo.x - xs * vd.x) * gt, (oo.y - xs * vd.y) * gt, (oo.z - xs * vd.z) * gt, (oo.w - xs * vd.w) * gt);
+    float4 r = oo;
+    if (vdir) {  // (none for the block drafter's layers: no XSA, no gate)
+        const float4 vd = *reinterpret_cast<const float4*>(vdir + (size_t(t) * n_kv + g) * D + d0);
+        const float pr = warp_sum(oo.x * vd.x + oo.y * vd.y + oo.z * vd.z + oo.w * vd.w);
+        const float xs = xsa[h] * pr, gt = gates[size_t(t) * n_q + h];
+        r = make_float4((oo.x - xs * vd.x) * gt, (oo.y - xs * vd.y) * gt, (oo.z - xs * vd.z) * gt, (oo.w - xs * vd.w) * gt);
+    }
     *reinterpret_cast<float4*>(out + (size_t(t) * n_q + h) * D + d0) = r;
     if (out_b) *reinterpret_cast<uint2*>(out_b + (size_t(t) * n_q + h) * D + d0) = make_uint2(pack_bf16(r.x, r.y), pack_bf16(r.z, r.w));  // for a tensor-core o projection
 }
@@ -304,25 +307,29 @@ void launch_limite_qkv_post(float* qkv, const float* x, const float* inv_rms, co
                k_cache, v_cache, vdir, gates, ssq, ssq_tiles, ssq_stride);
 }
 // max_keys: the most keys a row of the step may see on this layer (its tile's eight slots included); part: room for
-// n * n_q * LIMITE_MAX_SPLITS partials of 132 floats. Heads per kv head other than 1, 2 and 5 (the reference's) take the
-// one-block-per-(token, head) kernel.
-void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
-                        const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
+// n * n_q * LIMITE_MAX_SPLITS partials of 132 floats (or as many splits as max_keys / 64 can make); tiles: the step's
+// (first row, rows <= 8) pairs. More than 8 query heads per kv head take the one-block-per-(token, head) kernel.
+void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint32_t* tiles, uint32_t n_tiles,
+                        const uint16_t* k_cache, const uint16_t* v_cache, const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
                         uint32_t max_keys, float* part, float* out, uint16_t* out_b, uint32_t keys_per_block, cudaStream_t s) {
     const uint32_t G = n_q / kv.n_kv;
     if (G > 8) {
-        if (out_b) throw Error("internal: the one-block attention leaves no bf16 copy");
+        if (out_b || !vdir) throw Error("internal: the one-block attention leaves no bf16 copy and wants XSA directions and gates");
         launch_pdl(limite::attn_kernel, dim3(n, n_q), 128, 0, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, vdir, gates, xsa, out);
         return;
     }
-    // Enough blocks to fill the GPU twice over (three blocks of four warps an SM), of whole rounds of 64 keys (a tile of 16
-    // per warp), at most LIMITE_MAX_SPLITS.
-    const uint32_t want = (6 * 148 + n * kv.n_kv - 1) / std::max(n * kv.n_kv, 1u);  // (a B200's 148 SMs)
-    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, want}));
+    // A step whose tiles hold two rows or more on average (draft trees under verification, the block drafter's blocks)
+    // takes the kernel that reads a tile's keys once for all its rows; plain decoding the one that splits a row's keys
+    // over four warps. Enough blocks to fill the GPU twice over (three blocks of four warps, or one of eight, an SM), of
+    // whole rounds of 64 keys, at most LIMITE_MAX_SPLITS.
+    const bool by_tile = tiles && n_tiles && n >= 2 * n_tiles;
+    const uint32_t units = std::max((by_tile ? n_tiles : n) * kv.n_kv, 1u), fill = (by_tile ? 2 : 6) * 148;  // (a B200's 148 SMs)
+    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, (fill + units - 1) / units}));
     if (keys_per_block) splits = std::max(1u, std::min(LIMITE_MAX_SPLITS, (max_keys + keys_per_block - 1) / keys_per_block));  // (a tuning override)
     const uint32_t kps = ((max_keys + splits - 1) / splits + 63) / 64 * 64;
     splits = (max_keys + kps - 1) / kps;
-    launch_limite_attn_mma(qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, n, kps, splits, part, s);
+    if (by_tile) launch_limite_attn_rows(qkv, meta, tin, vis, tiles, k_cache, v_cache, kv, n_q, window, scale, n_tiles, kps, splits, part, s);
+    else launch_limite_attn_mma(qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale, n, kps, splits, part, s);
     launch_pdl(limite::merge_kernel, dim3(n, n_q), 128, 0, s, part, splits, n_q, kv.n_kv, vdir, gates, xsa, out, out_b);
 }
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,

@@ -149,8 +149,8 @@ void launch_block_context(const float* kvp, const float* ctx, const float* ctx_i
                           const BlockDrafterDims& b, uint32_t n, uint16_t* k_ring, uint16_t* v_ring, float* ctx_ring, cudaStream_t s);
 void launch_block_embed(const uint16_t* table, const uint32_t* tin, const uint32_t* lens, const uint32_t* feed, const float* mask_emb, const float* ctx_ring,
                         const BlockDrafterDims& b, uint32_t vocab, uint32_t rows, float* x, float* last, uint32_t* meta, cudaStream_t s);
-void launch_block_conv(const float* x, const float* corr, const float* base, const uint32_t* tin, const float* resid, uint32_t hidden, uint32_t rows, float* out,
-                       cudaStream_t s);
+void launch_block_conv(const float* x, const float* corr, uint32_t corr_stride, const float* base, const uint32_t* tin, const float* resid, uint32_t hidden,
+                       uint32_t rows, float* out, cudaStream_t s);
 void launch_block_qkv_post(float* qkv, const uint32_t* meta, const float* rope, const BlockDrafterDims& b, uint32_t layer, uint32_t rows, uint16_t* k_ring,
                            uint16_t* v_ring, cudaStream_t s);
 void launch_block_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* rows_of, const uint16_t* k_ring, const uint16_t* v_ring,
@@ -174,7 +174,10 @@ constexpr uint32_t LIMITE_MAX_SPLITS = 128, LIMITE_PART = 132;  // key splits a 
 void launch_limite_attn_mma(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
                             const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, uint32_t n, uint32_t keys_per_split, uint32_t splits, float* part,
                             cudaStream_t s);
-void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
+void launch_limite_attn_rows(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint32_t* tiles, const uint16_t* k_cache,
+                             const uint16_t* v_cache, const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, uint32_t n_tiles, uint32_t keys_per_split,
+                             uint32_t splits, float* part, cudaStream_t s);
+void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint32_t* tiles, uint32_t n_tiles, const uint16_t* k_cache, const uint16_t* v_cache,
                         const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
                         uint32_t max_keys, float* part, float* out, uint16_t* out_b, uint32_t keys_per_block, cudaStream_t s);  // out_b: optional bf16 copy (heads per kv head 1, 2 or 5)
 void launch_limite_compact(const RunIn* runs, const uint32_t* path, const uint32_t* path_len, const uint32_t* lens, uint16_t* k_local, uint16_t* v_local,
