@@ -322,7 +322,7 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
     // takes the kernel that reads a tile's keys once for all its rows; plain decoding the one that splits a row's keys
     // over four warps. Enough blocks to fill the GPU twice over (three blocks of four warps, or one of eight, an SM), of
     // whole rounds of 64 keys, at most LIMITE_MAX_SPLITS.
-    const bool by_tile = tiles && n_tiles && n >= 2 * n_tiles;
+    const bool by_tile = tiles && n_tiles && n >= 2 * n_tiles && G <= 6;  // (8 rows x G heads in its 48 columns)
     const uint32_t units = std::max((by_tile ? n_tiles : n) * kv.n_kv, 1u), fill = (by_tile ? 2 : 6) * 148;  // (a B200's 148 SMs)
     uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, (fill + units - 1) / units}));
     if (keys_per_block) splits = std::max(1u, std::min(LIMITE_MAX_SPLITS, (max_keys + keys_per_block - 1) / keys_per_block));  // (a tuning override)

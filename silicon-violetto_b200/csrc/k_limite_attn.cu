@@ -242,15 +242,21 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
     }
 }
 
-// A tile of up to eight rows of one run per block -- a verified draft tree, whose rows share their cached keys: grid
-// (tiles, kv heads, key splits), eight warps, warp w the tile's row w. The block walks the union of its rows' keys (from
-// the smallest window start; then the tile's eight slots) in tiles of 16 that all 256 threads copy into a ring of stages
-// once, and every warp multiplies each tile with its own row under that row's window start and `vis` mask, so the cache
-// is read once per tile of rows and not once per row. No meeting of warps at the end: a warp holds its row's whole
-// partial for the split.
-constexpr uint32_t ROW_WARPS = 8, ROW_STAGES = 4;
+// A tile of up to eight rows of one run per block -- a verified draft tree or a drafter's block, whose rows share their
+// cached keys: grid (tiles, kv heads, key splits), eight warps. The tile's rows x the kv head's G query heads are packed
+// into the MMAs' query dimension (column p = G i + h is row i, head h: kernels.metal:896), at most 48 columns: warp
+// (half, kw) takes columns 24 half .. 24 half + 23 (three n-tiles) of key tiles kw, kw + 4, ... . The block walks the
+// union of its rows' keys (from the smallest window start; then the tile's eight slots) in stages of 64 keys that all
+// 256 threads copy into a ring once, so the cache is read once per tile of rows and a K or V fragment feeds three MMAs;
+// Q^T (high parts and remainders) lies in shared memory and comes to the MMAs through ldmatrix. A column's row decides
+// what it sees: its own window start and `vis` mask. The four key-interleaved warps of a half meet in shared memory at the end.
+constexpr uint32_t ROW_WARPS = 8, ROW_STAGES = 3, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = 4 * TILE;
+constexpr uint32_t ROW_STAGE_BYTES = 4 * 2 * TILE_BYTES;  // four tiles, K then V each
+constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // one of the two Q^T copies (high parts; remainders); eight rows of padding, which the
+                                                          // second half's last ldmatrix.x4 reads beside its third n-tile and nobody uses
 constexpr uint32_t ROW_OS = D + 4;
-constexpr uint32_t ROW_SMEM = ROW_STAGES * 2 * TILE_BYTES > ROW_WARPS * 8 * ROW_OS * 4 ? ROW_STAGES * 2 * TILE_BYTES : ROW_WARPS * 8 * ROW_OS * 4;
+constexpr uint32_t ROW_SMEM = ROW_STAGES * ROW_STAGE_BYTES + 2 * ROW_Q_BYTES;
+static_assert(ROW_WARPS * 8 * ROW_NT * ROW_OS * 4 <= ROW_SMEM, "the merge buffers must fit in the ring and the Q^T copies");
 
 __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
     attn_mma_rows_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ vis,
@@ -259,83 +265,245 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
     pdl_start();
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t tile = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z, warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, tq = lane & 3;
+    const uint32_t half = warp & 1, kw = warp >> 1;
     const uint32_t G = n_q / kv.n_kv;
-    const uint32_t t0 = tiles[2 * tile], T = tiles[2 * tile + 1];
-    const bool has_row = warp < T;
-    const uint32_t t = t0 + (has_row ? warp : 0);  // (a warp without a row walks along with row 0's numbers and writes nothing)
+    const uint32_t t0 = tiles[2 * tile], T = tiles[2 * tile + 1], n_cols = T * G;
     const uint32_t slot = meta[2 * t0], row0 = tin[2 * t0 + 1];
     const uint32_t p0 = meta[2 * t0 + 1], p_run = meta[2 * (t0 - row0) + 1] + row0;  // the tile's first position; its first row's place in the cache
-    const uint32_t pos = meta[2 * t + 1], mask = has_row ? vis[t] : 0u;
     auto lo_of = [&](uint32_t p) { return kv.is_global ? 0u : (p > window ? p - window : 0u); };  // kernels.metal:809 `key_lo`
-    const uint32_t lo = lo_of(pos);
-    uint32_t lo_min = lo_of(p0);
-    for (uint32_t i = 1; i < T; i++) lo_min = min(lo_min, lo_of(meta[2 * (t0 + i) + 1]));
+    uint32_t lo_min = lo_of(p0), lo_max = lo_min;
+    for (uint32_t i = 1; i < T; i++) {
+        const uint32_t l = lo_of(meta[2 * (t0 + i) + 1]);
+        lo_min = min(lo_min, l);
+        lo_max = max(lo_max, l);
+    }
     const uint32_t n_old = p0 > lo_min ? p0 - lo_min : 0, total = n_old + 8;
     const uint32_t begin = sp * keys_per_split, end = min(begin + keys_per_split, total);
-    const uint32_t n_tiles = end > begin ? (end - begin + TILE - 1) / TILE : 0;
-    // Key i of the block's walk: cached position lo_min + i below n_old, then the tile's slot i - n_old.
-    auto in_walk = [&](uint32_t i) { return i < end; };
-    auto seen = [&](uint32_t i) { return has_row && i < end && (i < n_old ? lo_min + i >= lo : ((mask >> (i - n_old)) & 1u) != 0); };
+    const uint32_t n_stages = end > begin ? (end - begin + ROW_KEYS - 1) / ROW_KEYS : 0;
 
-    RowState r;
-    row_init(r, qkv + size_t(t) * (n_q + 2 * kv.n_kv) * D + size_t(kvh * G + min(g, G - 1)) * D, has_row && g < G, scale_log2, tq);
+    // Q^T into shared memory as [column][128 dims] bf16, twice (high parts, remainders), 16-byte chunks swizzled by the row.
+    const uint32_t ring = smem_u32(smem), q_hi = ring + ROW_STAGES * ROW_STAGE_BYTES, q_lo = q_hi + ROW_Q_BYTES;
+    for (uint32_t c = threadIdx.x; c < ROW_COLS * 16; c += ROW_WARPS * 32) {
+        const uint32_t pcol = c / 16, chunk = c % 16;
+        uint4 hi = make_uint4(0, 0, 0, 0), lo4 = hi;
+        if (pcol < n_cols) {
+            const float* qp = qkv + size_t(t0 + pcol / G) * (n_q + 2 * kv.n_kv) * D + size_t(kvh * G + pcol % G) * D + chunk * 8;
+            const float4 a = *reinterpret_cast<const float4*>(qp), bq = *reinterpret_cast<const float4*>(qp + 4);
+            const float v[8] = {a.x * scale_log2, a.y * scale_log2, a.z * scale_log2, a.w * scale_log2, bq.x * scale_log2, bq.y * scale_log2, bq.z * scale_log2, bq.w * scale_log2};
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                h[e] = pack_bf16(v[2 * e], v[2 * e + 1]);
+                l[e] = pack_bf16(v[2 * e] - bf16lo(h[e]), v[2 * e + 1] - bf16hi(h[e]));
+            }
+            hi = make_uint4(h[0], h[1], h[2], h[3]);
+            lo4 = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+        const uint32_t off = pcol * 256 + ((chunk ^ (pcol & 7)) << 4);
+        *reinterpret_cast<uint4*>(smem + ROW_STAGES * ROW_STAGE_BYTES + off) = hi;
+        *reinterpret_cast<uint4*>(smem + ROW_STAGES * ROW_STAGE_BYTES + ROW_Q_BYTES + off) = lo4;
+    }
 
-    const uint32_t ring = smem_u32(smem);
-    // Tile i into stage i % ROW_STAGES: thread j copies chunk j % 16 of key j / 16, K and V (a key past the split reads
-    // the tile's first row's own key: a valid address, masked for every row).
+    // This lane's columns: 24 half + 8 j + 2 tq (+ 1) of n-tile j; the window start and the mask of each one's row.
+    uint32_t c_lo[ROW_NT][2], c_mask[ROW_NT][2];
+#pragma unroll
+    for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const uint32_t pcol = 24 * half + 8 * j + 2 * tq + e;
+            const bool real = pcol < n_cols;
+            const uint32_t t = t0 + (real ? pcol / G : 0);
+            c_lo[j][e] = real ? lo_of(meta[2 * t + 1]) : 0xffffffffu;  // (a column that is none sees nothing)
+            c_mask[j][e] = real ? vis[t] : 0u;
+        }
+
+    // Stage i: keys begin + 64 i ..; thread j copies chunk j % 16 of keys j / 16 + 16 u, K and V (a key past the split, or a
+    // slot past the tile's rows, which has no place in the cache, reads the tile's first row's own key: a valid address
+    // that no column sees).
     auto issue = [&](uint32_t i) {
-        const uint32_t key = threadIdx.x >> 4, chunk = threadIdx.x & 15, idx = begin + i * TILE + key;
-        // (a slot past the tile's rows has no place in the cache: it reads the first row's, and no row's mask names it)
-        const uint32_t kp = !in_walk(idx) ? p_run : idx < n_old ? lo_min + idx : p_run + (idx - n_old < T ? idx - n_old : 0u);
-        const size_t src = size_t(kv_row_index(kv, slot, kvh, kp)) * D + chunk * 8;
-        const uint32_t at = ring + (i % ROW_STAGES) * 2 * TILE_BYTES + key * 256 + ((chunk ^ (key & 7)) << 4);
-        cp_async16(at, k_cache + src);
-        cp_async16(at + TILE_BYTES, v_cache + src);
+        const uint32_t chunk = threadIdx.x & 15;
+#pragma unroll
+        for (uint32_t u = 0; u < 4; u++) {
+            const uint32_t key = (threadIdx.x >> 4) + 16 * u, idx = begin + i * ROW_KEYS + key;
+            const uint32_t kp = idx >= end ? p_run : idx < n_old ? lo_min + idx : p_run + (idx - n_old < T ? idx - n_old : 0u);
+            const size_t src = size_t(kv_row_index(kv, slot, kvh, kp)) * D + chunk * 8;
+            const uint32_t at = ring + (i % ROW_STAGES) * ROW_STAGE_BYTES + (key >> 4) * 2 * TILE_BYTES + (key & 15) * 256 + ((chunk ^ (key & 7)) << 4);
+            cp_async16(at, k_cache + src);
+            cp_async16(at + TILE_BYTES, v_cache + src);
+        }
     };
     // One group per iteration, empty ones included: at iteration i all but the newest ROW_STAGES - 2 groups are complete,
-    // which is tile i; the barrier that follows also says that every warp is done with tile i - 1, whose stage the new
-    // copy takes.
+    // which is stage i; the barrier that follows also says that every warp is done with stage i - 1, which the new copy takes.
 #pragma unroll
     for (uint32_t i = 0; i + 1 < ROW_STAGES; i++) {
-        if (i < n_tiles) issue(i);
+        if (i < n_stages) issue(i);
         cp_async_commit();
     }
-    for (uint32_t i = 0; i < n_tiles; i++) {
+
+    const uint32_t lm = lane >> 3, lr = lane & 7;
+    const uint32_t k_row = (8 * (lm & 1) + lr) * 256, k_c = lm >> 1, v_row = (8 * (lm >> 1) + lr) * 256, v_c = lm & 1;
+    // Q^T as B: one ldmatrix.x4 brings b0, b1 of n-tile jq and of jq + 1: matrix lm -> column 24 half + 8 (jq + (lm >> 1)) + lr,
+    // chunk 2 ks + (lm & 1).
+    const uint32_t q_row = (24 * half + 8 * (lm >> 1) + lr) * 256, q_c = lm & 1;
+
+    float oacc[8][ROW_NT][4];
+    float m_run[ROW_NT][2], l_run[ROW_NT][2];
+#pragma unroll
+    for (int j = 0; j < int(ROW_NT); j++) {
+#pragma unroll
+        for (int dm = 0; dm < 8; dm++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) oacc[dm][j][e] = 0.0f;
+        m_run[j][0] = m_run[j][1] = -INFINITY;
+        l_run[j][0] = l_run[j][1] = 0.0f;
+    }
+
+    for (uint32_t i = 0; i < n_stages; i++) {
         cp_async_wait<ROW_STAGES - 2>();
-        __syncthreads();
-        if (i + ROW_STAGES - 1 < n_tiles) issue(i + ROW_STAGES - 1);
+        __syncthreads();  // (the first one also covers the Q^T stores)
+        if (i + ROW_STAGES - 1 < n_stages) issue(i + ROW_STAGES - 1);
         cp_async_commit();
-        if (!has_row) continue;
-        const uint32_t kbase = ring + (i % ROW_STAGES) * 2 * TILE_BYTES, i0 = begin + i * TILE;
-        row_tile(r, kbase, kbase + TILE_BYTES, seen(i0 + g), seen(i0 + g + 8), lane);
+        const uint32_t i0 = begin + i * ROW_KEYS + kw * TILE;  // this warp's tile of the stage
+        if (i0 >= end) continue;
+        const uint32_t kbase = ring + (i % ROW_STAGES) * ROW_STAGE_BYTES + kw * 2 * TILE_BYTES, vbase = kbase + TILE_BYTES;
+
+        float sacc[ROW_NT][4];
+#pragma unroll
+        for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) sacc[j][e] = 0.0f;
+#pragma unroll
+        for (uint32_t ks = 0; ks < 8; ks++) {
+            uint32_t ka[4], qa[4], qb[4], ra[4], rb[4];
+            ldmatrix_x4(ka, kbase + k_row + (((2 * ks + k_c) ^ lr) << 4));
+            const uint32_t qoff = q_row + (((2 * ks + q_c) ^ lr) << 4);
+            ldmatrix_x4(qa, q_hi + qoff);             // n-tiles 0 and 1, high parts
+            ldmatrix_x4(qb, q_hi + qoff + 16 * 256);  // n-tile 2 (and the rows after it: unused)
+            ldmatrix_x4(ra, q_lo + qoff);
+            ldmatrix_x4(rb, q_lo + qoff + 16 * 256);
+            mma16816(sacc[0], ka, qa[0], qa[1]);
+            mma16816(sacc[1], ka, qa[2], qa[3]);
+            mma16816(sacc[2], ka, qb[0], qb[1]);
+            mma16816(sacc[0], ka, ra[0], ra[1]);
+            mma16816(sacc[1], ka, ra[2], ra[3]);
+            mma16816(sacc[2], ka, rb[0], rb[1]);
+        }
+        // Who sees what: nothing to do for a tile of cached keys inside every row's window.
+        if (i0 + TILE > n_old || i0 + TILE > end || lo_min + i0 < lo_max) {
+#pragma unroll
+            for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t idx = i0 + g + 8 * (e >> 1);
+                    const bool seen = idx < end && (idx < n_old ? lo_min + idx >= c_lo[j][e & 1] : ((c_mask[j][e & 1] >> (idx - n_old)) & 1u) != 0);
+                    if (!seen) sacc[j][e] = -INFINITY;
+                }
+        } else {
+#pragma unroll
+            for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (c_lo[j][e & 1] == 0xffffffffu) sacc[j][e] = -INFINITY;  // (no such column)
+        }
+        bool over = false;
+#pragma unroll
+        for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) over = over || fmaxf(sacc[j][e], sacc[j][e + 2]) > m_run[j][e] + 8.0f;
+        if (__any_sync(0xffffffffu, over)) {
+#pragma unroll
+            for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    float mx = fmaxf(sacc[j][e], sacc[j][e + 2]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    const float m_new = fmaxf(m_run[j][e], mx);
+                    const float corr = fast_exp2(m_run[j][e] - (m_new == -INFINITY ? 0.0f : m_new));
+                    m_run[j][e] = m_new;
+                    l_run[j][e] *= corr;
+#pragma unroll
+                    for (int dm = 0; dm < 8; dm++) {
+                        oacc[dm][j][e] *= corr;
+                        oacc[dm][j][e + 2] *= corr;
+                    }
+                }
+        }
+        uint32_t pbh[ROW_NT][2], pbl[ROW_NT][2];
+#pragma unroll
+        for (int j = 0; j < int(ROW_NT); j++) {
+            const float m0 = m_run[j][0] == -INFINITY ? 0.0f : m_run[j][0], m1 = m_run[j][1] == -INFINITY ? 0.0f : m_run[j][1];
+            const float p0a = fast_exp2(sacc[j][0] - m0), p0b = fast_exp2(sacc[j][1] - m1);  // key g
+            const float p1a = fast_exp2(sacc[j][2] - m0), p1b = fast_exp2(sacc[j][3] - m1);  // key g + 8
+            l_run[j][0] += p0a + p1a;
+            l_run[j][1] += p0b + p1b;
+            const uint32_t h0 = pack_bf16(p0a, p0b), h1 = pack_bf16(p1a, p1b);
+            pbh[j][0] = movmatrix_trans(h0);
+            pbh[j][1] = movmatrix_trans(h1);
+            pbl[j][0] = movmatrix_trans(pack_bf16(p0a - bf16lo(h0), p0b - bf16hi(h0)));
+            pbl[j][1] = movmatrix_trans(pack_bf16(p1a - bf16lo(h1), p1b - bf16hi(h1)));
+        }
+#pragma unroll
+        for (uint32_t dm = 0; dm < 8; dm++) {
+            uint32_t va[4];
+            ldmatrix_x4_trans(va, vbase + v_row + (((2 * dm + v_c) ^ lr) << 4));
+#pragma unroll
+            for (int j = 0; j < int(ROW_NT); j++) {
+                mma16816(oacc[dm][j], va, pbh[j][0], pbh[j][1]);
+                mma16816(oacc[dm][j], va, pbl[j][0], pbl[j][1]);
+            }
+        }
     }
     cp_async_wait<0>();
-    row_finish(r);
-    __syncthreads();  // the ring is free: each warp lays its row's partial out in it, then writes it in whole rows
-    if (!has_row) return;
-    float* os = reinterpret_cast<float*>(smem) + warp * 8 * ROW_OS;  // [column][ROW_OS]: o[128], then m and l
 #pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const uint32_t col = 2 * tq + e;
-        if (col >= G) continue;
-        float* o = os + col * ROW_OS;
-        if (g == 0) {
-            o[D] = r.m_run[e];
-            o[D + 1] = r.l_run[e];
-        }
+    for (int j = 0; j < int(ROW_NT); j++)
 #pragma unroll
-        for (int dm = 0; dm < 8; dm++) {
-            o[16 * dm + g] = r.oacc[dm][e];
-            o[16 * dm + g + 8] = r.oacc[dm][e + 2];
+        for (int e = 0; e < 2; e++) {
+            l_run[j][e] += __shfl_xor_sync(0xffffffffu, l_run[j][e], 4);
+            l_run[j][e] += __shfl_xor_sync(0xffffffffu, l_run[j][e], 8);
+            l_run[j][e] += __shfl_xor_sync(0xffffffffu, l_run[j][e], 16);
         }
-    }
-    __syncwarp();
+    __syncthreads();  // the ring and the Q^T copies are free: every warp lays its columns' partials out in them
+    float* os = reinterpret_cast<float*>(smem);  // [warp][24 columns][ROW_OS]: o[128], then m and l
+#pragma unroll
+    for (int j = 0; j < int(ROW_NT); j++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const uint32_t lc = 8 * j + 2 * tq + e;
+            if (24 * half + lc >= n_cols) continue;
+            float* o = os + (warp * 24 + lc) * ROW_OS;
+            if (g == 0) {
+                o[D] = m_run[j][e];
+                o[D + 1] = l_run[j][e];
+            }
+#pragma unroll
+            for (int dm = 0; dm < 8; dm++) {
+                o[16 * dm + g] = oacc[dm][j][e];
+                o[16 * dm + g + 8] = oacc[dm][j][e + 2];
+            }
+        }
+    __syncthreads();
+    // The four key-interleaved warps of a half added up per column: warp w takes columns w, w + 8, ... of the tile.
     const uint32_t d0 = 4 * lane;
-    for (uint32_t h = 0; h < G; h++) {
-        const float* o = os + h * ROW_OS;
-        float* pp = part + ((size_t(t) * n_q + kvh * G + h) * max_splits + sp) * PART;
-        if (lane == 0) { pp[0] = o[D] * LN2; pp[1] = o[D + 1]; }  // (-inf stays -inf: nothing seen in this split)
-        *reinterpret_cast<float4*>(pp + 4 + d0) = *reinterpret_cast<const float4*>(o + d0);
+    for (uint32_t pcol = warp; pcol < n_cols; pcol += ROW_WARPS) {
+        const uint32_t hf = pcol / 24, lc = pcol % 24;
+        float mm = -INFINITY;
+#pragma unroll
+        for (uint32_t k = 0; k < 4; k++) mm = fmaxf(mm, os[((2 * k + hf) * 24 + lc) * ROW_OS + D]);
+        float ll = 0.0f;
+        float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (uint32_t k = 0; k < 4; k++) {
+            const float* o = os + ((2 * k + hf) * 24 + lc) * ROW_OS;
+            const float mk = o[D], wk = mk == -INFINITY ? 0.0f : fast_exp2(mk - mm);
+            const float4 ok = *reinterpret_cast<const float4*>(o + d0);
+            ll += o[D + 1] * wk;
+            oo.x += ok.x * wk; oo.y += ok.y * wk; oo.z += ok.z * wk; oo.w += ok.w * wk;
+        }
+        float* pp = part + ((size_t(t0 + pcol / G) * n_q + kvh * G + pcol % G) * max_splits + sp) * PART;
+        if (lane == 0) { pp[0] = mm * LN2; pp[1] = ll; }  // (-inf stays -inf: nothing seen in this split)
+        *reinterpret_cast<float4*>(pp + 4 + d0) = oo;
     }
 }
 
