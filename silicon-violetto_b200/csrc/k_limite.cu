@@ -320,11 +320,25 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
     }
     // A step whose tiles hold two rows or more on average (draft trees under verification, the block drafter's blocks)
     // takes the kernel that reads a tile's keys once for all its rows; plain decoding the one that splits a row's keys
-    // over four warps. Enough blocks to fill the GPU twice over (three blocks of four warps, or one of eight, an SM), of
-    // whole rounds of 64 keys, at most LIMITE_MAX_SPLITS.
+    // over four warps.
     const bool by_tile = tiles && n_tiles && n >= 2 * n_tiles && G <= 6;  // (8 rows x G heads in its 48 columns)
-    const uint32_t units = std::max((by_tile ? n_tiles : n) * kv.n_kv, 1u), fill = (by_tile ? 2 : 6) * 148;  // (a B200's 148 SMs)
-    uint32_t splits = std::max(1u, std::min({LIMITE_MAX_SPLITS, (max_keys + 63) / 64, (fill + units - 1) / units}));
+    // Key splits, in whole rounds of 64 keys, at most LIMITE_MAX_SPLITS. The one-row kernel (three blocks an SM, which
+    // need not run in step): enough blocks to fill a B200's 148 SMs twice over. The rows' kernel (one block an SM): the count
+    // that makes waves of blocks times a block's keys, plus a fixed part of about 128 keys' worth, least.
+    const uint32_t most = std::max(1u, std::min(LIMITE_MAX_SPLITS, (max_keys + 63) / 64));
+    uint32_t splits = 1;
+    if (by_tile) {
+        const uint32_t units = std::max(n_tiles * kv.n_kv, 1u), slots = 148;
+        uint64_t best = ~0ull;
+        for (uint32_t c = 1; c <= most; c++) {
+            const uint32_t k = ((max_keys + c - 1) / c + 63) / 64 * 64, real = (max_keys + k - 1) / k;
+            const uint64_t cost = uint64_t((units * real + slots - 1) / slots) * (k + 128);
+            if (cost < best) { best = cost; splits = real; }
+        }
+    } else {
+        const uint32_t units = std::max(n * kv.n_kv, 1u);
+        splits = std::max(1u, std::min(most, (6 * 148 + units - 1) / units));
+    }
     if (keys_per_block) splits = std::max(1u, std::min(LIMITE_MAX_SPLITS, (max_keys + keys_per_block - 1) / keys_per_block));  // (a tuning override)
     const uint32_t kps = ((max_keys + splits - 1) / splits + 63) / 64 * 64;
     splits = (max_keys + kps - 1) / kps;

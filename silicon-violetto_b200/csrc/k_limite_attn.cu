@@ -248,15 +248,17 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
 // (half, kw) takes columns 24 half .. 24 half + 23 (three n-tiles) of key tiles kw, kw + 4, ... . The block walks the
 // union of its rows' keys (from the smallest window start; then the tile's eight slots) in stages of 64 keys that all
 // 256 threads copy into a ring once, so the cache is read once per tile of rows and a K or V fragment feeds three MMAs;
-// Q^T (high parts and remainders) lies in shared memory and comes to the MMAs through ldmatrix. A column's row decides
+// Q^T lies in shared memory and comes to the MMAs through ldmatrix. q and p go in as plain bf16 here, as in the plain
+// decoder's kernel: with the remainders as well (the one-row kernel's way) the 8 x G columns make this kernel bound by
+// mma.sync's rate, 56 us of it for a global layer of 32 streams at 8k against 41 us of memory time. A column's row decides
 // what it sees: its own window start and `vis` mask. The four key-interleaved warps of a half meet in shared memory at the end.
 constexpr uint32_t ROW_WARPS = 8, ROW_STAGES = 3, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = 4 * TILE;
 constexpr uint32_t ROW_STAGE_BYTES = 4 * 2 * TILE_BYTES;  // four tiles, K then V each
-constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // one of the two Q^T copies (high parts; remainders); eight rows of padding, which the
-                                                          // second half's last ldmatrix.x4 reads beside its third n-tile and nobody uses
+constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // Q^T; eight rows of padding, which the second half's last ldmatrix.x4 reads beside its
+                                                          // third n-tile and nobody uses
 constexpr uint32_t ROW_OS = D + 4;
-constexpr uint32_t ROW_SMEM = ROW_STAGES * ROW_STAGE_BYTES + 2 * ROW_Q_BYTES;
-static_assert(ROW_WARPS * 8 * ROW_NT * ROW_OS * 4 <= ROW_SMEM, "the merge buffers must fit in the ring and the Q^T copies");
+constexpr uint32_t ROW_SMEM = ROW_STAGES * ROW_STAGE_BYTES + ROW_Q_BYTES;
+static_assert(ROW_WARPS * 8 * ROW_NT * ROW_OS * 4 <= ROW_SMEM, "the merge buffers must fit in the ring and the Q^T rows");
 
 __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
     attn_mma_rows_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ vis,
@@ -281,27 +283,19 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
     const uint32_t begin = sp * keys_per_split, end = min(begin + keys_per_split, total);
     const uint32_t n_stages = end > begin ? (end - begin + ROW_KEYS - 1) / ROW_KEYS : 0;
 
-    // Q^T into shared memory as [column][128 dims] bf16, twice (high parts, remainders), 16-byte chunks swizzled by the row.
-    const uint32_t ring = smem_u32(smem), q_hi = ring + ROW_STAGES * ROW_STAGE_BYTES, q_lo = q_hi + ROW_Q_BYTES;
+    // Q^T into shared memory as [column][128 dims] bf16, 16-byte chunks swizzled by the row.
+    const uint32_t ring = smem_u32(smem), q_hi = ring + ROW_STAGES * ROW_STAGE_BYTES;
     for (uint32_t c = threadIdx.x; c < ROW_COLS * 16; c += ROW_WARPS * 32) {
         const uint32_t pcol = c / 16, chunk = c % 16;
-        uint4 hi = make_uint4(0, 0, 0, 0), lo4 = hi;
+        uint4 hi = make_uint4(0, 0, 0, 0);
         if (pcol < n_cols) {
             const float* qp = qkv + size_t(t0 + pcol / G) * (n_q + 2 * kv.n_kv) * D + size_t(kvh * G + pcol % G) * D + chunk * 8;
             const float4 a = *reinterpret_cast<const float4*>(qp), bq = *reinterpret_cast<const float4*>(qp + 4);
             const float v[8] = {a.x * scale_log2, a.y * scale_log2, a.z * scale_log2, a.w * scale_log2, bq.x * scale_log2, bq.y * scale_log2, bq.z * scale_log2, bq.w * scale_log2};
-            uint32_t h[4], l[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                h[e] = pack_bf16(v[2 * e], v[2 * e + 1]);
-                l[e] = pack_bf16(v[2 * e] - bf16lo(h[e]), v[2 * e + 1] - bf16hi(h[e]));
-            }
-            hi = make_uint4(h[0], h[1], h[2], h[3]);
-            lo4 = make_uint4(l[0], l[1], l[2], l[3]);
+            hi = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
         }
         const uint32_t off = pcol * 256 + ((chunk ^ (pcol & 7)) << 4);
         *reinterpret_cast<uint4*>(smem + ROW_STAGES * ROW_STAGE_BYTES + off) = hi;
-        *reinterpret_cast<uint4*>(smem + ROW_STAGES * ROW_STAGE_BYTES + ROW_Q_BYTES + off) = lo4;
     }
 
     // This lane's columns: 24 half + 8 j + 2 tq (+ 1) of n-tile j; the window start and the mask of each one's row.
@@ -374,19 +368,14 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
             for (int e = 0; e < 4; e++) sacc[j][e] = 0.0f;
 #pragma unroll
         for (uint32_t ks = 0; ks < 8; ks++) {
-            uint32_t ka[4], qa[4], qb[4], ra[4], rb[4];
+            uint32_t ka[4], qa[4], qb[4];
             ldmatrix_x4(ka, kbase + k_row + (((2 * ks + k_c) ^ lr) << 4));
             const uint32_t qoff = q_row + (((2 * ks + q_c) ^ lr) << 4);
-            ldmatrix_x4(qa, q_hi + qoff);             // n-tiles 0 and 1, high parts
+            ldmatrix_x4(qa, q_hi + qoff);             // n-tiles 0 and 1
             ldmatrix_x4(qb, q_hi + qoff + 16 * 256);  // n-tile 2 (and the rows after it: unused)
-            ldmatrix_x4(ra, q_lo + qoff);
-            ldmatrix_x4(rb, q_lo + qoff + 16 * 256);
             mma16816(sacc[0], ka, qa[0], qa[1]);
             mma16816(sacc[1], ka, qa[2], qa[3]);
             mma16816(sacc[2], ka, qb[0], qb[1]);
-            mma16816(sacc[0], ka, ra[0], ra[1]);
-            mma16816(sacc[1], ka, ra[2], ra[3]);
-            mma16816(sacc[2], ka, rb[0], rb[1]);
         }
         // Who sees what: nothing to do for a tile of cached keys inside every row's window.
         if (i0 + TILE > n_old || i0 + TILE > end || lo_min + i0 < lo_max) {
@@ -430,7 +419,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
                     }
                 }
         }
-        uint32_t pbh[ROW_NT][2], pbl[ROW_NT][2];
+        uint32_t pbh[ROW_NT][2];
 #pragma unroll
         for (int j = 0; j < int(ROW_NT); j++) {
             const float m0 = m_run[j][0] == -INFINITY ? 0.0f : m_run[j][0], m1 = m_run[j][1] == -INFINITY ? 0.0f : m_run[j][1];
@@ -438,21 +427,15 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
             const float p1a = fast_exp2(sacc[j][2] - m0), p1b = fast_exp2(sacc[j][3] - m1);  // key g + 8
             l_run[j][0] += p0a + p1a;
             l_run[j][1] += p0b + p1b;
-            const uint32_t h0 = pack_bf16(p0a, p0b), h1 = pack_bf16(p1a, p1b);
-            pbh[j][0] = movmatrix_trans(h0);
-            pbh[j][1] = movmatrix_trans(h1);
-            pbl[j][0] = movmatrix_trans(pack_bf16(p0a - bf16lo(h0), p0b - bf16hi(h0)));
-            pbl[j][1] = movmatrix_trans(pack_bf16(p1a - bf16lo(h1), p1b - bf16hi(h1)));
+            pbh[j][0] = movmatrix_trans(pack_bf16(p0a, p0b));
+            pbh[j][1] = movmatrix_trans(pack_bf16(p1a, p1b));
         }
 #pragma unroll
         for (uint32_t dm = 0; dm < 8; dm++) {
             uint32_t va[4];
             ldmatrix_x4_trans(va, vbase + v_row + (((2 * dm + v_c) ^ lr) << 4));
 #pragma unroll
-            for (int j = 0; j < int(ROW_NT); j++) {
-                mma16816(oacc[dm][j], va, pbh[j][0], pbh[j][1]);
-                mma16816(oacc[dm][j], va, pbl[j][0], pbl[j][1]);
-            }
+            for (int j = 0; j < int(ROW_NT); j++) mma16816(oacc[dm][j], va, pbh[j][0], pbh[j][1]);
         }
     }
     cp_async_wait<0>();
