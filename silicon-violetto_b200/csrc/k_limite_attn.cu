@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
 // decoder's kernel: with the remainders as well (the one-row kernel's way) the 8 x G columns make this kernel bound by
 // mma.sync's rate, 56 us of it for a global layer of 32 streams at 8k against 41 us of memory time. A column's row decides
 // what it sees: its own window start and `vis` mask. The four key-interleaved warps of a half meet in shared memory at the end.
-constexpr uint32_t ROW_WARPS = 8, ROW_STAGES = 3, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = 4 * TILE;
+constexpr uint32_t ROW_WARPS = 8, ROW_STAGES = 4, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = 4 * TILE;
 constexpr uint32_t ROW_STAGE_BYTES = 4 * 2 * TILE_BYTES;  // four tiles, K then V each
 constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // Q^T; eight rows of padding, which the second half's last ldmatrix.x4 reads beside its
                                                           // third n-tile and nobody uses
@@ -355,10 +355,12 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
     for (uint32_t i = 0; i < n_stages; i++) {
         cp_async_wait<ROW_STAGES - 2>();
         __syncthreads();  // (the first one also covers the Q^T stores)
-        if (i + ROW_STAGES - 1 < n_stages) issue(i + ROW_STAGES - 1);
-        cp_async_commit();
         const uint32_t i0 = begin + i * ROW_KEYS + kw * TILE;  // this warp's tile of the stage
-        if (i0 >= end) continue;
+        if (i0 >= end) {
+            if (i + ROW_STAGES - 1 < n_stages) issue(i + ROW_STAGES - 1);
+            cp_async_commit();
+            continue;
+        }
         const uint32_t kbase = ring + (i % ROW_STAGES) * ROW_STAGE_BYTES + kw * 2 * TILE_BYTES, vbase = kbase + TILE_BYTES;
 
         float sacc[ROW_NT][4];
@@ -437,6 +439,10 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
 #pragma unroll
             for (int j = 0; j < int(ROW_NT); j++) mma16816(oacc[dm][j], va, pbh[j][0], pbh[j][1]);
         }
+        // The next copies go out behind the arithmetic (their addresses take a page-table load each), into the stage every
+        // warp left before this iteration's barrier.
+        if (i + ROW_STAGES - 1 < n_stages) issue(i + ROW_STAGES - 1);
+        cp_async_commit();
     }
     cp_async_wait<0>();
 #pragma unroll
