@@ -558,6 +558,10 @@ def main():
                 out["reference_architecture_pass"] = limite_figure(E, local, args.ctx)
             except Exception as e:  # noqa: BLE001
                 out["reference_architecture_pass"] = {"error": str(e)[:300]}
+            try:  # the same target behind the reference's block drafter: trees of 8 rows drafted and verified
+                out["reference_pairing_pass"] = limite_figure(E, local, args.ctx, stream_counts=(1, 32), drafter=True)
+            except Exception as e:  # noqa: BLE001
+                out["reference_pairing_pass"] = {"error": str(e)[:300]}
     if world == 1 and not args.no_cpu:
         t_step, cores, em = cpu_reference(args, args.cpu_streams, args.cpu_steps)
         out["cpu_baseline"] = {"value": em / t_step, "unit": "tokens/s", "cores": cores, "kind": "port",
