@@ -323,12 +323,12 @@ void launch_limite_attn(const float* qkv, const uint32_t* meta, const uint32_t* 
     // over four warps.
     const bool by_tile = tiles && n_tiles && n >= 2 * n_tiles && G <= 6;  // (8 rows x G heads in its 48 columns)
     // Key splits, in whole rounds of 64 keys, at most LIMITE_MAX_SPLITS. The one-row kernel (three blocks an SM, which
-    // need not run in step): enough blocks to fill a B200's 148 SMs twice over. The rows' kernel (one block an SM): the count
+    // need not run in step): enough blocks to fill a B200's 148 SMs twice over. The rows' kernel (two blocks an SM): the count
     // that makes waves of blocks times a block's keys, plus a fixed part of about 128 keys' worth, least.
     const uint32_t most = std::max(1u, std::min(LIMITE_MAX_SPLITS, (max_keys + 63) / 64));
     uint32_t splits = 1;
     if (by_tile) {
-        const uint32_t units = std::max(n_tiles * kv.n_kv, 1u), slots = 148;
+        const uint32_t units = std::max(n_tiles * kv.n_kv, 1u), slots = 2 * 148;
         uint64_t best = ~0ull;
         for (uint32_t c = 1; c <= most; c++) {
             const uint32_t k = ((max_keys + c - 1) / c + 63) / 64 * 64, real = (max_keys + k - 1) / k;

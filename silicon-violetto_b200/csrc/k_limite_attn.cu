@@ -243,24 +243,24 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
 }
 
 // A tile of up to eight rows of one run per block -- a verified draft tree or a drafter's block, whose rows share their
-// cached keys: grid (tiles, kv heads, key splits), eight warps. The tile's rows x the kv head's G query heads are packed
+// cached keys: grid (tiles, kv heads, key splits), four warps, two blocks an SM. The tile's rows x the kv head's G query heads are packed
 // into the MMAs' query dimension (column p = G i + h is row i, head h: kernels.metal:896), at most 48 columns: warp
-// (half, kw) takes columns 24 half .. 24 half + 23 (three n-tiles) of key tiles kw, kw + 4, ... . The block walks the
-// union of its rows' keys (from the smallest window start; then the tile's eight slots) in stages of 64 keys that all
-// 256 threads copy into a ring once, so the cache is read once per tile of rows and a K or V fragment feeds three MMAs;
+// (half, kw) takes columns 24 half .. 24 half + 23 (three n-tiles) of key tiles kw, kw + 2, ... . The block walks the
+// union of its rows' keys (from the smallest window start; then the tile's eight slots) in stages of 32 keys that all
+// 128 threads copy into a ring once, so the cache is read once per tile of rows and a K or V fragment feeds three MMAs;
 // Q^T lies in shared memory and comes to the MMAs through ldmatrix. q and p go in as plain bf16 here, as in the plain
 // decoder's kernel: with the remainders as well (the one-row kernel's way) the 8 x G columns make this kernel bound by
 // mma.sync's rate, 56 us of it for a global layer of 32 streams at 8k against 41 us of memory time. A column's row decides
-// what it sees: its own window start and `vis` mask. The four key-interleaved warps of a half meet in shared memory at the end.
-constexpr uint32_t ROW_WARPS = 8, ROW_STAGES = 4, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = 4 * TILE;
-constexpr uint32_t ROW_STAGE_BYTES = 4 * 2 * TILE_BYTES;  // four tiles, K then V each
+// what it sees: its own window start and `vis` mask. The two key-interleaved warps of a half meet in shared memory at the end.
+constexpr uint32_t ROW_WARPS = 4, ROW_KW = ROW_WARPS / 2, ROW_STAGES = 4, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = ROW_KW * TILE;
+constexpr uint32_t ROW_STAGE_BYTES = ROW_KW * 2 * TILE_BYTES;  // a tile per key-interleaved warp, K then V each
 constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // Q^T; eight rows of padding, which the second half's last ldmatrix.x4 reads beside its
                                                           // third n-tile and nobody uses
 constexpr uint32_t ROW_OS = D + 4;
 constexpr uint32_t ROW_SMEM = ROW_STAGES * ROW_STAGE_BYTES + ROW_Q_BYTES;
 static_assert(ROW_WARPS * 8 * ROW_NT * ROW_OS * 4 <= ROW_SMEM, "the merge buffers must fit in the ring and the Q^T rows");
 
-__global__ void __launch_bounds__(ROW_WARPS * 32, 1)
+__global__ void __launch_bounds__(ROW_WARPS * 32, 2)
     attn_mma_rows_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ vis,
                          const uint32_t* __restrict__ tiles, const uint16_t* __restrict__ k_cache, const uint16_t* __restrict__ v_cache, const LimiteKv kv, uint32_t n_q,
                          uint32_t window, float scale_log2, uint32_t keys_per_split, uint32_t max_splits, float* part) {
@@ -311,14 +311,14 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
             c_mask[j][e] = real ? vis[t] : 0u;
         }
 
-    // Stage i: keys begin + 64 i ..; thread j copies chunk j % 16 of keys j / 16 + 16 u, K and V (a key past the split, or a
+    // Stage i: keys begin + ROW_KEYS i ..; thread j copies chunk j % 16 of keys j / 16 + 8 u, K and V (a key past the split, or a
     // slot past the tile's rows, which has no place in the cache, reads the tile's first row's own key: a valid address
     // that no column sees).
     auto issue = [&](uint32_t i) {
         const uint32_t chunk = threadIdx.x & 15;
 #pragma unroll
-        for (uint32_t u = 0; u < 4; u++) {
-            const uint32_t key = (threadIdx.x >> 4) + 16 * u, idx = begin + i * ROW_KEYS + key;
+        for (uint32_t u = 0; u < ROW_KEYS * 16 / (ROW_WARPS * 32); u++) {
+            const uint32_t key = (threadIdx.x >> 4) + ROW_WARPS * 2 * u, idx = begin + i * ROW_KEYS + key;
             const uint32_t kp = idx >= end ? p_run : idx < n_old ? lo_min + idx : p_run + (idx - n_old < T ? idx - n_old : 0u);
             const size_t src = size_t(kv_row_index(kv, slot, kvh, kp)) * D + chunk * 8;
             const uint32_t at = ring + (i % ROW_STAGES) * ROW_STAGE_BYTES + (key >> 4) * 2 * TILE_BYTES + (key & 15) * 256 + ((chunk ^ (key & 7)) << 4);
@@ -473,17 +473,17 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 1)
             }
         }
     __syncthreads();
-    // The four key-interleaved warps of a half added up per column: warp w takes columns w, w + 8, ... of the tile.
+    // The key-interleaved warps of a half added up per column: warp w takes columns w, w + ROW_WARPS, ... of the tile.
     const uint32_t d0 = 4 * lane;
     for (uint32_t pcol = warp; pcol < n_cols; pcol += ROW_WARPS) {
         const uint32_t hf = pcol / 24, lc = pcol % 24;
         float mm = -INFINITY;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; k++) mm = fmaxf(mm, os[((2 * k + hf) * 24 + lc) * ROW_OS + D]);
+        for (uint32_t k = 0; k < ROW_KW; k++) mm = fmaxf(mm, os[((2 * k + hf) * 24 + lc) * ROW_OS + D]);
         float ll = 0.0f;
         float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-        for (uint32_t k = 0; k < 4; k++) {
+        for (uint32_t k = 0; k < ROW_KW; k++) {
             const float* o = os + ((2 * k + hf) * 24 + lc) * ROW_OS;
             const float mk = o[D], wk = mk == -INFINITY ? 0.0f : fast_exp2(mk - mm);
             const float4 ok = *reinterpret_cast<const float4*>(o + d0);
