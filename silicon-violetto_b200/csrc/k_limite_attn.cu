@@ -315,12 +315,20 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
     // slot past the tile's rows, which has no place in the cache, reads the tile's first row's own key: a valid address
     // that no column sees).
     auto issue = [&](uint32_t i) {
-        const uint32_t chunk = threadIdx.x & 15;
+        const uint32_t chunk = threadIdx.x & 15, first = begin + i * ROW_KEYS, p_first = lo_min + first;
+        // A stage of cached keys that lie in one page, or in one stretch of the ring, takes one address and counts on.
+        const bool together = first + ROW_KEYS <= n_old && first + ROW_KEYS <= end &&
+                              (kv.is_global ? (p_first >> kv.page_shift) == ((p_first + ROW_KEYS - 1) >> kv.page_shift) : p_first % kv.ring + ROW_KEYS <= kv.ring);
+        const uint32_t row_first = together ? kv_row_index(kv, slot, kvh, p_first) : 0u;
 #pragma unroll
         for (uint32_t u = 0; u < ROW_KEYS * 16 / (ROW_WARPS * 32); u++) {
-            const uint32_t key = (threadIdx.x >> 4) + ROW_WARPS * 2 * u, idx = begin + i * ROW_KEYS + key;
-            const uint32_t kp = idx >= end ? p_run : idx < n_old ? lo_min + idx : p_run + (idx - n_old < T ? idx - n_old : 0u);
-            const size_t src = size_t(kv_row_index(kv, slot, kvh, kp)) * D + chunk * 8;
+            const uint32_t key = (threadIdx.x >> 4) + ROW_WARPS * 2 * u, idx = first + key;
+            uint32_t rowi = row_first + key;
+            if (!together) {
+                const uint32_t kp = idx >= end ? p_run : idx < n_old ? lo_min + idx : p_run + (idx - n_old < T ? idx - n_old : 0u);
+                rowi = kv_row_index(kv, slot, kvh, kp);
+            }
+            const size_t src = size_t(rowi) * D + chunk * 8;
             const uint32_t at = ring + (i % ROW_STAGES) * ROW_STAGE_BYTES + (key >> 4) * 2 * TILE_BYTES + (key & 15) * 256 + ((chunk ^ (key & 7)) << 4);
             cp_async16(at, k_cache + src);
             cp_async16(at + TILE_BYTES, v_cache + src);
