@@ -4,7 +4,8 @@
 // `draft_ctx`, `draft_embed`, `draft_conv`) and, for the block rows, the local-layer path of `qkv_post` and
 // `attn_verify` (kernels.metal:704-736, 749-801, 808-811): q and k rms-normed per head of 128 and turned on their first
 // 64 dims, keys and values in a ring per (layer, slot), a row seeing the `window` positions before it below its block,
-// and its whole block.
+// and its whole block. (That attention runs through k_limite_attn.cu's rows kernel when a kv head has at most six query
+// heads; the kernel here serves the others.)
 #include <cfloat>
 
 #include "kernels.h"

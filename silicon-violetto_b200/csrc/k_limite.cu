@@ -1,6 +1,6 @@
 // The reference's own architecture (engine/src/model.rs, engine/src/engine/encode.rs:99-192): what its layers do beyond
-// a plain decoder's, as small kernels of their own. The projections are the engine's streamed matmul with the matrix
-// scales and residual lambdas in its epilogue. Here: `mudd` (kernels.metal:1364-1407), the per-token work after the qkv
+// a plain decoder's, as small kernels of their own. The projections are the engine's streamed matmul and tensor-core GEMM
+// with the matrix scales and residual lambdas in their epilogues. Here: `mudd` (kernels.metal:1364-1407), the per-token work after the qkv
 // projection (`qkv_post` / `new_key`, :725-801,910-945: q/k RMS-norm per head of 128, RoPE on the first 64 dims of local
 // layers, gated value embeddings, K/V rounded into a ring per (local layer, slot) or into the paged pool of the global
 // layers, XSA directions, attention gates), the merge of the attention's key splits with XSA and the gate applied
