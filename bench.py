@@ -263,7 +263,7 @@ def spec_accept_figure(E, eng, hbm_peak):
             "frac_of_hbm_peak": nbytes / secs / 1e9 / hbm_peak, "mean_accepted": float(acc.mean())}
 
 
-def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_block=0, drafter=False):
+def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_block=0, drafter=False, int8=False):
     """The reference's own architecture at its shapes (48 layers, hidden 1280, 10 query / 2 kv heads of 128, FFN 3328,
     151 680 ids, bf16, random-init): decoding one token a step
     at 1, 8 and 32 streams over contexts advanced without computing them. With `drafter`, the reference's pairing: its
@@ -272,17 +272,19 @@ def limite_figure(E, local, ctx, steps=30, stream_counts=(1, 8, 32), keys_per_bl
     the target verifies it. Not BASELINE's metric: figures for the record."""
     from silicon_violetto_b200 import synth
     CACHE.mkdir(parents=True, exist_ok=True)
-    path = CACHE / "limite_48x1280_bf16.vlt"
+    # int8: the reference converter's default format (tools/convert.py:20): scale groups of 64, of 8 for the head.
+    kind = "int8" if int8 else "bf16"
+    path = CACHE / f"limite_48x1280_{kind}.vlt"
     done = path.with_suffix(".ok")
     if not done.exists():
-        synth.write_limite(path, n_layers=48, hidden=1280, n_kv=2, ffn=3328, vocab=151680, seed=0)
+        synth.write_limite(path, n_layers=48, hidden=1280, n_kv=2, ffn=3328, vocab=151680, seed=0, int8_group=64 if int8 else None)
         done.write_text("ok")
-    dpath = CACHE / "block_drafter_1280_bf16.vlt"
+    dpath = CACHE / f"block_drafter_1280_{kind}.vlt"
     if drafter and not dpath.with_suffix(".ok").exists():
-        synth.write_block_drafter(dpath, synth.block_drafter_state(1))
+        synth.write_block_drafter(dpath, synth.block_drafter_state(1), int8=int8)
         dpath.with_suffix(".ok").write_text("ok")
     what = "the block drafter's tree of up to 8 rows verified per stream and step" if drafter else "one token per stream and step"
-    out = {"workload": f"reference architecture 48 x 1280, bf16, ctx {ctx}, {what}"}
+    out = {"workload": f"reference architecture 48 x 1280, {'int8 in groups of 64 (head: 8)' if int8 else 'bf16'}, ctx {ctx}, {what}"}
     for n_s in stream_counts:
         cfg = E.EngineConfig(max_seqs=n_s, max_step_tokens=max(64, 8 * n_s), max_chunk=32, global_kv_tokens=n_s * (ctx + 512), max_seq_len=ctx + 512, max_head_rows=8 * n_s,
                              device_ordinal=local)
@@ -362,6 +364,7 @@ def main():
     ap.add_argument("--no-limite", action="store_true", help="skip the reference-architecture pass of the extras (it writes a 2 GB file first)")
     ap.add_argument("--limite-streams", default="1,8,32", help="stream counts of --only limite")
     ap.add_argument("--limite-drafter", action="store_true", help="--only limite: with the reference's block drafter loaded (tree drafts of up to 8 rows)")
+    ap.add_argument("--limite-int8", action="store_true", help="--only limite: int8 weights in the reference converter's default groups (64; the head 8)")
     ap.add_argument("--limite-keys", type=int, default=0, help="--only limite: keys per attention block (VltTuning.attn_keys_per_cta); 0 = the library's choice")
     ap.add_argument("--only", default="", help="'prefill', 'acceptance' or 'limite' (the reference's own architecture at its shapes, decoding): run that one pass alone and print its figure (not the bench line)")
     args = ap.parse_args()
@@ -417,7 +420,7 @@ def main():
             e1, _ = make_engine(E, path, 2, 64, 8, local)
             print(json.dumps(spec_accept_figure(E, e1, hbm_peak)))
         elif args.only == "limite":
-            print(json.dumps(limite_figure(E, local, args.ctx, min(args.steps, 30), [int(x) for x in args.limite_streams.split(",")], args.limite_keys, args.limite_drafter)))
+            print(json.dumps(limite_figure(E, local, args.ctx, min(args.steps, 30), [int(x) for x in args.limite_streams.split(",")], args.limite_keys, args.limite_drafter, args.limite_int8)))
         else:
             raise SystemExit(f"--only {args.only}: 'prefill', 'acceptance' or 'limite'")
         return

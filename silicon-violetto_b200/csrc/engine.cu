@@ -473,7 +473,7 @@ bool Engine::use_gemm(const Matrix& w, uint32_t n) const {
 bool Engine::gemm_fits(const Matrix& w, uint32_t n) const {
     const uint32_t min_rows = tuning.gemm_min_rows ? tuning.gemm_min_rows : 9;
     const bool grouped = w.int8 && w.group < w.k;
-    return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && !grouped;
+    return n >= min_rows && w.m % 128 == 0 && w.k % 64 == 0 && (!grouped || (w.group >= 8 && !(w.group & (w.group - 1))));  // (scale groups: powers of two from 8, as the reference's own int8 files have)
 }
 
 bool Engine::layer_carries(const Layer& l, uint32_t n) const {
@@ -798,9 +798,9 @@ void Engine::encode_forward_limite(uint32_t set, const Plan& p) {
     const float* cur = L.hist0.as<float>();
     const uint32_t* meta = s.meta.as<uint32_t>();
     const uint32_t* tin = st.in<uint32_t>(st.o_tin);
-    // From 9 tokens on, and if the projections' shapes and scales fit it (bf16, or int8 with one scale per row -- the
-    // reference's own int8 files have groups of 64 and stay on the streamed kernel), a layer takes the tensor-core GEMM:
-    // activations go in as bf16 copies, 1 / rms from a row pass or from the sums of squares the GEMM before left.
+    // From 9 tokens on, and if the projections' shapes and scales fit it (bf16, or int8 with one scale per row or per 64
+    // weights of a row, the reference's own int8 files), a layer takes the tensor-core GEMM: activations go in as bf16
+    // copies, 1 / rms from a row pass or from the sums of squares the GEMM before left.
     auto big_of = [&](uint32_t li) {
         const Layer& l = model.layers[li];
         return gemm_fits(l.qkv, n) && gemm_fits(l.o, n) && gemm_fits(l.gate_up, n) && gemm_fits(l.down, n) && md.n_heads / md.n_kv <= 8 && md.d % 128 == 0;

@@ -341,7 +341,21 @@ __global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 :
         const uint32_t grp = (warp - FIRST_CONV) / CONV_WPG, quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t row_off = row * 64, sw = (row >> 1) & 3, lane_base = tmem_base + ((quarter * 32) << 16) + a.tmem_a0;
         uint32_t r = grp % R, rph = (grp / R) & 1, c = grp % CA, cph = ((grp / CA) & 1) ^ 1;
+        // Scale groups along k (powers of two from 8; the reference's own int8 files: 64, and 8 for the head): a group's scale
+        // goes onto its weights here, q * s rounded once to bf16 (the reference multiplies in fp32: this adds what a bf16
+        // weight file's rounding adds); one scale per row goes onto the sums in the epilogue, exactly.
+        const bool grouped = a.m.group < a.m.k;
+        const uint32_t gshift = 31 - __clz(max(a.m.group, 1u));
+        const uint16_t* row_scales = grouped ? a.m.scales + size_t(row0 + row) * (a.m.k >> gshift) : nullptr;
         for (uint32_t i = grp; i < nkb; i += CONV_GROUPS) {
+            uint32_t sc8[8];  // the scale (twice, as a bf16 pair) of elements 8 e .. 8 e + 7 of this row's k block
+            if (grouped) {
+#pragma unroll
+                for (uint32_t e = 0; e < 8; e++) {
+                    const uint32_t sv = __ldg(row_scales + (((kb_begin + i) * BK + 8 * e) >> gshift));
+                    sc8[e] = sv | (sv << 16);
+                }
+            }
             ok = wait_or_abort(bar_rfull + 8 * r, rph, abort_flag) && wait_or_abort(bar_aempty + 8 * c, cph, abort_flag);
             if (!ok) break;
             if (lane == 0 && quarter == 3) PROBE(1, i);
@@ -356,6 +370,10 @@ __global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 :
                 cvt_i8x4(raw.y, v[8 * j + 2], v[8 * j + 3]);
                 cvt_i8x4(raw.z, v[8 * j + 4], v[8 * j + 5]);
                 cvt_i8x4(raw.w, v[8 * j + 6], v[8 * j + 7]);
+            }
+            if (grouped) {
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j++) asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v[j]) : "r"(sc8[j / 4]));
             }
             tmem_st32(lane_base + 32 * c, v);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -516,7 +534,7 @@ __global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 :
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // The warps that share a quarter of the TMEM lanes (rows) take groups of 16 tokens in turn.
             const uint32_t quarter = warp & 3, half = ew >> 2, r = quarter * 32 + lane;
-            const float scale = INT8 ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
+            const float scale = INT8 && m.group >= m.k ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;  // (scale groups went onto the weights)
             if (splits == 1) {  // no other block adds to this tile: straight out
                 for (uint32_t c0 = 16 * half; c0 < n_pad; c0 += 16 * (CONV_WARPS / 4)) {
                     float acc[16];
@@ -566,7 +584,7 @@ __global__ void __launch_bounds__(threads_of(CONV_WARPS), CONV_WARPS == 16 ? 1 :
             // An item: 32 rows x 8 tokens (half a group), so that two groups a block already keep all its warps busy.
             for (uint32_t item = ew; item < ch_count * 2 * (BM / 32); item += CONV_WARPS) {
                 const uint32_t lc = item / (2 * (BM / 32)), hf = (item / (BM / 32)) & 1, r = 32 * (item % (BM / 32)) + lane;
-                const float scale = INT8 ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;
+                const float scale = INT8 && m.group >= m.k ? bf16_to_f32(__ldg(m.scales + row0 + r)) : 1.0f;  // (scale groups went onto the weights)
                 float v[8];
 #pragma unroll
                 for (uint32_t j = 0; j < 8; j++) v[j] = 0.0f;
@@ -614,8 +632,8 @@ static GemmEntry gemm_entry(bool int8, uint32_t epi, bool paired = false) {
 }
 
 bool gemm_supported(const MatArgs& a) {
-    const bool grouped = a.int8 && a.group < a.k;
-    return a.n >= 1 && a.n <= 256 && a.m % gemm::BM == 0 && a.k % gemm::BK == 0 && !grouped && a.Xb != nullptr &&
+    const bool grouped = a.int8 && a.group < a.k;  // scale groups: powers of two from 8
+    return a.n >= 1 && a.n <= 256 && a.m % gemm::BM == 0 && a.k % gemm::BK == 0 && (!grouped || (a.group >= 8 && !(a.group & (a.group - 1)))) && a.Xb != nullptr &&
            (a.epi == EPI_RESID || a.epi == EPI_RAW || a.epi == EPI_HEAD_CAP || a.inv_in != nullptr || a.ssq_in != nullptr);
 }
 
