@@ -1206,21 +1206,29 @@ void Engine::load_block_drafter(const std::string& path) {
         f(d->inv, rows);
         f(d->attn, rows * n_q * D);
         f(d->act, rows * d->ffn);
-        // bf16 correction matrices also as copies of 256 rows (zero past the file's 192), which the GEMM's 128-row tiles take.
+        // The correction matrices also as copies of 256 rows (zero past the file's 192), which the GEMM's 128-row tiles take:
+        // bf16 weights, or int8 weights and behind them their scales.
         d->corr_stride = 2 * 128;
-        if (!d->layers.empty() && !d->layers[0].conv_corr[0].int8) {
-            const size_t one = size_t(d->corr_stride) * H * 2;
+        {
+            const size_t one = size_t(d->corr_stride) * H * 2 + 256;  // (room for either format, the scales 256-byte aligned)
             d->conv_pad.alloc(one * 4 * n_layers, false);  // (zeroed)
             for (uint32_t i = 0; i < n_layers; i++)
                 for (uint32_t c = 0; c < 4; c++) {
                     uint8_t* at = d->conv_pad.as<uint8_t>() + (size_t(i) * 4 + c) * one;
                     const Matrix& src = d->layers[i].conv_corr[c];
-                    if (src.int8) continue;
-                    VLT_CUDA(cudaMemcpy(at, src.w, size_t(BLOCK_CONV_KC) * H * 2, cudaMemcpyDeviceToDevice));
                     Matrix& g = d->layers[i].conv_corr_gemm[c];
+                    g = src;
                     g.w = at;
                     g.m = d->corr_stride;
-                    g.k = H;
+                    if (!src.int8) {
+                        VLT_CUDA(cudaMemcpy(at, src.w, size_t(BLOCK_CONV_KC) * H * 2, cudaMemcpyDeviceToDevice));
+                        continue;
+                    }
+                    const size_t w_bytes = size_t(d->corr_stride) * H, groups = H / src.group;
+                    uint8_t* sc = at + (w_bytes + 255) / 256 * 256;
+                    VLT_CUDA(cudaMemcpy(at, src.w, size_t(BLOCK_CONV_KC) * H, cudaMemcpyDeviceToDevice));
+                    VLT_CUDA(cudaMemcpy(sc, src.scales, size_t(BLOCK_CONV_KC) * groups * 2, cudaMemcpyDeviceToDevice));
+                    g.scales = reinterpret_cast<const uint16_t*>(sc);
                 }
         }
         f(d->corr, rows * d->corr_stride);

@@ -249,7 +249,7 @@ class Engine {
             Matrix qkv, o, gate_up, down;
             const float* conv_base[4];
             Matrix conv_corr[4];       // [192][H] as the file holds them
-            Matrix conv_corr_gemm[4];  // bf16 files: copies padded with zero rows to the GEMM's 128-row tiles (m = 0: none)
+            Matrix conv_corr_gemm[4];  // copies padded with zero rows to the GEMM's 128-row tiles
         };
         std::vector<DLayer> layers;
         std::vector<uint32_t> taps;
