@@ -32,6 +32,24 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+__device__ __forceinline__ void cluster_sync() { asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address of this block's shared-memory location `addr` in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
 // kernels.metal:704-715 `kv_row_of`, in rows of 128 elements.
 __device__ __forceinline__ uint32_t kv_row_index(const LimiteKv& kv, uint32_t slot, uint32_t g, uint32_t pos) {
     if (kv.is_global) {
@@ -140,11 +158,17 @@ __device__ __forceinline__ void row_finish(RowState& r) {
     }
 }
 
-// One row per block: grid (tokens, kv heads, key splits), four warps that share out the split's tiles.
+// One row per block: grid (tokens, kv heads, key splits), four warps that share out the split's tiles. CLUSTER: the
+// splits of a (token, kv head) are one thread-block cluster (at most 8 blocks); instead of writing partials for
+// merge_kernel, every block stores its heads' (m, l, o) into the first block's shared memory and that block adds them
+// up, applies XSA and the gate (kernels.metal:1314-1362 `attn_dec_reduce`) and writes the layer's attention output: no
+// second kernel, no round trip of the partials through L2.
+template <bool CLUSTER>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
     attn_mma_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ vis,
                     const uint16_t* __restrict__ k_cache, const uint16_t* __restrict__ v_cache, const LimiteKv kv, uint32_t n_q, uint32_t window, float scale_log2,
-                    uint32_t keys_per_split, uint32_t max_splits, float* part) {
+                    uint32_t keys_per_split, uint32_t max_splits, float* part, const float* __restrict__ vdir, const float* __restrict__ gates,
+                    const float* __restrict__ xsa, float* out, uint16_t* out_b) {
     pdl_start();
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t t = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z, warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, tq = lane & 3;
@@ -223,7 +247,15 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
     }
     __syncthreads();
     const uint32_t d0 = 4 * lane;
-    for (uint32_t h = warp; h < G; h += MMA_WARPS) {
+    float mm2[2], ll2[2];  // this warp's heads: warp and warp + MMA_WARPS
+    float4 oo2[2];
+#pragma unroll
+    for (uint32_t hi = 0; hi < 2; hi++) {
+        const uint32_t h = warp + hi * MMA_WARPS;
+        mm2[hi] = -INFINITY;
+        ll2[hi] = 0.0f;
+        oo2[hi] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (h >= G) continue;
         float mm = ms[h];
 #pragma unroll
         for (uint32_t k = 1; k < MMA_WARPS; k++) mm = fmaxf(mm, ms[k * 8 + h]);
@@ -236,9 +268,58 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
             ll += ls[k * 8 + h] * wk;
             oo.x += ok.x * wk; oo.y += ok.y * wk; oo.z += ok.z * wk; oo.w += ok.w * wk;
         }
-        float* pp = part + ((size_t(t) * n_q + kvh * G + h) * max_splits + sp) * PART;
-        if (lane == 0) { pp[0] = mm * LN2; pp[1] = ll; }  // (-inf stays -inf: an empty split)
-        *reinterpret_cast<float4*>(pp + 4 + d0) = oo;
+        mm2[hi] = mm;
+        ll2[hi] = ll;
+        oo2[hi] = oo;
+        if (!CLUSTER) {
+            float* pp = part + ((size_t(t) * n_q + kvh * G + h) * max_splits + sp) * PART;
+            if (lane == 0) { pp[0] = mm * LN2; pp[1] = ll; }  // (-inf stays -inf: an empty split)
+            *reinterpret_cast<float4*>(pp + 4 + d0) = oo;
+        }
+    }
+    if (!CLUSTER) return;
+    // The cluster's blocks (its ranks are the key splits) meet in the first one's shared memory, [rank][head][PART] over
+    // its stage ring: the first barrier says that every block is done with its ring, its own sums read out of it included;
+    // the second that every partial is where it will be added up. Every thread of every block reaches both.
+    const uint32_t rank = cluster_rank(), n_ranks = gridDim.z;
+    static_assert(8 * 8 * PART * 4 <= MMA_SMEM, "the cluster's partials must fit in the stage rings");
+    cluster_sync();
+#pragma unroll
+    for (uint32_t hi = 0; hi < 2; hi++) {
+        const uint32_t h = warp + hi * MMA_WARPS;
+        if (h >= G) continue;
+        const uint32_t dst = cluster_addr(smem_u32(smem) + (rank * 8 + h) * PART * 4, 0);
+        if (lane == 0) {
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(mm2[hi]) : "memory");
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + 4), "f"(ll2[hi]) : "memory");
+        }
+        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (4 + d0) * 4), "f"(oo2[hi].x), "f"(oo2[hi].y), "f"(oo2[hi].z), "f"(oo2[hi].w) : "memory");
+    }
+    cluster_sync();
+    if (rank != 0) return;
+    const float* recv = reinterpret_cast<const float*>(smem);
+#pragma unroll
+    for (uint32_t hi = 0; hi < 2; hi++) {
+        const uint32_t h = warp + hi * MMA_WARPS, hq = kvh * G + h;
+        if (h >= G) continue;
+        float mm = -INFINITY;
+        for (uint32_t k = 0; k < n_ranks; k++) mm = fmaxf(mm, recv[(k * 8 + h) * PART]);
+        float ll = 0.0f;
+        float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t k = 0; k < n_ranks; k++) {
+            const float* pk = recv + (k * 8 + h) * PART;
+            const float mk = pk[0], wk = mk == -INFINITY ? 0.0f : fast_exp2(mk - mm);
+            const float4 ok = *reinterpret_cast<const float4*>(pk + 4 + d0);
+            ll += pk[1] * wk;
+            oo.x += ok.x * wk; oo.y += ok.y * wk; oo.z += ok.z * wk; oo.w += ok.w * wk;
+        }
+        oo.x /= ll; oo.y /= ll; oo.z /= ll; oo.w /= ll;
+        const float4 vd = *reinterpret_cast<const float4*>(vdir + (size_t(t) * kv.n_kv + kvh) * D + d0);
+        const float pr = warp_sum(oo.x * vd.x + oo.y * vd.y + oo.z * vd.z + oo.w * vd.w);
+        const float xs = xsa[hq] * pr, gt = gates[size_t(t) * n_q + hq];
+        const float4 res = make_float4((oo.x - xs * vd.x) * gt, (oo.y - xs * vd.y) * gt, (oo.z - xs * vd.z) * gt, (oo.w - xs * vd.w) * gt);
+        *reinterpret_cast<float4*>(out + (size_t(t) * n_q + hq) * D + d0) = res;
+        if (out_b) *reinterpret_cast<uint2*>(out_b + (size_t(t) * n_q + hq) * D + d0) = make_uint2(pack_bf16(res.x, res.y), pack_bf16(res.z, res.w));  // for a tensor-core o projection
     }
 }
 
@@ -511,9 +592,35 @@ void launch_limite_attn_mma(const float* qkv, const uint32_t* meta, const uint32
                             const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, uint32_t n, uint32_t keys_per_split, uint32_t splits, float* part,
                             cudaStream_t s) {
     static PerDevice configured;
-    configured.once([] { VLT_CUDA(cudaFuncSetAttribute(limite::attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(limite::MMA_SMEM))); });
-    launch_pdl(limite::attn_mma_kernel, dim3(n, kv.n_kv, splits), limite::MMA_WARPS * 32, limite::MMA_SMEM, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window,
-               scale * limite::LOG2E, keys_per_split, splits, part);
+    configured.once([] { VLT_CUDA(cudaFuncSetAttribute(limite::attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(limite::MMA_SMEM))); });
+    launch_pdl(limite::attn_mma_kernel<false>, dim3(n, kv.n_kv, splits), limite::MMA_WARPS * 32, limite::MMA_SMEM, s, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q,
+               window, scale * limite::LOG2E, keys_per_split, splits, part, static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+               static_cast<const float*>(nullptr), static_cast<float*>(nullptr), static_cast<uint16_t*>(nullptr));
+}
+// The same with a (token, kv head)'s splits (at most 8) as a thread-block cluster that finishes the attention itself.
+void launch_limite_attn_cluster(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint16_t* k_cache, const uint16_t* v_cache,
+                                const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, const float* vdir, const float* gates, const float* xsa, uint32_t n,
+                                uint32_t keys_per_split, uint32_t splits, float* out, uint16_t* out_b, cudaStream_t s) {
+    if (splits < 1 || splits > 8) throw Error("internal: a cluster of 1..8 key splits");
+    static PerDevice configured;
+    configured.once([] { VLT_CUDA(cudaFuncSetAttribute(limite::attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(limite::MMA_SMEM))); });
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n, kv.n_kv, splits);
+    cfg.blockDim = dim3(limite::MMA_WARPS * 32);
+    cfg.dynamicSmemBytes = limite::MMA_SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    VLT_CUDA(cudaLaunchKernelEx(&cfg, limite::attn_mma_kernel<true>, qkv, meta, tin, vis, k_cache, v_cache, kv, n_q, window, scale * limite::LOG2E, keys_per_split, splits,
+                                static_cast<float*>(nullptr), vdir, gates, xsa, out, out_b));
+    launch_counter().fetch_add(1, std::memory_order_relaxed);
 }
 void launch_limite_attn_rows(const float* qkv, const uint32_t* meta, const uint32_t* tin, const uint32_t* vis, const uint32_t* tiles, const uint16_t* k_cache,
                              const uint16_t* v_cache, const LimiteKv& kv, uint32_t n_q, uint32_t window, float scale, uint32_t n_tiles, uint32_t keys_per_split,

@@ -30,10 +30,10 @@ def model(request, tmp_path_factory):
     return path, desc
 
 
-def _pair(path, **kw):
+def _pair(path, tuning=None, **kw):
     cfg = dict(max_seqs=3, max_step_tokens=64, max_chunk=32, global_kv_tokens=128 * 8, max_seq_len=512, max_head_rows=32)
     cfg.update(kw)
-    prod = E.Engine(path, E.EngineConfig(**cfg))
+    prod = E.Engine(path, E.EngineConfig(**cfg), tuning or E.Tuning())
     orc = oracle.Engine(path, max_seqs=cfg["max_seqs"], max_step_tokens=cfg["max_step_tokens"], max_chunk=cfg["max_chunk"], kv_tokens=cfg["global_kv_tokens"],
                         max_seq_len=cfg["max_seq_len"], max_head_rows=cfg["max_head_rows"])
     return prod, orc
@@ -67,9 +67,14 @@ def _step(prod, orc, runs, vocab_real, replay=None):
     return err
 
 
-def test_limite_forward_matches_the_oracle(model):
+@pytest.mark.parametrize("keys_per_block", [0, 64], ids=["the library's key splits", "splits of 64 keys"])
+def test_limite_forward_matches_the_oracle(model, keys_per_block):
+    """keys_per_block (VltTuning.attn_keys_per_cta) = 64: a row's keys in many splits whatever the context (the partials and
+    merge_kernel path as a long context takes it)."""
     path, desc = model
-    prod, orc = _pair(path)
+    if keys_per_block and desc["n_layers"] != 26:
+        pytest.skip("the override's path is covered on one model")
+    prod, orc = _pair(path, E.Tuning(attn_keys_per_cta=keys_per_block))
     assert (prod.desc.n_layers, prod.desc.d_model, prod.desc.head_dim, prod.desc.page_size) == (desc["n_layers"], desc["d"], 128, 128)
     vr = desc["vocab_real"]
     rng = np.random.default_rng(17)
@@ -201,4 +206,27 @@ def test_limite_rings_wrap_and_windows_slide(tmp_path):
     for _ in range(3):
         errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
     print(f"limite past the ring: logits max-abs errors, largest {max(errs):.1e}, last {errs[-1]:.1e}")
+    prod.close()
+
+
+def test_limite_many_streams_merge_their_key_splits_in_a_cluster(tmp_path):
+    """Fifty streams decoding a token each, one of them over a context of 300 tokens: with that many rows and so few keys
+    a row's key splits are one thread-block cluster that merges them in its first block's shared memory and finishes
+    the attention itself (the short streams' later splits are empty)."""
+    path = tmp_path / "limite_many.vlt"
+    desc = synth.write_limite(path, seed=7, n_layers=5, hidden=256, n_kv=1, ffn=512, vocab=640, vocab_real=630)
+    prod, orc = _pair(path, max_seqs=50, max_seq_len=512, global_kv_tokens=128 * 56, max_head_rows=64)
+    vr = desc["vocab_real"]
+    rng = np.random.default_rng(29)
+    seqs = [prod.new_seq() for _ in range(50)]
+    assert [orc.new_seq() for _ in range(50)] == seqs
+    prompt = rng.integers(0, vr, 300).astype(np.uint32)
+    for at in range(0, 288, 32):
+        _step(prod, orc, [(seqs[0], prompt[at:at + 32], E.Rows.NONE, False)], vr)
+    first = [(seqs[0], prompt[288:], E.Rows.LAST, False)] + [(s, rng.integers(0, vr, 1).astype(np.uint32), E.Rows.LAST, False) for s in seqs[1:]]
+    errs = [_step(prod, orc, first, vr)]
+    for _ in range(3):
+        errs.append(_step(prod, orc, [(s, [E.FEED_ROW], E.Rows.LAST, False) for s in seqs], vr))
+    assert prod.seq_len(seqs[0]) == orc.seq_len(seqs[0]) == 303
+    print(f"limite, 50 streams: logits max-abs errors {['%.1e' % e for e in errs]}")
     prod.close()
