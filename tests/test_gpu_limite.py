@@ -230,3 +230,37 @@ def test_limite_many_streams_merge_their_key_splits_in_a_cluster(tmp_path):
     assert prod.seq_len(seqs[0]) == orc.seq_len(seqs[0]) == 303
     print(f"limite, 50 streams: logits max-abs errors {['%.1e' % e for e in errs]}")
     prod.close()
+
+
+@pytest.mark.parametrize("hidden,n_kv", [(768, 6), (768, 2), (1024, 2), (768, 1), (896, 1), (1024, 1)],
+                         ids=["1 query head a kv head", "3", "4", "6", "7", "8"])
+def test_limite_attention_for_every_head_grouping(tmp_path, hidden, n_kv):
+    """The attention kernels pack a kv head's query heads into the MMAs' columns: every grouping from 1 to 8 heads a kv
+    head (6 fills the rows kernel's 48 columns with a tile of 8 rows; 7 and 8 keep a row per block) through a prompt chunk
+    of 32 rows, decoding, a verified chain of 8 rows with its compaction, and decoding again, on 4 layers (three local,
+    one global)."""
+    path = tmp_path / "limite_g.vlt"
+    desc = synth.write_limite(path, seed=11, n_layers=4, hidden=hidden, n_kv=n_kv, ffn=512, vocab=640, vocab_real=630)
+    prod, orc = _pair(path, max_seqs=2)
+    vr = desc["vocab_real"]
+    rng = np.random.default_rng(37)
+    a, b = prod.new_seq(), prod.new_seq()
+    assert (orc.new_seq(), orc.new_seq()) == (a, b)
+    errs = [_step(prod, orc, [(a, rng.integers(0, vr, 32).astype(np.uint32), E.Rows.LAST, False), (b, rng.integers(0, vr, 5).astype(np.uint32), E.Rows.LAST, False)], vr)]
+    errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    feed = orc.array("feed").reshape(-1, 16).copy()
+    tree = orc.array("tree").reshape(-1, 16).copy()
+    node = lambda depth, parent, sees: depth | parent << 8 | sees << 16
+    feed[a][1:8] = rng.integers(0, vr, 7)
+    tree[a][1:8] = [node(i, i - 1, (1 << (i + 1)) - 1) for i in range(1, 8)]
+    for w in (prod.debug_write, orc.write):
+        w("feed", 0, feed.reshape(-1))
+        w("tree", 0, tree.reshape(-1))
+    errs.append(_step(prod, orc, [(a, [E.FEED_ROW + i for i in range(8)], E.Rows.LAST, True), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    e = int(orc.array("emitted")[0])
+    prod.settle(a, 8 - e)
+    orc.settle(a, 8 - e)
+    assert prod.seq_len(a) == orc.seq_len(a)
+    errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    print(f"limite hidden {hidden}, {n_kv} kv heads: logits max-abs errors {['%.1e' % x for x in errs]}")
+    prod.close()
