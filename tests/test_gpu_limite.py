@@ -264,3 +264,23 @@ def test_limite_attention_for_every_head_grouping(tmp_path, hidden, n_kv):
     errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
     print(f"limite hidden {hidden}, {n_kv} kv heads: logits max-abs errors {['%.1e' % x for x in errs]}")
     prod.close()
+
+
+@pytest.mark.parametrize("group", [16, 32, 128, 256])
+def test_limite_int8_scale_groups_through_the_gemm(tmp_path, group):
+    """int8 projections with scale groups along k other than the converter's default 64 (the head stays at 8): steps of 40
+    and 12 rows take the tensor-core GEMM, whose converter warps put the groups' scales onto the weights -- groups within
+    a k block of 64 and groups that span two and four of them -- then decoding on the streamed kernel."""
+    path = tmp_path / "limite_q.vlt"
+    desc = synth.write_limite(path, seed=13, n_layers=4, hidden=256, n_kv=1, ffn=512, vocab=640, vocab_real=630, int8_group=group)
+    prod, orc = _pair(path, max_seqs=2)
+    vr = desc["vocab_real"]
+    rng = np.random.default_rng(41)
+    a, b = prod.new_seq(), prod.new_seq()
+    assert (orc.new_seq(), orc.new_seq()) == (a, b)
+    errs = [_step(prod, orc, [(a, rng.integers(0, vr, 30).astype(np.uint32), E.Rows.LAST, False), (b, rng.integers(0, vr, 10).astype(np.uint32), E.Rows.ALL, False)], vr)]
+    errs.append(_step(prod, orc, [(a, rng.integers(0, vr, 11).astype(np.uint32), E.Rows.ALL, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    errs.append(_step(prod, orc, [(a, [E.FEED_ROW], E.Rows.LAST, False), (b, [E.FEED_ROW], E.Rows.LAST, False)], vr))
+    print(f"limite int8 in groups of {group}: logits max-abs errors {['%.1e' % x for x in errs]}")
+    assert max(errs) <= 2e-2
+    prod.close()
