@@ -284,3 +284,22 @@ def test_limite_int8_scale_groups_through_the_gemm(tmp_path, group):
     print(f"limite int8 in groups of {group}: logits max-abs errors {['%.1e' % x for x in errs]}")
     assert max(errs) <= 2e-2
     prod.close()
+
+
+def test_limite_step_longer_than_a_gemm_launch(tmp_path):
+    """Ten streams' prompt chunks of 32 rows in one step of 320 tokens: the GEMMs run in blocks of 256 and 64 tokens (the
+    bf16 inputs and sums of squares a layer's last projection leaves for the next are indexed by the step's token, not
+    the block's), the attention in 40 tiles of 8 rows; then all ten decode."""
+    path = tmp_path / "limite_wide.vlt"
+    desc = synth.write_limite(path, seed=15, n_layers=5, hidden=256, n_kv=1, ffn=512, vocab=640, vocab_real=630)
+    prod, orc = _pair(path, max_seqs=10, max_step_tokens=320, global_kv_tokens=128 * 12, max_head_rows=32)
+    vr = desc["vocab_real"]
+    rng = np.random.default_rng(43)
+    seqs = [prod.new_seq() for _ in range(10)]
+    assert [orc.new_seq() for _ in range(10)] == seqs
+    errs = [_step(prod, orc, [(s, rng.integers(0, vr, 32).astype(np.uint32), E.Rows.LAST, False) for s in seqs], vr)]
+    for _ in range(2):
+        errs.append(_step(prod, orc, [(s, [E.FEED_ROW], E.Rows.LAST, False) for s in seqs], vr))
+    print(f"limite, a step of 320 tokens: logits max-abs errors {['%.1e' % x for x in errs]}")
+    assert max(errs) <= 2e-2
+    prod.close()
