@@ -324,22 +324,23 @@ __global__ void __launch_bounds__(MMA_WARPS * 32, 3)
 }
 
 // A tile of up to eight rows of one run per block -- a verified draft tree or a drafter's block, whose rows share their
-// cached keys: grid (tiles, kv heads, key splits), four warps, two blocks an SM. The tile's rows x the kv head's G query heads are packed
-// into the MMAs' query dimension (column p = G i + h is row i, head h: kernels.metal:896), at most 48 columns: warp
-// (half, kw) takes columns 24 half .. 24 half + 23 (three n-tiles) of key tiles kw, kw + 2, ... . The block walks the
-// union of its rows' keys (from the smallest window start; then the tile's eight slots) in stages of 32 keys that all
-// 128 threads copy into a ring once, so the cache is read once per tile of rows and a K or V fragment feeds three MMAs;
+// cached keys: grid (tiles, kv heads, key splits), six warps, two blocks an SM. The tile's rows x the kv head's G query
+// heads are packed into the MMAs' query dimension (column p = G i + h is row i, head h: kernels.metal:896), at most 48
+// columns: warp (grp, kw) takes columns 16 grp .. 16 grp + 15 (two n-tiles) of key tiles kw, kw + 2, ... . The block walks
+// the union of its rows' keys (from the smallest window start; then the tile's eight slots) in stages of 32 keys that all
+// its threads copy into a ring once, so the cache is read once per tile of rows and a K or V fragment feeds two MMAs;
 // Q^T lies in shared memory and comes to the MMAs through ldmatrix. q and p go in as plain bf16 here, as in the plain
 // decoder's kernel: with the remainders as well (the one-row kernel's way) the 8 x G columns make this kernel bound by
 // mma.sync's rate, 56 us of it for a global layer of 32 streams at 8k against 41 us of memory time. A column's row decides
-// what it sees: its own window start and `vis` mask. The two key-interleaved warps of a half meet in shared memory at the end.
-constexpr uint32_t ROW_WARPS = 4, ROW_KW = ROW_WARPS / 2, ROW_STAGES = 4, ROW_NT = 3, ROW_COLS = 2 * 8 * ROW_NT, ROW_KEYS = ROW_KW * TILE;
+// what it sees: its own window start and `vis` mask. The key-interleaved warps of a column group meet in shared memory at
+// the end. (Two groups of three n-tiles, 242 registers and 8 warps an SM, ran at the same speed.)
+constexpr uint32_t ROW_GROUPS = 3, ROW_NT = 2, ROW_CG = 8 * ROW_NT;  // column groups a block's warps split the 48 columns into; n-tiles and columns of one
+constexpr uint32_t ROW_KW = 2, ROW_WARPS = ROW_GROUPS * ROW_KW, ROW_STAGES = 4, ROW_COLS = ROW_GROUPS * ROW_CG, ROW_KEYS = ROW_KW * TILE;
 constexpr uint32_t ROW_STAGE_BYTES = ROW_KW * 2 * TILE_BYTES;  // a tile per key-interleaved warp, K then V each
-constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // Q^T; eight rows of padding, which the second half's last ldmatrix.x4 reads beside its
-                                                          // third n-tile and nobody uses
+constexpr uint32_t ROW_Q_BYTES = (ROW_COLS + 8) * D * 2;  // Q^T; eight rows of padding, which an odd n-tile count's last ldmatrix.x4 would read
 constexpr uint32_t ROW_OS = D + 4;
 constexpr uint32_t ROW_SMEM = ROW_STAGES * ROW_STAGE_BYTES + ROW_Q_BYTES;
-static_assert(ROW_WARPS * 8 * ROW_NT * ROW_OS * 4 <= ROW_SMEM, "the merge buffers must fit in the ring and the Q^T rows");
+static_assert(ROW_NT <= 4 && ROW_COLS == 48 && ROW_WARPS * 8 * ROW_NT * ROW_OS * 4 <= ROW_SMEM, "the merge buffers must fit in the ring and the Q^T rows");
 
 __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
     attn_mma_rows_kernel(const float* __restrict__ qkv, const uint32_t* __restrict__ meta, const uint32_t* __restrict__ tin, const uint32_t* __restrict__ vis,
@@ -348,7 +349,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
     pdl_start();
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t tile = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z, warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, tq = lane & 3;
-    const uint32_t half = warp & 1, kw = warp >> 1;
+    const uint32_t grp = warp % ROW_GROUPS, kw = warp / ROW_GROUPS;
     const uint32_t G = n_q / kv.n_kv;
     const uint32_t t0 = tiles[2 * tile], T = tiles[2 * tile + 1], n_cols = T * G;
     const uint32_t slot = meta[2 * t0], row0 = tin[2 * t0 + 1];
@@ -379,13 +380,13 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
         *reinterpret_cast<uint4*>(smem + ROW_STAGES * ROW_STAGE_BYTES + off) = hi;
     }
 
-    // This lane's columns: 24 half + 8 j + 2 tq (+ 1) of n-tile j; the window start and the mask of each one's row.
+    // This lane's columns: ROW_CG grp + 8 j + 2 tq (+ 1) of n-tile j; the window start and the mask of each one's row.
     uint32_t c_lo[ROW_NT][2], c_mask[ROW_NT][2];
 #pragma unroll
     for (int j = 0; j < int(ROW_NT); j++)
 #pragma unroll
         for (int e = 0; e < 2; e++) {
-            const uint32_t pcol = 24 * half + 8 * j + 2 * tq + e;
+            const uint32_t pcol = ROW_CG * grp + 8 * j + 2 * tq + e;
             const bool real = pcol < n_cols;
             const uint32_t t = t0 + (real ? pcol / G : 0);
             c_lo[j][e] = real ? lo_of(meta[2 * t + 1]) : 0xffffffffu;  // (a column that is none sees nothing)
@@ -402,8 +403,9 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
                               (kv.is_global ? (p_first >> kv.page_shift) == ((p_first + ROW_KEYS - 1) >> kv.page_shift) : p_first % kv.ring + ROW_KEYS <= kv.ring);
         const uint32_t row_first = together ? kv_row_index(kv, slot, kvh, p_first) : 0u;
 #pragma unroll
-        for (uint32_t u = 0; u < ROW_KEYS * 16 / (ROW_WARPS * 32); u++) {
+        for (uint32_t u = 0; u < (ROW_KEYS + ROW_WARPS * 2 - 1) / (ROW_WARPS * 2); u++) {
             const uint32_t key = (threadIdx.x >> 4) + ROW_WARPS * 2 * u, idx = first + key;
+            if (key >= ROW_KEYS) break;
             uint32_t rowi = row_first + key;
             if (!together) {
                 const uint32_t kp = idx >= end ? p_run : idx < n_old ? lo_min + idx : p_run + (idx - n_old < T ? idx - n_old : 0u);
@@ -425,9 +427,9 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
 
     const uint32_t lm = lane >> 3, lr = lane & 7;
     const uint32_t k_row = (8 * (lm & 1) + lr) * 256, k_c = lm >> 1, v_row = (8 * (lm >> 1) + lr) * 256, v_c = lm & 1;
-    // Q^T as B: one ldmatrix.x4 brings b0, b1 of n-tile jq and of jq + 1: matrix lm -> column 24 half + 8 (jq + (lm >> 1)) + lr,
+    // Q^T as B: one ldmatrix.x4 brings b0, b1 of n-tile jq and of jq + 1: matrix lm -> column ROW_CG grp + 8 (jq + (lm >> 1)) + lr,
     // chunk 2 ks + (lm & 1).
-    const uint32_t q_row = (24 * half + 8 * (lm >> 1) + lr) * 256, q_c = lm & 1;
+    const uint32_t q_row = (ROW_CG * grp + 8 * (lm >> 1) + lr) * 256, q_c = lm & 1;
 
     float oacc[8][ROW_NT][4];
     float m_run[ROW_NT][2], l_run[ROW_NT][2];
@@ -459,14 +461,16 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
             for (int e = 0; e < 4; e++) sacc[j][e] = 0.0f;
 #pragma unroll
         for (uint32_t ks = 0; ks < 8; ks++) {
-            uint32_t ka[4], qa[4], qb[4];
+            uint32_t ka[4];
             ldmatrix_x4(ka, kbase + k_row + (((2 * ks + k_c) ^ lr) << 4));
             const uint32_t qoff = q_row + (((2 * ks + q_c) ^ lr) << 4);
-            ldmatrix_x4(qa, q_hi + qoff);             // n-tiles 0 and 1
-            ldmatrix_x4(qb, q_hi + qoff + 16 * 256);  // n-tile 2 (and the rows after it: unused)
-            mma16816(sacc[0], ka, qa[0], qa[1]);
-            mma16816(sacc[1], ka, qa[2], qa[3]);
-            mma16816(sacc[2], ka, qb[0], qb[1]);
+#pragma unroll
+            for (uint32_t jq = 0; jq < ROW_NT; jq += 2) {  // (an odd count's last load also reads the eight rows after its n-tile: unused)
+                uint32_t qa[4];
+                ldmatrix_x4(qa, q_hi + qoff + jq * 8 * 256);
+                mma16816(sacc[jq], ka, qa[0], qa[1]);
+                if (jq + 1 < ROW_NT) mma16816(sacc[jq + 1 < ROW_NT ? jq + 1 : jq], ka, qa[2], qa[3]);
+            }
         }
         // Who sees what: nothing to do for a tile of cached keys inside every row's window.
         if (i0 + TILE > n_old || i0 + TILE > end || lo_min + i0 < lo_max) {
@@ -543,14 +547,14 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
             l_run[j][e] += __shfl_xor_sync(0xffffffffu, l_run[j][e], 16);
         }
     __syncthreads();  // the ring and the Q^T copies are free: every warp lays its columns' partials out in them
-    float* os = reinterpret_cast<float*>(smem);  // [warp][24 columns][ROW_OS]: o[128], then m and l
+    float* os = reinterpret_cast<float*>(smem);  // [warp][ROW_CG columns][ROW_OS]: o[128], then m and l
 #pragma unroll
     for (int j = 0; j < int(ROW_NT); j++)
 #pragma unroll
         for (int e = 0; e < 2; e++) {
             const uint32_t lc = 8 * j + 2 * tq + e;
-            if (24 * half + lc >= n_cols) continue;
-            float* o = os + (warp * 24 + lc) * ROW_OS;
+            if (ROW_CG * grp + lc >= n_cols) continue;
+            float* o = os + (warp * ROW_CG + lc) * ROW_OS;
             if (g == 0) {
                 o[D] = m_run[j][e];
                 o[D + 1] = l_run[j][e];
@@ -562,18 +566,18 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
             }
         }
     __syncthreads();
-    // The key-interleaved warps of a half added up per column: warp w takes columns w, w + ROW_WARPS, ... of the tile.
+    // The key-interleaved warps of a column group added up per column: warp w takes columns w, w + ROW_WARPS, ... of the tile.
     const uint32_t d0 = 4 * lane;
     for (uint32_t pcol = warp; pcol < n_cols; pcol += ROW_WARPS) {
-        const uint32_t hf = pcol / 24, lc = pcol % 24;
+        const uint32_t cg = pcol / ROW_CG, lc = pcol % ROW_CG;
         float mm = -INFINITY;
 #pragma unroll
-        for (uint32_t k = 0; k < ROW_KW; k++) mm = fmaxf(mm, os[((2 * k + hf) * 24 + lc) * ROW_OS + D]);
+        for (uint32_t k = 0; k < ROW_KW; k++) mm = fmaxf(mm, os[((ROW_GROUPS * k + cg) * ROW_CG + lc) * ROW_OS + D]);
         float ll = 0.0f;
         float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (uint32_t k = 0; k < ROW_KW; k++) {
-            const float* o = os + ((2 * k + hf) * 24 + lc) * ROW_OS;
+            const float* o = os + ((ROW_GROUPS * k + cg) * ROW_CG + lc) * ROW_OS;
             const float mk = o[D], wk = mk == -INFINITY ? 0.0f : fast_exp2(mk - mm);
             const float4 ok = *reinterpret_cast<const float4*>(o + d0);
             ll += o[D + 1] * wk;
