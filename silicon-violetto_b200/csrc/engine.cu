@@ -1230,6 +1230,7 @@ void Engine::load_block_drafter(const std::string& path) {
                     VLT_CUDA(cudaMemcpy(sc, src.scales, size_t(BLOCK_CONV_KC) * groups * 2, cudaMemcpyDeviceToDevice));
                     g.scales = reinterpret_cast<const uint16_t*>(sc);
                 }
+            VLT_CUDA(cudaDeviceSynchronize());  // (device-to-device copies on the legacy stream: done before the engine's own streams read them)
         }
         f(d->corr, rows * d->corr_stride);
         f(d->corr_inv, rows);
